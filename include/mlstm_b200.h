@@ -1,0 +1,95 @@
+/* C ABI of the B200 mLSTM kernel library (libmlstm_b200.so).
+ *
+ * Plain pointers and sizes only.  Every pointer is a DEVICE pointer unless stated otherwise; all
+ * tensors are contiguous row-major, [B, NH, S, D] for q, k, v, o, h and their gradients and
+ * [B, NH, S] for f, i, m, b and their gradients (the reference's hand-computed offsets,
+ * mlstm_matmul.py:46-55).  Every entry point only enqueues work on `stream` (a cudaStream_t passed
+ * as void*; NULL = the default stream) and returns at once with 0 or a negative MLSTM_E_* code; it
+ * never prints, aborts or synchronises.  The library is stateless: scratch memory is a caller-owned
+ * workspace whose size the matching *_workspace() function reports.  The first 256 bytes of a
+ * workspace hold a device status word that kernels set when they give up on an internal wait;
+ * mlstm_read_status() copies it to the host (this one call synchronises the stream).
+ */
+#ifndef MLSTM_B200_H
+#define MLSTM_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+#define MLSTM_DT_F32 0
+#define MLSTM_DT_F16 1
+#define MLSTM_DT_BF16 2
+
+/* status codes */
+#define MLSTM_OK 0
+#define MLSTM_E_ARG (-1)         /* null pointer, non-positive size, unknown dtype or flag      */
+#define MLSTM_E_SHAPE (-2)       /* shape outside what the kernels accept                        */
+#define MLSTM_E_ALIGN (-3)       /* a tensor pointer is not 16-byte aligned                      */
+#define MLSTM_E_UNSUPPORTED (-4) /* the tensor-core path was demanded for a case it cannot do    */
+#define MLSTM_E_WORKSPACE (-5)   /* workspace missing or too small                               */
+#define MLSTM_E_CUDA (-6)        /* a CUDA runtime or driver call failed                         */
+#define MLSTM_E_TIMEOUT (-7)     /* a kernel gave up on an internal wait (see mlstm_read_status) */
+
+/* flags */
+#define MLSTM_F_FORCE_SIMT 1 /* use the CUDA-core kernels even where the tensor-core path applies */
+#define MLSTM_F_FORCE_TC 2   /* fail with MLSTM_E_UNSUPPORTED instead of using the CUDA-core path */
+
+const char* mlstm_status_string(int status);
+
+/* 1 when the tcgen05 path handles this case (16-bit inputs, D in {64, 128, 256}), else 0. */
+int mlstm_tc_supported(int S, int D, int dtype);
+
+/* Parallel (matmul) forward.
+ * Replaces the launch in Triton_mLSTM.forward / mlstm_matmul (mlstm_matmul.py:121-129, 371-381) of
+ * mlstm_matmul_kernel (mlstm_matmul.py:37-101).
+ *   q, k, v [B,NH,S,D], f, i [B,NH,S] of `dtype`; h [B,NH,S,D] of `h_dtype` (MLSTM_DT_F32 as the
+ *   reference's Python path, or the input type); m, b [B,NH,S] fp32 (the reference's saved M, B).
+ */
+size_t mlstm_mm_fwd_workspace(int B, int NH, int S, int D, int dtype);
+int mlstm_mm_fwd(const void* q, const void* k, const void* v, const void* f, const void* i, void* h, float* m,
+                 float* b, void* workspace, size_t workspace_bytes, int B, int NH, int S, int D, int dtype,
+                 int h_dtype, int flags, void* stream);
+
+/* Parallel (matmul) backward.
+ * Replaces the three launches of Triton_mLSTM.backward (mlstm_matmul.py:383-405):
+ * mlstm_matmul_kernel_backward_db (:132-197), mlstm_matmul_kernel_backward (:200-316) and
+ * mlstm_matmul_kernel_df (:319-333).
+ *   dh, h of `h_dtype`; q, k, v, f, i and the outputs dq, dk, dv, df, di of `dtype`; m, b fp32 as
+ *   written by mlstm_mm_fwd.  df[..., 0] is exactly 0 (mlstm_matmul.py:316, 392).
+ */
+size_t mlstm_mm_bwd_workspace(int B, int NH, int S, int D, int dtype, int h_dtype);
+int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, const void* f, const void* i,
+                 const void* h, const float* m, const float* b, void* dq, void* dk, void* dv, void* df, void* di,
+                 void* workspace, size_t workspace_bytes, int B, int NH, int S, int D, int dtype, int h_dtype,
+                 int flags, void* stream);
+
+/* Forward scan with output gate: h = mLSTM(q, k, v, f, i) * silu(o).
+ * Replaces the four launches of mlstm_scan (mlstm_scan.py:281-327): stabilize_fi (:47-69),
+ * precompute_mlstm_triton_scan (:74-137), reduce_mlstm_triton (:143-195), mlstm_triton_scan
+ * (:200-278).  q, k, v, o [B,NH,S,D], f, i [B,NH,S] of `dtype`; h fp32 [B,NH,S,D].
+ */
+size_t mlstm_scan_fwd_workspace(int B, int NH, int S, int D, int dtype);
+int mlstm_scan_fwd(const void* q, const void* k, const void* v, const void* f, const void* i, const void* o,
+                   void* h, void* workspace, size_t workspace_bytes, int B, int NH, int S, int D, int dtype,
+                   int flags, void* stream);
+
+/* Single-head fp16 forward of the C++ driver.
+ * Replaces the launch mlstm_forward<64,16,128,16,8,8><<<S/64,128,smem>>>(Q,K,V,F,I,H,S)
+ * (cuda-src/mlstm_forward.cu:12-15, 235-238).  Q, K, V, H [S,D] half, F, I [S] half.
+ */
+size_t mlstm_forward_f16_workspace(unsigned S, unsigned D);
+int mlstm_forward_f16(const void* Q, const void* K, const void* V, const void* F, const void* I, void* H,
+                      unsigned S, unsigned D, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Copies the workspace's device status word to *host_status after synchronising `stream`.
+ * Returns MLSTM_OK, or MLSTM_E_TIMEOUT when the word is non-zero, or MLSTM_E_CUDA. */
+int mlstm_read_status(const void* workspace, int* host_status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLSTM_B200_H */

@@ -1,0 +1,127 @@
+"""GPU parity tests of the parallel (matmul) path, through the C ABI, against the CPU oracle.
+
+Tolerances (max |a-b| / max |b|): 1e-4 for the fp32 CUDA-core path (the reference computes IEEE fp32
+dots), 1e-2 for 16-bit tensor-core math (the reference's own check tolerance, utils.py:4).
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import mlstm_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-4
+TOL_16 = 1e-2
+
+
+@pytest.fixture(scope="module")
+def gc():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from tests import gpu_cases
+    return gpu_cases
+
+
+@pytest.mark.parametrize("name", ["matmul_s128_d32_f0.npz", "matmul_s192_d64_f3.npz"])
+def test_fp32_against_reference_golden(gc, golden_dir, name):
+    z = np.load(f"{golden_dir}/{name}")
+    x = {k: torch.from_numpy(z[k]) for k in ("q", "k", "v", "f", "i", "dh")}
+    h, m, b = gc.run_forward(x)
+    assert orc.max_abs_rel(h, torch.from_numpy(z["h"])) < TOL_F32
+    ok, frac = orc.check(h, torch.from_numpy(z["h"]))
+    assert ok, frac
+    grads = gc.run_backward(x, h, m, b)
+    for key, g in zip(("dq", "dk", "dv", "df", "di"), grads):
+        ref = torch.from_numpy(z[key]).clone()
+        if key == "df":
+            ref[..., 0] = 0.0
+            assert float(g[..., 0].abs().max()) == 0.0
+        assert orc.max_abs_rel(g, ref) < 2e-4, key
+
+
+@pytest.mark.parametrize("B,NH,S,D,f_mean", [
+    (1, 4, 2048, 64, 0.0),     # the reference demo / configuration 2
+    (2, 3, 200, 40, 3.0),      # ragged S, D not a tile multiple
+    (1, 2, 64, 8, -3.0),
+    (1, 1, 1, 16, 0.0),        # single step
+])
+def test_fp32_simt_forward_backward(gc, B, NH, S, D, f_mean):
+    x = gc.make_inputs(B, NH, S, D, torch.float32, f_mean=f_mean, seed=S + D)
+    h, m, b = gc.run_forward(x)
+    ef = gc.errors_forward(x, h, m, b)
+    assert ef["h"] < TOL_F32 and ef["m"] < 1e-5 and ef["b"] < TOL_F32, ef
+    eb = gc.errors_backward(x, gc.run_backward(x, h, m, b), torch.float32)
+    assert all(v < 3e-4 for v in eb.values()), eb
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D", [64, 128, 256])
+@pytest.mark.parametrize("S,f_mean", [(128, 0.0), (512, 3.0), (328, 0.0)])
+def test_tensor_core_forward_backward(gc, dtype, D, S, f_mean):
+    x = gc.make_inputs(1, 3, S, D, dtype, f_mean=f_mean, qkv_scale=D ** -0.5, seed=D + S)
+    flags = gc._lib.F_FORCE_TC
+    for h_dtype in (torch.float32, dtype):
+        h, m, b = gc.run_forward(x, h_dtype=h_dtype, flags=flags)
+        ef = gc.errors_forward(x, h, m, b)
+        assert ef["h"] < TOL_16 and ef["m"] < 1e-5 and ef["b"] < TOL_16, (h_dtype, ef)
+        eb = gc.errors_backward(x, gc.run_backward(x, h, m, b, flags=flags), h_dtype)
+        assert all(v < TOL_16 for v in eb.values()), (h_dtype, eb)
+
+
+def test_tensor_core_matches_simt_on_device(gc):
+    """Same 16-bit inputs through both kernel families."""
+    x = gc.make_inputs(2, 2, 640, 128, torch.bfloat16, f_mean=3.0, qkv_scale=128 ** -0.5, seed=3)
+    h1, m1, b1 = gc.run_forward(x, flags=gc._lib.F_FORCE_TC)
+    h2, m2, b2 = gc.run_forward(x, flags=gc._lib.F_FORCE_SIMT)
+    assert orc.max_abs_rel(h1, h2) < TOL_16
+    assert torch.equal(m1, m2)
+    g1 = gc.run_backward(x, h2, m2, b2, flags=gc._lib.F_FORCE_TC)
+    g2 = gc.run_backward(x, h2, m2, b2, flags=gc._lib.F_FORCE_SIMT)
+    for a, b_ in zip(g1, g2):
+        assert orc.max_abs_rel(a.float(), b_.float()) < TOL_16
+
+
+def test_autograd_function_matches_reference_api(gc):
+    """Triton_mLSTM.apply(q,k,v,f,i,SB,NUM_WARPS) + h.backward(dh), as the reference demo does."""
+    x = gc.make_inputs(1, 2, 256, 64, torch.float32, seed=11)
+    dev = torch.device("cuda", 0)
+    t = {n: x[n].to(dev).requires_grad_(True) for n in ("q", "k", "v", "f", "i")}
+    h = gc.PKG.Triton_mLSTM.apply(t["q"], t["k"], t["v"], t["f"], t["i"], 32, 4)
+    assert h.dtype == torch.float32
+    h.backward(x["dh"].to(dev))
+    ref = gc.oracle_backward(x, torch.float32)
+    for n, r in zip(("q", "k", "v", "f", "i"), ref):
+        assert t[n].grad.dtype == t[n].dtype
+        assert orc.max_abs_rel(t[n].grad, r) < 3e-4, n
+    h2 = gc.PKG.mlstm_matmul(*(t[n].detach() for n in ("q", "k", "v", "f", "i")), SB=32, num_warps=4)
+    assert torch.equal(h2, h.detach())
+
+
+def test_model_scale_slice_properties(gc):
+    """Configuration-4 shape per slice (S=4096, D=256, bf16) on a few slices: oracle parity on one
+    slice, and slice independence (each slice equals the same slice run alone)."""
+    x = gc.make_inputs(1, 3, 4096, 256, torch.bfloat16, f_mean=3.0, qkv_scale=256 ** -0.5, seed=0)
+    h, m, b = gc.run_forward(x, h_dtype=torch.bfloat16)
+    grads = gc.run_backward(x, h, m, b)
+    one = {k: v[:, 1:2].contiguous() for k, v in x.items()}
+    h1, m1, b1 = gc.run_forward(one, h_dtype=torch.bfloat16)
+    assert torch.equal(h1, h[:, 1:2])
+    g1 = gc.run_backward(one, h1, m1, b1)
+    for a, b_ in zip(g1, grads):
+        assert torch.equal(a, b_[:, 1:2])
+    ef = gc.errors_forward(one, h1, m1, b1)
+    assert ef["h"] < TOL_16, ef
+    eb = gc.errors_backward(one, g1, torch.bfloat16)
+    assert all(v < TOL_16 for v in eb.values()), eb
+
+
+def test_argument_errors(gc):
+    L = gc._lib.lib()
+    assert L.mlstm_mm_fwd(None, None, None, None, None, None, None, None, None, 0, 1, 1, 8, 8, 0, 0, 0, None) == -1
+    x = gc.make_inputs(1, 1, 64, 12, torch.float32)
+    with pytest.raises(gc._lib.MlstmError):
+        gc.run_forward(x)  # D not a multiple of 8
+    x = gc.make_inputs(1, 1, 64, 32, torch.float32)
+    with pytest.raises(gc._lib.MlstmError):
+        gc.run_forward(x, flags=gc._lib.F_FORCE_TC)  # fp32 has no tensor-core path

@@ -1,0 +1,83 @@
+"""GPU parity tests of the scan API and of the C++ driver's single-head fp16 forward."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import mlstm_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gc():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from tests import gpu_cases
+    return gpu_cases
+
+
+@pytest.mark.parametrize("name", ["scan_s96_d16_f0.npz", "scan_s64_d32_f3.npz"])
+def test_scan_against_reference_golden(gc, golden_dir, name):
+    z = np.load(f"{golden_dir}/{name}")
+    dev = torch.device("cuda", 0)
+    args = [torch.from_numpy(z[k]).to(dev) for k in ("q", "k", "v", "f", "i", "o")]
+    h = gc.PKG.mlstm_scan(*args, reduce_block_size=4, value_block_size=4)
+    assert h.dtype == torch.float32
+    assert orc.max_abs_rel(h, torch.from_numpy(z["h"])) < 1e-4
+    ok, frac = orc.check(h, torch.from_numpy(z["h"]))
+    assert ok, frac
+
+
+def test_scan_vs_recurrent_oracle(gc):
+    """The recurrent oracle (one step per time index) on a seeded case with retention-biased gates."""
+    x = gc.make_inputs(1, 2, 256, 64, torch.float32, f_mean=3.0, seed=21, with_o=True)
+    dev = torch.device("cuda", 0)
+    h = gc.PKG.mlstm_scan(*(x[n].to(dev) for n in ("q", "k", "v", "f", "i", "o")))
+    ref = orc.scan_forward(x["q"], x["k"], x["v"], x["f"], x["i"], x["o"])
+    assert orc.max_abs_rel(h, ref) < 1e-4
+
+
+def test_scan_config3_shape_properties(gc):
+    """Configuration 3 (B=1, NH=4, S=2048, D=1024, fp32): the parallel oracle times silu(o) on one
+    head, and the reference's own tolerance."""
+    x = gc.make_inputs(1, 4, 2048, 1024, torch.float32, seed=0, with_o=True)
+    dev = torch.device("cuda", 0)
+    h = gc.PKG.mlstm_scan(*(x[n].to(dev) for n in ("q", "k", "v", "f", "i", "o")), reduce_block_size=4,
+                          value_block_size=4).cpu()
+    hd = 2
+    ref = orc.matmul_forward(*(x[n][:, hd] for n in ("q", "k", "v", "f", "i")), dtype=torch.float32)
+    ref = ref * torch.nn.functional.silu(x["o"][:, hd])
+    assert orc.max_abs_rel(h[:, hd], ref) < 1e-3
+    ok, frac = orc.check(h[:, hd], ref)
+    assert ok, frac
+
+
+def test_scan_argument_checks(gc):
+    x = gc.make_inputs(1, 1, 64, 16, torch.float32, with_o=True)
+    dev = torch.device("cuda", 0)
+    args = [x[n].to(dev) for n in ("q", "k", "v", "f", "i", "o")]
+    with pytest.raises(ValueError):
+        gc.PKG.mlstm_scan(*args, reduce_block_size=3)
+    with pytest.raises(ValueError):
+        gc.PKG.mlstm_scan(*args, value_block_size=0)
+
+
+@pytest.mark.parametrize("name", ["cpp_forward_seed100_s640_d128.npz", "cpp_forward_seed100_s128_d128.npz"])
+def test_cpp_forward_against_reference_golden(gc, golden_dir, name):
+    """mlstm_forward_f16 on the reference demo's own inputs (srand(100) recipe) against the output of
+    the reference's mlstmCpu; the reference's comparator counts |a - b| > 0.01."""
+    z = np.load(f"{golden_dir}/{name}")
+    dev = torch.device("cuda", 0)
+    Q, K, V, F, I = (torch.from_numpy(z[k]).to(dev) for k in ("Q", "K", "V", "F", "I"))
+    S, D = Q.shape
+    H = torch.empty_like(Q)
+    L = gc._lib.lib()
+    ws = gc._lib.workspace(L.mlstm_forward_f16_workspace(S, D), dev)
+    rc = L.mlstm_forward_f16(Q.data_ptr(), K.data_ptr(), V.data_ptr(), F.data_ptr(), I.data_ptr(), H.data_ptr(),
+                             S, D, ws.data_ptr(), ws.numel(), gc._lib.stream_ptr(dev))
+    assert rc == 0
+    gc._lib.read_status(ws, dev, "mlstm_forward_f16")
+    diff = (H.float().cpu() - torch.from_numpy(z["H"]).float()).abs()
+    assert int((diff > 0.01).sum()) == 0, float(diff.max())

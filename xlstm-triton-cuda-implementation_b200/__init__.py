@@ -1,0 +1,13 @@
+"""B200-native mLSTM kernels behind the reference project's operator API.
+
+    from <this package>.mlstm_matmul import Triton_mLSTM, mlstm_matmul
+    from <this package>.mlstm_scan import mlstm_scan
+
+The compute lives in libmlstm_b200.so (CUDA for sm_100a, C ABI in include/mlstm_b200.h), loaded on
+first use.  There is no CPU, PyTorch or Triton fallback: without the built library calls raise.
+"""
+from . import _lib
+from .mlstm_matmul import Triton_mLSTM, mlstm_matmul, mlstm_matmul_backward, mlstm_matmul_forward
+from .mlstm_scan import mlstm_scan
+
+__all__ = ["Triton_mLSTM", "mlstm_matmul", "mlstm_matmul_forward", "mlstm_matmul_backward", "mlstm_scan", "_lib"]

@@ -1,0 +1,254 @@
+// extern "C" entry points of libmlstm_b200.so (declared in include/mlstm_b200.h): argument checks,
+// workspace carving and the launch sequences.  Nothing here allocates or synchronises.
+#include <cmath>
+
+#include "mlstm_common.cuh"
+
+namespace mlstm {
+namespace {
+
+constexpr size_t WS_ALIGN = 256;
+inline size_t al(size_t x) { return (x + WS_ALIGN - 1) / WS_ALIGN * WS_ALIGN; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline size_t esize(int dt) { return dt == MLSTM_DT_F32 ? 4 : 2; }
+inline bool dtype_ok(int dt) { return dt == MLSTM_DT_F32 || dt == MLSTM_DT_F16 || dt == MLSTM_DT_BF16; }
+
+struct Carver {
+    uint8_t* base;
+    size_t off = 0;
+    explicit Carver(void* b) : base(static_cast<uint8_t*>(b)) {}
+    template <typename T>
+    T* take(size_t bytes) {
+        T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+        off += al(bytes);
+        return p;
+    }
+};
+
+struct FwdWs {
+    int* status;
+    float *ga, *gAn, *m, *b;
+    size_t bytes;
+};
+// with_mb: also carve m and b (entry points whose caller does not pass them)
+FwdWs carve_fwd(void* ws, int BH, int S, bool with_mb) {
+    Carver c(ws);
+    FwdWs w{};
+    const size_t vec = static_cast<size_t>(BH) * round_up(S, TILE) * sizeof(float);
+    w.status = c.take<int>(WS_ALIGN);
+    w.ga = c.take<float>(vec);
+    w.gAn = c.take<float>(vec);
+    if (with_mb) {
+        w.m = c.take<float>(static_cast<size_t>(BH) * S * sizeof(float));
+        w.b = c.take<float>(static_cast<size_t>(BH) * S * sizeof(float));
+    }
+    w.bytes = c.off;
+    return w;
+}
+
+struct BwdWs {
+    int* status;
+    float *ga, *gAn, *gB, *g, *dI, *R;
+    void* dh16;
+    size_t bytes;
+};
+BwdWs carve_bwd(void* ws, int BH, int S, int D, bool need_dh16) {
+    Carver c(ws);
+    BwdWs w{};
+    const size_t vec = static_cast<size_t>(BH) * round_up(S, TILE) * sizeof(float);
+    w.status = c.take<int>(WS_ALIGN);
+    w.ga = c.take<float>(vec);
+    w.gAn = c.take<float>(vec);
+    w.gB = c.take<float>(vec);
+    w.g = c.take<float>(vec);
+    w.dI = c.take<float>(vec);
+    w.R = c.take<float>(vec);
+    w.dh16 = need_dh16 ? c.take<uint8_t>(static_cast<size_t>(BH) * S * D * 2) : nullptr;
+    w.bytes = c.off;
+    return w;
+}
+
+int check_dims(int B, int NH, int S, int D) {
+    if (B <= 0 || NH <= 0 || S <= 0 || D <= 0) return MLSTM_E_ARG;
+    if (static_cast<long long>(B) * NH > 65535) return MLSTM_E_SHAPE;
+    if (D % 8 != 0) return MLSTM_E_SHAPE;  // rows must stay 16-byte aligned for vector access
+    if (static_cast<long long>(B) * NH * round_up(S, TILE) > 0x7fffffffLL / 32) return MLSTM_E_SHAPE;
+    return MLSTM_OK;
+}
+
+bool use_tc(int S, int D, int dtype, int flags, int* rc) {
+    *rc = MLSTM_OK;
+    if ((flags & MLSTM_F_FORCE_SIMT) && (flags & MLSTM_F_FORCE_TC)) {
+        *rc = MLSTM_E_ARG;
+        return false;
+    }
+    const bool can = tc_supported(S, D, dtype);
+    if (flags & MLSTM_F_FORCE_TC) {
+        if (!can) *rc = MLSTM_E_UNSUPPORTED;
+        return can;
+    }
+    return can && !(flags & MLSTM_F_FORCE_SIMT);
+}
+
+int run_pass(bool tc, int mode, const PassParams& p, int in_dt, int out_dt, cudaStream_t st) {
+    return tc ? launch_pass_tc(mode, p, in_dt, out_dt, st) : launch_pass_simt(mode, p, in_dt, out_dt, st);
+}
+
+int forward_impl(const void* q, const void* k, const void* v, const void* f, const void* i, const void* o, void* h,
+                 float* m, float* b, const FwdWs& w, int BH, int S, int D, int dtype, int h_dtype, int flags,
+                 cudaStream_t st) {
+    int rc;
+    const bool tc = use_tc(S, D, dtype, flags, &rc);
+    if (rc != MLSTM_OK) return rc;
+    const int Spad = round_up(S, TILE);
+    if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
+    if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, m, BH, S, Spad, dtype, st)) != MLSTM_OK) return rc;
+    PassParams p{};
+    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D;
+    p.X = q; p.Y = k; p.Z = v;
+    p.row_e = w.gAn; p.col_e = w.ga;
+    p.er_add = -0.5f * log2f(static_cast<float>(D));
+    p.out = h; p.m = m; p.b_out = b; p.ogate = o;
+    p.status = w.status;
+    return run_pass(tc, FWD, p, dtype, h_dtype, st);
+}
+
+}  // namespace
+}  // namespace mlstm
+
+using namespace mlstm;
+
+extern "C" {
+
+const char* mlstm_status_string(int s) {
+    switch (s) {
+        case MLSTM_OK: return "ok";
+        case MLSTM_E_ARG: return "bad argument (null pointer, non-positive size, unknown dtype or flag)";
+        case MLSTM_E_SHAPE: return "shape not accepted (D must be a multiple of 8; B*NH <= 65535)";
+        case MLSTM_E_ALIGN: return "tensor pointer not 16-byte aligned";
+        case MLSTM_E_UNSUPPORTED: return "tensor-core path demanded for an unsupported case";
+        case MLSTM_E_WORKSPACE: return "workspace missing or too small";
+        case MLSTM_E_CUDA: return "CUDA runtime or driver call failed";
+        case MLSTM_E_TIMEOUT: return "a kernel gave up on an internal wait";
+    }
+    return "unknown status";
+}
+
+int mlstm_tc_supported(int S, int D, int dtype) { return tc_supported(S, D, dtype) ? 1 : 0; }
+
+size_t mlstm_mm_fwd_workspace(int B, int NH, int S, int D, int dtype) {
+    (void)dtype;
+    if (check_dims(B, NH, S, D) != MLSTM_OK) return 0;
+    return carve_fwd(nullptr, B * NH, S, false).bytes;
+}
+
+int mlstm_mm_fwd(const void* q, const void* k, const void* v, const void* f, const void* i, void* h, float* m, float* b,
+                 void* workspace, size_t workspace_bytes, int B, int NH, int S, int D, int dtype, int h_dtype, int flags,
+                 void* stream) {
+    if (!q || !k || !v || !f || !i || !h || !m || !b) return MLSTM_E_ARG;
+    if (!dtype_ok(dtype) || (h_dtype != MLSTM_DT_F32 && h_dtype != dtype)) return MLSTM_E_ARG;
+    int rc = check_dims(B, NH, S, D);
+    if (rc != MLSTM_OK) return rc;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(h)) return MLSTM_E_ALIGN;
+    FwdWs w = carve_fwd(workspace, B * NH, S, false);
+    if (!workspace || workspace_bytes < w.bytes || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
+    return forward_impl(q, k, v, f, i, nullptr, h, m, b, w, B * NH, S, D, dtype, h_dtype, flags,
+                        static_cast<cudaStream_t>(stream));
+}
+
+size_t mlstm_mm_bwd_workspace(int B, int NH, int S, int D, int dtype, int h_dtype) {
+    if (check_dims(B, NH, S, D) != MLSTM_OK) return 0;
+    return carve_bwd(nullptr, B * NH, S, D, dtype != MLSTM_DT_F32 && h_dtype != dtype).bytes;
+}
+
+int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, const void* f, const void* i, const void* h,
+                 const float* m, const float* b, void* dq, void* dk, void* dv, void* df, void* di, void* workspace,
+                 size_t workspace_bytes, int B, int NH, int S, int D, int dtype, int h_dtype, int flags, void* stream) {
+    if (!dh || !q || !k || !v || !f || !i || !h || !m || !b || !dq || !dk || !dv || !df || !di) return MLSTM_E_ARG;
+    if (!dtype_ok(dtype) || (h_dtype != MLSTM_DT_F32 && h_dtype != dtype)) return MLSTM_E_ARG;
+    int rc = check_dims(B, NH, S, D);
+    if (rc != MLSTM_OK) return rc;
+    if (!aligned16(dh) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(h) || !aligned16(dq) ||
+        !aligned16(dk) || !aligned16(dv))
+        return MLSTM_E_ALIGN;
+    const int BH = B * NH, Spad = round_up(S, TILE);
+    const bool need16 = dtype != MLSTM_DT_F32 && h_dtype != dtype;
+    BwdWs w = carve_bwd(workspace, BH, S, D, need16);
+    if (!workspace || workspace_bytes < w.bytes || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
+    const bool tc = use_tc(S, D, dtype, flags, &rc);
+    if (rc != MLSTM_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
+    if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, nullptr, BH, S, Spad, dtype, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_bwd_prep(h, dh, b, m, w.gAn, w.gB, w.g, w.dh16, BH, S, Spad, D, h_dtype, dtype, st)) != MLSTM_OK)
+        return rc;
+    const void* dhp = need16 ? w.dh16 : dh;  // dh in the element type of q, k, v
+
+    PassParams p{};
+    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status;
+    // dQ = ((dH V^T + g_r) * decay) K
+    p.X = dhp; p.Y = v; p.Z = k;
+    p.row_e = w.gB; p.row_g = w.g; p.col_e = w.ga; p.col_g = nullptr;
+    p.out = dq; p.dot_src = q; p.dot_out = w.R;
+    if ((rc = run_pass(tc, DQ, p, dtype, dtype, st)) != MLSTM_OK) return rc;
+    // dK = ((V dH^T + g_c) * decay)  Q
+    p.X = v; p.Y = dhp; p.Z = q;
+    p.row_e = w.ga; p.row_g = nullptr; p.col_e = w.gB; p.col_g = w.g;
+    p.out = dk; p.dot_src = k; p.dot_out = w.dI;
+    if ((rc = run_pass(tc, DK, p, dtype, dtype, st)) != MLSTM_OK) return rc;
+    // dV = ((K Q^T) * decay / n) dH
+    p.X = k; p.Y = q; p.Z = dhp;
+    p.col_g = nullptr;
+    p.out = dv; p.dot_src = nullptr; p.dot_out = nullptr;
+    if ((rc = run_pass(tc, DV, p, dtype, dtype, st)) != MLSTM_OK) return rc;
+    return launch_df(f, w.dI, w.R, df, di, BH, S, Spad, dtype, st);
+}
+
+size_t mlstm_scan_fwd_workspace(int B, int NH, int S, int D, int dtype) {
+    (void)dtype;
+    if (check_dims(B, NH, S, D) != MLSTM_OK) return 0;
+    return carve_fwd(nullptr, B * NH, S, true).bytes;
+}
+
+int mlstm_scan_fwd(const void* q, const void* k, const void* v, const void* f, const void* i, const void* o, void* h,
+                   void* workspace, size_t workspace_bytes, int B, int NH, int S, int D, int dtype, int flags,
+                   void* stream) {
+    if (!q || !k || !v || !f || !i || !o || !h) return MLSTM_E_ARG;
+    if (!dtype_ok(dtype)) return MLSTM_E_ARG;
+    int rc = check_dims(B, NH, S, D);
+    if (rc != MLSTM_OK) return rc;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(h)) return MLSTM_E_ALIGN;
+    FwdWs w = carve_fwd(workspace, B * NH, S, true);
+    if (!workspace || workspace_bytes < w.bytes || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
+    return forward_impl(q, k, v, f, i, o, h, w.m, w.b, w, B * NH, S, D, dtype, MLSTM_DT_F32, flags,
+                        static_cast<cudaStream_t>(stream));
+}
+
+size_t mlstm_forward_f16_workspace(unsigned S, unsigned D) {
+    if (check_dims(1, 1, static_cast<int>(S), static_cast<int>(D)) != MLSTM_OK) return 0;
+    return carve_fwd(nullptr, 1, static_cast<int>(S), true).bytes;
+}
+
+int mlstm_forward_f16(const void* Q, const void* K, const void* V, const void* F, const void* I, void* H, unsigned S,
+                      unsigned D, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!Q || !K || !V || !F || !I || !H) return MLSTM_E_ARG;
+    if (S > 0x7fffffffu || D > 0x7fffffffu) return MLSTM_E_ARG;
+    int rc = check_dims(1, 1, static_cast<int>(S), static_cast<int>(D));
+    if (rc != MLSTM_OK) return rc;
+    if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(H)) return MLSTM_E_ALIGN;
+    FwdWs w = carve_fwd(workspace, 1, static_cast<int>(S), true);
+    if (!workspace || workspace_bytes < w.bytes || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
+    return forward_impl(Q, K, V, F, I, nullptr, H, w.m, w.b, w, 1, static_cast<int>(S), static_cast<int>(D), MLSTM_DT_F16,
+                        MLSTM_DT_F16, 0, static_cast<cudaStream_t>(stream));
+}
+
+int mlstm_read_status(const void* workspace, int* host_status, void* stream) {
+    if (!workspace || !host_status) return MLSTM_E_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaStreamSynchronize(st) != cudaSuccess) return MLSTM_E_CUDA;
+    if (cudaMemcpy(host_status, workspace, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return MLSTM_E_CUDA;
+    return *host_status == 0 ? MLSTM_OK : MLSTM_E_TIMEOUT;
+}
+
+}  // extern "C"

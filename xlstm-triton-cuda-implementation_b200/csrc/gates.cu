@@ -1,0 +1,247 @@
+// Gate passes of the parallel mLSTM: everything that is O(S) or O(S*D) per slice and needs no
+// contraction.  They take the place of the in-kernel log-sigmoid cumulative sums and running
+// maxima of the reference (mlstm_matmul.py:59, 73-84; cuda-src/gpu_utils.cuh:125-144), of its
+// db kernel (mlstm_matmul.py:132-197, reduced here to a row dot product by the identity
+// sum_c C~_rc dC_rc = n_r (dh_r . h_r)) and of its dF kernel (mlstm_matmul.py:319-333).
+#include "mlstm_common.cuh"
+
+namespace mlstm {
+namespace {
+
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr int SCAN_THREADS = 1024;
+
+// Inclusive block scans over SCAN_THREADS elements (one per thread) with a running carry.
+__device__ __forceinline__ double block_scan_add(double x, double* warp_tot, double& carry_smem_view) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        double y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+    }
+    if (lane == 31) warp_tot[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+        double t = warp_tot[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            double y = __shfl_up_sync(0xffffffffu, t, o);
+            if (lane >= o) t += y;
+        }
+        warp_tot[lane] = t;
+    }
+    __syncthreads();
+    const double before = (warp > 0 ? warp_tot[warp - 1] : 0.0) + carry_smem_view;
+    const double total = warp_tot[31];
+    __syncthreads();
+    if (threadIdx.x == 0) carry_smem_view += total;
+    __syncthreads();
+    return x + before;
+}
+
+__device__ __forceinline__ float block_scan_max(float x, float* warp_tot, float& carry_smem_view) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        float y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x = fmaxf(x, y);
+    }
+    if (lane == 31) warp_tot[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+        float t = warp_tot[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            float y = __shfl_up_sync(0xffffffffu, t, o);
+            if (lane >= o) t = fmaxf(t, y);
+        }
+        warp_tot[lane] = t;
+    }
+    __syncthreads();
+    const float before = fmaxf(warp > 0 ? warp_tot[warp - 1] : -INFINITY, carry_smem_view);
+    const float total = warp_tot[31];
+    __syncthreads();
+    if (threadIdx.x == 0) carry_smem_view = fmaxf(carry_smem_view, total);
+    __syncthreads();
+    return fmaxf(x, before);
+}
+
+// One block per slice.  ga = a*log2e, gAn = -A*log2e, m = F + A with F = cumsum(logsigmoid f),
+// a = i - F, A = running maximum of a.  The cumulative sum is carried in double so that a_c - A_r
+// keeps fp32 accuracy for long sequences.  Padding (t >= S): ga = -inf (a padded column contributes
+// exactly zero), gAn = 0.  m may be null.
+template <typename T>
+__global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __restrict__ f, const T* __restrict__ i,
+                                                                 float* __restrict__ ga, float* __restrict__ gAn,
+                                                                 float* __restrict__ m, int S, int Spad) {
+    __shared__ double wsum[32];
+    __shared__ float wmax[32];
+    __shared__ double carry_sum;
+    __shared__ float carry_max;
+    const int bh = blockIdx.x;
+    if (threadIdx.x == 0) {
+        carry_sum = 0.0;
+        carry_max = -INFINITY;
+    }
+    __syncthreads();
+    for (int base = 0; base < Spad; base += SCAN_THREADS) {
+        const int t = base + threadIdx.x;
+        const bool in = t < S;
+        double lf = 0.0;
+        float iv = 0.0f;
+        if (in) {
+            const double x = static_cast<double>(to_f32<T>(f[static_cast<size_t>(bh) * S + t]));
+            lf = x < 0.0 ? x - log1p(exp(x)) : -log1p(exp(-x));  // logsigmoid
+            iv = to_f32<T>(i[static_cast<size_t>(bh) * S + t]);
+        }
+        const double F = block_scan_add(lf, wsum, carry_sum);
+        const float a = in ? static_cast<float>(static_cast<double>(iv) - F) : -INFINITY;
+        const float A = block_scan_max(a, wmax, carry_max);
+        if (t < Spad) {
+            ga[static_cast<size_t>(bh) * Spad + t] = in ? a * LOG2E : -INFINITY;
+            gAn[static_cast<size_t>(bh) * Spad + t] = in ? -A * LOG2E : 0.0f;
+        }
+        if (in && m) m[static_cast<size_t>(bh) * S + t] = static_cast<float>(F + static_cast<double>(A));
+    }
+}
+
+// One warp per row: delta = dh.h, n, db, and from them the two per-row vectors of the backward:
+//   gB = gAn + log2(scale / n),   g = db * n   (db = sign(b) * (-delta / n) * [|b| > exp(-m)],
+// mlstm_matmul.py:194-196 with the sum replaced by n*delta).  Optionally writes dh converted to the
+// 16-bit input type for the tensor-core passes.  Padding rows: gB = -inf, g = 0.
+template <typename HT, typename T16>
+__global__ void bwd_prep_kernel(const HT* __restrict__ h, const HT* __restrict__ dh, const float* __restrict__ b,
+                                const float* __restrict__ m, const float* __restrict__ gAn, float* __restrict__ gB,
+                                float* __restrict__ g, T16* __restrict__ dh16, int BH, int S, int Spad, int D,
+                                float log2_scale) {
+    const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp_global >= BH * Spad) return;
+    const int bh = warp_global / Spad, t = warp_global % Spad;
+    if (t >= S) {
+        if (lane == 0) {
+            gB[warp_global] = -INFINITY;
+            g[warp_global] = 0.0f;
+        }
+        return;
+    }
+    const size_t row = (static_cast<size_t>(bh) * S + t) * D;
+    float delta = 0.0f;
+    for (int d = lane; d < D; d += 32) {
+        const float dv = to_f32<HT>(dh[row + d]);
+        delta += dv * to_f32<HT>(h[row + d]);
+        if (dh16) dh16[row + d] = from_f32<T16>(dv);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) delta += __shfl_xor_sync(0xffffffffu, delta, o);
+    if (lane == 0) {
+        const size_t idx = static_cast<size_t>(bh) * S + t;
+        const float bb = b[idx];
+        const float em = expf(-m[idx]);
+        const float n = fmaxf(fabsf(bb), em) + 1e-6f;
+        const float sgn = bb > 0.0f ? 1.0f : (bb < 0.0f ? -1.0f : 0.0f);
+        const float db = (fabsf(bb) > em) ? sgn * (-delta / n) : 0.0f;
+        const float gg = db * n;
+        g[warp_global] = isfinite(gg) ? gg : 0.0f;
+        gB[warp_global] = gAn[warp_global] + (log2_scale - log2f(n));
+    }
+}
+
+// One block per slice: dF_t = sigmoid(-f_t) * sum_{s<t} (dI_s - R_s), dF_0 = 0, and dI converted to
+// the output type (mlstm_matmul.py:316, 319-333).
+template <typename T>
+__global__ void __launch_bounds__(SCAN_THREADS) df_kernel(const T* __restrict__ f, const float* __restrict__ dI,
+                                                          const float* __restrict__ R, T* __restrict__ df,
+                                                          T* __restrict__ di, int S, int Spad) {
+    __shared__ double wsum[32];
+    __shared__ double carry_sum;
+    const int bh = blockIdx.x;
+    if (threadIdx.x == 0) carry_sum = 0.0;
+    __syncthreads();
+    for (int base = 0; base < S; base += SCAN_THREADS) {
+        const int t = base + threadIdx.x;
+        const bool in = t < S;
+        double x = 0.0;
+        float dIv = 0.0f;
+        if (in) {
+            dIv = dI[static_cast<size_t>(bh) * Spad + t];
+            x = static_cast<double>(dIv) - static_cast<double>(R[static_cast<size_t>(bh) * Spad + t]);
+        }
+        const double G = block_scan_add(x, wsum, carry_sum);  // inclusive
+        if (in) {
+            const float fv = to_f32<T>(f[static_cast<size_t>(bh) * S + t]);
+            const double sig = 1.0 / (1.0 + exp(static_cast<double>(fv)));  // sigmoid(-f)
+            const double val = t == 0 ? 0.0 : sig * (G - x);
+            df[static_cast<size_t>(bh) * S + t] = from_f32<T>(static_cast<float>(val));
+            di[static_cast<size_t>(bh) * S + t] = from_f32<T>(dIv);
+        }
+    }
+}
+
+}  // namespace
+
+int launch_gates_fwd(const void* f, const void* i, float* ga, float* gA, float* m, int BH, int S, int Spad, int dtype,
+                     cudaStream_t st) {
+    switch (dtype) {
+        case MLSTM_DT_F32:
+            gates_fwd_kernel<float><<<BH, SCAN_THREADS, 0, st>>>((const float*)f, (const float*)i, ga, gA, m, S, Spad);
+            break;
+        case MLSTM_DT_F16:
+            gates_fwd_kernel<__half><<<BH, SCAN_THREADS, 0, st>>>((const __half*)f, (const __half*)i, ga, gA, m, S, Spad);
+            break;
+        case MLSTM_DT_BF16:
+            gates_fwd_kernel<__nv_bfloat16>
+                <<<BH, SCAN_THREADS, 0, st>>>((const __nv_bfloat16*)f, (const __nv_bfloat16*)i, ga, gA, m, S, Spad);
+            break;
+        default: return MLSTM_E_ARG;
+    }
+    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+}
+
+template <typename HT>
+static int bwd_prep_dispatch(const void* h, const void* dh, const float* b, const float* m, const float* gA, float* gB,
+                             float* g, void* dh16, int BH, int S, int Spad, int D, int dtype, cudaStream_t st) {
+    const long long warps = static_cast<long long>(BH) * Spad;
+    const int threads = 256;
+    const long long blocks = (warps * 32 + threads - 1) / threads;
+    if (blocks > 0x7fffffffLL) return MLSTM_E_SHAPE;
+    const float log2_scale = -0.5f * log2f(static_cast<float>(D));
+    if (dtype == MLSTM_DT_BF16)
+        bwd_prep_kernel<HT, __nv_bfloat16><<<(unsigned)blocks, threads, 0, st>>>(
+            (const HT*)h, (const HT*)dh, b, m, gA, gB, g, (__nv_bfloat16*)dh16, BH, S, Spad, D, log2_scale);
+    else
+        bwd_prep_kernel<HT, __half><<<(unsigned)blocks, threads, 0, st>>>((const HT*)h, (const HT*)dh, b, m, gA, gB, g,
+                                                                         (__half*)dh16, BH, S, Spad, D, log2_scale);
+    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+}
+
+int launch_bwd_prep(const void* h, const void* dh, const float* b, const float* m, const float* gA, float* gB, float* g,
+                    void* dh16, int BH, int S, int Spad, int D, int h_dtype, int dtype, cudaStream_t st) {
+    switch (h_dtype) {
+        case MLSTM_DT_F32: return bwd_prep_dispatch<float>(h, dh, b, m, gA, gB, g, dh16, BH, S, Spad, D, dtype, st);
+        case MLSTM_DT_F16: return bwd_prep_dispatch<__half>(h, dh, b, m, gA, gB, g, dh16, BH, S, Spad, D, dtype, st);
+        case MLSTM_DT_BF16:
+            return bwd_prep_dispatch<__nv_bfloat16>(h, dh, b, m, gA, gB, g, dh16, BH, S, Spad, D, dtype, st);
+    }
+    return MLSTM_E_ARG;
+}
+
+int launch_df(const void* f, const float* dI, const float* R, void* df, void* di, int BH, int S, int Spad, int dtype,
+              cudaStream_t st) {
+    switch (dtype) {
+        case MLSTM_DT_F32:
+            df_kernel<float><<<BH, SCAN_THREADS, 0, st>>>((const float*)f, dI, R, (float*)df, (float*)di, S, Spad);
+            break;
+        case MLSTM_DT_F16:
+            df_kernel<__half><<<BH, SCAN_THREADS, 0, st>>>((const __half*)f, dI, R, (__half*)df, (__half*)di, S, Spad);
+            break;
+        case MLSTM_DT_BF16:
+            df_kernel<__nv_bfloat16><<<BH, SCAN_THREADS, 0, st>>>((const __nv_bfloat16*)f, dI, R, (__nv_bfloat16*)df,
+                                                                 (__nv_bfloat16*)di, S, Spad);
+            break;
+        default: return MLSTM_E_ARG;
+    }
+    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+}
+
+}  // namespace mlstm

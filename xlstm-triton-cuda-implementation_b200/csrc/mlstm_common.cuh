@@ -1,0 +1,107 @@
+// Shared definitions of the mLSTM kernels: status codes, element types, the per-row gate vectors
+// and the one elementwise rule that all four contraction passes share.
+//
+// Decomposition used by every kernel of this library (per batch*head slice, rows r, columns c):
+//   F_t  = inclusive cumulative sum of logsigmoid(f)          (reference: mlstm_matmul.py:59, 73-82, 106)
+//   a_t  = i_t - F_t,   A_t = max_{s<=t} a_s,   m_t = F_t + A_t (the reference's running row maximum,
+//                                                               mlstm_matmul.py:84, is this prefix maximum)
+//   exp(d_tilde_rc - m_r) = exp(a_c - A_r)   for c <= r        (mlstm_matmul.py:85-86)
+// so the stabiliser is known before the contraction starts and no accumulator is ever rescaled.
+// With n_r = max(|b_r|, exp(-m_r)) + 1e-6 (mlstm_matmul.py:95) all four passes have the form
+//   T = X Y^T  (contraction over the head dimension)
+//   W = (T + g) * exp2(ec[c] + er[r])   on the causal side of the diagonal, 0 elsewhere
+//   ACC += W Z (contraction over the streamed tile's 128 rows)
+// with (scale = 1/sqrt(D), log2 units, "gA" = A*log2e, "ga" = a*log2e, ln_r = log2(scale / n_r);
+// the gate pass stores gAn = -gA and the backward preparation stores gB = gAn + ln):
+//   FWD  rows = queries  X=Q  Y=K  Z=V   er = -gA_r + log2(scale)  ec = ga_c       g = 0         out = ACC / n_r
+//   DQ   rows = queries  X=dH Y=V  Z=K   er = -gA_r + ln_r         ec = ga_c       g = db_r n_r  out = ACC
+//   DK   rows = keys     X=V  Y=dH Z=Q   er = ga_r                 ec = -gA_c+ln_c g = db_c n_c  out = ACC
+//   DV   rows = keys     X=K  Y=Q  Z=dH  er = ga_r                 ec = -gA_c+ln_c g = 0         out = ACC
+// (backward formulas: mlstm_matmul.py:183-197, 256-316, 336-365).
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/mlstm_b200.h"
+
+namespace mlstm {
+
+enum Mode : int { FWD = 0, DQ = 1, DK = 2, DV = 3 };
+
+constexpr int TILE = 128;  // rows of a tensor-core tile; gate vectors are padded to a multiple of it
+
+__host__ __device__ inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+// Arguments of one contraction pass, shared by the tensor-core and the SIMT kernels.
+struct PassParams {
+    int S;      // sequence length
+    int Spad;   // S rounded up to TILE: stride of every gate vector per slice
+    int BH;     // batch * heads
+    int D;      // head dimension
+    const void* X;  // stationary operand  [BH, S, D]
+    const void* Y;  // first streamed operand
+    const void* Z;  // second streamed operand
+    const float* row_e;  // er without the constant term, [BH, Spad]
+    const float* row_g;  // g per row (DQ) or nullptr
+    const float* col_e;  // ec, [BH, Spad]
+    const float* col_g;  // g per column (DK) or nullptr
+    float er_add;        // constant added to er (FWD: log2(scale))
+    void* out;           // [BH, S, D], element type chosen by the kernel template
+    // FWD only
+    const float* m;      // [BH, S] stabiliser, written by the gate pass
+    float* b_out;        // [BH, S] row sums of the gated tile (the reference's B output) or nullptr
+    const void* ogate;   // [BH, S, D] optional output gate pre-activation (scan API), input type
+    // DQ / DK only: dot_out[r] = sum_d ACC[r, d] * dot_src[r, d], taken on the fp32 accumulator
+    const void* dot_src; // [BH, S, D] input type (q for DQ, k for DK)
+    float* dot_out;      // [BH, Spad]
+    int* status;         // device word; a kernel that gave up on a wait stores a non-zero code
+};
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T x);
+template <>
+__device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float x);
+template <>
+__device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+// Causal side of the diagonal.  Rows are queries in FWD/DQ (column <= row is valid) and keys in
+// DK/DV (column >= row is valid).
+template <int MODE>
+__device__ __forceinline__ bool causal_ok(int row, int col) {
+    return (MODE == FWD || MODE == DQ) ? (col <= row) : (col >= row);
+}
+
+// Launchers implemented in the .cu files.  All return an MLSTM_* status and never synchronise.
+int launch_gates_fwd(const void* f, const void* i, float* ga, float* gAn, float* m, int BH, int S, int Spad,
+                     int dtype, cudaStream_t st);
+int launch_bwd_prep(const void* h, const void* dh, const float* b, const float* m, const float* gAn, float* gB,
+                    float* g, void* dh16, int BH, int S, int Spad, int D, int h_dtype, int dtype, cudaStream_t st);
+int launch_df(const void* f, const float* dI, const float* R, void* df, void* di, int BH, int S, int Spad, int dtype,
+              cudaStream_t st);
+int launch_pass_simt(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st);
+int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st);
+bool tc_supported(int S, int D, int in_dtype);
+
+}  // namespace mlstm

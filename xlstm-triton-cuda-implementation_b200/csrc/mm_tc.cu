@@ -1,0 +1,455 @@
+// Tensor-core contraction pass of the parallel mLSTM for sm_100a (tcgen05 MMA, TMEM accumulators,
+// TMA-staged 128-byte-swizzled shared-memory tiles).  One kernel template serves the forward and
+// the three backward passes (see mlstm_common.cuh for the algebra).  It takes the place of the
+// reference's mlstm_matmul_kernel (mlstm_matmul.py:37-101), mlstm_matmul_kernel_backward_db
+// (:132-197) and mlstm_matmul_kernel_backward (:200-316), and of the single-head fp16 kernel
+// mlstm_forward (cuda-src/mlstm_forward.cu:12-189).
+//
+// One CTA owns one stationary 128-row tile (queries in FWD/DQ, keys in DK/DV) of one batch*head
+// slice and streams the tiles on the causal side of it.  Warp roles (384 threads):
+//   warp 0      TMA producer: stationary tile once, then streamed tiles through a ring of slots
+//   warp 1      MMA issuer (one thread) and TMEM allocator
+//   warps 4-7   gate group 0: turns even steps' T tiles into gated 16-bit W tiles, in TMEM
+//   warps 8-11  gate group 1: odd steps
+// TMEM (512 columns): T0 [0,128) and T1 [128,256) fp32 128x128, W aliases the first 64 columns of
+// its T (two 16-bit values per column), ACC [256, 256+D) fp32 128xD.
+// The second contraction reads W straight from TMEM as the A operand and the streamed Z tile from
+// shared memory as an MN-major B operand, so the gated tile never touches shared or global memory.
+//
+// Every wait is bounded: a wait that runs out sets a CTA-wide abort word, every role leaves its
+// loop, the CTA stores a non-zero code in the status word, waits a little for copies in flight,
+// frees its TMEM and returns.
+#include "mlstm_common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace mlstm {
+namespace {
+
+using namespace ptx;
+
+constexpr int NTHREADS = 384;
+constexpr int BOX_BYTES = 128 * 128;  // one TMA box: 128 rows of 128 bytes (64 16-bit elements)
+constexpr long long WAIT_LIMIT = 4000000000LL;  // cycles (about two seconds)
+
+template <int D>
+struct TcCfg {
+    static constexpr int CH = D < 128 ? D : 128;            // elements of D per ring slot
+    static constexpr int NHALF = D / CH;                    // slots per streamed tile
+    static constexpr int SLOT_BYTES = (CH / 64) * BOX_BYTES;
+    static constexpr int X_BYTES = (D / 64) * BOX_BYTES;
+    static constexpr int NSLOT = D == 256 ? 5 : (D == 128 ? 6 : 8);
+    static constexpr int NBAR = 1 + 2 * NSLOT + 2 + 2 + 1 + 1;  // x, slot full/empty, t_full, w_full, acc, part
+    static constexpr int SMEM_BYTES = 1024 /*align slack*/ + X_BYTES + NSLOT * SLOT_BYTES + NBAR * 8 + 64 +
+                                      2 * 128 * 4 /*row partials*/;
+};
+
+struct SmemTail {  // lives after the tiles
+    float part[2][128];  // one partial per gate group and row (row sums in FWD, row dots in DQ/DK)
+};
+
+template <int MODE, int D, int ABFMT, typename OutT>
+__global__ void __launch_bounds__(NTHREADS, 1)
+mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
+              const __grid_constant__ CUtensorMap tmZ, const PassParams p) {
+    using C = TcCfg<D>;
+    using InT = typename std::conditional<ABFMT == 1, __nv_bfloat16, __half>::type;
+    constexpr bool ROWS_ARE_Q = (MODE == FWD || MODE == DQ);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sX = smem;
+    uint8_t* sSlot = smem + C::X_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sSlot + C::NSLOT * C::SLOT_BYTES);
+    uint64_t* bar_x = bars;
+    uint64_t* bar_full = bars + 1;
+    uint64_t* bar_empty = bars + 1 + C::NSLOT;
+    uint64_t* bar_t = bars + 1 + 2 * C::NSLOT;  // [2] T tile written by the first contraction
+    uint64_t* bar_w = bar_t + 2;                // [2] W tile written by a gate group
+    uint64_t* bar_acc = bar_w + 2;              // accumulator complete
+    uint64_t* bar_part = bar_acc + 1;           // row partials of both gate groups in shared memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    SmemTail* tail = reinterpret_cast<SmemTail*>(reinterpret_cast<uint8_t*>(bars) + C::NBAR * 8 + 64);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int NT = p.Spad / TILE;
+    const int bh = blockIdx.x % p.BH;
+    const int w = blockIdx.x / p.BH;  // heaviest tiles are launched first
+    const int tile = ROWS_ARE_Q ? (NT - 1 - w) : w;
+    const int nsteps = ROWS_ARE_Q ? (tile + 1) : (NT - tile);
+    // streamed tile of step t: FWD/DQ visit key tiles 0..tile (diagonal last), DK/DV visit query
+    // tiles tile..NT-1 (diagonal first)
+    auto stream_tile = [&](int t) { return ROWS_ARE_Q ? t : (tile + t); };
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_x, 1);
+        for (int s = 0; s < C::NSLOT; s++) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_empty[s], 1);
+        }
+        mbar_init(&bar_t[0], 1);
+        mbar_init(&bar_t[1], 1);
+        mbar_init(&bar_w[0], 128);
+        mbar_init(&bar_w[1], 128);
+        mbar_init(bar_acc, 1);
+        mbar_init(bar_part, 256);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_T0 = tmem_base;
+    const uint32_t tmem_ACC = tmem_base + 256;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            prefetch_tmap(&tmX);
+            prefetch_tmap(&tmY);
+            prefetch_tmap(&tmZ);
+            mbar_expect_tx(bar_x, C::X_BYTES);
+            for (int c = 0; c < D / 64; c++) tma_load_3d(sX + c * BOX_BYTES, &tmX, bar_x, c * 64, tile * TILE, bh);
+            int it = 0;
+            bool ok = true;
+            auto load_tile = [&](const CUtensorMap* map, int st) {
+                for (int hf = 0; hf < C::NHALF && ok; hf++, it++) {
+                    const int s = it % C::NSLOT;
+                    ok = mbar_wait(&bar_empty[s], ((it / C::NSLOT) & 1) ^ 1, abort_flag, WAIT_LIMIT);
+                    if (!ok) break;
+                    mbar_expect_tx(&bar_full[s], C::SLOT_BYTES);
+                    uint8_t* dst = sSlot + s * C::SLOT_BYTES;
+                    for (int c = 0; c < C::CH / 64; c++)
+                        tma_load_3d(dst + c * BOX_BYTES, map, &bar_full[s], (hf * (C::CH / 64) + c) * 64, st * TILE,
+                                    bh);
+                }
+            };
+            // same order as the MMA issuer consumes: Y(0), then Y(t), Z(t-1) ..., Z(last)
+            load_tile(&tmY, stream_tile(0));
+            for (int t = 1; t < nsteps && ok; t++) {
+                load_tile(&tmY, stream_tile(t));
+                load_tile(&tmZ, stream_tile(t - 1));
+            }
+            if (ok) load_tile(&tmZ, stream_tile(nsteps - 1));
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc1 = make_idesc(ABFMT, 128, 128, 0, 0);
+            constexpr uint32_t idesc2 = make_idesc(ABFMT, 128, C::CH, 0, 1);
+            const uint32_t sX_addr = smem_u32(sX);
+            const uint32_t sSlot_addr = smem_u32(sSlot);
+            int it = 0;
+            bool ok = mbar_wait(bar_x, 0, abort_flag, WAIT_LIMIT);
+            tc_fence_after();
+            auto second = [&](int u) {  // ACC += W(u) Z(u)
+                ok = ok && mbar_wait(&bar_w[u & 1], (u >> 1) & 1, abort_flag, WAIT_LIMIT);
+                if (!ok) return;
+                tc_fence_after();
+                const uint32_t w_tmem = tmem_T0 + (u & 1) * 128;
+                for (int hf = 0; hf < C::NHALF; hf++, it++) {
+                    const int s = it % C::NSLOT;
+                    ok = mbar_wait(&bar_full[s], (it / C::NSLOT) & 1, abort_flag, WAIT_LIMIT);
+                    if (!ok) return;
+                    tc_fence_after();
+                    const uint32_t zaddr = sSlot_addr + s * C::SLOT_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < 8; kk++) {  // 16 streamed rows per MMA
+                        const uint64_t bdesc = smem_desc_sw128(zaddr + kk * 2048, BOX_BYTES, 1024);
+                        mma_ts<false>(tmem_ACC + hf * C::CH, w_tmem + kk * 8, bdesc, idesc2, (u > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&bar_empty[s]);
+                }
+            };
+            for (int t = 0; t < nsteps && ok; t++) {
+                // T(t) = X Y(t)^T
+                for (int hf = 0; hf < C::NHALF; hf++, it++) {
+                    const int s = it % C::NSLOT;
+                    ok = mbar_wait(&bar_full[s], (it / C::NSLOT) & 1, abort_flag, WAIT_LIMIT);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t yaddr = sSlot_addr + s * C::SLOT_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < C::CH / 16; kk++) {
+                        const int kx = hf * (C::CH / 16) + kk;  // K step inside the stationary tile
+                        const uint64_t adesc = smem_desc_sw128(sX_addr + (kx >> 2) * BOX_BYTES + (kx & 3) * 32, 16, 1024);
+                        const uint64_t bdesc = smem_desc_sw128(yaddr + (kk >> 2) * BOX_BYTES + (kk & 3) * 32, 16, 1024);
+                        mma_ss<false>(tmem_T0 + (t & 1) * 128, adesc, bdesc, idesc1, kx > 0 ? 1u : 0u);
+                    }
+                    tc_commit(&bar_empty[s]);
+                }
+                if (!ok) break;
+                tc_commit(&bar_t[t & 1]);
+                if (t >= 1) second(t - 1);
+            }
+            if (ok) second(nsteps - 1);
+            if (ok) tc_commit(bar_acc);
+        }
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------ gate groups
+        const int grp = (warp - 4) >> 2;
+        const int r = (warp & 3) * 32 + lane;          // TMEM lane == row inside the tile
+        const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const int grow = tile * TILE + r;              // row inside the slice (may be >= S in the last tile)
+        const size_t vec_base = static_cast<size_t>(bh) * p.Spad;
+        const float er = p.row_e[vec_base + grow] + p.er_add;
+        const float g_row = (MODE == DQ) ? p.row_g[vec_base + grow] : 0.0f;
+        float rowsum = 0.0f;
+        bool ok = true;
+
+        for (int t = grp; t < nsteps; t += 2) {
+            const int buf = t & 1;
+            ok = mbar_wait(&bar_t[buf], (t >> 1) & 1, abort_flag, WAIT_LIMIT);
+            if (!ok) break;
+            tc_fence_after();
+            const int st = stream_tile(t);
+            const bool diag = (st == tile);
+            const float4* ce4 = reinterpret_cast<const float4*>(p.col_e + vec_base + st * TILE);
+            const float4* cg4 = (MODE == DK) ? reinterpret_cast<const float4*>(p.col_g + vec_base + st * TILE) : nullptr;
+            const uint32_t t_tmem = tmem_T0 + buf * 128 + lane_bits;
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t tv[32];
+                tmem_ld32(t_tmem + ch * 32, tv);
+                float wv[32];
+#pragma unroll
+                for (int q4 = 0; q4 < 8; q4++) {
+                    const float4 e4 = __ldg(ce4 + ch * 8 + q4);
+                    wv[q4 * 4 + 0] = e4.x; wv[q4 * 4 + 1] = e4.y; wv[q4 * 4 + 2] = e4.z; wv[q4 * 4 + 3] = e4.w;
+                }
+                tc_wait_ld();
+                if (MODE == DK) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; q4++) {
+                        const float4 g4 = __ldg(cg4 + ch * 8 + q4);
+                        tv[q4 * 4 + 0] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 0]) + g4.x);
+                        tv[q4 * 4 + 1] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 1]) + g4.y);
+                        tv[q4 * 4 + 2] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 2]) + g4.z);
+                        tv[q4 * 4 + 3] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 3]) + g4.w);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    float tval = __uint_as_float(tv[j]);
+                    if (MODE == DQ) tval += g_row;
+                    float wj = tval * fast_exp2(wv[j] + er);
+                    if (diag && !causal_ok<MODE>(r, ch * 32 + j)) wj = 0.0f;
+                    wv[j] = wj;
+                    if (MODE == FWD) rowsum += wj;
+                }
+                uint32_t pk[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    if constexpr (ABFMT == 1) {
+                        __nv_bfloat162 v2 = __floats2bfloat162_rn(wv[2 * j], wv[2 * j + 1]);
+                        pk[j] = *reinterpret_cast<uint32_t*>(&v2);
+                    } else {
+                        __half2 v2 = __floats2half2_rn(wv[2 * j], wv[2 * j + 1]);
+                        pk[j] = *reinterpret_cast<uint32_t*>(&v2);
+                    }
+                }
+                tmem_st16(t_tmem + ch * 16, pk);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bar_w[buf]);
+        }
+
+        // ---- epilogue: each group drains half of the accumulator's columns for all 128 rows
+        if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, WAIT_LIMIT);
+        if (ok) {
+            tc_fence_after();
+            constexpr int HALF = D / 2;
+            const int c0 = grp * HALF;
+            const bool row_ok = grow < p.S;
+            const size_t row_off = (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * D;
+            float inv_n = 1.0f;
+            if (MODE == FWD) {
+                tail->part[grp][r] = rowsum;
+                mbar_arrive(bar_part);
+                ok = mbar_wait(bar_part, 0, abort_flag, WAIT_LIMIT);
+                if (ok) {
+                    const float bsum = tail->part[0][r] + tail->part[1][r];
+                    const float mrow = row_ok ? p.m[static_cast<size_t>(bh) * p.S + grow] : 0.0f;
+                    const float n = fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f;
+                    inv_n = 1.0f / n;
+                    if (grp == 0 && row_ok && p.b_out) p.b_out[static_cast<size_t>(bh) * p.S + grow] = bsum;
+                }
+            }
+            float dot = 0.0f;
+            if (ok) {
+                OutT* orow = reinterpret_cast<OutT*>(p.out) + row_off + c0;
+                const InT* ogate_row = (MODE == FWD && p.ogate) ? reinterpret_cast<const InT*>(p.ogate) + row_off + c0 : nullptr;
+                const InT* drow = ((MODE == DQ || MODE == DK) && p.dot_src)
+                                      ? reinterpret_cast<const InT*>(p.dot_src) + row_off + c0 : nullptr;
+#pragma unroll 1
+                for (int ch = 0; ch < HALF / 32; ch++) {
+                    uint32_t av[32];
+                    tmem_ld32(tmem_ACC + lane_bits + c0 + ch * 32, av);
+                    tc_wait_ld();
+                    if (row_ok) {
+                        float vals[32];
+#pragma unroll
+                        for (int j = 0; j < 32; j++) vals[j] = __uint_as_float(av[j]) * inv_n;
+                        if (MODE == FWD && ogate_row) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) vals[j] *= silu_f(to_f32<InT>(ogate_row[ch * 32 + j]));
+                        }
+                        if ((MODE == DQ || MODE == DK) && drow) {
+#pragma unroll
+                            for (int j8 = 0; j8 < 4; j8++) {
+                                const uint4 raw = *reinterpret_cast<const uint4*>(drow + ch * 32 + j8 * 8);
+                                const InT* e8 = reinterpret_cast<const InT*>(&raw);
+#pragma unroll
+                                for (int j = 0; j < 8; j++) dot += vals[j8 * 8 + j] * to_f32<InT>(e8[j]);
+                            }
+                        }
+                        if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+                            for (int j4 = 0; j4 < 8; j4++) {
+                                float4 o4 = make_float4(vals[j4 * 4], vals[j4 * 4 + 1], vals[j4 * 4 + 2], vals[j4 * 4 + 3]);
+                                *reinterpret_cast<float4*>(reinterpret_cast<float*>(orow) + ch * 32 + j4 * 4) = o4;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j8 = 0; j8 < 4; j8++) {
+                                uint4 o4;
+                                uint32_t* o32 = reinterpret_cast<uint32_t*>(&o4);
+#pragma unroll
+                                for (int j = 0; j < 4; j++) {
+                                    OutT lo = from_f32<OutT>(vals[j8 * 8 + 2 * j]);
+                                    OutT hi = from_f32<OutT>(vals[j8 * 8 + 2 * j + 1]);
+                                    o32[j] = static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&lo)) |
+                                             (static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&hi)) << 16);
+                                }
+                                *reinterpret_cast<uint4*>(orow + ch * 32 + j8 * 8) = o4;
+                            }
+                        }
+                    }
+                }
+            }
+            if ((MODE == DQ || MODE == DK) && p.dot_out && ok) {
+                tail->part[grp][r] = dot;
+                mbar_arrive(bar_part);
+                ok = mbar_wait(bar_part, 0, abort_flag, WAIT_LIMIT);
+                if (ok && grp == 0)
+                    p.dot_out[vec_base + grow] = row_ok ? (tail->part[0][r] + tail->part[1][r]) : 0.0f;
+            }
+        }
+        tc_fence_before();
+    }
+
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.status, 1000 + MODE);
+        // give copies and MMAs that are still in flight time to land before the CTA's memory goes away
+        for (int k = 0; k < 64; k++) __nanosleep(16000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+    return fn;
+}
+
+// [BH, S, D] 16-bit tensor, boxes of 64 elements x 128 rows, 128-byte swizzle, zero fill past S.
+int make_map(CUtensorMap* map, const void* base, int BH, int S, int D, int dtype) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return MLSTM_E_CUDA;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(BH)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(S) * D * 2};
+    cuuint32_t box[3] = {64, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUtensorMapDataType dt = dtype == MLSTM_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? MLSTM_OK : MLSTM_E_CUDA;
+}
+
+template <int MODE, int D, int ABFMT, typename OutT>
+int launch_one(const PassParams& p, int in_dtype, cudaStream_t st) {
+    CUtensorMap mx, my, mz;
+    int rc;
+    if ((rc = make_map(&mx, p.X, p.BH, p.S, D, in_dtype)) != MLSTM_OK) return rc;
+    if ((rc = make_map(&my, p.Y, p.BH, p.S, D, in_dtype)) != MLSTM_OK) return rc;
+    if ((rc = make_map(&mz, p.Z, p.BH, p.S, D, in_dtype)) != MLSTM_OK) return rc;
+    auto kern = mlstm_tc_pass<MODE, D, ABFMT, OutT>;
+    constexpr int smem = TcCfg<D>::SMEM_BYTES;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+        cudaGetLastError();
+        return MLSTM_E_CUDA;
+    }
+    const int NT = p.Spad / TILE;
+    const long long nblk = static_cast<long long>(NT) * p.BH;
+    if (nblk > 0x7fffffffLL) return MLSTM_E_SHAPE;
+    kern<<<static_cast<unsigned>(nblk), NTHREADS, smem, st>>>(mx, my, mz, p);
+    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+}
+
+template <int MODE, int D, int ABFMT>
+int launch_out(const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) {
+    if (out_dtype == MLSTM_DT_F32) return launch_one<MODE, D, ABFMT, float>(p, in_dtype, st);
+    if (out_dtype == in_dtype) {
+        if (ABFMT == 1) return launch_one<MODE, D, ABFMT, __nv_bfloat16>(p, in_dtype, st);
+        return launch_one<MODE, D, ABFMT, __half>(p, in_dtype, st);
+    }
+    return MLSTM_E_ARG;
+}
+
+template <int MODE, int D>
+int launch_fmt(const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) {
+    if (in_dtype == MLSTM_DT_BF16) return launch_out<MODE, D, 1>(p, in_dtype, out_dtype, st);
+    return launch_out<MODE, D, 0>(p, in_dtype, out_dtype, st);
+}
+
+template <int MODE>
+int launch_d(const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) {
+    switch (p.D) {
+        case 64: return launch_fmt<MODE, 64>(p, in_dtype, out_dtype, st);
+        case 128: return launch_fmt<MODE, 128>(p, in_dtype, out_dtype, st);
+        case 256: return launch_fmt<MODE, 256>(p, in_dtype, out_dtype, st);
+    }
+    return MLSTM_E_UNSUPPORTED;
+}
+
+}  // namespace
+
+bool tc_supported(int S, int D, int in_dtype) {
+    return S >= 1 && (D == 64 || D == 128 || D == 256) && (in_dtype == MLSTM_DT_F16 || in_dtype == MLSTM_DT_BF16);
+}
+
+int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) {
+    if (!tc_supported(p.S, p.D, in_dtype)) return MLSTM_E_UNSUPPORTED;
+    switch (mode) {
+        case FWD: return launch_d<FWD>(p, in_dtype, out_dtype, st);
+        case DQ: return launch_d<DQ>(p, in_dtype, out_dtype, st);
+        case DK: return launch_d<DK>(p, in_dtype, out_dtype, st);
+        case DV: return launch_d<DV>(p, in_dtype, out_dtype, st);
+    }
+    return MLSTM_E_ARG;
+}
+
+}  // namespace mlstm

@@ -1,0 +1,98 @@
+"""Parallel (matmul) mLSTM forward and backward on the B200 kernels.
+
+Same names, arguments and results as the reference module of this name
+(mlstm_matmul.py:121-129 ``mlstm_matmul``; :368-405 ``Triton_mLSTM``):
+
+    h = Triton_mLSTM.apply(q, k, v, f, i, SB, NUM_WARPS)
+    h.backward(dh)          # q.grad, k.grad, v.grad, f.grad, i.grad
+
+q, k, v: [B, NH, S, D]; f, i: [B, NH, S]; CUDA, contiguous, float32 / float16 / bfloat16.
+``h`` is float32 whatever the inputs are, as in the reference (mlstm_matmul.py:373); gradients have
+the inputs' type (:389-393).  ``SB`` and ``num_warps`` are the reference's tiling hints: they are
+checked (positive integers) and otherwise ignored, the kernels pick their own tiles.
+"""
+import torch
+
+from . import _lib
+
+__all__ = ["Triton_mLSTM", "mlstm_matmul", "mlstm_matmul_forward", "mlstm_matmul_backward"]
+
+
+def _check_hints(SB, num_warps):
+    if int(SB) <= 0 or int(num_warps) <= 0:
+        raise ValueError("SB and num_warps must be positive")
+
+
+def _check_shapes(q, k, v, f, i):
+    if q.dim() != 4 or k.shape != q.shape or v.shape != q.shape:
+        raise ValueError("q, k, v must share the shape [B, NH, S, D]")
+    if f.shape != q.shape[:3] or i.shape != q.shape[:3]:
+        raise ValueError("f, i must have the shape [B, NH, S]")
+    if not (k.dtype == v.dtype == f.dtype == i.dtype == q.dtype):
+        raise TypeError("q, k, v, f, i must share one element type")
+
+
+def mlstm_matmul_forward(q, k, v, f, i, h_dtype=torch.float32, flags=0):
+    """Run the forward; returns (h, m, b) with m, b the float32 stabiliser and row sums."""
+    _check_shapes(q, k, v, f, i)
+    dev = _lib.require_cuda(q, k, v, f, i)
+    B, NH, S, D = q.shape
+    dt = _lib.dtype_code(q)
+    h = torch.empty((B, NH, S, D), device=dev, dtype=h_dtype)
+    m = torch.empty((B, NH, S), device=dev, dtype=torch.float32)
+    b = torch.empty((B, NH, S), device=dev, dtype=torch.float32)
+    L = _lib.lib()
+    ws = _lib.workspace(L.mlstm_mm_fwd_workspace(B, NH, S, D, dt), dev)
+    with torch.cuda.device(dev):
+        rc = L.mlstm_mm_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), f.data_ptr(), i.data_ptr(), h.data_ptr(),
+                            m.data_ptr(), b.data_ptr(), ws.data_ptr(), ws.numel(), B, NH, S, D, dt,
+                            _lib.dtype_code(h), flags, _lib.stream_ptr(dev))
+    _lib.check(rc, "mlstm_mm_fwd")
+    _lib.maybe_read_status(ws, dev, "mlstm_mm_fwd")
+    return h, m, b
+
+
+def mlstm_matmul_backward(dh, q, k, v, f, i, h, m, b, flags=0):
+    """Run the backward; returns (dq, dk, dv, df, di) in the inputs' element type."""
+    dev = _lib.require_cuda(dh, q, k, v, f, i, h, m, b)
+    B, NH, S, D = q.shape
+    if dh.shape != q.shape or dh.dtype != h.dtype:
+        raise ValueError("dh must match h in shape and element type")
+    dt, hdt = _lib.dtype_code(q), _lib.dtype_code(h)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    df, di = torch.empty_like(f), torch.empty_like(i)
+    L = _lib.lib()
+    ws = _lib.workspace(L.mlstm_mm_bwd_workspace(B, NH, S, D, dt, hdt), dev)
+    with torch.cuda.device(dev):
+        rc = L.mlstm_mm_bwd(dh.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), f.data_ptr(), i.data_ptr(),
+                            h.data_ptr(), m.data_ptr(), b.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                            df.data_ptr(), di.data_ptr(), ws.data_ptr(), ws.numel(), B, NH, S, D, dt, hdt, flags,
+                            _lib.stream_ptr(dev))
+    _lib.check(rc, "mlstm_mm_bwd")
+    _lib.maybe_read_status(ws, dev, "mlstm_mm_bwd")
+    return dq, dk, dv, df, di
+
+
+class Triton_mLSTM(torch.autograd.Function):
+    """Drop-in for the reference's autograd function (mlstm_matmul.py:368-405); the name is kept."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, f, i, SB=16, num_warps=8):
+        _check_hints(SB, num_warps)
+        h, m, b = mlstm_matmul_forward(q, k, v, f, i)
+        ctx.save_for_backward(q, k, v, f, i, m, b, h)
+        ctx.sb = SB
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        assert dh.is_contiguous()  # mlstm_matmul.py:385
+        q, k, v, f, i, m, b, h = ctx.saved_tensors
+        dq, dk, dv, df, di = mlstm_matmul_backward(dh, q, k, v, f, i, h, m, b)
+        return dq, dk, dv, df, di, None, None
+
+
+def mlstm_matmul(q, k, v, f, i, SB=16, num_warps=8):
+    """Forward without autograd (mlstm_matmul.py:121-129)."""
+    _check_hints(SB, num_warps)
+    return mlstm_matmul_forward(q, k, v, f, i)[0]
