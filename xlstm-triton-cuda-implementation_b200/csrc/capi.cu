@@ -28,6 +28,7 @@ struct Carver {
 struct FwdWs {
     int* status;
     float *ga, *gAn, *m, *b;
+    double *a_ref, *An_ref;
     size_t bytes;
 };
 // with_mb: also carve m and b (entry points whose caller does not pass them)
@@ -38,6 +39,8 @@ FwdWs carve_fwd(void* ws, int BH, int S, bool with_mb) {
     w.status = c.take<int>(WS_ALIGN);
     w.ga = c.take<float>(vec);
     w.gAn = c.take<float>(vec);
+    w.a_ref = c.take<double>(vec / REF_BLOCK * 2);
+    w.An_ref = c.take<double>(vec / REF_BLOCK * 2);
     if (with_mb) {
         w.m = c.take<float>(static_cast<size_t>(BH) * S * sizeof(float));
         w.b = c.take<float>(static_cast<size_t>(BH) * S * sizeof(float));
@@ -49,6 +52,7 @@ FwdWs carve_fwd(void* ws, int BH, int S, bool with_mb) {
 struct BwdWs {
     int* status;
     float *ga, *gAn, *gB, *g, *dI, *R;
+    double *a_ref, *An_ref;
     void* dh16;
     size_t bytes;
 };
@@ -59,6 +63,8 @@ BwdWs carve_bwd(void* ws, int BH, int S, int D, bool need_dh16) {
     w.status = c.take<int>(WS_ALIGN);
     w.ga = c.take<float>(vec);
     w.gAn = c.take<float>(vec);
+    w.a_ref = c.take<double>(vec / REF_BLOCK * 2);
+    w.An_ref = c.take<double>(vec / REF_BLOCK * 2);
     w.gB = c.take<float>(vec);
     w.g = c.take<float>(vec);
     w.dI = c.take<float>(vec);
@@ -102,11 +108,11 @@ int forward_impl(const void* q, const void* k, const void* v, const void* f, con
     if (rc != MLSTM_OK) return rc;
     const int Spad = round_up(S, TILE);
     if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
-    if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, m, BH, S, Spad, dtype, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, m, BH, S, Spad, dtype, st)) != MLSTM_OK) return rc;
     PassParams p{};
     p.S = S; p.Spad = Spad; p.BH = BH; p.D = D;
     p.X = q; p.Y = k; p.Z = v;
-    p.row_e = w.gAn; p.col_e = w.ga;
+    p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_ref = w.a_ref;
     p.er_add = -0.5f * log2f(static_cast<float>(D));
     p.out = h; p.m = m; p.b_out = b; p.ogate = o;
     p.status = w.status;
@@ -180,7 +186,7 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
-    if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, nullptr, BH, S, Spad, dtype, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, nullptr, BH, S, Spad, dtype, st)) != MLSTM_OK) return rc;
     if ((rc = launch_bwd_prep(h, dh, b, m, w.gAn, w.gB, w.g, w.dh16, BH, S, Spad, D, h_dtype, dtype, st)) != MLSTM_OK)
         return rc;
     const void* dhp = need16 ? w.dh16 : dh;  // dh in the element type of q, k, v
@@ -189,12 +195,12 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status;
     // dQ = ((dH V^T + g_r) * decay) K
     p.X = dhp; p.Y = v; p.Z = k;
-    p.row_e = w.gB; p.row_g = w.g; p.col_e = w.ga; p.col_g = nullptr;
+    p.row_rel = w.gB; p.row_ref = w.An_ref; p.row_g = w.g; p.col_rel = w.ga; p.col_ref = w.a_ref; p.col_g = nullptr;
     p.out = dq; p.dot_src = q; p.dot_out = w.R;
     if ((rc = run_pass(tc, DQ, p, dtype, dtype, st)) != MLSTM_OK) return rc;
     // dK = ((V dH^T + g_c) * decay)  Q
     p.X = v; p.Y = dhp; p.Z = q;
-    p.row_e = w.ga; p.row_g = nullptr; p.col_e = w.gB; p.col_g = w.g;
+    p.row_rel = w.ga; p.row_ref = w.a_ref; p.row_g = nullptr; p.col_rel = w.gB; p.col_ref = w.An_ref; p.col_g = w.g;
     p.out = dk; p.dot_src = k; p.dot_out = w.dI;
     if ((rc = run_pass(tc, DK, p, dtype, dtype, st)) != MLSTM_OK) return rc;
     // dV = ((K Q^T) * decay / n) dH

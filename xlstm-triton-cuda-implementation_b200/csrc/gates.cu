@@ -8,7 +8,7 @@
 namespace mlstm {
 namespace {
 
-constexpr float LOG2E = 1.4426950408889634f;
+constexpr double LOG2E_D = 1.4426950408889634;
 constexpr int SCAN_THREADS = 1024;
 
 // Inclusive block scans over SCAN_THREADS elements (one per thread) with a running carry.
@@ -39,46 +39,54 @@ __device__ __forceinline__ double block_scan_add(double x, double* warp_tot, dou
     return x + before;
 }
 
-__device__ __forceinline__ float block_scan_max(float x, float* warp_tot, float& carry_smem_view) {
+__device__ __forceinline__ double block_scan_max(double x, double* warp_tot, double& carry_smem_view) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-        float y = __shfl_up_sync(0xffffffffu, x, o);
-        if (lane >= o) x = fmaxf(x, y);
+        double y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x = fmax(x, y);
     }
     if (lane == 31) warp_tot[warp] = x;
     __syncthreads();
     if (warp == 0) {
-        float t = warp_tot[lane];
+        double t = warp_tot[lane];
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            float y = __shfl_up_sync(0xffffffffu, t, o);
-            if (lane >= o) t = fmaxf(t, y);
+            double y = __shfl_up_sync(0xffffffffu, t, o);
+            if (lane >= o) t = fmax(t, y);
         }
         warp_tot[lane] = t;
     }
     __syncthreads();
-    const float before = fmaxf(warp > 0 ? warp_tot[warp - 1] : -INFINITY, carry_smem_view);
-    const float total = warp_tot[31];
+    const double before = fmax(warp > 0 ? warp_tot[warp - 1] : -INFINITY, carry_smem_view);
+    const double total = warp_tot[31];
     __syncthreads();
-    if (threadIdx.x == 0) carry_smem_view = fmaxf(carry_smem_view, total);
+    if (threadIdx.x == 0) carry_smem_view = fmax(carry_smem_view, total);
     __syncthreads();
-    return fmaxf(x, before);
+    return fmax(x, before);
 }
 
-// One block per slice.  ga = a*log2e, gAn = -A*log2e, m = F + A with F = cumsum(logsigmoid f),
-// a = i - F, A = running maximum of a.  The cumulative sum is carried in double so that a_c - A_r
-// keeps fp32 accuracy for long sequences.  Padding (t >= S): ga = -inf (a padded column contributes
-// exactly zero), gAn = 0.  m may be null.
+// One block per slice.  With F = cumsum(logsigmoid f), a = i - F, A = running maximum of a (all in
+// double), it writes m = F + A and the two gate vectors in log2 units, re-centred per block of
+// REF_BLOCK positions so that fp32 keeps its relative accuracy however long the sequence is:
+//   ga_rel[t]  = (a_t - a_first(block)) * log2e      a_ref[block]  = a_first * log2e      (double)
+//   gAn_rel[t] = (A_first(block) - A_t) * log2e      An_ref[block] = -A_first * log2e     (double)
+// A kernel forms exp2(col_rel[c] + float(row_rel[r] + row_ref[r / REF_BLOCK] + col_ref[c / REF_BLOCK])),
+// the bracket in double once per block of columns.  Padding (t >= S): ga_rel = -inf (a padded column
+// contributes exactly zero), gAn_rel = 0, references 0.  m may be null.
 template <typename T>
 __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __restrict__ f, const T* __restrict__ i,
-                                                                 float* __restrict__ ga, float* __restrict__ gAn,
+                                                                 float* __restrict__ ga_rel, float* __restrict__ gAn_rel,
+                                                                 double* __restrict__ a_ref, double* __restrict__ An_ref,
                                                                  float* __restrict__ m, int S, int Spad) {
     __shared__ double wsum[32];
-    __shared__ float wmax[32];
+    __shared__ double wmax[32];
     __shared__ double carry_sum;
-    __shared__ float carry_max;
+    __shared__ double carry_max;
+    __shared__ double ref_a[SCAN_THREADS / REF_BLOCK];
+    __shared__ double ref_A[SCAN_THREADS / REF_BLOCK];
     const int bh = blockIdx.x;
+    const int nref = Spad / REF_BLOCK;
     if (threadIdx.x == 0) {
         carry_sum = 0.0;
         carry_max = -INFINITY;
@@ -87,50 +95,69 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
     for (int base = 0; base < Spad; base += SCAN_THREADS) {
         const int t = base + threadIdx.x;
         const bool in = t < S;
-        double lf = 0.0;
-        float iv = 0.0f;
+        double lf = 0.0, iv = 0.0;
         if (in) {
             const double x = static_cast<double>(to_f32<T>(f[static_cast<size_t>(bh) * S + t]));
             lf = x < 0.0 ? x - log1p(exp(x)) : -log1p(exp(-x));  // logsigmoid
-            iv = to_f32<T>(i[static_cast<size_t>(bh) * S + t]);
+            iv = static_cast<double>(to_f32<T>(i[static_cast<size_t>(bh) * S + t]));
         }
         const double F = block_scan_add(lf, wsum, carry_sum);
-        const float a = in ? static_cast<float>(static_cast<double>(iv) - F) : -INFINITY;
-        const float A = block_scan_max(a, wmax, carry_max);
-        if (t < Spad) {
-            ga[static_cast<size_t>(bh) * Spad + t] = in ? a * LOG2E : -INFINITY;
-            gAn[static_cast<size_t>(bh) * Spad + t] = in ? -A * LOG2E : 0.0f;
+        const double a = in ? iv - F : -INFINITY;
+        const double A = block_scan_max(a, wmax, carry_max);
+        if ((threadIdx.x % REF_BLOCK) == 0) {
+            ref_a[threadIdx.x / REF_BLOCK] = in ? a : 0.0;
+            ref_A[threadIdx.x / REF_BLOCK] = in ? A : 0.0;
         }
-        if (in && m) m[static_cast<size_t>(bh) * S + t] = static_cast<float>(F + static_cast<double>(A));
+        __syncthreads();
+        if (t < Spad) {
+            const double ra = ref_a[threadIdx.x / REF_BLOCK], rA = ref_A[threadIdx.x / REF_BLOCK];
+            ga_rel[static_cast<size_t>(bh) * Spad + t] = in ? static_cast<float>((a - ra) * LOG2E_D) : -INFINITY;
+            gAn_rel[static_cast<size_t>(bh) * Spad + t] = in ? static_cast<float>((rA - A) * LOG2E_D) : 0.0f;
+            if ((threadIdx.x % REF_BLOCK) == 0) {
+                a_ref[static_cast<size_t>(bh) * nref + t / REF_BLOCK] = ra * LOG2E_D;
+                An_ref[static_cast<size_t>(bh) * nref + t / REF_BLOCK] = -rA * LOG2E_D;
+            }
+        }
+        if (in && m) m[static_cast<size_t>(bh) * S + t] = static_cast<float>(F + A);
+        __syncthreads();
     }
 }
 
 // One warp per row: delta = dh.h, n, db, and from them the two per-row vectors of the backward:
-//   gB = gAn + log2(scale / n),   g = db * n   (db = sign(b) * (-delta / n) * [|b| > exp(-m)],
-// mlstm_matmul.py:194-196 with the sum replaced by n*delta).  Optionally writes dh converted to the
-// 16-bit input type for the tensor-core passes.  Padding rows: gB = -inf, g = 0.
+//   gB_rel = gAn_rel + log2(scale / n)  (same block references as gAn_rel),   g = db * n
+// (db = sign(b) * (-delta / n) * [|b| > exp(-m)], mlstm_matmul.py:194-196 with the sum replaced by
+// n*delta).  Optionally writes dh converted to the 16-bit input type for the tensor-core passes.
+// Rows are read with 16-byte accesses.  Padding rows: gB_rel = -inf, g = 0.
 template <typename HT, typename T16>
 __global__ void bwd_prep_kernel(const HT* __restrict__ h, const HT* __restrict__ dh, const float* __restrict__ b,
-                                const float* __restrict__ m, const float* __restrict__ gAn, float* __restrict__ gB,
-                                float* __restrict__ g, T16* __restrict__ dh16, int BH, int S, int Spad, int D,
-                                float log2_scale) {
+                                const float* __restrict__ m, const float* __restrict__ gAn_rel,
+                                float* __restrict__ gB_rel, float* __restrict__ g, T16* __restrict__ dh16, int BH, int S,
+                                int Spad, int D, float log2_scale) {
+    constexpr int VEC = 16 / sizeof(HT);
     const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (warp_global >= BH * Spad) return;
     const int bh = warp_global / Spad, t = warp_global % Spad;
     if (t >= S) {
         if (lane == 0) {
-            gB[warp_global] = -INFINITY;
+            gB_rel[warp_global] = -INFINITY;
             g[warp_global] = 0.0f;
         }
         return;
     }
     const size_t row = (static_cast<size_t>(bh) * S + t) * D;
     float delta = 0.0f;
-    for (int d = lane; d < D; d += 32) {
-        const float dv = to_f32<HT>(dh[row + d]);
-        delta += dv * to_f32<HT>(h[row + d]);
-        if (dh16) dh16[row + d] = from_f32<T16>(dv);
+    for (int d = lane * VEC; d < D; d += 32 * VEC) {
+        const uint4 hraw = *reinterpret_cast<const uint4*>(h + row + d);
+        const uint4 draw = *reinterpret_cast<const uint4*>(dh + row + d);
+        const HT* hv = reinterpret_cast<const HT*>(&hraw);
+        const HT* dv = reinterpret_cast<const HT*>(&draw);
+#pragma unroll
+        for (int j = 0; j < VEC; j++) {
+            const float x = to_f32<HT>(dv[j]);
+            delta += x * to_f32<HT>(hv[j]);
+            if (dh16) dh16[row + d + j] = from_f32<T16>(x);
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) delta += __shfl_xor_sync(0xffffffffu, delta, o);
@@ -143,7 +170,7 @@ __global__ void bwd_prep_kernel(const HT* __restrict__ h, const HT* __restrict__
         const float db = (fabsf(bb) > em) ? sgn * (-delta / n) : 0.0f;
         const float gg = db * n;
         g[warp_global] = isfinite(gg) ? gg : 0.0f;
-        gB[warp_global] = gAn[warp_global] + (log2_scale - log2f(n));
+        gB_rel[warp_global] = gAn_rel[warp_global] + (log2_scale - log2f(n));
     }
 }
 
@@ -180,18 +207,18 @@ __global__ void __launch_bounds__(SCAN_THREADS) df_kernel(const T* __restrict__ 
 
 }  // namespace
 
-int launch_gates_fwd(const void* f, const void* i, float* ga, float* gA, float* m, int BH, int S, int Spad, int dtype,
-                     cudaStream_t st) {
+int launch_gates_fwd(const void* f, const void* i, float* ga, float* gA, double* a_ref, double* An_ref, float* m, int BH,
+                     int S, int Spad, int dtype, cudaStream_t st) {
     switch (dtype) {
         case MLSTM_DT_F32:
-            gates_fwd_kernel<float><<<BH, SCAN_THREADS, 0, st>>>((const float*)f, (const float*)i, ga, gA, m, S, Spad);
+            gates_fwd_kernel<float><<<BH, SCAN_THREADS, 0, st>>>((const float*)f, (const float*)i, ga, gA, a_ref, An_ref, m, S, Spad);
             break;
         case MLSTM_DT_F16:
-            gates_fwd_kernel<__half><<<BH, SCAN_THREADS, 0, st>>>((const __half*)f, (const __half*)i, ga, gA, m, S, Spad);
+            gates_fwd_kernel<__half><<<BH, SCAN_THREADS, 0, st>>>((const __half*)f, (const __half*)i, ga, gA, a_ref, An_ref, m, S, Spad);
             break;
         case MLSTM_DT_BF16:
             gates_fwd_kernel<__nv_bfloat16>
-                <<<BH, SCAN_THREADS, 0, st>>>((const __nv_bfloat16*)f, (const __nv_bfloat16*)i, ga, gA, m, S, Spad);
+                <<<BH, SCAN_THREADS, 0, st>>>((const __nv_bfloat16*)f, (const __nv_bfloat16*)i, ga, gA, a_ref, An_ref, m, S, Spad);
             break;
         default: return MLSTM_E_ARG;
     }

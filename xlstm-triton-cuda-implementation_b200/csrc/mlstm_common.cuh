@@ -12,7 +12,8 @@
 //   W = (T + g) * exp2(ec[c] + er[r])   on the causal side of the diagonal, 0 elsewhere
 //   ACC += W Z (contraction over the streamed tile's 128 rows)
 // with (scale = 1/sqrt(D), log2 units, "gA" = A*log2e, "ga" = a*log2e, ln_r = log2(scale / n_r);
-// the gate pass stores gAn = -gA and the backward preparation stores gB = gAn + ln):
+// the gate pass stores ga and -gA, the backward preparation -gA + ln, each re-centred per block of
+// REF_BLOCK positions around a double reference, see gates.cu):
 //   FWD  rows = queries  X=Q  Y=K  Z=V   er = -gA_r + log2(scale)  ec = ga_c       g = 0         out = ACC / n_r
 //   DQ   rows = queries  X=dH Y=V  Z=K   er = -gA_r + ln_r         ec = ga_c       g = db_r n_r  out = ACC
 //   DK   rows = keys     X=V  Y=dH Z=Q   er = ga_r                 ec = -gA_c+ln_c g = db_c n_c  out = ACC
@@ -31,7 +32,8 @@ namespace mlstm {
 
 enum Mode : int { FWD = 0, DQ = 1, DK = 2, DV = 3 };
 
-constexpr int TILE = 128;  // rows of a tensor-core tile; gate vectors are padded to a multiple of it
+constexpr int TILE = 128;      // rows of a tensor-core tile; gate vectors are padded to a multiple of it
+constexpr int REF_BLOCK = 64;  // positions per reference block of the re-centred gate vectors (gates.cu)
 
 __host__ __device__ inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
@@ -44,11 +46,15 @@ struct PassParams {
     const void* X;  // stationary operand  [BH, S, D]
     const void* Y;  // first streamed operand
     const void* Z;  // second streamed operand
-    const float* row_e;  // er without the constant term, [BH, Spad]
-    const float* row_g;  // g per row (DQ) or nullptr
-    const float* col_e;  // ec, [BH, Spad]
-    const float* col_g;  // g per column (DK) or nullptr
-    float er_add;        // constant added to er (FWD: log2(scale))
+    // er[r] + ec[c] = col_rel[c] + float(row_rel[r] + row_ref[r / REF_BLOCK] + col_ref[c / REF_BLOCK] + er_add):
+    // the gate vectors are stored relative to a double reference per block of REF_BLOCK positions
+    const float* row_rel;   // [BH, Spad]
+    const double* row_ref;  // [BH, Spad / REF_BLOCK]
+    const float* row_g;     // g per row (DQ) or nullptr
+    const float* col_rel;   // [BH, Spad]
+    const double* col_ref;  // [BH, Spad / REF_BLOCK]
+    const float* col_g;     // g per column (DK) or nullptr
+    float er_add;           // constant term of er (FWD: log2(scale))
     void* out;           // [BH, S, D], element type chosen by the kernel template
     // FWD only
     const float* m;      // [BH, S] stabiliser, written by the gate pass
@@ -94,8 +100,8 @@ __device__ __forceinline__ bool causal_ok(int row, int col) {
 }
 
 // Launchers implemented in the .cu files.  All return an MLSTM_* status and never synchronise.
-int launch_gates_fwd(const void* f, const void* i, float* ga, float* gAn, float* m, int BH, int S, int Spad,
-                     int dtype, cudaStream_t st);
+int launch_gates_fwd(const void* f, const void* i, float* ga_rel, float* gAn_rel, double* a_ref, double* An_ref, float* m,
+                     int BH, int S, int Spad, int dtype, cudaStream_t st);
 int launch_bwd_prep(const void* h, const void* dh, const float* b, const float* m, const float* gAn, float* gB,
                     float* g, void* dh16, int BH, int S, int Spad, int D, int h_dtype, int dtype, cudaStream_t st);
 int launch_df(const void* f, const float* dI, const float* R, void* df, void* di, int BH, int S, int Spad, int dtype,

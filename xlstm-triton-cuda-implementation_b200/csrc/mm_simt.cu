@@ -42,12 +42,15 @@ __global__ void __launch_bounds__(256) mlstm_simt_pass(const PassParams p) {
     const InT* Y = reinterpret_cast<const InT*>(p.Y) + slice;
     const InT* Z = reinterpret_cast<const InT*>(p.Z) + slice;
 
-    float er[4], gr_[4];
+    static_assert(BT == REF_BLOCK, "one streamed tile = one reference block of the gate vectors");
+    const size_t ref = static_cast<size_t>(bh) * (p.Spad / REF_BLOCK);
+    double er_d[4];
+    float gr_[4];
     int rows[4];
 #pragma unroll
     for (int rr = 0; rr < 4; rr++) {
         rows[rr] = tile * BT + ty * 4 + rr;
-        er[rr] = p.row_e[vec + rows[rr]] + p.er_add;
+        er_d[rr] = static_cast<double>(p.row_rel[vec + rows[rr]]) + p.row_ref[ref + tile] + static_cast<double>(p.er_add);
         gr_[rr] = (MODE == DQ) ? p.row_g[vec + rows[rr]] : 0.0f;
     }
     float acc[4][4] = {};
@@ -79,10 +82,13 @@ __global__ void __launch_bounds__(256) mlstm_simt_pass(const PassParams p) {
             __syncthreads();
         }
         // gate the tile
+        float er[4];
+#pragma unroll
+        for (int rr = 0; rr < 4; rr++) er[rr] = static_cast<float>(er_d[rr] + p.col_ref[ref + st]);
 #pragma unroll
         for (int cc = 0; cc < 4; cc++) {
             const int col = st * BT + tx * 4 + cc;
-            const float ec = p.col_e[vec + col];
+            const float ec = p.col_rel[vec + col];
             const float gc = (MODE == DK) ? p.col_g[vec + col] : 0.0f;
 #pragma unroll
             for (int rr = 0; rr < 4; rr++) {

@@ -198,7 +198,10 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const int grow = tile * TILE + r;              // row inside the slice (may be >= S in the last tile)
         const size_t vec_base = static_cast<size_t>(bh) * p.Spad;
-        const float er = p.row_e[vec_base + grow] + p.er_add;
+        const size_t ref_base = static_cast<size_t>(bh) * (p.Spad / REF_BLOCK);
+        // row part of the exponent in double; the column block's reference is added per block
+        const double er_d = static_cast<double>(p.row_rel[vec_base + grow]) + p.row_ref[ref_base + grow / REF_BLOCK] +
+                            static_cast<double>(p.er_add);
         const float g_row = (MODE == DQ) ? p.row_g[vec_base + grow] : 0.0f;
         float rowsum = 0.0f;
         bool ok = true;
@@ -210,13 +213,16 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             tc_fence_after();
             const int st = stream_tile(t);
             const bool diag = (st == tile);
-            const float4* ce4 = reinterpret_cast<const float4*>(p.col_e + vec_base + st * TILE);
+            const float4* ce4 = reinterpret_cast<const float4*>(p.col_rel + vec_base + st * TILE);
+            const double* cref = p.col_ref + ref_base + st * (TILE / REF_BLOCK);
+            const float er_blk[2] = {static_cast<float>(er_d + cref[0]), static_cast<float>(er_d + cref[1])};
             const float4* cg4 = (MODE == DK) ? reinterpret_cast<const float4*>(p.col_g + vec_base + st * TILE) : nullptr;
             const uint32_t t_tmem = tmem_T0 + buf * 128 + lane_bits;
 #pragma unroll 1
             for (int ch = 0; ch < 4; ch++) {
                 uint32_t tv[32];
                 tmem_ld32(t_tmem + ch * 32, tv);
+                const float er = er_blk[ch >> 1];
                 float wv[32];
 #pragma unroll
                 for (int q4 = 0; q4 < 8; q4++) {
