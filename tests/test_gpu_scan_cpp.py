@@ -81,3 +81,17 @@ def test_cpp_forward_against_reference_golden(gc, golden_dir, name):
     gc._lib.read_status(ws, dev, "mlstm_forward_f16")
     diff = (H.float().cpu() - torch.from_numpy(z["H"]).float()).abs()
     assert int((diff > 0.01).sum()) == 0, float(diff.max())
+
+
+@pytest.mark.parametrize("S", [640, 1280])
+def test_cpp_driver_program(gc, S):
+    """The C++ driver program (tests/cpp/driver_forward.cu): reference recipe inputs, launch through
+    include/mlstm_forward.cuh with the reference's template arguments, reference-style check."""
+    import os
+    import subprocess
+    exe = os.path.join(os.path.dirname(os.path.abspath(__file__)), "cpp", "driver_forward")
+    if not os.path.exists(exe):
+        pytest.fail("tests/cpp/driver_forward not built: run __graft_entry__.build()")
+    r = subprocess.run([exe, str(S)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "Non_matching count: 0" in r.stdout
