@@ -33,6 +33,7 @@ extern "C" {
 #define MLSTM_E_WORKSPACE (-5)   /* workspace missing or too small                               */
 #define MLSTM_E_CUDA (-6)        /* a CUDA runtime or driver call failed                         */
 #define MLSTM_E_TIMEOUT (-7)     /* a kernel gave up on an internal wait (see mlstm_read_status) */
+#define MLSTM_E_STATIC_LIMIT (-8) /* S beyond what mlstm_forward_f16_static's built-in scratch holds */
 
 /* flags */
 #define MLSTM_F_FORCE_SIMT 1 /* use the CUDA-core kernels even where the tensor-core path applies */
@@ -84,6 +85,25 @@ int mlstm_scan_fwd(const void* q, const void* k, const void* v, const void* f, c
 size_t mlstm_forward_f16_workspace(unsigned S, unsigned D);
 int mlstm_forward_f16(const void* Q, const void* K, const void* V, const void* F, const void* I, void* H,
                       unsigned S, unsigned D, void* workspace, size_t workspace_bytes, void* stream);
+
+/* The same forward as mlstm_forward_f16 for callers that cannot supply scratch memory.
+ * No counterpart in the reference: its launcher has no scratch because its kernel needs none.
+ * Who needs it: callers that are not allowed to call cudaMalloc at the point of use (on a
+ * latency-critical path, because cudaMalloc/cudaFree stall the whole device; in a process with a
+ * fixed memory budget and no allocator of its own) and that use the reference driver's argument list
+ * (Q, K, V, F, I, H, S), which has no room for a workspace.  The scratch is a fixed array inside the
+ * library's device image: MLSTM_STATIC_SCRATCH_BYTES per GPU that loads the library, held until the
+ * process exits.  Limits and rules:
+ *   - S <= MLSTM_STATIC_MAX_S, else MLSTM_E_STATIC_LIMIT (use mlstm_forward_f16 with a workspace);
+ *   - the first call on each device looks the array's device address up (cudaGetSymbolAddress, with
+ *     that device current): make that first call outside any stream capture;
+ *   - it calls no cudaMalloc, cudaFree or other allocating routine, on any call;
+ *   - all calls on a device share the one array; calls whose kernels may overlap on the GPU race.
+ *     Order them on one stream or with events. */
+#define MLSTM_STATIC_MAX_S 16384u
+#define MLSTM_STATIC_SCRATCH_BYTES 266496u
+int mlstm_forward_f16_static(const void* Q, const void* K, const void* V, const void* F, const void* I, void* H,
+                             unsigned S, unsigned D, void* stream);
 
 /* Copies the workspace's device status word to *host_status after synchronising `stream`.
  * Returns MLSTM_OK, or MLSTM_E_TIMEOUT when the word is non-zero, or MLSTM_E_CUDA. */

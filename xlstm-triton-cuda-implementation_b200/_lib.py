@@ -56,6 +56,8 @@ def lib():
     L.mlstm_forward_f16_workspace.argtypes = [u32, u32]
     L.mlstm_forward_f16.restype = i32
     L.mlstm_forward_f16.argtypes = [vp] * 6 + [u32, u32, vp, sz, vp]
+    L.mlstm_forward_f16_static.restype = i32
+    L.mlstm_forward_f16_static.argtypes = [vp] * 6 + [u32, u32, vp]
     L.mlstm_read_status.restype = i32
     L.mlstm_read_status.argtypes = [vp, ctypes.POINTER(i32), vp]
     _lib = L
@@ -65,7 +67,7 @@ def lib():
 EXPORTS = [
     "mlstm_status_string", "mlstm_tc_supported", "mlstm_mm_fwd_workspace", "mlstm_mm_fwd",
     "mlstm_mm_bwd_workspace", "mlstm_mm_bwd", "mlstm_scan_fwd_workspace", "mlstm_scan_fwd",
-    "mlstm_forward_f16_workspace", "mlstm_forward_f16", "mlstm_read_status",
+    "mlstm_forward_f16_workspace", "mlstm_forward_f16", "mlstm_forward_f16_static", "mlstm_read_status",
 ]
 
 

@@ -1,6 +1,7 @@
 // extern "C" entry points of libmlstm_b200.so (declared in include/mlstm_b200.h): argument checks,
 // workspace carving and the launch sequences.  Nothing here allocates or synchronises.
 #include <cmath>
+#include <mutex>
 
 #include "mlstm_common.cuh"
 
@@ -136,6 +137,9 @@ const char* mlstm_status_string(int s) {
         case MLSTM_E_WORKSPACE: return "workspace missing or too small";
         case MLSTM_E_CUDA: return "CUDA runtime or driver call failed";
         case MLSTM_E_TIMEOUT: return "a kernel gave up on an internal wait";
+        case MLSTM_E_STATIC_LIMIT:
+            return "sequence too long for the built-in scratch of mlstm_forward_f16_static (S <= 16384); "
+                   "use mlstm_forward_f16 with a workspace";
     }
     return "unknown status";
 }
@@ -245,6 +249,69 @@ int mlstm_forward_f16(const void* Q, const void* K, const void* V, const void* F
     if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(H)) return MLSTM_E_ALIGN;
     FwdWs w = carve_fwd(workspace, 1, static_cast<int>(S), true);
     if (!workspace || workspace_bytes < w.bytes || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
+    return forward_impl(Q, K, V, F, I, nullptr, H, w.m, w.b, w, 1, static_cast<int>(S), static_cast<int>(D), MLSTM_DT_F16,
+                        MLSTM_DT_F16, 0, static_cast<cudaStream_t>(stream));
+}
+
+// ------------------------------------------------------------------------------------------------
+// Single-head fp16 forward for callers that have no way to hand over scratch memory.
+//
+// The C++ driver's launch (Q, K, V, F, I, H, S) has no workspace argument, and some of its callers
+// cannot create one: code on a latency-critical path, where cudaMalloc and cudaFree serialise the
+// whole device, and embedders that were given a fixed memory budget and no allocator.  For them the
+// scratch of the forward (status word, the two gate vectors with their block references, m and b)
+// lives in one array in the library's device image.  It costs MLSTM_STATIC_SCRATCH_BYTES on every
+// GPU that loads the library, for as long as the process lives, hence the modest length limit.
+//
+// In host code the array's name is only a handle of the host-side shadow; its device address comes
+// from cudaGetSymbolAddress, asked once per device with that device current, on the first call
+// there.  That first call must therefore not happen inside a stream capture.  All calls on one
+// device share the array: the status word is cleared at the start of each call, everything else is
+// rewritten before it is read, and two calls whose kernels overlap on the GPU (different streams,
+// no dependency) corrupt each other.
+constexpr unsigned STATIC_MAX_S = MLSTM_STATIC_MAX_S;
+constexpr size_t static_scratch_bytes(size_t S) {
+    const size_t spad = (S + TILE - 1) / TILE * TILE;
+    const size_t a = 256;
+    const size_t vec = (spad * 4 + a - 1) / a * a;
+    const size_t ref = (spad / REF_BLOCK * 8 + a - 1) / a * a;
+    const size_t row = (S * 4 + a - 1) / a * a;
+    return a + 2 * vec + 2 * ref + 2 * row;
+}
+static_assert(static_scratch_bytes(STATIC_MAX_S) == MLSTM_STATIC_SCRATCH_BYTES, "keep the header's figure in step");
+static __device__ __align__(256) unsigned char g_static_scratch[MLSTM_STATIC_SCRATCH_BYTES];
+
+static int static_scratch_address(void** out) {
+    constexpr int MAX_DEVICES = 64;
+    static std::mutex mu;
+    static void* addr[MAX_DEVICES] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return MLSTM_E_CUDA;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!addr[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) {
+            cudaGetLastError();
+            return MLSTM_E_CUDA;
+        }
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return MLSTM_OK;
+}
+
+int mlstm_forward_f16_static(const void* Q, const void* K, const void* V, const void* F, const void* I, void* H,
+                             unsigned S, unsigned D, void* stream) {
+    if (!Q || !K || !V || !F || !I || !H) return MLSTM_E_ARG;
+    if (S == 0 || D == 0 || D > 0x7fffffffu) return MLSTM_E_ARG;
+    if (S > STATIC_MAX_S) return MLSTM_E_STATIC_LIMIT;
+    int rc = check_dims(1, 1, static_cast<int>(S), static_cast<int>(D));
+    if (rc != MLSTM_OK) return rc;
+    if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(H)) return MLSTM_E_ALIGN;
+    void* scratch = nullptr;
+    if ((rc = static_scratch_address(&scratch)) != MLSTM_OK) return rc;
+    FwdWs w = carve_fwd(scratch, 1, static_cast<int>(S), true);
+    if (w.bytes > MLSTM_STATIC_SCRATCH_BYTES) return MLSTM_E_STATIC_LIMIT;
     return forward_impl(Q, K, V, F, I, nullptr, H, w.m, w.b, w, 1, static_cast<int>(S), static_cast<int>(D), MLSTM_DT_F16,
                         MLSTM_DT_F16, 0, static_cast<cudaStream_t>(stream));
 }
