@@ -9,10 +9,10 @@
 // slice and streams the tiles on the causal side of it.  Warp roles (384 threads):
 //   warp 0      TMA producer: stationary tile once, then streamed tiles through a ring of slots
 //   warp 1      MMA issuer (one thread) and TMEM allocator
-//   warps 4-7   gate group 0: turns even steps' T tiles into gated 16-bit W tiles, in TMEM
-//   warps 8-11  gate group 1: odd steps
-// TMEM (512 columns): T0 [0,128) and T1 [128,256) fp32 128x128, W aliases the first 64 columns of
-// its T (two 16-bit values per column), ACC [256, 256+D) fp32 128xD.
+//   warps 4-7   gate group 0: turns columns [0,64) of every T tile into gated 16-bit W values, in TMEM
+//   warps 8-11  gate group 1: columns [64,128)
+// TMEM (512 columns): T0 [0,128) and T1 [128,256) fp32 128x128; each group writes its half of W
+// (two 16-bit values per column) over the first 32 of its own 64 T columns; ACC [256, 256+D) fp32.
 // The second contraction reads W straight from TMEM as the A operand and the streamed Z tile from
 // shared memory as an MN-major B operand, so the gated tile never touches shared or global memory.
 //
@@ -30,6 +30,7 @@ using namespace ptx;
 constexpr int NTHREADS = 384;
 constexpr int BOX_BYTES = 128 * 128;  // one TMA box: 128 rows of 128 bytes (64 16-bit elements)
 constexpr long long WAIT_LIMIT = 4000000000LL;  // cycles (about two seconds)
+constexpr int SLICE_SET = 8;                    // slices whose CTAs are interleaved in launch order
 
 template <int D>
 struct TcCfg {
@@ -74,8 +75,17 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int NT = p.Spad / TILE;
-    const int bh = blockIdx.x % p.BH;
-    const int w = blockIdx.x / p.BH;  // heaviest tiles are launched first
+    // CTA order: slices in sets of SLICE_SET; inside a set the heaviest tiles come first.  The CTAs
+    // resident at one time then share the K/V (or Q/dH) of a few slices, which stay in L2.
+    int bh, w;
+    {
+        const int per_set = NT * SLICE_SET;
+        const int set = blockIdx.x / per_set;
+        const int within = blockIdx.x - set * per_set;
+        const int set_size = min(SLICE_SET, p.BH - set * SLICE_SET);
+        w = within / set_size;
+        bh = set * SLICE_SET + (within - w * set_size);
+    }
     const int tile = ROWS_ARE_Q ? (NT - 1 - w) : w;
     const int nsteps = ROWS_ARE_Q ? (tile + 1) : (NT - tile);
     // streamed tile of step t: FWD/DQ visit key tiles 0..tile (diagonal last), DK/DV visit query
@@ -90,8 +100,8 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         }
         mbar_init(&bar_t[0], 1);
         mbar_init(&bar_t[1], 1);
-        mbar_init(&bar_w[0], 128);
-        mbar_init(&bar_w[1], 128);
+        mbar_init(&bar_w[0], 256);
+        mbar_init(&bar_w[1], 256);
         mbar_init(bar_acc, 1);
         mbar_init(bar_part, 256);
         *abort_flag = 0;
@@ -162,7 +172,9 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
 #pragma unroll
                     for (int kk = 0; kk < 8; kk++) {  // 16 streamed rows per MMA
                         const uint64_t bdesc = smem_desc_sw128(zaddr + kk * 2048, BOX_BYTES, 1024);
-                        mma_ts<false>(tmem_ACC + hf * C::CH, w_tmem + kk * 8, bdesc, idesc2, (u > 0 || kk > 0) ? 1u : 0u);
+                        // W rows 0-63 of the streamed tile sit in columns [0,32), rows 64-127 in columns [64,96)
+                        const uint32_t a_tmem = w_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
+                        mma_ts<false>(tmem_ACC + hf * C::CH, a_tmem, bdesc, idesc2, (u > 0 || kk > 0) ? 1u : 0u);
                     }
                     tc_commit(&bar_empty[s]);
                 }
@@ -206,62 +218,66 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         float rowsum = 0.0f;
         bool ok = true;
 
-        for (int t = grp; t < nsteps; t += 2) {
+        // Both groups work on every step: group g gates columns [64g, 64g+64) of the T tile (one
+        // reference block of the gate vectors) and writes its half of W over the first 32 of them.
+        const int cbase = grp * 64;
+        auto load_cols = [&](const float* base, int sub, float (&dst)[32]) {
+            const float4* p4 = reinterpret_cast<const float4*>(base + cbase + sub * 32);
+#pragma unroll
+            for (int q4 = 0; q4 < 8; q4++) {
+                const float4 e4 = __ldg(p4 + q4);
+                dst[q4 * 4 + 0] = e4.x; dst[q4 * 4 + 1] = e4.y; dst[q4 * 4 + 2] = e4.z; dst[q4 * 4 + 3] = e4.w;
+            }
+        };
+        for (int t = 0; t < nsteps; t++) {
             const int buf = t & 1;
+            const int st = stream_tile(t);
+            const bool diag = (st == tile);
+            const float* ce = p.col_rel + vec_base + st * TILE;
+            // column terms do not depend on the contraction: fetch the first half before waiting
+            float cv[32];
+            load_cols(ce, 0, cv);
+            const float er = static_cast<float>(er_d + p.col_ref[ref_base + st * (TILE / REF_BLOCK) + grp]);
             ok = mbar_wait(&bar_t[buf], (t >> 1) & 1, abort_flag, WAIT_LIMIT);
             if (!ok) break;
             tc_fence_after();
-            const int st = stream_tile(t);
-            const bool diag = (st == tile);
-            const float4* ce4 = reinterpret_cast<const float4*>(p.col_rel + vec_base + st * TILE);
-            const double* cref = p.col_ref + ref_base + st * (TILE / REF_BLOCK);
-            const float er_blk[2] = {static_cast<float>(er_d + cref[0]), static_cast<float>(er_d + cref[1])};
-            const float4* cg4 = (MODE == DK) ? reinterpret_cast<const float4*>(p.col_g + vec_base + st * TILE) : nullptr;
-            const uint32_t t_tmem = tmem_T0 + buf * 128 + lane_bits;
-#pragma unroll 1
-            for (int ch = 0; ch < 4; ch++) {
-                uint32_t tv[32];
-                tmem_ld32(t_tmem + ch * 32, tv);
-                const float er = er_blk[ch >> 1];
-                float wv[32];
+            const uint32_t t_tmem = tmem_T0 + buf * 128 + lane_bits + cbase;
+            uint32_t tv0[32], tv1[32];
+            tmem_ld32(t_tmem, tv0);
+            tmem_ld32(t_tmem + 32, tv1);
+            uint32_t pk[32];
+            tc_wait_ld();
 #pragma unroll
-                for (int q4 = 0; q4 < 8; q4++) {
-                    const float4 e4 = __ldg(ce4 + ch * 8 + q4);
-                    wv[q4 * 4 + 0] = e4.x; wv[q4 * 4 + 1] = e4.y; wv[q4 * 4 + 2] = e4.z; wv[q4 * 4 + 3] = e4.w;
-                }
-                tc_wait_ld();
+            for (int sub = 0; sub < 2; sub++) {
+                uint32_t (&tv)[32] = sub == 0 ? tv0 : tv1;
+                if (sub == 1) load_cols(ce, 1, cv);
                 if (MODE == DK) {
+                    float gv[32];
+                    load_cols(p.col_g + vec_base + st * TILE, sub, gv);
 #pragma unroll
-                    for (int q4 = 0; q4 < 8; q4++) {
-                        const float4 g4 = __ldg(cg4 + ch * 8 + q4);
-                        tv[q4 * 4 + 0] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 0]) + g4.x);
-                        tv[q4 * 4 + 1] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 1]) + g4.y);
-                        tv[q4 * 4 + 2] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 2]) + g4.z);
-                        tv[q4 * 4 + 3] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 3]) + g4.w);
-                    }
+                    for (int j = 0; j < 32; j++) tv[j] = __float_as_uint(__uint_as_float(tv[j]) + gv[j]);
                 }
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
                     float tval = __uint_as_float(tv[j]);
                     if (MODE == DQ) tval += g_row;
-                    float wj = tval * fast_exp2(wv[j] + er);
-                    if (diag && !causal_ok<MODE>(r, ch * 32 + j)) wj = 0.0f;
-                    wv[j] = wj;
+                    float wj = tval * fast_exp2(cv[j] + er);
+                    if (diag && !causal_ok<MODE>(r, cbase + sub * 32 + j)) wj = 0.0f;
+                    cv[j] = wj;
                     if (MODE == FWD) rowsum += wj;
                 }
-                uint32_t pk[16];
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     if constexpr (ABFMT == 1) {
-                        __nv_bfloat162 v2 = __floats2bfloat162_rn(wv[2 * j], wv[2 * j + 1]);
-                        pk[j] = *reinterpret_cast<uint32_t*>(&v2);
+                        __nv_bfloat162 v2 = __floats2bfloat162_rn(cv[2 * j], cv[2 * j + 1]);
+                        pk[sub * 16 + j] = *reinterpret_cast<uint32_t*>(&v2);
                     } else {
-                        __half2 v2 = __floats2half2_rn(wv[2 * j], wv[2 * j + 1]);
-                        pk[j] = *reinterpret_cast<uint32_t*>(&v2);
+                        __half2 v2 = __floats2half2_rn(cv[2 * j], cv[2 * j + 1]);
+                        pk[sub * 16 + j] = *reinterpret_cast<uint32_t*>(&v2);
                     }
                 }
-                tmem_st16(t_tmem + ch * 16, pk);
             }
+            tmem_st32(t_tmem, pk);
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(&bar_w[buf]);
