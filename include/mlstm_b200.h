@@ -105,6 +105,31 @@ int mlstm_forward_f16(const void* Q, const void* K, const void* V, const void* F
 int mlstm_forward_f16_static(const void* Q, const void* K, const void* V, const void* F, const void* I, void* H,
                              unsigned S, unsigned D, void* stream);
 
+/* Chunkwise forward for long sequences, with a state that can be carried across segments (GPUs).
+ * The reference has no such entry point; the mechanism it extends is the scan path's inter-block carry
+ * (mlstm_scan.py:143-195, operators :15-26).  16-bit inputs, D = 128, chunk a multiple of 128.
+ * A segment is processed in this order (all on one stream, one workspace):
+ *   mlstm_chunk_gate_summary  (optional, sequence-parallel only) local {F_end, A_end} per slice with no
+ *                             carry, from which the caller derives every segment's carry_in
+ *   mlstm_chunk_prepare       gates (with carry_in[bh] = {F, A} of the preceding segments, or NULL) and
+ *                             the per-block states; summary_out[bh] = {F_end, A_end} incl. the carry
+ *   mlstm_chunk_local_state   (optional) the state this segment adds: S_end [B,NH,D,D] (key, value),
+ *                             z_end [B,NH,D], stabilised by A_end
+ *   mlstm_chunk_apply         h for the segment, given the inbound state (S_in, z_in stabilised by the
+ *                             carried-in A, or NULL/NULL); optionally the outbound state S_out, z_out
+ * summary / carry arrays are device doubles [B*NH][2] in natural-log units. */
+size_t mlstm_chunk_workspace(int B, int NH, int S, int D, int dtype, int chunk);
+int mlstm_chunk_gate_summary(const void* f, const void* i, double* summary, int B, int NH, int S, int dtype,
+                             void* stream);
+int mlstm_chunk_prepare(const void* k, const void* v, const void* f, const void* i, const double* carry_in,
+                        double* summary_out, void* workspace, size_t workspace_bytes, int B, int NH, int S, int D,
+                        int dtype, int chunk, void* stream);
+int mlstm_chunk_local_state(void* workspace, size_t workspace_bytes, float* S_end, float* z_end, int B, int NH, int S,
+                            int D, int dtype, int chunk, void* stream);
+int mlstm_chunk_apply(const void* q, const void* k, const void* v, const float* S_in, const float* z_in, void* h,
+                      int h_dtype, float* S_out, float* z_out, void* workspace, size_t workspace_bytes, int B, int NH,
+                      int S, int D, int dtype, int chunk, void* stream);
+
 /* Copies the workspace's device status word to *host_status after synchronising `stream`.
  * Returns MLSTM_OK, or MLSTM_E_TIMEOUT when the word is non-zero, or MLSTM_E_CUDA. */
 int mlstm_read_status(const void* workspace, int* host_status, void* stream);

@@ -62,3 +62,57 @@ def backward(dh, q, k, v, f, i, h, m, b, round_w=None):
     dF[..., 1:] = torch.sigmoid(-f.double()[..., 1:]) * G[..., :-1]
     R_identity = delta + db * b
     return dQ, dK, dV, dF, dI, R, R_identity
+
+
+class ChunkSegmentModel:
+    """Dense fp64 model of the chunkwise segment stages (same interface as the library's
+    ChunkSegment: gate_summary / prepare / local_state / apply), used to test the sequence-parallel
+    protocol on CPU.  State convention as in the library: S[key, value] = sum_j exp(a_j - A_ref) k_j v_j^T,
+    z[key] = sum_j exp(a_j - A_ref) k_j, with a = i - F in global terms and A its prefix maximum."""
+
+    def __init__(self, q, k, v, f, i, chunk_size=256):
+        self.q, self.k, self.v = (t.double().flatten(0, 1) for t in (q, k, v))   # [BH, S, D]
+        self.f, self.i = f.double().flatten(0, 1), i.double().flatten(0, 1)      # [BH, S]
+        self.shape = q.shape
+        self.chunk = chunk_size
+
+    def _gates(self, F_in, A_in):
+        Fc = torch.cumsum(F.logsigmoid(self.f), -1) + F_in[:, None]
+        a = self.i - Fc
+        A = torch.maximum(torch.cummax(a, -1)[0], A_in[:, None])
+        return Fc, a, A
+
+    def gate_summary(self):
+        BH = self.f.shape[0]
+        Fc, a, A = self._gates(torch.zeros(BH, dtype=torch.float64), torch.full((BH,), -float("inf"), dtype=torch.float64))
+        return torch.stack([Fc[:, -1], A[:, -1]], 1)
+
+    def prepare(self, carry_in=None):
+        BH = self.f.shape[0]
+        if carry_in is None:
+            carry_in = torch.stack([torch.zeros(BH, dtype=torch.float64),
+                                    torch.full((BH,), -float("inf"), dtype=torch.float64)], 1)
+        self.A_in = carry_in[:, 1].double()
+        self.Fc, self.a, self.A = self._gates(carry_in[:, 0].double(), self.A_in)
+        return torch.stack([self.Fc[:, -1], self.A[:, -1]], 1)
+
+    def local_state(self):
+        w = torch.exp(self.a - self.A[:, -1:])                                   # [BH, S]
+        S = torch.einsum("bs,bsk,bsv->bkv", w, self.k, self.v)
+        z = torch.einsum("bs,bsk->bk", w, self.k)
+        return S.float(), z.float()
+
+    def apply(self, state_in=None, h_dtype=torch.float32, return_state=False):
+        B, NH, S, D = self.shape
+        mask = torch.tril(torch.ones(S, S, dtype=torch.bool))
+        e = torch.where(mask, torch.exp(self.a[:, None, :] - self.A[:, :, None]), torch.zeros((), dtype=torch.float64))
+        w = (self.q @ self.k.transpose(-1, -2)) / math.sqrt(D) * e
+        num = w @ self.v
+        b = w.sum(-1)
+        if state_in is not None:
+            s_w = torch.exp(self.A_in[:, None] - self.A) / math.sqrt(D)          # [BH, S]
+            num = num + s_w[..., None] * (self.q @ state_in[0].double())
+            b = b + s_w * (self.q @ state_in[1].double()[..., None])[..., 0]
+        m = self.Fc + self.A
+        n = torch.maximum(b.abs(), torch.exp(-m)) + 1e-6
+        return (num / n[..., None]).reshape(B, NH, S, D).to(h_dtype)

@@ -1,0 +1,119 @@
+"""GPU parity tests of the chunkwise forward (single GPU and sequence-parallel over NCCL)."""
+import importlib
+import os
+import socket
+
+import pytest
+import torch
+
+from oracle import mlstm_oracle as orc
+from tests import kernel_model as km
+
+pytestmark = pytest.mark.gpu
+PKG = "xlstm-triton-cuda-implementation_b200"
+TOL_16 = 1e-2
+
+
+@pytest.fixture(scope="module")
+def gc():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from tests import gpu_cases
+    return gpu_cases
+
+
+def _dev(x, names=("q", "k", "v", "f", "i")):
+    return [x[n].cuda() for n in names]
+
+
+@pytest.mark.parametrize("dtype,S,chunk,f_mean", [
+    (torch.bfloat16, 1024, 256, 3.0),
+    (torch.bfloat16, 1000, 256, 0.0),     # ragged last block
+    (torch.float16, 768, 128, 3.0),
+    (torch.bfloat16, 256, 256, -2.0),     # a single block: no inbound state anywhere
+    (torch.bfloat16, 2048, 512, 5.0),
+])
+def test_chunkwise_against_oracle(gc, dtype, S, chunk, f_mean):
+    x = gc.make_inputs(1, 2, S, 128, dtype, f_mean=f_mean, qkv_scale=128 ** -0.5, seed=S + chunk)
+    h = gc.PKG.mlstm_chunkwise(*_dev(x), chunk_size=chunk)
+    torch.cuda.synchronize()
+    assert h.dtype == torch.float32
+    assert orc.max_abs_rel(h, orc.matmul_forward(x["q"], x["k"], x["v"], x["f"], x["i"])) < TOL_16
+
+
+def test_chunkwise_matches_quadratic_kernel_at_4096(gc):
+    x = gc.make_inputs(2, 2, 4096, 128, torch.bfloat16, f_mean=3.0, qkv_scale=128 ** -0.5, seed=9)
+    d = _dev(x)
+    h1 = gc.PKG.mlstm_chunkwise(*d, chunk_size=256)
+    h2 = gc.PKG.mlstm_matmul(*d)
+    assert orc.max_abs_rel(h1, h2) < TOL_16
+
+
+def test_segment_stages_against_model(gc):
+    """gate summary, carried gates and the segment's added state against the dense fp64 model."""
+    x = gc.make_inputs(1, 2, 512, 128, torch.bfloat16, f_mean=2.0, qkv_scale=128 ** -0.5, seed=4)
+    host = [x[n] for n in ("q", "k", "v", "f", "i")]
+    mc = importlib.import_module(PKG + ".mlstm_chunkwise")
+    seg = mc.ChunkSegment(*_dev(x), chunk_size=256)
+    model = km.ChunkSegmentModel(*host, chunk_size=256)
+    assert orc.max_abs_rel(seg.gate_summary().cpu(), model.gate_summary()) < 1e-9
+    carry = torch.tensor([[-3.0, 1.5], [-1.0, -0.25]], dtype=torch.float64)
+    assert orc.max_abs_rel(seg.prepare(carry).cpu(), model.prepare(carry)) < 1e-9
+    S_g, z_g = seg.local_state()
+    S_m, z_m = model.local_state()
+    assert orc.max_abs_rel(S_g.cpu(), S_m) < TOL_16
+    assert orc.max_abs_rel(z_g.cpu(), z_m) < TOL_16
+
+
+def test_state_continuation_equals_one_call(gc):
+    """Two calls with the state carried through `initial` / `return_state` against the unsplit oracle."""
+    x = gc.make_inputs(1, 2, 1536, 128, torch.bfloat16, f_mean=3.0, qkv_scale=128 ** -0.5, seed=5)
+    cut = 512
+    first = [t[:, :, :cut].contiguous() for t in _dev(x)]
+    second = [t[:, :, cut:].contiguous() for t in _dev(x)]
+    h1, st = gc.PKG.mlstm_chunkwise(*first, chunk_size=256, return_state=True)
+    h2 = gc.PKG.mlstm_chunkwise(*second, chunk_size=256, initial=st)
+    ref = orc.matmul_forward(x["q"], x["k"], x["v"], x["f"], x["i"])
+    assert orc.max_abs_rel(torch.cat([h1, h2], 2), ref) < TOL_16
+
+
+def test_chunkwise_rejects_unsupported_cases(gc):
+    x = gc.make_inputs(1, 1, 256, 64, torch.bfloat16)
+    with pytest.raises(gc._lib.MlstmError):
+        gc.PKG.mlstm_chunkwise(*_dev(x))              # D != 128
+    x = gc.make_inputs(1, 1, 256, 128, torch.bfloat16)
+    with pytest.raises(gc._lib.MlstmError):
+        gc.PKG.mlstm_chunkwise(*_dev(x), chunk_size=200)   # chunk not a multiple of 128
+
+
+def _sp_worker(rank, world, port, x, out):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        pkg = importlib.import_module(PKG)
+        S = x["q"].shape[2]
+        a, b = rank * S // world, (rank + 1) * S // world
+        seg = [x[n][:, :, a:b].contiguous().cuda() for n in ("q", "k", "v", "f", "i")]
+        h = pkg.mlstm_chunkwise_sequence_parallel(*seg, chunk_size=256)
+        torch.cuda.synchronize()
+        ref = orc.matmul_forward(x["q"], x["k"], x["v"], x["f"], x["i"])[:, :, a:b]
+        out[rank] = orc.max_abs_rel(h, ref)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sequence_parallel_over_nccl(gc):
+    """Contiguous segments on 2 (or 4) GPUs, carry over NCCL all-gathers, against the unsplit oracle."""
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    x = gc.make_inputs(1, 2, 4096, 128, torch.bfloat16, f_mean=3.0, qkv_scale=128 ** -0.5, seed=6)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = mp.Manager().dict()
+    mp.spawn(_sp_worker, args=(world, port, x, out), nprocs=world, join=True)
+    assert len(out) == world and all(e < TOL_16 for e in out.values()), dict(out)

@@ -9,5 +9,7 @@ first use.  There is no CPU, PyTorch or Triton fallback: without the built libra
 from . import _lib
 from .mlstm_matmul import Triton_mLSTM, mlstm_matmul, mlstm_matmul_backward, mlstm_matmul_forward
 from .mlstm_scan import mlstm_scan
+from .mlstm_chunkwise import mlstm_chunkwise, mlstm_chunkwise_sequence_parallel
 
-__all__ = ["Triton_mLSTM", "mlstm_matmul", "mlstm_matmul_forward", "mlstm_matmul_backward", "mlstm_scan", "_lib"]
+__all__ = ["Triton_mLSTM", "mlstm_matmul", "mlstm_matmul_forward", "mlstm_matmul_backward", "mlstm_scan",
+           "mlstm_chunkwise", "mlstm_chunkwise_sequence_parallel", "_lib"]

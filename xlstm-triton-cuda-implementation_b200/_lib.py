@@ -58,6 +58,16 @@ def lib():
     L.mlstm_forward_f16.argtypes = [vp] * 6 + [u32, u32, vp, sz, vp]
     L.mlstm_forward_f16_static.restype = i32
     L.mlstm_forward_f16_static.argtypes = [vp] * 6 + [u32, u32, vp]
+    L.mlstm_chunk_workspace.restype = sz
+    L.mlstm_chunk_workspace.argtypes = [i32] * 6
+    L.mlstm_chunk_gate_summary.restype = i32
+    L.mlstm_chunk_gate_summary.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
+    L.mlstm_chunk_prepare.restype = i32
+    L.mlstm_chunk_prepare.argtypes = [vp] * 6 + [vp, sz] + [i32] * 6 + [vp]
+    L.mlstm_chunk_local_state.restype = i32
+    L.mlstm_chunk_local_state.argtypes = [vp, sz, vp, vp] + [i32] * 6 + [vp]
+    L.mlstm_chunk_apply.restype = i32
+    L.mlstm_chunk_apply.argtypes = [vp] * 6 + [i32, vp, vp, vp, sz] + [i32] * 6 + [vp]
     L.mlstm_read_status.restype = i32
     L.mlstm_read_status.argtypes = [vp, ctypes.POINTER(i32), vp]
     _lib = L
@@ -68,6 +78,8 @@ EXPORTS = [
     "mlstm_status_string", "mlstm_tc_supported", "mlstm_mm_fwd_workspace", "mlstm_mm_fwd",
     "mlstm_mm_bwd_workspace", "mlstm_mm_bwd", "mlstm_scan_fwd_workspace", "mlstm_scan_fwd",
     "mlstm_forward_f16_workspace", "mlstm_forward_f16", "mlstm_forward_f16_static", "mlstm_read_status",
+    "mlstm_chunk_workspace", "mlstm_chunk_gate_summary", "mlstm_chunk_prepare", "mlstm_chunk_local_state",
+    "mlstm_chunk_apply",
 ]
 
 

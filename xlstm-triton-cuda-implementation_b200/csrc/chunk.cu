@@ -1,0 +1,228 @@
+// Chunkwise forward of the mLSTM for long sequences, with an inbound / outbound state so that a
+// sequence can be split into contiguous segments across GPUs.
+//
+// The reference has no such entry point; its only long-sequence mechanism is the inter-block carry of
+// the scan path (mlstm_scan.py:143-195: per-block (C, n) states reduced over blocks).  This file
+// gives that mechanism the stabiliser algebra of the parallel path: with the prefix maximum A known
+// up front (gates.cu), every weight is exp(a_j - A_ref) <= 1 and the carry is a plain linear
+// recurrence
+//     S_{k+1} = exp(A_end(k-1) - A_end(k)) S_k + U_k,    U_k = sum_{j in block k} exp(a_j - A_end(k)) k_j v_j^T
+// (S is indexed [key, value]; z is the same with v dropped: the normaliser vector).  A query t of block k
+// gets   num_t = intra-block part + exp(A_end(k-1) - A_t) (q_t S_k) / sqrt(D)   and the same for b_t.
+// Both contractions run on the tensor-core pass kernel (modes STATE and FWDC, mm_tc.cu).
+#include "mlstm_common.cuh"
+
+namespace mlstm {
+namespace {
+
+constexpr size_t WS_ALIGN = 256;
+inline size_t al(size_t x) { return (x + WS_ALIGN - 1) / WS_ALIGN * WS_ALIGN; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename T16>
+__global__ void identity_kernel(T16* ident) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < TILE * TILE) ident[idx] = from_f32<T16>((idx / TILE) == (idx % TILE) ? 1.0f : 0.0f);
+}
+
+// One thread owns four consecutive elements of a slice's [D*D + D] state (matrix, then normaliser
+// vector) and walks the blocks in order.  It writes the INBOUND state of every block (16-bit matrix
+// for the tensor cores, fp32 vector) and, optionally, the state after the last block.
+template <typename T16>
+__global__ void state_scan_kernel(const float* __restrict__ U, const float* __restrict__ zU,
+                                  const double* __restrict__ An_bound, const float* __restrict__ S_in,
+                                  const float* __restrict__ z_in, T16* __restrict__ states, float* __restrict__ zstate,
+                                  float* __restrict__ S_end, float* __restrict__ z_end, int NB, int D) {
+    const int bh = blockIdx.y;
+    const int DD = D * D;
+    const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (e >= DD + D) return;
+    const bool is_vec = e >= DD;
+    const int off = is_vec ? e - DD : e;
+    const size_t per_block = is_vec ? D : DD;
+    const float* src = (is_vec ? zU : U) + static_cast<size_t>(bh) * NB * per_block + off;
+    const float* init = is_vec ? z_in : S_in;
+    float4 s = init ? *reinterpret_cast<const float4*>(init + static_cast<size_t>(bh) * per_block + off)
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
+    const double* bound = An_bound + static_cast<size_t>(bh) * (NB + 1);
+    for (int k = 0; k < NB; k++) {
+        if (is_vec) {
+            *reinterpret_cast<float4*>(zstate + (static_cast<size_t>(bh) * NB + k) * D + off) = s;
+        } else {
+            T16 o[4] = {from_f32<T16>(s.x), from_f32<T16>(s.y), from_f32<T16>(s.z), from_f32<T16>(s.w)};
+            *reinterpret_cast<uint2*>(states + (static_cast<size_t>(bh) * NB + k) * DD + off) = *reinterpret_cast<uint2*>(o);
+        }
+        // exp(A_end(k-1) - A_end(k)); 0 for the first block when there is no inbound carry (bound[0] = +inf)
+        const float d = exp2f(static_cast<float>(bound[k + 1] - bound[k]));
+        const float4 u = *reinterpret_cast<const float4*>(src + static_cast<size_t>(k) * per_block);
+        s.x = (d == 0.0f ? 0.0f : d * s.x) + u.x;
+        s.y = (d == 0.0f ? 0.0f : d * s.y) + u.y;
+        s.z = (d == 0.0f ? 0.0f : d * s.z) + u.z;
+        s.w = (d == 0.0f ? 0.0f : d * s.w) + u.w;
+    }
+    float* dst = is_vec ? z_end : S_end;
+    if (dst) *reinterpret_cast<float4*>(dst + static_cast<size_t>(bh) * per_block + off) = s;
+}
+
+struct ChunkWs {
+    int* status;
+    float *ga, *gAn, *m, *b, *U, *zU, *zstate;
+    double *a_ref, *An_ref, *An_bound;
+    void *ident, *states;
+    int NB;
+    size_t bytes;
+};
+
+ChunkWs carve(void* ws, int BH, int S, int D, int chunk) {
+    ChunkWs w{};
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        void* p = base ? base + off : nullptr;
+        off += al(bytes);
+        return p;
+    };
+    const size_t Spad = round_up(S, TILE);
+    const size_t vec = static_cast<size_t>(BH) * Spad * sizeof(float);
+    w.NB = (S + chunk - 1) / chunk;
+    const size_t nblk = static_cast<size_t>(BH) * w.NB;
+    w.status = static_cast<int*>(take(WS_ALIGN));
+    w.ga = static_cast<float*>(take(vec));
+    w.gAn = static_cast<float*>(take(vec));
+    w.a_ref = static_cast<double*>(take(vec / REF_BLOCK * 2));
+    w.An_ref = static_cast<double*>(take(vec / REF_BLOCK * 2));
+    w.m = static_cast<float*>(take(static_cast<size_t>(BH) * S * sizeof(float)));
+    w.b = static_cast<float*>(take(static_cast<size_t>(BH) * S * sizeof(float)));
+    w.An_bound = static_cast<double*>(take(static_cast<size_t>(BH) * (w.NB + 1) * sizeof(double)));
+    w.ident = take(static_cast<size_t>(TILE) * TILE * 2);
+    w.U = static_cast<float*>(take(nblk * D * D * sizeof(float)));
+    w.zU = static_cast<float*>(take(nblk * D * sizeof(float)));
+    w.states = take(nblk * D * D * 2);
+    w.zstate = static_cast<float*>(take(nblk * D * sizeof(float)));
+    w.bytes = off;
+    return w;
+}
+
+int check_chunk_args(int B, int NH, int S, int D, int dtype, int chunk) {
+    if (B <= 0 || NH <= 0 || S <= 0 || D <= 0 || chunk <= 0) return MLSTM_E_ARG;
+    if (dtype != MLSTM_DT_F16 && dtype != MLSTM_DT_BF16) return MLSTM_E_UNSUPPORTED;  // tensor-core path only
+    if (D != 128) return MLSTM_E_UNSUPPORTED;
+    if (chunk % TILE != 0) return MLSTM_E_SHAPE;
+    if (static_cast<long long>(B) * NH > 65535) return MLSTM_E_SHAPE;
+    return MLSTM_OK;
+}
+
+}  // namespace
+
+int launch_identity(void* ident, int dtype, cudaStream_t st) {
+    const int n = TILE * TILE;
+    if (dtype == MLSTM_DT_BF16)
+        identity_kernel<__nv_bfloat16><<<(n + 255) / 256, 256, 0, st>>>(static_cast<__nv_bfloat16*>(ident));
+    else
+        identity_kernel<__half><<<(n + 255) / 256, 256, 0, st>>>(static_cast<__half*>(ident));
+    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+}
+
+int launch_state_scan(const float* U, const float* zU, const double* An_bound, const float* S_in, const float* z_in,
+                      void* states16, float* zstate, float* S_end, float* z_end, int BH, int NB, int D, int dtype,
+                      cudaStream_t st) {
+    const int threads = 256;
+    const int work = (D * D + D) / 4;
+    dim3 grid((work + threads - 1) / threads, BH);
+    if (dtype == MLSTM_DT_BF16)
+        state_scan_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(U, zU, An_bound, S_in, z_in,
+                                                                   static_cast<__nv_bfloat16*>(states16), zstate, S_end,
+                                                                   z_end, NB, D);
+    else
+        state_scan_kernel<__half><<<grid, threads, 0, st>>>(U, zU, An_bound, S_in, z_in, static_cast<__half*>(states16),
+                                                            zstate, S_end, z_end, NB, D);
+    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+}
+
+}  // namespace mlstm
+
+using namespace mlstm;
+
+extern "C" {
+
+size_t mlstm_chunk_workspace(int B, int NH, int S, int D, int dtype, int chunk) {
+    if (check_chunk_args(B, NH, S, D, dtype, chunk) != MLSTM_OK) return 0;
+    return carve(nullptr, B * NH, S, D, chunk).bytes;
+}
+
+int mlstm_chunk_gate_summary(const void* f, const void* i, double* summary, int B, int NH, int S, int dtype, void* stream) {
+    if (!f || !i || !summary || B <= 0 || NH <= 0 || S <= 0) return MLSTM_E_ARG;
+    return launch_gates_fwd(f, i, nullptr, nullptr, nullptr, nullptr, nullptr, B * NH, S, round_up(S, TILE), dtype,
+                            static_cast<cudaStream_t>(stream), nullptr, summary, nullptr, 0);
+}
+
+int mlstm_chunk_prepare(const void* k, const void* v, const void* f, const void* i, const double* carry_in,
+                        double* summary_out, void* workspace, size_t workspace_bytes, int B, int NH, int S, int D,
+                        int dtype, int chunk, void* stream) {
+    if (!k || !v || !f || !i) return MLSTM_E_ARG;
+    int rc = check_chunk_args(B, NH, S, D, dtype, chunk);
+    if (rc != MLSTM_OK) return rc;
+    if (!aligned16(k) || !aligned16(v)) return MLSTM_E_ALIGN;
+    const int BH = B * NH, Spad = round_up(S, TILE);
+    ChunkWs w = carve(workspace, BH, S, D, chunk);
+    if (!workspace || workspace_bytes < w.bytes || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
+    if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, w.m, BH, S, Spad, dtype, st, carry_in, summary_out,
+                               w.An_bound, chunk)) != MLSTM_OK)
+        return rc;
+    if ((rc = launch_identity(w.ident, dtype, st)) != MLSTM_OK) return rc;
+    // U_k[key, value] = sum_j exp(a_j - A_end(k)) k_j[key] v_j[value];  zU_k[key] = sum_j exp(...) k_j[key]
+    PassParams p{};
+    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status;
+    p.X = k;  // unused by STATE (the stationary operand is the identity); keeps the tensor map valid
+    p.Y = k; p.Z = v;
+    p.col_rel = w.ga; p.col_ref = w.a_ref;
+    p.row_rel = w.gAn; p.row_ref = w.An_ref;  // unused by STATE
+    p.out = w.U; p.b_out = w.zU;
+    p.chunk_tiles = chunk / TILE; p.NB = w.NB; p.An_bound = w.An_bound; p.ident = w.ident;
+    return launch_pass_tc(STATE, p, dtype, MLSTM_DT_F32, st);
+}
+
+int mlstm_chunk_local_state(void* workspace, size_t workspace_bytes, float* S_end, float* z_end, int B, int NH, int S,
+                            int D, int dtype, int chunk, void* stream) {
+    if (!S_end || !z_end) return MLSTM_E_ARG;
+    int rc = check_chunk_args(B, NH, S, D, dtype, chunk);
+    if (rc != MLSTM_OK) return rc;
+    ChunkWs w = carve(workspace, B * NH, S, D, chunk);
+    if (!workspace || workspace_bytes < w.bytes) return MLSTM_E_WORKSPACE;
+    // the recurrence is linear: the state this segment adds is the scan from a zero state, with the
+    // first decay taken from the carried-in stabiliser (a zero state makes that decay irrelevant)
+    return launch_state_scan(w.U, w.zU, w.An_bound, nullptr, nullptr, w.states, w.zstate, S_end, z_end, B * NH, w.NB, D,
+                             dtype, static_cast<cudaStream_t>(stream));
+}
+
+int mlstm_chunk_apply(const void* q, const void* k, const void* v, const float* S_in, const float* z_in, void* h,
+                      int h_dtype, float* S_out, float* z_out, void* workspace, size_t workspace_bytes, int B, int NH,
+                      int S, int D, int dtype, int chunk, void* stream) {
+    if (!q || !k || !v || !h) return MLSTM_E_ARG;
+    if ((S_in == nullptr) != (z_in == nullptr)) return MLSTM_E_ARG;
+    int rc = check_chunk_args(B, NH, S, D, dtype, chunk);
+    if (rc != MLSTM_OK) return rc;
+    if (h_dtype != MLSTM_DT_F32 && h_dtype != dtype) return MLSTM_E_ARG;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(h) || !aligned16(S_in) || !aligned16(z_in))
+        return MLSTM_E_ALIGN;
+    const int BH = B * NH, Spad = round_up(S, TILE);
+    ChunkWs w = carve(workspace, BH, S, D, chunk);
+    if (!workspace || workspace_bytes < w.bytes) return MLSTM_E_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if ((rc = launch_state_scan(w.U, w.zU, w.An_bound, S_in, z_in, w.states, w.zstate, S_out, z_out, BH, w.NB, D, dtype,
+                                st)) != MLSTM_OK)
+        return rc;
+    PassParams p{};
+    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status;
+    p.X = q; p.Y = k; p.Z = v;
+    p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_ref = w.a_ref;
+    p.er_add = -0.5f * log2f(static_cast<float>(D));
+    p.out = h; p.m = w.m; p.b_out = w.b;
+    p.chunk_tiles = chunk / TILE; p.NB = w.NB; p.An_bound = w.An_bound; p.ident = w.ident;
+    p.states = w.states; p.zstate = w.zstate;
+    return launch_pass_tc(FWDC, p, dtype, h_dtype, st);
+}
+
+}  // extern "C"

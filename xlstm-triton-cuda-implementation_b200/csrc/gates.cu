@@ -74,11 +74,18 @@ __device__ __forceinline__ double block_scan_max(double x, double* warp_tot, dou
 // A kernel forms exp2(col_rel[c] + float(row_rel[r] + row_ref[r / REF_BLOCK] + col_ref[c / REF_BLOCK])),
 // the bracket in double once per block of columns.  Padding (t >= S): ga_rel = -inf (a padded column
 // contributes exactly zero), gAn_rel = 0, references 0.  m may be null.
+// Chunkwise / sequence-parallel extras (all optional): carry_in[bh] = {F, A} at the end of the
+// preceding segment (natural-log units; absent = {0, -inf}); summary_out[bh] = {F, A} at the end of
+// this segment; An_bound[bh][0] = -A_in*log2e and An_bound[bh][k+1] = -A*log2e at the last position
+// of block k (blocks of chunk_len positions).  The vector outputs may be null (summary only).
 template <typename T>
 __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __restrict__ f, const T* __restrict__ i,
                                                                  float* __restrict__ ga_rel, float* __restrict__ gAn_rel,
                                                                  double* __restrict__ a_ref, double* __restrict__ An_ref,
-                                                                 float* __restrict__ m, int S, int Spad) {
+                                                                 float* __restrict__ m, int S, int Spad,
+                                                                 const double* __restrict__ carry_in,
+                                                                 double* __restrict__ summary_out,
+                                                                 double* __restrict__ An_bound, int chunk_len) {
     __shared__ double wsum[32];
     __shared__ double wmax[32];
     __shared__ double carry_sum;
@@ -87,9 +94,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
     __shared__ double ref_A[SCAN_THREADS / REF_BLOCK];
     const int bh = blockIdx.x;
     const int nref = Spad / REF_BLOCK;
+    const int nb = chunk_len > 0 ? (S + chunk_len - 1) / chunk_len : 0;
     if (threadIdx.x == 0) {
-        carry_sum = 0.0;
-        carry_max = -INFINITY;
+        carry_sum = carry_in ? carry_in[2 * bh] : 0.0;
+        carry_max = carry_in ? carry_in[2 * bh + 1] : -INFINITY;
+        if (An_bound) An_bound[static_cast<size_t>(bh) * (nb + 1)] = -carry_max * LOG2E_D;
     }
     __syncthreads();
     for (int base = 0; base < Spad; base += SCAN_THREADS) {
@@ -109,7 +118,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
             ref_A[threadIdx.x / REF_BLOCK] = in ? A : 0.0;
         }
         __syncthreads();
-        if (t < Spad) {
+        if (t < Spad && ga_rel) {
             const double ra = ref_a[threadIdx.x / REF_BLOCK], rA = ref_A[threadIdx.x / REF_BLOCK];
             ga_rel[static_cast<size_t>(bh) * Spad + t] = in ? static_cast<float>((a - ra) * LOG2E_D) : -INFINITY;
             gAn_rel[static_cast<size_t>(bh) * Spad + t] = in ? static_cast<float>((rA - A) * LOG2E_D) : 0.0f;
@@ -119,7 +128,13 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
             }
         }
         if (in && m) m[static_cast<size_t>(bh) * S + t] = static_cast<float>(F + A);
+        if (in && An_bound && ((t + 1) % chunk_len == 0 || t == S - 1))
+            An_bound[static_cast<size_t>(bh) * (nb + 1) + t / chunk_len + 1] = -A * LOG2E_D;
         __syncthreads();
+    }
+    if (threadIdx.x == 0 && summary_out) {
+        summary_out[2 * bh] = carry_sum;
+        summary_out[2 * bh + 1] = carry_max;
     }
 }
 
@@ -208,17 +223,21 @@ __global__ void __launch_bounds__(SCAN_THREADS) df_kernel(const T* __restrict__ 
 }  // namespace
 
 int launch_gates_fwd(const void* f, const void* i, float* ga, float* gA, double* a_ref, double* An_ref, float* m, int BH,
-                     int S, int Spad, int dtype, cudaStream_t st) {
+                     int S, int Spad, int dtype, cudaStream_t st, const double* carry_in, double* summary_out,
+                     double* An_bound, int chunk_len) {
     switch (dtype) {
         case MLSTM_DT_F32:
-            gates_fwd_kernel<float><<<BH, SCAN_THREADS, 0, st>>>((const float*)f, (const float*)i, ga, gA, a_ref, An_ref, m, S, Spad);
+            gates_fwd_kernel<float><<<BH, SCAN_THREADS, 0, st>>>((const float*)f, (const float*)i, ga, gA, a_ref, An_ref, m, S,
+                                                                 Spad, carry_in, summary_out, An_bound, chunk_len);
             break;
         case MLSTM_DT_F16:
-            gates_fwd_kernel<__half><<<BH, SCAN_THREADS, 0, st>>>((const __half*)f, (const __half*)i, ga, gA, a_ref, An_ref, m, S, Spad);
+            gates_fwd_kernel<__half><<<BH, SCAN_THREADS, 0, st>>>((const __half*)f, (const __half*)i, ga, gA, a_ref, An_ref, m,
+                                                                  S, Spad, carry_in, summary_out, An_bound, chunk_len);
             break;
         case MLSTM_DT_BF16:
-            gates_fwd_kernel<__nv_bfloat16>
-                <<<BH, SCAN_THREADS, 0, st>>>((const __nv_bfloat16*)f, (const __nv_bfloat16*)i, ga, gA, a_ref, An_ref, m, S, Spad);
+            gates_fwd_kernel<__nv_bfloat16><<<BH, SCAN_THREADS, 0, st>>>((const __nv_bfloat16*)f, (const __nv_bfloat16*)i, ga, gA,
+                                                                         a_ref, An_ref, m, S, Spad, carry_in, summary_out,
+                                                                         An_bound, chunk_len);
             break;
         default: return MLSTM_E_ARG;
     }

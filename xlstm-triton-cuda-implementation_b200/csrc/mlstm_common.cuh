@@ -30,7 +30,11 @@
 
 namespace mlstm {
 
-enum Mode : int { FWD = 0, DQ = 1, DK = 2, DV = 3 };
+// FWDC and STATE are the two passes of the chunkwise forward (chunk.cu): STATE builds, per block of
+// `chunk_tiles` tiles, U = sum_j w_j k_j v_j^T (rows = key dimensions, X = identity, Y = K, Z = V);
+// FWDC is FWD restricted to the query's own block plus one step that applies the block's inbound
+// state (Y = identity, Z = state), so T = Q and W = Q scaled per row.
+enum Mode : int { FWD = 0, DQ = 1, DK = 2, DV = 3, FWDC = 4, STATE = 5 };
 
 constexpr int TILE = 128;      // rows of a tensor-core tile; gate vectors are padded to a multiple of it
 constexpr int REF_BLOCK = 64;  // positions per reference block of the re-centred gate vectors (gates.cu)
@@ -63,6 +67,13 @@ struct PassParams {
     // DQ / DK only: dot_out[r] = sum_d ACC[r, d] * dot_src[r, d], taken on the fp32 accumulator
     const void* dot_src; // [BH, S, D] input type (q for DQ, k for DK)
     float* dot_out;      // [BH, Spad]
+    // chunkwise passes only
+    int chunk_tiles;         // tiles per block
+    int NB;                  // blocks per slice
+    const double* An_bound;  // [BH, NB + 1]  -A*log2e at the block boundaries (entry 0: the inbound carry)
+    const void* ident;       // [128, 128] identity in the input type
+    const void* states;      // FWDC: [BH, NB, D, D] inbound state of every block, input type
+    const float* zstate;     // FWDC: [BH, NB, D] inbound normaliser vector of every block
     int* status;         // device word; a kernel that gave up on a wait stores a non-zero code
 };
 
@@ -96,12 +107,18 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)
 // DK/DV (column >= row is valid).
 template <int MODE>
 __device__ __forceinline__ bool causal_ok(int row, int col) {
-    return (MODE == FWD || MODE == DQ) ? (col <= row) : (col >= row);
+    return (MODE == FWD || MODE == DQ || MODE == FWDC) ? (col <= row) : (col >= row);
 }
 
 // Launchers implemented in the .cu files.  All return an MLSTM_* status and never synchronise.
 int launch_gates_fwd(const void* f, const void* i, float* ga_rel, float* gAn_rel, double* a_ref, double* An_ref, float* m,
-                     int BH, int S, int Spad, int dtype, cudaStream_t st);
+                     int BH, int S, int Spad, int dtype, cudaStream_t st, const double* carry_in = nullptr,
+                     double* summary_out = nullptr, double* An_bound = nullptr, int chunk_len = 0);
+// chunk.cu
+int launch_identity(void* ident, int dtype, cudaStream_t st);
+int launch_state_scan(const float* U, const float* zU, const double* An_bound, const float* S_in, const float* z_in,
+                      void* states16, float* zstate, float* S_end, float* z_end, int BH, int NB, int D, int dtype,
+                      cudaStream_t st);
 int launch_bwd_prep(const void* h, const void* dh, const float* b, const float* m, const float* gAn, float* gB,
                     float* g, void* dh16, int BH, int S, int Spad, int D, int h_dtype, int dtype, cudaStream_t st);
 int launch_df(const void* f, const float* dI, const float* R, void* df, void* di, int BH, int S, int Spad, int dtype,

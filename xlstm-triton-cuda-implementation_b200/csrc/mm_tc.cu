@@ -51,10 +51,13 @@ struct SmemTail {  // lives after the tiles
 template <int MODE, int D, int ABFMT, typename OutT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
-              const __grid_constant__ CUtensorMap tmZ, const PassParams p) {
+              const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmI,
+              const __grid_constant__ CUtensorMap tmS, const PassParams p) {
     using C = TcCfg<D>;
     using InT = typename std::conditional<ABFMT == 1, __nv_bfloat16, __half>::type;
-    constexpr bool ROWS_ARE_Q = (MODE == FWD || MODE == DQ);
+    constexpr bool ROWS_ARE_Q = (MODE == FWD || MODE == DQ || MODE == FWDC);
+    constexpr bool IS_FWD = (MODE == FWD || MODE == FWDC);   // normalised output, row sums kept
+    static_assert((MODE != FWDC && MODE != STATE) || D == 128, "chunkwise passes are built for D = 128");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -79,18 +82,30 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     // resident at one time then share the K/V (or Q/dH) of a few slices, which stay in L2.
     int bh, w;
     {
-        const int per_set = NT * SLICE_SET;
+        const int per_slice = (MODE == STATE) ? p.NB : NT;  // CTAs per slice
+        const int per_set = per_slice * SLICE_SET;
         const int set = blockIdx.x / per_set;
         const int within = blockIdx.x - set * per_set;
         const int set_size = min(SLICE_SET, p.BH - set * SLICE_SET);
         w = within / set_size;
         bh = set * SLICE_SET + (within - w * set_size);
     }
-    const int tile = ROWS_ARE_Q ? (NT - 1 - w) : w;
-    const int nsteps = ROWS_ARE_Q ? (tile + 1) : (NT - tile);
-    // streamed tile of step t: FWD/DQ visit key tiles 0..tile (diagonal last), DK/DV visit query
-    // tiles tile..NT-1 (diagonal first)
-    auto stream_tile = [&](int t) { return ROWS_ARE_Q ? t : (tile + t); };
+    // tile: the stationary tile (STATE: the block).  nsteps / stream_tile: what is streamed.
+    //   FWD, DQ   key tiles 0..tile, diagonal last          DK, DV  query tiles tile..NT-1, diagonal first
+    //   FWDC      step 0 applies the block's inbound state, then key tiles block_start..tile
+    //   STATE     the block's tiles
+    const int tile = (MODE == STATE) ? w : (ROWS_ARE_Q ? (NT - 1 - w) : w);
+    const int blk = (MODE == FWDC) ? tile / p.chunk_tiles : (MODE == STATE ? tile : 0);
+    const int first = (MODE == FWDC || MODE == STATE) ? blk * p.chunk_tiles : 0;
+    const int nsteps = (MODE == FWDC) ? (tile - first + 2)
+                     : (MODE == STATE) ? (min(p.chunk_tiles, NT - first))
+                     : (ROWS_ARE_Q ? (tile + 1) : (NT - tile));
+    auto stream_tile = [&](int t) {
+        if (MODE == FWDC) return first + t - 1;  // t >= 1
+        if (MODE == STATE) return first + t;
+        return ROWS_ARE_Q ? t : (tile + t);
+    };
+    auto is_state_step = [&](int t) { return MODE == FWDC && t == 0; };
 
     if (threadIdx.x == 0) {
         mbar_init(bar_x, 1);
@@ -124,11 +139,16 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             prefetch_tmap(&tmX);
             prefetch_tmap(&tmY);
             prefetch_tmap(&tmZ);
+            prefetch_tmap(&tmI);
+            prefetch_tmap(&tmS);
             mbar_expect_tx(bar_x, C::X_BYTES);
-            for (int c = 0; c < D / 64; c++) tma_load_3d(sX + c * BOX_BYTES, &tmX, bar_x, c * 64, tile * TILE, bh);
+            for (int c = 0; c < D / 64; c++) {
+                if (MODE == STATE) tma_load_3d(sX + c * BOX_BYTES, &tmI, bar_x, c * 64, 0, 0);
+                else tma_load_3d(sX + c * BOX_BYTES, &tmX, bar_x, c * 64, tile * TILE, bh);
+            }
             int it = 0;
             bool ok = true;
-            auto load_tile = [&](const CUtensorMap* map, int st) {
+            auto load_tile = [&](const CUtensorMap* map, int row, int z) {
                 for (int hf = 0; hf < C::NHALF && ok; hf++, it++) {
                     const int s = it % C::NSLOT;
                     ok = mbar_wait(&bar_empty[s], ((it / C::NSLOT) & 1) ^ 1, abort_flag, WAIT_LIMIT);
@@ -136,17 +156,24 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     mbar_expect_tx(&bar_full[s], C::SLOT_BYTES);
                     uint8_t* dst = sSlot + s * C::SLOT_BYTES;
                     for (int c = 0; c < C::CH / 64; c++)
-                        tma_load_3d(dst + c * BOX_BYTES, map, &bar_full[s], (hf * (C::CH / 64) + c) * 64, st * TILE,
-                                    bh);
+                        tma_load_3d(dst + c * BOX_BYTES, map, &bar_full[s], (hf * (C::CH / 64) + c) * 64, row, z);
                 }
             };
+            auto load_y = [&](int t) {
+                if (is_state_step(t)) load_tile(&tmI, 0, 0);
+                else load_tile(&tmY, stream_tile(t) * TILE, bh);
+            };
+            auto load_z = [&](int t) {
+                if (is_state_step(t)) load_tile(&tmS, 0, bh * p.NB + blk);
+                else load_tile(&tmZ, stream_tile(t) * TILE, bh);
+            };
             // same order as the MMA issuer consumes: Y(0), then Y(t), Z(t-1) ..., Z(last)
-            load_tile(&tmY, stream_tile(0));
+            load_y(0);
             for (int t = 1; t < nsteps && ok; t++) {
-                load_tile(&tmY, stream_tile(t));
-                load_tile(&tmZ, stream_tile(t - 1));
+                load_y(t);
+                load_z(t - 1);
             }
-            if (ok) load_tile(&tmZ, stream_tile(nsteps - 1));
+            if (ok) load_z(nsteps - 1);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
@@ -212,8 +239,14 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         const size_t vec_base = static_cast<size_t>(bh) * p.Spad;
         const size_t ref_base = static_cast<size_t>(bh) * (p.Spad / REF_BLOCK);
         // row part of the exponent in double; the column block's reference is added per block
-        const double er_d = static_cast<double>(p.row_rel[vec_base + grow]) + p.row_ref[ref_base + grow / REF_BLOCK] +
-                            static_cast<double>(p.er_add);
+        // (STATE: rows are key dimensions; every row carries the block-end stabiliser)
+        const double* bound = (MODE == FWDC || MODE == STATE) ? p.An_bound + static_cast<size_t>(bh) * (p.NB + 1) + blk : nullptr;
+        const double er_d = (MODE == STATE)
+                                ? bound[1]
+                                : static_cast<double>(p.row_rel[vec_base + grow]) + p.row_ref[ref_base + grow / REF_BLOCK] +
+                                      static_cast<double>(p.er_add);
+        // inbound-state step of FWDC: weight exp(A_prev_block_end - A_row) / sqrt(D); -inf when there is no carry
+        const float er_state = (MODE == FWDC) ? static_cast<float>(er_d - bound[0]) : 0.0f;
         const float g_row = (MODE == DQ) ? p.row_g[vec_base + grow] : 0.0f;
         float rowsum = 0.0f;
         bool ok = true;
@@ -231,13 +264,17 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         };
         for (int t = 0; t < nsteps; t++) {
             const int buf = t & 1;
-            const int st = stream_tile(t);
-            const bool diag = (st == tile);
-            const float* ce = p.col_rel + vec_base + st * TILE;
+            const bool state_step = is_state_step(t);
+            const int st = state_step ? 0 : stream_tile(t);
+            const bool diag = (MODE != STATE) && !state_step && (st == tile);
+            // state step: the column term is the inbound normaliser vector z (a weight, not an exponent)
+            const float* ce = state_step ? p.zstate + (static_cast<size_t>(bh) * p.NB + blk) * D
+                                         : p.col_rel + vec_base + st * TILE;
             // column terms do not depend on the contraction: fetch the first half before waiting
             float cv[32];
             load_cols(ce, 0, cv);
-            const float er = static_cast<float>(er_d + p.col_ref[ref_base + st * (TILE / REF_BLOCK) + grp]);
+            const float er = state_step ? er_state
+                                        : static_cast<float>(er_d + p.col_ref[ref_base + st * (TILE / REF_BLOCK) + grp]);
             ok = mbar_wait(&bar_t[buf], (t >> 1) & 1, abort_flag, WAIT_LIMIT);
             if (!ok) break;
             tc_fence_after();
@@ -246,6 +283,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             tmem_ld32(t_tmem, tv0);
             tmem_ld32(t_tmem + 32, tv1);
             uint32_t pk[32];
+            const float er_w = (MODE == FWDC && state_step) ? fast_exp2(er) : 0.0f;
             tc_wait_ld();
 #pragma unroll
             for (int sub = 0; sub < 2; sub++) {
@@ -261,10 +299,16 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 for (int j = 0; j < 32; j++) {
                     float tval = __uint_as_float(tv[j]);
                     if (MODE == DQ) tval += g_row;
-                    float wj = tval * fast_exp2(cv[j] + er);
-                    if (diag && !causal_ok<MODE>(r, cbase + sub * 32 + j)) wj = 0.0f;
+                    float wj;
+                    if (MODE == FWDC && state_step) {
+                        wj = tval * er_w;              // T = Q: scale the row, b += (scaled q) . z
+                        rowsum = fmaf(wj, cv[j], rowsum);
+                    } else {
+                        wj = tval * fast_exp2(cv[j] + er);
+                        if (diag && !causal_ok<MODE>(r, cbase + sub * 32 + j)) wj = 0.0f;
+                        if (IS_FWD || MODE == STATE) rowsum += wj;
+                    }
                     cv[j] = wj;
-                    if (MODE == FWD) rowsum += wj;
                 }
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
@@ -289,10 +333,20 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             tc_fence_after();
             constexpr int HALF = D / 2;
             const int c0 = grp * HALF;
-            const bool row_ok = grow < p.S;
-            const size_t row_off = (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * D;
+            const bool row_ok = (MODE == STATE) ? true : (grow < p.S);
+            // STATE writes block (bh, blk) of [BH, NB, D, D]; everything else row `grow` of [BH, S, D]
+            const size_t row_off = (MODE == STATE)
+                                       ? ((static_cast<size_t>(bh) * p.NB + blk) * D + r) * D
+                                       : (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * D;
             float inv_n = 1.0f;
-            if (MODE == FWD) {
+            if (MODE == STATE) {
+                tail->part[grp][r] = rowsum;
+                mbar_arrive(bar_part);
+                ok = mbar_wait(bar_part, 0, abort_flag, WAIT_LIMIT);
+                if (ok && grp == 0 && p.b_out)
+                    p.b_out[(static_cast<size_t>(bh) * p.NB + blk) * D + r] = tail->part[0][r] + tail->part[1][r];
+            }
+            if (IS_FWD) {
                 tail->part[grp][r] = rowsum;
                 mbar_arrive(bar_part);
                 ok = mbar_wait(bar_part, 0, abort_flag, WAIT_LIMIT);
@@ -307,7 +361,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             float dot = 0.0f;
             if (ok) {
                 OutT* orow = reinterpret_cast<OutT*>(p.out) + row_off + c0;
-                const InT* ogate_row = (MODE == FWD && p.ogate) ? reinterpret_cast<const InT*>(p.ogate) + row_off + c0 : nullptr;
+                const InT* ogate_row = (IS_FWD && p.ogate) ? reinterpret_cast<const InT*>(p.ogate) + row_off + c0 : nullptr;
                 const InT* drow = ((MODE == DQ || MODE == DK) && p.dot_src)
                                       ? reinterpret_cast<const InT*>(p.dot_src) + row_off + c0 : nullptr;
 #pragma unroll 1
@@ -319,7 +373,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                         float vals[32];
 #pragma unroll
                         for (int j = 0; j < 32; j++) vals[j] = __uint_as_float(av[j]) * inv_n;
-                        if (MODE == FWD && ogate_row) {
+                        if (IS_FWD && ogate_row) {
 #pragma unroll
                             for (int j = 0; j < 32; j++) vals[j] *= silu_f(to_f32<InT>(ogate_row[ch * 32 + j]));
                         }
@@ -413,11 +467,21 @@ int make_map(CUtensorMap* map, const void* base, int BH, int S, int D, int dtype
 
 template <int MODE, int D, int ABFMT, typename OutT>
 int launch_one(const PassParams& p, int in_dtype, cudaStream_t st) {
-    CUtensorMap mx, my, mz;
+    CUtensorMap mx, my, mz, mi, ms;
     int rc;
     if ((rc = make_map(&mx, p.X, p.BH, p.S, D, in_dtype)) != MLSTM_OK) return rc;
     if ((rc = make_map(&my, p.Y, p.BH, p.S, D, in_dtype)) != MLSTM_OK) return rc;
     if ((rc = make_map(&mz, p.Z, p.BH, p.S, D, in_dtype)) != MLSTM_OK) return rc;
+    mi = mx;
+    ms = mx;
+    if (MODE == FWDC || MODE == STATE) {
+        if (!p.ident || p.chunk_tiles <= 0 || p.NB <= 0 || !p.An_bound) return MLSTM_E_ARG;
+        if ((rc = make_map(&mi, p.ident, 1, TILE, TILE, in_dtype)) != MLSTM_OK) return rc;
+    }
+    if (MODE == FWDC) {
+        if (!p.states || !p.zstate) return MLSTM_E_ARG;
+        if ((rc = make_map(&ms, p.states, p.BH * p.NB, D, D, in_dtype)) != MLSTM_OK) return rc;
+    }
     auto kern = mlstm_tc_pass<MODE, D, ABFMT, OutT>;
     constexpr int smem = TcCfg<D>::SMEM_BYTES;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
@@ -425,9 +489,9 @@ int launch_one(const PassParams& p, int in_dtype, cudaStream_t st) {
         return MLSTM_E_CUDA;
     }
     const int NT = p.Spad / TILE;
-    const long long nblk = static_cast<long long>(NT) * p.BH;
+    const long long nblk = static_cast<long long>(MODE == STATE ? p.NB : NT) * p.BH;
     if (nblk > 0x7fffffffLL) return MLSTM_E_SHAPE;
-    kern<<<static_cast<unsigned>(nblk), NTHREADS, smem, st>>>(mx, my, mz, p);
+    kern<<<static_cast<unsigned>(nblk), NTHREADS, smem, st>>>(mx, my, mz, mi, ms, p);
     return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
@@ -470,6 +534,12 @@ int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, c
         case DQ: return launch_d<DQ>(p, in_dtype, out_dtype, st);
         case DK: return launch_d<DK>(p, in_dtype, out_dtype, st);
         case DV: return launch_d<DV>(p, in_dtype, out_dtype, st);
+        case FWDC:
+            if (p.D != 128) return MLSTM_E_UNSUPPORTED;
+            return launch_fmt<FWDC, 128>(p, in_dtype, out_dtype, st);
+        case STATE:
+            if (p.D != 128 || out_dtype != MLSTM_DT_F32) return MLSTM_E_UNSUPPORTED;
+            return launch_fmt<STATE, 128>(p, in_dtype, out_dtype, st);
     }
     return MLSTM_E_ARG;
 }

@@ -1,0 +1,187 @@
+"""Chunkwise mLSTM forward for long sequences, on one GPU or sequence-parallel over several.
+
+    h = mlstm_chunkwise(q, k, v, f, i, chunk_size=256)
+    h_local = mlstm_chunkwise_sequence_parallel(q_seg, k_seg, v_seg, f_seg, i_seg, chunk_size=256, group=None)
+
+The reference has no long-sequence entry point of its own; what this extends is the inter-block carry
+of its scan path (mlstm_scan.py:143-195) with the carry algebra of its scan operators
+(mlstm_scan.py:15-26).  Inputs are 16-bit, D = 128; h is float32 unless ``h_dtype`` says otherwise.
+
+Sequence-parallel form: rank r of the group holds the r-th contiguous segment of every sequence
+(all heads).  Two small all-gathers connect the ranks and there is no other communication:
+  1. per-slice gate summaries {F_end, A_end} (16 bytes per slice) -> every rank's carry-in {F_in, A_in};
+  2. per-slice segment states (S [D,D], z [D], A_end; 0.53 MB per rank at 8 heads) -> every rank's
+     inbound state, folded locally from the lower ranks' states.
+The folds are plain tensor arithmetic (``fold_gate_summaries``, ``fold_states``) and do not care where
+the tensors live, which is how the CPU tests drive them over gloo.
+"""
+import torch
+
+from . import _lib
+
+__all__ = ["mlstm_chunkwise", "mlstm_chunkwise_sequence_parallel", "fold_gate_summaries", "fold_states",
+           "ChunkSegment"]
+
+
+class ChunkSegment:
+    """One segment's pass through the four C-ABI stages, holding its workspace."""
+
+    def __init__(self, q, k, v, f, i, chunk_size=256):
+        if q.dim() != 4 or k.shape != q.shape or v.shape != q.shape:
+            raise ValueError("q, k, v must share the shape [B, NH, S, D]")
+        if f.shape != q.shape[:3] or i.shape != q.shape[:3]:
+            raise ValueError("f, i must have the shape [B, NH, S]")
+        if not (k.dtype == v.dtype == f.dtype == i.dtype == q.dtype):
+            raise TypeError("q, k, v, f, i must share one element type")
+        self.dev = _lib.require_cuda(q, k, v, f, i)
+        self.q, self.k, self.v, self.f, self.i = q, k, v, f, i
+        self.B, self.NH, self.S, self.D = q.shape
+        self.dt = _lib.dtype_code(q)
+        self.chunk = int(chunk_size)
+        self.L = _lib.lib()
+        nbytes = self.L.mlstm_chunk_workspace(self.B, self.NH, self.S, self.D, self.dt, self.chunk)
+        if nbytes == 0:
+            raise _lib.MlstmError(-4, "mlstm_chunk_workspace (needs float16/bfloat16, D = 128, chunk % 128 == 0)")
+        self.ws = _lib.workspace(nbytes, self.dev)
+        self.dims = (self.B, self.NH, self.S, self.D, self.dt, self.chunk)
+
+    def _stream(self):
+        return _lib.stream_ptr(self.dev)
+
+    def gate_summary(self):
+        """{F_end, A_end} of this segment alone (no carry): float64 [B*NH, 2]."""
+        out = torch.empty((self.B * self.NH, 2), dtype=torch.float64, device=self.dev)
+        with torch.cuda.device(self.dev):
+            rc = self.L.mlstm_chunk_gate_summary(self.f.data_ptr(), self.i.data_ptr(), out.data_ptr(), self.B, self.NH,
+                                                 self.S, self.dt, self._stream())
+        _lib.check(rc, "mlstm_chunk_gate_summary")
+        return out
+
+    def prepare(self, carry_in=None):
+        """Gates (with the preceding segments' {F, A}, float64 [B*NH, 2], or None) and block states.
+        Returns {F_end, A_end} including the carry."""
+        if carry_in is not None:
+            carry_in = carry_in.to(device=self.dev, dtype=torch.float64).contiguous()
+        out = torch.empty((self.B * self.NH, 2), dtype=torch.float64, device=self.dev)
+        with torch.cuda.device(self.dev):
+            rc = self.L.mlstm_chunk_prepare(self.k.data_ptr(), self.v.data_ptr(), self.f.data_ptr(), self.i.data_ptr(),
+                                            carry_in.data_ptr() if carry_in is not None else None, out.data_ptr(),
+                                            self.ws.data_ptr(), self.ws.numel(), *self.dims, self._stream())
+        _lib.check(rc, "mlstm_chunk_prepare")
+        self._keep = carry_in
+        return out
+
+    def local_state(self):
+        """The state this segment adds: S [B*NH, D, D] (key, value), z [B*NH, D], stabilised by A_end."""
+        S = torch.empty((self.B * self.NH, self.D, self.D), dtype=torch.float32, device=self.dev)
+        z = torch.empty((self.B * self.NH, self.D), dtype=torch.float32, device=self.dev)
+        with torch.cuda.device(self.dev):
+            rc = self.L.mlstm_chunk_local_state(self.ws.data_ptr(), self.ws.numel(), S.data_ptr(), z.data_ptr(),
+                                                *self.dims, self._stream())
+        _lib.check(rc, "mlstm_chunk_local_state")
+        return S, z
+
+    def apply(self, state_in=None, h_dtype=torch.float32, return_state=False):
+        """h of the segment given the inbound (S, z) (stabilised by the carried-in A) or None."""
+        h = torch.empty((self.B, self.NH, self.S, self.D), dtype=h_dtype, device=self.dev)
+        S_in = z_in = None
+        if state_in is not None:
+            S_in = state_in[0].to(device=self.dev, dtype=torch.float32).contiguous()
+            z_in = state_in[1].to(device=self.dev, dtype=torch.float32).contiguous()
+        S_out = z_out = None
+        if return_state:
+            S_out = torch.empty((self.B * self.NH, self.D, self.D), dtype=torch.float32, device=self.dev)
+            z_out = torch.empty((self.B * self.NH, self.D), dtype=torch.float32, device=self.dev)
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        with torch.cuda.device(self.dev):
+            rc = self.L.mlstm_chunk_apply(self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), ptr(S_in), ptr(z_in),
+                                          h.data_ptr(), _lib.dtype_code(h), ptr(S_out), ptr(z_out), self.ws.data_ptr(),
+                                          self.ws.numel(), *self.dims, self._stream())
+        _lib.check(rc, "mlstm_chunk_apply")
+        _lib.maybe_read_status(self.ws, self.dev, "mlstm_chunk_apply")
+        return (h, (S_out, z_out)) if return_state else h
+
+
+def mlstm_chunkwise(q, k, v, f, i, chunk_size=256, h_dtype=torch.float32, initial=None, return_state=False):
+    """Chunkwise forward on one GPU.
+
+    ``initial`` = (S, z, F, A) continues an earlier segment: S [B*NH, D, D] and z [B*NH, D] float32
+    stabilised by A, and F, A float64 [B*NH] (the log-forget total and the prefix maximum of a = i - F
+    at the end of that segment).  With ``return_state`` the same tuple for the end of this call is
+    returned beside h.
+    """
+    seg = ChunkSegment(q, k, v, f, i, chunk_size)
+    carry = None
+    state_in = None
+    if initial is not None:
+        S0, z0, F0, A0 = initial
+        carry = torch.stack([F0.double().reshape(-1), A0.double().reshape(-1)], dim=1)
+        state_in = (S0, z0)
+    summary = seg.prepare(carry)
+    out = seg.apply(state_in, h_dtype=h_dtype, return_state=return_state)
+    if return_state:
+        h, (S1, z1) = out
+        return h, (S1, z1, summary[:, 0].clone(), summary[:, 1].clone())
+    return out
+
+
+def fold_gate_summaries(local):
+    """local: [G, BH, 2] = every segment's own {F_end, A_end} (no carry, float64).
+    Returns carry_in [G, BH, 2]: {F, A} accumulated over the segments before each one (A of the first
+    segment is -inf).  With F_in the log-forget total before segment g, a position's a = i - F shifts
+    by -F_in, hence the segment's prefix maximum in global terms is A_local - F_in."""
+    local = local.double()
+    G = local.shape[0]
+    F_loc, A_loc = local[..., 0], local[..., 1]
+    F_in = torch.cumsum(F_loc, 0) - F_loc                      # exclusive prefix sum over segments
+    A_glob = A_loc - F_in
+    A_in = torch.full_like(A_glob, -float("inf"))
+    for g in range(1, G):
+        A_in[g] = torch.maximum(A_in[g - 1], A_glob[g - 1])
+    return torch.stack([F_in, A_in], dim=-1)
+
+
+def fold_states(S_all, z_all, A_end_all, rank):
+    """Inbound state of segment ``rank`` from the states the lower segments add.
+
+    S_all [G, BH, D, D], z_all [G, BH, D]: each segment's added state, stabilised by its own A_end
+    (A_end_all [G, BH], float64, carries included, non-decreasing in g).  The result is stabilised by
+    A_end of segment rank-1, i.e. by the carried-in A of segment ``rank``.  None for rank 0."""
+    if rank == 0:
+        return None
+    A_ref = A_end_all[rank - 1].double()
+    S = torch.zeros_like(S_all[0], dtype=torch.float32)
+    z = torch.zeros_like(z_all[0], dtype=torch.float32)
+    for g in range(rank):
+        w = torch.exp(A_end_all[g].double() - A_ref).float()    # <= 1
+        S = S + w[:, None, None] * S_all[g].float()
+        z = z + w[:, None] * z_all[g].float()
+    return S, z
+
+
+def _all_gather(t, group):
+    import torch.distributed as dist
+    out = [torch.empty_like(t) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(out, t.contiguous(), group=group)
+    return torch.stack(out, 0)
+
+
+def sequence_parallel_forward(segment, group=None, h_dtype=torch.float32):
+    """The sequence-parallel protocol over any object with the ChunkSegment interface."""
+    import torch.distributed as dist
+    rank = dist.get_rank(group)
+    local = segment.gate_summary()                                   # [BH, 2]
+    carry_all = fold_gate_summaries(_all_gather(local, group))       # [G, BH, 2]
+    summary = segment.prepare(carry_all[rank] if rank > 0 else None)  # [BH, 2] incl. carry
+    S_loc, z_loc = segment.local_state()
+    S_all = _all_gather(S_loc, group)
+    z_all = _all_gather(z_loc, group)
+    A_end_all = _all_gather(summary[:, 1].contiguous(), group)
+    state_in = fold_states(S_all, z_all, A_end_all, rank)
+    return segment.apply(state_in, h_dtype=h_dtype)
+
+
+def mlstm_chunkwise_sequence_parallel(q, k, v, f, i, chunk_size=256, group=None, h_dtype=torch.float32):
+    """Every rank passes its contiguous segment [B, NH, S/G, D] (rank order = sequence order) and gets
+    the outputs of that segment.  Needs an initialised torch.distributed process group (NCCL)."""
+    return sequence_parallel_forward(ChunkSegment(q, k, v, f, i, chunk_size), group=group, h_dtype=h_dtype)
