@@ -148,6 +148,163 @@ def run_reference(args, rank):
     }))
 
 
+def run_forward_workload(args, rank, world, local_rank):
+    """The forward-only configurations, same JSON contract as the headline workload."""
+    import ctypes
+    import importlib
+    import torch
+    from oracle import mlstm_oracle as orc
+    pkg = importlib.import_module("xlstm-triton-cuda-implementation_b200")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    g = torch.Generator().manual_seed(0)
+    mk = lambda *s: torch.randn(*s, generator=g)
+    peaks = measured_peaks()
+    name = args.workload
+    scaling = "weak"
+    if name == "cfg5":
+        B, NH, S, D = 1, 8, 65536, 128
+        full = {"q": (mk(B, NH, S, D) * D ** -0.5).bfloat16(), "k": (mk(B, NH, S, D) * D ** -0.5).bfloat16(),
+                "v": (mk(B, NH, S, D) * D ** -0.5).bfloat16(), "f": (3.0 + mk(B, NH, S)).bfloat16(), "i": mk(B, NH, S).bfloat16()}
+        a, b = rank * S // world, (rank + 1) * S // world   # contiguous segment of this rank
+        host = {k: v[:, :, a:b].contiguous() for k, v in full.items()}
+        scaling = "strong"
+        if world > 1:
+            fn = lambda t: pkg.mlstm_chunkwise_sequence_parallel(t["q"], t["k"], t["v"], t["f"], t["i"], chunk_size=256,
+                                                                 h_dtype=torch.bfloat16)
+        else:
+            fn = lambda t: pkg.mlstm_chunkwise(t["q"], t["k"], t["v"], t["f"], t["i"], chunk_size=256, h_dtype=torch.bfloat16)
+        L = 256
+        flops = (4 * D * (L * (L + 1) // 2) * (S // L) + 4 * S * D * D) * B * NH      # intra + inter, whole job
+        units, unit, metric = B * S, "tokens/s", "mlstm_chunkwise_fwd_tokens_per_s"
+        workload = "cfg5: chunkwise mLSTM forward B=1 NH=8 S=65536 D=128 bf16, chunk 256"
+        bound, alg = "tensor", flops
+        launches = 5 if world == 1 else 7
+    elif name == "cfg3":
+        B, NH, S, D = 1, 4, 2048, 1024
+        host = {"q": mk(B, NH, S, D), "k": mk(B, NH, S, D), "v": mk(B, NH, S, D), "f": mk(B, NH, S), "i": mk(B, NH, S),
+                "o": mk(B, NH, S, D)}
+        fn = lambda t: pkg.mlstm_scan(t["q"], t["k"], t["v"], t["f"], t["i"], t["o"], reduce_block_size=4, value_block_size=4)
+        alg = (5 * B * NH * S * D + 2 * B * NH * S) * 4                                   # 4 reads + 1 write, fp32
+        units, unit, metric = alg / 1e9, "GB/s", "mlstm_scan_fwd_GB_per_s"
+        workload = "cfg3: mLSTM scan forward with output gate B=1 NH=4 S=2048 D=1024 fp32"
+        bound = "hbm"
+        launches = 2
+    else:
+        S, D = 640, 128
+        u = lambda *s: (torch.rand(*s, generator=g) * 2 - 1).half()
+        host = {"q": u(S, D), "k": u(S, D), "v": u(S, D), "f": u(S), "i": u(S)}
+        L_ = pkg._lib.lib()
+        ws = pkg._lib.workspace(L_.mlstm_forward_f16_workspace(S, D), dev)
+        hbuf = torch.empty(S, D, dtype=torch.float16, device=dev)
+
+        def fn(t):
+            rc = L_.mlstm_forward_f16(t["q"].data_ptr(), t["k"].data_ptr(), t["v"].data_ptr(), t["f"].data_ptr(),
+                                      t["i"].data_ptr(), hbuf.data_ptr(), S, D, ws.data_ptr(), ws.numel(),
+                                      pkg._lib.stream_ptr(dev))
+            pkg._lib.check(rc, "mlstm_forward_f16")
+            return hbuf
+        alg = 4 * D * (S * (S + 1) // 2)
+        units, unit, metric = S, "tokens/s", "mlstm_forward_f16_tokens_per_s"
+        workload = "cfg1: C++ driver single-head fp16 forward S=640 D=128"
+        bound = "tensor"
+        launches = 2
+    host = {k: v.pin_memory() for k, v in host.items()}
+    d = {k: v.to(dev) for k, v in host.items()}
+    small = sum(v.numel() * v.element_size() for v in host.values()) < 200e6
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if small else None
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        fn(d)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    sampler.mark(0)
+    total_ms = 0.0
+    for _ in range(args.steps):
+        if flush is not None:
+            flush.zero_()                       # inputs fit in L2: flush it between timed iterations
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        out = fn(d)
+        e1.record()
+        barrier()
+        total_ms += e0.elapsed_time(e1)
+    sampler.mark(1)
+    clocks = sampler.stop()
+    out_host = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+    e2e_ms = 0.0
+    for _ in range(args.steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        t = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+        out_host.copy_(fn(t), non_blocking=True)
+        e1.record()
+        barrier()
+        e2e_ms += e0.elapsed_time(e1)
+    times = torch.tensor([total_ms, e2e_ms], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = times.tolist()
+    if rank == 0:
+        ms = total_ms / args.steps
+        value = units / (ms * 1e-3)
+        if bound == "tensor":
+            achieved, peak, runit = alg / (ms * 1e-3) / 1e12, peaks["tflops"], "TFLOP/s"
+        else:
+            achieved, peak, runit = alg / (ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
+        line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+                "ms_per_step": ms, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+                "dtype": {"cfg5": "bf16", "cfg3": "f32", "cfg1": "f16"}[name], "data": "synthetic",
+                "config": {"workload": workload, "l2": "L2 flushed between timed iterations" if small else "inputs larger than L2"},
+                "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": runit, "frac": achieved / peak,
+                             "peak_source": peaks["source"], "traffic": None},
+                "e2e": {"value": units / (e2e_ms / args.steps * 1e-3), "unit": unit,
+                        "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in host.values()),
+                        "d2h_bytes_per_step": out_host.numel() * out_host.element_size()},
+                "gpu_launches": launches * args.steps, "clocks": clocks}
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            torch.set_num_threads(threads)
+            if name == "cfg1":
+                lib = ctypes.CDLL(os.path.join(ROOT, "oracle", "libmlstm_oracle.so"))
+                arrs = [host[k].float().numpy().copy() for k in ("q", "k", "v", "f", "i")]
+                import numpy as np
+                H = np.zeros((S, D), dtype=np.float32)
+                p = lambda a_: a_.ctypes.data_as(ctypes.c_void_p)
+                t0 = time.perf_counter()
+                lib.mlstm_cpu_forward(*[p(a_) for a_ in arrs], p(H), ctypes.c_uint(S), ctypes.c_uint(D), ctypes.c_int(1))
+                dt = time.perf_counter() - t0
+                line["cpu_baseline"] = {"value": S / dt, "unit": unit, "cores": threads, "kind": "port",
+                                        "sample": f"whole workload, C restatement of mlstmCpu with OpenMP, {dt:.3f} s"}
+            else:
+                steps_cpu = 96   # recurrent oracle, one head, a bounded number of time steps
+                sl = {k: v[:, :1, :steps_cpu].float() for k, v in host.items()}
+                o = sl.get("o", torch.zeros_like(sl["q"]))
+                t0 = time.perf_counter()
+                orc.scan_forward(sl["q"], sl["k"], sl["v"], sl["f"], sl["i"], o, dtype=torch.float32)
+                dt = time.perf_counter() - t0
+                frac = steps_cpu / (host["q"].shape[1] * host["q"].shape[2])   # of all (head, position) pairs
+                line["cpu_baseline"] = {"value": units * frac / dt, "unit": unit, "cores": threads, "kind": "port",
+                                        "sample": f"{steps_cpu} time steps of one head of the recurrent oracle, {dt:.2f} s"}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -155,12 +312,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="cfg4", choices=["cfg4", "cfg5", "cfg3", "cfg1"],
+                    help="cfg4 (default, the headline): matmul fwd+bwd; cfg5: chunkwise forward S=65536, "
+                         "sequence-parallel for N>1; cfg3: scan forward fp32 D=1024; cfg1: C++ single-head fp16 forward")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload != "cfg4":
+        run_forward_workload(args, rank, world, local_rank)
         return
 
     import importlib

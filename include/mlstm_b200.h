@@ -6,7 +6,8 @@
  * mlstm_matmul.py:46-55).  Every entry point only enqueues work on `stream` (a cudaStream_t passed
  * as void*; NULL = the default stream) and returns at once with 0 or a negative MLSTM_E_* code; it
  * never prints, aborts or synchronises.  The library is stateless: scratch memory is a caller-owned
- * workspace whose size the matching *_workspace() function reports.  The first 256 bytes of a
+ * workspace whose size the matching *_workspace() function reports (pass it the same flags as the call:
+ * fp32 inputs on the tensor cores need room for tf32-rounded copies of the operands).  The first 256 bytes of a
  * workspace hold a device status word that kernels set when they give up on an internal wait;
  * mlstm_read_status() copies it to the host (this one call synchronises the stream).
  */
@@ -38,10 +39,15 @@ extern "C" {
 /* flags */
 #define MLSTM_F_FORCE_SIMT 1 /* use the CUDA-core kernels even where the tensor-core path applies */
 #define MLSTM_F_FORCE_TC 2   /* fail with MLSTM_E_UNSUPPORTED instead of using the CUDA-core path */
+#define MLSTM_F_ALLOW_TF32 4 /* fp32 inputs may use the tensor cores with tf32 operands (fp32 accumulate);
+                                without it fp32 inputs get IEEE fp32 dot products, as the reference's
+                                tl.dot(..., allow_tf32=False) (mlstm_matmul.py:19) */
 
 const char* mlstm_status_string(int status);
 
-/* 1 when the tcgen05 path handles this case (16-bit inputs, D in {64, 128, 256}), else 0. */
+/* Whether the tcgen05 path handles this case (D in {64, 128, 256}): 1 for 16-bit inputs, 2 for fp32
+ * inputs (used only with MLSTM_F_ALLOW_TF32), else 0.  The scan entry also takes D = 512 .. 4096 in
+ * multiples of 256 on the tensor cores (sliced forward). */
 int mlstm_tc_supported(int S, int D, int dtype);
 
 /* Parallel (matmul) forward.
@@ -50,7 +56,7 @@ int mlstm_tc_supported(int S, int D, int dtype);
  *   q, k, v [B,NH,S,D], f, i [B,NH,S] of `dtype`; h [B,NH,S,D] of `h_dtype` (MLSTM_DT_F32 as the
  *   reference's Python path, or the input type); m, b [B,NH,S] fp32 (the reference's saved M, B).
  */
-size_t mlstm_mm_fwd_workspace(int B, int NH, int S, int D, int dtype);
+size_t mlstm_mm_fwd_workspace(int B, int NH, int S, int D, int dtype, int flags);
 int mlstm_mm_fwd(const void* q, const void* k, const void* v, const void* f, const void* i, void* h, float* m,
                  float* b, void* workspace, size_t workspace_bytes, int B, int NH, int S, int D, int dtype,
                  int h_dtype, int flags, void* stream);
@@ -62,7 +68,7 @@ int mlstm_mm_fwd(const void* q, const void* k, const void* v, const void* f, con
  *   dh, h of `h_dtype`; q, k, v, f, i and the outputs dq, dk, dv, df, di of `dtype`; m, b fp32 as
  *   written by mlstm_mm_fwd.  df[..., 0] is exactly 0 (mlstm_matmul.py:316, 392).
  */
-size_t mlstm_mm_bwd_workspace(int B, int NH, int S, int D, int dtype, int h_dtype);
+size_t mlstm_mm_bwd_workspace(int B, int NH, int S, int D, int dtype, int h_dtype, int flags);
 int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, const void* f, const void* i,
                  const void* h, const float* m, const float* b, void* dq, void* dk, void* dv, void* df, void* di,
                  void* workspace, size_t workspace_bytes, int B, int NH, int S, int D, int dtype, int h_dtype,
@@ -73,7 +79,7 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
  * precompute_mlstm_triton_scan (:74-137), reduce_mlstm_triton (:143-195), mlstm_triton_scan
  * (:200-278).  q, k, v, o [B,NH,S,D], f, i [B,NH,S] of `dtype`; h fp32 [B,NH,S,D].
  */
-size_t mlstm_scan_fwd_workspace(int B, int NH, int S, int D, int dtype);
+size_t mlstm_scan_fwd_workspace(int B, int NH, int S, int D, int dtype, int flags);
 int mlstm_scan_fwd(const void* q, const void* k, const void* v, const void* f, const void* i, const void* o,
                    void* h, void* workspace, size_t workspace_bytes, int B, int NH, int S, int D, int dtype,
                    int flags, void* stream);

@@ -23,11 +23,12 @@ def test_library_exports_every_declared_symbol(pkg):
 
 def test_workspace_sizes_and_support_matrix(pkg):
     L = pkg._lib.lib()
-    assert L.mlstm_mm_fwd_workspace(1, 1, 128, 64, 2) >= 256 + 2 * 128 * 4
-    assert L.mlstm_mm_fwd_workspace(0, 1, 128, 64, 2) == 0
-    assert L.mlstm_mm_bwd_workspace(1, 1, 100, 64, 2, 0) > L.mlstm_mm_bwd_workspace(1, 1, 100, 64, 2, 2)
+    assert L.mlstm_mm_fwd_workspace(1, 1, 128, 64, 2, 0) >= 256 + 2 * 128 * 4
+    assert L.mlstm_mm_fwd_workspace(0, 1, 128, 64, 2, 0) == 0
+    assert L.mlstm_mm_bwd_workspace(1, 1, 100, 64, 2, 0, 0) > L.mlstm_mm_bwd_workspace(1, 1, 100, 64, 2, 2, 0)
+    assert L.mlstm_mm_fwd_workspace(1, 1, 128, 64, 0, 4) > L.mlstm_mm_fwd_workspace(1, 1, 128, 64, 0, 0)   # tf32 copies
     assert L.mlstm_tc_supported(4096, 256, 2) == 1
-    assert L.mlstm_tc_supported(4096, 256, 0) == 0
+    assert L.mlstm_tc_supported(4096, 256, 0) == 2   # fp32: only with MLSTM_F_ALLOW_TF32
     assert L.mlstm_tc_supported(4096, 96, 2) == 0
 
 

@@ -82,6 +82,19 @@ def test_tensor_core_forward_backward(gc, dtype, D, S, f_mean):
         assert all(v < TOL_16 for v in eb.values()), (h_dtype, eb)
 
 
+@pytest.mark.parametrize("D", [64, 128, 256])
+def test_tf32_tensor_core_forward_backward(gc, D):
+    """fp32 inputs on the tensor cores (tf32 operands, fp32 accumulate), opt-in by flag."""
+    x = gc.make_inputs(1, 2, 328, D, torch.float32, f_mean=1.0, qkv_scale=D ** -0.5, seed=D)
+    flags = gc._lib.F_FORCE_TC | gc._lib.F_ALLOW_TF32
+    h, m, b = gc.run_forward(x, flags=flags)
+    ef = gc.errors_forward(x, h, m, b)
+    # tf32 keeps 10 mantissa bits of every operand: about 1e-3 on h, 1e-3 .. 5e-3 on gradients (measured)
+    assert ef["h"] < 3e-3 and ef["m"] < 1e-5 and ef["b"] < 3e-3, ef
+    eb = gc.errors_backward(x, gc.run_backward(x, h, m, b, flags=flags), torch.float32)
+    assert all(v < TOL_16 for v in eb.values()), eb
+
+
 def test_tensor_core_matches_simt_on_device(gc):
     """Same 16-bit inputs through both kernel families."""
     x = gc.make_inputs(2, 2, 640, 128, torch.bfloat16, f_mean=3.0, qkv_scale=128 ** -0.5, seed=3)

@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libmlstm_b200.so")
 
 DT_F32, DT_F16, DT_BF16 = 0, 1, 2
-F_FORCE_SIMT, F_FORCE_TC = 1, 2
+F_FORCE_SIMT, F_FORCE_TC, F_ALLOW_TF32 = 1, 2, 4
 _DTYPES = {torch.float32: DT_F32, torch.float16: DT_F16, torch.bfloat16: DT_BF16}
 
 _lib = None
@@ -41,15 +41,15 @@ def lib():
     L.mlstm_tc_supported.restype = i32
     L.mlstm_tc_supported.argtypes = [i32, i32, i32]
     L.mlstm_mm_fwd_workspace.restype = sz
-    L.mlstm_mm_fwd_workspace.argtypes = [i32] * 5
+    L.mlstm_mm_fwd_workspace.argtypes = [i32] * 6
     L.mlstm_mm_fwd.restype = i32
     L.mlstm_mm_fwd.argtypes = [vp] * 8 + [vp, sz] + [i32] * 7 + [vp]
     L.mlstm_mm_bwd_workspace.restype = sz
-    L.mlstm_mm_bwd_workspace.argtypes = [i32] * 6
+    L.mlstm_mm_bwd_workspace.argtypes = [i32] * 7
     L.mlstm_mm_bwd.restype = i32
     L.mlstm_mm_bwd.argtypes = [vp] * 14 + [vp, sz] + [i32] * 7 + [vp]
     L.mlstm_scan_fwd_workspace.restype = sz
-    L.mlstm_scan_fwd_workspace.argtypes = [i32] * 5
+    L.mlstm_scan_fwd_workspace.argtypes = [i32] * 6
     L.mlstm_scan_fwd.restype = i32
     L.mlstm_scan_fwd.argtypes = [vp] * 7 + [vp, sz] + [i32] * 6 + [vp]
     L.mlstm_forward_f16_workspace.restype = sz
@@ -106,10 +106,24 @@ def stream_ptr(dev) -> int:
     return torch.cuda.current_stream(dev).cuda_stream
 
 
+_WS_CACHE = {}
+
+
 def workspace(nbytes: int, dev) -> torch.Tensor:
+    """Scratch memory for one library call: a grow-only buffer per (device, stream).
+
+    Calls that share a stream run in order, so they can share one buffer; calls on different
+    streams get different buffers.  Keeping it avoids a large allocation per call (hundreds of MB
+    at the largest configurations)."""
     if nbytes <= 0:
         raise MlstmError(-2, "workspace query")
-    return torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    dev = torch.device(dev)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), stream_ptr(dev))
+    buf = _WS_CACHE.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        _WS_CACHE[key] = buf
+    return buf
 
 
 def check(code: int, where: str):

@@ -89,12 +89,31 @@ bool use_tc(int S, int D, int dtype, int flags, int* rc) {
         *rc = MLSTM_E_ARG;
         return false;
     }
-    const bool can = tc_supported(S, D, dtype);
+    // fp32 inputs take the tensor cores (as tf32) only when the caller allows that arithmetic
+    const bool can = tc_supported(S, D, dtype) && (dtype != MLSTM_DT_F32 || (flags & MLSTM_F_ALLOW_TF32));
     if (flags & MLSTM_F_FORCE_TC) {
         if (!can) *rc = MLSTM_E_UNSUPPORTED;
         return can;
     }
     return can && !(flags & MLSTM_F_FORCE_SIMT);
+}
+
+// fp32 inputs on the tensor cores are first rounded to tf32 into workspace copies (n tensors)
+size_t tf32_copy_bytes(int BH, int S, int D, int dtype, int flags, int ntensors) {
+    const bool tc = (tc_supported(S, D, dtype) || tc_split_supported(S, D, dtype)) && (flags & MLSTM_F_ALLOW_TF32) &&
+                    !(flags & MLSTM_F_FORCE_SIMT);
+    return (dtype == MLSTM_DT_F32 && tc) ? ntensors * al(static_cast<size_t>(BH) * S * D * sizeof(float)) : 0;
+}
+// rounds `count` tensors into consecutive regions of `buf` and redirects the pointers
+int round_inputs(const void** ptrs, int count, void* buf, int BH, int S, int D, cudaStream_t st) {
+    const size_t one = al(static_cast<size_t>(BH) * S * D * sizeof(float));
+    for (int k = 0; k < count; k++) {
+        void* dst = static_cast<uint8_t*>(buf) + k * one;
+        int rc = launch_round_tf32(ptrs[k], dst, static_cast<long long>(BH) * S * D, st);
+        if (rc != MLSTM_OK) return rc;
+        ptrs[k] = dst;
+    }
+    return MLSTM_OK;
 }
 
 int run_pass(bool tc, int mode, const PassParams& p, int in_dt, int out_dt, cudaStream_t st) {
@@ -103,16 +122,21 @@ int run_pass(bool tc, int mode, const PassParams& p, int in_dt, int out_dt, cuda
 
 int forward_impl(const void* q, const void* k, const void* v, const void* f, const void* i, const void* o, void* h,
                  float* m, float* b, const FwdWs& w, int BH, int S, int D, int dtype, int h_dtype, int flags,
-                 cudaStream_t st) {
+                 cudaStream_t st, void* tf32buf = nullptr) {
     int rc;
     const bool tc = use_tc(S, D, dtype, flags, &rc);
     if (rc != MLSTM_OK) return rc;
     const int Spad = round_up(S, TILE);
     if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
     if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, m, BH, S, Spad, dtype, st)) != MLSTM_OK) return rc;
+    const void* in[3] = {q, k, v};
+    if (tc && dtype == MLSTM_DT_F32) {
+        if (!tf32buf) return MLSTM_E_WORKSPACE;
+        if ((rc = round_inputs(in, 3, tf32buf, BH, S, D, st)) != MLSTM_OK) return rc;
+    }
     PassParams p{};
     p.S = S; p.Spad = Spad; p.BH = BH; p.D = D;
-    p.X = q; p.Y = k; p.Z = v;
+    p.X = in[0]; p.Y = in[1]; p.Z = in[2];
     p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_ref = w.a_ref;
     p.er_add = -0.5f * log2f(static_cast<float>(D));
     p.out = h; p.m = m; p.b_out = b; p.ogate = o;
@@ -144,12 +168,14 @@ const char* mlstm_status_string(int s) {
     return "unknown status";
 }
 
-int mlstm_tc_supported(int S, int D, int dtype) { return tc_supported(S, D, dtype) ? 1 : 0; }
+int mlstm_tc_supported(int S, int D, int dtype) {
+    if (!tc_supported(S, D, dtype)) return 0;
+    return dtype == MLSTM_DT_F32 ? 2 : 1;
+}
 
-size_t mlstm_mm_fwd_workspace(int B, int NH, int S, int D, int dtype) {
-    (void)dtype;
+size_t mlstm_mm_fwd_workspace(int B, int NH, int S, int D, int dtype, int flags) {
     if (check_dims(B, NH, S, D) != MLSTM_OK) return 0;
-    return carve_fwd(nullptr, B * NH, S, false).bytes;
+    return carve_fwd(nullptr, B * NH, S, false).bytes + tf32_copy_bytes(B * NH, S, D, dtype, flags, 3);
 }
 
 int mlstm_mm_fwd(const void* q, const void* k, const void* v, const void* f, const void* i, void* h, float* m, float* b,
@@ -161,14 +187,16 @@ int mlstm_mm_fwd(const void* q, const void* k, const void* v, const void* f, con
     if (rc != MLSTM_OK) return rc;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(h)) return MLSTM_E_ALIGN;
     FwdWs w = carve_fwd(workspace, B * NH, S, false);
-    if (!workspace || workspace_bytes < w.bytes || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
+    const size_t extra = tf32_copy_bytes(B * NH, S, D, dtype, flags, 3);
+    if (!workspace || workspace_bytes < w.bytes + extra || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
     return forward_impl(q, k, v, f, i, nullptr, h, m, b, w, B * NH, S, D, dtype, h_dtype, flags,
-                        static_cast<cudaStream_t>(stream));
+                        static_cast<cudaStream_t>(stream), extra ? static_cast<uint8_t*>(workspace) + w.bytes : nullptr);
 }
 
-size_t mlstm_mm_bwd_workspace(int B, int NH, int S, int D, int dtype, int h_dtype) {
+size_t mlstm_mm_bwd_workspace(int B, int NH, int S, int D, int dtype, int h_dtype, int flags) {
     if (check_dims(B, NH, S, D) != MLSTM_OK) return 0;
-    return carve_bwd(nullptr, B * NH, S, D, dtype != MLSTM_DT_F32 && h_dtype != dtype).bytes;
+    return carve_bwd(nullptr, B * NH, S, D, dtype != MLSTM_DT_F32 && h_dtype != dtype).bytes +
+           tf32_copy_bytes(B * NH, S, D, dtype, flags, 4);
 }
 
 int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, const void* f, const void* i, const void* h,
@@ -184,7 +212,8 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     const int BH = B * NH, Spad = round_up(S, TILE);
     const bool need16 = dtype != MLSTM_DT_F32 && h_dtype != dtype;
     BwdWs w = carve_bwd(workspace, BH, S, D, need16);
-    if (!workspace || workspace_bytes < w.bytes || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
+    const size_t extra = tf32_copy_bytes(BH, S, D, dtype, flags, 4);
+    if (!workspace || workspace_bytes < w.bytes + extra || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
     const bool tc = use_tc(S, D, dtype, flags, &rc);
     if (rc != MLSTM_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -194,18 +223,26 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     if ((rc = launch_bwd_prep(h, dh, b, m, w.gAn, w.gB, w.g, w.dh16, BH, S, Spad, D, h_dtype, dtype, st)) != MLSTM_OK)
         return rc;
     const void* dhp = need16 ? w.dh16 : dh;  // dh in the element type of q, k, v
+    const void* orig_q = q;
+    const void* orig_k = k;
+    if (tc && dtype == MLSTM_DT_F32) {  // tf32 operands: rounded copies of q, k, v, dh
+        if (!extra) return MLSTM_E_WORKSPACE;
+        const void* in[4] = {q, k, v, dhp};
+        if ((rc = round_inputs(in, 4, static_cast<uint8_t*>(workspace) + w.bytes, BH, S, D, st)) != MLSTM_OK) return rc;
+        q = in[0]; k = in[1]; v = in[2]; dhp = in[3];
+    }
 
     PassParams p{};
     p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status;
     // dQ = ((dH V^T + g_r) * decay) K
     p.X = dhp; p.Y = v; p.Z = k;
     p.row_rel = w.gB; p.row_ref = w.An_ref; p.row_g = w.g; p.col_rel = w.ga; p.col_ref = w.a_ref; p.col_g = nullptr;
-    p.out = dq; p.dot_src = q; p.dot_out = w.R;
+    p.out = dq; p.dot_src = orig_q; p.dot_out = w.R;
     if ((rc = run_pass(tc, DQ, p, dtype, dtype, st)) != MLSTM_OK) return rc;
     // dK = ((V dH^T + g_c) * decay)  Q
     p.X = v; p.Y = dhp; p.Z = q;
     p.row_rel = w.ga; p.row_ref = w.a_ref; p.row_g = nullptr; p.col_rel = w.gB; p.col_ref = w.An_ref; p.col_g = w.g;
-    p.out = dk; p.dot_src = k; p.dot_out = w.dI;
+    p.out = dk; p.dot_src = orig_k; p.dot_out = w.dI;
     if ((rc = run_pass(tc, DK, p, dtype, dtype, st)) != MLSTM_OK) return rc;
     // dV = ((K Q^T) * decay / n) dH
     p.X = k; p.Y = q; p.Z = dhp;
@@ -215,10 +252,15 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     return launch_df(f, w.dI, w.R, df, di, BH, S, Spad, dtype, st);
 }
 
-size_t mlstm_scan_fwd_workspace(int B, int NH, int S, int D, int dtype) {
-    (void)dtype;
+// the sliced forward (head dimension above 256) also needs an fp32 numerator buffer [BH, S, D]
+static size_t scan_num_bytes(int BH, int S, int D, int dtype) {
+    return tc_split_supported(S, D, dtype) ? al(static_cast<size_t>(BH) * S * D * sizeof(float)) : 0;
+}
+
+size_t mlstm_scan_fwd_workspace(int B, int NH, int S, int D, int dtype, int flags) {
     if (check_dims(B, NH, S, D) != MLSTM_OK) return 0;
-    return carve_fwd(nullptr, B * NH, S, true).bytes;
+    return carve_fwd(nullptr, B * NH, S, true).bytes + scan_num_bytes(B * NH, S, D, dtype) +
+           tf32_copy_bytes(B * NH, S, D, dtype, flags, 3);
 }
 
 int mlstm_scan_fwd(const void* q, const void* k, const void* v, const void* f, const void* i, const void* o, void* h,
@@ -229,10 +271,37 @@ int mlstm_scan_fwd(const void* q, const void* k, const void* v, const void* f, c
     int rc = check_dims(B, NH, S, D);
     if (rc != MLSTM_OK) return rc;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(h)) return MLSTM_E_ALIGN;
-    FwdWs w = carve_fwd(workspace, B * NH, S, true);
-    if (!workspace || workspace_bytes < w.bytes || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
-    return forward_impl(q, k, v, f, i, o, h, w.m, w.b, w, B * NH, S, D, dtype, MLSTM_DT_F32, flags,
-                        static_cast<cudaStream_t>(stream));
+    const int BH = B * NH;
+    FwdWs w = carve_fwd(workspace, BH, S, true);
+    const size_t num_bytes = scan_num_bytes(BH, S, D, dtype);
+    const size_t extra = tf32_copy_bytes(BH, S, D, dtype, flags, 3);
+    if (!workspace || workspace_bytes < w.bytes + num_bytes + extra || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
+    void* tf32buf = extra ? static_cast<uint8_t*>(workspace) + w.bytes + num_bytes : nullptr;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool math_ok = dtype != MLSTM_DT_F32 || (flags & MLSTM_F_ALLOW_TF32);
+    if (num_bytes && math_ok && !(flags & MLSTM_F_FORCE_SIMT)) {
+        // head dimension above 256: contraction and output columns are sliced over CTAs, partial
+        // numerators and row sums are added up in fp32, then normalised and gated in one more pass
+        float* num = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + w.bytes);
+        const int Spad = round_up(S, TILE);
+        if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
+        if (cudaMemsetAsync(num, 0, static_cast<size_t>(BH) * S * D * sizeof(float), st) != cudaSuccess) return MLSTM_E_CUDA;
+        if (cudaMemsetAsync(w.b, 0, static_cast<size_t>(BH) * S * sizeof(float), st) != cudaSuccess) return MLSTM_E_CUDA;
+        if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, w.m, BH, S, Spad, dtype, st)) != MLSTM_OK) return rc;
+        const void* in[3] = {q, k, v};
+        if (dtype == MLSTM_DT_F32 && (rc = round_inputs(in, 3, tf32buf, BH, S, D, st)) != MLSTM_OK) return rc;
+        PassParams p{};
+        p.S = S; p.Spad = Spad; p.BH = BH; p.D = 256; p.Dfull = D;
+        p.X = in[0]; p.Y = in[1]; p.Z = in[2];
+        p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_ref = w.a_ref;
+        p.er_add = -0.5f * log2f(static_cast<float>(D));
+        p.out = num; p.m = w.m; p.b_out = w.b;
+        p.status = w.status;
+        if ((rc = launch_fwd_split_tc(p, dtype, st)) != MLSTM_OK) return rc;
+        return launch_scan_finalize(num, w.b, w.m, o, static_cast<float*>(h), BH, S, D, dtype, st);
+    }
+    if ((flags & MLSTM_F_FORCE_TC) && D > 256) return MLSTM_E_UNSUPPORTED;
+    return forward_impl(q, k, v, f, i, o, h, w.m, w.b, w, BH, S, D, dtype, MLSTM_DT_F32, flags, st, tf32buf);
 }
 
 size_t mlstm_forward_f16_workspace(unsigned S, unsigned D) {

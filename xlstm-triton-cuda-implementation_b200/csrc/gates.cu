@@ -220,7 +220,73 @@ __global__ void __launch_bounds__(SCAN_THREADS) df_kernel(const T* __restrict__ 
     }
 }
 
+// Last step of the sliced forward: h = num / (max(|b|, exp(-m)) + 1e-6) * silu(o), four columns per thread
+// (mlstm_scan.py:273-278).
+template <typename T>
+__global__ void scan_finalize_kernel(const float* __restrict__ num, const float* __restrict__ b,
+                                     const float* __restrict__ m, const T* __restrict__ o, float* __restrict__ h,
+                                     long long rows, int D) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int per_row = D / 4;
+    if (idx >= rows * per_row) return;
+    const long long row = idx / per_row;
+    const size_t off = static_cast<size_t>(idx) * 4;
+    const float n = fmaxf(fabsf(b[row]), expf(-m[row])) + 1e-6f;
+    const float4 x = *reinterpret_cast<const float4*>(num + off);
+    float4 y;
+    y.x = x.x / n * silu_f(to_f32<T>(o[off + 0]));
+    y.y = x.y / n * silu_f(to_f32<T>(o[off + 1]));
+    y.z = x.z / n * silu_f(to_f32<T>(o[off + 2]));
+    y.w = x.w / n * silu_f(to_f32<T>(o[off + 3]));
+    *reinterpret_cast<float4*>(h + off) = y;
+}
+
+// Round fp32 values to the nearest tf32 (10 mantissa bits).  The tensor cores drop the low 13 bits
+// of fp32 operands; rounding first halves the error and removes its bias.
+__global__ void round_tf32_kernel(const float4* __restrict__ in, float4* __restrict__ out, long long n4) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= n4) return;
+    const float4 x = in[idx];
+    uint4 y;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(y.x) : "f"(x.x));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(y.y) : "f"(x.y));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(y.z) : "f"(x.z));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(y.w) : "f"(x.w));
+    out[idx] = *reinterpret_cast<float4*>(&y);
+}
+
 }  // namespace
+
+int launch_round_tf32(const void* in, void* out, long long n, cudaStream_t st) {
+    const long long n4 = n / 4;
+    const int threads = 256;
+    const long long blocks = (n4 + threads - 1) / threads;
+    if (blocks > 0x7fffffffLL || (n & 3)) return MLSTM_E_SHAPE;
+    round_tf32_kernel<<<(unsigned)blocks, threads, 0, st>>>(static_cast<const float4*>(in), static_cast<float4*>(out), n4);
+    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+}
+
+int launch_scan_finalize(const float* num, const float* b, const float* m, const void* o, float* h, int BH, int S, int D,
+                         int dtype, cudaStream_t st) {
+    const long long rows = static_cast<long long>(BH) * S;
+    const long long work = rows * (D / 4);
+    const int threads = 256;
+    const long long blocks = (work + threads - 1) / threads;
+    if (blocks > 0x7fffffffLL) return MLSTM_E_SHAPE;
+    switch (dtype) {
+        case MLSTM_DT_F32:
+            scan_finalize_kernel<float><<<(unsigned)blocks, threads, 0, st>>>(num, b, m, (const float*)o, h, rows, D);
+            break;
+        case MLSTM_DT_F16:
+            scan_finalize_kernel<__half><<<(unsigned)blocks, threads, 0, st>>>(num, b, m, (const __half*)o, h, rows, D);
+            break;
+        case MLSTM_DT_BF16:
+            scan_finalize_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, st>>>(num, b, m, (const __nv_bfloat16*)o, h, rows, D);
+            break;
+        default: return MLSTM_E_ARG;
+    }
+    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+}
 
 int launch_gates_fwd(const void* f, const void* i, float* ga, float* gA, double* a_ref, double* An_ref, float* m, int BH,
                      int S, int Spad, int dtype, cudaStream_t st, const double* carry_in, double* summary_out,

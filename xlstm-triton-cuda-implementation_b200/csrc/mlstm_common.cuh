@@ -46,7 +46,8 @@ struct PassParams {
     int S;      // sequence length
     int Spad;   // S rounded up to TILE: stride of every gate vector per slice
     int BH;     // batch * heads
-    int D;      // head dimension
+    int D;      // head dimension (sliced forward: the slice width)
+    int Dfull;  // sliced forward only: the head dimension
     const void* X;  // stationary operand  [BH, S, D]
     const void* Y;  // first streamed operand
     const void* Z;  // second streamed operand
@@ -126,5 +127,10 @@ int launch_df(const void* f, const float* dI, const float* R, void* df, void* di
 int launch_pass_simt(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st);
 int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st);
 bool tc_supported(int S, int D, int in_dtype);
+bool tc_split_supported(int S, int D, int in_dtype);
+int launch_fwd_split_tc(const PassParams& p, int in_dtype, cudaStream_t st);
+int launch_round_tf32(const void* in, void* out, long long n, cudaStream_t st);
+int launch_scan_finalize(const float* num, const float* b, const float* m, const void* o, float* h, int BH, int S, int D,
+                         int dtype, cudaStream_t st);
 
 }  // namespace mlstm

@@ -1,24 +1,33 @@
 // Tensor-core contraction pass of the parallel mLSTM for sm_100a (tcgen05 MMA, TMEM accumulators,
 // TMA-staged 128-byte-swizzled shared-memory tiles).  One kernel template serves the forward and
-// the three backward passes (see mlstm_common.cuh for the algebra).  It takes the place of the
-// reference's mlstm_matmul_kernel (mlstm_matmul.py:37-101), mlstm_matmul_kernel_backward_db
-// (:132-197) and mlstm_matmul_kernel_backward (:200-316), and of the single-head fp16 kernel
-// mlstm_forward (cuda-src/mlstm_forward.cu:12-189).
+// the three backward passes (see mlstm_common.cuh for the algebra) and the two chunkwise passes.
+// It takes the place of the reference's mlstm_matmul_kernel (mlstm_matmul.py:37-101),
+// mlstm_matmul_kernel_backward_db (:132-197) and mlstm_matmul_kernel_backward (:200-316), of the
+// single-head fp16 kernel mlstm_forward (cuda-src/mlstm_forward.cu:12-189) and, with its sliced
+// form, of the scan kernels' contractions (mlstm_scan.py:74-137, 200-278).
 //
 // One CTA owns one stationary 128-row tile (queries in FWD/DQ, keys in DK/DV) of one batch*head
 // slice and streams the tiles on the causal side of it.  Warp roles (384 threads):
 //   warp 0      TMA producer: stationary tile once, then streamed tiles through a ring of slots
 //   warp 1      MMA issuer (one thread) and TMEM allocator
-//   warps 4-7   gate group 0: turns columns [0,64) of every T tile into gated 16-bit W values, in TMEM
+//   warps 4-7   gate group 0: turns columns [0,64) of every T tile into gated W values, in TMEM
 //   warps 8-11  gate group 1: columns [64,128)
-// TMEM (512 columns): T0 [0,128) and T1 [128,256) fp32 128x128; each group writes its half of W
-// (two 16-bit values per column) over the first 32 of its own 64 T columns; ACC [256, 256+D) fp32.
+// TMEM (512 columns): T0 [0,128) and T1 [128,256) fp32 128x128; ACC [256, 256+D) fp32.  W overwrites
+// T in place: 16-bit W packs two values per column, each group writing its half over the first 32 of
+// its own 64 T columns; 32-bit (tf32) W sits column for column on T.
 // The second contraction reads W straight from TMEM as the A operand and the streamed Z tile from
 // shared memory as an MN-major B operand, so the gated tile never touches shared or global memory.
+//
+// Element types: fp16 / bf16 (kind::f16) and fp32 read as tf32 (kind::tf32).  D is the width this CTA
+// contracts over in T and produces in ACC.  In the sliced form (SPLIT) the head dimension is larger
+// than D: a CTA takes one slice of the contraction and one slice of the output columns, and because
+// W and ACC are linear in T the partial results are summed with atomic adds (forward only).
 //
 // Every wait is bounded: a wait that runs out sets a CTA-wide abort word, every role leaves its
 // loop, the CTA stores a non-zero code in the status word, waits a little for copies in flight,
 // frees its TMEM and returns.
+#include <type_traits>
+
 #include "mlstm_common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -28,36 +37,50 @@ namespace {
 using namespace ptx;
 
 constexpr int NTHREADS = 384;
-constexpr int BOX_BYTES = 128 * 128;  // one TMA box: 128 rows of 128 bytes (64 16-bit elements)
+constexpr int BOX_BYTES = 128 * 128;  // one TMA box: 128 rows of 128 bytes
 constexpr long long WAIT_LIMIT = 4000000000LL;  // cycles (about two seconds)
 constexpr int SLICE_SET = 8;                    // slices whose CTAs are interleaved in launch order
 
-template <int D>
+template <int D, int ES>
 struct TcCfg {
-    static constexpr int CH = D < 128 ? D : 128;            // elements of D per ring slot
-    static constexpr int NHALF = D / CH;                    // slots per streamed tile
-    static constexpr int SLOT_BYTES = (CH / 64) * BOX_BYTES;
-    static constexpr int X_BYTES = (D / 64) * BOX_BYTES;
-    static constexpr int NSLOT = D == 256 ? 5 : (D == 128 ? 6 : 8);
+    static constexpr int EPB = 128 / ES;                      // elements per box row
+    static constexpr int KSTEP = 32 / ES;                     // contraction elements per MMA
+    static constexpr int CHMAX = ES == 2 ? 128 : 64;
+    static constexpr int CH = D < CHMAX ? D : CHMAX;          // elements of D per ring slot
+    static constexpr int NHALF = D / CH;                      // slots per streamed tile
+    static constexpr int SLOT_BYTES = (CH / EPB) * BOX_BYTES;
+    static constexpr int X_BYTES = (D / EPB) * BOX_BYTES;
+    static constexpr int NSLOT = ES == 2 ? (D == 256 ? 5 : (D == 128 ? 6 : 8)) : (D == 256 ? 3 : (D == 128 ? 5 : 6));
     static constexpr int NBAR = 1 + 2 * NSLOT + 2 + 2 + 1 + 1;  // x, slot full/empty, t_full, w_full, acc, part
     static constexpr int SMEM_BYTES = 1024 /*align slack*/ + X_BYTES + NSLOT * SLOT_BYTES + NBAR * 8 + 64 +
                                       2 * 128 * 4 /*row partials*/;
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA may have");
 };
 
 struct SmemTail {  // lives after the tiles
     float part[2][128];  // one partial per gate group and row (row sums in FWD, row dots in DQ/DK)
 };
 
-template <int MODE, int D, int ABFMT, typename OutT>
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+    uint32_t y;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(y) : "f"(x));
+    return y;
+}
+
+template <int MODE, int D, int ABFMT, typename OutT, bool SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
               const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmI,
               const __grid_constant__ CUtensorMap tmS, const PassParams p) {
-    using C = TcCfg<D>;
-    using InT = typename std::conditional<ABFMT == 1, __nv_bfloat16, __half>::type;
+    constexpr int ES = ABFMT == 2 ? 4 : 2;
+    constexpr bool TF32 = ABFMT == 2;
+    using C = TcCfg<D, ES>;
+    using InT = typename std::conditional<ABFMT == 2, float,
+                                          typename std::conditional<ABFMT == 1, __nv_bfloat16, __half>::type>::type;
     constexpr bool ROWS_ARE_Q = (MODE == FWD || MODE == DQ || MODE == FWDC);
     constexpr bool IS_FWD = (MODE == FWD || MODE == FWDC);   // normalised output, row sums kept
-    static_assert((MODE != FWDC && MODE != STATE) || D == 128, "chunkwise passes are built for D = 128");
+    static_assert((MODE != FWDC && MODE != STATE) || (D == 128 && ES == 2), "chunkwise passes are built for 16-bit D = 128");
+    static_assert(!SPLIT || MODE == FWD, "only the forward is sliced");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -68,7 +91,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     uint64_t* bar_full = bars + 1;
     uint64_t* bar_empty = bars + 1 + C::NSLOT;
     uint64_t* bar_t = bars + 1 + 2 * C::NSLOT;  // [2] T tile written by the first contraction
-    uint64_t* bar_w = bar_t + 2;                // [2] W tile written by a gate group
+    uint64_t* bar_w = bar_t + 2;                // [2] W tile written by the gate groups
     uint64_t* bar_acc = bar_w + 2;              // accumulator complete
     uint64_t* bar_part = bar_acc + 1;           // row partials of both gate groups in shared memory
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
@@ -78,6 +101,12 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int NT = p.Spad / TILE;
+    // full head dimension (row stride of every [BH, S, .] tensor) and this CTA's slices of it
+    const int Dfull = SPLIT ? p.Dfull : D;
+    const int nks = SPLIT ? Dfull / D : 1;
+    const int kslice = SPLIT ? static_cast<int>(blockIdx.y) % nks : 0;   // slice of the T contraction
+    const int vslice = SPLIT ? static_cast<int>(blockIdx.y) / nks : 0;   // slice of the output columns
+    const int xk0 = kslice * D, zv0 = vslice * D;
     // CTA order: slices in sets of SLICE_SET; inside a set the heaviest tiles come first.  The CTAs
     // resident at one time then share the K/V (or Q/dH) of a few slices, which stay in L2.
     int bh, w;
@@ -142,30 +171,31 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             prefetch_tmap(&tmI);
             prefetch_tmap(&tmS);
             mbar_expect_tx(bar_x, C::X_BYTES);
-            for (int c = 0; c < D / 64; c++) {
-                if (MODE == STATE) tma_load_3d(sX + c * BOX_BYTES, &tmI, bar_x, c * 64, 0, 0);
-                else tma_load_3d(sX + c * BOX_BYTES, &tmX, bar_x, c * 64, tile * TILE, bh);
+            for (int c = 0; c < D / C::EPB; c++) {
+                if (MODE == STATE) tma_load_3d(sX + c * BOX_BYTES, &tmI, bar_x, c * C::EPB, 0, 0);
+                else tma_load_3d(sX + c * BOX_BYTES, &tmX, bar_x, xk0 + c * C::EPB, tile * TILE, bh);
             }
             int it = 0;
             bool ok = true;
-            auto load_tile = [&](const CUtensorMap* map, int row, int z) {
+            // one streamed tile = NHALF slots of CH columns starting at column x0
+            auto load_tile = [&](const CUtensorMap* map, int x0, int row, int z) {
                 for (int hf = 0; hf < C::NHALF && ok; hf++, it++) {
                     const int s = it % C::NSLOT;
                     ok = mbar_wait(&bar_empty[s], ((it / C::NSLOT) & 1) ^ 1, abort_flag, WAIT_LIMIT);
                     if (!ok) break;
                     mbar_expect_tx(&bar_full[s], C::SLOT_BYTES);
                     uint8_t* dst = sSlot + s * C::SLOT_BYTES;
-                    for (int c = 0; c < C::CH / 64; c++)
-                        tma_load_3d(dst + c * BOX_BYTES, map, &bar_full[s], (hf * (C::CH / 64) + c) * 64, row, z);
+                    for (int c = 0; c < C::CH / C::EPB; c++)
+                        tma_load_3d(dst + c * BOX_BYTES, map, &bar_full[s], x0 + hf * C::CH + c * C::EPB, row, z);
                 }
             };
             auto load_y = [&](int t) {
-                if (is_state_step(t)) load_tile(&tmI, 0, 0);
-                else load_tile(&tmY, stream_tile(t) * TILE, bh);
+                if (is_state_step(t)) load_tile(&tmI, 0, 0, 0);
+                else load_tile(&tmY, xk0, stream_tile(t) * TILE, bh);
             };
             auto load_z = [&](int t) {
-                if (is_state_step(t)) load_tile(&tmS, 0, bh * p.NB + blk);
-                else load_tile(&tmZ, stream_tile(t) * TILE, bh);
+                if (is_state_step(t)) load_tile(&tmS, 0, 0, bh * p.NB + blk);
+                else load_tile(&tmZ, zv0, stream_tile(t) * TILE, bh);
             };
             // same order as the MMA issuer consumes: Y(0), then Y(t), Z(t-1) ..., Z(last)
             load_y(0);
@@ -180,6 +210,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         if (lane == 0) {
             constexpr uint32_t idesc1 = make_idesc(ABFMT, 128, 128, 0, 0);
             constexpr uint32_t idesc2 = make_idesc(ABFMT, 128, C::CH, 0, 1);
+            constexpr int KROWS_BYTES = C::KSTEP * 128;  // KSTEP streamed rows of the Z tile
             const uint32_t sX_addr = smem_u32(sX);
             const uint32_t sSlot_addr = smem_u32(sSlot);
             int it = 0;
@@ -197,11 +228,15 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     tc_fence_after();
                     const uint32_t zaddr = sSlot_addr + s * C::SLOT_BYTES;
 #pragma unroll
-                    for (int kk = 0; kk < 8; kk++) {  // 16 streamed rows per MMA
-                        const uint64_t bdesc = smem_desc_sw128(zaddr + kk * 2048, BOX_BYTES, 1024);
-                        // W rows 0-63 of the streamed tile sit in columns [0,32), rows 64-127 in columns [64,96)
-                        const uint32_t a_tmem = w_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
-                        mma_ts<false>(tmem_ACC + hf * C::CH, a_tmem, bdesc, idesc2, (u > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < TILE / C::KSTEP; kk++) {  // KSTEP streamed rows per MMA
+                        // Z is MN-major: 16-bit tiles use the plain 128-byte swizzle (groups of 8 rows),
+                        // 32-bit tiles the 32-byte-atom variant (groups of 4 rows)
+                        const uint64_t bdesc = TF32 ? smem_desc_sw128(zaddr + kk * KROWS_BYTES, BOX_BYTES, 512, 1)
+                                                    : smem_desc_sw128(zaddr + kk * KROWS_BYTES, BOX_BYTES, 1024, 2);
+                        // 16-bit W: streamed rows 0-63 in columns [0,32), rows 64-127 in columns [64,96);
+                        // 32-bit W: row j in column j.  Either way a K step is 8 columns.
+                        const uint32_t a_tmem = TF32 ? (w_tmem + kk * 8) : (w_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8));
+                        mma_ts<TF32>(tmem_ACC + hf * C::CH, a_tmem, bdesc, idesc2, (u > 0 || kk > 0) ? 1u : 0u);
                     }
                     tc_commit(&bar_empty[s]);
                 }
@@ -215,11 +250,12 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     tc_fence_after();
                     const uint32_t yaddr = sSlot_addr + s * C::SLOT_BYTES;
 #pragma unroll
-                    for (int kk = 0; kk < C::CH / 16; kk++) {
-                        const int kx = hf * (C::CH / 16) + kk;  // K step inside the stationary tile
+                    for (int kk = 0; kk < C::CH / C::KSTEP; kk++) {
+                        const int kx = hf * (C::CH / C::KSTEP) + kk;  // K step inside the stationary tile
+                        // four K steps (4 x 32 bytes) per 128-byte box row
                         const uint64_t adesc = smem_desc_sw128(sX_addr + (kx >> 2) * BOX_BYTES + (kx & 3) * 32, 16, 1024);
                         const uint64_t bdesc = smem_desc_sw128(yaddr + (kk >> 2) * BOX_BYTES + (kk & 3) * 32, 16, 1024);
-                        mma_ss<false>(tmem_T0 + (t & 1) * 128, adesc, bdesc, idesc1, kx > 0 ? 1u : 0u);
+                        mma_ss<TF32>(tmem_T0 + (t & 1) * 128, adesc, bdesc, idesc1, kx > 0 ? 1u : 0u);
                     }
                     tc_commit(&bar_empty[s]);
                 }
@@ -252,7 +288,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         bool ok = true;
 
         // Both groups work on every step: group g gates columns [64g, 64g+64) of the T tile (one
-        // reference block of the gate vectors) and writes its half of W over the first 32 of them.
+        // reference block of the gate vectors) and writes its part of W over them.
         const int cbase = grp * 64;
         auto load_cols = [&](const float* base, int sub, float (&dst)[32]) {
             const float4* p4 = reinterpret_cast<const float4*>(base + cbase + sub * 32);
@@ -282,7 +318,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             uint32_t tv0[32], tv1[32];
             tmem_ld32(t_tmem, tv0);
             tmem_ld32(t_tmem + 32, tv1);
-            uint32_t pk[32];
+            uint32_t pk[TF32 ? 1 : 32];
             const float er_w = (MODE == FWDC && state_step) ? fast_exp2(er) : 0.0f;
             tc_wait_ld();
 #pragma unroll
@@ -310,18 +346,24 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     }
                     cv[j] = wj;
                 }
+                if constexpr (TF32) {
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    if constexpr (ABFMT == 1) {
-                        __nv_bfloat162 v2 = __floats2bfloat162_rn(cv[2 * j], cv[2 * j + 1]);
-                        pk[sub * 16 + j] = *reinterpret_cast<uint32_t*>(&v2);
-                    } else {
-                        __half2 v2 = __floats2half2_rn(cv[2 * j], cv[2 * j + 1]);
-                        pk[sub * 16 + j] = *reinterpret_cast<uint32_t*>(&v2);
+                    for (int j = 0; j < 32; j++) tv[j] = to_tf32(cv[j]);
+                    tmem_st32(t_tmem + sub * 32, tv);   // in place: column for column
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        if constexpr (ABFMT == 1) {
+                            __nv_bfloat162 v2 = __floats2bfloat162_rn(cv[2 * j], cv[2 * j + 1]);
+                            pk[sub * 16 + j] = *reinterpret_cast<uint32_t*>(&v2);
+                        } else {
+                            __half2 v2 = __floats2half2_rn(cv[2 * j], cv[2 * j + 1]);
+                            pk[sub * 16 + j] = *reinterpret_cast<uint32_t*>(&v2);
+                        }
                     }
                 }
             }
-            tmem_st32(t_tmem, pk);
+            if constexpr (!TF32) tmem_st32(t_tmem, pk);
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(&bar_w[buf]);
@@ -332,12 +374,13 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         if (ok) {
             tc_fence_after();
             constexpr int HALF = D / 2;
+            constexpr int VEC = 16 / sizeof(InT);          // input elements per 16-byte access
             const int c0 = grp * HALF;
             const bool row_ok = (MODE == STATE) ? true : (grow < p.S);
-            // STATE writes block (bh, blk) of [BH, NB, D, D]; everything else row `grow` of [BH, S, D]
+            // STATE writes block (bh, blk) of [BH, NB, D, D]; everything else row `grow` of [BH, S, Dfull]
             const size_t row_off = (MODE == STATE)
                                        ? ((static_cast<size_t>(bh) * p.NB + blk) * D + r) * D
-                                       : (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * D;
+                                       : (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * Dfull + zv0;
             float inv_n = 1.0f;
             if (MODE == STATE) {
                 tail->part[grp][r] = rowsum;
@@ -352,16 +395,21 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 ok = mbar_wait(bar_part, 0, abort_flag, WAIT_LIMIT);
                 if (ok) {
                     const float bsum = tail->part[0][r] + tail->part[1][r];
-                    const float mrow = row_ok ? p.m[static_cast<size_t>(bh) * p.S + grow] : 0.0f;
-                    const float n = fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f;
-                    inv_n = 1.0f / n;
-                    if (grp == 0 && row_ok && p.b_out) p.b_out[static_cast<size_t>(bh) * p.S + grow] = bsum;
+                    if constexpr (SPLIT) {
+                        // partial row sum of this contraction slice; the normaliser is applied afterwards
+                        if (grp == 0 && row_ok && vslice == 0) atomicAdd(&p.b_out[static_cast<size_t>(bh) * p.S + grow], bsum);
+                    } else {
+                        const float mrow = row_ok ? p.m[static_cast<size_t>(bh) * p.S + grow] : 0.0f;
+                        const float n = fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f;
+                        inv_n = 1.0f / n;
+                        if (grp == 0 && row_ok && p.b_out) p.b_out[static_cast<size_t>(bh) * p.S + grow] = bsum;
+                    }
                 }
             }
             float dot = 0.0f;
             if (ok) {
                 OutT* orow = reinterpret_cast<OutT*>(p.out) + row_off + c0;
-                const InT* ogate_row = (IS_FWD && p.ogate) ? reinterpret_cast<const InT*>(p.ogate) + row_off + c0 : nullptr;
+                const InT* ogate_row = (IS_FWD && !SPLIT && p.ogate) ? reinterpret_cast<const InT*>(p.ogate) + row_off + c0 : nullptr;
                 const InT* drow = ((MODE == DQ || MODE == DK) && p.dot_src)
                                       ? reinterpret_cast<const InT*>(p.dot_src) + row_off + c0 : nullptr;
 #pragma unroll 1
@@ -379,14 +427,20 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                         }
                         if ((MODE == DQ || MODE == DK) && drow) {
 #pragma unroll
-                            for (int j8 = 0; j8 < 4; j8++) {
-                                const uint4 raw = *reinterpret_cast<const uint4*>(drow + ch * 32 + j8 * 8);
-                                const InT* e8 = reinterpret_cast<const InT*>(&raw);
+                            for (int jv = 0; jv < 32 / VEC; jv++) {
+                                const uint4 raw = *reinterpret_cast<const uint4*>(drow + ch * 32 + jv * VEC);
+                                const InT* ev = reinterpret_cast<const InT*>(&raw);
 #pragma unroll
-                                for (int j = 0; j < 8; j++) dot += vals[j8 * 8 + j] * to_f32<InT>(e8[j]);
+                                for (int j = 0; j < VEC; j++) dot += vals[jv * VEC + j] * to_f32<InT>(ev[j]);
                             }
                         }
-                        if constexpr (sizeof(OutT) == 4) {
+                        if constexpr (SPLIT) {
+#pragma unroll
+                            for (int j4 = 0; j4 < 8; j4++) {
+                                float4 o4 = make_float4(vals[j4 * 4], vals[j4 * 4 + 1], vals[j4 * 4 + 2], vals[j4 * 4 + 3]);
+                                atomicAdd(reinterpret_cast<float4*>(reinterpret_cast<float*>(orow) + ch * 32 + j4 * 4), o4);
+                            }
+                        } else if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
                             for (int j4 = 0; j4 < 8; j4++) {
                                 float4 o4 = make_float4(vals[j4 * 4], vals[j4 * 4 + 1], vals[j4 * 4 + 2], vals[j4 * 4 + 3]);
@@ -451,27 +505,35 @@ EncodeTiledFn get_encode() {
     return fn;
 }
 
-// [BH, S, D] 16-bit tensor, boxes of 64 elements x 128 rows, 128-byte swizzle, zero fill past S.
-int make_map(CUtensorMap* map, const void* base, int BH, int S, int D, int dtype) {
+// [N2, N1, N0] tensor (N0 contiguous), boxes of 128 bytes x 128 rows, 128-byte swizzle, zero fill
+// outside the tensor.
+// atom32: 128-byte swizzle with 32-byte atoms (needed where a 32-bit tile is read MN-major).
+int make_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, bool atom32 = false) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return MLSTM_E_CUDA;
-    cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(BH)};
-    cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(S) * D * 2};
-    cuuint32_t box[3] = {64, 128, 1};
+    const cuuint64_t es = dtype == MLSTM_DT_F32 ? 4 : 2;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(N0), static_cast<cuuint64_t>(N1), static_cast<cuuint64_t>(N2)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(N0) * es, static_cast<cuuint64_t>(N1) * N0 * es};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / es), 128, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUtensorMapDataType dt = dtype == MLSTM_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMapDataType dt = dtype == MLSTM_DT_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                             : dtype == MLSTM_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
-template <int MODE, int D, int ABFMT, typename OutT>
+template <int MODE, int D, int ABFMT, typename OutT, bool SPLIT>
 int launch_one(const PassParams& p, int in_dtype, cudaStream_t st) {
     CUtensorMap mx, my, mz, mi, ms;
     int rc;
-    if ((rc = make_map(&mx, p.X, p.BH, p.S, D, in_dtype)) != MLSTM_OK) return rc;
-    if ((rc = make_map(&my, p.Y, p.BH, p.S, D, in_dtype)) != MLSTM_OK) return rc;
-    if ((rc = make_map(&mz, p.Z, p.BH, p.S, D, in_dtype)) != MLSTM_OK) return rc;
+    const int Dfull = SPLIT ? p.Dfull : D;
+    if (SPLIT && (Dfull <= 0 || Dfull % D != 0)) return MLSTM_E_SHAPE;
+    if ((rc = make_map(&mx, p.X, p.BH, p.S, Dfull, in_dtype)) != MLSTM_OK) return rc;
+    if ((rc = make_map(&my, p.Y, p.BH, p.S, Dfull, in_dtype)) != MLSTM_OK) return rc;
+    if ((rc = make_map(&mz, p.Z, p.BH, p.S, Dfull, in_dtype, ABFMT == 2)) != MLSTM_OK) return rc;
     mi = mx;
     ms = mx;
     if (MODE == FWDC || MODE == STATE) {
@@ -482,8 +544,8 @@ int launch_one(const PassParams& p, int in_dtype, cudaStream_t st) {
         if (!p.states || !p.zstate) return MLSTM_E_ARG;
         if ((rc = make_map(&ms, p.states, p.BH * p.NB, D, D, in_dtype)) != MLSTM_OK) return rc;
     }
-    auto kern = mlstm_tc_pass<MODE, D, ABFMT, OutT>;
-    constexpr int smem = TcCfg<D>::SMEM_BYTES;
+    auto kern = mlstm_tc_pass<MODE, D, ABFMT, OutT, SPLIT>;
+    constexpr int smem = TcCfg<D, ABFMT == 2 ? 4 : 2>::SMEM_BYTES;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
         cudaGetLastError();
         return MLSTM_E_CUDA;
@@ -491,16 +553,20 @@ int launch_one(const PassParams& p, int in_dtype, cudaStream_t st) {
     const int NT = p.Spad / TILE;
     const long long nblk = static_cast<long long>(MODE == STATE ? p.NB : NT) * p.BH;
     if (nblk > 0x7fffffffLL) return MLSTM_E_SHAPE;
-    kern<<<static_cast<unsigned>(nblk), NTHREADS, smem, st>>>(mx, my, mz, mi, ms, p);
+    const int nsl = SPLIT ? (Dfull / D) * (Dfull / D) : 1;  // contraction slices x output slices
+    if (nsl > 65535) return MLSTM_E_SHAPE;
+    kern<<<dim3(static_cast<unsigned>(nblk), nsl), NTHREADS, smem, st>>>(mx, my, mz, mi, ms, p);
     return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
 template <int MODE, int D, int ABFMT>
 int launch_out(const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) {
-    if (out_dtype == MLSTM_DT_F32) return launch_one<MODE, D, ABFMT, float>(p, in_dtype, st);
-    if (out_dtype == in_dtype) {
-        if (ABFMT == 1) return launch_one<MODE, D, ABFMT, __nv_bfloat16>(p, in_dtype, st);
-        return launch_one<MODE, D, ABFMT, __half>(p, in_dtype, st);
+    if (out_dtype == MLSTM_DT_F32) return launch_one<MODE, D, ABFMT, float, false>(p, in_dtype, st);
+    if constexpr (ABFMT != 2) {
+        if (out_dtype == in_dtype) {
+            if (ABFMT == 1) return launch_one<MODE, D, ABFMT, __nv_bfloat16, false>(p, in_dtype, st);
+            return launch_one<MODE, D, ABFMT, __half, false>(p, in_dtype, st);
+        }
     }
     return MLSTM_E_ARG;
 }
@@ -508,7 +574,11 @@ int launch_out(const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st
 template <int MODE, int D>
 int launch_fmt(const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) {
     if (in_dtype == MLSTM_DT_BF16) return launch_out<MODE, D, 1>(p, in_dtype, out_dtype, st);
-    return launch_out<MODE, D, 0>(p, in_dtype, out_dtype, st);
+    if (in_dtype == MLSTM_DT_F16) return launch_out<MODE, D, 0>(p, in_dtype, out_dtype, st);
+    if constexpr (MODE != FWDC && MODE != STATE) {
+        if (in_dtype == MLSTM_DT_F32) return launch_out<MODE, D, 2>(p, in_dtype, out_dtype, st);
+    }
+    return MLSTM_E_UNSUPPORTED;
 }
 
 template <int MODE>
@@ -524,7 +594,13 @@ int launch_d(const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) 
 }  // namespace
 
 bool tc_supported(int S, int D, int in_dtype) {
-    return S >= 1 && (D == 64 || D == 128 || D == 256) && (in_dtype == MLSTM_DT_F16 || in_dtype == MLSTM_DT_BF16);
+    return S >= 1 && (D == 64 || D == 128 || D == 256) &&
+           (in_dtype == MLSTM_DT_F16 || in_dtype == MLSTM_DT_BF16 || in_dtype == MLSTM_DT_F32);
+}
+
+bool tc_split_supported(int S, int D, int in_dtype) {
+    return S >= 1 && D > 256 && D % 256 == 0 && D <= 4096 &&
+           (in_dtype == MLSTM_DT_F16 || in_dtype == MLSTM_DT_BF16 || in_dtype == MLSTM_DT_F32);
 }
 
 int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) {
@@ -540,6 +616,19 @@ int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, c
         case STATE:
             if (p.D != 128 || out_dtype != MLSTM_DT_F32) return MLSTM_E_UNSUPPORTED;
             return launch_fmt<STATE, 128>(p, in_dtype, out_dtype, st);
+    }
+    return MLSTM_E_ARG;
+}
+
+// Sliced forward for head dimensions above 256: p.D is the slice width (256), p.Dfull the head
+// dimension, p.out an fp32 [BH, S, Dfull] buffer and p.b_out an fp32 [BH, S] buffer, both zeroed by
+// the caller; the launch adds the un-normalised numerator and the row sums into them.
+int launch_fwd_split_tc(const PassParams& p, int in_dtype, cudaStream_t st) {
+    if (p.D != 256 || !tc_split_supported(p.S, p.Dfull, in_dtype)) return MLSTM_E_UNSUPPORTED;
+    switch (in_dtype) {
+        case MLSTM_DT_F32: return launch_one<FWD, 256, 2, float, true>(p, in_dtype, st);
+        case MLSTM_DT_BF16: return launch_one<FWD, 256, 1, float, true>(p, in_dtype, st);
+        case MLSTM_DT_F16: return launch_one<FWD, 256, 0, float, true>(p, in_dtype, st);
     }
     return MLSTM_E_ARG;
 }

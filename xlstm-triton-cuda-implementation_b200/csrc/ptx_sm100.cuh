@@ -174,13 +174,17 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 //   MN-major use (contraction index runs across rows): stride-dimension offset = 1024 B (eight
 //     contraction rows), leading-dimension offset = distance between two 128-byte-wide column
 //     groups of the tile.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+//   MN-major use with 32-bit elements (tf32): the only layout the hardware takes is the 128-byte
+//     swizzle with 32-byte atoms (layout type 1; what a TMA box written with SWIZZLE_128B_ATOM_32B
+//     looks like): groups of four contraction rows, stride-dimension offset = 512 B.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                    uint32_t layout_type = 2) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
     d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= static_cast<uint64_t>(1) << 46;  // descriptor version of this architecture
-    d |= static_cast<uint64_t>(2) << 61;  // SWIZZLE_128B
+    d |= static_cast<uint64_t>(layout_type) << 61;  // 2 = SWIZZLE_128B, 1 = SWIZZLE_128B with 32-byte atoms
     return d;
 }
 

@@ -42,7 +42,7 @@ class ChunkSegment:
         nbytes = self.L.mlstm_chunk_workspace(self.B, self.NH, self.S, self.D, self.dt, self.chunk)
         if nbytes == 0:
             raise _lib.MlstmError(-4, "mlstm_chunk_workspace (needs float16/bfloat16, D = 128, chunk % 128 == 0)")
-        self.ws = _lib.workspace(nbytes, self.dev)
+        self.ws = torch.empty(nbytes, dtype=torch.uint8, device=self.dev)   # holds state between the stages: not shared
         self.dims = (self.B, self.NH, self.S, self.D, self.dt, self.chunk)
 
     def _stream(self):

@@ -10,12 +10,21 @@ q, k, v: [B, NH, S, D]; f, i: [B, NH, S]; CUDA, contiguous, float32 / float16 / 
 ``h`` is float32 whatever the inputs are, as in the reference (mlstm_matmul.py:373); gradients have
 the inputs' type (:389-393).  ``SB`` and ``num_warps`` are the reference's tiling hints: they are
 checked (positive integers) and otherwise ignored, the kernels pick their own tiles.
+
+float32 inputs are computed with IEEE fp32 dot products, like the reference's
+``tl.dot(..., allow_tf32=False)`` (mlstm_matmul.py:19).  Setting the environment variable
+``MLSTM_B200_TF32=1`` (or passing ``flags=_lib.F_ALLOW_TF32`` to the two plain functions) lets them
+use the tensor cores with tf32 operands instead (D in {64, 128, 256}; error about 5e-4).
 """
+import os
 import torch
 
 from . import _lib
 
 __all__ = ["Triton_mLSTM", "mlstm_matmul", "mlstm_matmul_forward", "mlstm_matmul_backward"]
+
+
+_DEFAULT_FLAGS = _lib.F_ALLOW_TF32 if os.environ.get("MLSTM_B200_TF32", "0") not in ("", "0") else 0
 
 
 def _check_hints(SB, num_warps):
@@ -42,7 +51,7 @@ def mlstm_matmul_forward(q, k, v, f, i, h_dtype=torch.float32, flags=0):
     m = torch.empty((B, NH, S), device=dev, dtype=torch.float32)
     b = torch.empty((B, NH, S), device=dev, dtype=torch.float32)
     L = _lib.lib()
-    ws = _lib.workspace(L.mlstm_mm_fwd_workspace(B, NH, S, D, dt), dev)
+    ws = _lib.workspace(L.mlstm_mm_fwd_workspace(B, NH, S, D, dt, flags), dev)
     with torch.cuda.device(dev):
         rc = L.mlstm_mm_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), f.data_ptr(), i.data_ptr(), h.data_ptr(),
                             m.data_ptr(), b.data_ptr(), ws.data_ptr(), ws.numel(), B, NH, S, D, dt,
@@ -62,7 +71,7 @@ def mlstm_matmul_backward(dh, q, k, v, f, i, h, m, b, flags=0):
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     df, di = torch.empty_like(f), torch.empty_like(i)
     L = _lib.lib()
-    ws = _lib.workspace(L.mlstm_mm_bwd_workspace(B, NH, S, D, dt, hdt), dev)
+    ws = _lib.workspace(L.mlstm_mm_bwd_workspace(B, NH, S, D, dt, hdt, flags), dev)
     with torch.cuda.device(dev):
         rc = L.mlstm_mm_bwd(dh.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), f.data_ptr(), i.data_ptr(),
                             h.data_ptr(), m.data_ptr(), b.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
@@ -79,7 +88,7 @@ class Triton_mLSTM(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, f, i, SB=16, num_warps=8):
         _check_hints(SB, num_warps)
-        h, m, b = mlstm_matmul_forward(q, k, v, f, i)
+        h, m, b = mlstm_matmul_forward(q, k, v, f, i, flags=_DEFAULT_FLAGS)
         ctx.save_for_backward(q, k, v, f, i, m, b, h)
         ctx.sb = SB
         return h
@@ -88,11 +97,11 @@ class Triton_mLSTM(torch.autograd.Function):
     def backward(ctx, dh):
         assert dh.is_contiguous()  # mlstm_matmul.py:385
         q, k, v, f, i, m, b, h = ctx.saved_tensors
-        dq, dk, dv, df, di = mlstm_matmul_backward(dh, q, k, v, f, i, h, m, b)
+        dq, dk, dv, df, di = mlstm_matmul_backward(dh, q, k, v, f, i, h, m, b, flags=_DEFAULT_FLAGS)
         return dq, dk, dv, df, di, None, None
 
 
 def mlstm_matmul(q, k, v, f, i, SB=16, num_warps=8):
     """Forward without autograd (mlstm_matmul.py:121-129)."""
     _check_hints(SB, num_warps)
-    return mlstm_matmul_forward(q, k, v, f, i)[0]
+    return mlstm_matmul_forward(q, k, v, f, i, flags=_DEFAULT_FLAGS)[0]
