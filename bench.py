@@ -53,54 +53,62 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle-reason samples taken in-process through NVML while the timed region runs
+    (two light queries every 25 ms; a polling nvidia-smi process disturbed sub-millisecond kernels)."""
+    REASONS = (("hw_slowdown", 0x8), ("sw_power_cap", 0x4), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40))
 
     def __init__(self, index):
-        self.index, self.proc, self.lines = str(index), None, []
+        self.index, self.samples, self.stop_flag, self.thread = int(index), [], False, None
         self.window = [None, None]  # wall-clock bounds of the timed region
+        self.nvml = None
 
     def mark(self, which):
         self.window[which] = time.time()
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", self.index, f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "20"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = self.index
+            if vis:
+                entry = vis.split(",")[self.index].strip()
+                idx = int(entry) if entry.isdigit() else self.index
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self.nvml = pynvml
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nvml = None
+            return
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append((time.time(), line.strip()))
+    def _loop(self):
+        n = self.nvml
+        while not self.stop_flag:
+            try:
+                clk = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                reasons = int(n.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                self.samples.append((time.time(), clk, reasons))
+            except Exception:
+                pass
+            time.sleep(0.025)
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
+        if self.nvml is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"], "samples": 0}
+        self.stop_flag = True
         self.thread.join(timeout=2)
-        sm, smax, reasons = [], None, set()
         lo, hi = self.window
-        for ts, ln in self.lines:
-            if lo is not None and hi is not None and not (lo <= ts <= hi + 0.02):
+        sm, seen = [], set()
+        for ts, clk, reasons in self.samples:
+            if lo is not None and hi is not None and not (lo <= ts <= hi + 0.03):
                 continue
-            parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                smax = float(parts[2])
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+            sm.append(clk)
+            for name, bit in self.REASONS:
+                if reasons & bit:
+                    seen.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.sm_max, "reasons": sorted(seen),
                 "samples": len(sm)}
 
 
@@ -225,8 +233,9 @@ def run_forward_workload(args, rank, world, local_rank):
             torch.cuda.synchronize()
 
     warmup = max(args.warmup, 3)
+    out = None
     for _ in range(warmup):
-        fn(d)
+        out = fn(d)          # held like in the timed loop, so the allocator reaches its steady state
     sampler = ClockSampler(local_rank)
     sampler.start()
     barrier()
@@ -364,8 +373,10 @@ def main():
 
     sampler = ClockSampler(local_rank)  # started early: the first samples take a while to arrive
     sampler.start()
-    for _ in range(warmup):
-        step(d)
+    h = m = b = None
+    for _ in range(warmup):  # same tensor lifetimes as the timed loop, so the allocator reaches its steady state
+        h, m, b = pkg.mlstm_matmul_forward(d["q"], d["k"], d["v"], d["f"], d["i"], h_dtype=torch.bfloat16)
+        pkg.mlstm_matmul_backward(d["dh"], d["q"], d["k"], d["v"], d["f"], d["i"], h, m, b)
     barrier()
 
     # ---- device-resident timing, with separate events around the forward and the backward call

@@ -125,8 +125,8 @@ int mlstm_forward_f16_static(const void* Q, const void* K, const void* V, const 
  *                             carried-in A, or NULL/NULL); optionally the outbound state S_out, z_out
  * summary / carry arrays are device doubles [B*NH][2] in natural-log units. */
 size_t mlstm_chunk_workspace(int B, int NH, int S, int D, int dtype, int chunk);
-int mlstm_chunk_gate_summary(const void* f, const void* i, double* summary, int B, int NH, int S, int dtype,
-                             void* stream);
+int mlstm_chunk_gate_summary(const void* f, const void* i, double* summary, void* workspace, size_t workspace_bytes,
+                             int B, int NH, int S, int D, int dtype, int chunk, void* stream);
 int mlstm_chunk_prepare(const void* k, const void* v, const void* f, const void* i, const double* carry_in,
                         double* summary_out, void* workspace, size_t workspace_bytes, int B, int NH, int S, int D,
                         int dtype, int chunk, void* stream);

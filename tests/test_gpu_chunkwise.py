@@ -32,6 +32,7 @@ def _dev(x, names=("q", "k", "v", "f", "i")):
     (torch.float16, 768, 128, 3.0),
     (torch.bfloat16, 256, 256, -2.0),     # a single block: no inbound state anywhere
     (torch.bfloat16, 2048, 512, 5.0),
+    (torch.bfloat16, 9000, 256, 3.0),     # long enough for the segmented gate scan, ragged
 ])
 def test_chunkwise_against_oracle(gc, dtype, S, chunk, f_mean):
     x = gc.make_inputs(1, 2, S, 128, dtype, f_mean=f_mean, qkv_scale=128 ** -0.5, seed=S + chunk)
@@ -56,9 +57,10 @@ def test_segment_stages_against_model(gc):
     mc = importlib.import_module(PKG + ".mlstm_chunkwise")
     seg = mc.ChunkSegment(*_dev(x), chunk_size=256)
     model = km.ChunkSegmentModel(*host, chunk_size=256)
-    assert orc.max_abs_rel(seg.gate_summary().cpu(), model.gate_summary()) < 1e-9
+    # log-sigmoid is evaluated in fp32 (1e-7 relative per term) and summed in double
+    assert orc.max_abs_rel(seg.gate_summary().cpu(), model.gate_summary()) < 1e-6
     carry = torch.tensor([[-3.0, 1.5], [-1.0, -0.25]], dtype=torch.float64)
-    assert orc.max_abs_rel(seg.prepare(carry).cpu(), model.prepare(carry)) < 1e-9
+    assert orc.max_abs_rel(seg.prepare(carry).cpu(), model.prepare(carry)) < 1e-6
     S_g, z_g = seg.local_state()
     S_m, z_m = model.local_state()
     assert orc.max_abs_rel(S_g.cpu(), S_m) < TOL_16

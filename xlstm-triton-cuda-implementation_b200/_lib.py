@@ -61,7 +61,7 @@ def lib():
     L.mlstm_chunk_workspace.restype = sz
     L.mlstm_chunk_workspace.argtypes = [i32] * 6
     L.mlstm_chunk_gate_summary.restype = i32
-    L.mlstm_chunk_gate_summary.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
+    L.mlstm_chunk_gate_summary.argtypes = [vp, vp, vp, vp, sz] + [i32] * 6 + [vp]
     L.mlstm_chunk_prepare.restype = i32
     L.mlstm_chunk_prepare.argtypes = [vp] * 6 + [vp, sz] + [i32] * 6 + [vp]
     L.mlstm_chunk_local_state.restype = i32

@@ -45,20 +45,33 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
     float4 s = init ? *reinterpret_cast<const float4*>(init + static_cast<size_t>(bh) * per_block + off)
                     : make_float4(0.f, 0.f, 0.f, 0.f);
     const double* bound = An_bound + static_cast<size_t>(bh) * (NB + 1);
-    for (int k = 0; k < NB; k++) {
-        if (is_vec) {
-            *reinterpret_cast<float4*>(zstate + (static_cast<size_t>(bh) * NB + k) * D + off) = s;
-        } else {
-            T16 o[4] = {from_f32<T16>(s.x), from_f32<T16>(s.y), from_f32<T16>(s.z), from_f32<T16>(s.w)};
-            *reinterpret_cast<uint2*>(states + (static_cast<size_t>(bh) * NB + k) * DD + off) = *reinterpret_cast<uint2*>(o);
+    constexpr int PF = 8;  // blocks whose contributions are fetched ahead of the serial update
+    for (int k0 = 0; k0 < NB; k0 += PF) {
+        float4 u[PF];
+        float d[PF];
+#pragma unroll
+        for (int j = 0; j < PF; j++) {
+            if (k0 + j < NB) {
+                u[j] = __ldg(reinterpret_cast<const float4*>(src + static_cast<size_t>(k0 + j) * per_block));
+                // exp(A_end(k-1) - A_end(k)); 0 for the first block when there is no inbound carry (bound[0] = +inf)
+                d[j] = exp2f(static_cast<float>(bound[k0 + j + 1] - bound[k0 + j]));
+            }
         }
-        // exp(A_end(k-1) - A_end(k)); 0 for the first block when there is no inbound carry (bound[0] = +inf)
-        const float d = exp2f(static_cast<float>(bound[k + 1] - bound[k]));
-        const float4 u = *reinterpret_cast<const float4*>(src + static_cast<size_t>(k) * per_block);
-        s.x = (d == 0.0f ? 0.0f : d * s.x) + u.x;
-        s.y = (d == 0.0f ? 0.0f : d * s.y) + u.y;
-        s.z = (d == 0.0f ? 0.0f : d * s.z) + u.z;
-        s.w = (d == 0.0f ? 0.0f : d * s.w) + u.w;
+#pragma unroll
+        for (int j = 0; j < PF; j++) {
+            const int k = k0 + j;
+            if (k >= NB) break;
+            if (is_vec) {
+                *reinterpret_cast<float4*>(zstate + (static_cast<size_t>(bh) * NB + k) * D + off) = s;
+            } else {
+                T16 o[4] = {from_f32<T16>(s.x), from_f32<T16>(s.y), from_f32<T16>(s.z), from_f32<T16>(s.w)};
+                *reinterpret_cast<uint2*>(states + (static_cast<size_t>(bh) * NB + k) * DD + off) = *reinterpret_cast<uint2*>(o);
+            }
+            s.x = (d[j] == 0.0f ? 0.0f : d[j] * s.x) + u[j].x;
+            s.y = (d[j] == 0.0f ? 0.0f : d[j] * s.y) + u[j].y;
+            s.z = (d[j] == 0.0f ? 0.0f : d[j] * s.z) + u[j].z;
+            s.w = (d[j] == 0.0f ? 0.0f : d[j] * s.w) + u[j].w;
+        }
     }
     float* dst = is_vec ? z_end : S_end;
     if (dst) *reinterpret_cast<float4*>(dst + static_cast<size_t>(bh) * per_block + off) = s;
@@ -67,7 +80,7 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
 struct ChunkWs {
     int* status;
     float *ga, *gAn, *m, *b, *U, *zU, *zstate;
-    double *a_ref, *An_ref, *An_bound;
+    double *a_ref, *An_ref, *An_bound, *gscratch;
     void *ident, *states;
     int NB;
     size_t bytes;
@@ -94,6 +107,8 @@ ChunkWs carve(void* ws, int BH, int S, int D, int chunk) {
     w.m = static_cast<float*>(take(static_cast<size_t>(BH) * S * sizeof(float)));
     w.b = static_cast<float*>(take(static_cast<size_t>(BH) * S * sizeof(float)));
     w.An_bound = static_cast<double*>(take(static_cast<size_t>(BH) * (w.NB + 1) * sizeof(double)));
+    const size_t gs = gates_scratch_bytes(BH, static_cast<int>(Spad));
+    w.gscratch = gs ? static_cast<double*>(take(gs)) : nullptr;
     w.ident = take(static_cast<size_t>(TILE) * TILE * 2);
     w.U = static_cast<float*>(take(nblk * D * D * sizeof(float)));
     w.zU = static_cast<float*>(take(nblk * D * sizeof(float)));
@@ -150,10 +165,15 @@ size_t mlstm_chunk_workspace(int B, int NH, int S, int D, int dtype, int chunk) 
     return carve(nullptr, B * NH, S, D, chunk).bytes;
 }
 
-int mlstm_chunk_gate_summary(const void* f, const void* i, double* summary, int B, int NH, int S, int dtype, void* stream) {
-    if (!f || !i || !summary || B <= 0 || NH <= 0 || S <= 0) return MLSTM_E_ARG;
+int mlstm_chunk_gate_summary(const void* f, const void* i, double* summary, void* workspace, size_t workspace_bytes, int B,
+                             int NH, int S, int D, int dtype, int chunk, void* stream) {
+    if (!f || !i || !summary) return MLSTM_E_ARG;
+    int rc = check_chunk_args(B, NH, S, D, dtype, chunk);
+    if (rc != MLSTM_OK) return rc;
+    ChunkWs w = carve(workspace, B * NH, S, D, chunk);
+    if (!workspace || workspace_bytes < w.bytes) return MLSTM_E_WORKSPACE;
     return launch_gates_fwd(f, i, nullptr, nullptr, nullptr, nullptr, nullptr, B * NH, S, round_up(S, TILE), dtype,
-                            static_cast<cudaStream_t>(stream), nullptr, summary, nullptr, 0);
+                            static_cast<cudaStream_t>(stream), nullptr, summary, nullptr, 0, w.gscratch);
 }
 
 int mlstm_chunk_prepare(const void* k, const void* v, const void* f, const void* i, const double* carry_in,
@@ -169,7 +189,7 @@ int mlstm_chunk_prepare(const void* k, const void* v, const void* f, const void*
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
     if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, w.m, BH, S, Spad, dtype, st, carry_in, summary_out,
-                               w.An_bound, chunk)) != MLSTM_OK)
+                               w.An_bound, chunk, w.gscratch)) != MLSTM_OK)
         return rc;
     if ((rc = launch_identity(w.ident, dtype, st)) != MLSTM_OK) return rc;
     // U_k[key, value] = sum_j exp(a_j - A_end(k)) k_j[key] v_j[value];  zU_k[key] = sum_j exp(...) k_j[key]

@@ -10,6 +10,7 @@ namespace {
 
 constexpr double LOG2E_D = 1.4426950408889634;
 constexpr int SCAN_THREADS = 1024;
+constexpr int GATE_SEG_TOKENS = 4096;  // positions per block when a slice is cut into segments
 
 // Inclusive block scans over SCAN_THREADS elements (one per thread) with a running carry.
 __device__ __forceinline__ double block_scan_add(double x, double* warp_tot, double& carry_smem_view) {
@@ -78,6 +79,10 @@ __device__ __forceinline__ double block_scan_max(double x, double* warp_tot, dou
 // preceding segment (natural-log units; absent = {0, -inf}); summary_out[bh] = {F, A} at the end of
 // this segment; An_bound[bh][0] = -A_in*log2e and An_bound[bh][k+1] = -A*log2e at the last position
 // of block k (blocks of chunk_len positions).  The vector outputs may be null (summary only).
+// Long sequences are cut into segments of seg_tokens positions, one block each (blockIdx.x =
+// slice * nseg + segment; carry_in and summary_out are then per block): first a summary-only launch
+// with no carries, then gates_fold_kernel turns the segment summaries into per-segment carries, then
+// the full launch.  nseg = 1 is the plain one-block-per-slice form.
 template <typename T>
 __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __restrict__ f, const T* __restrict__ i,
                                                                  float* __restrict__ ga_rel, float* __restrict__ gAn_rel,
@@ -85,29 +90,34 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
                                                                  float* __restrict__ m, int S, int Spad,
                                                                  const double* __restrict__ carry_in,
                                                                  double* __restrict__ summary_out,
-                                                                 double* __restrict__ An_bound, int chunk_len) {
+                                                                 double* __restrict__ An_bound, int chunk_len, int nseg,
+                                                                 int seg_tokens) {
     __shared__ double wsum[32];
     __shared__ double wmax[32];
     __shared__ double carry_sum;
     __shared__ double carry_max;
     __shared__ double ref_a[SCAN_THREADS / REF_BLOCK];
     __shared__ double ref_A[SCAN_THREADS / REF_BLOCK];
-    const int bh = blockIdx.x;
+    const int bh = blockIdx.x / nseg;
+    const int seg = blockIdx.x - bh * nseg;
+    const int t_begin = seg * seg_tokens;
+    const int t_end = min(t_begin + seg_tokens, Spad);
     const int nref = Spad / REF_BLOCK;
     const int nb = chunk_len > 0 ? (S + chunk_len - 1) / chunk_len : 0;
     if (threadIdx.x == 0) {
-        carry_sum = carry_in ? carry_in[2 * bh] : 0.0;
-        carry_max = carry_in ? carry_in[2 * bh + 1] : -INFINITY;
-        if (An_bound) An_bound[static_cast<size_t>(bh) * (nb + 1)] = -carry_max * LOG2E_D;
+        carry_sum = carry_in ? carry_in[2 * blockIdx.x] : 0.0;
+        carry_max = carry_in ? carry_in[2 * blockIdx.x + 1] : -INFINITY;
+        if (An_bound && seg == 0) An_bound[static_cast<size_t>(bh) * (nb + 1)] = -carry_max * LOG2E_D;
     }
     __syncthreads();
-    for (int base = 0; base < Spad; base += SCAN_THREADS) {
+    for (int base = t_begin; base < t_end; base += SCAN_THREADS) {
         const int t = base + threadIdx.x;
         const bool in = t < S;
         double lf = 0.0, iv = 0.0;
         if (in) {
-            const double x = static_cast<double>(to_f32<T>(f[static_cast<size_t>(bh) * S + t]));
-            lf = x < 0.0 ? x - log1p(exp(x)) : -log1p(exp(-x));  // logsigmoid
+            // logsigmoid in fp32 (relative error 1e-7 per term), summed in double
+            const float x = to_f32<T>(f[static_cast<size_t>(bh) * S + t]);
+            lf = static_cast<double>(x < 0.0f ? x - log1pf(expf(x)) : -log1pf(expf(-x)));
             iv = static_cast<double>(to_f32<T>(i[static_cast<size_t>(bh) * S + t]));
         }
         const double F = block_scan_add(lf, wsum, carry_sum);
@@ -133,8 +143,30 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
         __syncthreads();
     }
     if (threadIdx.x == 0 && summary_out) {
-        summary_out[2 * bh] = carry_sum;
-        summary_out[2 * bh + 1] = carry_max;
+        summary_out[2 * blockIdx.x] = carry_sum;
+        summary_out[2 * blockIdx.x + 1] = carry_max;
+    }
+}
+
+// One thread per slice: segment summaries taken with no carry ({F_loc, A_loc}) -> the carry of every
+// segment and the slice's own summary.  A position's a = i - F shifts by -F_in when F_in precedes it,
+// so a segment's prefix maximum in slice terms is A_loc - F_in.
+__global__ void gates_fold_kernel(const double* __restrict__ local, const double* __restrict__ slice_carry,
+                                  double* __restrict__ seg_carry, double* __restrict__ slice_summary, int BH, int nseg) {
+    const int bh = blockIdx.x * blockDim.x + threadIdx.x;
+    if (bh >= BH) return;
+    double F = slice_carry ? slice_carry[2 * bh] : 0.0;
+    double A = slice_carry ? slice_carry[2 * bh + 1] : -INFINITY;
+    for (int s = 0; s < nseg; s++) {
+        const size_t k = (static_cast<size_t>(bh) * nseg + s) * 2;
+        seg_carry[k] = F;
+        seg_carry[k + 1] = A;
+        A = fmax(A, local[k + 1] - F);
+        F += local[k];
+    }
+    if (slice_summary) {
+        slice_summary[2 * bh] = F;
+        slice_summary[2 * bh + 1] = A;
     }
 }
 
@@ -288,26 +320,51 @@ int launch_scan_finalize(const float* num, const float* b, const float* m, const
     return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
+namespace {
+template <typename T>
+int gates_launch_typed(const void* f, const void* i, float* ga, float* gA, double* a_ref, double* An_ref, float* m, int BH,
+                       int S, int Spad, cudaStream_t st, const double* carry_in, double* summary_out, double* An_bound,
+                       int chunk_len, double* scratch) {
+    const int nseg = scratch ? (Spad + GATE_SEG_TOKENS - 1) / GATE_SEG_TOKENS : 1;
+    if (nseg <= 1) {
+        gates_fwd_kernel<T><<<BH, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, ga, gA, a_ref, An_ref, m, S, Spad, carry_in,
+                                                         summary_out, An_bound, chunk_len, 1, Spad);
+        return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+    }
+    double* local = scratch;                                         // [BH * nseg][2]
+    double* seg_carry = scratch + static_cast<size_t>(BH) * nseg * 2;  // [BH * nseg][2]
+    gates_fwd_kernel<T><<<BH * nseg, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, nullptr, nullptr, nullptr, nullptr,
+                                                            nullptr, S, Spad, nullptr, local, nullptr, 0, nseg,
+                                                            GATE_SEG_TOKENS);
+    gates_fold_kernel<<<(BH + 127) / 128, 128, 0, st>>>(local, carry_in, seg_carry, summary_out, BH, nseg);
+    if (ga || m || An_bound)
+        gates_fwd_kernel<T><<<BH * nseg, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, ga, gA, a_ref, An_ref, m, S, Spad,
+                                                                seg_carry, nullptr, An_bound, chunk_len, nseg,
+                                                                GATE_SEG_TOKENS);
+    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+}
+}  // namespace
+
+size_t gates_scratch_bytes(int BH, int Spad) {
+    const size_t nseg = (static_cast<size_t>(Spad) + GATE_SEG_TOKENS - 1) / GATE_SEG_TOKENS;
+    return nseg > 1 ? static_cast<size_t>(BH) * nseg * 4 * sizeof(double) : 0;
+}
+
 int launch_gates_fwd(const void* f, const void* i, float* ga, float* gA, double* a_ref, double* An_ref, float* m, int BH,
                      int S, int Spad, int dtype, cudaStream_t st, const double* carry_in, double* summary_out,
-                     double* An_bound, int chunk_len) {
+                     double* An_bound, int chunk_len, double* scratch) {
     switch (dtype) {
         case MLSTM_DT_F32:
-            gates_fwd_kernel<float><<<BH, SCAN_THREADS, 0, st>>>((const float*)f, (const float*)i, ga, gA, a_ref, An_ref, m, S,
-                                                                 Spad, carry_in, summary_out, An_bound, chunk_len);
-            break;
+            return gates_launch_typed<float>(f, i, ga, gA, a_ref, An_ref, m, BH, S, Spad, st, carry_in, summary_out, An_bound,
+                                             chunk_len, scratch);
         case MLSTM_DT_F16:
-            gates_fwd_kernel<__half><<<BH, SCAN_THREADS, 0, st>>>((const __half*)f, (const __half*)i, ga, gA, a_ref, An_ref, m,
-                                                                  S, Spad, carry_in, summary_out, An_bound, chunk_len);
-            break;
+            return gates_launch_typed<__half>(f, i, ga, gA, a_ref, An_ref, m, BH, S, Spad, st, carry_in, summary_out, An_bound,
+                                              chunk_len, scratch);
         case MLSTM_DT_BF16:
-            gates_fwd_kernel<__nv_bfloat16><<<BH, SCAN_THREADS, 0, st>>>((const __nv_bfloat16*)f, (const __nv_bfloat16*)i, ga, gA,
-                                                                         a_ref, An_ref, m, S, Spad, carry_in, summary_out,
-                                                                         An_bound, chunk_len);
-            break;
-        default: return MLSTM_E_ARG;
+            return gates_launch_typed<__nv_bfloat16>(f, i, ga, gA, a_ref, An_ref, m, BH, S, Spad, st, carry_in, summary_out,
+                                                     An_bound, chunk_len, scratch);
     }
-    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+    return MLSTM_E_ARG;
 }
 
 template <typename HT>

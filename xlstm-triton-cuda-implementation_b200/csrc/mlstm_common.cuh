@@ -114,7 +114,10 @@ __device__ __forceinline__ bool causal_ok(int row, int col) {
 // Launchers implemented in the .cu files.  All return an MLSTM_* status and never synchronise.
 int launch_gates_fwd(const void* f, const void* i, float* ga_rel, float* gAn_rel, double* a_ref, double* An_ref, float* m,
                      int BH, int S, int Spad, int dtype, cudaStream_t st, const double* carry_in = nullptr,
-                     double* summary_out = nullptr, double* An_bound = nullptr, int chunk_len = 0);
+                     double* summary_out = nullptr, double* An_bound = nullptr, int chunk_len = 0,
+                     double* scratch = nullptr);
+// bytes of `scratch` that let launch_gates_fwd cut long slices into segments (0: not worth it)
+size_t gates_scratch_bytes(int BH, int Spad);
 // chunk.cu
 int launch_identity(void* ident, int dtype, cudaStream_t st);
 int launch_state_scan(const float* U, const float* zU, const double* An_bound, const float* S_in, const float* z_in,

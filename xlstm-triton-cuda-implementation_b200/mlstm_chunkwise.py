@@ -26,7 +26,7 @@ __all__ = ["mlstm_chunkwise", "mlstm_chunkwise_sequence_parallel", "fold_gate_su
 class ChunkSegment:
     """One segment's pass through the four C-ABI stages, holding its workspace."""
 
-    def __init__(self, q, k, v, f, i, chunk_size=256):
+    def __init__(self, q, k, v, f, i, chunk_size=256, shared_workspace=False):
         if q.dim() != 4 or k.shape != q.shape or v.shape != q.shape:
             raise ValueError("q, k, v must share the shape [B, NH, S, D]")
         if f.shape != q.shape[:3] or i.shape != q.shape[:3]:
@@ -42,7 +42,11 @@ class ChunkSegment:
         nbytes = self.L.mlstm_chunk_workspace(self.B, self.NH, self.S, self.D, self.dt, self.chunk)
         if nbytes == 0:
             raise _lib.MlstmError(-4, "mlstm_chunk_workspace (needs float16/bfloat16, D = 128, chunk % 128 == 0)")
-        self.ws = torch.empty(nbytes, dtype=torch.uint8, device=self.dev)   # holds state between the stages: not shared
+        # The workspace carries the gates and block states from stage to stage.  A private buffer is safe
+        # however segments are interleaved; the per-stream shared one saves a large allocation per call
+        # and is what the one-shot functions below use (they finish a segment before starting another).
+        self.ws = (_lib.workspace(nbytes, self.dev) if shared_workspace
+                   else torch.empty(nbytes, dtype=torch.uint8, device=self.dev))
         self.dims = (self.B, self.NH, self.S, self.D, self.dt, self.chunk)
 
     def _stream(self):
@@ -52,8 +56,8 @@ class ChunkSegment:
         """{F_end, A_end} of this segment alone (no carry): float64 [B*NH, 2]."""
         out = torch.empty((self.B * self.NH, 2), dtype=torch.float64, device=self.dev)
         with torch.cuda.device(self.dev):
-            rc = self.L.mlstm_chunk_gate_summary(self.f.data_ptr(), self.i.data_ptr(), out.data_ptr(), self.B, self.NH,
-                                                 self.S, self.dt, self._stream())
+            rc = self.L.mlstm_chunk_gate_summary(self.f.data_ptr(), self.i.data_ptr(), out.data_ptr(), self.ws.data_ptr(),
+                                                 self.ws.numel(), *self.dims, self._stream())
         _lib.check(rc, "mlstm_chunk_gate_summary")
         return out
 
@@ -110,7 +114,7 @@ def mlstm_chunkwise(q, k, v, f, i, chunk_size=256, h_dtype=torch.float32, initia
     at the end of that segment).  With ``return_state`` the same tuple for the end of this call is
     returned beside h.
     """
-    seg = ChunkSegment(q, k, v, f, i, chunk_size)
+    seg = ChunkSegment(q, k, v, f, i, chunk_size, shared_workspace=True)
     carry = None
     state_in = None
     if initial is not None:
@@ -184,4 +188,5 @@ def sequence_parallel_forward(segment, group=None, h_dtype=torch.float32):
 def mlstm_chunkwise_sequence_parallel(q, k, v, f, i, chunk_size=256, group=None, h_dtype=torch.float32):
     """Every rank passes its contiguous segment [B, NH, S/G, D] (rank order = sequence order) and gets
     the outputs of that segment.  Needs an initialised torch.distributed process group (NCCL)."""
-    return sequence_parallel_forward(ChunkSegment(q, k, v, f, i, chunk_size), group=group, h_dtype=h_dtype)
+    return sequence_parallel_forward(ChunkSegment(q, k, v, f, i, chunk_size, shared_workspace=True), group=group,
+                                     h_dtype=h_dtype)
