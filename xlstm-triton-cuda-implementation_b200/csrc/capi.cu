@@ -140,7 +140,7 @@ int forward_impl(const void* q, const void* k, const void* v, const void* f, con
     p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_ref = w.a_ref;
     p.er_add = -0.5f * log2f(static_cast<float>(D));
     p.out = h; p.m = m; p.b_out = b; p.ogate = o;
-    p.status = w.status;
+    p.status = w.status; p.sched = w.status + 8;
     return run_pass(tc, FWD, p, dtype, h_dtype, st);
 }
 
@@ -233,7 +233,7 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     }
 
     PassParams p{};
-    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status;
+    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8;
     // dQ = ((dH V^T + g_r) * decay) K
     p.X = dhp; p.Y = v; p.Z = k;
     p.row_rel = w.gB; p.row_ref = w.An_ref; p.row_g = w.g; p.col_rel = w.ga; p.col_ref = w.a_ref; p.col_g = nullptr;
@@ -296,7 +296,7 @@ int mlstm_scan_fwd(const void* q, const void* k, const void* v, const void* f, c
         p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_ref = w.a_ref;
         p.er_add = -0.5f * log2f(static_cast<float>(D));
         p.out = num; p.m = w.m; p.b_out = w.b;
-        p.status = w.status;
+        p.status = w.status; p.sched = w.status + 8;
         if ((rc = launch_fwd_split_tc(p, dtype, st)) != MLSTM_OK) return rc;
         return launch_scan_finalize(num, w.b, w.m, o, static_cast<float*>(h), BH, S, D, dtype, st);
     }

@@ -194,7 +194,7 @@ int mlstm_chunk_prepare(const void* k, const void* v, const void* f, const void*
     if ((rc = launch_identity(w.ident, dtype, st)) != MLSTM_OK) return rc;
     // U_k[key, value] = sum_j exp(a_j - A_end(k)) k_j[key] v_j[value];  zU_k[key] = sum_j exp(...) k_j[key]
     PassParams p{};
-    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status;
+    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8;
     p.X = k;  // unused by STATE (the stationary operand is the identity); keeps the tensor map valid
     p.Y = k; p.Z = v;
     p.col_rel = w.ga; p.col_ref = w.a_ref;
@@ -235,7 +235,7 @@ int mlstm_chunk_apply(const void* q, const void* k, const void* v, const float* 
                                 st)) != MLSTM_OK)
         return rc;
     PassParams p{};
-    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status;
+    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8;
     p.X = q; p.Y = k; p.Z = v;
     p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_ref = w.a_ref;
     p.er_add = -0.5f * log2f(static_cast<float>(D));

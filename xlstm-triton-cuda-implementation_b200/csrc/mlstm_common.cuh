@@ -76,6 +76,7 @@ struct PassParams {
     const void* states;      // FWDC: [BH, NB, D, D] inbound state of every block, input type
     const float* zstate;     // FWDC: [BH, NB, D] inbound normaliser vector of every block
     int* status;         // device word; a kernel that gave up on a wait stores a non-zero code
+    int* sched;          // tensor-core passes: 8 device words, one work-item counter per pass mode
 };
 
 template <typename T>

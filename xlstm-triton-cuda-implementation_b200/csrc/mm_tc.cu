@@ -51,14 +51,14 @@ struct TcCfg {
     static constexpr int SLOT_BYTES = (CH / EPB) * BOX_BYTES;
     static constexpr int X_BYTES = (D / EPB) * BOX_BYTES;
     static constexpr int NSLOT = ES == 2 ? (D == 256 ? 5 : (D == 128 ? 6 : 8)) : (D == 256 ? 3 : (D == 128 ? 5 : 6));
-    static constexpr int NBAR = 1 + 2 * NSLOT + 2 + 2 + 1 + 1;  // x, slot full/empty, t_full, w_full, acc, part
+    static constexpr int NBAR = 1 + 2 * NSLOT + 2 + 2 + 1 + 1 + 2 + 4;  // x, slot full/empty, t, w, acc, part, xfree, accfree, item[4]
     static constexpr int SMEM_BYTES = 1024 /*align slack*/ + X_BYTES + NSLOT * SLOT_BYTES + NBAR * 8 + 64 +
                                       2 * 128 * 4 /*row partials*/;
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA may have");
 };
 
 struct SmemTail {  // lives after the tiles
-    float part[2][128];  // one partial per gate group and row (row sums in FWD, row dots in DQ/DK)
+    float part[2][128];  // [gate group][row]: row sums in FWD / STATE, row dots in DQ / DK
 };
 
 __device__ __forceinline__ uint32_t to_tf32(float x) {
@@ -94,50 +94,72 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     uint64_t* bar_w = bar_t + 2;                // [2] W tile written by the gate groups
     uint64_t* bar_acc = bar_w + 2;              // accumulator complete
     uint64_t* bar_part = bar_acc + 1;           // row partials of both gate groups in shared memory
+    uint64_t* bar_xfree = bar_part + 1;         // stationary tile no longer read by the item's contractions
+    uint64_t* bar_accfree = bar_xfree + 1;      // accumulator drained by the item's epilogue
+    uint64_t* bar_item = bar_accfree + 1;       // [4] work item published by the producer
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* item_ids = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [4] ring of published work items
     SmemTail* tail = reinterpret_cast<SmemTail*>(reinterpret_cast<uint8_t*>(bars) + C::NBAR * 8 + 64);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int NT = p.Spad / TILE;
-    // full head dimension (row stride of every [BH, S, .] tensor) and this CTA's slices of it
+    // full head dimension (row stride of every [BH, S, .] tensor)
     const int Dfull = SPLIT ? p.Dfull : D;
     const int nks = SPLIT ? Dfull / D : 1;
-    const int kslice = SPLIT ? static_cast<int>(blockIdx.y) % nks : 0;   // slice of the T contraction
-    const int vslice = SPLIT ? static_cast<int>(blockIdx.y) / nks : 0;   // slice of the output columns
-    const int xk0 = kslice * D, zv0 = vslice * D;
-    // CTA order: slices in sets of SLICE_SET; inside a set the heaviest tiles come first.  The CTAs
-    // resident at one time then share the K/V (or Q/dH) of a few slices, which stay in L2.
-    int bh, w;
-    {
-        const int per_slice = (MODE == STATE) ? p.NB : NT;  // CTAs per slice
+    const int per_slice = (MODE == STATE) ? p.NB : NT;     // work items per batch*head slice
+    const int nblk = per_slice * p.BH;                      // items per (contraction slice, output slice)
+    const int total = nblk * nks * nks;
+
+    // A work item = one stationary tile (STATE: one block) of one slice.  The CTA is persistent and
+    // takes the next item from a global counter whenever it is ready for one (the producer thread
+    // fetches it and publishes it to the other roles through a four-deep ring in shared memory; it
+    // can run at most two items ahead of the slowest role, see the waits on bar_xfree / bar_accfree).
+    // Item order: slices in sets of SLICE_SET, inside a set the heaviest tiles first, so that the
+    // CTAs running at one time share the K/V (or Q/dH) of a few slices, which stay in L2.
+    auto next_item = [&](int n, bool& ok) {   // every role but the producer
+        ok = mbar_wait(&bar_item[n & 3], (n >> 2) & 1, abort_flag, WAIT_LIMIT);
+        return ok ? item_ids[n & 3] : -1;
+    };
+    struct Item {
+        int bh, tile, blk, first, nsteps, xk0, zv0, vslice;
+    };
+    auto decode = [&](int id) {
+        Item it;
+        const int y = id / nblk, x = id - y * nblk;
+        const int kslice = y % nks;                          // slice of the T contraction
+        it.vslice = y / nks;                                 // slice of the output columns
+        it.xk0 = kslice * D;
+        it.zv0 = it.vslice * D;
         const int per_set = per_slice * SLICE_SET;
-        const int set = blockIdx.x / per_set;
-        const int within = blockIdx.x - set * per_set;
+        const int set = x / per_set;
+        const int within = x - set * per_set;
         const int set_size = min(SLICE_SET, p.BH - set * SLICE_SET);
-        w = within / set_size;
-        bh = set * SLICE_SET + (within - w * set_size);
-    }
-    // tile: the stationary tile (STATE: the block).  nsteps / stream_tile: what is streamed.
-    //   FWD, DQ   key tiles 0..tile, diagonal last          DK, DV  query tiles tile..NT-1, diagonal first
-    //   FWDC      step 0 applies the block's inbound state, then key tiles block_start..tile
-    //   STATE     the block's tiles
-    const int tile = (MODE == STATE) ? w : (ROWS_ARE_Q ? (NT - 1 - w) : w);
-    const int blk = (MODE == FWDC) ? tile / p.chunk_tiles : (MODE == STATE ? tile : 0);
-    const int first = (MODE == FWDC || MODE == STATE) ? blk * p.chunk_tiles : 0;
-    const int nsteps = (MODE == FWDC) ? (tile - first + 2)
-                     : (MODE == STATE) ? (min(p.chunk_tiles, NT - first))
-                     : (ROWS_ARE_Q ? (tile + 1) : (NT - tile));
-    auto stream_tile = [&](int t) {
-        if (MODE == FWDC) return first + t - 1;  // t >= 1
-        if (MODE == STATE) return first + t;
-        return ROWS_ARE_Q ? t : (tile + t);
+        const int w = within / set_size;
+        it.bh = set * SLICE_SET + (within - w * set_size);
+        // tile: the stationary tile (STATE: the block).  nsteps / stream_tile: what is streamed.
+        //   FWD, DQ   key tiles 0..tile, diagonal last          DK, DV  query tiles tile..NT-1, diagonal first
+        //   FWDC      step 0 applies the block's inbound state, then key tiles block_start..tile
+        //   STATE     the block's tiles
+        it.tile = (MODE == STATE) ? w : (ROWS_ARE_Q ? (NT - 1 - w) : w);
+        it.blk = (MODE == FWDC) ? it.tile / p.chunk_tiles : (MODE == STATE ? it.tile : 0);
+        it.first = (MODE == FWDC || MODE == STATE) ? it.blk * p.chunk_tiles : 0;
+        it.nsteps = (MODE == FWDC) ? (it.tile - it.first + 2)
+                  : (MODE == STATE) ? (min(p.chunk_tiles, NT - it.first))
+                  : (ROWS_ARE_Q ? (it.tile + 1) : (NT - it.tile));
+        return it;
+    };
+    auto stream_tile = [&](const Item& it, int t) {
+        if (MODE == FWDC) return it.first + t - 1;  // t >= 1
+        if (MODE == STATE) return it.first + t;
+        return ROWS_ARE_Q ? t : (it.tile + t);
     };
     auto is_state_step = [&](int t) { return MODE == FWDC && t == 0; };
 
     if (threadIdx.x == 0) {
         mbar_init(bar_x, 1);
+        mbar_init(bar_xfree, 1);
         for (int s = 0; s < C::NSLOT; s++) {
             mbar_init(&bar_full[s], 1);
             mbar_init(&bar_empty[s], 1);
@@ -147,7 +169,9 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         mbar_init(&bar_w[0], 256);
         mbar_init(&bar_w[1], 256);
         mbar_init(bar_acc, 1);
+        mbar_init(bar_accfree, 256);
         mbar_init(bar_part, 256);
+        for (int k = 0; k < 4; k++) mbar_init(&bar_item[k], 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -170,18 +194,13 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             prefetch_tmap(&tmZ);
             prefetch_tmap(&tmI);
             prefetch_tmap(&tmS);
-            mbar_expect_tx(bar_x, C::X_BYTES);
-            for (int c = 0; c < D / C::EPB; c++) {
-                if (MODE == STATE) tma_load_3d(sX + c * BOX_BYTES, &tmI, bar_x, c * C::EPB, 0, 0);
-                else tma_load_3d(sX + c * BOX_BYTES, &tmX, bar_x, xk0 + c * C::EPB, tile * TILE, bh);
-            }
-            int it = 0;
+            int slot_it = 0;
             bool ok = true;
             // one streamed tile = NHALF slots of CH columns starting at column x0
             auto load_tile = [&](const CUtensorMap* map, int x0, int row, int z) {
-                for (int hf = 0; hf < C::NHALF && ok; hf++, it++) {
-                    const int s = it % C::NSLOT;
-                    ok = mbar_wait(&bar_empty[s], ((it / C::NSLOT) & 1) ^ 1, abort_flag, WAIT_LIMIT);
+                for (int hf = 0; hf < C::NHALF && ok; hf++, slot_it++) {
+                    const int s = slot_it % C::NSLOT;
+                    ok = mbar_wait(&bar_empty[s], ((slot_it / C::NSLOT) & 1) ^ 1, abort_flag, WAIT_LIMIT);
                     if (!ok) break;
                     mbar_expect_tx(&bar_full[s], C::SLOT_BYTES);
                     uint8_t* dst = sSlot + s * C::SLOT_BYTES;
@@ -189,21 +208,37 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                         tma_load_3d(dst + c * BOX_BYTES, map, &bar_full[s], x0 + hf * C::CH + c * C::EPB, row, z);
                 }
             };
-            auto load_y = [&](int t) {
-                if (is_state_step(t)) load_tile(&tmI, 0, 0, 0);
-                else load_tile(&tmY, xk0, stream_tile(t) * TILE, bh);
-            };
-            auto load_z = [&](int t) {
-                if (is_state_step(t)) load_tile(&tmS, 0, 0, bh * p.NB + blk);
-                else load_tile(&tmZ, zv0, stream_tile(t) * TILE, bh);
-            };
-            // same order as the MMA issuer consumes: Y(0), then Y(t), Z(t-1) ..., Z(last)
-            load_y(0);
-            for (int t = 1; t < nsteps && ok; t++) {
-                load_y(t);
-                load_z(t - 1);
+            for (int n = 0; ok; n++) {
+                int id = atomicAdd(p.sched + MODE, 1);
+                if (id >= total) id = -1;
+                item_ids[n & 3] = id;
+                mbar_arrive(&bar_item[n & 3]);     // release: the id is visible to whoever passes the wait
+                if (id < 0) break;
+                const Item it = decode(id);
+                // the stationary tile's buffer is free once the previous item's first contractions are done
+                ok = mbar_wait(bar_xfree, (n & 1) ^ 1, abort_flag, WAIT_LIMIT);
+                if (!ok) break;
+                mbar_expect_tx(bar_x, C::X_BYTES);
+                for (int c = 0; c < D / C::EPB; c++) {
+                    if (MODE == STATE) tma_load_3d(sX + c * BOX_BYTES, &tmI, bar_x, c * C::EPB, 0, 0);
+                    else tma_load_3d(sX + c * BOX_BYTES, &tmX, bar_x, it.xk0 + c * C::EPB, it.tile * TILE, it.bh);
+                }
+                auto load_y = [&](int t) {
+                    if (is_state_step(t)) load_tile(&tmI, 0, 0, 0);
+                    else load_tile(&tmY, it.xk0, stream_tile(it, t) * TILE, it.bh);
+                };
+                auto load_z = [&](int t) {
+                    if (is_state_step(t)) load_tile(&tmS, 0, 0, it.bh * p.NB + it.blk);
+                    else load_tile(&tmZ, it.zv0, stream_tile(it, t) * TILE, it.bh);
+                };
+                // same order as the MMA issuer consumes: Y(0), then Y(t), Z(t-1) ..., Z(last)
+                load_y(0);
+                for (int t = 1; t < it.nsteps && ok; t++) {
+                    load_y(t);
+                    load_z(t - 1);
+                }
+                if (ok) load_z(it.nsteps - 1);
             }
-            if (ok) load_z(nsteps - 1);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
@@ -213,64 +248,96 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             constexpr int KROWS_BYTES = C::KSTEP * 128;  // KSTEP streamed rows of the Z tile
             const uint32_t sX_addr = smem_u32(sX);
             const uint32_t sSlot_addr = smem_u32(sSlot);
-            int it = 0;
-            bool ok = mbar_wait(bar_x, 0, abort_flag, WAIT_LIMIT);
-            tc_fence_after();
-            auto second = [&](int u) {  // ACC += W(u) Z(u)
-                ok = ok && mbar_wait(&bar_w[u & 1], (u >> 1) & 1, abort_flag, WAIT_LIMIT);
-                if (!ok) return;
+            int slot_it = 0;
+            int gstep = 0;     // steps issued by this CTA over all its items: T buffer and barrier phases follow it
+            bool ok = true;
+            for (int n = 0; ok; n++) {
+                const int id = next_item(n, ok);
+                if (id < 0) break;
+                const Item it = decode(id);
+                ok = mbar_wait(bar_x, n & 1, abort_flag, WAIT_LIMIT);
+                if (!ok) break;
                 tc_fence_after();
-                const uint32_t w_tmem = tmem_T0 + (u & 1) * 128;
-                for (int hf = 0; hf < C::NHALF; hf++, it++) {
-                    const int s = it % C::NSLOT;
-                    ok = mbar_wait(&bar_full[s], (it / C::NSLOT) & 1, abort_flag, WAIT_LIMIT);
+                auto second = [&](int u) {  // ACC += W(u) Z(u)
+                    const int gu = gstep + u;
+                    ok = ok && mbar_wait(&bar_w[gu & 1], (gu >> 1) & 1, abort_flag, WAIT_LIMIT);
+                    // the accumulator must have been drained by the previous item's epilogue
+                    if (ok && u == 0) ok = mbar_wait(bar_accfree, (n & 1) ^ 1, abort_flag, WAIT_LIMIT);
                     if (!ok) return;
                     tc_fence_after();
-                    const uint32_t zaddr = sSlot_addr + s * C::SLOT_BYTES;
+                    const uint32_t w_tmem = tmem_T0 + (gu & 1) * 128;
+                    for (int hf = 0; hf < C::NHALF; hf++, slot_it++) {
+                        const int s = slot_it % C::NSLOT;
+                        ok = mbar_wait(&bar_full[s], (slot_it / C::NSLOT) & 1, abort_flag, WAIT_LIMIT);
+                        if (!ok) return;
+                        tc_fence_after();
+                        const uint32_t zaddr = sSlot_addr + s * C::SLOT_BYTES;
 #pragma unroll
-                    for (int kk = 0; kk < TILE / C::KSTEP; kk++) {  // KSTEP streamed rows per MMA
-                        // Z is MN-major: 16-bit tiles use the plain 128-byte swizzle (groups of 8 rows),
-                        // 32-bit tiles the 32-byte-atom variant (groups of 4 rows)
-                        const uint64_t bdesc = TF32 ? smem_desc_sw128(zaddr + kk * KROWS_BYTES, BOX_BYTES, 512, 1)
-                                                    : smem_desc_sw128(zaddr + kk * KROWS_BYTES, BOX_BYTES, 1024, 2);
-                        // 16-bit W: streamed rows 0-63 in columns [0,32), rows 64-127 in columns [64,96);
-                        // 32-bit W: row j in column j.  Either way a K step is 8 columns.
-                        const uint32_t a_tmem = TF32 ? (w_tmem + kk * 8) : (w_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8));
-                        mma_ts<TF32>(tmem_ACC + hf * C::CH, a_tmem, bdesc, idesc2, (u > 0 || kk > 0) ? 1u : 0u);
+                        for (int kk = 0; kk < TILE / C::KSTEP; kk++) {  // KSTEP streamed rows per MMA
+                            // Z is MN-major: 16-bit tiles use the plain 128-byte swizzle (groups of 8 rows),
+                            // 32-bit tiles the 32-byte-atom variant (groups of 4 rows)
+                            const uint64_t bdesc = TF32 ? smem_desc_sw128(zaddr + kk * KROWS_BYTES, BOX_BYTES, 512, 1)
+                                                        : smem_desc_sw128(zaddr + kk * KROWS_BYTES, BOX_BYTES, 1024, 2);
+                            // 16-bit W: streamed rows 0-63 in columns [0,32), rows 64-127 in columns [64,96);
+                            // 32-bit W: row j in column j.  Either way a K step is 8 columns.
+                            const uint32_t a_tmem = TF32 ? (w_tmem + kk * 8) : (w_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8));
+                            mma_ts<TF32>(tmem_ACC + hf * C::CH, a_tmem, bdesc, idesc2, (u > 0 || kk > 0) ? 1u : 0u);
+                        }
+                        tc_commit(&bar_empty[s]);
                     }
-                    tc_commit(&bar_empty[s]);
-                }
-            };
-            for (int t = 0; t < nsteps && ok; t++) {
-                // T(t) = X Y(t)^T
-                for (int hf = 0; hf < C::NHALF; hf++, it++) {
-                    const int s = it % C::NSLOT;
-                    ok = mbar_wait(&bar_full[s], (it / C::NSLOT) & 1, abort_flag, WAIT_LIMIT);
+                };
+                for (int t = 0; t < it.nsteps && ok; t++) {
+                    // T(t) = X Y(t)^T
+                    const int gt = gstep + t;
+                    for (int hf = 0; hf < C::NHALF; hf++, slot_it++) {
+                        const int s = slot_it % C::NSLOT;
+                        ok = mbar_wait(&bar_full[s], (slot_it / C::NSLOT) & 1, abort_flag, WAIT_LIMIT);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t yaddr = sSlot_addr + s * C::SLOT_BYTES;
+#pragma unroll
+                        for (int kk = 0; kk < C::CH / C::KSTEP; kk++) {
+                            const int kx = hf * (C::CH / C::KSTEP) + kk;  // K step inside the stationary tile
+                            // four K steps (4 x 32 bytes) per 128-byte box row
+                            const uint64_t adesc = smem_desc_sw128(sX_addr + (kx >> 2) * BOX_BYTES + (kx & 3) * 32, 16, 1024);
+                            const uint64_t bdesc = smem_desc_sw128(yaddr + (kk >> 2) * BOX_BYTES + (kk & 3) * 32, 16, 1024);
+                            mma_ss<TF32>(tmem_T0 + (gt & 1) * 128, adesc, bdesc, idesc1, kx > 0 ? 1u : 0u);
+                        }
+                        tc_commit(&bar_empty[s]);
+                    }
                     if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t yaddr = sSlot_addr + s * C::SLOT_BYTES;
-#pragma unroll
-                    for (int kk = 0; kk < C::CH / C::KSTEP; kk++) {
-                        const int kx = hf * (C::CH / C::KSTEP) + kk;  // K step inside the stationary tile
-                        // four K steps (4 x 32 bytes) per 128-byte box row
-                        const uint64_t adesc = smem_desc_sw128(sX_addr + (kx >> 2) * BOX_BYTES + (kx & 3) * 32, 16, 1024);
-                        const uint64_t bdesc = smem_desc_sw128(yaddr + (kk >> 2) * BOX_BYTES + (kk & 3) * 32, 16, 1024);
-                        mma_ss<TF32>(tmem_T0 + (t & 1) * 128, adesc, bdesc, idesc1, kx > 0 ? 1u : 0u);
-                    }
-                    tc_commit(&bar_empty[s]);
+                    tc_commit(&bar_t[gt & 1]);
+                    if (t == it.nsteps - 1) tc_commit(bar_xfree);   // the stationary tile has been read for the last time
+                    if (t >= 1) second(t - 1);
                 }
-                if (!ok) break;
-                tc_commit(&bar_t[t & 1]);
-                if (t >= 1) second(t - 1);
+                if (ok) second(it.nsteps - 1);
+                if (ok) tc_commit(bar_acc);
+                gstep += it.nsteps;
             }
-            if (ok) second(nsteps - 1);
-            if (ok) tc_commit(bar_acc);
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------ gate groups
         const int grp = (warp - 4) >> 2;
         const int r = (warp & 3) * 32 + lane;          // TMEM lane == row inside the tile
         const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        // Both groups work on every step: group g gates columns [64g, 64g+64) of the T tile (one
+        // reference block of the gate vectors) and writes its part of W over them.
+        const int cbase = grp * 64;
+        auto load_cols = [&](const float* base, int sub, float (&dst)[32]) {
+            const float4* p4 = reinterpret_cast<const float4*>(base + cbase + sub * 32);
+#pragma unroll
+            for (int q4 = 0; q4 < 8; q4++) {
+                const float4 e4 = __ldg(p4 + q4);
+                dst[q4 * 4 + 0] = e4.x; dst[q4 * 4 + 1] = e4.y; dst[q4 * 4 + 2] = e4.z; dst[q4 * 4 + 3] = e4.w;
+            }
+        };
+        bool ok = true;
+        int gstep = 0;
+        for (int n = 0; ok; n++) {
+        const int id = next_item(n, ok);
+        if (id < 0) break;
+        const Item it = decode(id);
+        const int bh = it.bh, tile = it.tile, blk = it.blk, nsteps = it.nsteps, zv0 = it.zv0, vslice = it.vslice;
         const int grow = tile * TILE + r;              // row inside the slice (may be >= S in the last tile)
         const size_t vec_base = static_cast<size_t>(bh) * p.Spad;
         const size_t ref_base = static_cast<size_t>(bh) * (p.Spad / REF_BLOCK);
@@ -285,23 +352,12 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         const float er_state = (MODE == FWDC) ? static_cast<float>(er_d - bound[0]) : 0.0f;
         const float g_row = (MODE == DQ) ? p.row_g[vec_base + grow] : 0.0f;
         float rowsum = 0.0f;
-        bool ok = true;
 
-        // Both groups work on every step: group g gates columns [64g, 64g+64) of the T tile (one
-        // reference block of the gate vectors) and writes its part of W over them.
-        const int cbase = grp * 64;
-        auto load_cols = [&](const float* base, int sub, float (&dst)[32]) {
-            const float4* p4 = reinterpret_cast<const float4*>(base + cbase + sub * 32);
-#pragma unroll
-            for (int q4 = 0; q4 < 8; q4++) {
-                const float4 e4 = __ldg(p4 + q4);
-                dst[q4 * 4 + 0] = e4.x; dst[q4 * 4 + 1] = e4.y; dst[q4 * 4 + 2] = e4.z; dst[q4 * 4 + 3] = e4.w;
-            }
-        };
         for (int t = 0; t < nsteps; t++) {
-            const int buf = t & 1;
+            const int gt = gstep + t;
+            const int buf = gt & 1;
             const bool state_step = is_state_step(t);
-            const int st = state_step ? 0 : stream_tile(t);
+            const int st = state_step ? 0 : stream_tile(it, t);
             const bool diag = (MODE != STATE) && !state_step && (st == tile);
             // state step: the column term is the inbound normaliser vector z (a weight, not an exponent)
             const float* ce = state_step ? p.zstate + (static_cast<size_t>(bh) * p.NB + blk) * D
@@ -311,7 +367,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             load_cols(ce, 0, cv);
             const float er = state_step ? er_state
                                         : static_cast<float>(er_d + p.col_ref[ref_base + st * (TILE / REF_BLOCK) + grp]);
-            ok = mbar_wait(&bar_t[buf], (t >> 1) & 1, abort_flag, WAIT_LIMIT);
+            ok = mbar_wait(&bar_t[buf], (gt >> 1) & 1, abort_flag, WAIT_LIMIT);
             if (!ok) break;
             tc_fence_after();
             const uint32_t t_tmem = tmem_T0 + buf * 128 + lane_bits + cbase;
@@ -368,40 +424,48 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             tc_fence_before();
             mbar_arrive(&bar_w[buf]);
         }
+        if (!ok) break;
+        gstep += nsteps;
 
         // ---- epilogue: each group drains half of the accumulator's columns for all 128 rows
-        if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, WAIT_LIMIT);
-        if (ok) {
+        ok = mbar_wait(bar_acc, n & 1, abort_flag, WAIT_LIMIT);
+        if (!ok) break;
+        {
             tc_fence_after();
             constexpr int HALF = D / 2;
             constexpr int VEC = 16 / sizeof(InT);          // input elements per 16-byte access
             const int c0 = grp * HALF;
             const bool row_ok = (MODE == STATE) ? true : (grow < p.S);
+            float* part = tail->part[0];                   // [2][128]
+            // the partials of the previous item have been read by everybody once its accumulator was
+            // released (each thread reads them before it drains its share)
+            if (n > 0) ok = mbar_wait(bar_accfree, (n - 1) & 1, abort_flag, WAIT_LIMIT);
+            if (!ok) break;
             // STATE writes block (bh, blk) of [BH, NB, D, D]; everything else row `grow` of [BH, S, Dfull]
             const size_t row_off = (MODE == STATE)
                                        ? ((static_cast<size_t>(bh) * p.NB + blk) * D + r) * D
                                        : (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * Dfull + zv0;
             float inv_n = 1.0f;
             if (MODE == STATE) {
-                tail->part[grp][r] = rowsum;
+                part[grp * 128 + r] = rowsum;
                 mbar_arrive(bar_part);
-                ok = mbar_wait(bar_part, 0, abort_flag, WAIT_LIMIT);
+                ok = mbar_wait(bar_part, n & 1, abort_flag, WAIT_LIMIT);
                 if (ok && grp == 0 && p.b_out)
-                    p.b_out[(static_cast<size_t>(bh) * p.NB + blk) * D + r] = tail->part[0][r] + tail->part[1][r];
+                    p.b_out[(static_cast<size_t>(bh) * p.NB + blk) * D + r] = part[r] + part[128 + r];
             }
             if (IS_FWD) {
-                tail->part[grp][r] = rowsum;
+                part[grp * 128 + r] = rowsum;
                 mbar_arrive(bar_part);
-                ok = mbar_wait(bar_part, 0, abort_flag, WAIT_LIMIT);
+                ok = mbar_wait(bar_part, n & 1, abort_flag, WAIT_LIMIT);
                 if (ok) {
-                    const float bsum = tail->part[0][r] + tail->part[1][r];
+                    const float bsum = part[r] + part[128 + r];
                     if constexpr (SPLIT) {
                         // partial row sum of this contraction slice; the normaliser is applied afterwards
                         if (grp == 0 && row_ok && vslice == 0) atomicAdd(&p.b_out[static_cast<size_t>(bh) * p.S + grow], bsum);
                     } else {
                         const float mrow = row_ok ? p.m[static_cast<size_t>(bh) * p.S + grow] : 0.0f;
-                        const float n = fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f;
-                        inv_n = 1.0f / n;
+                        const float nrm = fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f;
+                        inv_n = 1.0f / nrm;
                         if (grp == 0 && row_ok && p.b_out) p.b_out[static_cast<size_t>(bh) * p.S + grow] = bsum;
                     }
                 }
@@ -417,6 +481,11 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     uint32_t av[32];
                     tmem_ld32(tmem_ACC + lane_bits + c0 + ch * 32, av);
                     tc_wait_ld();
+                    if (ch == HALF / 32 - 1) {
+                        // this thread's share of the accumulator is in registers: the next item may overwrite it
+                        tc_fence_before();
+                        mbar_arrive(bar_accfree);
+                    }
                     if (row_ok) {
                         float vals[32];
 #pragma unroll
@@ -463,15 +532,18 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                         }
                     }
                 }
+            } else {
+                break;
             }
-            if ((MODE == DQ || MODE == DK) && p.dot_out && ok) {
-                tail->part[grp][r] = dot;
+            if ((MODE == DQ || MODE == DK) && p.dot_out) {
+                part[grp * 128 + r] = dot;
                 mbar_arrive(bar_part);
-                ok = mbar_wait(bar_part, 0, abort_flag, WAIT_LIMIT);
+                ok = mbar_wait(bar_part, n & 1, abort_flag, WAIT_LIMIT);
                 if (ok && grp == 0)
-                    p.dot_out[vec_base + grow] = row_ok ? (tail->part[0][r] + tail->part[1][r]) : 0.0f;
+                    p.dot_out[vec_base + grow] = row_ok ? (part[r] + part[128 + r]) : 0.0f;
             }
         }
+        }  // items
         tc_fence_before();
     }
 
@@ -525,6 +597,18 @@ int make_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dty
     return r == CUDA_SUCCESS ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
+int sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 template <int MODE, int D, int ABFMT, typename OutT, bool SPLIT>
 int launch_one(const PassParams& p, int in_dtype, cudaStream_t st) {
     CUtensorMap mx, my, mz, mi, ms;
@@ -551,11 +635,15 @@ int launch_one(const PassParams& p, int in_dtype, cudaStream_t st) {
         return MLSTM_E_CUDA;
     }
     const int NT = p.Spad / TILE;
-    const long long nblk = static_cast<long long>(MODE == STATE ? p.NB : NT) * p.BH;
-    if (nblk > 0x7fffffffLL) return MLSTM_E_SHAPE;
     const int nsl = SPLIT ? (Dfull / D) * (Dfull / D) : 1;  // contraction slices x output slices
-    if (nsl > 65535) return MLSTM_E_SHAPE;
-    kern<<<dim3(static_cast<unsigned>(nblk), nsl), NTHREADS, smem, st>>>(mx, my, mz, mi, ms, p);
+    const long long total = static_cast<long long>(MODE == STATE ? p.NB : NT) * p.BH * nsl;
+    if (total > 0x7fffffffLL) return MLSTM_E_SHAPE;
+    const int sms = sm_count();
+    if (sms <= 0) return MLSTM_E_CUDA;
+    const unsigned grid = static_cast<unsigned>(total < sms ? total : sms);  // persistent: one CTA per SM
+    if (!p.sched) return MLSTM_E_ARG;
+    if (cudaMemsetAsync(p.sched + MODE, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;  // this pass's item counter
+    kern<<<grid, NTHREADS, smem, st>>>(mx, my, mz, mi, ms, p);
     return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
