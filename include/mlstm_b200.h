@@ -44,6 +44,8 @@ extern "C" {
                                 tl.dot(..., allow_tf32=False) (mlstm_matmul.py:19) */
 
 const char* mlstm_status_string(int status);
+/* Text of the last CUDA failure behind an MLSTM_E_CUDA on this host thread (which call, which error). */
+const char* mlstm_last_error_detail(void);
 
 /* Whether the tcgen05 path handles this case (D in {64, 128, 256}): 1 for 16-bit inputs, 2 for fp32
  * inputs (used only with MLSTM_F_ALLOW_TF32), else 0.  The scan entry also takes D = 512 .. 4096 in

@@ -22,6 +22,10 @@ class MlstmError(RuntimeError):
     def __init__(self, code, where):
         self.code = code
         msg = lib().mlstm_status_string(code).decode()
+        if code == -6:
+            detail = lib().mlstm_last_error_detail().decode()
+            if detail:
+                msg += " [" + detail + "]"
         super().__init__(f"{where}: {msg} (status {code})")
 
 
@@ -38,6 +42,8 @@ def lib():
     vp, i32, u32, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_size_t
     L.mlstm_status_string.restype = ctypes.c_char_p
     L.mlstm_status_string.argtypes = [i32]
+    L.mlstm_last_error_detail.restype = ctypes.c_char_p
+    L.mlstm_last_error_detail.argtypes = []
     L.mlstm_tc_supported.restype = i32
     L.mlstm_tc_supported.argtypes = [i32, i32, i32]
     L.mlstm_mm_fwd_workspace.restype = sz
@@ -75,7 +81,7 @@ def lib():
 
 
 EXPORTS = [
-    "mlstm_status_string", "mlstm_tc_supported", "mlstm_mm_fwd_workspace", "mlstm_mm_fwd",
+    "mlstm_status_string", "mlstm_last_error_detail", "mlstm_tc_supported", "mlstm_mm_fwd_workspace", "mlstm_mm_fwd",
     "mlstm_mm_bwd_workspace", "mlstm_mm_bwd", "mlstm_scan_fwd_workspace", "mlstm_scan_fwd",
     "mlstm_forward_f16_workspace", "mlstm_forward_f16", "mlstm_forward_f16_static", "mlstm_read_status",
     "mlstm_chunk_workspace", "mlstm_chunk_gate_summary", "mlstm_chunk_prepare", "mlstm_chunk_local_state",

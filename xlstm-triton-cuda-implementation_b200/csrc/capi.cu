@@ -1,6 +1,7 @@
 // extern "C" entry points of libmlstm_b200.so (declared in include/mlstm_b200.h): argument checks,
 // workspace carving and the launch sequences.  Nothing here allocates or synchronises.
 #include <cmath>
+#include <cstdio>
 #include <mutex>
 
 #include "mlstm_common.cuh"
@@ -145,6 +146,12 @@ int forward_impl(const void* q, const void* k, const void* v, const void* f, con
 }
 
 }  // namespace
+
+static thread_local char g_error_detail[256] = "";
+int note_cuda_error(cudaError_t err, const char* where) {
+    snprintf(g_error_detail, sizeof(g_error_detail), "%s: %s (%s)", where, cudaGetErrorString(err), cudaGetErrorName(err));
+    return MLSTM_E_CUDA;
+}
 }  // namespace mlstm
 
 using namespace mlstm;
@@ -167,6 +174,8 @@ const char* mlstm_status_string(int s) {
     }
     return "unknown status";
 }
+
+const char* mlstm_last_error_detail(void) { return g_error_detail; }
 
 int mlstm_tc_supported(int S, int D, int dtype) {
     if (!tc_supported(S, D, dtype)) return 0;

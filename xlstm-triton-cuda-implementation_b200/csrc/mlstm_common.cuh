@@ -112,6 +112,9 @@ __device__ __forceinline__ bool causal_ok(int row, int col) {
     return (MODE == FWD || MODE == DQ || MODE == FWDC) ? (col <= row) : (col >= row);
 }
 
+// Remembers the last CUDA failure of this host thread for mlstm_last_error_detail(); returns MLSTM_E_CUDA.
+int note_cuda_error(cudaError_t err, const char* where);
+
 // Launchers implemented in the .cu files.  All return an MLSTM_* status and never synchronise.
 int launch_gates_fwd(const void* f, const void* i, float* ga_rel, float* gAn_rel, double* a_ref, double* An_ref, float* m,
                      int BH, int S, int Spad, int dtype, cudaStream_t st, const double* carry_in = nullptr,

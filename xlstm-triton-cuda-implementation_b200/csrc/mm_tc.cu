@@ -7,14 +7,14 @@
 // form, of the scan kernels' contractions (mlstm_scan.py:74-137, 200-278).
 //
 // One CTA owns one stationary 128-row tile (queries in FWD/DQ, keys in DK/DV) of one batch*head
-// slice and streams the tiles on the causal side of it.  Warp roles (384 threads):
-//   warp 0      TMA producer: stationary tile once, then streamed tiles through a ring of slots
-//   warp 1      MMA issuer (one thread) and TMEM allocator
-//   warps 4-7   gate group 0: turns columns [0,64) of every T tile into gated W values, in TMEM
-//   warps 8-11  gate group 1: columns [64,128)
+// slice and streams the tiles on the causal side of it.  Warp roles (576 threads):
+//   warp 0       TMA producer: stationary tile once per item, then streamed tiles through a ring of slots
+//   warp 1       MMA issuer (one thread) and TMEM allocator
+//   warps 2-17   four gate groups of four warps: group g turns columns [32g, 32g+32) of every T tile
+//                into gated W values, in TMEM (a thread owns one TMEM lane = one row of the tile)
 // TMEM (512 columns): T0 [0,128) and T1 [128,256) fp32 128x128; ACC [256, 256+D) fp32.  W overwrites
-// T in place: 16-bit W packs two values per column, each group writing its half over the first 32 of
-// its own 64 T columns; 32-bit (tf32) W sits column for column on T.
+// T in place: 16-bit W packs two values per column, each group writing over the first 16 of its own
+// 32 T columns; 32-bit (tf32) W sits column for column on T.
 // The second contraction reads W straight from TMEM as the A operand and the streamed Z tile from
 // shared memory as an MN-major B operand, so the gated tile never touches shared or global memory.
 //
@@ -36,7 +36,9 @@ namespace {
 
 using namespace ptx;
 
-constexpr int NTHREADS = 384;
+constexpr int NGROUPS = 4;                      // gate groups: each gates 32 of a T tile's 128 columns
+constexpr int NGATE = NGROUPS * 128;            // gate threads
+constexpr int NTHREADS = 64 + NGATE;            // + producer warp and MMA warp
 constexpr int BOX_BYTES = 128 * 128;  // one TMA box: 128 rows of 128 bytes
 constexpr long long WAIT_LIMIT = 4000000000LL;  // cycles (about two seconds)
 constexpr int SLICE_SET = 8;                    // slices whose CTAs are interleaved in launch order
@@ -52,13 +54,13 @@ struct TcCfg {
     static constexpr int X_BYTES = (D / EPB) * BOX_BYTES;
     static constexpr int NSLOT = ES == 2 ? (D == 256 ? 5 : (D == 128 ? 6 : 8)) : (D == 256 ? 3 : (D == 128 ? 5 : 6));
     static constexpr int NBAR = 1 + 2 * NSLOT + 2 + 2 + 1 + 1 + 2 + 4;  // x, slot full/empty, t, w, acc, part, xfree, accfree, item[4]
-    static constexpr int SMEM_BYTES = 1024 /*align slack*/ + X_BYTES + NSLOT * SLOT_BYTES + NBAR * 8 + 64 +
-                                      2 * 128 * 4 /*row partials*/;
+    // the tiles start at the (1024-byte aligned, checked at run time) base of the dynamic shared memory
+    static constexpr int SMEM_BYTES = X_BYTES + NSLOT * SLOT_BYTES + NBAR * 8 + 64 + NGROUPS * 128 * 4 /*row partials*/;
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA may have");
 };
 
 struct SmemTail {  // lives after the tiles
-    float part[2][128];  // [gate group][row]: row sums in FWD / STATE, row dots in DQ / DK
+    float part[NGROUPS][128];  // [gate group][row]: row sums in FWD / STATE, row dots in DQ / DK
 };
 
 __device__ __forceinline__ uint32_t to_tf32(float x) {
@@ -68,6 +70,7 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
 }
 
 template <int MODE, int D, int ABFMT, typename OutT, bool SPLIT>
+// 18 warps = up to 5 per SM sub-partition (16384 registers each): at most 96 registers per thread
 __global__ void __launch_bounds__(NTHREADS, 1)
 mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
               const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmI,
@@ -82,8 +85,12 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     static_assert((MODE != FWDC && MODE != STATE) || (D == 128 && ES == 2), "chunkwise passes are built for 16-bit D = 128");
     static_assert(!SPLIT || MODE == FWD, "only the forward is sliced");
 
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
+    if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base; never seen otherwise
+        if (threadIdx.x == 0) atomicExch(p.status, 2000);
+        return;
+    }
     uint8_t* sX = smem;
     uint8_t* sSlot = smem + C::X_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sSlot + C::NSLOT * C::SLOT_BYTES);
@@ -166,11 +173,11 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         }
         mbar_init(&bar_t[0], 1);
         mbar_init(&bar_t[1], 1);
-        mbar_init(&bar_w[0], 256);
-        mbar_init(&bar_w[1], 256);
+        mbar_init(&bar_w[0], NGATE);
+        mbar_init(&bar_w[1], NGATE);
         mbar_init(bar_acc, 1);
-        mbar_init(bar_accfree, 256);
-        mbar_init(bar_part, 256);
+        mbar_init(bar_accfree, NGATE);
+        mbar_init(bar_part, NGATE);
         for (int k = 0; k < 4; k++) mbar_init(&bar_item[k], 1);
         *abort_flag = 0;
         fence_mbar_init();
@@ -246,8 +253,12 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             constexpr uint32_t idesc1 = make_idesc(ABFMT, 128, 128, 0, 0);
             constexpr uint32_t idesc2 = make_idesc(ABFMT, 128, C::CH, 0, 1);
             constexpr int KROWS_BYTES = C::KSTEP * 128;  // KSTEP streamed rows of the Z tile
-            const uint32_t sX_addr = smem_u32(sX);
-            const uint32_t sSlot_addr = smem_u32(sSlot);
+            // The issuing thread shares its scheduler with gate warps, so every instruction it spends per
+            // MMA shows up as an idle tensor pipe: descriptors are built once and advanced with one add.
+            const uint64_t xdesc0 = smem_desc_sw128(smem_u32(sX), 16, 1024);           // K-major stationary tile
+            const uint64_t ydesc0 = smem_desc_sw128(smem_u32(sSlot), 16, 1024);        // K-major view of slot 0
+            const uint64_t zdesc0 = TF32 ? smem_desc_sw128(smem_u32(sSlot), BOX_BYTES, 512, 1)   // MN-major view of slot 0:
+                                         : smem_desc_sw128(smem_u32(sSlot), BOX_BYTES, 1024, 2); // 32-bit tiles use the 32-byte-atom swizzle
             int slot_it = 0;
             int gstep = 0;     // steps issued by this CTA over all its items: T buffer and barrier phases follow it
             bool ok = true;
@@ -266,22 +277,20 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     if (!ok) return;
                     tc_fence_after();
                     const uint32_t w_tmem = tmem_T0 + (gu & 1) * 128;
+#pragma unroll
                     for (int hf = 0; hf < C::NHALF; hf++, slot_it++) {
                         const int s = slot_it % C::NSLOT;
                         ok = mbar_wait(&bar_full[s], (slot_it / C::NSLOT) & 1, abort_flag, WAIT_LIMIT);
                         if (!ok) return;
                         tc_fence_after();
-                        const uint32_t zaddr = sSlot_addr + s * C::SLOT_BYTES;
+                        const uint64_t zdesc = smem_desc_advance(zdesc0, s * C::SLOT_BYTES);
 #pragma unroll
                         for (int kk = 0; kk < TILE / C::KSTEP; kk++) {  // KSTEP streamed rows per MMA
-                            // Z is MN-major: 16-bit tiles use the plain 128-byte swizzle (groups of 8 rows),
-                            // 32-bit tiles the 32-byte-atom variant (groups of 4 rows)
-                            const uint64_t bdesc = TF32 ? smem_desc_sw128(zaddr + kk * KROWS_BYTES, BOX_BYTES, 512, 1)
-                                                        : smem_desc_sw128(zaddr + kk * KROWS_BYTES, BOX_BYTES, 1024, 2);
-                            // 16-bit W: streamed rows 0-63 in columns [0,32), rows 64-127 in columns [64,96);
-                            // 32-bit W: row j in column j.  Either way a K step is 8 columns.
-                            const uint32_t a_tmem = TF32 ? (w_tmem + kk * 8) : (w_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8));
-                            mma_ts<TF32>(tmem_ACC + hf * C::CH, a_tmem, bdesc, idesc2, (u > 0 || kk > 0) ? 1u : 0u);
+                            // 16-bit W: gate group g packed streamed rows [32g, 32g+32) into columns
+                            // [32g, 32g+16); 32-bit W: row j in column j.  Either way a K step is 8 columns.
+                            const uint32_t a_tmem = TF32 ? (w_tmem + kk * 8) : (w_tmem + (kk >> 1) * 32 + (kk & 1) * 8);
+                            mma_ts<TF32>(tmem_ACC + hf * C::CH, a_tmem, smem_desc_advance(zdesc, kk * KROWS_BYTES), idesc2,
+                                         (u > 0 || kk > 0) ? 1u : 0u);
                         }
                         tc_commit(&bar_empty[s]);
                     }
@@ -289,19 +298,20 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 for (int t = 0; t < it.nsteps && ok; t++) {
                     // T(t) = X Y(t)^T
                     const int gt = gstep + t;
+                    const uint32_t t_tmem = tmem_T0 + (gt & 1) * 128;
+#pragma unroll
                     for (int hf = 0; hf < C::NHALF; hf++, slot_it++) {
                         const int s = slot_it % C::NSLOT;
                         ok = mbar_wait(&bar_full[s], (slot_it / C::NSLOT) & 1, abort_flag, WAIT_LIMIT);
                         if (!ok) break;
                         tc_fence_after();
-                        const uint32_t yaddr = sSlot_addr + s * C::SLOT_BYTES;
+                        const uint64_t ydesc = smem_desc_advance(ydesc0, s * C::SLOT_BYTES);
 #pragma unroll
                         for (int kk = 0; kk < C::CH / C::KSTEP; kk++) {
                             const int kx = hf * (C::CH / C::KSTEP) + kk;  // K step inside the stationary tile
                             // four K steps (4 x 32 bytes) per 128-byte box row
-                            const uint64_t adesc = smem_desc_sw128(sX_addr + (kx >> 2) * BOX_BYTES + (kx & 3) * 32, 16, 1024);
-                            const uint64_t bdesc = smem_desc_sw128(yaddr + (kk >> 2) * BOX_BYTES + (kk & 3) * 32, 16, 1024);
-                            mma_ss<TF32>(tmem_T0 + (gt & 1) * 128, adesc, bdesc, idesc1, kx > 0 ? 1u : 0u);
+                            mma_ss<TF32>(t_tmem, smem_desc_advance(xdesc0, (kx >> 2) * BOX_BYTES + (kx & 3) * 32),
+                                         smem_desc_advance(ydesc, (kk >> 2) * BOX_BYTES + (kk & 3) * 32), idesc1, kx > 0 ? 1u : 0u);
                         }
                         tc_commit(&bar_empty[s]);
                     }
@@ -315,16 +325,16 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 gstep += it.nsteps;
             }
         }
-    } else if (warp >= 4) {
+    } else {
         // ------------------------------------------------------------ gate groups
-        const int grp = (warp - 4) >> 2;
-        const int r = (warp & 3) * 32 + lane;          // TMEM lane == row inside the tile
+        const int grp = (warp - 2) >> 2;               // warps 2..17: four groups of four warps
+        const int r = (warp & 3) * 32 + lane;          // TMEM lane == row inside the tile (lane quarter = warp % 4)
         const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        // Both groups work on every step: group g gates columns [64g, 64g+64) of the T tile (one
-        // reference block of the gate vectors) and writes its part of W over them.
-        const int cbase = grp * 64;
-        auto load_cols = [&](const float* base, int sub, float (&dst)[32]) {
-            const float4* p4 = reinterpret_cast<const float4*>(base + cbase + sub * 32);
+        // Every group works on every step: group g gates columns [32g, 32g+32) of the T tile and writes
+        // its part of W over them.
+        const int cbase = grp * 32;
+        auto load_cols = [&](const float* base, float (&dst)[32]) {
+            const float4* p4 = reinterpret_cast<const float4*>(base + cbase);
 #pragma unroll
             for (int q4 = 0; q4 < 8; q4++) {
                 const float4 e4 = __ldg(p4 + q4);
@@ -362,64 +372,75 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             // state step: the column term is the inbound normaliser vector z (a weight, not an exponent)
             const float* ce = state_step ? p.zstate + (static_cast<size_t>(bh) * p.NB + blk) * D
                                          : p.col_rel + vec_base + st * TILE;
-            // column terms do not depend on the contraction: fetch the first half before waiting
+            // column terms do not depend on the contraction: fetch them before waiting
             float cv[32];
-            load_cols(ce, 0, cv);
+            load_cols(ce, cv);
             const float er = state_step ? er_state
-                                        : static_cast<float>(er_d + p.col_ref[ref_base + st * (TILE / REF_BLOCK) + grp]);
+                                        : static_cast<float>(er_d + p.col_ref[ref_base + st * (TILE / REF_BLOCK) + (grp >> 1)]);
+            const float er_w = (MODE == FWDC && state_step) ? fast_exp2(er) : 0.0f;
             ok = mbar_wait(&bar_t[buf], (gt >> 1) & 1, abort_flag, WAIT_LIMIT);
             if (!ok) break;
             tc_fence_after();
             const uint32_t t_tmem = tmem_T0 + buf * 128 + lane_bits + cbase;
-            uint32_t tv0[32], tv1[32];
-            tmem_ld32(t_tmem, tv0);
-            tmem_ld32(t_tmem + 32, tv1);
-            uint32_t pk[TF32 ? 1 : 32];
-            const float er_w = (MODE == FWDC && state_step) ? fast_exp2(er) : 0.0f;
+            uint32_t tv[32];
+            tmem_ld32(t_tmem, tv);
             tc_wait_ld();
+            if (MODE == DK) {   // T + g with g per column: added eight columns at a time to keep registers free
+                const float4* g4 = reinterpret_cast<const float4*>(p.col_g + vec_base + st * TILE + cbase);
 #pragma unroll
-            for (int sub = 0; sub < 2; sub++) {
-                uint32_t (&tv)[32] = sub == 0 ? tv0 : tv1;
-                if (sub == 1) load_cols(ce, 1, cv);
-                if (MODE == DK) {
-                    float gv[32];
-                    load_cols(p.col_g + vec_base + st * TILE, sub, gv);
-#pragma unroll
-                    for (int j = 0; j < 32; j++) tv[j] = __float_as_uint(__uint_as_float(tv[j]) + gv[j]);
+                for (int q4 = 0; q4 < 8; q4++) {
+                    const float4 gq = __ldg(g4 + q4);
+                    tv[q4 * 4 + 0] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 0]) + gq.x);
+                    tv[q4 * 4 + 1] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 1]) + gq.y);
+                    tv[q4 * 4 + 2] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 2]) + gq.z);
+                    tv[q4 * 4 + 3] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 3]) + gq.w);
                 }
+            }
+            if (MODE == FWDC && state_step) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    const float wj = __uint_as_float(tv[j]) * er_w;   // T = Q: scale the row, b += (scaled q) . z
+                    rowsum = fmaf(wj, cv[j], rowsum);
+                    cv[j] = wj;
+                }
+            } else if (diag) {
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
                     float tval = __uint_as_float(tv[j]);
                     if (MODE == DQ) tval += g_row;
-                    float wj;
-                    if (MODE == FWDC && state_step) {
-                        wj = tval * er_w;              // T = Q: scale the row, b += (scaled q) . z
-                        rowsum = fmaf(wj, cv[j], rowsum);
-                    } else {
-                        wj = tval * fast_exp2(cv[j] + er);
-                        if (diag && !causal_ok<MODE>(r, cbase + sub * 32 + j)) wj = 0.0f;
-                        if (IS_FWD || MODE == STATE) rowsum += wj;
-                    }
+                    float wj = tval * fast_exp2(cv[j] + er);
+                    if (!causal_ok<MODE>(r, cbase + j)) wj = 0.0f;
+                    if (IS_FWD) rowsum += wj;
                     cv[j] = wj;
                 }
-                if constexpr (TF32) {
+            } else {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) tv[j] = to_tf32(cv[j]);
-                    tmem_st32(t_tmem + sub * 32, tv);   // in place: column for column
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        if constexpr (ABFMT == 1) {
-                            __nv_bfloat162 v2 = __floats2bfloat162_rn(cv[2 * j], cv[2 * j + 1]);
-                            pk[sub * 16 + j] = *reinterpret_cast<uint32_t*>(&v2);
-                        } else {
-                            __half2 v2 = __floats2half2_rn(cv[2 * j], cv[2 * j + 1]);
-                            pk[sub * 16 + j] = *reinterpret_cast<uint32_t*>(&v2);
-                        }
-                    }
+                for (int j = 0; j < 32; j++) {
+                    float tval = __uint_as_float(tv[j]);
+                    if (MODE == DQ) tval += g_row;
+                    const float wj = tval * fast_exp2(cv[j] + er);
+                    if (IS_FWD || MODE == STATE) rowsum += wj;
+                    cv[j] = wj;
                 }
             }
-            if constexpr (!TF32) tmem_st32(t_tmem, pk);
+            if constexpr (TF32) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) tv[j] = to_tf32(cv[j]);
+                tmem_st32(t_tmem, tv);   // in place: column for column
+            } else {
+                uint32_t pk[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    if constexpr (ABFMT == 1) {
+                        __nv_bfloat162 v2 = __floats2bfloat162_rn(cv[2 * j], cv[2 * j + 1]);
+                        pk[j] = *reinterpret_cast<uint32_t*>(&v2);
+                    } else {
+                        __half2 v2 = __floats2half2_rn(cv[2 * j], cv[2 * j + 1]);
+                        pk[j] = *reinterpret_cast<uint32_t*>(&v2);
+                    }
+                }
+                tmem_st16(t_tmem, pk);   // two values per column, over the first 16 of this group's 32 columns
+            }
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(&bar_w[buf]);
@@ -427,16 +448,17 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         if (!ok) break;
         gstep += nsteps;
 
-        // ---- epilogue: each group drains half of the accumulator's columns for all 128 rows
+        // ---- epilogue: each group drains a quarter of the accumulator's columns for all 128 rows
         ok = mbar_wait(bar_acc, n & 1, abort_flag, WAIT_LIMIT);
         if (!ok) break;
         {
             tc_fence_after();
-            constexpr int HALF = D / 2;
+            constexpr int QUART = D / NGROUPS;             // 16, 32 or 64 columns
+            constexpr int CW = QUART < 32 ? QUART : 32;    // columns per TMEM load
             constexpr int VEC = 16 / sizeof(InT);          // input elements per 16-byte access
-            const int c0 = grp * HALF;
+            const int c0 = grp * QUART;
             const bool row_ok = (MODE == STATE) ? true : (grow < p.S);
-            float* part = tail->part[0];                   // [2][128]
+            float* part = tail->part[0];                   // [NGROUPS][128]
             // the partials of the previous item have been read by everybody once its accumulator was
             // released (each thread reads them before it drains its share)
             if (n > 0) ok = mbar_wait(bar_accfree, (n - 1) & 1, abort_flag, WAIT_LIMIT);
@@ -446,19 +468,19 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                                        ? ((static_cast<size_t>(bh) * p.NB + blk) * D + r) * D
                                        : (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * Dfull + zv0;
             float inv_n = 1.0f;
-            if (MODE == STATE) {
-                part[grp * 128 + r] = rowsum;
+            auto exchange = [&](float x) {   // sum of one value per gate group for this row
+                part[grp * 128 + r] = x;
                 mbar_arrive(bar_part);
                 ok = mbar_wait(bar_part, n & 1, abort_flag, WAIT_LIMIT);
-                if (ok && grp == 0 && p.b_out)
-                    p.b_out[(static_cast<size_t>(bh) * p.NB + blk) * D + r] = part[r] + part[128 + r];
+                return ok ? (part[r] + part[128 + r]) + (part[256 + r] + part[384 + r]) : 0.0f;
+            };
+            if (MODE == STATE) {
+                const float zsum = exchange(rowsum);
+                if (ok && grp == 0 && p.b_out) p.b_out[(static_cast<size_t>(bh) * p.NB + blk) * D + r] = zsum;
             }
             if (IS_FWD) {
-                part[grp * 128 + r] = rowsum;
-                mbar_arrive(bar_part);
-                ok = mbar_wait(bar_part, n & 1, abort_flag, WAIT_LIMIT);
+                const float bsum = exchange(rowsum);
                 if (ok) {
-                    const float bsum = part[r] + part[128 + r];
                     if constexpr (SPLIT) {
                         // partial row sum of this contraction slice; the normaliser is applied afterwards
                         if (grp == 0 && row_ok && vslice == 0) atomicAdd(&p.b_out[static_cast<size_t>(bh) * p.S + grow], bsum);
@@ -470,77 +492,75 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     }
                 }
             }
+            if (!ok) break;
             float dot = 0.0f;
-            if (ok) {
-                OutT* orow = reinterpret_cast<OutT*>(p.out) + row_off + c0;
-                const InT* ogate_row = (IS_FWD && !SPLIT && p.ogate) ? reinterpret_cast<const InT*>(p.ogate) + row_off + c0 : nullptr;
-                const InT* drow = ((MODE == DQ || MODE == DK) && p.dot_src)
-                                      ? reinterpret_cast<const InT*>(p.dot_src) + row_off + c0 : nullptr;
+            OutT* orow = reinterpret_cast<OutT*>(p.out) + row_off + c0;
+            const InT* ogate_row = (IS_FWD && !SPLIT && p.ogate) ? reinterpret_cast<const InT*>(p.ogate) + row_off + c0 : nullptr;
+            const InT* drow = ((MODE == DQ || MODE == DK) && p.dot_src)
+                                  ? reinterpret_cast<const InT*>(p.dot_src) + row_off + c0 : nullptr;
 #pragma unroll 1
-                for (int ch = 0; ch < HALF / 32; ch++) {
-                    uint32_t av[32];
+            for (int ch = 0; ch < QUART / CW; ch++) {
+                uint32_t av[32];
+                if constexpr (CW == 32) {
                     tmem_ld32(tmem_ACC + lane_bits + c0 + ch * 32, av);
-                    tc_wait_ld();
-                    if (ch == HALF / 32 - 1) {
-                        // this thread's share of the accumulator is in registers: the next item may overwrite it
-                        tc_fence_before();
-                        mbar_arrive(bar_accfree);
+                } else {
+                    tmem_ld16(tmem_ACC + lane_bits + c0, reinterpret_cast<uint32_t (&)[16]>(av));
+                }
+                tc_wait_ld();
+                if (ch == QUART / CW - 1) {
+                    // this thread's share of the accumulator is in registers: the next item may overwrite it
+                    tc_fence_before();
+                    mbar_arrive(bar_accfree);
+                }
+                if (row_ok) {
+                    float vals[CW];
+#pragma unroll
+                    for (int j = 0; j < CW; j++) vals[j] = __uint_as_float(av[j]) * inv_n;
+                    if (IS_FWD && ogate_row) {
+#pragma unroll
+                        for (int j = 0; j < CW; j++) vals[j] *= silu_f(to_f32<InT>(ogate_row[ch * CW + j]));
                     }
-                    if (row_ok) {
-                        float vals[32];
+                    if ((MODE == DQ || MODE == DK) && drow) {
 #pragma unroll
-                        for (int j = 0; j < 32; j++) vals[j] = __uint_as_float(av[j]) * inv_n;
-                        if (IS_FWD && ogate_row) {
+                        for (int jv = 0; jv < CW / VEC; jv++) {
+                            const uint4 raw = *reinterpret_cast<const uint4*>(drow + ch * CW + jv * VEC);
+                            const InT* ev = reinterpret_cast<const InT*>(&raw);
 #pragma unroll
-                            for (int j = 0; j < 32; j++) vals[j] *= silu_f(to_f32<InT>(ogate_row[ch * 32 + j]));
+                            for (int j = 0; j < VEC; j++) dot += vals[jv * VEC + j] * to_f32<InT>(ev[j]);
                         }
-                        if ((MODE == DQ || MODE == DK) && drow) {
+                    }
+                    if constexpr (SPLIT) {
 #pragma unroll
-                            for (int jv = 0; jv < 32 / VEC; jv++) {
-                                const uint4 raw = *reinterpret_cast<const uint4*>(drow + ch * 32 + jv * VEC);
-                                const InT* ev = reinterpret_cast<const InT*>(&raw);
-#pragma unroll
-                                for (int j = 0; j < VEC; j++) dot += vals[jv * VEC + j] * to_f32<InT>(ev[j]);
-                            }
+                        for (int j4 = 0; j4 < CW / 4; j4++) {
+                            float4 o4 = make_float4(vals[j4 * 4], vals[j4 * 4 + 1], vals[j4 * 4 + 2], vals[j4 * 4 + 3]);
+                            atomicAdd(reinterpret_cast<float4*>(reinterpret_cast<float*>(orow) + ch * CW + j4 * 4), o4);
                         }
-                        if constexpr (SPLIT) {
+                    } else if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
-                            for (int j4 = 0; j4 < 8; j4++) {
-                                float4 o4 = make_float4(vals[j4 * 4], vals[j4 * 4 + 1], vals[j4 * 4 + 2], vals[j4 * 4 + 3]);
-                                atomicAdd(reinterpret_cast<float4*>(reinterpret_cast<float*>(orow) + ch * 32 + j4 * 4), o4);
+                        for (int j4 = 0; j4 < CW / 4; j4++) {
+                            float4 o4 = make_float4(vals[j4 * 4], vals[j4 * 4 + 1], vals[j4 * 4 + 2], vals[j4 * 4 + 3]);
+                            *reinterpret_cast<float4*>(reinterpret_cast<float*>(orow) + ch * CW + j4 * 4) = o4;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j8 = 0; j8 < CW / 8; j8++) {
+                            uint4 o4;
+                            uint32_t* o32 = reinterpret_cast<uint32_t*>(&o4);
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                OutT lo = from_f32<OutT>(vals[j8 * 8 + 2 * j]);
+                                OutT hi = from_f32<OutT>(vals[j8 * 8 + 2 * j + 1]);
+                                o32[j] = static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&lo)) |
+                                         (static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&hi)) << 16);
                             }
-                        } else if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-                            for (int j4 = 0; j4 < 8; j4++) {
-                                float4 o4 = make_float4(vals[j4 * 4], vals[j4 * 4 + 1], vals[j4 * 4 + 2], vals[j4 * 4 + 3]);
-                                *reinterpret_cast<float4*>(reinterpret_cast<float*>(orow) + ch * 32 + j4 * 4) = o4;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j8 = 0; j8 < 4; j8++) {
-                                uint4 o4;
-                                uint32_t* o32 = reinterpret_cast<uint32_t*>(&o4);
-#pragma unroll
-                                for (int j = 0; j < 4; j++) {
-                                    OutT lo = from_f32<OutT>(vals[j8 * 8 + 2 * j]);
-                                    OutT hi = from_f32<OutT>(vals[j8 * 8 + 2 * j + 1]);
-                                    o32[j] = static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&lo)) |
-                                             (static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&hi)) << 16);
-                                }
-                                *reinterpret_cast<uint4*>(orow + ch * 32 + j8 * 8) = o4;
-                            }
+                            *reinterpret_cast<uint4*>(orow + ch * CW + j8 * 8) = o4;
                         }
                     }
                 }
-            } else {
-                break;
             }
             if ((MODE == DQ || MODE == DK) && p.dot_out) {
-                part[grp * 128 + r] = dot;
-                mbar_arrive(bar_part);
-                ok = mbar_wait(bar_part, n & 1, abort_flag, WAIT_LIMIT);
-                if (ok && grp == 0)
-                    p.dot_out[vec_base + grow] = row_ok ? (part[r] + part[128 + r]) : 0.0f;
+                const float dsum = exchange(dot);
+                if (ok && grp == 0) p.dot_out[vec_base + grow] = row_ok ? dsum : 0.0f;
             }
         }
         }  // items
@@ -630,9 +650,10 @@ int launch_one(const PassParams& p, int in_dtype, cudaStream_t st) {
     }
     auto kern = mlstm_tc_pass<MODE, D, ABFMT, OutT, SPLIT>;
     constexpr int smem = TcCfg<D, ABFMT == 2 ? 4 : 2>::SMEM_BYTES;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (ce != cudaSuccess) {
         cudaGetLastError();
-        return MLSTM_E_CUDA;
+        return note_cuda_error(ce, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
     }
     const int NT = p.Spad / TILE;
     const int nsl = SPLIT ? (Dfull / D) * (Dfull / D) : 1;  // contraction slices x output slices
@@ -642,9 +663,11 @@ int launch_one(const PassParams& p, int in_dtype, cudaStream_t st) {
     if (sms <= 0) return MLSTM_E_CUDA;
     const unsigned grid = static_cast<unsigned>(total < sms ? total : sms);  // persistent: one CTA per SM
     if (!p.sched) return MLSTM_E_ARG;
-    if (cudaMemsetAsync(p.sched + MODE, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;  // this pass's item counter
+    ce = cudaMemsetAsync(p.sched + MODE, 0, sizeof(int), st);  // this pass's item counter
+    if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
     kern<<<grid, NTHREADS, smem, st>>>(mx, my, mz, mi, ms, p);
-    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+    ce = cudaGetLastError();
+    return ce == cudaSuccess ? MLSTM_OK : note_cuda_error(ce, "launch of mlstm_tc_pass");
 }
 
 template <int MODE, int D, int ABFMT>

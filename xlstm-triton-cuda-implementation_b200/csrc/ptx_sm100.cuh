@@ -145,6 +145,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -186,6 +195,13 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
     d |= static_cast<uint64_t>(1) << 46;  // descriptor version of this architecture
     d |= static_cast<uint64_t>(layout_type) << 61;  // 2 = SWIZZLE_128B, 1 = SWIZZLE_128B with 32-byte atoms
     return d;
+}
+
+// A descriptor for the same tile `byte_off` bytes further on (byte_off a multiple of 16; the address
+// field cannot carry into its neighbours while the tile stays inside shared memory): one 32-bit add.
+__device__ __forceinline__ uint64_t smem_desc_advance(uint64_t desc, uint32_t byte_off) {
+    const uint32_t lo = static_cast<uint32_t>(desc) + (byte_off >> 4);
+    return (desc & 0xFFFFFFFF00000000ull) | lo;
 }
 
 // Instruction descriptor, fp32 accumulate.  ab_format: 0 = fp16, 1 = bf16, 2 = tf32.
