@@ -29,7 +29,7 @@ struct Carver {
 
 struct FwdWs {
     int* status;
-    float *ga, *gAn, *m, *b;
+    float *ga, *gAn, *gaw, *m, *b;
     double *a_ref, *An_ref;
     size_t bytes;
 };
@@ -41,6 +41,7 @@ FwdWs carve_fwd(void* ws, int BH, int S, bool with_mb) {
     w.status = c.take<int>(WS_ALIGN);
     w.ga = c.take<float>(vec);
     w.gAn = c.take<float>(vec);
+    w.gaw = c.take<float>(vec);
     w.a_ref = c.take<double>(vec / REF_BLOCK * 2);
     w.An_ref = c.take<double>(vec / REF_BLOCK * 2);
     if (with_mb) {
@@ -53,7 +54,7 @@ FwdWs carve_fwd(void* ws, int BH, int S, bool with_mb) {
 
 struct BwdWs {
     int* status;
-    float *ga, *gAn, *gB, *g, *dI, *R;
+    float *ga, *gAn, *gaw, *gB, *gBw, *g, *dI, *R;
     double *a_ref, *An_ref;
     void* dh16;
     size_t bytes;
@@ -67,7 +68,9 @@ BwdWs carve_bwd(void* ws, int BH, int S, int D, bool need_dh16) {
     w.gAn = c.take<float>(vec);
     w.a_ref = c.take<double>(vec / REF_BLOCK * 2);
     w.An_ref = c.take<double>(vec / REF_BLOCK * 2);
+    w.gaw = c.take<float>(vec);
     w.gB = c.take<float>(vec);
+    w.gBw = c.take<float>(vec);
     w.g = c.take<float>(vec);
     w.dI = c.take<float>(vec);
     w.R = c.take<float>(vec);
@@ -129,7 +132,9 @@ int forward_impl(const void* q, const void* k, const void* v, const void* f, con
     if (rc != MLSTM_OK) return rc;
     const int Spad = round_up(S, TILE);
     if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
-    if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, m, BH, S, Spad, dtype, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, m, BH, S, Spad, dtype, st, nullptr, nullptr, nullptr, 0, nullptr,
+                               w.gaw)) != MLSTM_OK)
+        return rc;
     const void* in[3] = {q, k, v};
     if (tc && dtype == MLSTM_DT_F32) {
         if (!tf32buf) return MLSTM_E_WORKSPACE;
@@ -138,7 +143,7 @@ int forward_impl(const void* q, const void* k, const void* v, const void* f, con
     PassParams p{};
     p.S = S; p.Spad = Spad; p.BH = BH; p.D = D;
     p.X = in[0]; p.Y = in[1]; p.Z = in[2];
-    p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_ref = w.a_ref;
+    p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_w = w.gaw; p.col_ref = w.a_ref;
     p.er_add = -0.5f * log2f(static_cast<float>(D));
     p.out = h; p.m = m; p.b_out = b; p.ogate = o;
     p.status = w.status; p.sched = w.status + 8;
@@ -228,8 +233,10 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
-    if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, nullptr, BH, S, Spad, dtype, st)) != MLSTM_OK) return rc;
-    if ((rc = launch_bwd_prep(h, dh, b, m, w.gAn, w.gB, w.g, w.dh16, BH, S, Spad, D, h_dtype, dtype, st)) != MLSTM_OK)
+    if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, nullptr, BH, S, Spad, dtype, st, nullptr, nullptr, nullptr, 0,
+                               nullptr, w.gaw)) != MLSTM_OK)
+        return rc;
+    if ((rc = launch_bwd_prep(h, dh, b, m, w.gAn, w.gB, w.gBw, w.g, w.dh16, BH, S, Spad, D, h_dtype, dtype, st)) != MLSTM_OK)
         return rc;
     const void* dhp = need16 ? w.dh16 : dh;  // dh in the element type of q, k, v
     const void* orig_q = q;
@@ -245,12 +252,12 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8;
     // dQ = ((dH V^T + g_r) * decay) K
     p.X = dhp; p.Y = v; p.Z = k;
-    p.row_rel = w.gB; p.row_ref = w.An_ref; p.row_g = w.g; p.col_rel = w.ga; p.col_ref = w.a_ref; p.col_g = nullptr;
+    p.row_rel = w.gB; p.row_ref = w.An_ref; p.row_g = w.g; p.col_rel = w.ga; p.col_w = w.gaw; p.col_ref = w.a_ref; p.col_g = nullptr;
     p.out = dq; p.dot_src = orig_q; p.dot_out = w.R;
     if ((rc = run_pass(tc, DQ, p, dtype, dtype, st)) != MLSTM_OK) return rc;
     // dK = ((V dH^T + g_c) * decay)  Q
     p.X = v; p.Y = dhp; p.Z = q;
-    p.row_rel = w.ga; p.row_ref = w.a_ref; p.row_g = nullptr; p.col_rel = w.gB; p.col_ref = w.An_ref; p.col_g = w.g;
+    p.row_rel = w.ga; p.row_ref = w.a_ref; p.row_g = nullptr; p.col_rel = w.gB; p.col_w = w.gBw; p.col_ref = w.An_ref; p.col_g = w.g;
     p.out = dk; p.dot_src = orig_k; p.dot_out = w.dI;
     if ((rc = run_pass(tc, DK, p, dtype, dtype, st)) != MLSTM_OK) return rc;
     // dV = ((K Q^T) * decay / n) dH
@@ -296,13 +303,15 @@ int mlstm_scan_fwd(const void* q, const void* k, const void* v, const void* f, c
         if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
         if (cudaMemsetAsync(num, 0, static_cast<size_t>(BH) * S * D * sizeof(float), st) != cudaSuccess) return MLSTM_E_CUDA;
         if (cudaMemsetAsync(w.b, 0, static_cast<size_t>(BH) * S * sizeof(float), st) != cudaSuccess) return MLSTM_E_CUDA;
-        if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, w.m, BH, S, Spad, dtype, st)) != MLSTM_OK) return rc;
+        if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, w.m, BH, S, Spad, dtype, st, nullptr, nullptr, nullptr, 0,
+                                   nullptr, w.gaw)) != MLSTM_OK)
+            return rc;
         const void* in[3] = {q, k, v};
         if (dtype == MLSTM_DT_F32 && (rc = round_inputs(in, 3, tf32buf, BH, S, D, st)) != MLSTM_OK) return rc;
         PassParams p{};
         p.S = S; p.Spad = Spad; p.BH = BH; p.D = 256; p.Dfull = D;
         p.X = in[0]; p.Y = in[1]; p.Z = in[2];
-        p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_ref = w.a_ref;
+        p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_w = w.gaw; p.col_ref = w.a_ref;
         p.er_add = -0.5f * log2f(static_cast<float>(D));
         p.out = num; p.m = w.m; p.b_out = w.b;
         p.status = w.status; p.sched = w.status + 8;

@@ -79,7 +79,7 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
 
 struct ChunkWs {
     int* status;
-    float *ga, *gAn, *m, *b, *U, *zU, *zstate;
+    float *ga, *gAn, *gaw, *m, *b, *U, *zU, *zstate;
     double *a_ref, *An_ref, *An_bound, *gscratch;
     void *ident, *states;
     int NB;
@@ -102,6 +102,7 @@ ChunkWs carve(void* ws, int BH, int S, int D, int chunk) {
     w.status = static_cast<int*>(take(WS_ALIGN));
     w.ga = static_cast<float*>(take(vec));
     w.gAn = static_cast<float*>(take(vec));
+    w.gaw = static_cast<float*>(take(vec));
     w.a_ref = static_cast<double*>(take(vec / REF_BLOCK * 2));
     w.An_ref = static_cast<double*>(take(vec / REF_BLOCK * 2));
     w.m = static_cast<float*>(take(static_cast<size_t>(BH) * S * sizeof(float)));
@@ -189,7 +190,7 @@ int mlstm_chunk_prepare(const void* k, const void* v, const void* f, const void*
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
     if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, w.m, BH, S, Spad, dtype, st, carry_in, summary_out,
-                               w.An_bound, chunk, w.gscratch)) != MLSTM_OK)
+                               w.An_bound, chunk, w.gscratch, w.gaw)) != MLSTM_OK)
         return rc;
     if ((rc = launch_identity(w.ident, dtype, st)) != MLSTM_OK) return rc;
     // U_k[key, value] = sum_j exp(a_j - A_end(k)) k_j[key] v_j[value];  zU_k[key] = sum_j exp(...) k_j[key]
@@ -197,7 +198,7 @@ int mlstm_chunk_prepare(const void* k, const void* v, const void* f, const void*
     p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8;
     p.X = k;  // unused by STATE (the stationary operand is the identity); keeps the tensor map valid
     p.Y = k; p.Z = v;
-    p.col_rel = w.ga; p.col_ref = w.a_ref;
+    p.col_rel = w.ga; p.col_w = w.gaw; p.col_ref = w.a_ref;
     p.row_rel = w.gAn; p.row_ref = w.An_ref;  // unused by STATE
     p.out = w.U; p.b_out = w.zU;
     p.chunk_tiles = chunk / TILE; p.NB = w.NB; p.An_bound = w.An_bound; p.ident = w.ident;
@@ -237,7 +238,7 @@ int mlstm_chunk_apply(const void* q, const void* k, const void* v, const float* 
     PassParams p{};
     p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8;
     p.X = q; p.Y = k; p.Z = v;
-    p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_ref = w.a_ref;
+    p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_w = w.gaw; p.col_ref = w.a_ref;
     p.er_add = -0.5f * log2f(static_cast<float>(D));
     p.out = h; p.m = w.m; p.b_out = w.b;
     p.chunk_tiles = chunk / TILE; p.NB = w.NB; p.An_bound = w.An_bound; p.ident = w.ident;

@@ -70,8 +70,10 @@ __device__ __forceinline__ double block_scan_max(double x, double* warp_tot, dou
 // One block per slice.  With F = cumsum(logsigmoid f), a = i - F, A = running maximum of a (all in
 // double), it writes m = F + A and the two gate vectors in log2 units, re-centred per block of
 // REF_BLOCK positions so that fp32 keeps its relative accuracy however long the sequence is:
-//   ga_rel[t]  = (a_t - a_first(block)) * log2e      a_ref[block]  = a_first * log2e      (double)
-//   gAn_rel[t] = (A_first(block) - A_t) * log2e      An_ref[block] = -A_first * log2e     (double)
+//   ga_rel[t]  = (a_t - a_max(block)) * log2e  <= 0  a_ref[block]  = a_max * log2e        (double)
+//   gAn_rel[t] = (A_first(block) - A_t) * log2e <= 0 An_ref[block] = -A_first * log2e     (double)
+//   ga_w[t]    = exp2(ga_rel[t])  (optional): off the diagonal the kernels use exp2(x + y) = exp2(x) exp2(y)
+//                with the row factor exp2(row term + references) <= const computed once per row and block
 // A kernel forms exp2(col_rel[c] + float(row_rel[r] + row_ref[r / REF_BLOCK] + col_ref[c / REF_BLOCK])),
 // the bracket in double once per block of columns.  Padding (t >= S): ga_rel = -inf (a padded column
 // contributes exactly zero), gAn_rel = 0, references 0.  m may be null.
@@ -86,6 +88,7 @@ __device__ __forceinline__ double block_scan_max(double x, double* warp_tot, dou
 template <typename T>
 __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __restrict__ f, const T* __restrict__ i,
                                                                  float* __restrict__ ga_rel, float* __restrict__ gAn_rel,
+                                                                 float* __restrict__ ga_w,
                                                                  double* __restrict__ a_ref, double* __restrict__ An_ref,
                                                                  float* __restrict__ m, int S, int Spad,
                                                                  const double* __restrict__ carry_in,
@@ -123,14 +126,24 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
         const double F = block_scan_add(lf, wsum, carry_sum);
         const double a = in ? iv - F : -INFINITY;
         const double A = block_scan_max(a, wmax, carry_max);
+        // reference of a: the block's maximum (so ga_rel <= 0 and exp2(ga_rel) cannot overflow);
+        // reference of -A: the block's first element, which is its maximum because A never decreases
+        double amax = a;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmax(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = amax;   // wmax is free between the scans
+        if ((threadIdx.x % REF_BLOCK) == 0) ref_A[threadIdx.x / REF_BLOCK] = in ? A : 0.0;
+        __syncthreads();
         if ((threadIdx.x % REF_BLOCK) == 0) {
-            ref_a[threadIdx.x / REF_BLOCK] = in ? a : 0.0;
-            ref_A[threadIdx.x / REF_BLOCK] = in ? A : 0.0;
+            const double bm = fmax(wmax[threadIdx.x >> 5], wmax[(threadIdx.x >> 5) + 1]);
+            ref_a[threadIdx.x / REF_BLOCK] = (bm == -INFINITY) ? 0.0 : bm;
         }
         __syncthreads();
         if (t < Spad && ga_rel) {
             const double ra = ref_a[threadIdx.x / REF_BLOCK], rA = ref_A[threadIdx.x / REF_BLOCK];
-            ga_rel[static_cast<size_t>(bh) * Spad + t] = in ? static_cast<float>((a - ra) * LOG2E_D) : -INFINITY;
+            const float rel = in ? static_cast<float>((a - ra) * LOG2E_D) : -INFINITY;
+            ga_rel[static_cast<size_t>(bh) * Spad + t] = rel;
+            if (ga_w) ga_w[static_cast<size_t>(bh) * Spad + t] = exp2f(rel);   // in (0, 1]; 0 in the padding
             gAn_rel[static_cast<size_t>(bh) * Spad + t] = in ? static_cast<float>((rA - A) * LOG2E_D) : 0.0f;
             if ((threadIdx.x % REF_BLOCK) == 0) {
                 a_ref[static_cast<size_t>(bh) * nref + t / REF_BLOCK] = ra * LOG2E_D;
@@ -178,8 +191,8 @@ __global__ void gates_fold_kernel(const double* __restrict__ local, const double
 template <typename HT, typename T16>
 __global__ void bwd_prep_kernel(const HT* __restrict__ h, const HT* __restrict__ dh, const float* __restrict__ b,
                                 const float* __restrict__ m, const float* __restrict__ gAn_rel,
-                                float* __restrict__ gB_rel, float* __restrict__ g, T16* __restrict__ dh16, int BH, int S,
-                                int Spad, int D, float log2_scale) {
+                                float* __restrict__ gB_rel, float* __restrict__ gB_w, float* __restrict__ g,
+                                T16* __restrict__ dh16, int BH, int S, int Spad, int D, float log2_scale) {
     constexpr int VEC = 16 / sizeof(HT);
     const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -188,6 +201,7 @@ __global__ void bwd_prep_kernel(const HT* __restrict__ h, const HT* __restrict__
     if (t >= S) {
         if (lane == 0) {
             gB_rel[warp_global] = -INFINITY;
+            gB_w[warp_global] = 0.0f;
             g[warp_global] = 0.0f;
         }
         return;
@@ -217,7 +231,9 @@ __global__ void bwd_prep_kernel(const HT* __restrict__ h, const HT* __restrict__
         const float db = (fabsf(bb) > em) ? sgn * (-delta / n) : 0.0f;
         const float gg = db * n;
         g[warp_global] = isfinite(gg) ? gg : 0.0f;
-        gB_rel[warp_global] = gAn_rel[warp_global] + (log2_scale - log2f(n));
+        const float rel = gAn_rel[warp_global] + (log2_scale - log2f(n));
+        gB_rel[warp_global] = rel;
+        gB_w[warp_global] = exp2f(rel);   // the same quantity as a factor, for the off-diagonal tiles
     }
 }
 
@@ -324,21 +340,21 @@ namespace {
 template <typename T>
 int gates_launch_typed(const void* f, const void* i, float* ga, float* gA, double* a_ref, double* An_ref, float* m, int BH,
                        int S, int Spad, cudaStream_t st, const double* carry_in, double* summary_out, double* An_bound,
-                       int chunk_len, double* scratch) {
+                       int chunk_len, double* scratch, float* ga_w) {
     const int nseg = scratch ? (Spad + GATE_SEG_TOKENS - 1) / GATE_SEG_TOKENS : 1;
     if (nseg <= 1) {
-        gates_fwd_kernel<T><<<BH, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, ga, gA, a_ref, An_ref, m, S, Spad, carry_in,
+        gates_fwd_kernel<T><<<BH, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, ga, gA, ga_w, a_ref, An_ref, m, S, Spad, carry_in,
                                                          summary_out, An_bound, chunk_len, 1, Spad);
         return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
     }
     double* local = scratch;                                         // [BH * nseg][2]
     double* seg_carry = scratch + static_cast<size_t>(BH) * nseg * 2;  // [BH * nseg][2]
-    gates_fwd_kernel<T><<<BH * nseg, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, nullptr, nullptr, nullptr, nullptr,
+    gates_fwd_kernel<T><<<BH * nseg, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, nullptr, nullptr, nullptr, nullptr, nullptr,
                                                             nullptr, S, Spad, nullptr, local, nullptr, 0, nseg,
                                                             GATE_SEG_TOKENS);
     gates_fold_kernel<<<(BH + 127) / 128, 128, 0, st>>>(local, carry_in, seg_carry, summary_out, BH, nseg);
     if (ga || m || An_bound)
-        gates_fwd_kernel<T><<<BH * nseg, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, ga, gA, a_ref, An_ref, m, S, Spad,
+        gates_fwd_kernel<T><<<BH * nseg, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, ga, gA, ga_w, a_ref, An_ref, m, S, Spad,
                                                                 seg_carry, nullptr, An_bound, chunk_len, nseg,
                                                                 GATE_SEG_TOKENS);
     return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
@@ -352,24 +368,24 @@ size_t gates_scratch_bytes(int BH, int Spad) {
 
 int launch_gates_fwd(const void* f, const void* i, float* ga, float* gA, double* a_ref, double* An_ref, float* m, int BH,
                      int S, int Spad, int dtype, cudaStream_t st, const double* carry_in, double* summary_out,
-                     double* An_bound, int chunk_len, double* scratch) {
+                     double* An_bound, int chunk_len, double* scratch, float* ga_w) {
     switch (dtype) {
         case MLSTM_DT_F32:
             return gates_launch_typed<float>(f, i, ga, gA, a_ref, An_ref, m, BH, S, Spad, st, carry_in, summary_out, An_bound,
-                                             chunk_len, scratch);
+                                             chunk_len, scratch, ga_w);
         case MLSTM_DT_F16:
             return gates_launch_typed<__half>(f, i, ga, gA, a_ref, An_ref, m, BH, S, Spad, st, carry_in, summary_out, An_bound,
-                                              chunk_len, scratch);
+                                              chunk_len, scratch, ga_w);
         case MLSTM_DT_BF16:
             return gates_launch_typed<__nv_bfloat16>(f, i, ga, gA, a_ref, An_ref, m, BH, S, Spad, st, carry_in, summary_out,
-                                                     An_bound, chunk_len, scratch);
+                                                     An_bound, chunk_len, scratch, ga_w);
     }
     return MLSTM_E_ARG;
 }
 
 template <typename HT>
 static int bwd_prep_dispatch(const void* h, const void* dh, const float* b, const float* m, const float* gA, float* gB,
-                             float* g, void* dh16, int BH, int S, int Spad, int D, int dtype, cudaStream_t st) {
+                             float* gBw, float* g, void* dh16, int BH, int S, int Spad, int D, int dtype, cudaStream_t st) {
     const long long warps = static_cast<long long>(BH) * Spad;
     const int threads = 256;
     const long long blocks = (warps * 32 + threads - 1) / threads;
@@ -377,20 +393,20 @@ static int bwd_prep_dispatch(const void* h, const void* dh, const float* b, cons
     const float log2_scale = -0.5f * log2f(static_cast<float>(D));
     if (dtype == MLSTM_DT_BF16)
         bwd_prep_kernel<HT, __nv_bfloat16><<<(unsigned)blocks, threads, 0, st>>>(
-            (const HT*)h, (const HT*)dh, b, m, gA, gB, g, (__nv_bfloat16*)dh16, BH, S, Spad, D, log2_scale);
+            (const HT*)h, (const HT*)dh, b, m, gA, gB, gBw, g, (__nv_bfloat16*)dh16, BH, S, Spad, D, log2_scale);
     else
-        bwd_prep_kernel<HT, __half><<<(unsigned)blocks, threads, 0, st>>>((const HT*)h, (const HT*)dh, b, m, gA, gB, g,
+        bwd_prep_kernel<HT, __half><<<(unsigned)blocks, threads, 0, st>>>((const HT*)h, (const HT*)dh, b, m, gA, gB, gBw, g,
                                                                          (__half*)dh16, BH, S, Spad, D, log2_scale);
     return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
-int launch_bwd_prep(const void* h, const void* dh, const float* b, const float* m, const float* gA, float* gB, float* g,
-                    void* dh16, int BH, int S, int Spad, int D, int h_dtype, int dtype, cudaStream_t st) {
+int launch_bwd_prep(const void* h, const void* dh, const float* b, const float* m, const float* gA, float* gB, float* gBw,
+                    float* g, void* dh16, int BH, int S, int Spad, int D, int h_dtype, int dtype, cudaStream_t st) {
     switch (h_dtype) {
-        case MLSTM_DT_F32: return bwd_prep_dispatch<float>(h, dh, b, m, gA, gB, g, dh16, BH, S, Spad, D, dtype, st);
-        case MLSTM_DT_F16: return bwd_prep_dispatch<__half>(h, dh, b, m, gA, gB, g, dh16, BH, S, Spad, D, dtype, st);
+        case MLSTM_DT_F32: return bwd_prep_dispatch<float>(h, dh, b, m, gA, gB, gBw, g, dh16, BH, S, Spad, D, dtype, st);
+        case MLSTM_DT_F16: return bwd_prep_dispatch<__half>(h, dh, b, m, gA, gB, gBw, g, dh16, BH, S, Spad, D, dtype, st);
         case MLSTM_DT_BF16:
-            return bwd_prep_dispatch<__nv_bfloat16>(h, dh, b, m, gA, gB, g, dh16, BH, S, Spad, D, dtype, st);
+            return bwd_prep_dispatch<__nv_bfloat16>(h, dh, b, m, gA, gB, gBw, g, dh16, BH, S, Spad, D, dtype, st);
     }
     return MLSTM_E_ARG;
 }

@@ -57,6 +57,7 @@ struct PassParams {
     const double* row_ref;  // [BH, Spad / REF_BLOCK]
     const float* row_g;     // g per row (DQ) or nullptr
     const float* col_rel;   // [BH, Spad]
+    const float* col_w;     // [BH, Spad] exp2(col_rel): the tensor-core kernel's factorised path off the diagonal
     const double* col_ref;  // [BH, Spad / REF_BLOCK]
     const float* col_g;     // g per column (DK) or nullptr
     float er_add;           // constant term of er (FWD: log2(scale))
@@ -77,6 +78,7 @@ struct PassParams {
     const float* zstate;     // FWDC: [BH, NB, D] inbound normaliser vector of every block
     int* status;         // device word; a kernel that gave up on a wait stores a non-zero code
     int* sched;          // tensor-core passes: 8 device words, one work-item counter per pass mode
+    int slice_set;       // tensor-core passes: slices interleaved in the work-item order (set by the launcher)
 };
 
 template <typename T>
@@ -119,7 +121,7 @@ int note_cuda_error(cudaError_t err, const char* where);
 int launch_gates_fwd(const void* f, const void* i, float* ga_rel, float* gAn_rel, double* a_ref, double* An_ref, float* m,
                      int BH, int S, int Spad, int dtype, cudaStream_t st, const double* carry_in = nullptr,
                      double* summary_out = nullptr, double* An_bound = nullptr, int chunk_len = 0,
-                     double* scratch = nullptr);
+                     double* scratch = nullptr, float* ga_w = nullptr);
 // bytes of `scratch` that let launch_gates_fwd cut long slices into segments (0: not worth it)
 size_t gates_scratch_bytes(int BH, int Spad);
 // chunk.cu
@@ -128,7 +130,7 @@ int launch_state_scan(const float* U, const float* zU, const double* An_bound, c
                       void* states16, float* zstate, float* S_end, float* z_end, int BH, int NB, int D, int dtype,
                       cudaStream_t st);
 int launch_bwd_prep(const void* h, const void* dh, const float* b, const float* m, const float* gAn, float* gB,
-                    float* g, void* dh16, int BH, int S, int Spad, int D, int h_dtype, int dtype, cudaStream_t st);
+                    float* gBw, float* g, void* dh16, int BH, int S, int Spad, int D, int h_dtype, int dtype, cudaStream_t st);
 int launch_df(const void* f, const float* dI, const float* R, void* df, void* di, int BH, int S, int Spad, int dtype,
               cudaStream_t st);
 int launch_pass_simt(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st);

@@ -26,6 +26,7 @@
 // Every wait is bounded: a wait that runs out sets a CTA-wide abort word, every role leaves its
 // loop, the CTA stores a non-zero code in the status word, waits a little for copies in flight,
 // frees its TMEM and returns.
+#include <cstdlib>
 #include <type_traits>
 
 #include "mlstm_common.cuh"
@@ -41,7 +42,7 @@ constexpr int NGATE = NGROUPS * 128;            // gate threads
 constexpr int NTHREADS = 64 + NGATE;            // + producer warp and MMA warp
 constexpr int BOX_BYTES = 128 * 128;  // one TMA box: 128 rows of 128 bytes
 constexpr long long WAIT_LIMIT = 4000000000LL;  // cycles (about two seconds)
-constexpr int SLICE_SET = 8;                    // slices whose CTAs are interleaved in launch order
+constexpr int SLICE_SET_DEFAULT = 8;            // slices whose work items are interleaved in item order
 
 template <int D, int ES>
 struct TcCfg {
@@ -139,6 +140,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         it.vslice = y / nks;                                 // slice of the output columns
         it.xk0 = kslice * D;
         it.zv0 = it.vslice * D;
+        const int SLICE_SET = p.slice_set;
         const int per_set = per_slice * SLICE_SET;
         const int set = x / per_set;
         const int within = x - set * per_set;
@@ -370,8 +372,10 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             const int st = state_step ? 0 : stream_tile(it, t);
             const bool diag = (MODE != STATE) && !state_step && (st == tile);
             // state step: the column term is the inbound normaliser vector z (a weight, not an exponent)
+            // off the diagonal the column term comes as a factor exp2(ec) (see gates.cu), on the diagonal tile as
+            // the exponent itself: there a masked column can lie above the row's maximum and only the sum is safe
             const float* ce = state_step ? p.zstate + (static_cast<size_t>(bh) * p.NB + blk) * D
-                                         : p.col_rel + vec_base + st * TILE;
+                                         : (diag ? p.col_rel : p.col_w) + vec_base + st * TILE;
             // column terms do not depend on the contraction: fetch them before waiting
             float cv[32];
             load_cols(ce, cv);
@@ -414,11 +418,14 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     cv[j] = wj;
                 }
             } else {
+                // exp2(ec + er) = exp2(ec) exp2(er): one exponential per row and step; both factors are <= const
+                // because every column of an off-diagonal tile is on the causal side of every row
+                const float u = fast_exp2(er);
+                const float gu = (MODE == DQ) ? g_row * u : 0.0f;
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
-                    float tval = __uint_as_float(tv[j]);
-                    if (MODE == DQ) tval += g_row;
-                    const float wj = tval * fast_exp2(cv[j] + er);
+                    const float tu = (MODE == DQ) ? fmaf(__uint_as_float(tv[j]), u, gu) : __uint_as_float(tv[j]) * u;
+                    const float wj = tu * cv[j];
                     if (IS_FWD || MODE == STATE) rowsum += wj;
                     cv[j] = wj;
                 }
@@ -630,7 +637,16 @@ int sm_count() {
 }
 
 template <int MODE, int D, int ABFMT, typename OutT, bool SPLIT>
-int launch_one(const PassParams& p, int in_dtype, cudaStream_t st) {
+int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
+    PassParams p = p_in;
+    {
+        static int slice_set = 0;   // MLSTM_SLICE_SET overrides the default (tuning aid)
+        if (slice_set == 0) {
+            const char* e = getenv("MLSTM_SLICE_SET");
+            slice_set = (e && atoi(e) > 0) ? atoi(e) : SLICE_SET_DEFAULT;
+        }
+        p.slice_set = slice_set;
+    }
     CUtensorMap mx, my, mz, mi, ms;
     int rc;
     const int Dfull = SPLIT ? p.Dfull : D;
