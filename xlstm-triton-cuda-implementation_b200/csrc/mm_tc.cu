@@ -44,6 +44,18 @@ constexpr int BOX_BYTES = 128 * 128;  // one TMA box: 128 rows of 128 bytes
 constexpr long long WAIT_LIMIT = 4000000000LL;  // cycles (about two seconds)
 constexpr int SLICE_SET_DEFAULT = 8;            // slices whose work items are interleaved in item order
 
+#ifdef MLSTM_TRACE
+// Timing aid for kernel development (not built into the library): CTA 0 stamps clock64() at a few
+// points of its first work item.  g_trace[(role * 64 + step) * 4 + event].
+__device__ long long g_trace[3 * 64 * 4];
+#define TRACE(role, step, ev)                                                                  \
+    do {                                                                                       \
+        if (blockIdx.x == 0 && trace_on && (step) < 64) g_trace[((role) * 64 + (step)) * 4 + (ev)] = clock64(); \
+    } while (0)
+#else
+#define TRACE(role, step, ev) do { } while (0)
+#endif
+
 template <int D, int ES>
 struct TcCfg {
     static constexpr int EPB = 128 / ES;                      // elements per box row
@@ -175,10 +187,10 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         }
         mbar_init(&bar_t[0], 1);
         mbar_init(&bar_t[1], 1);
-        mbar_init(&bar_w[0], NGATE);
-        mbar_init(&bar_w[1], NGATE);
+        mbar_init(&bar_w[0], NGATE / 32);   // one arrival per gate warp
+        mbar_init(&bar_w[1], NGATE / 32);
         mbar_init(bar_acc, 1);
-        mbar_init(bar_accfree, NGATE);
+        mbar_init(bar_accfree, NGATE / 32);
         mbar_init(bar_part, NGATE);
         for (int k = 0; k < 4; k++) mbar_init(&bar_item[k], 1);
         *abort_flag = 0;
@@ -232,13 +244,16 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     if (MODE == STATE) tma_load_3d(sX + c * BOX_BYTES, &tmI, bar_x, c * C::EPB, 0, 0);
                     else tma_load_3d(sX + c * BOX_BYTES, &tmX, bar_x, it.xk0 + c * C::EPB, it.tile * TILE, it.bh);
                 }
+                [[maybe_unused]] const bool trace_on = (n == 0);
                 auto load_y = [&](int t) {
                     if (is_state_step(t)) load_tile(&tmI, 0, 0, 0);
                     else load_tile(&tmY, it.xk0, stream_tile(it, t) * TILE, it.bh);
+                    TRACE(0, t, 0);
                 };
                 auto load_z = [&](int t) {
                     if (is_state_step(t)) load_tile(&tmS, 0, 0, it.bh * p.NB + it.blk);
                     else load_tile(&tmZ, it.zv0, stream_tile(it, t) * TILE, it.bh);
+                    TRACE(0, t, 1);
                 };
                 // same order as the MMA issuer consumes: Y(0), then Y(t), Z(t-1) ..., Z(last)
                 load_y(0);
@@ -271,9 +286,11 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 ok = mbar_wait(bar_x, n & 1, abort_flag, WAIT_LIMIT);
                 if (!ok) break;
                 tc_fence_after();
+                [[maybe_unused]] const bool trace_on = (n == 0);
                 auto second = [&](int u) {  // ACC += W(u) Z(u)
                     const int gu = gstep + u;
                     ok = ok && mbar_wait(&bar_w[gu & 1], (gu >> 1) & 1, abort_flag, WAIT_LIMIT);
+                    TRACE(1, u, 2);
                     // the accumulator must have been drained by the previous item's epilogue
                     if (ok && u == 0) ok = mbar_wait(bar_accfree, (n & 1) ^ 1, abort_flag, WAIT_LIMIT);
                     if (!ok) return;
@@ -286,21 +303,31 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                         if (!ok) return;
                         tc_fence_after();
                         const uint64_t zdesc = smem_desc_advance(zdesc0, s * C::SLOT_BYTES);
+                        // all operands first, then the MMAs back to back: the issuing thread has no second
+                        // instruction stream to hide its own dependent-issue latency behind
+                        constexpr int KS2 = TILE / C::KSTEP;   // KSTEP streamed rows per MMA
+                        uint64_t bd[KS2];
+                        uint32_t at[KS2];
 #pragma unroll
-                        for (int kk = 0; kk < TILE / C::KSTEP; kk++) {  // KSTEP streamed rows per MMA
+                        for (int kk = 0; kk < KS2; kk++) {
+                            bd[kk] = smem_desc_advance(zdesc, kk * KROWS_BYTES);
                             // 16-bit W: gate group g packed streamed rows [32g, 32g+32) into columns
                             // [32g, 32g+16); 32-bit W: row j in column j.  Either way a K step is 8 columns.
-                            const uint32_t a_tmem = TF32 ? (w_tmem + kk * 8) : (w_tmem + (kk >> 1) * 32 + (kk & 1) * 8);
-                            mma_ts<TF32>(tmem_ACC + hf * C::CH, a_tmem, smem_desc_advance(zdesc, kk * KROWS_BYTES), idesc2,
-                                         (u > 0 || kk > 0) ? 1u : 0u);
+                            at[kk] = TF32 ? (w_tmem + kk * 8) : (w_tmem + (kk >> 1) * 32 + (kk & 1) * 8);
                         }
+                        const uint32_t acc_first = (u > 0) ? 1u : 0u;
+                        mma_ts<TF32>(tmem_ACC + hf * C::CH, at[0], bd[0], idesc2, acc_first);
+#pragma unroll
+                        for (int kk = 1; kk < KS2; kk++) mma_ts<TF32>(tmem_ACC + hf * C::CH, at[kk], bd[kk], idesc2, 1u);
                         tc_commit(&bar_empty[s]);
                     }
+                    TRACE(1, u, 3);
                 };
                 for (int t = 0; t < it.nsteps && ok; t++) {
                     // T(t) = X Y(t)^T
                     const int gt = gstep + t;
                     const uint32_t t_tmem = tmem_T0 + (gt & 1) * 128;
+                    TRACE(1, t, 0);
 #pragma unroll
                     for (int hf = 0; hf < C::NHALF; hf++, slot_it++) {
                         const int s = slot_it % C::NSLOT;
@@ -308,16 +335,21 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                         if (!ok) break;
                         tc_fence_after();
                         const uint64_t ydesc = smem_desc_advance(ydesc0, s * C::SLOT_BYTES);
+                        constexpr int KS1 = C::CH / C::KSTEP;
+                        uint64_t ad[KS1], bd[KS1];
 #pragma unroll
-                        for (int kk = 0; kk < C::CH / C::KSTEP; kk++) {
-                            const int kx = hf * (C::CH / C::KSTEP) + kk;  // K step inside the stationary tile
-                            // four K steps (4 x 32 bytes) per 128-byte box row
-                            mma_ss<TF32>(t_tmem, smem_desc_advance(xdesc0, (kx >> 2) * BOX_BYTES + (kx & 3) * 32),
-                                         smem_desc_advance(ydesc, (kk >> 2) * BOX_BYTES + (kk & 3) * 32), idesc1, kx > 0 ? 1u : 0u);
+                        for (int kk = 0; kk < KS1; kk++) {
+                            const int kx = hf * KS1 + kk;  // K step inside the stationary tile; four (4 x 32 bytes) per box row
+                            ad[kk] = smem_desc_advance(xdesc0, (kx >> 2) * BOX_BYTES + (kx & 3) * 32);
+                            bd[kk] = smem_desc_advance(ydesc, (kk >> 2) * BOX_BYTES + (kk & 3) * 32);
                         }
+                        mma_ss<TF32>(t_tmem, ad[0], bd[0], idesc1, hf > 0 ? 1u : 0u);
+#pragma unroll
+                        for (int kk = 1; kk < KS1; kk++) mma_ss<TF32>(t_tmem, ad[kk], bd[kk], idesc1, 1u);
                         tc_commit(&bar_empty[s]);
                     }
                     if (!ok) break;
+                    TRACE(1, t, 1);
                     tc_commit(&bar_t[gt & 1]);
                     if (t == it.nsteps - 1) tc_commit(bar_xfree);   // the stationary tile has been read for the last time
                     if (t >= 1) second(t - 1);
@@ -382,13 +414,17 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             const float er = state_step ? er_state
                                         : static_cast<float>(er_d + p.col_ref[ref_base + st * (TILE / REF_BLOCK) + (grp >> 1)]);
             const float er_w = (MODE == FWDC && state_step) ? fast_exp2(er) : 0.0f;
+            [[maybe_unused]] const bool trace_on = (n == 0) && threadIdx.x == 64;
+            TRACE(2, t, 0);
             ok = mbar_wait(&bar_t[buf], (gt >> 1) & 1, abort_flag, WAIT_LIMIT);
             if (!ok) break;
+            TRACE(2, t, 1);
             tc_fence_after();
             const uint32_t t_tmem = tmem_T0 + buf * 128 + lane_bits + cbase;
             uint32_t tv[32];
             tmem_ld32(t_tmem, tv);
             tc_wait_ld();
+            TRACE(2, t, 2);
             if (MODE == DK) {   // T + g with g per column: added eight columns at a time to keep registers free
                 const float4* g4 = reinterpret_cast<const float4*>(p.col_g + vec_base + st * TILE + cbase);
 #pragma unroll
@@ -450,7 +486,9 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             }
             tc_wait_st();
             tc_fence_before();
-            mbar_arrive(&bar_w[buf]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_w[buf]);   // 16 arrivals instead of 512 on one shared-memory word
+            TRACE(2, t, 3);
         }
         if (!ok) break;
         gstep += nsteps;
@@ -515,9 +553,10 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 }
                 tc_wait_ld();
                 if (ch == QUART / CW - 1) {
-                    // this thread's share of the accumulator is in registers: the next item may overwrite it
+                    // this warp's share of the accumulator is in registers: the next item may overwrite it
                     tc_fence_before();
-                    mbar_arrive(bar_accfree);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_accfree);
                 }
                 if (row_ok) {
                     float vals[CW];
@@ -719,6 +758,12 @@ int launch_d(const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) 
 }
 
 }  // namespace
+
+#ifdef MLSTM_TRACE
+extern "C" int mlstm_debug_trace(long long* out, int n) {
+    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * (n < 768 ? n : 768)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 bool tc_supported(int S, int D, int in_dtype) {
     return S >= 1 && (D == 64 || D == 128 || D == 256) &&
