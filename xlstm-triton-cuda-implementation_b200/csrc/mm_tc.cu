@@ -31,6 +31,7 @@
 
 #include "mlstm_common.cuh"
 #include "ptx_sm100.cuh"
+#include "tc_host.cuh"
 
 namespace mlstm {
 namespace {
@@ -41,19 +42,30 @@ constexpr int NGROUPS = 4;                      // gate groups: each gates 32 of
 constexpr int NGATE = NGROUPS * 128;            // gate threads
 constexpr int NTHREADS = 64 + NGATE;            // + producer warp and MMA warp
 constexpr int BOX_BYTES = 128 * 128;  // one TMA box: 128 rows of 128 bytes
-constexpr long long WAIT_LIMIT = 4000000000LL;  // cycles (about two seconds)
+constexpr long long WAIT_LIMIT = 4000000000LL;
+constexpr int SLACK_SLEEP_NS = 64;              // poll interval of the roles that wait with slack (gate warps, producer)  // cycles (about two seconds)
 constexpr int SLICE_SET_DEFAULT = 8;            // slices whose work items are interleaved in item order
 
 #ifdef MLSTM_TRACE
 // Timing aid for kernel development (not built into the library): CTA 0 stamps clock64() at a few
-// points of its first work item.  g_trace[(role * 64 + step) * 4 + event].
-__device__ long long g_trace[3 * 64 * 4];
+// points.  Per step of its first work item (only with MLSTM_TRACE_STEPS: a stamp costs about 100
+// cycles): g_trace[(role * 64 + step) * 8 + event].  Per work item: g_trace[2048 + item * 8 + event].
+__device__ long long g_trace[4 * 64 * 8 + 64 * 8];
+#ifdef MLSTM_TRACE_STEPS
 #define TRACE(role, step, ev)                                                                  \
     do {                                                                                       \
-        if (blockIdx.x == 0 && trace_on && (step) < 64) g_trace[((role) * 64 + (step)) * 4 + (ev)] = clock64(); \
+        if (blockIdx.x == 0 && trace_on && (step) < 64) g_trace[((role) * 64 + (step)) * 8 + (ev)] = clock64(); \
     } while (0)
 #else
 #define TRACE(role, step, ev) do { } while (0)
+#endif
+#define TRACE_ITEM(item, ev, val)                                                              \
+    do {                                                                                       \
+        if (blockIdx.x == 0 && issuer && (item) < 64) g_trace[2048 + (item) * 8 + (ev)] = (val); \
+    } while (0)
+#else
+#define TRACE(role, step, ev) do { } while (0)
+#define TRACE_ITEM(item, ev, val) do { } while (0)
 #endif
 
 template <int D, int ES>
@@ -66,7 +78,13 @@ struct TcCfg {
     static constexpr int SLOT_BYTES = (CH / EPB) * BOX_BYTES;
     static constexpr int X_BYTES = (D / EPB) * BOX_BYTES;
     static constexpr int NSLOT = ES == 2 ? (D == 256 ? 5 : (D == 128 ? 6 : 8)) : (D == 256 ? 3 : (D == 128 ? 5 : 6));
-    static constexpr int NBAR = 1 + 2 * NSLOT + 2 + 2 + 1 + 1 + 2 + 4;  // x, slot full/empty, t, w, acc, part, xfree, accfree, item[4]
+    // Streamed tiles are signalled in units of UH slots (a whole tile unless it has more than two slots):
+    // one "loaded" and one "consumed" barrier per unit, in rings of RING.
+    static constexpr int UH = NHALF <= 2 ? NHALF : 2;
+    static constexpr int UPT = NHALF / UH;                    // units per streamed tile
+    static constexpr int RING = 8;                            // >= units in flight (NSLOT / UH)
+    static_assert(NSLOT / UH <= RING && NSLOT > UH, "barrier ring too small / unit larger than the slot ring");
+    static constexpr int NBAR = 1 + 2 * RING + 2 + 1 + 1 + 1 + 1 + 4;  // x, unit full/consumed, w[2], acc, part, xfree, accfree, item[4]
     // the tiles start at the (1024-byte aligned, checked at run time) base of the dynamic shared memory
     static constexpr int SMEM_BYTES = X_BYTES + NSLOT * SLOT_BYTES + NBAR * 8 + 64 + NGROUPS * 128 * 4 /*row partials*/;
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA may have");
@@ -108,10 +126,10 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     uint8_t* sSlot = smem + C::X_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sSlot + C::NSLOT * C::SLOT_BYTES);
     uint64_t* bar_x = bars;
-    uint64_t* bar_full = bars + 1;
-    uint64_t* bar_empty = bars + 1 + C::NSLOT;
-    uint64_t* bar_t = bars + 1 + 2 * C::NSLOT;  // [2] T tile written by the first contraction
-    uint64_t* bar_w = bar_t + 2;                // [2] W tile written by the gate groups
+    uint64_t* bar_full = bars + 1;              // [RING] unit loaded
+    uint64_t* bar_cons = bars + 1 + C::RING;    // [RING] unit consumed: every MMA that reads it has completed.  For the
+                                                // last unit of a Y tile this also says "T tile written".
+    uint64_t* bar_w = bars + 1 + 2 * C::RING;   // [2] W tile written by the gate groups
     uint64_t* bar_acc = bar_w + 2;              // accumulator complete
     uint64_t* bar_part = bar_acc + 1;           // row partials of both gate groups in shared memory
     uint64_t* bar_xfree = bar_part + 1;         // stationary tile no longer read by the item's contractions
@@ -138,9 +156,9 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     // can run at most two items ahead of the slowest role, see the waits on bar_xfree / bar_accfree).
     // Item order: slices in sets of SLICE_SET, inside a set the heaviest tiles first, so that the
     // CTAs running at one time share the K/V (or Q/dH) of a few slices, which stay in L2.
-    auto next_item = [&](int n, bool& ok) {   // every role but the producer
-        ok = mbar_wait(&bar_item[n & 3], (n >> 2) & 1, abort_flag, WAIT_LIMIT);
-        return ok ? item_ids[n & 3] : -1;
+    auto next_item = [&](int n, bool& ok) {   // gate warps (converged)
+        ok = mbar_wait_warp<SLACK_SLEEP_NS>(&bar_item[n & 3], (n >> 2) & 1, abort_flag, WAIT_LIMIT);
+        return ok ? __shfl_sync(0xffffffffu, item_ids[n & 3], 0) : -1;
     };
     struct Item {
         int bh, tile, blk, first, nsteps, xk0, zv0, vslice;
@@ -181,17 +199,15 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     if (threadIdx.x == 0) {
         mbar_init(bar_x, 1);
         mbar_init(bar_xfree, 1);
-        for (int s = 0; s < C::NSLOT; s++) {
+        for (int s = 0; s < C::RING; s++) {
             mbar_init(&bar_full[s], 1);
-            mbar_init(&bar_empty[s], 1);
+            mbar_init(&bar_cons[s], 1);
         }
-        mbar_init(&bar_t[0], 1);
-        mbar_init(&bar_t[1], 1);
         mbar_init(&bar_w[0], NGATE / 32);   // one arrival per gate warp
         mbar_init(&bar_w[1], NGATE / 32);
         mbar_init(bar_acc, 1);
         mbar_init(bar_accfree, NGATE / 32);
-        mbar_init(bar_part, NGATE);
+        mbar_init(bar_part, NGATE / 32);
         for (int k = 0; k < 4; k++) mbar_init(&bar_item[k], 1);
         *abort_flag = 0;
         fence_mbar_init();
@@ -215,18 +231,25 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             prefetch_tmap(&tmZ);
             prefetch_tmap(&tmI);
             prefetch_tmap(&tmS);
-            int slot_it = 0;
+            int useq = 0;      // units loaded so far; the MMA warp consumes them in the same order
             bool ok = true;
-            // one streamed tile = NHALF slots of CH columns starting at column x0
+            // one streamed tile = NHALF slots of CH columns starting at column x0, signalled in units of UH slots
             auto load_tile = [&](const CUtensorMap* map, int x0, int row, int z) {
-                for (int hf = 0; hf < C::NHALF && ok; hf++, slot_it++) {
-                    const int s = slot_it % C::NSLOT;
-                    ok = mbar_wait(&bar_empty[s], ((slot_it / C::NSLOT) & 1) ^ 1, abort_flag, WAIT_LIMIT);
-                    if (!ok) break;
-                    mbar_expect_tx(&bar_full[s], C::SLOT_BYTES);
-                    uint8_t* dst = sSlot + s * C::SLOT_BYTES;
-                    for (int c = 0; c < C::CH / C::EPB; c++)
-                        tma_load_3d(dst + c * BOX_BYTES, map, &bar_full[s], x0 + hf * C::CH + c * C::EPB, row, z);
+                for (int un = 0; un < C::UPT && ok; un++, useq++) {
+                    uint64_t* fb = &bar_full[useq % C::RING];
+                    for (int h2 = 0; h2 < C::UH; h2++) {
+                        const int j = useq * C::UH + h2;          // slot sequence number
+                        if (j >= C::NSLOT) {                      // the slot's previous unit must have been consumed
+                            const int prev = (j - C::NSLOT) / C::UH;
+                            ok = mbar_wait<SLACK_SLEEP_NS>(&bar_cons[prev % C::RING], (prev / C::RING) & 1, abort_flag, WAIT_LIMIT);
+                            if (!ok) return;
+                        }
+                        if (h2 == 0) mbar_expect_tx(fb, C::UH * C::SLOT_BYTES);
+                        uint8_t* dst = sSlot + (j % C::NSLOT) * C::SLOT_BYTES;
+                        const int hf = un * C::UH + h2;
+                        for (int c = 0; c < C::CH / C::EPB; c++)
+                            tma_load_3d(dst + c * BOX_BYTES, map, fb, x0 + hf * C::CH + c * C::EPB, row, z);
+                    }
                 }
             };
             for (int n = 0; ok; n++) {
@@ -237,7 +260,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 if (id < 0) break;
                 const Item it = decode(id);
                 // the stationary tile's buffer is free once the previous item's first contractions are done
-                ok = mbar_wait(bar_xfree, (n & 1) ^ 1, abort_flag, WAIT_LIMIT);
+                ok = mbar_wait<SLACK_SLEEP_NS>(bar_xfree, (n & 1) ^ 1, abort_flag, WAIT_LIMIT);
                 if (!ok) break;
                 mbar_expect_tx(bar_x, C::X_BYTES);
                 for (int c = 0; c < D / C::EPB; c++) {
@@ -266,96 +289,160 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // The whole warp runs this loop and one elected lane issues the MMAs and commits.  tcgen05.mma takes
+        // its descriptors and addresses from warp-uniform registers: inside a one-lane branch the compiler
+        // has to move every operand there instruction by instruction, and the issue of one MMA then costs
+        // more cycles (about 100, measured) than a 128x128x16 MMA runs (64).  Kept convergent, with the
+        // values that come out of memory passed through a shuffle from lane 0 so that they count as
+        // uniform, the address arithmetic stays on the uniform datapath.
+        {
+            const bool issuer = elect_one();
+            auto uni = [](int x) { return __shfl_sync(0xffffffffu, x, 0); };
+            auto wait_u = [&](uint64_t* bar, uint32_t parity) { return mbar_wait_warp(bar, parity, abort_flag, WAIT_LIMIT); };
             constexpr uint32_t idesc1 = make_idesc(ABFMT, 128, 128, 0, 0);
             constexpr uint32_t idesc2 = make_idesc(ABFMT, 128, C::CH, 0, 1);
             constexpr int KROWS_BYTES = C::KSTEP * 128;  // KSTEP streamed rows of the Z tile
-            // The issuing thread shares its scheduler with gate warps, so every instruction it spends per
-            // MMA shows up as an idle tensor pipe: descriptors are built once and advanced with one add.
-            const uint64_t xdesc0 = smem_desc_sw128(smem_u32(sX), 16, 1024);           // K-major stationary tile
-            const uint64_t ydesc0 = smem_desc_sw128(smem_u32(sSlot), 16, 1024);        // K-major view of slot 0
-            const uint64_t zdesc0 = TF32 ? smem_desc_sw128(smem_u32(sSlot), BOX_BYTES, 512, 1)   // MN-major view of slot 0:
-                                         : smem_desc_sw128(smem_u32(sSlot), BOX_BYTES, 1024, 2); // 32-bit tiles use the 32-byte-atom swizzle
-            int slot_it = 0;
+            const uint32_t sX_u = static_cast<uint32_t>(uni(static_cast<int>(smem_u32(sX))));
+            const uint32_t sSlot_u = sX_u + C::X_BYTES;
+            const uint32_t tmem_T0u = static_cast<uint32_t>(uni(static_cast<int>(tmem_T0)));
+            const uint32_t tmem_ACCu = tmem_T0u + 256;
+            const uint64_t xdesc0 = smem_desc_sw128(sX_u, 16, 1024);           // K-major stationary tile
+            const uint64_t ydesc0 = smem_desc_sw128(sSlot_u, 16, 1024);        // K-major view of slot 0
+            const uint64_t zdesc0 = TF32 ? smem_desc_sw128(sSlot_u, BOX_BYTES, 512, 1)   // MN-major view of slot 0:
+                                         : smem_desc_sw128(sSlot_u, BOX_BYTES, 1024, 2); // 32-bit tiles use the 32-byte-atom swizzle
+            int useq = 0;      // units consumed so far
             int gstep = 0;     // steps issued by this CTA over all its items: T buffer and barrier phases follow it
             bool ok = true;
             for (int n = 0; ok; n++) {
-                const int id = next_item(n, ok);
+                ok = wait_u(&bar_item[n & 3], (n >> 2) & 1);
+                if (!ok) break;
+                const int id = uni(item_ids[n & 3]);
                 if (id < 0) break;
                 const Item it = decode(id);
-                ok = mbar_wait(bar_x, n & 1, abort_flag, WAIT_LIMIT);
+                TRACE_ITEM(n, 0, clock64());
+                ok = wait_u(bar_x, n & 1);
                 if (!ok) break;
                 tc_fence_after();
-                [[maybe_unused]] const bool trace_on = (n == 0);
+                TRACE_ITEM(n, 1, clock64());
+                TRACE_ITEM(n, 4, it.nsteps);
+                [[maybe_unused]] const bool trace_on = (n == 0) && issuer;
+                // Between two MMAs the issuing lane has time to spare (the tensor pipe holds the issue back to its
+                // own pace), between two batches it has none: whatever the warp does there leaves the pipe idle.
+                // So the barriers the next batch depends on are tested in the middle of the current batch; at the
+                // boundary a barrier is waited for only if that test failed.
+                auto try_u = [&](uint64_t* bar, uint32_t parity) {
+                    return __all_sync(0xffffffffu, mbar_test_wait(bar, parity) ? 1 : 0) != 0;
+                };
+                bool preY = false;   // "loaded" barrier of the next Y tile's first unit seen complete
+                bool preW = false;   // W(t-1) seen complete (and the tcgen05 fence after it executed)
+                bool preZ = false;   // "loaded" barrier of Z(t-1)'s first unit seen complete
                 auto second = [&](int u) {  // ACC += W(u) Z(u)
                     const int gu = gstep + u;
-                    ok = ok && mbar_wait(&bar_w[gu & 1], (gu >> 1) & 1, abort_flag, WAIT_LIMIT);
+                    TRACE(0, u, 2);   // directly after the caller's stamp: what a stamp costs
+                    if (!preW) {
+                        ok = ok && wait_u(&bar_w[gu & 1], (gu >> 1) & 1);
+                        if (ok) tc_fence_after();
+                    }
                     TRACE(1, u, 2);
                     // the accumulator must have been drained by the previous item's epilogue
-                    if (ok && u == 0) ok = mbar_wait(bar_accfree, (n & 1) ^ 1, abort_flag, WAIT_LIMIT);
+                    if (ok && u == 0) {
+                        ok = wait_u(bar_accfree, (n & 1) ^ 1);
+                        if (ok) tc_fence_after();
+                    }
                     if (!ok) return;
-                    tc_fence_after();
-                    const uint32_t w_tmem = tmem_T0 + (gu & 1) * 128;
+                    TRACE(1, u, 5);
+                    const uint32_t w_tmem = tmem_T0u + (gu & 1) * 128;
+                    constexpr int KS2 = TILE / C::KSTEP;   // KSTEP streamed rows per MMA
+                    preY = false;
 #pragma unroll
-                    for (int hf = 0; hf < C::NHALF; hf++, slot_it++) {
-                        const int s = slot_it % C::NSLOT;
-                        ok = mbar_wait(&bar_full[s], (slot_it / C::NSLOT) & 1, abort_flag, WAIT_LIMIT);
+                    for (int un = 0; un < C::UPT; un++, useq++) {
+                        if (!(un == 0 && preZ)) ok = wait_u(&bar_full[useq % C::RING], (useq / C::RING) & 1);   // TMA data: no tcgen05 fence
                         if (!ok) return;
-                        tc_fence_after();
-                        const uint64_t zdesc = smem_desc_advance(zdesc0, s * C::SLOT_BYTES);
-                        // all operands first, then the MMAs back to back: the issuing thread has no second
-                        // instruction stream to hide its own dependent-issue latency behind
-                        constexpr int KS2 = TILE / C::KSTEP;   // KSTEP streamed rows per MMA
-                        uint64_t bd[KS2];
-                        uint32_t at[KS2];
+                        if (un == 0) TRACE(1, u, 6);
 #pragma unroll
-                        for (int kk = 0; kk < KS2; kk++) {
-                            bd[kk] = smem_desc_advance(zdesc, kk * KROWS_BYTES);
-                            // 16-bit W: gate group g packed streamed rows [32g, 32g+32) into columns
-                            // [32g, 32g+16); 32-bit W: row j in column j.  Either way a K step is 8 columns.
-                            at[kk] = TF32 ? (w_tmem + kk * 8) : (w_tmem + (kk >> 1) * 32 + (kk & 1) * 8);
+                        for (int part = 0; part < 2; part++) {
+                            if (issuer) {
+#pragma unroll
+                                for (int h2 = 0; h2 < C::UH; h2++) {
+                                    const int hf = un * C::UH + h2;
+                                    const uint64_t zdesc = smem_desc_advance(zdesc0, ((useq * C::UH + h2) % C::NSLOT) * C::SLOT_BYTES);
+#pragma unroll
+                                    for (int kk = 0; kk < KS2; kk++) {
+                                        if (((h2 * KS2 + kk) * 2) / (C::UH * KS2) != part) continue;
+                                        // 16-bit W: gate group g packed streamed rows [32g, 32g+32) into columns
+                                        // [32g, 32g+16); 32-bit W: row j in column j.  Either way a K step is 8 columns.
+                                        const uint32_t at = TF32 ? (w_tmem + kk * 8) : (w_tmem + (kk >> 1) * 32 + (kk & 1) * 8);
+                                        mma_ts<TF32>(tmem_ACCu + hf * C::CH, at, smem_desc_advance(zdesc, kk * KROWS_BYTES), idesc2,
+                                                     (u > 0 || kk > 0) ? 1u : 0u);
+                                    }
+                                }
+                                if (part == 1) tc_commit(&bar_cons[useq % C::RING]);
+                            }
+                            __syncwarp();
+                            // next in line after this tile: Y(u + 2), if the item has one
+                            if (part == 0 && un == C::UPT - 1 && u + 2 < it.nsteps)
+                                preY = try_u(&bar_full[(useq + 1) % C::RING], ((useq + 1) / C::RING) & 1);
                         }
-                        const uint32_t acc_first = (u > 0) ? 1u : 0u;
-                        mma_ts<TF32>(tmem_ACC + hf * C::CH, at[0], bd[0], idesc2, acc_first);
-#pragma unroll
-                        for (int kk = 1; kk < KS2; kk++) mma_ts<TF32>(tmem_ACC + hf * C::CH, at[kk], bd[kk], idesc2, 1u);
-                        tc_commit(&bar_empty[s]);
                     }
                     TRACE(1, u, 3);
                 };
                 for (int t = 0; t < it.nsteps && ok; t++) {
                     // T(t) = X Y(t)^T
                     const int gt = gstep + t;
-                    const uint32_t t_tmem = tmem_T0 + (gt & 1) * 128;
+                    const uint32_t t_tmem = tmem_T0u + (gt & 1) * 128;
                     TRACE(1, t, 0);
+                    constexpr int KS1 = C::CH / C::KSTEP;
+                    preW = false;
+                    preZ = false;
 #pragma unroll
-                    for (int hf = 0; hf < C::NHALF; hf++, slot_it++) {
-                        const int s = slot_it % C::NSLOT;
-                        ok = mbar_wait(&bar_full[s], (slot_it / C::NSLOT) & 1, abort_flag, WAIT_LIMIT);
+                    for (int un = 0; un < C::UPT; un++, useq++) {
+                        if (!(un == 0 && preY)) ok = wait_u(&bar_full[useq % C::RING], (useq / C::RING) & 1);
                         if (!ok) break;
-                        tc_fence_after();
-                        const uint64_t ydesc = smem_desc_advance(ydesc0, s * C::SLOT_BYTES);
-                        constexpr int KS1 = C::CH / C::KSTEP;
-                        uint64_t ad[KS1], bd[KS1];
+                        if (un == 0) TRACE(1, t, 7);
 #pragma unroll
-                        for (int kk = 0; kk < KS1; kk++) {
-                            const int kx = hf * KS1 + kk;  // K step inside the stationary tile; four (4 x 32 bytes) per box row
-                            ad[kk] = smem_desc_advance(xdesc0, (kx >> 2) * BOX_BYTES + (kx & 3) * 32);
-                            bd[kk] = smem_desc_advance(ydesc, (kk >> 2) * BOX_BYTES + (kk & 3) * 32);
+                        for (int part = 0; part < 2; part++) {
+                            if (issuer) {
+#pragma unroll
+                                for (int h2 = 0; h2 < C::UH; h2++) {
+                                    const int hf = un * C::UH + h2;
+                                    const uint64_t ydesc = smem_desc_advance(ydesc0, ((useq * C::UH + h2) % C::NSLOT) * C::SLOT_BYTES);
+#pragma unroll
+                                    for (int kk = 0; kk < KS1; kk++) {
+                                        if (((h2 * KS1 + kk) * 2) / (C::UH * KS1) != part) continue;
+                                        const int kx = hf * KS1 + kk;  // K step inside the stationary tile; four (4 x 32 bytes) per box row
+                                        mma_ss<TF32>(t_tmem, smem_desc_advance(xdesc0, (kx >> 2) * BOX_BYTES + (kx & 3) * 32),
+                                                     smem_desc_advance(ydesc, (kk >> 2) * BOX_BYTES + (kk & 3) * 32), idesc1,
+                                                     (hf > 0 || kk > 0) ? 1u : 0u);
+                                    }
+                                }
+                                if (part == 1) {
+                                    // the unit is consumed; for the tile's last unit this is also "T(t) written"
+                                    tc_commit(&bar_cons[useq % C::RING]);
+                                    if (un == C::UPT - 1 && t == it.nsteps - 1) tc_commit(bar_xfree);   // stationary tile read for the last time
+                                }
+                            }
+                            __syncwarp();
+                            if (part == 0 && un == C::UPT - 1 && t >= 1) {   // next in line: W(t-1), then Z(t-1)
+                                const int gu = gt - 1;
+                                preW = try_u(&bar_w[gu & 1], (gu >> 1) & 1);
+                                if (preW) tc_fence_after();
+                                preZ = try_u(&bar_full[(useq + 1) % C::RING], ((useq + 1) / C::RING) & 1);
+                            }
                         }
-                        mma_ss<TF32>(t_tmem, ad[0], bd[0], idesc1, hf > 0 ? 1u : 0u);
-#pragma unroll
-                        for (int kk = 1; kk < KS1; kk++) mma_ss<TF32>(t_tmem, ad[kk], bd[kk], idesc1, 1u);
-                        tc_commit(&bar_empty[s]);
                     }
+                    preY = false;
                     if (!ok) break;
                     TRACE(1, t, 1);
-                    tc_commit(&bar_t[gt & 1]);
-                    if (t == it.nsteps - 1) tc_commit(bar_xfree);   // the stationary tile has been read for the last time
+                    TRACE(1, t, 4);
                     if (t >= 1) second(t - 1);
                 }
+                preW = false;
+                preZ = false;
+                TRACE_ITEM(n, 2, clock64());
                 if (ok) second(it.nsteps - 1);
-                if (ok) tc_commit(bar_acc);
+                if (ok && issuer) tc_commit(bar_acc);
+                __syncwarp();
+                TRACE_ITEM(n, 3, clock64());
                 gstep += it.nsteps;
             }
         }
@@ -414,17 +501,20 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             const float er = state_step ? er_state
                                         : static_cast<float>(er_d + p.col_ref[ref_base + st * (TILE / REF_BLOCK) + (grp >> 1)]);
             const float er_w = (MODE == FWDC && state_step) ? fast_exp2(er) : 0.0f;
-            [[maybe_unused]] const bool trace_on = (n == 0) && threadIdx.x == 64;
-            TRACE(2, t, 0);
-            ok = mbar_wait(&bar_t[buf], (gt >> 1) & 1, abort_flag, WAIT_LIMIT);
+            [[maybe_unused]] const bool trace_on = (n == 0) && (threadIdx.x == 64 || threadIdx.x == 64 + 15 * 32);
+            [[maybe_unused]] const int trole = threadIdx.x == 64 ? 2 : 3;
+            TRACE(trole, t, 0);
+            // units before the last one of Y(t): tiles go Y(0), Y(1), Z(0), Y(2), Z(1), ... in every item
+            const int sq = (2 * gstep + (t == 0 ? 0 : 2 * t - 1) + 1) * C::UPT - 1;
+            ok = mbar_wait_warp<SLACK_SLEEP_NS>(&bar_cons[sq % C::RING], (sq / C::RING) & 1, abort_flag, WAIT_LIMIT);
             if (!ok) break;
-            TRACE(2, t, 1);
+            TRACE(trole, t, 1);
             tc_fence_after();
             const uint32_t t_tmem = tmem_T0 + buf * 128 + lane_bits + cbase;
             uint32_t tv[32];
             tmem_ld32(t_tmem, tv);
             tc_wait_ld();
-            TRACE(2, t, 2);
+            TRACE(trole, t, 2);
             if (MODE == DK) {   // T + g with g per column: added eight columns at a time to keep registers free
                 const float4* g4 = reinterpret_cast<const float4*>(p.col_g + vec_base + st * TILE + cbase);
 #pragma unroll
@@ -466,6 +556,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     cv[j] = wj;
                 }
             }
+            TRACE(trole, t, 3);
             if constexpr (TF32) {
 #pragma unroll
                 for (int j = 0; j < 32; j++) tv[j] = to_tf32(cv[j]);
@@ -484,17 +575,19 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 }
                 tmem_st16(t_tmem, pk);   // two values per column, over the first 16 of this group's 32 columns
             }
+            TRACE(trole, t, 4);
             tc_wait_st();
+            TRACE(trole, t, 5);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_w[buf]);   // 16 arrivals instead of 512 on one shared-memory word
-            TRACE(2, t, 3);
+            TRACE(trole, t, 6);
         }
         if (!ok) break;
         gstep += nsteps;
 
         // ---- epilogue: each group drains a quarter of the accumulator's columns for all 128 rows
-        ok = mbar_wait(bar_acc, n & 1, abort_flag, WAIT_LIMIT);
+        ok = mbar_wait_warp<SLACK_SLEEP_NS>(bar_acc, n & 1, abort_flag, WAIT_LIMIT);
         if (!ok) break;
         {
             tc_fence_after();
@@ -504,10 +597,8 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             const int c0 = grp * QUART;
             const bool row_ok = (MODE == STATE) ? true : (grow < p.S);
             float* part = tail->part[0];                   // [NGROUPS][128]
-            // the partials of the previous item have been read by everybody once its accumulator was
-            // released (each thread reads them before it drains its share)
-            if (n > 0) ok = mbar_wait(bar_accfree, (n - 1) & 1, abort_flag, WAIT_LIMIT);
-            if (!ok) break;
+            // The row partials of the previous item are no longer read by anybody: a thread gets here only after
+            // every gate warp has finished this item's gate steps, which follow that item's epilogue.
             // STATE writes block (bh, blk) of [BH, NB, D, D]; everything else row `grow` of [BH, S, Dfull]
             const size_t row_off = (MODE == STATE)
                                        ? ((static_cast<size_t>(bh) * p.NB + blk) * D + r) * D
@@ -515,8 +606,9 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             float inv_n = 1.0f;
             auto exchange = [&](float x) {   // sum of one value per gate group for this row
                 part[grp * 128 + r] = x;
-                mbar_arrive(bar_part);
-                ok = mbar_wait(bar_part, n & 1, abort_flag, WAIT_LIMIT);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_part);
+                ok = mbar_wait_warp<SLACK_SLEEP_NS>(bar_part, n & 1, abort_flag, WAIT_LIMIT);
                 return ok ? (part[r] + part[128 + r]) + (part[256 + r] + part[384 + r]) : 0.0f;
             };
             if (MODE == STATE) {
@@ -646,13 +738,13 @@ EncodeTiledFn get_encode() {
 // [N2, N1, N0] tensor (N0 contiguous), boxes of 128 bytes x 128 rows, 128-byte swizzle, zero fill
 // outside the tensor.
 // atom32: 128-byte swizzle with 32-byte atoms (needed where a 32-bit tile is read MN-major).
-int make_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, bool atom32 = false) {
+int make_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, bool atom32 = false, int box_rows = 128) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return MLSTM_E_CUDA;
     const cuuint64_t es = dtype == MLSTM_DT_F32 ? 4 : 2;
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(N0), static_cast<cuuint64_t>(N1), static_cast<cuuint64_t>(N2)};
     cuuint64_t strides[2] = {static_cast<cuuint64_t>(N0) * es, static_cast<cuuint64_t>(N1) * N0 * es};
-    cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / es), 128, 1};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(box_rows), 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUtensorMapDataType dt = dtype == MLSTM_DT_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                              : dtype == MLSTM_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -678,14 +770,7 @@ int sm_count() {
 template <int MODE, int D, int ABFMT, typename OutT, bool SPLIT>
 int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
     PassParams p = p_in;
-    {
-        static int slice_set = 0;   // MLSTM_SLICE_SET overrides the default (tuning aid)
-        if (slice_set == 0) {
-            const char* e = getenv("MLSTM_SLICE_SET");
-            slice_set = (e && atoi(e) > 0) ? atoi(e) : SLICE_SET_DEFAULT;
-        }
-        p.slice_set = slice_set;
-    }
+    p.slice_set = tc_slice_set();
     CUtensorMap mx, my, mz, mi, ms;
     int rc;
     const int Dfull = SPLIT ? p.Dfull : D;
@@ -761,9 +846,24 @@ int launch_d(const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) 
 
 #ifdef MLSTM_TRACE
 extern "C" int mlstm_debug_trace(long long* out, int n) {
-    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * (n < 768 ? n : 768)) == cudaSuccess ? 0 : -1;
+    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * (n < 2560 ? n : 2560)) == cudaSuccess ? 0 : -1;
 }
 #endif
+
+int tc_make_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, bool atom32, int box_rows) {
+    return make_map(map, base, N2, N1, N0, dtype, atom32, box_rows);
+}
+
+int tc_sm_count() { return sm_count(); }
+
+int tc_slice_set() {
+    static int slice_set = 0;   // MLSTM_SLICE_SET overrides the default (tuning aid)
+    if (slice_set == 0) {
+        const char* e = getenv("MLSTM_SLICE_SET");
+        slice_set = (e && atoi(e) > 0) ? atoi(e) : SLICE_SET_DEFAULT;
+    }
+    return slice_set;
+}
 
 bool tc_supported(int S, int D, int in_dtype) {
     return S >= 1 && (D == 64 || D == 128 || D == 256) &&
@@ -777,6 +877,14 @@ bool tc_split_supported(int S, int D, int in_dtype) {
 
 int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) {
     if (!tc_supported(p.S, p.D, in_dtype)) return MLSTM_E_UNSUPPORTED;
+    if (mode <= DV && tc_pair_supported(p.S, p.D, in_dtype)) {
+        static int use_pairs = -1;   // MLSTM_NO_PAIR=1 keeps the one-CTA kernel (comparison aid)
+        if (use_pairs < 0) {
+            const char* e = getenv("MLSTM_NO_PAIR");
+            use_pairs = (e && atoi(e) > 0) ? 0 : 1;
+        }
+        if (use_pairs) return launch_pass_tc_pair(mode, p, in_dtype, out_dtype, st);
+    }
     switch (mode) {
         case FWD: return launch_d<FWD>(p, in_dtype, out_dtype, st);
         case DQ: return launch_d<DQ>(p, in_dtype, out_dtype, st);

@@ -1,0 +1,616 @@
+// Tensor-core contraction pass on CTA PAIRS for the head dimension 256 (16-bit inputs): the same four
+// passes and the same algebra as mm_tc.cu (see there and mlstm_common.cuh), with two CTAs of a
+// cluster working on two neighbouring stationary tiles of one slice and sharing every streamed tile.
+//
+// Why: at D = 256 a single CTA streams 128 KB per step through the 160 KB that remain beside its
+// stationary tile, so barely more than one step of loads can be in flight, and both operands of the
+// first contraction come from shared memory at exactly its bandwidth.  With tcgen05.mma.cta_group::2
+// one thread of the leader CTA issues M = 256 MMAs that run on both SMs: each CTA supplies its own 128
+// rows of A (its stationary tile, or its W tile in TMEM) and HALF of B (64 of the 128 rows of the
+// streamed Y tile for T = X Y^T; 128 of the 256 columns of the streamed Z tile for ACC += W Z), and
+// gets its 128 rows of the result in its own TMEM.  Every CTA therefore loads 64 KB per step instead
+// of 128 KB, and the ring holds two and a half steps.
+//
+// Roles per CTA as in mm_tc.cu (TMA producer warp, MMA warp, four gate groups); only the leader's MMA
+// warp issues MMAs.  Barriers that the MMA thread waits on live in the leader (slot full, X loaded,
+// W written, accumulator drained: the follower's TMA loads and gate warps signal them remotely);
+// barriers that the MMA thread signals exist in both CTAs and get one tcgen05.commit each.  No load
+// uses cluster multicast.  Every wait is bounded as in mm_tc.cu; the two hardware cluster barriers
+// (after initialisation, before exit) are reached by every thread on every path.
+#include <cstdlib>
+#include <type_traits>
+
+#include "mlstm_common.cuh"
+#include "ptx_sm100.cuh"
+#include "tc_host.cuh"
+
+namespace mlstm {
+namespace {
+
+using namespace ptx;
+
+constexpr int D = 256;
+constexpr int NGROUPS = 4;
+constexpr int NGATE = NGROUPS * 128;
+constexpr int NTHREADS = 64 + NGATE;
+constexpr int BOX_BYTES = 128 * 128;           // 128 rows x 128 bytes
+constexpr int HBOX_BYTES = 64 * 128;           // 64 rows x 128 bytes (half of a streamed Y tile's rows)
+constexpr int X_BYTES = (D / 64) * BOX_BYTES;  // 64 KB stationary tile
+constexpr int SLOT_BYTES = 32 * 1024;          // Y half: 64 rows x 256 cols; Z half: 128 rows x 128 cols
+constexpr int NSLOT = 5;
+constexpr int NBAR = 1 + 2 * NSLOT + 2 + 2 + 1 + 1 + 2 + 4;
+constexpr int SMEM_BYTES = X_BYTES + NSLOT * SLOT_BYTES + NBAR * 8 + 64 + NGROUPS * 128 * 4;
+constexpr long long WAIT_LIMIT = 4000000000LL;
+constexpr int SLACK_SLEEP_NS = 64;              // poll interval of the roles that wait with slack (gate warps, producer)
+static_assert(SMEM_BYTES <= 232448, "exceeds the shared memory of a CTA");
+
+#ifdef MLSTM_TRACE
+__device__ long long g_trace_pair[3 * 64 * 8];   // development aid: leader MMA warp of cluster 0, first item, [step][event]
+#define PTRACE(step, ev)                                                                                   \
+    do {                                                                                                   \
+        if (blockIdx.x == 0 && n == 0 && issuer && (step) < 64) g_trace_pair[(step) * 8 + (ev)] = clock64(); \
+    } while (0)
+#define GTRACE(step, ev)                                                                                   \
+    do {                                                                                                   \
+        if (blockIdx.x < 2 && n == 0 && threadIdx.x == 64 && (step) < 64)                                  \
+            g_trace_pair[(1 + blockIdx.x) * 512 + (step) * 8 + (ev)] = clock64();                          \
+    } while (0)
+#else
+#define PTRACE(step, ev) do { } while (0)
+#define GTRACE(step, ev) do { } while (0)
+#endif
+
+template <int MODE, int ABFMT, typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1)
+mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmYh,
+                   const __grid_constant__ CUtensorMap tmZ, const PassParams p) {
+    using InT = typename std::conditional<ABFMT == 1, __nv_bfloat16, __half>::type;
+    constexpr bool ROWS_ARE_Q = (MODE == FWD || MODE == DQ);
+    constexpr bool IS_FWD = (MODE == FWD);
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
+    uint8_t* sX = smem;
+    uint8_t* sSlot = smem + X_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sSlot + NSLOT * SLOT_BYTES);
+    uint64_t* bar_x = bars;                     // leader: both stationary tiles loaded
+    uint64_t* bar_full = bars + 1;              // leader: both halves of a slot loaded
+    uint64_t* bar_empty = bars + 1 + NSLOT;     // both: slot no longer read by MMAs
+    uint64_t* bar_t = bars + 1 + 2 * NSLOT;     // both [2]: T tile written
+    uint64_t* bar_w = bar_t + 2;                // leader [2]: W tiles of both CTAs written (32 warp arrivals)
+    uint64_t* bar_acc = bar_w + 2;              // both: accumulators complete
+    uint64_t* bar_part = bar_acc + 1;           // own: row partials exchanged
+    uint64_t* bar_xfree = bar_part + 1;         // both: stationary tiles no longer read
+    uint64_t* bar_accfree = bar_xfree + 1;      // leader: accumulators of both CTAs drained (32 warp arrivals)
+    uint64_t* bar_item = bar_accfree + 1;       // both [4]: work item published
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBAR);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* item_ids = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + NBAR * 8 + 64);  // [NGROUPS][128]
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();    // 0 = leader
+    const uint32_t peer = rank ^ 1u;
+    const int NT = p.Spad / TILE;
+    const int NP = (NT + 1) / 2;                 // tile pairs per slice
+    const int total = NP * p.BH;
+    const bool misaligned = (smem_u32(smem) & 1023u) != 0;   // uniform over the cluster in practice; never seen
+
+    struct Item {
+        int bh, pair, tile, nsteps;
+    };
+    auto decode = [&](int id) {
+        Item it;
+        const int SLICE_SET = p.slice_set;
+        const int per_set = NP * SLICE_SET;
+        const int set = id / per_set;
+        const int within = id - set * per_set;
+        const int set_size = min(SLICE_SET, p.BH - set * SLICE_SET);
+        const int w = within / set_size;
+        it.bh = set * SLICE_SET + (within - w * set_size);
+        it.pair = ROWS_ARE_Q ? (NP - 1 - w) : w;           // heaviest first
+        it.tile = 2 * it.pair + static_cast<int>(rank);     // this CTA's stationary tile (may be == NT: idle half)
+        it.nsteps = ROWS_ARE_Q ? min(2 * it.pair + 2, NT) : (NT - 2 * it.pair);
+        return it;
+    };
+    auto stream_tile = [&](const Item& it, int t) { return ROWS_ARE_Q ? t : (2 * it.pair + t); };
+
+    // shared::cluster addresses of the leader's and the peer's copies of a barrier
+    auto at_leader = [&](const void* local) { return mapa_u32(smem_u32(local), 0u); };
+    auto at_peer = [&](const void* local) { return mapa_u32(smem_u32(local), peer); };
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_x, 1);
+        mbar_init(bar_xfree, 1);
+        for (int s = 0; s < NSLOT; s++) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_empty[s], 1);
+        }
+        mbar_init(&bar_t[0], 1);
+        mbar_init(&bar_t[1], 1);
+        mbar_init(&bar_w[0], 2 * NGATE / 32);
+        mbar_init(&bar_w[1], 2 * NGATE / 32);
+        mbar_init(bar_acc, 1);
+        mbar_init(bar_accfree, 2 * NGATE / 32);
+        mbar_init(bar_part, NGATE / 32);
+        for (int k = 0; k < 4; k++) mbar_init(&bar_item[k], 1);
+        *abort_flag = misaligned ? 1 : 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();           // the peer's barriers are initialised before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_T0 = tmem_base;
+    const uint32_t tmem_ACC = tmem_base + 256;
+
+    auto next_item = [&](int n, bool& ok) {        // one thread (the follower's producer)
+        ok = mbar_wait_cluster<SLACK_SLEEP_NS>(&bar_item[n & 3], (n >> 2) & 1, abort_flag, WAIT_LIMIT);
+        return ok ? item_ids[n & 3] : -1;
+    };
+    auto next_item_warp = [&](int n, bool& ok) {   // gate warps (converged)
+        ok = mbar_wait_cluster_warp<SLACK_SLEEP_NS>(&bar_item[n & 3], (n >> 2) & 1, abort_flag, WAIT_LIMIT);
+        return ok ? __shfl_sync(0xffffffffu, item_ids[n & 3], 0) : -1;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (one per CTA)
+        if (lane == 0) {
+            prefetch_tmap(&tmX);
+            prefetch_tmap(&tmYh);
+            prefetch_tmap(&tmZ);
+            int slot_it = 0;
+            bool ok = !*abort_flag;
+            const uint32_t lead_x = at_leader(bar_x);
+            for (int n = 0; ok; n++) {
+                int id;
+                if (rank == 0) {
+                    id = atomicAdd(p.sched + MODE, 1);
+                    if (id >= total) id = -1;
+                    item_ids[n & 3] = id;
+                    st_cluster_u32(at_peer(const_cast<int*>(&item_ids[n & 3])), static_cast<uint32_t>(id));
+                    mbar_arrive(&bar_item[n & 3]);
+                    mbar_arrive_cluster(at_peer(&bar_item[n & 3]));   // release at cluster scope: the peer sees the id
+                } else {
+                    id = next_item(n, ok);
+                }
+                if (id < 0) break;
+                const Item it = decode(id);
+                ok = mbar_wait<SLACK_SLEEP_NS>(bar_xfree, (n & 1) ^ 1, abort_flag, WAIT_LIMIT);
+                if (!ok) break;
+                if (rank == 0) mbar_expect_tx(bar_x, 2 * X_BYTES);
+                for (int c = 0; c < D / 64; c++)   // rows past the end of the slice (idle half, ragged S) read as zeros
+                    tma_load_3d_pair(sX + c * BOX_BYTES, &tmX, lead_x, c * 64, it.tile * TILE, it.bh);
+                auto load_y = [&](int t) {   // this CTA's 64 rows of the streamed tile, all 256 columns
+                    const int s = slot_it % NSLOT;
+                    ok = ok && mbar_wait<SLACK_SLEEP_NS>(&bar_empty[s], ((slot_it / NSLOT) & 1) ^ 1, abort_flag, WAIT_LIMIT);
+                    if (!ok) return;
+                    if (rank == 0) mbar_expect_tx(&bar_full[s], 2 * SLOT_BYTES);
+                    const uint32_t lead_full = at_leader(&bar_full[s]);
+                    uint8_t* dst = sSlot + s * SLOT_BYTES;
+                    const int row = stream_tile(it, t) * TILE + static_cast<int>(rank) * 64;
+                    for (int c = 0; c < D / 64; c++) tma_load_3d_pair(dst + c * HBOX_BYTES, &tmYh, lead_full, c * 64, row, it.bh);
+                    slot_it++;
+                };
+                auto load_z = [&](int t) {   // all 128 rows of the streamed tile, this CTA's 128 columns
+                    const int s = slot_it % NSLOT;
+                    ok = ok && mbar_wait<SLACK_SLEEP_NS>(&bar_empty[s], ((slot_it / NSLOT) & 1) ^ 1, abort_flag, WAIT_LIMIT);
+                    if (!ok) return;
+                    if (rank == 0) mbar_expect_tx(&bar_full[s], 2 * SLOT_BYTES);
+                    const uint32_t lead_full = at_leader(&bar_full[s]);
+                    uint8_t* dst = sSlot + s * SLOT_BYTES;
+                    for (int c = 0; c < 2; c++)
+                        tma_load_3d_pair(dst + c * BOX_BYTES, &tmZ, lead_full, static_cast<int>(rank) * 128 + c * 64,
+                                         stream_tile(it, t) * TILE, it.bh);
+                    slot_it++;
+                };
+                load_y(0);
+                for (int t = 1; t < it.nsteps && ok; t++) {
+                    load_y(t);
+                    load_z(t - 1);
+                }
+                if (ok) load_z(it.nsteps - 1);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader only)
+        // the whole warp runs the loop, one elected lane issues (see mm_tc.cu for why)
+        if (rank == 0) {
+            const bool issuer = elect_one();
+            auto uni = [](int x) { return __shfl_sync(0xffffffffu, x, 0); };
+            auto wait_u = [&](uint64_t* bar, uint32_t parity) { return mbar_wait_warp(bar, parity, abort_flag, WAIT_LIMIT); };
+            constexpr uint32_t idesc1 = make_idesc(ABFMT, 256, 128, 0, 0);
+            constexpr uint32_t idesc2 = make_idesc(ABFMT, 256, 256, 0, 1);
+            const uint32_t sX_u = static_cast<uint32_t>(uni(static_cast<int>(smem_u32(sX))));
+            const uint32_t sSlot_u = sX_u + X_BYTES;
+            const uint32_t bars_u = sSlot_u + NSLOT * SLOT_BYTES;          // this CTA's barriers ...
+            const uint32_t bars_peer_u = static_cast<uint32_t>(uni(static_cast<int>(at_peer(bars))));   // ... and the peer's
+            const uint32_t tmem_T0u = static_cast<uint32_t>(uni(static_cast<int>(tmem_T0)));
+            const uint32_t tmem_ACCu = tmem_T0u + 256;
+            const uint64_t xdesc0 = smem_desc_sw128(sX_u, 16, 1024);
+            const uint64_t ydesc0 = smem_desc_sw128(sSlot_u, 16, 1024);
+            const uint64_t zdesc0 = smem_desc_sw128(sSlot_u, BOX_BYTES, 1024, 2);
+            auto commit_both = [&](const uint64_t* bar) {   // one arrival in either CTA
+                const uint32_t off = static_cast<uint32_t>(bar - bars) * 8u;
+                tc_commit_pair(bars_u + off);
+                tc_commit_pair(bars_peer_u + off);
+            };
+            int slot_it = 0;
+            int gstep = 0;
+            bool ok = __all_sync(0xffffffffu, *abort_flag ? 0 : 1) != 0;
+            for (int n = 0; ok; n++) {
+                ok = mbar_wait_cluster_warp(&bar_item[n & 3], (n >> 2) & 1, abort_flag, WAIT_LIMIT);
+                if (!ok) break;
+                const int id = uni(item_ids[n & 3]);
+                if (id < 0) break;
+                const Item it = decode(id);
+                ok = wait_u(bar_x, n & 1);
+                if (!ok) break;
+                tc_fence_after();
+                auto second = [&](int u) {  // ACC += W(u) Z(u), both CTAs
+                    const int gu = gstep + u;
+                    ok = ok && wait_u(&bar_w[gu & 1], (gu >> 1) & 1);
+                    PTRACE(u, 3);
+                    if (ok && u == 0) ok = wait_u(bar_accfree, (n & 1) ^ 1);
+                    if (!ok) return;
+                    tc_fence_after();
+                    const int s = slot_it % NSLOT;
+                    ok = wait_u(&bar_full[s], (slot_it / NSLOT) & 1);
+                    if (!ok) return;
+                    PTRACE(u, 4);
+                    const uint32_t w_tmem = tmem_T0u + (gu & 1) * 128;
+                    const uint64_t zdesc = smem_desc_advance(zdesc0, s * SLOT_BYTES);
+                    if (issuer) {
+#pragma unroll
+                        for (int kk = 0; kk < 8; kk++) {   // 16 streamed rows per MMA; N = 256 (128 columns from each CTA)
+                            const uint32_t a_tmem = w_tmem + (kk >> 1) * 32 + (kk & 1) * 8;
+                            mma_ts_pair(tmem_ACCu, a_tmem, smem_desc_advance(zdesc, kk * 2048), idesc2, (u > 0 || kk > 0) ? 1u : 0u);
+                        }
+                        commit_both(&bar_empty[s]);
+                    }
+                    __syncwarp();
+                    PTRACE(u, 5);
+                    slot_it++;
+                };
+                for (int t = 0; t < it.nsteps && ok; t++) {
+                    const int gt = gstep + t;
+                    const uint32_t t_tmem = tmem_T0u + (gt & 1) * 128;
+                    const int s = slot_it % NSLOT;
+                    PTRACE(t, 0);
+                    ok = wait_u(&bar_full[s], (slot_it / NSLOT) & 1);
+                    if (!ok) break;
+                    PTRACE(t, 1);
+                    const uint64_t ydesc = smem_desc_advance(ydesc0, s * SLOT_BYTES);
+                    if (issuer) {
+#pragma unroll
+                        for (int kx = 0; kx < D / 16; kx++) {   // T(t) = X Y(t)^T: N = 128 (64 rows of Y from each CTA)
+                            mma_ss_pair(t_tmem, smem_desc_advance(xdesc0, (kx >> 2) * BOX_BYTES + (kx & 3) * 32),
+                                        smem_desc_advance(ydesc, (kx >> 2) * HBOX_BYTES + (kx & 3) * 32), idesc1, kx > 0 ? 1u : 0u);
+                        }
+                        commit_both(&bar_empty[s]);
+                        commit_both(&bar_t[gt & 1]);
+                        if (t == it.nsteps - 1) commit_both(bar_xfree);
+                    }
+                    __syncwarp();
+                    PTRACE(t, 2);
+                    slot_it++;
+                    if (t >= 1) second(t - 1);
+                }
+                if (ok) second(it.nsteps - 1);
+                if (ok && issuer) commit_both(bar_acc);
+                __syncwarp();
+                gstep += it.nsteps;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ gate groups
+        const int grp = (warp - 2) >> 2;
+        const int r = (warp & 3) * 32 + lane;
+        const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const int cbase = grp * 32;
+        auto load_cols = [&](const float* base, float (&dst)[32]) {
+            const float4* p4 = reinterpret_cast<const float4*>(base + cbase);
+#pragma unroll
+            for (int q4 = 0; q4 < 8; q4++) {
+                const float4 e4 = __ldg(p4 + q4);
+                dst[q4 * 4 + 0] = e4.x; dst[q4 * 4 + 1] = e4.y; dst[q4 * 4 + 2] = e4.z; dst[q4 * 4 + 3] = e4.w;
+            }
+        };
+        const uint32_t lead_w[2] = {at_leader(&bar_w[0]), at_leader(&bar_w[1])};
+        const uint32_t lead_accfree = at_leader(bar_accfree);
+        bool ok = __all_sync(0xffffffffu, *abort_flag == 0) != 0;
+        int gstep = 0;
+        for (int n = 0; ok; n++) {
+        const int id = next_item_warp(n, ok);
+        if (id < 0) break;
+        const Item it = decode(id);
+        const int bh = it.bh, tile = it.tile, nsteps = it.nsteps;
+        const bool active = tile < NT;                 // the idle half of an odd last pair only keeps the protocol going
+        const int grow = tile * TILE + r;
+        const size_t vec_base = static_cast<size_t>(bh) * p.Spad;
+        const size_t ref_base = static_cast<size_t>(bh) * (p.Spad / REF_BLOCK);
+        const double er_d = active ? static_cast<double>(p.row_rel[vec_base + grow]) + p.row_ref[ref_base + grow / REF_BLOCK] +
+                                         static_cast<double>(p.er_add)
+                                   : 0.0;
+        const float g_row = (MODE == DQ && active) ? p.row_g[vec_base + grow] : 0.0f;
+        float rowsum = 0.0f;
+
+        for (int t = 0; t < nsteps; t++) {
+            const int gt = gstep + t;
+            const int buf = gt & 1;
+            const int st = stream_tile(it, t);
+            const bool diag = (st == tile);
+            // tiles on the wrong side of this CTA's diagonal (they belong to the partner's triangle) give W = 0
+            const bool dead = !active || (ROWS_ARE_Q ? (st > tile) : (st < tile));
+            float cv[32];
+            if (!dead) load_cols((diag ? p.col_rel : p.col_w) + vec_base + st * TILE, cv);
+            const float er = dead ? 0.0f : static_cast<float>(er_d + p.col_ref[ref_base + st * (TILE / REF_BLOCK) + (grp >> 1)]);
+            GTRACE(t, 0);
+            ok = mbar_wait_warp<SLACK_SLEEP_NS>(&bar_t[buf], (gt >> 1) & 1, abort_flag, WAIT_LIMIT);
+            if (!ok) break;
+            GTRACE(t, 1);
+            tc_fence_after();
+            const uint32_t t_tmem = tmem_T0 + buf * 128 + lane_bits + cbase;
+            uint32_t pk[16];
+            if (dead) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) pk[j] = 0u;
+            } else {
+                uint32_t tv[32];
+                tmem_ld32(t_tmem, tv);
+                tc_wait_ld();
+                if (MODE == DK) {
+                    const float4* g4 = reinterpret_cast<const float4*>(p.col_g + vec_base + st * TILE + cbase);
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; q4++) {
+                        const float4 gq = __ldg(g4 + q4);
+                        tv[q4 * 4 + 0] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 0]) + gq.x);
+                        tv[q4 * 4 + 1] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 1]) + gq.y);
+                        tv[q4 * 4 + 2] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 2]) + gq.z);
+                        tv[q4 * 4 + 3] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 3]) + gq.w);
+                    }
+                }
+                if (diag) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        float tval = __uint_as_float(tv[j]);
+                        if (MODE == DQ) tval += g_row;
+                        float wj = tval * fast_exp2(cv[j] + er);
+                        if (!causal_ok<MODE>(r, cbase + j)) wj = 0.0f;
+                        if (IS_FWD) rowsum += wj;
+                        cv[j] = wj;
+                    }
+                } else {
+                    const float u = fast_exp2(er);
+                    const float gu = (MODE == DQ) ? g_row * u : 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float tu = (MODE == DQ) ? fmaf(__uint_as_float(tv[j]), u, gu) : __uint_as_float(tv[j]) * u;
+                        const float wj = tu * cv[j];
+                        if (IS_FWD) rowsum += wj;
+                        cv[j] = wj;
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    if constexpr (ABFMT == 1) {
+                        __nv_bfloat162 v2 = __floats2bfloat162_rn(cv[2 * j], cv[2 * j + 1]);
+                        pk[j] = *reinterpret_cast<uint32_t*>(&v2);
+                    } else {
+                        __half2 v2 = __floats2half2_rn(cv[2 * j], cv[2 * j + 1]);
+                        pk[j] = *reinterpret_cast<uint32_t*>(&v2);
+                    }
+                }
+            }
+            GTRACE(t, 2);
+            tmem_st16(t_tmem, pk);
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(lead_w[buf]);
+            GTRACE(t, 3);
+        }
+        if (!ok) break;
+        gstep += nsteps;
+
+        // ---- epilogue: each group drains a quarter of this CTA's accumulator columns
+        ok = mbar_wait_warp<SLACK_SLEEP_NS>(bar_acc, n & 1, abort_flag, WAIT_LIMIT);
+        if (!ok) break;
+        {
+            tc_fence_after();
+            constexpr int QUART = D / NGROUPS;   // 64
+            const int c0 = grp * QUART;
+            const bool row_ok = active && (grow < p.S);
+            // The row partials of the previous item are no longer read by anybody: a thread gets here only after
+            // every gate warp of the pair has finished this item's gate steps, which follow that item's epilogue.
+            const size_t row_off = (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * D;
+            float inv_n = 1.0f;
+            auto exchange = [&](float x) {
+                part[grp * 128 + r] = x;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_part);
+                ok = mbar_wait_warp<SLACK_SLEEP_NS>(bar_part, n & 1, abort_flag, WAIT_LIMIT);
+                return ok ? (part[r] + part[128 + r]) + (part[256 + r] + part[384 + r]) : 0.0f;
+            };
+            if (IS_FWD) {
+                const float bsum = exchange(rowsum);
+                if (ok) {
+                    const float mrow = row_ok ? p.m[static_cast<size_t>(bh) * p.S + grow] : 0.0f;
+                    inv_n = 1.0f / (fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f);
+                    if (grp == 0 && row_ok && p.b_out) p.b_out[static_cast<size_t>(bh) * p.S + grow] = bsum;
+                }
+            }
+            if (!ok) break;
+            float dot = 0.0f;
+            OutT* orow = reinterpret_cast<OutT*>(p.out) + row_off + c0;
+            const InT* ogate_row = (IS_FWD && p.ogate) ? reinterpret_cast<const InT*>(p.ogate) + row_off + c0 : nullptr;
+            const InT* drow = ((MODE == DQ || MODE == DK) && p.dot_src) ? reinterpret_cast<const InT*>(p.dot_src) + row_off + c0
+                                                                        : nullptr;
+#pragma unroll 1
+            for (int ch = 0; ch < QUART / 32; ch++) {
+                uint32_t av[32];
+                tmem_ld32(tmem_ACC + lane_bits + c0 + ch * 32, av);
+                tc_wait_ld();
+                if (ch == QUART / 32 - 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_remote(lead_accfree);
+                }
+                if (row_ok) {
+                    float vals[32];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) vals[j] = __uint_as_float(av[j]) * inv_n;
+                    if (IS_FWD && ogate_row) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) vals[j] *= silu_f(to_f32<InT>(ogate_row[ch * 32 + j]));
+                    }
+                    if ((MODE == DQ || MODE == DK) && drow) {
+#pragma unroll
+                        for (int jv = 0; jv < 4; jv++) {
+                            const uint4 raw = *reinterpret_cast<const uint4*>(drow + ch * 32 + jv * 8);
+                            const InT* ev = reinterpret_cast<const InT*>(&raw);
+#pragma unroll
+                            for (int j = 0; j < 8; j++) dot += vals[jv * 8 + j] * to_f32<InT>(ev[j]);
+                        }
+                    }
+                    if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+                        for (int j4 = 0; j4 < 8; j4++) {
+                            float4 o4 = make_float4(vals[j4 * 4], vals[j4 * 4 + 1], vals[j4 * 4 + 2], vals[j4 * 4 + 3]);
+                            *reinterpret_cast<float4*>(reinterpret_cast<float*>(orow) + ch * 32 + j4 * 4) = o4;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j8 = 0; j8 < 4; j8++) {
+                            uint4 o4;
+                            uint32_t* o32 = reinterpret_cast<uint32_t*>(&o4);
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                OutT lo = from_f32<OutT>(vals[j8 * 8 + 2 * j]);
+                                OutT hi = from_f32<OutT>(vals[j8 * 8 + 2 * j + 1]);
+                                o32[j] = static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&lo)) |
+                                         (static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&hi)) << 16);
+                            }
+                            *reinterpret_cast<uint4*>(orow + ch * 32 + j8 * 8) = o4;
+                        }
+                    }
+                }
+            }
+            if ((MODE == DQ || MODE == DK) && p.dot_out) {
+                const float dsum = exchange(dot);
+                if (ok && grp == 0 && active) p.dot_out[vec_base + grow] = row_ok ? dsum : 0.0f;
+            }
+        }
+        }  // items
+        tc_fence_before();
+    }
+
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.status, misaligned ? 2000 : 3000 + MODE);
+        for (int k = 0; k < 64; k++) __nanosleep(16000);
+        __syncthreads();
+    }
+    cluster_sync_all();   // neither CTA releases shared memory or TMEM the other may still touch
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
+template <int MODE, int ABFMT, typename OutT>
+int launch_pair_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
+    PassParams p = p_in;
+    p.slice_set = tc_slice_set();
+    CUtensorMap mx, myh, mz;
+    int rc;
+    if ((rc = tc_make_map(&mx, p.X, p.BH, p.S, D, in_dtype, false, 128)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map(&myh, p.Y, p.BH, p.S, D, in_dtype, false, 64)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map(&mz, p.Z, p.BH, p.S, D, in_dtype, false, 128)) != MLSTM_OK) return rc;
+    auto kern = mlstm_tc_pass_pair<MODE, ABFMT, OutT>;
+    // per device: shared-memory opt-in and how many pairs can be resident at once
+    static int pairs_resident[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MLSTM_E_CUDA;
+    if (pairs_resident[dev] == 0) {
+        cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (ce != cudaSuccess) {
+            cudaGetLastError();
+            return note_cuda_error(ce, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
+        }
+        const int sms = tc_sm_count();
+        if (sms <= 1) return MLSTM_E_CUDA;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1), 1, 1);
+        cfg.blockDim = dim3(NTHREADS, 1, 1);
+        cfg.dynamicSmemBytes = SMEM_BYTES;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int nclusters = 0;
+        ce = cudaOccupancyMaxActiveClusters(&nclusters, kern, &cfg);
+        if (ce != cudaSuccess || nclusters <= 0) {
+            cudaGetLastError();
+            nclusters = sms / 2;   // the grid does not have to be resident at once: CTAs only wait inside their pair
+        }
+        pairs_resident[dev] = nclusters < sms / 2 ? nclusters : sms / 2;
+    }
+    const int NT = p.Spad / TILE;
+    const long long total = static_cast<long long>((NT + 1) / 2) * p.BH;
+    if (total > 0x3fffffffLL) return MLSTM_E_SHAPE;
+    const unsigned npairs = static_cast<unsigned>(total < pairs_resident[dev] ? total : pairs_resident[dev]);
+    if (!p.sched) return MLSTM_E_ARG;
+    cudaError_t ce = cudaMemsetAsync(p.sched + MODE, 0, sizeof(int), st);
+    if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
+    kern<<<2 * npairs, NTHREADS, SMEM_BYTES, st>>>(mx, myh, mz, p);
+    ce = cudaGetLastError();
+    return ce == cudaSuccess ? MLSTM_OK : note_cuda_error(ce, "launch of mlstm_tc_pass_pair");
+}
+
+template <int MODE>
+int launch_pair_fmt(const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) {
+    if (in_dtype == MLSTM_DT_BF16) {
+        if (out_dtype == MLSTM_DT_F32) return launch_pair_one<MODE, 1, float>(p, in_dtype, st);
+        if (out_dtype == in_dtype) return launch_pair_one<MODE, 1, __nv_bfloat16>(p, in_dtype, st);
+    } else if (in_dtype == MLSTM_DT_F16) {
+        if (out_dtype == MLSTM_DT_F32) return launch_pair_one<MODE, 0, float>(p, in_dtype, st);
+        if (out_dtype == in_dtype) return launch_pair_one<MODE, 0, __half>(p, in_dtype, st);
+    }
+    return MLSTM_E_ARG;
+}
+
+}  // namespace
+
+#ifdef MLSTM_TRACE
+extern "C" int mlstm_debug_trace_pair(long long* out, int n) {
+    return cudaMemcpyFromSymbol(out, g_trace_pair, sizeof(long long) * (n < 1536 ? n : 1536)) == cudaSuccess ? 0 : -1;
+}
+#endif
+
+// 16-bit inputs, head dimension 256, at least two tiles per slice (a single tile has no partner)
+bool tc_pair_supported(int S, int Dh, int in_dtype) {
+    return S > TILE && Dh == 256 && (in_dtype == MLSTM_DT_F16 || in_dtype == MLSTM_DT_BF16);
+}
+
+int launch_pass_tc_pair(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) {
+    if (!tc_pair_supported(p.S, p.D, in_dtype)) return MLSTM_E_UNSUPPORTED;
+    switch (mode) {
+        case FWD: return launch_pair_fmt<FWD>(p, in_dtype, out_dtype, st);
+        case DQ: return launch_pair_fmt<DQ>(p, in_dtype, out_dtype, st);
+        case DK: return launch_pair_fmt<DK>(p, in_dtype, out_dtype, st);
+        case DV: return launch_pair_fmt<DV>(p, in_dtype, out_dtype, st);
+    }
+    return MLSTM_E_UNSUPPORTED;
+}
+
+}  // namespace mlstm
