@@ -37,33 +37,49 @@ constexpr int BOX_BYTES = 128 * 128;           // 128 rows x 128 bytes
 constexpr int HBOX_BYTES = 64 * 128;           // 64 rows x 128 bytes (half of a streamed Y tile's rows)
 constexpr int X_BYTES = (D / 64) * BOX_BYTES;  // 64 KB stationary tile
 constexpr int SLOT_BYTES = 32 * 1024;          // Y half: 64 rows x 256 cols; Z half: 128 rows x 128 cols
-constexpr int NSLOT = 5;
+constexpr int NSLOT = 4;                       // two steps of streamed tiles
+constexpr int STAGE_BYTES = 2048;              // per gate warp: 32 rows x 64 bytes of output on their way to a TMA store
+constexpr int OUT_BYTES = (NGATE / 32) * STAGE_BYTES;
 constexpr int NBAR = 1 + 2 * NSLOT + 2 + 2 + 1 + 1 + 2 + 4;
-constexpr int SMEM_BYTES = X_BYTES + NSLOT * SLOT_BYTES + NBAR * 8 + 64 + NGROUPS * 128 * 4;
+constexpr int SMEM_BYTES = X_BYTES + NSLOT * SLOT_BYTES + OUT_BYTES + NBAR * 8 + 64 + NGROUPS * 128 * 4;
 constexpr long long WAIT_LIMIT = 4000000000LL;
 constexpr int SLACK_SLEEP_NS = 64;              // poll interval of the roles that wait with slack (gate warps, producer)
 static_assert(SMEM_BYTES <= 232448, "exceeds the shared memory of a CTA");
 
 #ifdef MLSTM_TRACE
-__device__ long long g_trace_pair[3 * 64 * 8];   // development aid: leader MMA warp of cluster 0, first item, [step][event]
+// Development aid (not built into the library): clock64() stamps of cluster 0.
+//   [0, 512)      leader MMA warp, item 1, [step][event]
+//   [512, 1536)   gate warp 2 of the leader / follower, item 1, [step][event]; step 60 = epilogue of item 0
+//   [1536, 2048)  leader MMA warp, per item [item][event]
+__device__ long long g_trace_pair[4 * 64 * 8];
 #define PTRACE(step, ev)                                                                                   \
     do {                                                                                                   \
-        if (blockIdx.x == 0 && n == 0 && issuer && (step) < 64) g_trace_pair[(step) * 8 + (ev)] = clock64(); \
+        if (blockIdx.x == 0 && n == 1 && issuer && (step) < 64) g_trace_pair[(step) * 8 + (ev)] = clock64(); \
+    } while (0)
+#define ETRACE(ev)                                                                                         \
+    do {                                                                                                   \
+        if (blockIdx.x < 2 && n == 0 && threadIdx.x == 64) g_trace_pair[(1 + blockIdx.x) * 512 + 60 * 8 + (ev)] = clock64(); \
+    } while (0)
+#define ITRACE(item, ev, val)                                                                              \
+    do {                                                                                                   \
+        if (blockIdx.x == 0 && issuer && (item) < 64) g_trace_pair[1536 + (item) * 8 + (ev)] = (val);      \
     } while (0)
 #define GTRACE(step, ev)                                                                                   \
     do {                                                                                                   \
-        if (blockIdx.x < 2 && n == 0 && threadIdx.x == 64 && (step) < 64)                                  \
+        if (blockIdx.x < 2 && n == 1 && threadIdx.x == 64 && (step) < 60)                                  \
             g_trace_pair[(1 + blockIdx.x) * 512 + (step) * 8 + (ev)] = clock64();                          \
     } while (0)
 #else
 #define PTRACE(step, ev) do { } while (0)
+#define ETRACE(ev) do { } while (0)
+#define ITRACE(item, ev, val) do { } while (0)
 #define GTRACE(step, ev) do { } while (0)
 #endif
 
 template <int MODE, int ABFMT, typename OutT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1)
 mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmYh,
-                   const __grid_constant__ CUtensorMap tmZ, const PassParams p) {
+                   const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmO, const PassParams p) {
     using InT = typename std::conditional<ABFMT == 1, __nv_bfloat16, __half>::type;
     constexpr bool ROWS_ARE_Q = (MODE == FWD || MODE == DQ);
     constexpr bool IS_FWD = (MODE == FWD);
@@ -72,7 +88,8 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     uint8_t* smem = smem_raw;
     uint8_t* sX = smem;
     uint8_t* sSlot = smem + X_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sSlot + NSLOT * SLOT_BYTES);
+    uint8_t* sOut = sSlot + NSLOT * SLOT_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + OUT_BYTES);
     uint64_t* bar_x = bars;                     // leader: both stationary tiles loaded
     uint64_t* bar_full = bars + 1;              // leader: both halves of a slot loaded
     uint64_t* bar_empty = bars + 1 + NSLOT;     // both: slot no longer read by MMAs
@@ -229,7 +246,7 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             constexpr uint32_t idesc2 = make_idesc(ABFMT, 256, 256, 0, 1);
             const uint32_t sX_u = static_cast<uint32_t>(uni(static_cast<int>(smem_u32(sX))));
             const uint32_t sSlot_u = sX_u + X_BYTES;
-            const uint32_t bars_u = sSlot_u + NSLOT * SLOT_BYTES;          // this CTA's barriers ...
+            const uint32_t bars_u = sSlot_u + NSLOT * SLOT_BYTES + OUT_BYTES;   // this CTA's barriers ...
             const uint32_t bars_peer_u = static_cast<uint32_t>(uni(static_cast<int>(at_peer(bars))));   // ... and the peer's
             const uint32_t tmem_T0u = static_cast<uint32_t>(uni(static_cast<int>(tmem_T0)));
             const uint32_t tmem_ACCu = tmem_T0u + 256;
@@ -250,9 +267,12 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                 const int id = uni(item_ids[n & 3]);
                 if (id < 0) break;
                 const Item it = decode(id);
+                ITRACE(n, 0, clock64());
                 ok = wait_u(bar_x, n & 1);
                 if (!ok) break;
                 tc_fence_after();
+                ITRACE(n, 1, clock64());
+                ITRACE(n, 4, it.nsteps);
                 auto second = [&](int u) {  // ACC += W(u) Z(u), both CTAs
                     const int gu = gstep + u;
                     ok = ok && wait_u(&bar_w[gu & 1], (gu >> 1) & 1);
@@ -302,9 +322,11 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                     slot_it++;
                     if (t >= 1) second(t - 1);
                 }
+                ITRACE(n, 2, clock64());
                 if (ok) second(it.nsteps - 1);
                 if (ok && issuer) commit_both(bar_acc);
                 __syncwarp();
+                ITRACE(n, 3, clock64());
                 gstep += it.nsteps;
             }
         }
@@ -326,19 +348,33 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         const uint32_t lead_accfree = at_leader(bar_accfree);
         bool ok = __all_sync(0xffffffffu, *abort_flag == 0) != 0;
         int gstep = 0;
-        for (int n = 0; ok; n++) {
-        const int id = next_item_warp(n, ok);
-        if (id < 0) break;
+        uint8_t* stage = sOut + (warp - 2) * STAGE_BYTES;
+        if (lane == 0) prefetch_tmap(&tmO);
+
+        // row terms of a work item: the row part of the exponent (double) and the DQ additive term
+        auto row_terms = [&](const Item& it, double& er_d, float& g_row) {
+            const int grow = it.tile * TILE + r;
+            const bool active = it.tile < NT;
+            const size_t vec_base = static_cast<size_t>(it.bh) * p.Spad;
+            const size_t ref_base = static_cast<size_t>(it.bh) * (p.Spad / REF_BLOCK);
+            er_d = active ? static_cast<double>(p.row_rel[vec_base + grow]) + p.row_ref[ref_base + grow / REF_BLOCK] +
+                                static_cast<double>(p.er_add)
+                          : 0.0;
+            g_row = (MODE == DQ && active) ? p.row_g[vec_base + grow] : 0.0f;
+        };
+        constexpr int UNKNOWN = -2;
+        int id = next_item_warp(0, ok);
+        double er_d = 0.0;
+        float g_row = 0.0f;
+        if (ok && id >= 0) row_terms(decode(id), er_d, g_row);
+
+        for (int n = 0; ok && id >= 0; n++) {
         const Item it = decode(id);
         const int bh = it.bh, tile = it.tile, nsteps = it.nsteps;
         const bool active = tile < NT;                 // the idle half of an odd last pair only keeps the protocol going
         const int grow = tile * TILE + r;
         const size_t vec_base = static_cast<size_t>(bh) * p.Spad;
         const size_t ref_base = static_cast<size_t>(bh) * (p.Spad / REF_BLOCK);
-        const double er_d = active ? static_cast<double>(p.row_rel[vec_base + grow]) + p.row_ref[ref_base + grow / REF_BLOCK] +
-                                         static_cast<double>(p.er_add)
-                                   : 0.0;
-        const float g_row = (MODE == DQ && active) ? p.row_g[vec_base + grow] : 0.0f;
         float rowsum = 0.0f;
 
         for (int t = 0; t < nsteps; t++) {
@@ -419,36 +455,52 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         if (!ok) break;
         gstep += nsteps;
 
+        // ---- while the last contractions run: everything of the epilogue that does not need the accumulator
+        const bool row_ok = active && (grow < p.S);
+        float inv_n = 1.0f;
+        auto exchange = [&](float x) {   // sum of one value per gate group for this row
+            part[grp * 128 + r] = x;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_part);
+            ok = mbar_wait_warp<SLACK_SLEEP_NS>(bar_part, n & 1, abort_flag, WAIT_LIMIT);
+            return ok ? (part[r] + part[128 + r]) + (part[256 + r] + part[384 + r]) : 0.0f;
+        };
+        auto fwd_norm = [&]() {
+            const float bsum = exchange(rowsum);
+            if (ok) {
+                const float mrow = row_ok ? p.m[static_cast<size_t>(bh) * p.S + grow] : 0.0f;
+                inv_n = 1.0f / (fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f);
+                if (grp == 0 && row_ok && p.b_out) p.b_out[static_cast<size_t>(bh) * p.S + grow] = bsum;
+            }
+        };
+        // The row partials are reused from item to item.  Nobody still reads the previous item's: a warp gets
+        // past step 2 of this item only after every gate warp of the pair has finished step 0 of it (the third
+        // T tile follows the first W tile), which follows its previous epilogue.  Shorter items exchange later.
+        ETRACE(0);
+        if (IS_FWD && nsteps > 2) fwd_norm();
+        if (!ok) break;
+        // next work item, if it is published already, and its row terms
+        int id_next = UNKNOWN;
+        double er_next = 0.0;
+        float g_next = 0.0f;
+        if (__all_sync(0xffffffffu, mbar_test_wait_cluster(&bar_item[(n + 1) & 3], ((n + 1) >> 2) & 1) ? 1 : 0)) {
+            id_next = __shfl_sync(0xffffffffu, item_ids[(n + 1) & 3], 0);
+            if (id_next >= 0) row_terms(decode(id_next), er_next, g_next);
+        }
+
         // ---- epilogue: each group drains a quarter of this CTA's accumulator columns
         ok = mbar_wait_warp<SLACK_SLEEP_NS>(bar_acc, n & 1, abort_flag, WAIT_LIMIT);
         if (!ok) break;
+        ETRACE(1);
         {
             tc_fence_after();
             constexpr int QUART = D / NGROUPS;   // 64
             const int c0 = grp * QUART;
-            const bool row_ok = active && (grow < p.S);
-            // The row partials of the previous item are no longer read by anybody: a thread gets here only after
-            // every gate warp of the pair has finished this item's gate steps, which follow that item's epilogue.
             const size_t row_off = (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * D;
-            float inv_n = 1.0f;
-            auto exchange = [&](float x) {
-                part[grp * 128 + r] = x;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_part);
-                ok = mbar_wait_warp<SLACK_SLEEP_NS>(bar_part, n & 1, abort_flag, WAIT_LIMIT);
-                return ok ? (part[r] + part[128 + r]) + (part[256 + r] + part[384 + r]) : 0.0f;
-            };
-            if (IS_FWD) {
-                const float bsum = exchange(rowsum);
-                if (ok) {
-                    const float mrow = row_ok ? p.m[static_cast<size_t>(bh) * p.S + grow] : 0.0f;
-                    inv_n = 1.0f / (fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f);
-                    if (grp == 0 && row_ok && p.b_out) p.b_out[static_cast<size_t>(bh) * p.S + grow] = bsum;
-                }
-            }
+            if (IS_FWD && nsteps <= 2) fwd_norm();
             if (!ok) break;
+            ETRACE(2);
             float dot = 0.0f;
-            OutT* orow = reinterpret_cast<OutT*>(p.out) + row_off + c0;
             const InT* ogate_row = (IS_FWD && p.ogate) ? reinterpret_cast<const InT*>(p.ogate) + row_off + c0 : nullptr;
             const InT* drow = ((MODE == DQ || MODE == DK) && p.dot_src) ? reinterpret_cast<const InT*>(p.dot_src) + row_off + c0
                                                                         : nullptr;
@@ -457,15 +509,17 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                 uint32_t av[32];
                 tmem_ld32(tmem_ACC + lane_bits + c0 + ch * 32, av);
                 tc_wait_ld();
+                if (ch == 0) ETRACE(5);
                 if (ch == QUART / 32 - 1) {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_remote(lead_accfree);
+                    ETRACE(3);
                 }
-                if (row_ok) {
-                    float vals[32];
+                float vals[32];
 #pragma unroll
-                    for (int j = 0; j < 32; j++) vals[j] = __uint_as_float(av[j]) * inv_n;
+                for (int j = 0; j < 32; j++) vals[j] = __uint_as_float(av[j]) * inv_n;
+                if (row_ok) {
                     if (IS_FWD && ogate_row) {
 #pragma unroll
                         for (int j = 0; j < 32; j++) vals[j] *= silu_f(to_f32<InT>(ogate_row[ch * 32 + j]));
@@ -479,35 +533,63 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                             for (int j = 0; j < 8; j++) dot += vals[jv * 8 + j] * to_f32<InT>(ev[j]);
                         }
                     }
+                }
+                // This warp's 32 rows x 32 columns go out through its staging buffer and a TMA store (rows past
+                // the end of the slice are not written): scattered 16-byte stores from registers took several
+                // thousand cycles per item during which the tensor pipe had nothing to do.
+                constexpr int NSUB = sizeof(OutT) == 4 ? 2 : 1;    // 64 bytes per row and store
+#pragma unroll
+                for (int sub = 0; sub < NSUB; sub++) {
+                    if (lane == 0) bulk_wait_read_all();   // the previous store has read the buffer
+                    __syncwarp();
+                    if (ch == 0 && sub == 0) ETRACE(6);
+                    uint4* srow = reinterpret_cast<uint4*>(stage + lane * 64);
                     if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
-                        for (int j4 = 0; j4 < 8; j4++) {
-                            float4 o4 = make_float4(vals[j4 * 4], vals[j4 * 4 + 1], vals[j4 * 4 + 2], vals[j4 * 4 + 3]);
-                            *reinterpret_cast<float4*>(reinterpret_cast<float*>(orow) + ch * 32 + j4 * 4) = o4;
-                        }
+                        for (int j4 = 0; j4 < 4; j4++)
+                            srow[j4] = make_uint4(__float_as_uint(vals[sub * 16 + j4 * 4]), __float_as_uint(vals[sub * 16 + j4 * 4 + 1]),
+                                                  __float_as_uint(vals[sub * 16 + j4 * 4 + 2]), __float_as_uint(vals[sub * 16 + j4 * 4 + 3]));
                     } else {
 #pragma unroll
-                        for (int j8 = 0; j8 < 4; j8++) {
-                            uint4 o4;
-                            uint32_t* o32 = reinterpret_cast<uint32_t*>(&o4);
+                        for (int j4 = 0; j4 < 4; j4++) {
+                            uint32_t o32[4];
 #pragma unroll
                             for (int j = 0; j < 4; j++) {
-                                OutT lo = from_f32<OutT>(vals[j8 * 8 + 2 * j]);
-                                OutT hi = from_f32<OutT>(vals[j8 * 8 + 2 * j + 1]);
+                                OutT lo = from_f32<OutT>(vals[j4 * 8 + 2 * j]);
+                                OutT hi = from_f32<OutT>(vals[j4 * 8 + 2 * j + 1]);
                                 o32[j] = static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&lo)) |
                                          (static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&hi)) << 16);
                             }
-                            *reinterpret_cast<uint4*>(orow + ch * 32 + j8 * 8) = o4;
+                            srow[j4] = make_uint4(o32[0], o32[1], o32[2], o32[3]);
                         }
                     }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && active) {
+                        tma_store_3d(&tmO, stage, c0 + ch * 32 + sub * (64 / static_cast<int>(sizeof(OutT))),
+                                     tile * TILE + (warp & 3) * 32, bh);
+                        bulk_commit();
+                    }
+                    if (ch == 0 && sub == 0) ETRACE(7);
                 }
             }
+            ETRACE(4);
             if ((MODE == DQ || MODE == DK) && p.dot_out) {
                 const float dsum = exchange(dot);
                 if (ok && grp == 0 && active) p.dot_out[vec_base + grow] = row_ok ? dsum : 0.0f;
             }
         }
+        if (!ok) break;
+        // ---- on to the next item
+        if (id_next == UNKNOWN) {
+            id_next = next_item_warp(n + 1, ok);
+            if (ok && id_next >= 0) row_terms(decode(id_next), er_next, g_next);
+        }
+        id = id_next;
+        er_d = er_next;
+        g_row = g_next;
         }  // items
+        if (lane == 0) bulk_wait_all();   // the last stores have left shared memory before the CTA goes away
         tc_fence_before();
     }
 
@@ -528,8 +610,10 @@ template <int MODE, int ABFMT, typename OutT>
 int launch_pair_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
     PassParams p = p_in;
     p.slice_set = tc_slice_set();
-    CUtensorMap mx, myh, mz;
+    CUtensorMap mx, myh, mz, mo;
     int rc;
+    constexpr int out_dtype = sizeof(OutT) == 4 ? MLSTM_DT_F32 : (ABFMT == 1 ? MLSTM_DT_BF16 : MLSTM_DT_F16);
+    if ((rc = tc_make_map_plain(&mo, p.out, p.BH, p.S, D, out_dtype, 64 / static_cast<int>(sizeof(OutT)), 32)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map(&mx, p.X, p.BH, p.S, D, in_dtype, false, 128)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map(&myh, p.Y, p.BH, p.S, D, in_dtype, false, 64)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map(&mz, p.Z, p.BH, p.S, D, in_dtype, false, 128)) != MLSTM_OK) return rc;
@@ -572,7 +656,7 @@ int launch_pair_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
     if (!p.sched) return MLSTM_E_ARG;
     cudaError_t ce = cudaMemsetAsync(p.sched + MODE, 0, sizeof(int), st);
     if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
-    kern<<<2 * npairs, NTHREADS, SMEM_BYTES, st>>>(mx, myh, mz, p);
+    kern<<<2 * npairs, NTHREADS, SMEM_BYTES, st>>>(mx, myh, mz, mo, p);
     ce = cudaGetLastError();
     return ce == cudaSuccess ? MLSTM_OK : note_cuda_error(ce, "launch of mlstm_tc_pass_pair");
 }
@@ -593,7 +677,7 @@ int launch_pair_fmt(const PassParams& p, int in_dtype, int out_dtype, cudaStream
 
 #ifdef MLSTM_TRACE
 extern "C" int mlstm_debug_trace_pair(long long* out, int n) {
-    return cudaMemcpyFromSymbol(out, g_trace_pair, sizeof(long long) * (n < 1536 ? n : 1536)) == cudaSuccess ? 0 : -1;
+    return cudaMemcpyFromSymbol(out, g_trace_pair, sizeof(long long) * (n < 2048 ? n : 2048)) == cudaSuccess ? 0 : -1;
 }
 #endif
 
