@@ -854,19 +854,19 @@ int tc_make_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int 
     return make_map(map, base, N2, N1, N0, dtype, atom32, box_rows);
 }
 
-int tc_make_map_plain(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, int box_cols, int box_rows) {
+int tc_make_map_out(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, int box_rows) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return MLSTM_E_CUDA;
     const cuuint64_t es = dtype == MLSTM_DT_F32 ? 4 : 2;
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(N0), static_cast<cuuint64_t>(N1), static_cast<cuuint64_t>(N2)};
     cuuint64_t strides[2] = {static_cast<cuuint64_t>(N0) * es, static_cast<cuuint64_t>(N1) * N0 * es};
-    cuuint32_t box[3] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows), 1};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(64 / es), static_cast<cuuint32_t>(box_rows), 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUtensorMapDataType dt = dtype == MLSTM_DT_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                              : dtype == MLSTM_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                       : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? MLSTM_OK : MLSTM_E_CUDA;
 }
 

@@ -544,26 +544,36 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                     __syncwarp();
                     if (ch == 0 && sub == 0) ETRACE(6);
                     uint4* srow = reinterpret_cast<uint4*>(stage + lane * 64);
+                    const int sw = (lane >> 1) & 3;   // 64-byte swizzle of the store's tensor map: no bank conflicts
                     if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
                         for (int j4 = 0; j4 < 4; j4++)
-                            srow[j4] = make_uint4(__float_as_uint(vals[sub * 16 + j4 * 4]), __float_as_uint(vals[sub * 16 + j4 * 4 + 1]),
+                            srow[j4 ^ sw] = make_uint4(__float_as_uint(vals[sub * 16 + j4 * 4]), __float_as_uint(vals[sub * 16 + j4 * 4 + 1]),
                                                   __float_as_uint(vals[sub * 16 + j4 * 4 + 2]), __float_as_uint(vals[sub * 16 + j4 * 4 + 3]));
                     } else {
 #pragma unroll
                         for (int j4 = 0; j4 < 4; j4++) {
                             uint32_t o32[4];
 #pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                OutT lo = from_f32<OutT>(vals[j4 * 8 + 2 * j]);
-                                OutT hi = from_f32<OutT>(vals[j4 * 8 + 2 * j + 1]);
-                                o32[j] = static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&lo)) |
-                                         (static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&hi)) << 16);
+                            for (int j = 0; j < 4; j++) {   // two values per conversion
+                                if constexpr (ABFMT == 1) {
+                                    __nv_bfloat162 v2 = __floats2bfloat162_rn(vals[j4 * 8 + 2 * j], vals[j4 * 8 + 2 * j + 1]);
+                                    o32[j] = *reinterpret_cast<uint32_t*>(&v2);
+                                } else {
+                                    __half2 v2 = __floats2half2_rn(vals[j4 * 8 + 2 * j], vals[j4 * 8 + 2 * j + 1]);
+                                    o32[j] = *reinterpret_cast<uint32_t*>(&v2);
+                                }
                             }
-                            srow[j4] = make_uint4(o32[0], o32[1], o32[2], o32[3]);
+                            srow[j4 ^ sw] = make_uint4(o32[0], o32[1], o32[2], o32[3]);
                         }
                     }
+#ifdef MLSTM_TRACE
+                    if (ch == 0 && sub == 0) ETRACE(6);   // after the shared-memory writes
                     fence_async_smem();
+                    if (ch == 0 && sub == 0) ETRACE(5);   // after the proxy fence
+#else
+                    fence_async_smem();
+#endif
                     __syncwarp();
                     if (lane == 0 && active) {
                         tma_store_3d(&tmO, stage, c0 + ch * 32 + sub * (64 / static_cast<int>(sizeof(OutT))),
@@ -613,7 +623,7 @@ int launch_pair_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
     CUtensorMap mx, myh, mz, mo;
     int rc;
     constexpr int out_dtype = sizeof(OutT) == 4 ? MLSTM_DT_F32 : (ABFMT == 1 ? MLSTM_DT_BF16 : MLSTM_DT_F16);
-    if ((rc = tc_make_map_plain(&mo, p.out, p.BH, p.S, D, out_dtype, 64 / static_cast<int>(sizeof(OutT)), 32)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map_out(&mo, p.out, p.BH, p.S, D, out_dtype, 32)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map(&mx, p.X, p.BH, p.S, D, in_dtype, false, 128)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map(&myh, p.Y, p.BH, p.S, D, in_dtype, false, 64)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map(&mz, p.Z, p.BH, p.S, D, in_dtype, false, 128)) != MLSTM_OK) return rc;

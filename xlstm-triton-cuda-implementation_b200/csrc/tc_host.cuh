@@ -10,8 +10,10 @@ namespace mlstm {
 // Tensor map of a [N2, N1, N0] tensor (N0 contiguous): boxes of 128 bytes x box_rows rows, 128-byte
 // swizzle (with 32-byte atoms if atom32), zero fill outside the tensor.
 int tc_make_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, bool atom32, int box_rows);
-// Same tensor, dense boxes of box_cols x box_rows elements without swizzle (TMA stores of output tiles).
-int tc_make_map_plain(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, int box_cols, int box_rows);
+// Same tensor for TMA stores of output tiles: boxes of 64 bytes x box_rows rows with the 64-byte swizzle
+// (in shared memory the 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3) of that row; the buffer
+// is 512-byte aligned).
+int tc_make_map_out(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, int box_rows);
 int tc_sm_count();    // SMs of the current device (cached), -1 on error
 int tc_slice_set();   // slices interleaved in the work-item order (MLSTM_SLICE_SET overrides the default)
 
