@@ -77,7 +77,12 @@ struct TcCfg {
     static constexpr int NHALF = D / CH;                      // slots per streamed tile
     static constexpr int SLOT_BYTES = (CH / EPB) * BOX_BYTES;
     static constexpr int X_BYTES = (D / EPB) * BOX_BYTES;
-    static constexpr int NSLOT = ES == 2 ? (D == 256 ? 5 : (D == 128 ? 6 : 8)) : (D == 256 ? 3 : (D == 128 ? 5 : 6));
+    // Output tiles leave through per-warp staging buffers and TMA stores where shared memory has room for them
+    // and a warp's share of a row is 64 bytes or a multiple (16-bit inputs, D = 128); elsewhere from registers.
+    static constexpr bool STAGED = (ES == 2 && D == 128);
+    static constexpr int STAGE_BYTES = 2048;                  // per gate warp: 32 rows x 64 bytes
+    static constexpr int OUT_BYTES = STAGED ? (NGATE / 32) * STAGE_BYTES : 0;
+    static constexpr int NSLOT = ES == 2 ? (D == 256 ? 5 : (D == 128 ? 5 : 8)) : (D == 256 ? 3 : (D == 128 ? 5 : 6));
     // Streamed tiles are signalled in units of UH slots (a whole tile unless it has more than two slots):
     // one "loaded" and one "consumed" barrier per unit, in rings of RING.
     static constexpr int UH = NHALF <= 2 ? NHALF : 2;
@@ -86,13 +91,13 @@ struct TcCfg {
     static_assert(NSLOT / UH <= RING && NSLOT > UH, "barrier ring too small / unit larger than the slot ring");
     static constexpr int NBAR = 1 + 2 * RING + 2 + 1 + 1 + 1 + 1 + 4;  // x, unit full/consumed, w[2], acc, part, xfree, accfree, item[4]
     // the tiles start at the (1024-byte aligned, checked at run time) base of the dynamic shared memory
-    static constexpr int SMEM_BYTES = X_BYTES + NSLOT * SLOT_BYTES + NBAR * 8 + 64 + NGROUPS * 128 * 4 /*row partials*/;
+    static constexpr int BASE_BYTES = X_BYTES + NSLOT * SLOT_BYTES + OUT_BYTES + NBAR * 8 + 64;
+    // row partials [NGROUPS][128], twice (alternating from item to item) where there is room
+    static constexpr int PARTS = (BASE_BYTES + 2 * NGROUPS * 128 * 4 <= 232448) ? 2 : 1;
+    static constexpr int SMEM_BYTES = BASE_BYTES + PARTS * NGROUPS * 128 * 4;
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA may have");
 };
 
-struct SmemTail {  // lives after the tiles
-    float part[NGROUPS][128];  // [gate group][row]: row sums in FWD / STATE, row dots in DQ / DK
-};
 
 __device__ __forceinline__ uint32_t to_tf32(float x) {
     uint32_t y;
@@ -105,7 +110,7 @@ template <int MODE, int D, int ABFMT, typename OutT, bool SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
               const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmI,
-              const __grid_constant__ CUtensorMap tmS, const PassParams p) {
+              const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmO, const PassParams p) {
     constexpr int ES = ABFMT == 2 ? 4 : 2;
     constexpr bool TF32 = ABFMT == 2;
     using C = TcCfg<D, ES>;
@@ -124,7 +129,8 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     }
     uint8_t* sX = smem;
     uint8_t* sSlot = smem + C::X_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sSlot + C::NSLOT * C::SLOT_BYTES);
+    uint8_t* sOut = sSlot + C::NSLOT * C::SLOT_BYTES;   // staging for TMA stores (C::OUT_BYTES, may be empty)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + C::OUT_BYTES);
     uint64_t* bar_x = bars;
     uint64_t* bar_full = bars + 1;              // [RING] unit loaded
     uint64_t* bar_cons = bars + 1 + C::RING;    // [RING] unit consumed: every MMA that reads it has completed.  For the
@@ -138,7 +144,9 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* item_ids = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [4] ring of published work items
-    SmemTail* tail = reinterpret_cast<SmemTail*>(reinterpret_cast<uint8_t*>(bars) + C::NBAR * 8 + 64);
+    // [PARTS][NGROUPS][128]: row sums in FWD / STATE, row dots in DQ / DK, one value per gate group and row
+    float* part_base = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + C::NBAR * 8 + 64);
+    constexpr bool STAGED = C::STAGED && !SPLIT;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -464,24 +472,36 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         };
         bool ok = true;
         int gstep = 0;
-        for (int n = 0; ok; n++) {
-        const int id = next_item(n, ok);
-        if (id < 0) break;
+        [[maybe_unused]] uint8_t* stage = sOut + (warp - 2) * C::STAGE_BYTES;
+        if (STAGED && lane == 0) prefetch_tmap(&tmO);
+        // row terms of a work item: the row part of the exponent in double (the column block's reference is added
+        // per block; STATE: rows are key dimensions and every row carries the block-end stabiliser), the weight of
+        // the inbound-state step of FWDC (exp(A_prev_block_end - A_row) / sqrt(D); -inf when there is no carry)
+        // and the additive term of DQ
+        auto row_terms = [&](const Item& it, double& er_d, float& er_state, float& g_row) {
+            const int grow = it.tile * TILE + r;
+            const size_t vec_base = static_cast<size_t>(it.bh) * p.Spad;
+            const size_t ref_base = static_cast<size_t>(it.bh) * (p.Spad / REF_BLOCK);
+            const double* bound =
+                (MODE == FWDC || MODE == STATE) ? p.An_bound + static_cast<size_t>(it.bh) * (p.NB + 1) + it.blk : nullptr;
+            er_d = (MODE == STATE) ? bound[1]
+                                   : static_cast<double>(p.row_rel[vec_base + grow]) + p.row_ref[ref_base + grow / REF_BLOCK] +
+                                         static_cast<double>(p.er_add);
+            er_state = (MODE == FWDC) ? static_cast<float>(er_d - bound[0]) : 0.0f;
+            g_row = (MODE == DQ) ? p.row_g[vec_base + grow] : 0.0f;
+        };
+        constexpr int UNKNOWN = -2;
+        int id = next_item(0, ok);
+        double er_d = 0.0;
+        float er_state = 0.0f, g_row = 0.0f;
+        if (ok && id >= 0) row_terms(decode(id), er_d, er_state, g_row);
+
+        for (int n = 0; ok && id >= 0; n++) {
         const Item it = decode(id);
         const int bh = it.bh, tile = it.tile, blk = it.blk, nsteps = it.nsteps, zv0 = it.zv0, vslice = it.vslice;
         const int grow = tile * TILE + r;              // row inside the slice (may be >= S in the last tile)
         const size_t vec_base = static_cast<size_t>(bh) * p.Spad;
         const size_t ref_base = static_cast<size_t>(bh) * (p.Spad / REF_BLOCK);
-        // row part of the exponent in double; the column block's reference is added per block
-        // (STATE: rows are key dimensions; every row carries the block-end stabiliser)
-        const double* bound = (MODE == FWDC || MODE == STATE) ? p.An_bound + static_cast<size_t>(bh) * (p.NB + 1) + blk : nullptr;
-        const double er_d = (MODE == STATE)
-                                ? bound[1]
-                                : static_cast<double>(p.row_rel[vec_base + grow]) + p.row_ref[ref_base + grow / REF_BLOCK] +
-                                      static_cast<double>(p.er_add);
-        // inbound-state step of FWDC: weight exp(A_prev_block_end - A_row) / sqrt(D); -inf when there is no carry
-        const float er_state = (MODE == FWDC) ? static_cast<float>(er_d - bound[0]) : 0.0f;
-        const float g_row = (MODE == DQ) ? p.row_g[vec_base + grow] : 0.0f;
         float rowsum = 0.0f;
 
         for (int t = 0; t < nsteps; t++) {
@@ -586,31 +606,22 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         if (!ok) break;
         gstep += nsteps;
 
-        // ---- epilogue: each group drains a quarter of the accumulator's columns for all 128 rows
-        ok = mbar_wait_warp<SLACK_SLEEP_NS>(bar_acc, n & 1, abort_flag, WAIT_LIMIT);
-        if (!ok) break;
-        {
-            tc_fence_after();
-            constexpr int QUART = D / NGROUPS;             // 16, 32 or 64 columns
-            constexpr int CW = QUART < 32 ? QUART : 32;    // columns per TMEM load
-            constexpr int VEC = 16 / sizeof(InT);          // input elements per 16-byte access
-            const int c0 = grp * QUART;
-            const bool row_ok = (MODE == STATE) ? true : (grow < p.S);
-            float* part = tail->part[0];                   // [NGROUPS][128]
-            // The row partials of the previous item are no longer read by anybody: a thread gets here only after
-            // every gate warp has finished this item's gate steps, which follow that item's epilogue.
-            // STATE writes block (bh, blk) of [BH, NB, D, D]; everything else row `grow` of [BH, S, Dfull]
-            const size_t row_off = (MODE == STATE)
-                                       ? ((static_cast<size_t>(bh) * p.NB + blk) * D + r) * D
-                                       : (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * Dfull + zv0;
-            float inv_n = 1.0f;
-            auto exchange = [&](float x) {   // sum of one value per gate group for this row
-                part[grp * 128 + r] = x;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_part);
-                ok = mbar_wait_warp<SLACK_SLEEP_NS>(bar_part, n & 1, abort_flag, WAIT_LIMIT);
-                return ok ? (part[r] + part[128 + r]) + (part[256 + r] + part[384 + r]) : 0.0f;
-            };
+        // ---- while the last contractions run: everything of the epilogue that does not need the accumulator
+        constexpr int QUART = D / NGROUPS;             // 16, 32 or 64 columns
+        constexpr int CW = QUART < 32 ? QUART : 32;    // columns per TMEM load
+        constexpr int VEC = 16 / sizeof(InT);          // input elements per 16-byte access
+        const int c0 = grp * QUART;
+        const bool row_ok = (MODE == STATE) ? true : (grow < p.S);
+        float* part = part_base + (C::PARTS == 2 ? (n & 1) * NGROUPS * 128 : 0);
+        float inv_n = 1.0f;
+        auto exchange = [&](float x) {   // sum of one value per gate group for this row (once per item)
+            part[grp * 128 + r] = x;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_part);
+            ok = mbar_wait_warp<SLACK_SLEEP_NS>(bar_part, n & 1, abort_flag, WAIT_LIMIT);
+            return ok ? (part[r] + part[128 + r]) + (part[256 + r] + part[384 + r]) : 0.0f;
+        };
+        auto row_sums = [&]() {
             if (MODE == STATE) {
                 const float zsum = exchange(rowsum);
                 if (ok && grp == 0 && p.b_out) p.b_out[(static_cast<size_t>(bh) * p.NB + blk) * D + r] = zsum;
@@ -629,7 +640,36 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     }
                 }
             }
+        };
+        // When may the row partials be written?  Once nobody reads the ones written two items ago (alternating
+        // buffers) resp. by the previous item (one buffer).  A warp is past this item's gate steps only after the
+        // previous item's accumulator was complete, i.e. after every warp had done that item's gate steps and with
+        // them its epilogue before: two items back is always safe.  With one buffer it is safe here only if this
+        // item has more than two steps (the third T tile follows the first W tile, which needs every warp), else
+        // after the accumulator wait (which needs every warp's last W tile of this item).
+        const bool sums_early = (C::PARTS == 2) || nsteps > 2;
+        if (sums_early) row_sums();
+        if (!ok) break;
+        // next work item, if it is published already, and its row terms
+        int id_next = UNKNOWN;
+        double er_next = 0.0;
+        float es_next = 0.0f, g_next = 0.0f;
+        if (__all_sync(0xffffffffu, mbar_test_wait(&bar_item[(n + 1) & 3], ((n + 1) >> 2) & 1) ? 1 : 0)) {
+            id_next = __shfl_sync(0xffffffffu, item_ids[(n + 1) & 3], 0);
+            if (id_next >= 0) row_terms(decode(id_next), er_next, es_next, g_next);
+        }
+
+        // ---- epilogue: each group drains a quarter of the accumulator's columns for all 128 rows
+        ok = mbar_wait_warp<SLACK_SLEEP_NS>(bar_acc, n & 1, abort_flag, WAIT_LIMIT);
+        if (!ok) break;
+        {
+            tc_fence_after();
+            if (!sums_early) row_sums();
             if (!ok) break;
+            // STATE writes block (bh, blk) of [BH, NB, D, D]; everything else row `grow` of [BH, S, Dfull]
+            const size_t row_off = (MODE == STATE)
+                                       ? ((static_cast<size_t>(bh) * p.NB + blk) * D + r) * D
+                                       : (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * Dfull + zv0;
             float dot = 0.0f;
             OutT* orow = reinterpret_cast<OutT*>(p.out) + row_off + c0;
             const InT* ogate_row = (IS_FWD && !SPLIT && p.ogate) ? reinterpret_cast<const InT*>(p.ogate) + row_off + c0 : nullptr;
@@ -650,10 +690,10 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_accfree);
                 }
-                if (row_ok) {
-                    float vals[CW];
+                float vals[CW];
 #pragma unroll
-                    for (int j = 0; j < CW; j++) vals[j] = __uint_as_float(av[j]) * inv_n;
+                for (int j = 0; j < CW; j++) vals[j] = __uint_as_float(av[j]) * inv_n;
+                if (row_ok) {
                     if (IS_FWD && ogate_row) {
 #pragma unroll
                         for (int j = 0; j < CW; j++) vals[j] *= silu_f(to_f32<InT>(ogate_row[ch * CW + j]));
@@ -667,6 +707,52 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                             for (int j = 0; j < VEC; j++) dot += vals[jv * VEC + j] * to_f32<InT>(ev[j]);
                         }
                     }
+                }
+                if constexpr (STAGED) {
+                    // This warp's 32 rows x 32 columns go out through its staging buffer (64-byte swizzle: no bank
+                    // conflicts) and a TMA store; rows past the end of the tensor are not written.  Scattered
+                    // stores from registers, one row per thread, keep the gate warps busy for thousands of cycles
+                    // per item, during which the tensor pipe has nothing to do.
+                    static_assert(CW == 32, "staged output is built for 32-column chunks");
+                    constexpr int NSUB = sizeof(OutT) == 4 ? 2 : 1;    // 64 bytes per row and store
+#pragma unroll
+                    for (int sub = 0; sub < NSUB; sub++) {
+                        if (lane == 0) bulk_wait_read_all();   // the previous store has read the buffer
+                        __syncwarp();
+                        uint4* srow = reinterpret_cast<uint4*>(stage + lane * 64);
+                        const int sw = (lane >> 1) & 3;
+                        if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+                            for (int j4 = 0; j4 < 4; j4++)
+                                srow[j4 ^ sw] = make_uint4(__float_as_uint(vals[sub * 16 + j4 * 4]), __float_as_uint(vals[sub * 16 + j4 * 4 + 1]),
+                                                           __float_as_uint(vals[sub * 16 + j4 * 4 + 2]), __float_as_uint(vals[sub * 16 + j4 * 4 + 3]));
+                        } else {
+#pragma unroll
+                            for (int j4 = 0; j4 < 4; j4++) {
+                                uint32_t o32[4];
+#pragma unroll
+                                for (int j = 0; j < 4; j++) {   // two values per conversion
+                                    if constexpr (ABFMT == 1) {
+                                        __nv_bfloat162 v2 = __floats2bfloat162_rn(vals[j4 * 8 + 2 * j], vals[j4 * 8 + 2 * j + 1]);
+                                        o32[j] = *reinterpret_cast<uint32_t*>(&v2);
+                                    } else {
+                                        __half2 v2 = __floats2half2_rn(vals[j4 * 8 + 2 * j], vals[j4 * 8 + 2 * j + 1]);
+                                        o32[j] = *reinterpret_cast<uint32_t*>(&v2);
+                                    }
+                                }
+                                srow[j4 ^ sw] = make_uint4(o32[0], o32[1], o32[2], o32[3]);
+                            }
+                        }
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            const int x = c0 + ch * 32 + sub * (64 / static_cast<int>(sizeof(OutT)));
+                            if (MODE == STATE) tma_store_3d(&tmO, stage, x, (warp & 3) * 32, bh * p.NB + blk);
+                            else tma_store_3d(&tmO, stage, zv0 + x, tile * TILE + (warp & 3) * 32, bh);
+                            bulk_commit();
+                        }
+                    }
+                } else if (row_ok) {
                     if constexpr (SPLIT) {
 #pragma unroll
                         for (int j4 = 0; j4 < CW / 4; j4++) {
@@ -701,7 +787,18 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 if (ok && grp == 0) p.dot_out[vec_base + grow] = row_ok ? dsum : 0.0f;
             }
         }
+        if (!ok) break;
+        // ---- on to the next item
+        if (id_next == UNKNOWN) {
+            id_next = next_item(n + 1, ok);
+            if (ok && id_next >= 0) row_terms(decode(id_next), er_next, es_next, g_next);
+        }
+        id = id_next;
+        er_d = er_next;
+        er_state = es_next;
+        g_row = g_next;
         }  // items
+        if (STAGED && lane == 0) bulk_wait_all();   // the last stores have left shared memory before the CTA goes away
         tc_fence_before();
     }
 
@@ -771,7 +868,7 @@ template <int MODE, int D, int ABFMT, typename OutT, bool SPLIT>
 int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
     PassParams p = p_in;
     p.slice_set = tc_slice_set();
-    CUtensorMap mx, my, mz, mi, ms;
+    CUtensorMap mx, my, mz, mi, ms, mo;
     int rc;
     const int Dfull = SPLIT ? p.Dfull : D;
     if (SPLIT && (Dfull <= 0 || Dfull % D != 0)) return MLSTM_E_SHAPE;
@@ -787,6 +884,13 @@ int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
     if (MODE == FWDC) {
         if (!p.states || !p.zstate) return MLSTM_E_ARG;
         if ((rc = make_map(&ms, p.states, p.BH * p.NB, D, D, in_dtype)) != MLSTM_OK) return rc;
+    }
+    mo = mx;
+    if (TcCfg<D, ABFMT == 2 ? 4 : 2>::STAGED && !SPLIT) {
+        constexpr int out_dtype = sizeof(OutT) == 4 ? MLSTM_DT_F32 : (ABFMT == 1 ? MLSTM_DT_BF16 : MLSTM_DT_F16);
+        if (MODE == STATE) rc = tc_make_map_out(&mo, p.out, p.BH * p.NB, D, D, out_dtype, 32);
+        else rc = tc_make_map_out(&mo, p.out, p.BH, p.S, D, out_dtype, 32);
+        if (rc != MLSTM_OK) return rc;
     }
     auto kern = mlstm_tc_pass<MODE, D, ABFMT, OutT, SPLIT>;
     constexpr int smem = TcCfg<D, ABFMT == 2 ? 4 : 2>::SMEM_BYTES;
@@ -805,7 +909,7 @@ int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
     if (!p.sched) return MLSTM_E_ARG;
     ce = cudaMemsetAsync(p.sched + MODE, 0, sizeof(int), st);  // this pass's item counter
     if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
-    kern<<<grid, NTHREADS, smem, st>>>(mx, my, mz, mi, ms, p);
+    kern<<<grid, NTHREADS, smem, st>>>(mx, my, mz, mi, ms, mo, p);
     ce = cudaGetLastError();
     return ce == cudaSuccess ? MLSTM_OK : note_cuda_error(ce, "launch of mlstm_tc_pass");
 }
