@@ -188,52 +188,78 @@ __global__ void gates_fold_kernel(const double* __restrict__ local, const double
 // (db = sign(b) * (-delta / n) * [|b| > exp(-m)], mlstm_matmul.py:194-196 with the sum replaced by
 // n*delta).  Optionally writes dh converted to the 16-bit input type for the tensor-core passes.
 // Rows are read with 16-byte accesses.  Padding rows: gB_rel = -inf, g = 0.
+constexpr int PREP_ROWS = 4;   // positions per warp in bwd_prep_kernel
+
 template <typename HT, typename T16>
 __global__ void bwd_prep_kernel(const HT* __restrict__ h, const HT* __restrict__ dh, const float* __restrict__ b,
                                 const float* __restrict__ m, const float* __restrict__ gAn_rel,
                                 float* __restrict__ gB_rel, float* __restrict__ gB_w, float* __restrict__ g,
                                 T16* __restrict__ dh16, int BH, int S, int Spad, int D, float log2_scale) {
+    // A warp takes PREP_ROWS consecutive positions of one slice (Spad is a multiple of 128): all of their row
+    // loads and the per-position scalars are requested before anything is used, so a warp pays the memory
+    // latency once instead of twice per position.
     constexpr int VEC = 16 / sizeof(HT);
     const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
-    if (warp_global >= BH * Spad) return;
-    const int bh = warp_global / Spad, t = warp_global % Spad;
-    if (t >= S) {
-        if (lane == 0) {
-            gB_rel[warp_global] = -INFINITY;
-            gB_w[warp_global] = 0.0f;
-            g[warp_global] = 0.0f;
-        }
-        return;
+    const long long first = static_cast<long long>(warp_global) * PREP_ROWS;
+    if (first >= static_cast<long long>(BH) * Spad) return;
+    const int bh = static_cast<int>(first / Spad), t0 = static_cast<int>(first % Spad);
+    // lane r < PREP_ROWS finishes position t0 + r
+    const int tl = t0 + lane;
+    const bool mine = lane < PREP_ROWS;
+    const bool mine_valid = mine && tl < S;
+    float bb = 0.0f, mm = 0.0f, ga = 0.0f;
+    if (mine_valid) {
+        const size_t idx = static_cast<size_t>(bh) * S + tl;
+        bb = b[idx];
+        mm = m[idx];
+        ga = gAn_rel[first + lane];
     }
-    const size_t row = (static_cast<size_t>(bh) * S + t) * D;
-    float delta = 0.0f;
-    for (int d = lane * VEC; d < D; d += 32 * VEC) {
-        const uint4 hraw = *reinterpret_cast<const uint4*>(h + row + d);
-        const uint4 draw = *reinterpret_cast<const uint4*>(dh + row + d);
-        const HT* hv = reinterpret_cast<const HT*>(&hraw);
-        const HT* dv = reinterpret_cast<const HT*>(&draw);
+    float delta[PREP_ROWS];
 #pragma unroll
-        for (int j = 0; j < VEC; j++) {
-            const float x = to_f32<HT>(dv[j]);
-            delta += x * to_f32<HT>(hv[j]);
-            if (dh16) dh16[row + d + j] = from_f32<T16>(x);
+    for (int r = 0; r < PREP_ROWS; r++) {
+        delta[r] = 0.0f;
+        if (t0 + r < S) {
+            const size_t row = (static_cast<size_t>(bh) * S + t0 + r) * D;
+            for (int d = lane * VEC; d < D; d += 32 * VEC) {
+                const uint4 hraw = *reinterpret_cast<const uint4*>(h + row + d);
+                const uint4 draw = *reinterpret_cast<const uint4*>(dh + row + d);
+                const HT* hv = reinterpret_cast<const HT*>(&hraw);
+                const HT* dv = reinterpret_cast<const HT*>(&draw);
+#pragma unroll
+                for (int j = 0; j < VEC; j++) {
+                    const float x = to_f32<HT>(dv[j]);
+                    delta[r] += x * to_f32<HT>(hv[j]);
+                    if (dh16) dh16[row + d + j] = from_f32<T16>(x);
+                }
+            }
         }
     }
+    float my_delta = 0.0f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) delta += __shfl_xor_sync(0xffffffffu, delta, o);
-    if (lane == 0) {
-        const size_t idx = static_cast<size_t>(bh) * S + t;
-        const float bb = b[idx];
-        const float em = expf(-m[idx]);
-        const float n = fmaxf(fabsf(bb), em) + 1e-6f;
-        const float sgn = bb > 0.0f ? 1.0f : (bb < 0.0f ? -1.0f : 0.0f);
-        const float db = (fabsf(bb) > em) ? sgn * (-delta / n) : 0.0f;
-        const float gg = db * n;
-        g[warp_global] = isfinite(gg) ? gg : 0.0f;
-        const float rel = gAn_rel[warp_global] + (log2_scale - log2f(n));
-        gB_rel[warp_global] = rel;
-        gB_w[warp_global] = exp2f(rel);   // the same quantity as a factor, for the off-diagonal tiles
+    for (int r = 0; r < PREP_ROWS; r++) {
+        float x = delta[r];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+        if (lane == r) my_delta = x;
+    }
+    if (mine) {
+        const size_t o = static_cast<size_t>(first) + lane;
+        if (!mine_valid) {   // padding positions
+            gB_rel[o] = -INFINITY;
+            gB_w[o] = 0.0f;
+            g[o] = 0.0f;
+        } else {
+            const float em = expf(-mm);
+            const float n = fmaxf(fabsf(bb), em) + 1e-6f;
+            const float sgn = bb > 0.0f ? 1.0f : (bb < 0.0f ? -1.0f : 0.0f);
+            const float db = (fabsf(bb) > em) ? sgn * (-my_delta / n) : 0.0f;
+            const float gg = db * n;
+            g[o] = isfinite(gg) ? gg : 0.0f;
+            const float rel = ga + (log2_scale - log2f(n));
+            gB_rel[o] = rel;
+            gB_w[o] = exp2f(rel);   // the same quantity as a factor, for the off-diagonal tiles
+        }
     }
 }
 
@@ -386,7 +412,7 @@ int launch_gates_fwd(const void* f, const void* i, float* ga, float* gA, double*
 template <typename HT>
 static int bwd_prep_dispatch(const void* h, const void* dh, const float* b, const float* m, const float* gA, float* gB,
                              float* gBw, float* g, void* dh16, int BH, int S, int Spad, int D, int dtype, cudaStream_t st) {
-    const long long warps = static_cast<long long>(BH) * Spad;
+    const long long warps = static_cast<long long>(BH) * Spad / PREP_ROWS;   // Spad is a multiple of 128
     const int threads = 256;
     const long long blocks = (warps * 32 + threads - 1) / threads;
     if (blocks > 0x7fffffffLL) return MLSTM_E_SHAPE;

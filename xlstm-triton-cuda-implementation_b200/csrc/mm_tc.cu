@@ -9,7 +9,7 @@
 // One CTA owns one stationary 128-row tile (queries in FWD/DQ, keys in DK/DV) of one batch*head
 // slice and streams the tiles on the causal side of it.  Warp roles (576 threads):
 //   warp 0       TMA producer: stationary tile once per item, then streamed tiles through a ring of slots
-//   warp 1       MMA issuer (one thread) and TMEM allocator
+//   warp 1       MMA warp and TMEM allocator: the whole warp runs the issue loop, one elected lane issues
 //   warps 2-17   four gate groups of four warps: group g turns columns [32g, 32g+32) of every T tile
 //                into gated W values, in TMEM (a thread owns one TMEM lane = one row of the tile)
 // TMEM (512 columns): T0 [0,128) and T1 [128,256) fp32 128x128; ACC [256, 256+D) fp32.  W overwrites
@@ -17,6 +17,18 @@
 // 32 T columns; 32-bit (tf32) W sits column for column on T.
 // The second contraction reads W straight from TMEM as the A operand and the streamed Z tile from
 // shared memory as an MN-major B operand, so the gated tile never touches shared or global memory.
+//
+// What the measurements behind this structure said (in-kernel clock64 stamps, D = 64 ... 256):
+//   * tcgen05.mma takes its operands from warp-uniform registers.  Issued from inside an `if (lane == 0)`
+//     branch every MMA cost about 100 cycles of issue (a 128x128x16 MMA runs 64); with the warp
+//     converged and one elected lane issuing, the tensor pipe itself sets the pace of a batch of MMAs.
+//   * Between two batches every instruction of the MMA warp is idle time of the pipe.  Streamed tiles
+//     are therefore signalled in whole units (one "loaded" and one "consumed" barrier per unit, the
+//     consumed barrier of a Y tile doubling as "T written"), and the barriers of the next batch are
+//     tested in the middle of the current one (mbarrier.test_wait; try_wait may suspend the thread).
+//   * The gate warps' epilogue (row-sum exchange, accumulator drain, output) sits between two work
+//     items with the pipe idle: the exchange and the next item's row terms are moved in front of the
+//     accumulator wait, and where shared memory has room the output leaves through TMA stores.
 //
 // Element types: fp16 / bf16 (kind::f16) and fp32 read as tf32 (kind::tf32).  D is the width this CTA
 // contracts over in T and produces in ACC.  In the sliced form (SPLIT) the head dimension is larger

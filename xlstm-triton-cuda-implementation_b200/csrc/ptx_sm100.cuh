@@ -308,7 +308,7 @@ __device__ __forceinline__ bool mbar_wait_cluster_warp(uint64_t* bar, uint32_t p
     return __all_sync(0xffffffffu, mbar_wait_cluster<SLEEP_NS>(bar, parity, abort_flag, limit_cycles) ? 1 : 0) != 0;
 }
 // TMA tile load of a CTA pair: data into this CTA's shared memory, bytes counted on a barrier that
-// may live in the peer CTA (mbar is a shared::cluster address).  No multicast.
+// may live in the peer CTA (mbar is a shared::cluster address); the data goes to this CTA only.
 __device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* m, uint32_t mbar_cluster_addr, int x, int y,
                                                  int z) {
     asm volatile(
