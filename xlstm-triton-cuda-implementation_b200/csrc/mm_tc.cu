@@ -533,6 +533,9 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             const float er = state_step ? er_state
                                         : static_cast<float>(er_d + p.col_ref[ref_base + st * (TILE / REF_BLOCK) + (grp >> 1)]);
             const float er_w = (MODE == FWDC && state_step) ? fast_exp2(er) : 0.0f;
+            // DK adds a per-column term to T.  Each lane fetches one column's value before the wait (32 more
+            // registers are not to be had) and the warp passes them round with shuffles afterwards.
+            const float g_lane = (MODE == DK) ? __ldg(p.col_g + vec_base + st * TILE + cbase + lane) : 0.0f;
             [[maybe_unused]] const bool trace_on = (n == 0) && (threadIdx.x == 64 || threadIdx.x == 64 + 15 * 32);
             [[maybe_unused]] const int trole = threadIdx.x == 64 ? 2 : 3;
             TRACE(trole, t, 0);
@@ -548,15 +551,9 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             tc_wait_ld();
             TRACE(trole, t, 2);
             if (MODE == DK) {   // T + g with g per column: added eight columns at a time to keep registers free
-                const float4* g4 = reinterpret_cast<const float4*>(p.col_g + vec_base + st * TILE + cbase);
 #pragma unroll
-                for (int q4 = 0; q4 < 8; q4++) {
-                    const float4 gq = __ldg(g4 + q4);
-                    tv[q4 * 4 + 0] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 0]) + gq.x);
-                    tv[q4 * 4 + 1] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 1]) + gq.y);
-                    tv[q4 * 4 + 2] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 2]) + gq.z);
-                    tv[q4 * 4 + 3] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 3]) + gq.w);
-                }
+                for (int j = 0; j < 32; j++)
+                    tv[j] = __float_as_uint(__uint_as_float(tv[j]) + __shfl_sync(0xffffffffu, g_lane, j));
             }
             if (MODE == FWDC && state_step) {
 #pragma unroll

@@ -395,6 +395,9 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             float cv[32];
             if (!dead) load_cols((diag ? p.col_rel : p.col_w) + vec_base + st * TILE, cv);
             const float er = dead ? 0.0f : static_cast<float>(er_d + p.col_ref[ref_base + st * (TILE / REF_BLOCK) + (grp >> 1)]);
+            // DK adds a per-column term to T.  Each lane fetches one column's value before the wait (32 more
+            // registers are not to be had) and the warp passes them round with shuffles afterwards.
+            const float g_lane = (MODE == DK && !dead) ? __ldg(p.col_g + vec_base + st * TILE + cbase + lane) : 0.0f;
             GTRACE(t, 0);
             ok = mbar_wait_warp<SLACK_SLEEP_NS>(&bar_t[buf], (gt >> 1) & 1, abort_flag, WAIT_LIMIT);
             if (!ok) break;
@@ -410,15 +413,9 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                 tmem_ld32(t_tmem, tv);
                 tc_wait_ld();
                 if (MODE == DK) {
-                    const float4* g4 = reinterpret_cast<const float4*>(p.col_g + vec_base + st * TILE + cbase);
 #pragma unroll
-                    for (int q4 = 0; q4 < 8; q4++) {
-                        const float4 gq = __ldg(g4 + q4);
-                        tv[q4 * 4 + 0] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 0]) + gq.x);
-                        tv[q4 * 4 + 1] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 1]) + gq.y);
-                        tv[q4 * 4 + 2] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 2]) + gq.z);
-                        tv[q4 * 4 + 3] = __float_as_uint(__uint_as_float(tv[q4 * 4 + 3]) + gq.w);
-                    }
+                    for (int j = 0; j < 32; j++)
+                        tv[j] = __float_as_uint(__uint_as_float(tv[j]) + __shfl_sync(0xffffffffu, g_lane, j));
                 }
                 if (diag) {
 #pragma unroll
