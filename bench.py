@@ -448,11 +448,11 @@ def main():
                        "parallelism": f"dp{world} over (batch, head) slices, no collective",
                        "l2": "inputs (1.07 GB per step) larger than L2"},
             "tflops_algorithmic": (ff + fb) * world / (ms_per_step * 1e-3) / 1e12,
-            "roofline": {"bound": "tensor", "kernel": "mlstm_tc_pass (FWD, DQ, DK, DV launches of one step, with the gate passes)",
+            "roofline": {"bound": "tensor", "kernel": "mlstm_tc_pass_pair (FWD, DQ, DK, DV launches of one step, with the gate passes)",
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
                          "peak_source": peaks["source"],
                          # DRAM bytes per launch from the ncu capture in profiles/ (B=4 case, scaled by slices)
-                         "traffic": 1.15e9, "traffic_source": "ncu, B=4 case x4, average of the four passes",
+                         "traffic": 1.19e9, "traffic_source": "ncu, B=4 case x4, average of the four passes",
                          "fwd_tflops": ff / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": fb / (bwd_ms * 1e-3) / 1e12,
                          "fwd_ms": fwd_ms, "bwd_ms": bwd_ms},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
