@@ -94,6 +94,19 @@ size_t mlstm_forward_f16_workspace(unsigned S, unsigned D);
 int mlstm_forward_f16(const void* Q, const void* K, const void* V, const void* F, const void* I, void* H,
                       unsigned S, unsigned D, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Single-head fp16 backward of the C++ driver, complete: dQ, dK, dV [S,D] half and dF, dI [S] half from
+ * dH, Q, K, V [S,D] half and F, I [S] half.
+ * Replaces the two launches matmul_backward_db<64,16,128,16,8,8><<<S/64,128,smem>>>(dH,Q,K,V,F,I,M,B,dB,S) and
+ * matmul_backward<...><<<S/64,128,smem>>>(dH,dB,Q,K,V,dQ,dK,dV,F,I,dI,M,B,S) (cuda-src/mlstm_backward.cu:11-12,
+ * 177-178, 621-628) and the never-instantiated backward_df (:507-540).  The reference's kernels stop at dB, dQ and
+ * dK (dV is a TODO there, :497-499, and dI / dF are not finished); they take M and B from a host computation.
+ * Here the forward is recomputed inside the call for h, m and b, so the argument list needs neither.
+ */
+size_t mlstm_backward_f16_workspace(unsigned S, unsigned D);
+int mlstm_backward_f16(const void* dH, const void* Q, const void* K, const void* V, const void* F, const void* I,
+                       void* dQ, void* dK, void* dV, void* dF, void* dI, unsigned S, unsigned D, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
 /* The same forward as mlstm_forward_f16 for callers that cannot supply scratch memory.
  * No counterpart in the reference: its launcher has no scratch because its kernel needs none.
  * Who needs it: callers that are not allowed to call cudaMalloc at the point of use (on a

@@ -65,6 +65,25 @@ def gen_cpp(name, S, D, seed):
     print(name, "sum H", float(H.astype(np.float64).sum()), H[0], H[-1])
 
 
+def gen_cpp_backward(name, S, D, seed):
+    """Inputs in the backward driver's recipe (uniform [-1, 1) halves, srand(seed); cuda-src/mlstm_backward.cu:
+    560-566), gradients from the reference's PyTorch backward (mlstm_matmul.py:336-365) in fp32 on those values.
+    The reference's C++ host backward covers dB, dQ and dK only and is not used."""
+    lib = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libmlstm_ref.so"))
+    mk = lambda n: np.zeros(n, dtype=np.float16)
+    Q, K, V, F, I, dH, scratch = mk(S * D), mk(S * D), mk(S * D), mk(S), mk(S), mk(S * D), mk(S * D)
+    p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    lib.ref_fill(ctypes.c_uint(seed), p(Q), p(K), p(V), p(F), p(I), ctypes.c_uint(S), ctypes.c_uint(D))
+    lib.ref_fill(ctypes.c_uint(seed + 1), p(dH), p(scratch), p(scratch), p(mk(S)), p(mk(S)), ctypes.c_uint(S), ctypes.c_uint(D))
+    t = lambda a, *shape: torch.from_numpy(a.astype(np.float32)).reshape(1, 1, *shape)
+    ref_mm.DEVICE = torch.device("cpu")
+    dq, dk, dv, df, di = ref_mm.mlstm_matmul_backward_pytorch(t(dH, S, D), t(Q, S, D), t(K, S, D), t(V, S, D), t(F, S), t(I, S))
+    np.savez(os.path.join(HERE, name), Q=Q.reshape(S, D), K=K.reshape(S, D), V=V.reshape(S, D), F=F, I=I,
+             dH=dH.reshape(S, D), dQ=dq[0, 0].numpy(), dK=dk[0, 0].numpy(), dV=dv[0, 0].numpy(), dF=df[0, 0].numpy(),
+             dI=di[0, 0].numpy())
+    print(name, "max |dQ|", float(dq.abs().max()), "max |dF|", float(df.abs().max()))
+
+
 if __name__ == "__main__":
     gen_matmul("matmul_s128_d32_f0.npz", 1, 2, 128, 32, 0.0, 0)
     gen_matmul("matmul_s192_d64_f3.npz", 2, 1, 192, 64, 3.0, 1)
@@ -73,3 +92,5 @@ if __name__ == "__main__":
     # the reference demo's own recipe: srand(100), S = 640 (the README's value), D = 128
     gen_cpp("cpp_forward_seed100_s640_d128.npz", 640, 128, 100)
     gen_cpp("cpp_forward_seed100_s128_d128.npz", 128, 128, 100)
+    # the backward driver's recipe: srand(1678), D = 128 (S = 192 keeps the fixture small and is not a tile multiple)
+    gen_cpp_backward("cpp_backward_seed1678_s192_d128.npz", 192, 128, 1678)

@@ -102,6 +102,35 @@ def test_cpp_forward_against_reference_golden(gc, golden_dir, name):
     assert int((diff > 0.01).sum()) == 0, float(diff.max())
 
 
+def test_cpp_backward_against_reference_golden(gc, golden_dir):
+    """mlstm_backward_f16 on inputs in the backward driver's recipe (srand(1678)) against the gradients of the
+    reference's PyTorch backward on the same values (tests/golden/make_golden.py).  Tolerance: the reference's
+    own 1e-2 (utils.py:4) as max-abs-rel per tensor."""
+    z = np.load(f"{golden_dir}/cpp_backward_seed1678_s192_d128.npz")
+    dev = torch.device("cuda", 0)
+    dH, Q, K, V, F, I = (torch.from_numpy(z[k]).to(dev) for k in ("dH", "Q", "K", "V", "F", "I"))
+    S, D = Q.shape
+    dQ, dK, dV = (torch.empty_like(Q) for _ in range(3))
+    dF, dI = torch.empty_like(F), torch.empty_like(I)
+    L = gc._lib.lib()
+    ws = gc._lib.workspace(L.mlstm_backward_f16_workspace(S, D), dev)
+    rc = L.mlstm_backward_f16(dH.data_ptr(), Q.data_ptr(), K.data_ptr(), V.data_ptr(), F.data_ptr(), I.data_ptr(),
+                              dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(), dF.data_ptr(), dI.data_ptr(), S, D,
+                              ws.data_ptr(), ws.numel(), gc._lib.stream_ptr(dev))
+    assert rc == 0, gc._lib.lib().mlstm_status_string(rc)
+    torch.cuda.synchronize()
+    for name, got in (("dQ", dQ), ("dK", dK), ("dV", dV), ("dF", dF), ("dI", dI)):
+        err = gc.orc.max_abs_rel(got.float().cpu(), torch.from_numpy(z[name]).float())
+        assert err < 1e-2, (name, err)
+    # argument checks
+    assert L.mlstm_backward_f16(None, Q.data_ptr(), K.data_ptr(), V.data_ptr(), F.data_ptr(), I.data_ptr(), dQ.data_ptr(),
+                                dK.data_ptr(), dV.data_ptr(), dF.data_ptr(), dI.data_ptr(), S, D, ws.data_ptr(), ws.numel(),
+                                None) == -1
+    assert L.mlstm_backward_f16(dH.data_ptr(), Q.data_ptr(), K.data_ptr(), V.data_ptr(), F.data_ptr(), I.data_ptr(),
+                                dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(), dF.data_ptr(), dI.data_ptr(), S, D,
+                                ws.data_ptr(), 16, None) == -5
+
+
 @pytest.mark.parametrize("S", [640, 1280])
 def test_cpp_driver_program(gc, S):
     """The C++ driver program (tests/cpp/driver_forward.cu): reference recipe inputs, launch through
@@ -114,3 +143,33 @@ def test_cpp_driver_program(gc, S):
     r = subprocess.run([exe, str(S)], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "Non_matching count: 0" in r.stdout
+
+
+def test_cpp_backward_driver_program(gc, tmp_path):
+    """The C++ backward driver program (tests/cpp/driver_backward.cu): reference recipe inputs (srand(1678),
+    S = 1280, D = 128 as in the reference's main), launch through include/mlstm_backward.cuh with the reference's
+    template arguments; the dumped gradients are compared with the CPU oracle on the dumped inputs."""
+    import os
+    import subprocess
+    exe = os.path.join(os.path.dirname(os.path.abspath(__file__)), "cpp", "driver_backward")
+    if not os.path.exists(exe):
+        pytest.fail("tests/cpp/driver_backward not built: run __graft_entry__.build()")
+    S, D = 1280, 128
+    out = tmp_path / "bwd.bin"
+    r = subprocess.run([exe, str(S), str(out)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "Non_finite count: 0" in r.stdout
+    raw = np.fromfile(out, dtype=np.float16)
+    sizes = [S * D] * 4 + [S, S] + [S * D] * 3 + [S, S]
+    parts, off = [], 0
+    for n in sizes:
+        parts.append(torch.from_numpy(raw[off:off + n].astype(np.float32)))
+        off += n
+    assert off == raw.size
+    dH, Q, K, V, F, I, dQ, dK, dV, dF, dI = parts
+    m4 = lambda a: a.reshape(1, 1, S, D)
+    v3 = lambda a: a.reshape(1, 1, S)
+    ref = orc.matmul_backward(m4(dH), m4(Q), m4(K), m4(V), v3(F), v3(I))
+    for name, got, want in zip(("dQ", "dK", "dV", "dF", "dI"), (m4(dQ), m4(dK), m4(dV), v3(dF), v3(dI)), ref):
+        err = orc.max_abs_rel(got, want)
+        assert err < 1e-2, (name, err)

@@ -65,6 +65,16 @@ def test_cpp_oracle_vs_reference_golden(golden_dir, name):
     assert float((h.float() - z["H"].float()).abs().max()) <= 2e-3
 
 
+def test_backward_oracle_vs_reference_golden_cpp_recipe(golden_dir):
+    """The oracle's backward against the reference's PyTorch backward on the backward driver's input recipe
+    (single head, fp16 values, srand(1678))."""
+    z = _load(golden_dir, "cpp_backward_seed1678_s192_d128.npz")
+    t = lambda k: z[k].float()[None, None]
+    grads = orc.matmul_backward(t("dH"), t("Q"), t("K"), t("V"), t("F"), t("I"))
+    for name, got in zip(("dQ", "dK", "dV", "dF", "dI"), grads):
+        assert orc.max_abs_rel(got[0, 0], z[name].double()) < 1e-5, name
+
+
 def _c_oracle():
     path = os.path.join(ROOT, "oracle", "libmlstm_oracle.so")
     if not os.path.exists(path):

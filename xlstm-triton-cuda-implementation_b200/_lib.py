@@ -62,6 +62,10 @@ def lib():
     L.mlstm_forward_f16_workspace.argtypes = [u32, u32]
     L.mlstm_forward_f16.restype = i32
     L.mlstm_forward_f16.argtypes = [vp] * 6 + [u32, u32, vp, sz, vp]
+    L.mlstm_backward_f16_workspace.restype = sz
+    L.mlstm_backward_f16_workspace.argtypes = [u32, u32]
+    L.mlstm_backward_f16.restype = i32
+    L.mlstm_backward_f16.argtypes = [vp] * 11 + [u32, u32, vp, sz, vp]
     L.mlstm_forward_f16_static.restype = i32
     L.mlstm_forward_f16_static.argtypes = [vp] * 6 + [u32, u32, vp]
     L.mlstm_chunk_workspace.restype = sz
@@ -83,7 +87,8 @@ def lib():
 EXPORTS = [
     "mlstm_status_string", "mlstm_last_error_detail", "mlstm_tc_supported", "mlstm_mm_fwd_workspace", "mlstm_mm_fwd",
     "mlstm_mm_bwd_workspace", "mlstm_mm_bwd", "mlstm_scan_fwd_workspace", "mlstm_scan_fwd",
-    "mlstm_forward_f16_workspace", "mlstm_forward_f16", "mlstm_forward_f16_static", "mlstm_read_status",
+    "mlstm_forward_f16_workspace", "mlstm_forward_f16", "mlstm_forward_f16_static", "mlstm_backward_f16_workspace",
+    "mlstm_backward_f16", "mlstm_read_status",
     "mlstm_chunk_workspace", "mlstm_chunk_gate_summary", "mlstm_chunk_prepare", "mlstm_chunk_local_state",
     "mlstm_chunk_apply",
 ]

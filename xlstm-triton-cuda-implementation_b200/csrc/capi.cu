@@ -340,6 +340,42 @@ int mlstm_forward_f16(const void* Q, const void* K, const void* V, const void* F
                         MLSTM_DT_F16, 0, static_cast<cudaStream_t>(stream));
 }
 
+// Single-head fp16 backward of the C++ driver: the forward is run first for h, m and b (the reference's
+// launches take M and B from a host computation and have no h; the row dots delta = dh . h used here need it),
+// then the three backward passes and the dF scan.  Workspace: forward scratch | h [S, D] half | backward scratch.
+static size_t bwd16_h_offset(int S) { return carve_fwd(nullptr, 1, S, true).bytes; }
+static size_t bwd16_bwd_offset(int S, int D) { return bwd16_h_offset(S) + al(static_cast<size_t>(S) * D * 2); }
+
+size_t mlstm_backward_f16_workspace(unsigned S, unsigned D) {
+    if (S > 0x7fffffffu || D > 0x7fffffffu) return 0;
+    if (check_dims(1, 1, static_cast<int>(S), static_cast<int>(D)) != MLSTM_OK) return 0;
+    return bwd16_bwd_offset(static_cast<int>(S), static_cast<int>(D)) +
+           mlstm_mm_bwd_workspace(1, 1, static_cast<int>(S), static_cast<int>(D), MLSTM_DT_F16, MLSTM_DT_F16, 0);
+}
+
+int mlstm_backward_f16(const void* dH, const void* Q, const void* K, const void* V, const void* F, const void* I, void* dQ,
+                       void* dK, void* dV, void* dF, void* dI, unsigned S, unsigned D, void* workspace,
+                       size_t workspace_bytes, void* stream) {
+    if (!dH || !Q || !K || !V || !F || !I || !dQ || !dK || !dV || !dF || !dI) return MLSTM_E_ARG;
+    if (S > 0x7fffffffu || D > 0x7fffffffu) return MLSTM_E_ARG;
+    const int s = static_cast<int>(S), d = static_cast<int>(D);
+    int rc = check_dims(1, 1, s, d);
+    if (rc != MLSTM_OK) return rc;
+    if (!aligned16(dH) || !aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(dQ) || !aligned16(dK) || !aligned16(dV))
+        return MLSTM_E_ALIGN;
+    const size_t need = mlstm_backward_f16_workspace(S, D);
+    if (!workspace || need == 0 || workspace_bytes < need || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
+    uint8_t* base = static_cast<uint8_t*>(workspace);
+    FwdWs w = carve_fwd(base, 1, s, true);
+    void* h = base + bwd16_h_offset(s);
+    rc = forward_impl(Q, K, V, F, I, nullptr, h, w.m, w.b, w, 1, s, d, MLSTM_DT_F16, MLSTM_DT_F16, 0,
+                      static_cast<cudaStream_t>(stream));
+    if (rc != MLSTM_OK) return rc;
+    const size_t off = bwd16_bwd_offset(s, d);
+    return mlstm_mm_bwd(dH, Q, K, V, F, I, h, w.m, w.b, dQ, dK, dV, dF, dI, base + off, workspace_bytes - off, 1, 1, s, d,
+                        MLSTM_DT_F16, MLSTM_DT_F16, 0, stream);
+}
+
 // ------------------------------------------------------------------------------------------------
 // Single-head fp16 forward for callers that have no way to hand over scratch memory.
 //

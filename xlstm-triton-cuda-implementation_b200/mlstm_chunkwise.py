@@ -10,8 +10,8 @@ of its scan path (mlstm_scan.py:143-195) with the carry algebra of its scan oper
 Sequence-parallel form: rank r of the group holds the r-th contiguous segment of every sequence
 (all heads).  Two small all-gathers connect the ranks and there is no other communication:
   1. per-slice gate summaries {F_end, A_end} (16 bytes per slice) -> every rank's carry-in {F_in, A_in};
-  2. per-slice segment states (S [D,D], z [D], A_end; 0.53 MB per rank at 8 heads) -> every rank's
-     inbound state, folded locally from the lower ranks' states.
+  2. per-slice segment states (S [D,D], z [D], A_end, packed into one buffer; 0.53 MB per rank at 8
+     heads) -> every rank's inbound state, folded locally from the lower ranks' states.
 The folds are plain tensor arithmetic (``fold_gate_summaries``, ``fold_states``) and do not care where
 the tensors live, which is how the CPU tests drive them over gloo.
 """
@@ -135,13 +135,12 @@ def fold_gate_summaries(local):
     segment is -inf).  With F_in the log-forget total before segment g, a position's a = i - F shifts
     by -F_in, hence the segment's prefix maximum in global terms is A_local - F_in."""
     local = local.double()
-    G = local.shape[0]
     F_loc, A_loc = local[..., 0], local[..., 1]
     F_in = torch.cumsum(F_loc, 0) - F_loc                      # exclusive prefix sum over segments
     A_glob = A_loc - F_in
     A_in = torch.full_like(A_glob, -float("inf"))
-    for g in range(1, G):
-        A_in[g] = torch.maximum(A_in[g - 1], A_glob[g - 1])
+    if A_glob.shape[0] > 1:
+        A_in[1:] = torch.cummax(A_glob, 0).values[:-1]         # exclusive prefix maximum over segments
     return torch.stack([F_in, A_in], dim=-1)
 
 
@@ -153,34 +152,40 @@ def fold_states(S_all, z_all, A_end_all, rank):
     A_end of segment rank-1, i.e. by the carried-in A of segment ``rank``.  None for rank 0."""
     if rank == 0:
         return None
-    A_ref = A_end_all[rank - 1].double()
-    S = torch.zeros_like(S_all[0], dtype=torch.float32)
-    z = torch.zeros_like(z_all[0], dtype=torch.float32)
-    for g in range(rank):
-        w = torch.exp(A_end_all[g].double() - A_ref).float()    # <= 1
-        S = S + w[:, None, None] * S_all[g].float()
-        z = z + w[:, None] * z_all[g].float()
+    A = A_end_all[:rank].double()
+    w = torch.exp(A - A[rank - 1]).float()                      # [rank, BH], <= 1
+    w = torch.nan_to_num(w, nan=0.0)                            # -inf - -inf (nothing seen yet): no contribution
+    S = (w[:, :, None, None] * S_all[:rank].float()).sum(0)
+    z = (w[:, :, None] * z_all[:rank].float()).sum(0)
     return S, z
 
 
 def _all_gather(t, group):
     import torch.distributed as dist
-    out = [torch.empty_like(t) for _ in range(dist.get_world_size(group))]
-    dist.all_gather(out, t.contiguous(), group=group)
-    return torch.stack(out, 0)
+    t = t.contiguous()
+    G = dist.get_world_size(group)
+    out = torch.empty((G * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)   # concatenated along dim 0
+    dist.all_gather_into_tensor(out, t, group=group)
+    return out.view((G,) + tuple(t.shape))
 
 
 def sequence_parallel_forward(segment, group=None, h_dtype=torch.float32):
-    """The sequence-parallel protocol over any object with the ChunkSegment interface."""
+    """The sequence-parallel protocol over any object with the ChunkSegment interface: two all-gathers
+    (gate summaries; then every segment's state with its A_end packed into one buffer)."""
     import torch.distributed as dist
     rank = dist.get_rank(group)
     local = segment.gate_summary()                                   # [BH, 2]
     carry_all = fold_gate_summaries(_all_gather(local, group))       # [G, BH, 2]
     summary = segment.prepare(carry_all[rank] if rank > 0 else None)  # [BH, 2] incl. carry
     S_loc, z_loc = segment.local_state()
-    S_all = _all_gather(S_loc, group)
-    z_all = _all_gather(z_loc, group)
-    A_end_all = _all_gather(summary[:, 1].contiguous(), group)
+    BH, D = z_loc.shape
+    # one buffer per rank: S [D*D] | z [D] | A_end (float64 carried as two float32 words)
+    a_words = summary[:, 1].contiguous().view(torch.float32).reshape(BH, 2)
+    packed = torch.cat([S_loc.reshape(BH, D * D).float(), z_loc.float(), a_words], dim=1)
+    allp = _all_gather(packed, group)                                # [G, BH, D*D + D + 2]
+    S_all = allp[:, :, :D * D].reshape(-1, BH, D, D)
+    z_all = allp[:, :, D * D:D * D + D]
+    A_end_all = allp[:, :, D * D + D:].contiguous().view(torch.float64).reshape(-1, BH)
     state_in = fold_states(S_all, z_all, A_end_all, rank)
     return segment.apply(state_in, h_dtype=h_dtype)
 
