@@ -321,6 +321,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="cfg4 only: a smaller batch of the same shape (profiler captures); the line's config says so")
     ap.add_argument("--workload", default="cfg4", choices=["cfg4", "cfg5", "cfg3", "cfg1"],
                     help="cfg4 (default, the headline): matmul fwd+bwd; cfg5: chunkwise forward S=65536, "
                          "sequence-parallel for N>1; cfg3: scan forward fp32 D=1024; cfg1: C++ single-head fp16 forward")
@@ -348,6 +350,10 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     B, NH, S, D = CFG["B"], CFG["NH"], CFG["S"], CFG["D"]
+    if args.batch is not None:
+        if not 1 <= args.batch <= CFG["B"]:
+            raise SystemExit("--batch must be between 1 and %d" % CFG["B"])
+        B = args.batch
     warmup = max(args.warmup, 3)
     g = torch.Generator().manual_seed(1234 + rank)
     mk = lambda *s: torch.randn(*s, generator=g)
@@ -443,10 +449,11 @@ def main():
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "cfg4: mLSTM matmul fwd+bwd B=16 NH=8 S=4096 D=256 bf16, fp32 accumulate",
+            "config": {"workload": ("cfg4: mLSTM matmul fwd+bwd B=16 NH=8 S=4096 D=256 bf16, fp32 accumulate" if B == CFG["B"] else
+                                    "cfg4 shape at a reduced batch B=%d (profiler case, not the benchmark)" % B),
                        "per_gpu_batch": B, "global_batch": B * world, "heads": NH, "seq_len": S, "head_dim": D,
                        "parallelism": f"dp{world} over (batch, head) slices, no collective",
-                       "l2": "inputs (1.07 GB per step) larger than L2"},
+                       "l2": "inputs (%.2f GB per step) larger than L2" % (h2d / 1e9)},
             "tflops_algorithmic": (ff + fb) * world / (ms_per_step * 1e-3) / 1e12,
             "roofline": {"bound": "tensor", "kernel": "mlstm_tc_pass_pair (FWD, DQ, DK, DV launches of one step, with the gate passes)",
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],

@@ -82,6 +82,23 @@ def test_tensor_core_forward_backward(gc, dtype, D, S, f_mean):
         assert all(v < TOL_16 for v in eb.values()), (h_dtype, eb)
 
 
+@pytest.mark.parametrize("dtype,D,S", [(torch.float16, 64, 192), (torch.bfloat16, 128, 192), (torch.float16, 256, 320),
+                                       (torch.bfloat16, 256, 448)])
+def test_strong_decay_with_a_fully_padded_column_block(gc, dtype, D, S):
+    """Ragged S whose last 128-row tile ends in a 64-position block of pure padding, with forget gates around
+    sigmoid(-0.5): the row term of the exponent alone reaches 2^140 for late keys, and the padded block has no
+    reference to balance it.  Its columns weigh 0; the product must be 0, not NaN (regression)."""
+    x = gc.make_inputs(1, 2, S, D, dtype, f_mean=-0.5, qkv_scale=D ** -0.5, seed=S + D)
+    flags = gc._lib.F_FORCE_TC
+    h, m, b = gc.run_forward(x, h_dtype=dtype, flags=flags)
+    ef = gc.errors_forward(x, h, m, b)
+    assert ef["h"] < TOL_16 and ef["b"] < TOL_16, ef
+    grads = gc.run_backward(x, h, m, b, flags=flags)
+    assert all(bool(torch.isfinite(t.float()).all()) for t in grads)
+    eb = gc.errors_backward(x, grads, dtype)
+    assert all(v < TOL_16 for v in eb.values()), eb
+
+
 @pytest.mark.parametrize("D", [64, 128, 256])
 def test_tf32_tensor_core_forward_backward(gc, D):
     """fp32 inputs on the tensor cores (tf32 operands, fp32 accumulate), opt-in by flag."""

@@ -55,6 +55,7 @@ constexpr int NGATE = NGROUPS * 128;            // gate threads
 constexpr int NTHREADS = 64 + NGATE;            // + producer warp and MMA warp
 constexpr int BOX_BYTES = 128 * 128;  // one TMA box: 128 rows of 128 bytes
 constexpr long long WAIT_LIMIT = 4000000000LL;
+constexpr float MAX_ROW_EXP2 = 60.0f;           // clamp of the per-row exponent off the diagonal tile (see its use)
 constexpr int SLACK_SLEEP_NS = 64;              // poll interval of the roles that wait with slack (gate warps, producer)  // cycles (about two seconds)
 constexpr int SLICE_SET_DEFAULT = 8;            // slices whose work items are interleaved in item order
 
@@ -575,7 +576,10 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             } else {
                 // exp2(ec + er) = exp2(ec) exp2(er): one exponential per row and step; both factors are <= const
                 // because every column of an off-diagonal tile is on the causal side of every row
-                const float u = fast_exp2(er);
+                // A 64-column block that is padding from end to end (ragged S) has no meaningful reference, and the
+                // row term alone can be large with strong decay: its column factors are 0, and 0 times an overflowed
+                // u would be NaN.  Real columns keep er far below the clamp.
+                const float u = fast_exp2(fminf(er, MAX_ROW_EXP2));
                 const float gu = (MODE == DQ) ? g_row * u : 0.0f;
 #pragma unroll
                 for (int j = 0; j < 32; j++) {

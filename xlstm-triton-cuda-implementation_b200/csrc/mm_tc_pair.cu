@@ -51,6 +51,7 @@ constexpr int OUT_BYTES = (NGATE / 32) * STAGE_BYTES;
 constexpr int NBAR = 1 + 2 * NSLOT + 2 + 2 + 1 + 1 + 2 + 4;
 constexpr int SMEM_BYTES = X_BYTES + NSLOT * SLOT_BYTES + OUT_BYTES + NBAR * 8 + 64 + NGROUPS * 128 * 4;
 constexpr long long WAIT_LIMIT = 4000000000LL;
+constexpr float MAX_ROW_EXP2 = 60.0f;           // clamp of the per-row exponent off the diagonal tile (see its use)
 constexpr int SLACK_SLEEP_NS = 64;              // poll interval of the roles that wait with slack (gate warps, producer)
 static_assert(SMEM_BYTES <= 232448, "exceeds the shared memory of a CTA");
 
@@ -428,7 +429,10 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                         cv[j] = wj;
                     }
                 } else {
-                    const float u = fast_exp2(er);
+                    // A 64-column block that is padding from end to end (ragged S) has no meaningful reference, and the
+                    // row term alone can be large with strong decay: its column factors are 0, and 0 times an overflowed
+                    // u would be NaN.  Real columns keep er far below the clamp.
+                    const float u = fast_exp2(fminf(er, MAX_ROW_EXP2));
                     const float gu = (MODE == DQ) ? g_row * u : 0.0f;
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
