@@ -459,7 +459,7 @@ def main():
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
                          "peak_source": peaks["source"],
                          # DRAM bytes per launch from the ncu capture in profiles/ (B=4 case, scaled by slices)
-                         "traffic": 1.19e9, "traffic_source": "ncu, B=4 case x4, average of the four passes",
+                         "traffic": 1.18e9, "traffic_source": "ncu, B=4 case x4, average of the four passes",
                          "fwd_tflops": ff / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": fb / (bwd_ms * 1e-3) / 1e12,
                          "fwd_ms": fwd_ms, "bwd_ms": bwd_ms},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
