@@ -96,9 +96,10 @@ struct TcCfg {
     static constexpr int STAGE_BYTES = 2048;                  // per gate warp: 32 rows x 64 bytes
     static constexpr int OUT_BYTES = STAGED ? (NGATE / 32) * STAGE_BYTES : 0;
     static constexpr int NSLOT = ES == 2 ? (D == 256 ? 5 : (D == 128 ? 5 : 8)) : (D == 256 ? 3 : (D == 128 ? 5 : 6));
-    // Streamed tiles are signalled in units of UH slots (a whole tile unless it has more than two slots):
-    // one "loaded" and one "consumed" barrier per unit, in rings of RING.
-    static constexpr int UH = NHALF <= 2 ? NHALF : 2;
+    // Streamed tiles are signalled in units of UH slots: a whole tile where the ring holds at least two tiles,
+    // single slots where it does not (tf32 at D = 256: four slots per tile, three in the ring).
+    // One "loaded" and one "consumed" barrier per unit, in rings of RING.
+    static constexpr int UH = (NSLOT >= 2 * NHALF) ? NHALF : 1;
     static constexpr int UPT = NHALF / UH;                    // units per streamed tile
     static constexpr int RING = 8;                            // >= units in flight (NSLOT / UH)
     static_assert(NSLOT / UH <= RING && NSLOT > UH, "barrier ring too small / unit larger than the slot ring");
