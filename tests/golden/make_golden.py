@@ -1,6 +1,6 @@
 """Generate the golden vectors under tests/golden/ from the reference project itself.
 
-Run where the reference checkout is present (default /root/reference, or $MLSTM_REF) and where
+Run where the reference checkout is present ($MLSTM_REF, or the default below) and where
 oracle/_ref/libmlstm_ref.so has been built (``make -C oracle ref``):
 
     python tests/golden/make_golden.py
