@@ -54,7 +54,7 @@ def measured_peaks():
 
 class ClockSampler:
     """SM clock and throttle-reason samples taken in-process through NVML while the timed region runs
-    (two light queries every 25 ms; a polling nvidia-smi process disturbed sub-millisecond kernels)."""
+    (two light queries every 10 ms; a polling nvidia-smi process disturbed sub-millisecond kernels)."""
     REASONS = (("hw_slowdown", 0x8), ("sw_power_cap", 0x4), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40))
 
     def __init__(self, index):
@@ -92,7 +92,7 @@ class ClockSampler:
                 self.samples.append((time.time(), clk, reasons))
             except Exception:
                 pass
-            time.sleep(0.025)
+            time.sleep(0.010)
 
     def stop(self):
         if self.nvml is None:
@@ -317,7 +317,7 @@ def run_forward_workload(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
