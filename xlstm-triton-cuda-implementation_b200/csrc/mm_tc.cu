@@ -95,7 +95,8 @@ struct TcCfg {
     static constexpr bool STAGED = (ES == 2 && D == 128);
     static constexpr int STAGE_BYTES = 2048;                  // per gate warp: 32 rows x 64 bytes
     static constexpr int OUT_BYTES = STAGED ? (NGATE / 32) * STAGE_BYTES : 0;
-    static constexpr int NSLOT = ES == 2 ? (D == 256 ? 5 : (D == 128 ? 5 : 8)) : (D == 256 ? 3 : (D == 128 ? 5 : 6));
+    // (16-bit D = 128: four slots = two steps, which leaves room for the second set of row partials below)
+    static constexpr int NSLOT = ES == 2 ? (D == 256 ? 5 : (D == 128 ? 4 : 8)) : (D == 256 ? 3 : (D == 128 ? 5 : 6));
     // Streamed tiles are signalled in units of UH slots: a whole tile where the ring holds at least two tiles,
     // single slots where it does not (tf32 at D = 256: four slots per tile, three in the ring).
     // One "loaded" and one "consumed" barrier per unit, in rings of RING.
