@@ -489,27 +489,36 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         int gstep = 0;
         [[maybe_unused]] uint8_t* stage = sOut + (warp - 2) * C::STAGE_BYTES;
         if (STAGED && lane == 0) prefetch_tmap(&tmO);
-        // row terms of a work item: the row part of the exponent in double (the column block's reference is added
+        // Row terms of a work item: the row part of the exponent in double (the column block's reference is added
         // per block; STATE: rows are key dimensions and every row carries the block-end stabiliser), the weight of
         // the inbound-state step of FWDC (exp(A_prev_block_end - A_row) / sqrt(D); -inf when there is no carry)
-        // and the additive term of DQ
-        auto row_terms = [&](const Item& it, double& er_d, float& er_state, float& g_row) {
+        // and the additive term of DQ.  Fetching (the loads) and combining (the first use of what was loaded) are
+        // separate steps: the next item's terms are requested before the accumulator wait of this item and combined
+        // only when that item starts, so nobody waits for those loads.
+        struct RowRaw {
+            float rel, g;
+            double ref, b0, b1;
+        };
+        auto fetch_rows = [&](const Item& it) {
+            RowRaw rr{0.0f, 0.0f, 0.0, 0.0, 0.0};
             const int grow = it.tile * TILE + r;
             const size_t vec_base = static_cast<size_t>(it.bh) * p.Spad;
-            const size_t ref_base = static_cast<size_t>(it.bh) * (p.Spad / REF_BLOCK);
-            const double* bound =
-                (MODE == FWDC || MODE == STATE) ? p.An_bound + static_cast<size_t>(it.bh) * (p.NB + 1) + it.blk : nullptr;
-            er_d = (MODE == STATE) ? bound[1]
-                                   : static_cast<double>(p.row_rel[vec_base + grow]) + p.row_ref[ref_base + grow / REF_BLOCK] +
-                                         static_cast<double>(p.er_add);
-            er_state = (MODE == FWDC) ? static_cast<float>(er_d - bound[0]) : 0.0f;
-            g_row = (MODE == DQ) ? p.row_g[vec_base + grow] : 0.0f;
+            if (MODE == FWDC || MODE == STATE) {
+                const double* bound = p.An_bound + static_cast<size_t>(it.bh) * (p.NB + 1) + it.blk;
+                rr.b0 = bound[0];
+                rr.b1 = bound[1];
+            }
+            if (MODE != STATE) {
+                rr.rel = p.row_rel[vec_base + grow];
+                rr.ref = p.row_ref[static_cast<size_t>(it.bh) * (p.Spad / REF_BLOCK) + grow / REF_BLOCK];
+            }
+            if (MODE == DQ) rr.g = p.row_g[vec_base + grow];
+            return rr;
         };
         constexpr int UNKNOWN = -2;
         int id = next_item(0, ok);
-        double er_d = 0.0;
-        float er_state = 0.0f, g_row = 0.0f;
-        if (ok && id >= 0) row_terms(decode(id), er_d, er_state, g_row);
+        RowRaw raw{0.0f, 0.0f, 0.0, 0.0, 0.0};
+        if (ok && id >= 0) raw = fetch_rows(decode(id));
 
         for (int n = 0; ok && id >= 0; n++) {
         const Item it = decode(id);
@@ -517,6 +526,9 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         const int grow = tile * TILE + r;              // row inside the slice (may be >= S in the last tile)
         const size_t vec_base = static_cast<size_t>(bh) * p.Spad;
         const size_t ref_base = static_cast<size_t>(bh) * (p.Spad / REF_BLOCK);
+        const double er_d = (MODE == STATE) ? raw.b1 : static_cast<double>(raw.rel) + raw.ref + static_cast<double>(p.er_add);
+        const float er_state = (MODE == FWDC) ? static_cast<float>(er_d - raw.b0) : 0.0f;
+        const float g_row = raw.g;
         float rowsum = 0.0f;
 
         for (int t = 0; t < nsteps; t++) {
@@ -642,13 +654,14 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 if (ok && grp == 0 && p.b_out) p.b_out[(static_cast<size_t>(bh) * p.NB + blk) * D + r] = zsum;
             }
             if (IS_FWD) {
+                // on its way during the exchange
+                const float mrow = (!SPLIT && row_ok) ? p.m[static_cast<size_t>(bh) * p.S + grow] : 0.0f;
                 const float bsum = exchange(rowsum);
                 if (ok) {
                     if constexpr (SPLIT) {
                         // partial row sum of this contraction slice; the normaliser is applied afterwards
                         if (grp == 0 && row_ok && vslice == 0) atomicAdd(&p.b_out[static_cast<size_t>(bh) * p.S + grow], bsum);
                     } else {
-                        const float mrow = row_ok ? p.m[static_cast<size_t>(bh) * p.S + grow] : 0.0f;
                         const float nrm = fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f;
                         inv_n = 1.0f / nrm;
                         if (grp == 0 && row_ok && p.b_out) p.b_out[static_cast<size_t>(bh) * p.S + grow] = bsum;
@@ -667,11 +680,10 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         if (!ok) break;
         // next work item, if it is published already, and its row terms
         int id_next = UNKNOWN;
-        double er_next = 0.0;
-        float es_next = 0.0f, g_next = 0.0f;
+        RowRaw raw_next{0.0f, 0.0f, 0.0, 0.0, 0.0};
         if (__all_sync(0xffffffffu, mbar_test_wait(&bar_item[(n + 1) & 3], ((n + 1) >> 2) & 1) ? 1 : 0)) {
             id_next = __shfl_sync(0xffffffffu, item_ids[(n + 1) & 3], 0);
-            if (id_next >= 0) row_terms(decode(id_next), er_next, es_next, g_next);
+            if (id_next >= 0) raw_next = fetch_rows(decode(id_next));
         }
 
         // ---- epilogue: each group drains a quarter of the accumulator's columns for all 128 rows
@@ -806,12 +818,10 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         // ---- on to the next item
         if (id_next == UNKNOWN) {
             id_next = next_item(n + 1, ok);
-            if (ok && id_next >= 0) row_terms(decode(id_next), er_next, es_next, g_next);
+            if (ok && id_next >= 0) raw_next = fetch_rows(decode(id_next));
         }
         id = id_next;
-        er_d = er_next;
-        er_state = es_next;
-        g_row = g_next;
+        raw = raw_next;
         }  // items
         if (STAGED && lane == 0) bulk_wait_all();   // the last stores have left shared memory before the CTA goes away
         tc_fence_before();

@@ -360,22 +360,29 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         uint8_t* stage = sOut + (warp - 2) * STAGE_BYTES;
         if (lane == 0) prefetch_tmap(&tmO);
 
-        // row terms of a work item: the row part of the exponent (double) and the DQ additive term
-        auto row_terms = [&](const Item& it, double& er_d, float& g_row) {
-            const int grow = it.tile * TILE + r;
-            const bool active = it.tile < NT;
-            const size_t vec_base = static_cast<size_t>(it.bh) * p.Spad;
-            const size_t ref_base = static_cast<size_t>(it.bh) * (p.Spad / REF_BLOCK);
-            er_d = active ? static_cast<double>(p.row_rel[vec_base + grow]) + p.row_ref[ref_base + grow / REF_BLOCK] +
-                                static_cast<double>(p.er_add)
-                          : 0.0;
-            g_row = (MODE == DQ && active) ? p.row_g[vec_base + grow] : 0.0f;
+        // Row terms of a work item: the row part of the exponent (a float relative to a double block reference,
+        // added up in double) and the DQ additive term.  Fetching (the loads) and combining (the first use of what
+        // was loaded) are separate steps: the next item's terms are requested before the accumulator wait of this
+        // item and combined only when that item starts, so nobody waits for those loads.
+        struct RowRaw {
+            float rel, g;
+            double ref;
+        };
+        auto fetch_rows = [&](const Item& it) {
+            RowRaw rr{0.0f, 0.0f, 0.0};
+            if (it.tile < NT) {
+                const int grow = it.tile * TILE + r;
+                const size_t vec_base = static_cast<size_t>(it.bh) * p.Spad;
+                rr.rel = p.row_rel[vec_base + grow];
+                rr.ref = p.row_ref[static_cast<size_t>(it.bh) * (p.Spad / REF_BLOCK) + grow / REF_BLOCK];
+                if (MODE == DQ) rr.g = p.row_g[vec_base + grow];
+            }
+            return rr;
         };
         constexpr int UNKNOWN = -2;
         int id = next_item_warp(0, ok);
-        double er_d = 0.0;
-        float g_row = 0.0f;
-        if (ok && id >= 0) row_terms(decode(id), er_d, g_row);
+        RowRaw raw{0.0f, 0.0f, 0.0};
+        if (ok && id >= 0) raw = fetch_rows(decode(id));
 
         for (int n = 0; ok && id >= 0; n++) {
         const Item it = decode(id);
@@ -384,6 +391,8 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         const int grow = tile * TILE + r;
         const size_t vec_base = static_cast<size_t>(bh) * p.Spad;
         const size_t ref_base = static_cast<size_t>(bh) * (p.Spad / REF_BLOCK);
+        const double er_d = active ? static_cast<double>(raw.rel) + raw.ref + static_cast<double>(p.er_add) : 0.0;
+        const float g_row = raw.g;
         float rowsum = 0.0f;
 
         for (int t = 0; t < nsteps; t++) {
@@ -475,9 +484,9 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             return ok ? (part[r] + part[128 + r]) + (part[256 + r] + part[384 + r]) : 0.0f;
         };
         auto fwd_norm = [&]() {
+            const float mrow = row_ok ? p.m[static_cast<size_t>(bh) * p.S + grow] : 0.0f;   // on its way during the exchange
             const float bsum = exchange(rowsum);
             if (ok) {
-                const float mrow = row_ok ? p.m[static_cast<size_t>(bh) * p.S + grow] : 0.0f;
                 inv_n = 1.0f / (fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f);
                 if (grp == 0 && row_ok && p.b_out) p.b_out[static_cast<size_t>(bh) * p.S + grow] = bsum;
             }
@@ -490,11 +499,10 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         if (!ok) break;
         // next work item, if it is published already, and its row terms
         int id_next = UNKNOWN;
-        double er_next = 0.0;
-        float g_next = 0.0f;
+        RowRaw raw_next{0.0f, 0.0f, 0.0};
         if (__all_sync(0xffffffffu, mbar_test_wait_cluster(&bar_item[(n + 1) & 3], ((n + 1) >> 2) & 1) ? 1 : 0)) {
             id_next = __shfl_sync(0xffffffffu, item_ids[(n + 1) & 3], 0);
-            if (id_next >= 0) row_terms(decode(id_next), er_next, g_next);
+            if (id_next >= 0) raw_next = fetch_rows(decode(id_next));
         }
 
         // ---- epilogue: each group drains a quarter of this CTA's accumulator columns
@@ -602,11 +610,10 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         // ---- on to the next item
         if (id_next == UNKNOWN) {
             id_next = next_item_warp(n + 1, ok);
-            if (ok && id_next >= 0) row_terms(decode(id_next), er_next, g_next);
+            if (ok && id_next >= 0) raw_next = fetch_rows(decode(id_next));
         }
         id = id_next;
-        er_d = er_next;
-        g_row = g_next;
+        raw = raw_next;
         }  // items
         if (lane == 0) bulk_wait_all();   // the last stores have left shared memory before the CTA goes away
         tc_fence_before();
