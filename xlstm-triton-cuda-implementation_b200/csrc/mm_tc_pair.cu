@@ -48,7 +48,7 @@ constexpr int SLOT_BYTES = 32 * 1024;          // Y half: 64 rows x 256 cols; Z 
 constexpr int NSLOT = 4;                       // two steps of streamed tiles
 constexpr int STAGE_BYTES = 2048;              // per gate warp: 32 rows x 64 bytes of output on their way to a TMA store
 constexpr int OUT_BYTES = (NGATE / 32) * STAGE_BYTES;
-constexpr int NBAR = 1 + 2 * NSLOT + 2 + 2 + 1 + 1 + 2 + 4;
+constexpr int NBAR = 1 + 2 * NSLOT + 2 + 2 + 1 + 1 + 2 + 4 + 4;
 constexpr int SMEM_BYTES = X_BYTES + NSLOT * SLOT_BYTES + OUT_BYTES + NBAR * 8 + 64 + NGROUPS * 128 * 4;
 constexpr long long WAIT_LIMIT = 4000000000LL;
 constexpr float MAX_ROW_EXP2 = 60.0f;           // clamp of the per-row exponent off the diagonal tile (see its use)
@@ -108,10 +108,12 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     uint64_t* bar_part = bar_acc + 1;           // own: row partials exchanged
     uint64_t* bar_xfree = bar_part + 1;         // both: stationary tiles no longer read
     uint64_t* bar_accfree = bar_xfree + 1;      // leader: accumulators of both CTAs drained (32 warp arrivals)
-    uint64_t* bar_item = bar_accfree + 1;       // both [4]: work item published
+    uint64_t* bar_item = bar_accfree + 1;       // both [4]: work item published inside the CTA (by its own producer)
+    uint64_t* bar_item_in = bar_item + 4;       // follower [4]: work item arrived from the leader's producer
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBAR);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    volatile int* item_ids = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    volatile int* item_ids = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [4] ring read by this CTA's roles
+    volatile int* item_in = reinterpret_cast<volatile int*>(tmem_slot + 6);    // [4] ring written by the leader (follower only)
     float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + NBAR * 8 + 64);  // [NGROUPS][128]
 
     const int warp = threadIdx.x >> 5;
@@ -160,7 +162,10 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         mbar_init(bar_acc, 1);
         mbar_init(bar_accfree, 2 * NGATE / 32);
         mbar_init(bar_part, NGATE / 32);
-        for (int k = 0; k < 4; k++) mbar_init(&bar_item[k], 1);
+        for (int k = 0; k < 4; k++) {
+            mbar_init(&bar_item[k], 1);
+            mbar_init(&bar_item_in[k], 1);
+        }
         *abort_flag = misaligned ? 1 : 0;
         fence_mbar_init();
     }
@@ -176,12 +181,11 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     const uint32_t tmem_T0 = tmem_base;
     const uint32_t tmem_ACC = tmem_base + 256;
 
-    auto next_item = [&](int n, bool& ok) {        // one thread (the follower's producer)
-        ok = mbar_wait_cluster<SLACK_SLEEP_NS>(&bar_item[n & 3], (n >> 2) & 1, abort_flag, WAIT_LIMIT);
-        return ok ? item_ids[n & 3] : -1;
-    };
+    // Work items cross the pair once, from the leader's producer to the follower's (an ordinary shared-memory word
+    // written remotely: cluster-scope release / acquire, which costs a thousand cycles and more); each producer
+    // then publishes the item inside its own CTA, where the other roles get it with CTA-scope waits.
     auto next_item_warp = [&](int n, bool& ok) {   // gate warps (converged)
-        ok = mbar_wait_cluster_warp<SLACK_SLEEP_NS>(&bar_item[n & 3], (n >> 2) & 1, abort_flag, WAIT_LIMIT);
+        ok = mbar_wait_warp<SLACK_SLEEP_NS>(&bar_item[n & 3], (n >> 2) & 1, abort_flag, WAIT_LIMIT);
         return ok ? __shfl_sync(0xffffffffu, item_ids[n & 3], 0) : -1;
     };
 
@@ -199,13 +203,14 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                 if (rank == 0) {
                     id = atomicAdd(p.sched + MODE, 1);
                     if (id >= total) id = -1;
-                    item_ids[n & 3] = id;
-                    st_cluster_u32(at_peer(const_cast<int*>(&item_ids[n & 3])), static_cast<uint32_t>(id));
-                    mbar_arrive(&bar_item[n & 3]);
-                    mbar_arrive_cluster(at_peer(&bar_item[n & 3]));   // release at cluster scope: the peer sees the id
+                    st_cluster_u32(at_peer(const_cast<int*>(&item_in[n & 3])), static_cast<uint32_t>(id));
+                    mbar_arrive_cluster(at_peer(&bar_item_in[n & 3]));   // release at cluster scope: the peer sees the id
                 } else {
-                    id = next_item(n, ok);
+                    ok = mbar_wait_cluster<SLACK_SLEEP_NS>(&bar_item_in[n & 3], (n >> 2) & 1, abort_flag, WAIT_LIMIT);
+                    id = ok ? item_in[n & 3] : -1;
                 }
+                item_ids[n & 3] = id;
+                mbar_arrive(&bar_item[n & 3]);   // CTA-scope release: this CTA's roles see the id
                 if (id < 0) break;
                 const Item it = decode(id);
                 ok = mbar_wait<SLACK_SLEEP_NS>(bar_xfree, (n & 1) ^ 1, abort_flag, WAIT_LIMIT);
@@ -271,7 +276,7 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             int gstep = 0;
             bool ok = __all_sync(0xffffffffu, *abort_flag ? 0 : 1) != 0;
             for (int n = 0; ok; n++) {
-                ok = mbar_wait_cluster_warp(&bar_item[n & 3], (n >> 2) & 1, abort_flag, WAIT_LIMIT);
+                ok = wait_u(&bar_item[n & 3], (n >> 2) & 1);
                 if (!ok) break;
                 const int id = uni(item_ids[n & 3]);
                 if (id < 0) break;
@@ -500,7 +505,7 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         // next work item, if it is published already, and its row terms
         int id_next = UNKNOWN;
         RowRaw raw_next{0.0f, 0.0f, 0.0};
-        if (__all_sync(0xffffffffu, mbar_test_wait_cluster(&bar_item[(n + 1) & 3], ((n + 1) >> 2) & 1) ? 1 : 0)) {
+        if (__all_sync(0xffffffffu, mbar_test_wait(&bar_item[(n + 1) & 3], ((n + 1) >> 2) & 1) ? 1 : 0)) {
             id_next = __shfl_sync(0xffffffffu, item_ids[(n + 1) & 3], 0);
             if (id_next >= 0) raw_next = fetch_rows(decode(id_next));
         }
