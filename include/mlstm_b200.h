@@ -5,11 +5,15 @@
  * [B, NH, S] for f, i, m, b and their gradients (the reference's hand-computed offsets,
  * mlstm_matmul.py:46-55).  Every entry point only enqueues work on `stream` (a cudaStream_t passed
  * as void*; NULL = the default stream) and returns at once with 0 or a negative MLSTM_E_* code; it
- * never prints, aborts or synchronises.  The library is stateless: scratch memory is a caller-owned
- * workspace whose size the matching *_workspace() function reports (pass it the same flags as the call:
- * fp32 inputs on the tensor cores need room for tf32-rounded copies of the operands).  The first 256 bytes of a
- * workspace hold a device status word that kernels set when they give up on an internal wait;
- * mlstm_read_status() copies it to the host (this one call synchronises the stream).
+ * never prints, aborts or synchronises.  Scratch memory is a caller-owned workspace whose size the
+ * matching *_workspace() function reports (pass it the same flags as the call: fp32 inputs on the
+ * tensor cores need room for converted copies of the operands).  Between calls the library keeps no
+ * device state of its own, with one exception: mlstm_forward_f16_static() works in a fixed array
+ * inside the library's device image (see there).  Host-side caches (tensor-map encoder entry point,
+ * per-device kernel attributes) are guarded for concurrent callers.
+ * The first 256 bytes of a workspace hold a device status word that kernels set when they give up on
+ * an internal wait; mlstm_read_status() copies it to the host (this one call synchronises the stream);
+ * mlstm_forward_f16_static_status() does the same for the built-in array.
  */
 #ifndef MLSTM_B200_H
 #define MLSTM_B200_H
@@ -49,7 +53,7 @@ const char* mlstm_last_error_detail(void);
 
 /* Whether the tcgen05 path handles this case (D in {64, 128, 256}): 1 for 16-bit inputs, 2 for fp32
  * inputs (used only with MLSTM_F_ALLOW_TF32), else 0.  The scan entry also takes D = 512 .. 4096 in
- * multiples of 256 on the tensor cores (sliced forward). */
+ * multiples of 256 on the tensor cores (two-pass forward). */
 int mlstm_tc_supported(int S, int D, int dtype);
 
 /* Parallel (matmul) forward.
@@ -80,11 +84,23 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
  * Replaces the four launches of mlstm_scan (mlstm_scan.py:281-327): stabilize_fi (:47-69),
  * precompute_mlstm_triton_scan (:74-137), reduce_mlstm_triton (:143-195), mlstm_triton_scan
  * (:200-278).  q, k, v, o [B,NH,S,D], f, i [B,NH,S] of `dtype`; h fp32 [B,NH,S,D].
+ * Three forms, chosen by shape: head dimensions above 256 (the reference demo, D = 1024) run as two
+ * tensor-core passes (gated S x S matrix once, then W V); sequences much longer than the head dimension
+ * run chunkwise (per-block states, inter-block carry, output from the carried state; 16-bit, D = 128);
+ * everything else is the parallel forward with the output gate in its epilogue.
  */
 size_t mlstm_scan_fwd_workspace(int B, int NH, int S, int D, int dtype, int flags);
 int mlstm_scan_fwd(const void* q, const void* k, const void* v, const void* f, const void* i, const void* o,
                    void* h, void* workspace, size_t workspace_bytes, int B, int NH, int S, int D, int dtype,
                    int flags, void* stream);
+
+/* Output gate as a step of its own, for the training path: h = h_inner * silu(o) and its derivative
+ * dh_inner = dh * silu(o), d_o = dh * h_inner * silu'(o), over n elements (what the reference leaves open at
+ * mlstm_matmul.py:36 "Integrate o" and computes only in the forward scan, mlstm_scan.py:273-278).
+ * h_inner, h, dh, dh_inner of `h_dtype`; o, d_o of `o_dtype` (h_dtype fp32 with any o_dtype, or both equal). */
+int mlstm_ogate_fwd(const void* h_inner, const void* o, void* h, long long n, int h_dtype, int o_dtype, void* stream);
+int mlstm_ogate_bwd(const void* dh, const void* h_inner, const void* o, void* dh_inner, void* d_o, long long n, int h_dtype,
+                    int o_dtype, void* stream);
 
 /* Single-head fp16 forward of the C++ driver.
  * Replaces the launch mlstm_forward<64,16,128,16,8,8><<<S/64,128,smem>>>(Q,K,V,F,I,H,S)
@@ -98,8 +114,8 @@ int mlstm_forward_f16(const void* Q, const void* K, const void* V, const void* F
  * dH, Q, K, V [S,D] half and F, I [S] half.
  * Replaces the two launches matmul_backward_db<64,16,128,16,8,8><<<S/64,128,smem>>>(dH,Q,K,V,F,I,M,B,dB,S) and
  * matmul_backward<...><<<S/64,128,smem>>>(dH,dB,Q,K,V,dQ,dK,dV,F,I,dI,M,B,S) (cuda-src/mlstm_backward.cu:11-12,
- * 177-178, 621-628) and the never-instantiated backward_df (:507-540).  The reference's kernels stop at dB, dQ and
- * dK (dV is a TODO there, :497-499, and dI / dF are not finished); they take M and B from a host computation.
+ * 177-178, 621-628) and the never-instantiated backward_df (:525-558).  The reference's kernels stop at dB, dQ and
+ * dK (dV is a TODO there, :506-508, and dI / dF are not finished); they take M and B from a host computation.
  * Here the forward is recomputed inside the call for h, m and b, so the argument list needs neither.
  */
 size_t mlstm_backward_f16_workspace(unsigned S, unsigned D);
@@ -120,24 +136,29 @@ int mlstm_backward_f16(const void* dH, const void* Q, const void* K, const void*
  *     that device current): make that first call outside any stream capture;
  *   - it calls no cudaMalloc, cudaFree or other allocating routine, on any call;
  *   - all calls on a device share the one array; calls whose kernels may overlap on the GPU race.
- *     Order them on one stream or with events. */
+ *     Order them on one stream or with events;
+ *   - the array starts with the same status word as a workspace; because its address is private to
+ *     the library, mlstm_forward_f16_static_status() reads it (after synchronising `stream`):
+ *     MLSTM_OK, or MLSTM_E_TIMEOUT with the kernel's code in *host_status. */
 #define MLSTM_STATIC_MAX_S 16384u
-#define MLSTM_STATIC_SCRATCH_BYTES 266496u
+#define MLSTM_STATIC_SCRATCH_BYTES 332032u /* forward scratch of one head at S = MLSTM_STATIC_MAX_S */
 int mlstm_forward_f16_static(const void* Q, const void* K, const void* V, const void* F, const void* I, void* H,
                              unsigned S, unsigned D, void* stream);
+int mlstm_forward_f16_static_status(int* host_status, void* stream);
 
 /* Chunkwise forward for long sequences, with a state that can be carried across segments (GPUs).
  * The reference has no such entry point; the mechanism it extends is the scan path's inter-block carry
  * (mlstm_scan.py:143-195, operators :15-26).  16-bit inputs, D = 128, chunk a multiple of 128.
+ * mlstm_scan_fwd uses it by itself for sequences much longer than the head dimension.
  * A segment is processed in this order (all on one stream, one workspace):
- *   mlstm_chunk_gate_summary  (optional, sequence-parallel only) local {F_end, A_end} per slice with no
- *                             carry, from which the caller derives every segment's carry_in
+ *   mlstm_chunk_gate_summary  (optional) local {F_end, A_end} per slice with no carry
  *   mlstm_chunk_prepare       gates (with carry_in[bh] = {F, A} of the preceding segments, or NULL) and
- *                             the per-block states; summary_out[bh] = {F_end, A_end} incl. the carry
+ *                             the per-block states; summary_out[bh] = {F_end, A_end} incl. the carry (or NULL)
  *   mlstm_chunk_local_state   (optional) the state this segment adds: S_end [B,NH,D,D] (key, value),
  *                             z_end [B,NH,D], stabilised by A_end
- *   mlstm_chunk_apply         h for the segment, given the inbound state (S_in, z_in stabilised by the
- *                             carried-in A, or NULL/NULL); optionally the outbound state S_out, z_out
+ *   mlstm_chunk_apply         h for the segment (times silu(o) when o is given), given the inbound state
+ *                             (S_in, z_in stabilised by the carried-in A, or NULL/NULL); optionally the
+ *                             outbound state S_out, z_out
  * summary / carry arrays are device doubles [B*NH][2] in natural-log units. */
 size_t mlstm_chunk_workspace(int B, int NH, int S, int D, int dtype, int chunk);
 int mlstm_chunk_gate_summary(const void* f, const void* i, double* summary, void* workspace, size_t workspace_bytes,
@@ -147,13 +168,39 @@ int mlstm_chunk_prepare(const void* k, const void* v, const void* f, const void*
                         int dtype, int chunk, void* stream);
 int mlstm_chunk_local_state(void* workspace, size_t workspace_bytes, float* S_end, float* z_end, int B, int NH, int S,
                             int D, int dtype, int chunk, void* stream);
-int mlstm_chunk_apply(const void* q, const void* k, const void* v, const float* S_in, const float* z_in, void* h,
-                      int h_dtype, float* S_out, float* z_out, void* workspace, size_t workspace_bytes, int B, int NH,
-                      int S, int D, int dtype, int chunk, void* stream);
+int mlstm_chunk_apply(const void* q, const void* k, const void* v, const void* o, const float* S_in, const float* z_in,
+                      void* h, int h_dtype, float* S_out, float* z_out, void* workspace, size_t workspace_bytes, int B,
+                      int NH, int S, int D, int dtype, int chunk, void* stream);
+
+/* Sequence-parallel form of the chunkwise forward: rank r of `world` holds the r-th contiguous segment
+ * of every sequence, and ONE exchange connects the ranks (the carry combine of mlstm_scan.py:15-26
+ * applied to whole segments; SURVEY of the reference: no multi-GPU code exists there).
+ *   mlstm_chunk_sp_local   everything that needs no other rank: gates, per-block states, and this
+ *                          segment's record [B*NH][mlstm_chunk_sp_record_floats(D)] fp32 =
+ *                          S (D*D, key-major) | z (D) | {F_end, A_end} as two doubles; the state is
+ *                          stabilised by the segment's own prefix maximum and F counts from zero
+ *   -- the caller all-gathers the records into gathered[world][B*NH][record] (NCCL, or any copy) --
+ *   mlstm_chunk_sp_apply   folds the records of the lower ranks into this segment's inbound state and
+ *                          carry (one kernel), carries it through the blocks and writes h (times
+ *                          silu(o) when o is given).  carry_out (optional): {F_in, A_in} per slice.
+ * Both calls use the same workspace (mlstm_chunk_workspace) and stream. */
+size_t mlstm_chunk_sp_record_floats(int D);
+int mlstm_chunk_sp_local(const void* k, const void* v, const void* f, const void* i, float* record, void* workspace,
+                         size_t workspace_bytes, int B, int NH, int S, int D, int dtype, int chunk, void* stream);
+int mlstm_chunk_sp_apply(const void* q, const void* k, const void* v, const void* o, const float* gathered, int world,
+                         int rank, void* h, int h_dtype, double* carry_out, void* workspace, size_t workspace_bytes,
+                         int B, int NH, int S, int D, int dtype, int chunk, void* stream);
 
 /* Copies the workspace's device status word to *host_status after synchronising `stream`.
  * Returns MLSTM_OK, or MLSTM_E_TIMEOUT when the word is non-zero, or MLSTM_E_CUDA. */
 int mlstm_read_status(const void* workspace, int* host_status, void* stream);
+
+/* Self-test of the bounded waits (no counterpart in the reference, whose kernels have no waits to bound):
+ * one warp waits on a barrier that nothing completes, gives up after `limit_cycles` SM cycles (1 ..
+ * 2e9; a few million = about a millisecond) and stores the code 4000 in the workspace's status word,
+ * exactly as a contraction kernel does when one of its waits runs out.  mlstm_read_status() then returns
+ * MLSTM_E_TIMEOUT, and the device stays usable.  `workspace`: at least 256 bytes. */
+int mlstm_selftest_wait_timeout(void* workspace, size_t workspace_bytes, long long limit_cycles, void* stream);
 
 #ifdef __cplusplus
 }

@@ -66,8 +66,8 @@ def backward(dh, q, k, v, f, i, h, m, b, round_w=None):
 
 class ChunkSegmentModel:
     """Dense fp64 model of the chunkwise segment stages (same interface as the library's
-    ChunkSegment: gate_summary / prepare / local_state / apply), used to test the sequence-parallel
-    protocol on CPU.  State convention as in the library: S[key, value] = sum_j exp(a_j - A_ref) k_j v_j^T,
+    ChunkSegment: gate_summary / prepare / local_state / apply and sp_local / sp_apply), used to test
+    the sequence-parallel protocol on CPU.  State convention as in the library: S[key, value] = sum_j exp(a_j - A_ref) k_j v_j^T,
     z[key] = sum_j exp(a_j - A_ref) k_j, with a = i - F in global terms and A its prefix maximum."""
 
     def __init__(self, q, k, v, f, i, chunk_size=256):
@@ -116,3 +116,19 @@ class ChunkSegmentModel:
         m = self.Fc + self.A
         n = torch.maximum(b.abs(), torch.exp(-m)) + 1e-6
         return (num / n[..., None]).reshape(B, NH, S, D).to(h_dtype)
+
+    # ---- the two stages of the one-exchange sequence-parallel protocol
+    def sp_local(self):
+        """Record per slice: S | z | {F_end, A_end} with no carry (the segment's own coordinates)."""
+        summary = self.prepare(None)                                             # [BH, 2] float64
+        S, z = self.local_state()
+        BH, D = z.shape
+        tail = summary.contiguous().view(torch.float32).reshape(BH, 4)
+        return torch.cat([S.reshape(BH, D * D), z, tail], 1)
+
+    def sp_apply(self, gathered, rank, h_dtype=torch.float32):
+        import importlib
+        mc = importlib.import_module("xlstm-triton-cuda-implementation_b200.mlstm_chunkwise")
+        S_in, z_in, F_in, A_in = mc.fold_records(gathered, rank)
+        self.prepare(torch.stack([F_in, A_in], 1))                               # gates again, now with the carry
+        return self.apply((S_in, z_in) if rank > 0 else None, h_dtype=h_dtype)

@@ -1,4 +1,4 @@
-"""CPU tests of the chunkwise / sequence-parallel host logic: the carry folds and the two-all-gather
+"""CPU tests of the chunkwise / sequence-parallel host logic: the carry folds and the one-all-gather
 protocol, driven over gloo with a dense fp64 model of the per-segment stages."""
 import importlib
 import os
@@ -46,6 +46,19 @@ def test_folds_reproduce_the_full_sequence(cuts):
     A_end = torch.stack([s[:, 1] for s in summaries])
     assert (A_end[1:] >= A_end[:-1]).all()
     h = torch.cat([s.apply(mc.fold_states(S_all, z_all, A_end, g), h_dtype=torch.float64) for g, s in enumerate(segs)], 2)
+    assert orc.max_abs_rel(h, orc.matmul_forward(*x)) < 1e-5   # the carried state passes through float32
+
+
+@pytest.mark.parametrize("cuts", [(40,), (17, 60), (32, 33, 80)])
+def test_record_fold_reproduces_the_full_sequence(cuts):
+    """Serial emulation of the one-exchange protocol: every segment's record with no carry, fold_records,
+    apply; compare with the unsplit oracle."""
+    x = _inputs(1, 2, 96, 16, 2.0, 4)
+    S = x[0].shape[2]
+    edges = (0,) + tuple(cuts) + (S,)
+    segs = [km.ChunkSegmentModel(*[t[:, :, a:b] for t in x]) for a, b in zip(edges[:-1], edges[1:])]
+    gathered = torch.stack([s.sp_local() for s in segs])
+    h = torch.cat([s.sp_apply(gathered, g, h_dtype=torch.float64) for g, s in enumerate(segs)], 2)
     assert orc.max_abs_rel(h, orc.matmul_forward(*x)) < 1e-5   # the carried state passes through float32
 
 

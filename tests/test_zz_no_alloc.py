@@ -10,6 +10,8 @@ result with the workspace-taking entry point, which runs the same kernels on cal
 The file name sorts last on purpose: a run that stops at the first failure has then already run
 every other test.
 """
+import ctypes
+
 import pytest
 import torch
 
@@ -64,6 +66,40 @@ def test_static_scratch_forward_matches_workspace_forward_twice(gc):
         # the reference driver's own comparator: no element further than 0.01 away
         assert float((got.float() - want.float()).abs().max()) <= 0.01
         assert torch.equal(got, want)  # same kernels, same inputs: in fact identical
+
+
+def test_static_scratch_matches_reference_golden(gc, golden_dir):
+    """The reference driver's own inputs (srand(100) recipe) against the output of the reference's host
+    forward, with the reference's comparator (no element further than 0.01 away)."""
+    import numpy as np
+    z = np.load(f"{golden_dir}/cpp_forward_seed100_s640_d128.npz")
+    dev = torch.device("cuda", 0)
+    args = [torch.from_numpy(z[k]).to(dev) for k in ("Q", "K", "V", "F", "I")]
+    got = _static(gc, *args)
+    diff = (got.float().cpu() - torch.from_numpy(z["H"]).float()).abs()
+    assert int((diff > 0.01).sum()) == 0, float(diff.max())
+    code = ctypes.c_int(-1)
+    assert gc._lib.lib().mlstm_forward_f16_static_status(ctypes.byref(code), gc._lib.stream_ptr(dev)) == 0
+    assert code.value == 0
+
+
+def test_static_scratch_at_its_length_limit(gc):
+    """S = MLSTM_STATIC_MAX_S must be served (the array is sized from the forward's real scratch layout);
+    checked against the workspace entry on all rows and against the CPU oracle on a causal prefix."""
+    from oracle import mlstm_oracle as orc
+    dev = torch.device("cuda", 0)
+    S, D = 16384, 128
+    args = _inputs(S, D, 7, dev)
+    got = _static(gc, *args)
+    want = _with_workspace(gc, *args)
+    assert torch.equal(got, want)
+    P = 1024   # h[:P] depends on positions < P only
+    ref = orc.mlstm_cpu_f16(*(a[:P].cpu() for a in args))
+    diff = (got[:P].float().cpu() - ref.float()).abs()
+    assert int((diff > 0.01).sum()) == 0, float(diff.max())
+    code = ctypes.c_int(-1)
+    assert gc._lib.lib().mlstm_forward_f16_static_status(ctypes.byref(code), gc._lib.stream_ptr(dev)) == 0
+    assert code.value == 0
 
 
 def test_static_scratch_rejects_long_sequences(gc):

@@ -77,7 +77,21 @@ def lib():
     L.mlstm_chunk_local_state.restype = i32
     L.mlstm_chunk_local_state.argtypes = [vp, sz, vp, vp] + [i32] * 6 + [vp]
     L.mlstm_chunk_apply.restype = i32
-    L.mlstm_chunk_apply.argtypes = [vp] * 6 + [i32, vp, vp, vp, sz] + [i32] * 6 + [vp]
+    L.mlstm_chunk_apply.argtypes = [vp] * 7 + [i32, vp, vp, vp, sz] + [i32] * 6 + [vp]
+    L.mlstm_chunk_sp_record_floats.restype = sz
+    L.mlstm_chunk_sp_record_floats.argtypes = [i32]
+    L.mlstm_chunk_sp_local.restype = i32
+    L.mlstm_chunk_sp_local.argtypes = [vp] * 5 + [vp, sz] + [i32] * 6 + [vp]
+    L.mlstm_chunk_sp_apply.restype = i32
+    L.mlstm_chunk_sp_apply.argtypes = [vp] * 5 + [i32, i32, vp, i32, vp, vp, sz] + [i32] * 6 + [vp]
+    L.mlstm_forward_f16_static_status.restype = i32
+    L.mlstm_forward_f16_static_status.argtypes = [ctypes.POINTER(i32), vp]
+    L.mlstm_ogate_fwd.restype = i32
+    L.mlstm_ogate_fwd.argtypes = [vp, vp, vp, ctypes.c_longlong, i32, i32, vp]
+    L.mlstm_ogate_bwd.restype = i32
+    L.mlstm_ogate_bwd.argtypes = [vp] * 5 + [ctypes.c_longlong, i32, i32, vp]
+    L.mlstm_selftest_wait_timeout.restype = i32
+    L.mlstm_selftest_wait_timeout.argtypes = [vp, sz, ctypes.c_longlong, vp]
     L.mlstm_read_status.restype = i32
     L.mlstm_read_status.argtypes = [vp, ctypes.POINTER(i32), vp]
     _lib = L
@@ -90,7 +104,8 @@ EXPORTS = [
     "mlstm_forward_f16_workspace", "mlstm_forward_f16", "mlstm_forward_f16_static", "mlstm_backward_f16_workspace",
     "mlstm_backward_f16", "mlstm_read_status",
     "mlstm_chunk_workspace", "mlstm_chunk_gate_summary", "mlstm_chunk_prepare", "mlstm_chunk_local_state",
-    "mlstm_chunk_apply",
+    "mlstm_chunk_apply", "mlstm_chunk_sp_record_floats", "mlstm_chunk_sp_local", "mlstm_chunk_sp_apply",
+    "mlstm_forward_f16_static_status", "mlstm_selftest_wait_timeout", "mlstm_ogate_fwd", "mlstm_ogate_bwd",
 ]
 
 

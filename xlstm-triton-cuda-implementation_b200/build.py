@@ -13,7 +13,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmlstm_b200.so")
-SOURCES = ["capi.cu", "chunk.cu", "gates.cu", "mm_simt.cu", "mm_tc.cu", "mm_tc_pair.cu"]
+SOURCES = ["capi.cu", "chunk.cu", "gates.cu", "mm_simt.cu", "mm_tc.cu", "mm_tc_pair.cu", "scan_gemm.cu", "selftest.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

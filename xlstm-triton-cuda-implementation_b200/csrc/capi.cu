@@ -10,7 +10,7 @@ namespace mlstm {
 namespace {
 
 constexpr size_t WS_ALIGN = 256;
-inline size_t al(size_t x) { return (x + WS_ALIGN - 1) / WS_ALIGN * WS_ALIGN; }
+constexpr size_t al(size_t x) { return (x + WS_ALIGN - 1) / WS_ALIGN * WS_ALIGN; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline size_t esize(int dt) { return dt == MLSTM_DT_F32 ? 4 : 2; }
 inline bool dtype_ok(int dt) { return dt == MLSTM_DT_F32 || dt == MLSTM_DT_F16 || dt == MLSTM_DT_BF16; }
@@ -33,22 +33,44 @@ struct FwdWs {
     double *a_ref, *An_ref;
     size_t bytes;
 };
-// with_mb: also carve m and b (entry points whose caller does not pass them)
+// Byte offsets of the forward scratch, usable at compile time (the built-in scratch of
+// mlstm_forward_f16_static is sized from it).  with_mb: also m and b (entry points whose caller does not pass them).
+struct FwdLayout {
+    size_t ga, gAn, gaw, a_ref, An_ref, m, b, bytes;
+};
+constexpr FwdLayout fwd_layout(size_t BH, size_t S, bool with_mb) {
+    FwdLayout l{};
+    const size_t spad = (S + TILE - 1) / TILE * TILE;
+    const size_t vec = BH * spad * sizeof(float);
+    size_t off = WS_ALIGN;   // status word and work-item counters
+    l.ga = off; off += al(vec);
+    l.gAn = off; off += al(vec);
+    l.gaw = off; off += al(vec);
+    l.a_ref = off; off += al(vec / REF_BLOCK * 2);
+    l.An_ref = off; off += al(vec / REF_BLOCK * 2);
+    l.m = off;
+    if (with_mb) off += al(BH * S * sizeof(float));
+    l.b = off;
+    if (with_mb) off += al(BH * S * sizeof(float));
+    l.bytes = off;
+    return l;
+}
 FwdWs carve_fwd(void* ws, int BH, int S, bool with_mb) {
-    Carver c(ws);
+    const FwdLayout l = fwd_layout(static_cast<size_t>(BH), static_cast<size_t>(S), with_mb);
+    uint8_t* base = static_cast<uint8_t*>(ws);
     FwdWs w{};
-    const size_t vec = static_cast<size_t>(BH) * round_up(S, TILE) * sizeof(float);
-    w.status = c.take<int>(WS_ALIGN);
-    w.ga = c.take<float>(vec);
-    w.gAn = c.take<float>(vec);
-    w.gaw = c.take<float>(vec);
-    w.a_ref = c.take<double>(vec / REF_BLOCK * 2);
-    w.An_ref = c.take<double>(vec / REF_BLOCK * 2);
+    w.bytes = l.bytes;
+    if (!base) return w;
+    w.status = reinterpret_cast<int*>(base);
+    w.ga = reinterpret_cast<float*>(base + l.ga);
+    w.gAn = reinterpret_cast<float*>(base + l.gAn);
+    w.gaw = reinterpret_cast<float*>(base + l.gaw);
+    w.a_ref = reinterpret_cast<double*>(base + l.a_ref);
+    w.An_ref = reinterpret_cast<double*>(base + l.An_ref);
     if (with_mb) {
-        w.m = c.take<float>(static_cast<size_t>(BH) * S * sizeof(float));
-        w.b = c.take<float>(static_cast<size_t>(BH) * S * sizeof(float));
+        w.m = reinterpret_cast<float*>(base + l.m);
+        w.b = reinterpret_cast<float*>(base + l.b);
     }
-    w.bytes = c.off;
     return w;
 }
 
@@ -104,8 +126,7 @@ bool use_tc(int S, int D, int dtype, int flags, int* rc) {
 
 // fp32 inputs on the tensor cores are first rounded to tf32 into workspace copies (n tensors)
 size_t tf32_copy_bytes(int BH, int S, int D, int dtype, int flags, int ntensors) {
-    const bool tc = (tc_supported(S, D, dtype) || tc_split_supported(S, D, dtype)) && (flags & MLSTM_F_ALLOW_TF32) &&
-                    !(flags & MLSTM_F_FORCE_SIMT);
+    const bool tc = tc_supported(S, D, dtype) && (flags & MLSTM_F_ALLOW_TF32) && !(flags & MLSTM_F_FORCE_SIMT);
     return (dtype == MLSTM_DT_F32 && tc) ? ntensors * al(static_cast<size_t>(BH) * S * D * sizeof(float)) : 0;
 }
 // rounds `count` tensors into consecutive regions of `buf` and redirects the pointers
@@ -268,15 +289,33 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     return launch_df(f, w.dI, w.R, df, di, BH, S, Spad, dtype, st);
 }
 
-// the sliced forward (head dimension above 256) also needs an fp32 numerator buffer [BH, S, D]
-static size_t scan_num_bytes(int BH, int S, int D, int dtype) {
-    return tc_split_supported(S, D, dtype) ? al(static_cast<size_t>(BH) * S * D * sizeof(float)) : 0;
+// Which of its three forms the scan entry uses.
+//   TWO_PASS   head dimension above 256: gated S x S matrix once, then W V (scan_gemm.cu)
+//   CHUNKWISE  sequence much longer than the head dimension: per-block states (C, n) with the stabiliser
+//              known up front, inter-block carry, output from the carried state (chunk.cu; the mechanism of
+//              mlstm_scan.py:74-137, 143-195, 200-278)
+//   QUADRATIC  the parallel forward with the output gate in its epilogue
+enum ScanRoute { SCAN_QUADRATIC = 0, SCAN_TWO_PASS = 1, SCAN_CHUNKWISE = 2 };
+constexpr int SCAN_CHUNK = 256;
+
+static int scan_route(int B, int NH, int S, int D, int dtype, int flags) {
+    const bool math_ok = dtype != MLSTM_DT_F32 || (flags & MLSTM_F_ALLOW_TF32);
+    if (flags & MLSTM_F_FORCE_SIMT) return SCAN_QUADRATIC;
+    if (scan_gemm_supported(S, D, dtype) && math_ok) return SCAN_TWO_PASS;
+    // the state form does 4 S D^2 flops per slice beside the blocks' own triangles, the quadratic form 2 S^2 D
+    if (S > 2 * D && S > 2 * SCAN_CHUNK && mlstm_chunk_workspace(B, NH, S, D, dtype, SCAN_CHUNK) != 0) return SCAN_CHUNKWISE;
+    return SCAN_QUADRATIC;
 }
 
 size_t mlstm_scan_fwd_workspace(int B, int NH, int S, int D, int dtype, int flags) {
     if (check_dims(B, NH, S, D) != MLSTM_OK) return 0;
-    return carve_fwd(nullptr, B * NH, S, true).bytes + scan_num_bytes(B * NH, S, D, dtype) +
-           tf32_copy_bytes(B * NH, S, D, dtype, flags, 3);
+    switch (scan_route(B, NH, S, D, dtype, flags)) {
+        case SCAN_TWO_PASS:
+            return carve_fwd(nullptr, B * NH, S, true).bytes + al(scan_gemm_bpart_bytes(B * NH, S, dtype)) +
+                   al(scan_gemm_w_bytes(B * NH, S, dtype));
+        case SCAN_CHUNKWISE: return mlstm_chunk_workspace(B, NH, S, D, dtype, SCAN_CHUNK);
+        default: return carve_fwd(nullptr, B * NH, S, true).bytes + tf32_copy_bytes(B * NH, S, D, dtype, flags, 3);
+    }
 }
 
 int mlstm_scan_fwd(const void* q, const void* k, const void* v, const void* f, const void* i, const void* o, void* h,
@@ -288,38 +327,50 @@ int mlstm_scan_fwd(const void* q, const void* k, const void* v, const void* f, c
     if (rc != MLSTM_OK) return rc;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(h)) return MLSTM_E_ALIGN;
     const int BH = B * NH;
-    FwdWs w = carve_fwd(workspace, BH, S, true);
-    const size_t num_bytes = scan_num_bytes(BH, S, D, dtype);
-    const size_t extra = tf32_copy_bytes(BH, S, D, dtype, flags, 3);
-    if (!workspace || workspace_bytes < w.bytes + num_bytes + extra || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
-    void* tf32buf = extra ? static_cast<uint8_t*>(workspace) + w.bytes + num_bytes : nullptr;
+    const size_t need = mlstm_scan_fwd_workspace(B, NH, S, D, dtype, flags);
+    if (!workspace || need == 0 || workspace_bytes < need || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const bool math_ok = dtype != MLSTM_DT_F32 || (flags & MLSTM_F_ALLOW_TF32);
-    if (num_bytes && math_ok && !(flags & MLSTM_F_FORCE_SIMT)) {
-        // head dimension above 256: contraction and output columns are sliced over CTAs, partial
-        // numerators and row sums are added up in fp32, then normalised and gated in one more pass
-        float* num = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + w.bytes);
+    const int route = scan_route(B, NH, S, D, dtype, flags);
+    if (route == SCAN_CHUNKWISE) {
+        if ((rc = mlstm_chunk_prepare(k, v, f, i, nullptr, nullptr, workspace, workspace_bytes, B, NH, S, D, dtype, SCAN_CHUNK,
+                                      stream)) != MLSTM_OK)
+            return rc;
+        return mlstm_chunk_apply(q, k, v, o, nullptr, nullptr, h, MLSTM_DT_F32, nullptr, nullptr, workspace, workspace_bytes,
+                                 B, NH, S, D, dtype, SCAN_CHUNK, stream);
+    }
+    FwdWs w = carve_fwd(workspace, BH, S, true);
+    if (route == SCAN_TWO_PASS) {
         const int Spad = round_up(S, TILE);
+        uint8_t* base = static_cast<uint8_t*>(workspace) + w.bytes;
+        float* bpart = reinterpret_cast<float*>(base);
+        void* W = base + al(scan_gemm_bpart_bytes(BH, S, dtype));
         if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
-        if (cudaMemsetAsync(num, 0, static_cast<size_t>(BH) * S * D * sizeof(float), st) != cudaSuccess) return MLSTM_E_CUDA;
-        if (cudaMemsetAsync(w.b, 0, static_cast<size_t>(BH) * S * sizeof(float), st) != cudaSuccess) return MLSTM_E_CUDA;
         if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, w.m, BH, S, Spad, dtype, st, nullptr, nullptr, nullptr, 0,
                                    nullptr, w.gaw)) != MLSTM_OK)
             return rc;
-        const void* in[3] = {q, k, v};
-        if (dtype == MLSTM_DT_F32 && (rc = round_inputs(in, 3, tf32buf, BH, S, D, st)) != MLSTM_OK) return rc;
-        PassParams p{};
-        p.S = S; p.Spad = Spad; p.BH = BH; p.D = 256; p.Dfull = D;
-        p.X = in[0]; p.Y = in[1]; p.Z = in[2];
-        p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_w = w.gaw; p.col_ref = w.a_ref;
-        p.er_add = -0.5f * log2f(static_cast<float>(D));
-        p.out = num; p.m = w.m; p.b_out = w.b;
-        p.status = w.status; p.sched = w.status + 8;
-        if ((rc = launch_fwd_split_tc(p, dtype, st)) != MLSTM_OK) return rc;
-        return launch_scan_finalize(num, w.b, w.m, o, static_cast<float*>(h), BH, S, D, dtype, st);
+        ScanGemmArgs a{};
+        a.S = S; a.Spad = Spad; a.BH = BH; a.D = D;
+        a.ga = w.ga; a.gAn = w.gAn; a.gaw = w.gaw; a.a_ref = w.a_ref; a.An_ref = w.An_ref; a.m = w.m;
+        a.bpart = bpart; a.status = w.status; a.counters = w.status + 8 + 6;
+        return launch_scan_gemm(q, k, v, o, static_cast<float*>(h), W, a, dtype, st);
     }
     if ((flags & MLSTM_F_FORCE_TC) && D > 256) return MLSTM_E_UNSUPPORTED;
+    const size_t extra = tf32_copy_bytes(BH, S, D, dtype, flags, 3);
+    void* tf32buf = extra ? static_cast<uint8_t*>(workspace) + w.bytes : nullptr;
     return forward_impl(q, k, v, f, i, o, h, w.m, w.b, w, BH, S, D, dtype, MLSTM_DT_F32, flags, st, tf32buf);
+}
+
+int mlstm_ogate_fwd(const void* h_inner, const void* o, void* h, long long n, int h_dtype, int o_dtype, void* stream) {
+    if (!h_inner || !o || !h || n <= 0) return MLSTM_E_ARG;
+    if (!dtype_ok(h_dtype) || !dtype_ok(o_dtype)) return MLSTM_E_ARG;
+    return launch_ogate_fwd(h_inner, o, h, n, h_dtype, o_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int mlstm_ogate_bwd(const void* dh, const void* h_inner, const void* o, void* dh_inner, void* d_o, long long n, int h_dtype,
+                    int o_dtype, void* stream) {
+    if (!dh || !h_inner || !o || !dh_inner || !d_o || n <= 0) return MLSTM_E_ARG;
+    if (!dtype_ok(h_dtype) || !dtype_ok(o_dtype)) return MLSTM_E_ARG;
+    return launch_ogate_bwd(dh, h_inner, o, dh_inner, d_o, n, h_dtype, o_dtype, static_cast<cudaStream_t>(stream));
 }
 
 size_t mlstm_forward_f16_workspace(unsigned S, unsigned D) {
@@ -382,7 +433,7 @@ int mlstm_backward_f16(const void* dH, const void* Q, const void* K, const void*
 // The C++ driver's launch (Q, K, V, F, I, H, S) has no workspace argument, and some of its callers
 // cannot create one: code on a latency-critical path, where cudaMalloc and cudaFree serialise the
 // whole device, and embedders that were given a fixed memory budget and no allocator.  For them the
-// scratch of the forward (status word, the two gate vectors with their block references, m and b)
+// scratch of the forward (status word, the three gate vectors with their block references, m and b)
 // lives in one array in the library's device image.  It costs MLSTM_STATIC_SCRATCH_BYTES on every
 // GPU that loads the library, for as long as the process lives, hence the modest length limit.
 //
@@ -393,15 +444,8 @@ int mlstm_backward_f16(const void* dH, const void* Q, const void* K, const void*
 // rewritten before it is read, and two calls whose kernels overlap on the GPU (different streams,
 // no dependency) corrupt each other.
 constexpr unsigned STATIC_MAX_S = MLSTM_STATIC_MAX_S;
-constexpr size_t static_scratch_bytes(size_t S) {
-    const size_t spad = (S + TILE - 1) / TILE * TILE;
-    const size_t a = 256;
-    const size_t vec = (spad * 4 + a - 1) / a * a;
-    const size_t ref = (spad / REF_BLOCK * 8 + a - 1) / a * a;
-    const size_t row = (S * 4 + a - 1) / a * a;
-    return a + 2 * vec + 2 * ref + 2 * row;
-}
-static_assert(static_scratch_bytes(STATIC_MAX_S) == MLSTM_STATIC_SCRATCH_BYTES, "keep the header's figure in step");
+static_assert(fwd_layout(1, STATIC_MAX_S, true).bytes == MLSTM_STATIC_SCRATCH_BYTES,
+              "the header's figure must be the forward scratch of one head at MLSTM_STATIC_MAX_S");
 static __device__ __align__(256) unsigned char g_static_scratch[MLSTM_STATIC_SCRATCH_BYTES];
 
 static int static_scratch_address(void** out) {
@@ -437,6 +481,14 @@ int mlstm_forward_f16_static(const void* Q, const void* K, const void* V, const 
     if (w.bytes > MLSTM_STATIC_SCRATCH_BYTES) return MLSTM_E_STATIC_LIMIT;
     return forward_impl(Q, K, V, F, I, nullptr, H, w.m, w.b, w, 1, static_cast<int>(S), static_cast<int>(D), MLSTM_DT_F16,
                         MLSTM_DT_F16, 0, static_cast<cudaStream_t>(stream));
+}
+
+int mlstm_forward_f16_static_status(int* host_status, void* stream) {
+    if (!host_status) return MLSTM_E_ARG;
+    void* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc != MLSTM_OK) return rc;
+    return mlstm_read_status(scratch, host_status, stream);
 }
 
 int mlstm_read_status(const void* workspace, int* host_status, void* stream) {

@@ -27,15 +27,27 @@ __global__ void identity_kernel(T16* ident) {
 
 // One thread owns four consecutive elements of a slice's [D*D + D] state (matrix, then normaliser
 // vector) and walks the blocks in order.  It writes the INBOUND state of every block (16-bit matrix
-// for the tensor cores, fp32 vector) and, optionally, the state after the last block.
+// for the tensor cores, fp32 vector; skipped when `states` is null) and, optionally, the state after
+// the last block (S_end / z_end with per-slice strides, so that they can sit inside a packed record).
+// late_bound (optional, per slice): a carry that became known after the gate pass, see PassParams;
+// block contributions U_k were stabilised by the local block-end maximum and are rescaled to the
+// later, larger one on the way in.
 template <typename T16>
 __global__ void state_scan_kernel(const float* __restrict__ U, const float* __restrict__ zU,
                                   const double* __restrict__ An_bound, const float* __restrict__ S_in,
                                   const float* __restrict__ z_in, T16* __restrict__ states, float* __restrict__ zstate,
-                                  float* __restrict__ S_end, float* __restrict__ z_end, int NB, int D) {
+                                  float* __restrict__ S_end, float* __restrict__ z_end, size_t S_end_stride,
+                                  size_t z_end_stride, int NB, int D, const double* __restrict__ late_bound,
+                                  const double* __restrict__ summary, double* __restrict__ summary_dst,
+                                  size_t summary_dst_stride) {
     const int bh = blockIdx.y;
     const int DD = D * D;
     const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (e == 0 && summary_dst) {
+        double* dst = reinterpret_cast<double*>(reinterpret_cast<float*>(summary_dst) + bh * summary_dst_stride);
+        dst[0] = summary[2 * bh];
+        dst[1] = summary[2 * bh + 1];
+    }
     if (e >= DD + D) return;
     const bool is_vec = e >= DD;
     const int off = is_vec ? e - DD : e;
@@ -45,16 +57,20 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
     float4 s = init ? *reinterpret_cast<const float4*>(init + static_cast<size_t>(bh) * per_block + off)
                     : make_float4(0.f, 0.f, 0.f, 0.f);
     const double* bound = An_bound + static_cast<size_t>(bh) * (NB + 1);
+    const double lb = late_bound ? late_bound[bh] : INFINITY;
     constexpr int PF = 8;  // blocks whose contributions are fetched ahead of the serial update
     for (int k0 = 0; k0 < NB; k0 += PF) {
         float4 u[PF];
-        float d[PF];
+        float d[PF], c[PF];
 #pragma unroll
         for (int j = 0; j < PF; j++) {
             if (k0 + j < NB) {
                 u[j] = __ldg(reinterpret_cast<const float4*>(src + static_cast<size_t>(k0 + j) * per_block));
-                // exp(A_end(k-1) - A_end(k)); 0 for the first block when there is no inbound carry (bound[0] = +inf)
-                d[j] = exp2f(static_cast<float>(bound[k0 + j + 1] - bound[k0 + j]));
+                const double b1 = bound[k0 + j + 1], b0 = bound[k0 + j];
+                const double b1c = fmin(b1, lb), b0c = fmin(b0, lb);
+                // exp(A_end(k-1) - A_end(k)); 0 for the first block when there is no inbound carry (bound = +inf)
+                d[j] = exp2f(static_cast<float>(b1c - b0c));
+                c[j] = exp2f(static_cast<float>(b1c - b1));   // 1 unless the late carry raised the block's stabiliser
             }
         }
 #pragma unroll
@@ -62,25 +78,68 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
             const int k = k0 + j;
             if (k >= NB) break;
             if (is_vec) {
-                *reinterpret_cast<float4*>(zstate + (static_cast<size_t>(bh) * NB + k) * D + off) = s;
-            } else {
+                if (zstate) *reinterpret_cast<float4*>(zstate + (static_cast<size_t>(bh) * NB + k) * D + off) = s;
+            } else if (states) {
                 T16 o[4] = {from_f32<T16>(s.x), from_f32<T16>(s.y), from_f32<T16>(s.z), from_f32<T16>(s.w)};
                 *reinterpret_cast<uint2*>(states + (static_cast<size_t>(bh) * NB + k) * DD + off) = *reinterpret_cast<uint2*>(o);
             }
-            s.x = (d[j] == 0.0f ? 0.0f : d[j] * s.x) + u[j].x;
-            s.y = (d[j] == 0.0f ? 0.0f : d[j] * s.y) + u[j].y;
-            s.z = (d[j] == 0.0f ? 0.0f : d[j] * s.z) + u[j].z;
-            s.w = (d[j] == 0.0f ? 0.0f : d[j] * s.w) + u[j].w;
+            s.x = (d[j] == 0.0f ? 0.0f : d[j] * s.x) + c[j] * u[j].x;
+            s.y = (d[j] == 0.0f ? 0.0f : d[j] * s.y) + c[j] * u[j].y;
+            s.z = (d[j] == 0.0f ? 0.0f : d[j] * s.z) + c[j] * u[j].z;
+            s.w = (d[j] == 0.0f ? 0.0f : d[j] * s.w) + c[j] * u[j].w;
         }
     }
     float* dst = is_vec ? z_end : S_end;
-    if (dst) *reinterpret_cast<float4*>(dst + static_cast<size_t>(bh) * per_block + off) = s;
+    const size_t stride = is_vec ? z_end_stride : S_end_stride;
+    if (dst) *reinterpret_cast<float4*>(dst + static_cast<size_t>(bh) * stride + off) = s;
+}
+
+// Sequence-parallel fold: from the gathered records of all segments (per slice: S | z | {F_end, A_end},
+// every segment's state stabilised by its OWN prefix maximum and its F counted from zero) to the
+// inbound state of segment `rank` and its late carry.  With F_in(g) the log-forget total before
+// segment g, segment g's stabiliser in global terms is A_g - F_in(g); the inbound maximum is
+// A_in = max_{g < rank} of those, S_in = sum_g exp(A_g - F_in(g) - A_in) S_g (weights <= 1), and the
+// late bound handed to the kernels is -(A_in + F_in(rank)) * log2e (+inf for the first segment).
+// This is the combine of the reference's scan operators (mlstm_scan.py:15-26) over segment summaries.
+__global__ void sp_fold_kernel(const float* __restrict__ gathered, int rank, int BH, int D, size_t rec_stride,
+                               float* __restrict__ S_in, float* __restrict__ z_in, double* __restrict__ late_bound,
+                               double* __restrict__ carry) {
+    const int bh = blockIdx.y;
+    const int DD = D * D;
+    const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (e >= DD + D) return;
+    auto rec = [&](int g) { return gathered + (static_cast<size_t>(g) * BH + bh) * rec_stride; };
+    auto tail = [&](int g) { return reinterpret_cast<const double*>(rec(g) + DD + D); };
+    double Fin = 0.0, Ain = -INFINITY;
+    for (int g = 0; g < rank; g++) {
+        const double* t = tail(g);
+        Ain = fmax(Ain, t[1] - Fin);
+        Fin += t[0];
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    double Fg = 0.0;
+    for (int g = 0; g < rank; g++) {
+        const double* t = tail(g);
+        const float w = static_cast<float>(exp(t[1] - Fg - Ain));
+        Fg += t[0];
+        const float4 x = __ldg(reinterpret_cast<const float4*>(rec(g) + e));
+        acc.x = fmaf(w, x.x, acc.x); acc.y = fmaf(w, x.y, acc.y); acc.z = fmaf(w, x.z, acc.z); acc.w = fmaf(w, x.w, acc.w);
+    }
+    if (e >= DD) *reinterpret_cast<float4*>(z_in + static_cast<size_t>(bh) * D + (e - DD)) = acc;
+    else *reinterpret_cast<float4*>(S_in + static_cast<size_t>(bh) * DD + e) = acc;
+    if (e == 0) {
+        late_bound[bh] = rank == 0 ? static_cast<double>(INFINITY) : -(Ain + Fin) * 1.4426950408889634;
+        if (carry) {
+            carry[2 * bh] = Fin;
+            carry[2 * bh + 1] = Ain;
+        }
+    }
 }
 
 struct ChunkWs {
     int* status;
-    float *ga, *gAn, *gaw, *m, *b, *U, *zU, *zstate;
-    double *a_ref, *An_ref, *An_bound, *gscratch;
+    float *ga, *gAn, *gaw, *m, *b, *U, *zU, *zstate, *S_in, *z_in;
+    double *a_ref, *An_ref, *An_bound, *gscratch, *summary, *late;
     void *ident, *states;
     int NB;
     size_t bytes;
@@ -115,6 +174,11 @@ ChunkWs carve(void* ws, int BH, int S, int D, int chunk) {
     w.zU = static_cast<float*>(take(nblk * D * sizeof(float)));
     w.states = take(nblk * D * D * 2);
     w.zstate = static_cast<float*>(take(nblk * D * sizeof(float)));
+    // sequence-parallel stages: this segment's gate summary, the folded inbound state and the late carry
+    w.summary = static_cast<double*>(take(static_cast<size_t>(BH) * 2 * sizeof(double)));
+    w.late = static_cast<double*>(take(static_cast<size_t>(BH) * sizeof(double)));
+    w.S_in = static_cast<float*>(take(static_cast<size_t>(BH) * D * D * sizeof(float)));
+    w.z_in = static_cast<float*>(take(static_cast<size_t>(BH) * D * sizeof(float)));
     w.bytes = off;
     return w;
 }
@@ -126,6 +190,21 @@ int check_chunk_args(int B, int NH, int S, int D, int dtype, int chunk) {
     if (chunk % TILE != 0) return MLSTM_E_SHAPE;
     if (static_cast<long long>(B) * NH > 65535) return MLSTM_E_SHAPE;
     return MLSTM_OK;
+}
+
+// h of the segment from the per-block inbound states (FWDC pass)
+int launch_fwdc(const void* q, const void* k, const void* v, const void* o, void* h, int h_dtype, const ChunkWs& w, int BH,
+                int S, int Spad, int D, int dtype, int chunk, const double* late_bound, cudaStream_t st) {
+    PassParams p{};
+    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8;
+    p.X = q; p.Y = k; p.Z = v;
+    p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_w = w.gaw; p.col_ref = w.a_ref;
+    p.er_add = -0.5f * log2f(static_cast<float>(D));
+    p.out = h; p.m = w.m; p.b_out = w.b; p.ogate = o;
+    p.chunk_tiles = chunk / TILE; p.NB = w.NB; p.An_bound = w.An_bound; p.ident = w.ident;
+    p.states = w.states; p.zstate = w.zstate;
+    p.late_bound = late_bound;
+    return launch_pass_tc(FWDC, p, dtype, h_dtype, st);
 }
 
 }  // namespace
@@ -141,17 +220,27 @@ int launch_identity(void* ident, int dtype, cudaStream_t st) {
 
 int launch_state_scan(const float* U, const float* zU, const double* An_bound, const float* S_in, const float* z_in,
                       void* states16, float* zstate, float* S_end, float* z_end, int BH, int NB, int D, int dtype,
-                      cudaStream_t st) {
+                      cudaStream_t st, const double* late_bound, float* rec, size_t rec_stride, const double* summary) {
     const int threads = 256;
     const int work = (D * D + D) / 4;
     dim3 grid((work + threads - 1) / threads, BH);
+    size_t s_stride = static_cast<size_t>(D) * D, z_stride = D;
+    double* sum_dst = nullptr;
+    if (rec) {   // S_end | z_end | summary inside per-slice records
+        S_end = rec;
+        z_end = rec + s_stride;
+        sum_dst = reinterpret_cast<double*>(rec + s_stride + D);
+        s_stride = z_stride = rec_stride;
+    }
     if (dtype == MLSTM_DT_BF16)
         state_scan_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(U, zU, An_bound, S_in, z_in,
                                                                    static_cast<__nv_bfloat16*>(states16), zstate, S_end,
-                                                                   z_end, NB, D);
+                                                                   z_end, s_stride, z_stride, NB, D, late_bound, summary,
+                                                                   sum_dst, rec_stride);
     else
         state_scan_kernel<__half><<<grid, threads, 0, st>>>(U, zU, An_bound, S_in, z_in, static_cast<__half*>(states16),
-                                                            zstate, S_end, z_end, NB, D);
+                                                            zstate, S_end, z_end, s_stride, z_stride, NB, D, late_bound,
+                                                            summary, sum_dst, rec_stride);
     return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
@@ -218,15 +307,16 @@ int mlstm_chunk_local_state(void* workspace, size_t workspace_bytes, float* S_en
                              dtype, static_cast<cudaStream_t>(stream));
 }
 
-int mlstm_chunk_apply(const void* q, const void* k, const void* v, const float* S_in, const float* z_in, void* h,
-                      int h_dtype, float* S_out, float* z_out, void* workspace, size_t workspace_bytes, int B, int NH,
-                      int S, int D, int dtype, int chunk, void* stream) {
+int mlstm_chunk_apply(const void* q, const void* k, const void* v, const void* o, const float* S_in, const float* z_in,
+                      void* h, int h_dtype, float* S_out, float* z_out, void* workspace, size_t workspace_bytes, int B,
+                      int NH, int S, int D, int dtype, int chunk, void* stream) {
     if (!q || !k || !v || !h) return MLSTM_E_ARG;
     if ((S_in == nullptr) != (z_in == nullptr)) return MLSTM_E_ARG;
     int rc = check_chunk_args(B, NH, S, D, dtype, chunk);
     if (rc != MLSTM_OK) return rc;
     if (h_dtype != MLSTM_DT_F32 && h_dtype != dtype) return MLSTM_E_ARG;
-    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(h) || !aligned16(S_in) || !aligned16(z_in))
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(h) || !aligned16(S_in) ||
+        !aligned16(z_in))
         return MLSTM_E_ALIGN;
     const int BH = B * NH, Spad = round_up(S, TILE);
     ChunkWs w = carve(workspace, BH, S, D, chunk);
@@ -235,15 +325,52 @@ int mlstm_chunk_apply(const void* q, const void* k, const void* v, const float* 
     if ((rc = launch_state_scan(w.U, w.zU, w.An_bound, S_in, z_in, w.states, w.zstate, S_out, z_out, BH, w.NB, D, dtype,
                                 st)) != MLSTM_OK)
         return rc;
-    PassParams p{};
-    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8;
-    p.X = q; p.Y = k; p.Z = v;
-    p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_w = w.gaw; p.col_ref = w.a_ref;
-    p.er_add = -0.5f * log2f(static_cast<float>(D));
-    p.out = h; p.m = w.m; p.b_out = w.b;
-    p.chunk_tiles = chunk / TILE; p.NB = w.NB; p.An_bound = w.An_bound; p.ident = w.ident;
-    p.states = w.states; p.zstate = w.zstate;
-    return launch_pass_tc(FWDC, p, dtype, h_dtype, st);
+    return launch_fwdc(q, k, v, o, h, h_dtype, w, BH, S, Spad, D, dtype, chunk, nullptr, st);
+}
+
+size_t mlstm_chunk_sp_record_floats(int D) { return D > 0 ? static_cast<size_t>(D) * D + D + 4 : 0; }
+
+int mlstm_chunk_sp_local(const void* k, const void* v, const void* f, const void* i, float* record, void* workspace,
+                         size_t workspace_bytes, int B, int NH, int S, int D, int dtype, int chunk, void* stream) {
+    if (!record) return MLSTM_E_ARG;
+    if (!aligned16(record)) return MLSTM_E_ALIGN;
+    ChunkWs w = carve(workspace, B * NH, S, D, chunk);
+    // gates and block states with no carry; this segment's own summary goes to the workspace
+    int rc = mlstm_chunk_prepare(k, v, f, i, nullptr, workspace ? w.summary : nullptr, workspace, workspace_bytes, B, NH, S, D,
+                                 dtype, chunk, stream);
+    if (rc != MLSTM_OK) return rc;
+    // the state the segment adds, stabilised by its own last prefix maximum, written into the record with the summary
+    return launch_state_scan(w.U, w.zU, w.An_bound, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, B * NH, w.NB, D,
+                             dtype, static_cast<cudaStream_t>(stream), nullptr, record, mlstm_chunk_sp_record_floats(D),
+                             w.summary);
+}
+
+int mlstm_chunk_sp_apply(const void* q, const void* k, const void* v, const void* o, const float* gathered, int world,
+                         int rank, void* h, int h_dtype, double* carry_out, void* workspace, size_t workspace_bytes, int B,
+                         int NH, int S, int D, int dtype, int chunk, void* stream) {
+    if (!q || !k || !v || !h || !gathered) return MLSTM_E_ARG;
+    if (world <= 0 || rank < 0 || rank >= world) return MLSTM_E_ARG;
+    int rc = check_chunk_args(B, NH, S, D, dtype, chunk);
+    if (rc != MLSTM_OK) return rc;
+    if (h_dtype != MLSTM_DT_F32 && h_dtype != dtype) return MLSTM_E_ARG;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(h) || !aligned16(gathered))
+        return MLSTM_E_ALIGN;
+    const int BH = B * NH, Spad = round_up(S, TILE);
+    ChunkWs w = carve(workspace, BH, S, D, chunk);
+    if (!workspace || workspace_bytes < w.bytes) return MLSTM_E_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    {
+        const int threads = 256;
+        const int work = (D * D + D) / 4;
+        dim3 grid((work + threads - 1) / threads, BH);
+        sp_fold_kernel<<<grid, threads, 0, st>>>(gathered, rank, BH, D, mlstm_chunk_sp_record_floats(D), w.S_in, w.z_in,
+                                                 w.late, carry_out);
+        if (cudaGetLastError() != cudaSuccess) return MLSTM_E_CUDA;
+    }
+    if ((rc = launch_state_scan(w.U, w.zU, w.An_bound, w.S_in, w.z_in, w.states, w.zstate, nullptr, nullptr, BH, w.NB, D,
+                                dtype, st, w.late)) != MLSTM_OK)
+        return rc;
+    return launch_fwdc(q, k, v, o, h, h_dtype, w, BH, S, Spad, D, dtype, chunk, w.late, st);
 }
 
 }  // extern "C"

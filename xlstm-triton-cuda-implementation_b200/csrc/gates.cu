@@ -294,25 +294,54 @@ __global__ void __launch_bounds__(SCAN_THREADS) df_kernel(const T* __restrict__ 
     }
 }
 
-// Last step of the sliced forward: h = num / (max(|b|, exp(-m)) + 1e-6) * silu(o), four columns per thread
-// (mlstm_scan.py:273-278).
-template <typename T>
-__global__ void scan_finalize_kernel(const float* __restrict__ num, const float* __restrict__ b,
-                                     const float* __restrict__ m, const T* __restrict__ o, float* __restrict__ h,
-                                     long long rows, int D) {
-    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    const int per_row = D / 4;
-    if (idx >= rows * per_row) return;
-    const long long row = idx / per_row;
-    const size_t off = static_cast<size_t>(idx) * 4;
-    const float n = fmaxf(fabsf(b[row]), expf(-m[row])) + 1e-6f;
-    const float4 x = *reinterpret_cast<const float4*>(num + off);
-    float4 y;
-    y.x = x.x / n * silu_f(to_f32<T>(o[off + 0]));
-    y.y = x.y / n * silu_f(to_f32<T>(o[off + 1]));
-    y.z = x.z / n * silu_f(to_f32<T>(o[off + 2]));
-    y.w = x.w / n * silu_f(to_f32<T>(o[off + 3]));
-    *reinterpret_cast<float4*>(h + off) = y;
+// Output gate, elementwise: h = h_inner * silu(o) (mlstm_scan.py:273-278; the "integrate o" note at
+// mlstm_matmul.py:36) and its derivative: dh_inner = dh * silu(o), do = dh * h_inner * silu'(o) with
+// silu'(x) = sigma(x) (1 + x (1 - sigma(x))).  Eight elements per thread, 16-byte accesses on the 16-bit side.
+template <typename HT, typename OT, bool BWD>
+__global__ void ogate_kernel(const HT* __restrict__ dh, const HT* __restrict__ h_inner, const OT* __restrict__ o,
+                             HT* __restrict__ out_h, OT* __restrict__ out_o, long long n) {
+    const long long base = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+    if (base >= n) return;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const long long e = base + j;
+        if (e >= n) break;
+        const float x = to_f32<OT>(o[e]);
+        const float sg = 1.0f / (1.0f + __expf(-x));
+        const float hi = to_f32<HT>(h_inner[e]);
+        if (BWD) {
+            const float g = to_f32<HT>(dh[e]);
+            out_h[e] = from_f32<HT>(g * x * sg);
+            out_o[e] = from_f32<OT>(g * hi * sg * (1.0f + x * (1.0f - sg)));
+        } else {
+            out_h[e] = from_f32<HT>(hi * x * sg);
+        }
+    }
+}
+
+template <bool BWD>
+static int ogate_dispatch(const void* dh, const void* h_inner, const void* o, void* out_h, void* out_o, long long n, int h_dtype,
+                          int o_dtype, cudaStream_t st) {
+    const int threads = 256;
+    const long long blocks = (n + threads * 8 - 1) / (threads * 8);
+    if (blocks <= 0 || blocks > 0x7fffffffLL) return MLSTM_E_SHAPE;
+#define OGATE_LAUNCH(HT, OT)                                                                                              \
+    ogate_kernel<HT, OT, BWD><<<(unsigned)blocks, threads, 0, st>>>((const HT*)dh, (const HT*)h_inner, (const OT*)o, (HT*)out_h, \
+                                                                    (OT*)out_o, n)
+    if (h_dtype == MLSTM_DT_F32) {
+        if (o_dtype == MLSTM_DT_F32) OGATE_LAUNCH(float, float);
+        else if (o_dtype == MLSTM_DT_F16) OGATE_LAUNCH(float, __half);
+        else if (o_dtype == MLSTM_DT_BF16) OGATE_LAUNCH(float, __nv_bfloat16);
+        else return MLSTM_E_ARG;
+    } else if (h_dtype == MLSTM_DT_F16 && o_dtype == MLSTM_DT_F16) {
+        OGATE_LAUNCH(__half, __half);
+    } else if (h_dtype == MLSTM_DT_BF16 && o_dtype == MLSTM_DT_BF16) {
+        OGATE_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    } else {
+        return MLSTM_E_ARG;
+    }
+#undef OGATE_LAUNCH
+    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
 // Round fp32 values to the nearest tf32 (10 mantissa bits).  The tensor cores drop the low 13 bits
@@ -331,34 +360,21 @@ __global__ void round_tf32_kernel(const float4* __restrict__ in, float4* __restr
 
 }  // namespace
 
+int launch_ogate_fwd(const void* h_inner, const void* o, void* h, long long n, int h_dtype, int o_dtype, cudaStream_t st) {
+    return ogate_dispatch<false>(nullptr, h_inner, o, h, nullptr, n, h_dtype, o_dtype, st);
+}
+
+int launch_ogate_bwd(const void* dh, const void* h_inner, const void* o, void* dh_inner, void* d_o, long long n, int h_dtype,
+                     int o_dtype, cudaStream_t st) {
+    return ogate_dispatch<true>(dh, h_inner, o, dh_inner, d_o, n, h_dtype, o_dtype, st);
+}
+
 int launch_round_tf32(const void* in, void* out, long long n, cudaStream_t st) {
     const long long n4 = n / 4;
     const int threads = 256;
     const long long blocks = (n4 + threads - 1) / threads;
     if (blocks > 0x7fffffffLL || (n & 3)) return MLSTM_E_SHAPE;
     round_tf32_kernel<<<(unsigned)blocks, threads, 0, st>>>(static_cast<const float4*>(in), static_cast<float4*>(out), n4);
-    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
-}
-
-int launch_scan_finalize(const float* num, const float* b, const float* m, const void* o, float* h, int BH, int S, int D,
-                         int dtype, cudaStream_t st) {
-    const long long rows = static_cast<long long>(BH) * S;
-    const long long work = rows * (D / 4);
-    const int threads = 256;
-    const long long blocks = (work + threads - 1) / threads;
-    if (blocks > 0x7fffffffLL) return MLSTM_E_SHAPE;
-    switch (dtype) {
-        case MLSTM_DT_F32:
-            scan_finalize_kernel<float><<<(unsigned)blocks, threads, 0, st>>>(num, b, m, (const float*)o, h, rows, D);
-            break;
-        case MLSTM_DT_F16:
-            scan_finalize_kernel<__half><<<(unsigned)blocks, threads, 0, st>>>(num, b, m, (const __half*)o, h, rows, D);
-            break;
-        case MLSTM_DT_BF16:
-            scan_finalize_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, st>>>(num, b, m, (const __nv_bfloat16*)o, h, rows, D);
-            break;
-        default: return MLSTM_E_ARG;
-    }
     return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 

@@ -39,15 +39,14 @@ enum Mode : int { FWD = 0, DQ = 1, DK = 2, DV = 3, FWDC = 4, STATE = 5 };
 constexpr int TILE = 128;      // rows of a tensor-core tile; gate vectors are padded to a multiple of it
 constexpr int REF_BLOCK = 64;  // positions per reference block of the re-centred gate vectors (gates.cu)
 
-__host__ __device__ inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+__host__ __device__ constexpr int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
 // Arguments of one contraction pass, shared by the tensor-core and the SIMT kernels.
 struct PassParams {
     int S;      // sequence length
     int Spad;   // S rounded up to TILE: stride of every gate vector per slice
     int BH;     // batch * heads
-    int D;      // head dimension (sliced forward: the slice width)
-    int Dfull;  // sliced forward only: the head dimension
+    int D;      // head dimension
     const void* X;  // stationary operand  [BH, S, D]
     const void* Y;  // first streamed operand
     const void* Z;  // second streamed operand
@@ -76,6 +75,11 @@ struct PassParams {
     const void* ident;       // [128, 128] identity in the input type
     const void* states;      // FWDC: [BH, NB, D, D] inbound state of every block, input type
     const float* zstate;     // FWDC: [BH, NB, D] inbound normaliser vector of every block
+    // FWDC, optional: a carry that became known after the gate pass (sequence-parallel segments).
+    // late_bound[bh] = -(A_in + F_in) * log2e, the inbound prefix maximum in this segment's own
+    // coordinates; every stabiliser -A*log2e of the slice (rows, block boundaries) becomes
+    // min(local value, late_bound[bh]) and m grows by the difference.  +inf = no carry.
+    const double* late_bound;
     int* status;         // device word; a kernel that gave up on a wait stores a non-zero code
     int* sched;          // tensor-core passes: 8 device words, one work-item counter per pass mode
     int slice_set;       // tensor-core passes: slices interleaved in the work-item order (set by the launcher)
@@ -126,9 +130,11 @@ int launch_gates_fwd(const void* f, const void* i, float* ga_rel, float* gAn_rel
 size_t gates_scratch_bytes(int BH, int Spad);
 // chunk.cu
 int launch_identity(void* ident, int dtype, cudaStream_t st);
+// rec (optional): per-slice records of rec_stride floats that receive S_end | z_end | summary {F, A} (two doubles)
 int launch_state_scan(const float* U, const float* zU, const double* An_bound, const float* S_in, const float* z_in,
                       void* states16, float* zstate, float* S_end, float* z_end, int BH, int NB, int D, int dtype,
-                      cudaStream_t st);
+                      cudaStream_t st, const double* late_bound = nullptr, float* rec = nullptr, size_t rec_stride = 0,
+                      const double* summary = nullptr);
 int launch_bwd_prep(const void* h, const void* dh, const float* b, const float* m, const float* gAn, float* gB,
                     float* gBw, float* g, void* dh16, int BH, int S, int Spad, int D, int h_dtype, int dtype, cudaStream_t st);
 int launch_df(const void* f, const float* dI, const float* R, void* df, void* di, int BH, int S, int Spad, int dtype,
@@ -136,10 +142,27 @@ int launch_df(const void* f, const float* dI, const float* R, void* df, void* di
 int launch_pass_simt(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st);
 int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st);
 bool tc_supported(int S, int D, int in_dtype);
-bool tc_split_supported(int S, int D, int in_dtype);
-int launch_fwd_split_tc(const PassParams& p, int in_dtype, cudaStream_t st);
 int launch_round_tf32(const void* in, void* out, long long n, cudaStream_t st);
-int launch_scan_finalize(const float* num, const float* b, const float* m, const void* o, float* h, int BH, int S, int D,
-                         int dtype, cudaStream_t st);
+int launch_ogate_fwd(const void* h_inner, const void* o, void* h, long long n, int h_dtype, int o_dtype, cudaStream_t st);
+int launch_ogate_bwd(const void* dh, const void* h_inner, const void* o, void* dh_inner, void* d_o, long long n, int h_dtype,
+                     int o_dtype, cudaStream_t st);
+
+// Two-pass forward for head dimensions above 256 (scan_gemm.cu).  Gate vectors as written by
+// launch_gates_fwd for all BH slices; bpart and W are scratch of scan_gemm_bpart_bytes / scan_gemm_w_bytes;
+// counters: two device words.
+struct ScanGemmArgs {
+    int S, Spad, BH, D;
+    const float *ga, *gAn, *gaw;
+    const double *a_ref, *An_ref;
+    const float* m;
+    float* bpart;
+    int* status;
+    int* counters;
+};
+bool scan_gemm_supported(int S, int D, int in_dtype);
+size_t scan_gemm_w_bytes(int BH, int S, int dtype);
+size_t scan_gemm_bpart_bytes(int BH, int S, int dtype);
+int launch_scan_gemm(const void* q, const void* k, const void* v, const void* o, float* h, void* W, const ScanGemmArgs& a,
+                     int dtype, cudaStream_t st);
 
 }  // namespace mlstm

@@ -31,14 +31,12 @@
 //     accumulator wait, and where shared memory has room the output leaves through TMA stores.
 //
 // Element types: fp16 / bf16 (kind::f16) and fp32 read as tf32 (kind::tf32).  D is the width this CTA
-// contracts over in T and produces in ACC.  In the sliced form (SPLIT) the head dimension is larger
-// than D: a CTA takes one slice of the contraction and one slice of the output columns, and because
-// W and ACC are linear in T the partial results are summed with atomic adds (forward only).
+// contracts over in T and produces in ACC (head dimensions above 256 are served by scan_gemm.cu).
 //
 // Every wait is bounded: a wait that runs out sets a CTA-wide abort word, every role leaves its
 // loop, the CTA stores a non-zero code in the status word, waits a little for copies in flight,
 // frees its TMEM and returns.
-#include <cstdlib>
+#include <atomic>
 #include <type_traits>
 
 #include "mlstm_common.cuh"
@@ -58,28 +56,8 @@ constexpr long long WAIT_LIMIT = 4000000000LL;
 constexpr float MAX_ROW_EXP2 = 60.0f;           // clamp of the per-row exponent off the diagonal tile (see its use)
 constexpr int SLACK_SLEEP_NS = 64;              // poll interval of the roles that wait with slack (gate warps, producer)  // cycles (about two seconds)
 constexpr int SLICE_SET_DEFAULT = 8;            // slices whose work items are interleaved in item order
+constexpr int MAX_DEVICES = 64;
 
-#ifdef MLSTM_TRACE
-// Timing aid for kernel development (not built into the library): CTA 0 stamps clock64() at a few
-// points.  Per step of its first work item (only with MLSTM_TRACE_STEPS: a stamp costs about 100
-// cycles): g_trace[(role * 64 + step) * 8 + event].  Per work item: g_trace[2048 + item * 8 + event].
-__device__ long long g_trace[4 * 64 * 8 + 64 * 8];
-#ifdef MLSTM_TRACE_STEPS
-#define TRACE(role, step, ev)                                                                  \
-    do {                                                                                       \
-        if (blockIdx.x == 0 && trace_on && (step) < 64) g_trace[((role) * 64 + (step)) * 8 + (ev)] = clock64(); \
-    } while (0)
-#else
-#define TRACE(role, step, ev) do { } while (0)
-#endif
-#define TRACE_ITEM(item, ev, val)                                                              \
-    do {                                                                                       \
-        if (blockIdx.x == 0 && issuer && (item) < 64) g_trace[2048 + (item) * 8 + (ev)] = (val); \
-    } while (0)
-#else
-#define TRACE(role, step, ev) do { } while (0)
-#define TRACE_ITEM(item, ev, val) do { } while (0)
-#endif
 
 template <int D, int ES>
 struct TcCfg {
@@ -120,7 +98,7 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
     return y;
 }
 
-template <int MODE, int D, int ABFMT, typename OutT, bool SPLIT>
+template <int MODE, int D, int ABFMT, typename OutT>
 // 18 warps = up to 5 per SM sub-partition (16384 registers each): at most 96 registers per thread
 __global__ void __launch_bounds__(NTHREADS, 1)
 mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
@@ -134,7 +112,6 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     constexpr bool ROWS_ARE_Q = (MODE == FWD || MODE == DQ || MODE == FWDC);
     constexpr bool IS_FWD = (MODE == FWD || MODE == FWDC);   // normalised output, row sums kept
     static_assert((MODE != FWDC && MODE != STATE) || (D == 128 && ES == 2), "chunkwise passes are built for 16-bit D = 128");
-    static_assert(!SPLIT || MODE == FWD, "only the forward is sliced");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
@@ -161,17 +138,13 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     volatile int* item_ids = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [4] ring of published work items
     // [PARTS][NGROUPS][128]: row sums in FWD / STATE, row dots in DQ / DK, one value per gate group and row
     float* part_base = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + C::NBAR * 8 + 64);
-    constexpr bool STAGED = C::STAGED && !SPLIT;
+    constexpr bool STAGED = C::STAGED;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int NT = p.Spad / TILE;
-    // full head dimension (row stride of every [BH, S, .] tensor)
-    const int Dfull = SPLIT ? p.Dfull : D;
-    const int nks = SPLIT ? Dfull / D : 1;
     const int per_slice = (MODE == STATE) ? p.NB : NT;     // work items per batch*head slice
-    const int nblk = per_slice * p.BH;                      // items per (contraction slice, output slice)
-    const int total = nblk * nks * nks;
+    const int total = per_slice * p.BH;
 
     // A work item = one stationary tile (STATE: one block) of one slice.  The CTA is persistent and
     // takes the next item from a global counter whenever it is ready for one (the producer thread
@@ -184,15 +157,11 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         return ok ? __shfl_sync(0xffffffffu, item_ids[n & 3], 0) : -1;
     };
     struct Item {
-        int bh, tile, blk, first, nsteps, xk0, zv0, vslice;
+        int bh, tile, blk, first, nsteps;
     };
     auto decode = [&](int id) {
         Item it;
-        const int y = id / nblk, x = id - y * nblk;
-        const int kslice = y % nks;                          // slice of the T contraction
-        it.vslice = y / nks;                                 // slice of the output columns
-        it.xk0 = kslice * D;
-        it.zv0 = it.vslice * D;
+        const int x = id;
         const int SLICE_SET = p.slice_set;
         const int per_set = per_slice * SLICE_SET;
         const int set = x / per_set;
@@ -288,18 +257,15 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 mbar_expect_tx(bar_x, C::X_BYTES);
                 for (int c = 0; c < D / C::EPB; c++) {
                     if (MODE == STATE) tma_load_3d(sX + c * BOX_BYTES, &tmI, bar_x, c * C::EPB, 0, 0);
-                    else tma_load_3d(sX + c * BOX_BYTES, &tmX, bar_x, it.xk0 + c * C::EPB, it.tile * TILE, it.bh);
+                    else tma_load_3d(sX + c * BOX_BYTES, &tmX, bar_x, c * C::EPB, it.tile * TILE, it.bh);
                 }
-                [[maybe_unused]] const bool trace_on = (n == 0);
                 auto load_y = [&](int t) {
                     if (is_state_step(t)) load_tile(&tmI, 0, 0, 0);
-                    else load_tile(&tmY, it.xk0, stream_tile(it, t) * TILE, it.bh);
-                    TRACE(0, t, 0);
+                    else load_tile(&tmY, 0, stream_tile(it, t) * TILE, it.bh);
                 };
                 auto load_z = [&](int t) {
                     if (is_state_step(t)) load_tile(&tmS, 0, 0, it.bh * p.NB + it.blk);
-                    else load_tile(&tmZ, it.zv0, stream_tile(it, t) * TILE, it.bh);
-                    TRACE(0, t, 1);
+                    else load_tile(&tmZ, 0, stream_tile(it, t) * TILE, it.bh);
                 };
                 // same order as the MMA issuer consumes: Y(0), then Y(t), Z(t-1) ..., Z(last)
                 load_y(0);
@@ -342,13 +308,9 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 const int id = uni(item_ids[n & 3]);
                 if (id < 0) break;
                 const Item it = decode(id);
-                TRACE_ITEM(n, 0, clock64());
                 ok = wait_u(bar_x, n & 1);
                 if (!ok) break;
                 tc_fence_after();
-                TRACE_ITEM(n, 1, clock64());
-                TRACE_ITEM(n, 4, it.nsteps);
-                [[maybe_unused]] const bool trace_on = (n == 0) && issuer;
                 // Between two MMAs the issuing lane has time to spare (the tensor pipe holds the issue back to its
                 // own pace), between two batches it has none: whatever the warp does there leaves the pipe idle.
                 // So the barriers the next batch depends on are tested in the middle of the current batch; at the
@@ -361,19 +323,16 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 bool preZ = false;   // "loaded" barrier of Z(t-1)'s first unit seen complete
                 auto second = [&](int u) {  // ACC += W(u) Z(u)
                     const int gu = gstep + u;
-                    TRACE(0, u, 2);   // directly after the caller's stamp: what a stamp costs
                     if (!preW) {
                         ok = ok && wait_u(&bar_w[gu & 1], (gu >> 1) & 1);
                         if (ok) tc_fence_after();
                     }
-                    TRACE(1, u, 2);
                     // the accumulator must have been drained by the previous item's epilogue
                     if (ok && u == 0) {
                         ok = wait_u(bar_accfree, (n & 1) ^ 1);
                         if (ok) tc_fence_after();
                     }
                     if (!ok) return;
-                    TRACE(1, u, 5);
                     const uint32_t w_tmem = tmem_T0u + (gu & 1) * 128;
                     constexpr int KS2 = TILE / C::KSTEP;   // KSTEP streamed rows per MMA
                     preY = false;
@@ -381,7 +340,6 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     for (int un = 0; un < C::UPT; un++, useq++) {
                         if (!(un == 0 && preZ)) ok = wait_u(&bar_full[useq % C::RING], (useq / C::RING) & 1);   // TMA data: no tcgen05 fence
                         if (!ok) return;
-                        if (un == 0) TRACE(1, u, 6);
 #pragma unroll
                         for (int part = 0; part < 2; part++) {
                             if (issuer) {
@@ -407,13 +365,11 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                                 preY = try_u(&bar_full[(useq + 1) % C::RING], ((useq + 1) / C::RING) & 1);
                         }
                     }
-                    TRACE(1, u, 3);
                 };
                 for (int t = 0; t < it.nsteps && ok; t++) {
                     // T(t) = X Y(t)^T
                     const int gt = gstep + t;
                     const uint32_t t_tmem = tmem_T0u + (gt & 1) * 128;
-                    TRACE(1, t, 0);
                     constexpr int KS1 = C::CH / C::KSTEP;
                     preW = false;
                     preZ = false;
@@ -421,7 +377,6 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     for (int un = 0; un < C::UPT; un++, useq++) {
                         if (!(un == 0 && preY)) ok = wait_u(&bar_full[useq % C::RING], (useq / C::RING) & 1);
                         if (!ok) break;
-                        if (un == 0) TRACE(1, t, 7);
 #pragma unroll
                         for (int part = 0; part < 2; part++) {
                             if (issuer) {
@@ -455,17 +410,13 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     }
                     preY = false;
                     if (!ok) break;
-                    TRACE(1, t, 1);
-                    TRACE(1, t, 4);
                     if (t >= 1) second(t - 1);
                 }
                 preW = false;
                 preZ = false;
-                TRACE_ITEM(n, 2, clock64());
                 if (ok) second(it.nsteps - 1);
                 if (ok && issuer) tc_commit(bar_acc);
                 __syncwarp();
-                TRACE_ITEM(n, 3, clock64());
                 gstep += it.nsteps;
             }
         }
@@ -497,16 +448,17 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         // only when that item starts, so nobody waits for those loads.
         struct RowRaw {
             float rel, g;
-            double ref, b0, b1;
+            double ref, b0, b1, lb;
         };
         auto fetch_rows = [&](const Item& it) {
-            RowRaw rr{0.0f, 0.0f, 0.0, 0.0, 0.0};
+            RowRaw rr{0.0f, 0.0f, 0.0, 0.0, 0.0, static_cast<double>(INFINITY)};
             const int grow = it.tile * TILE + r;
             const size_t vec_base = static_cast<size_t>(it.bh) * p.Spad;
             if (MODE == FWDC || MODE == STATE) {
                 const double* bound = p.An_bound + static_cast<size_t>(it.bh) * (p.NB + 1) + it.blk;
                 rr.b0 = bound[0];
                 rr.b1 = bound[1];
+                if (MODE == FWDC && p.late_bound) rr.lb = p.late_bound[it.bh];
             }
             if (MODE != STATE) {
                 rr.rel = p.row_rel[vec_base + grow];
@@ -517,17 +469,22 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         };
         constexpr int UNKNOWN = -2;
         int id = next_item(0, ok);
-        RowRaw raw{0.0f, 0.0f, 0.0, 0.0, 0.0};
+        RowRaw raw{0.0f, 0.0f, 0.0, 0.0, 0.0, static_cast<double>(INFINITY)};
         if (ok && id >= 0) raw = fetch_rows(decode(id));
 
         for (int n = 0; ok && id >= 0; n++) {
         const Item it = decode(id);
-        const int bh = it.bh, tile = it.tile, blk = it.blk, nsteps = it.nsteps, zv0 = it.zv0, vslice = it.vslice;
+        const int bh = it.bh, tile = it.tile, blk = it.blk, nsteps = it.nsteps;
         const int grow = tile * TILE + r;              // row inside the slice (may be >= S in the last tile)
         const size_t vec_base = static_cast<size_t>(bh) * p.Spad;
         const size_t ref_base = static_cast<size_t>(bh) * (p.Spad / REF_BLOCK);
-        const double er_d = (MODE == STATE) ? raw.b1 : static_cast<double>(raw.rel) + raw.ref + static_cast<double>(p.er_add);
-        const float er_state = (MODE == FWDC) ? static_cast<float>(er_d - raw.b0) : 0.0f;
+        // FWDC with a late carry: the row's stabiliser -A*log2e and the inbound block boundary are capped by the
+        // carried-in maximum, and m grows by what the cap took off
+        const double negA = static_cast<double>(raw.rel) + raw.ref;
+        const double negA_c = (MODE == FWDC) ? fmin(negA, raw.lb) : negA;
+        const float m_shift = (MODE == FWDC) ? static_cast<float>((negA - negA_c) * 0.6931471805599453) : 0.0f;
+        const double er_d = (MODE == STATE) ? raw.b1 : negA_c + static_cast<double>(p.er_add);
+        const float er_state = (MODE == FWDC) ? static_cast<float>(er_d - fmin(raw.b0, raw.lb)) : 0.0f;
         const float g_row = raw.g;
         float rowsum = 0.0f;
 
@@ -551,20 +508,15 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             // DK adds a per-column term to T.  Each lane fetches one column's value before the wait (32 more
             // registers are not to be had) and the warp passes them round with shuffles afterwards.
             const float g_lane = (MODE == DK) ? __ldg(p.col_g + vec_base + st * TILE + cbase + lane) : 0.0f;
-            [[maybe_unused]] const bool trace_on = (n == 0) && (threadIdx.x == 64 || threadIdx.x == 64 + 15 * 32);
-            [[maybe_unused]] const int trole = threadIdx.x == 64 ? 2 : 3;
-            TRACE(trole, t, 0);
             // units before the last one of Y(t): tiles go Y(0), Y(1), Z(0), Y(2), Z(1), ... in every item
             const int sq = (2 * gstep + (t == 0 ? 0 : 2 * t - 1) + 1) * C::UPT - 1;
             ok = mbar_wait_warp<SLACK_SLEEP_NS>(&bar_cons[sq % C::RING], (sq / C::RING) & 1, abort_flag, WAIT_LIMIT);
             if (!ok) break;
-            TRACE(trole, t, 1);
             tc_fence_after();
             const uint32_t t_tmem = tmem_T0 + buf * 128 + lane_bits + cbase;
             uint32_t tv[32];
             tmem_ld32(t_tmem, tv);
             tc_wait_ld();
-            TRACE(trole, t, 2);
             if (MODE == DK) {   // T + g with g per column: added eight columns at a time to keep registers free
 #pragma unroll
                 for (int j = 0; j < 32; j++)
@@ -603,7 +555,6 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     cv[j] = wj;
                 }
             }
-            TRACE(trole, t, 3);
             if constexpr (TF32) {
 #pragma unroll
                 for (int j = 0; j < 32; j++) tv[j] = to_tf32(cv[j]);
@@ -622,13 +573,10 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 }
                 tmem_st16(t_tmem, pk);   // two values per column, over the first 16 of this group's 32 columns
             }
-            TRACE(trole, t, 4);
             tc_wait_st();
-            TRACE(trole, t, 5);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_w[buf]);   // 16 arrivals instead of 512 on one shared-memory word
-            TRACE(trole, t, 6);
         }
         if (!ok) break;
         gstep += nsteps;
@@ -655,17 +603,12 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             }
             if (IS_FWD) {
                 // on its way during the exchange
-                const float mrow = (!SPLIT && row_ok) ? p.m[static_cast<size_t>(bh) * p.S + grow] : 0.0f;
+                const float mrow = row_ok ? p.m[static_cast<size_t>(bh) * p.S + grow] + m_shift : 0.0f;
                 const float bsum = exchange(rowsum);
                 if (ok) {
-                    if constexpr (SPLIT) {
-                        // partial row sum of this contraction slice; the normaliser is applied afterwards
-                        if (grp == 0 && row_ok && vslice == 0) atomicAdd(&p.b_out[static_cast<size_t>(bh) * p.S + grow], bsum);
-                    } else {
-                        const float nrm = fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f;
-                        inv_n = 1.0f / nrm;
-                        if (grp == 0 && row_ok && p.b_out) p.b_out[static_cast<size_t>(bh) * p.S + grow] = bsum;
-                    }
+                    const float nrm = fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f;
+                    inv_n = 1.0f / nrm;
+                    if (grp == 0 && row_ok && p.b_out) p.b_out[static_cast<size_t>(bh) * p.S + grow] = bsum;
                 }
             }
         };
@@ -680,7 +623,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         if (!ok) break;
         // next work item, if it is published already, and its row terms
         int id_next = UNKNOWN;
-        RowRaw raw_next{0.0f, 0.0f, 0.0, 0.0, 0.0};
+        RowRaw raw_next{0.0f, 0.0f, 0.0, 0.0, 0.0, static_cast<double>(INFINITY)};
         if (__all_sync(0xffffffffu, mbar_test_wait(&bar_item[(n + 1) & 3], ((n + 1) >> 2) & 1) ? 1 : 0)) {
             id_next = __shfl_sync(0xffffffffu, item_ids[(n + 1) & 3], 0);
             if (id_next >= 0) raw_next = fetch_rows(decode(id_next));
@@ -693,13 +636,13 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             tc_fence_after();
             if (!sums_early) row_sums();
             if (!ok) break;
-            // STATE writes block (bh, blk) of [BH, NB, D, D]; everything else row `grow` of [BH, S, Dfull]
+            // STATE writes block (bh, blk) of [BH, NB, D, D]; everything else row `grow` of [BH, S, D]
             const size_t row_off = (MODE == STATE)
                                        ? ((static_cast<size_t>(bh) * p.NB + blk) * D + r) * D
-                                       : (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * Dfull + zv0;
+                                       : (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * D;
             float dot = 0.0f;
             OutT* orow = reinterpret_cast<OutT*>(p.out) + row_off + c0;
-            const InT* ogate_row = (IS_FWD && !SPLIT && p.ogate) ? reinterpret_cast<const InT*>(p.ogate) + row_off + c0 : nullptr;
+            const InT* ogate_row = (IS_FWD && p.ogate) ? reinterpret_cast<const InT*>(p.ogate) + row_off + c0 : nullptr;
             const InT* drow = ((MODE == DQ || MODE == DK) && p.dot_src)
                                   ? reinterpret_cast<const InT*>(p.dot_src) + row_off + c0 : nullptr;
 #pragma unroll 1
@@ -775,18 +718,12 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                         if (lane == 0) {
                             const int x = c0 + ch * 32 + sub * (64 / static_cast<int>(sizeof(OutT)));
                             if (MODE == STATE) tma_store_3d(&tmO, stage, x, (warp & 3) * 32, bh * p.NB + blk);
-                            else tma_store_3d(&tmO, stage, zv0 + x, tile * TILE + (warp & 3) * 32, bh);
+                            else tma_store_3d(&tmO, stage, x, tile * TILE + (warp & 3) * 32, bh);
                             bulk_commit();
                         }
                     }
                 } else if (row_ok) {
-                    if constexpr (SPLIT) {
-#pragma unroll
-                        for (int j4 = 0; j4 < CW / 4; j4++) {
-                            float4 o4 = make_float4(vals[j4 * 4], vals[j4 * 4 + 1], vals[j4 * 4 + 2], vals[j4 * 4 + 3]);
-                            atomicAdd(reinterpret_cast<float4*>(reinterpret_cast<float*>(orow) + ch * CW + j4 * 4), o4);
-                        }
-                    } else if constexpr (sizeof(OutT) == 4) {
+                    if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
                         for (int j4 = 0; j4 < CW / 4; j4++) {
                             float4 o4 = make_float4(vals[j4 * 4], vals[j4 * 4 + 1], vals[j4 * 4 + 2], vals[j4 * 4 + 3]);
@@ -846,60 +783,100 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn get_encode() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn) return fn;
+    static std::atomic<EncodeTiledFn> fn{nullptr};   // the lookup is idempotent: concurrent first callers agree
+    EncodeTiledFn f = fn.load(std::memory_order_acquire);
+    if (f) return f;
     void* sym = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
         qres != cudaDriverEntryPointSuccess)
         return nullptr;
-    fn = reinterpret_cast<EncodeTiledFn>(sym);
-    return fn;
+    f = reinterpret_cast<EncodeTiledFn>(sym);
+    fn.store(f, std::memory_order_release);
+    return f;
 }
 
-// [N2, N1, N0] tensor (N0 contiguous), boxes of 128 bytes x 128 rows, 128-byte swizzle, zero fill
-// outside the tensor.
-// atom32: 128-byte swizzle with 32-byte atoms (needed where a 32-bit tile is read MN-major).
-int make_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, bool atom32 = false, int box_rows = 128) {
+// Encoding a tensor map costs about a microsecond of host time, and one call of the library needs the same
+// few maps in several passes: each host thread keeps the last maps it encoded, keyed by everything that goes in.
+struct MapKey {
+    const void* base;
+    int n2, n1, n0, dtype, swizzle, box_rows, box_bytes;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && n2 == o.n2 && n1 == o.n1 && n0 == o.n0 && dtype == o.dtype && swizzle == o.swizzle &&
+               box_rows == o.box_rows && box_bytes == o.box_bytes;
+    }
+};
+struct MapCache {
+    static constexpr int N = 32;
+    MapKey keys[N] = {};
+    CUtensorMap maps[N];
+    bool used[N] = {};
+    int next = 0;
+    const CUtensorMap* find(const MapKey& k) const {
+        for (int i = 0; i < N; i++)
+            if (used[i] && keys[i] == k) return &maps[i];
+        return nullptr;
+    }
+    void put(const MapKey& k, const CUtensorMap& m) {
+        keys[next] = k; maps[next] = m; used[next] = true;
+        next = (next + 1) % N;
+    }
+};
+thread_local MapCache g_map_cache;
+
+// [N2, N1, N0] tensor (N0 contiguous): boxes of box_bytes x box_rows, given swizzle, zero fill outside the tensor
+int encode_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, CUtensorMapSwizzle swz, int box_rows,
+               int box_bytes, CUtensorMapL2promotion promo) {
+    const MapKey key{base, N2, N1, N0, dtype, static_cast<int>(swz), box_rows, box_bytes};
+    if (const CUtensorMap* hit = g_map_cache.find(key)) {
+        *map = *hit;
+        return MLSTM_OK;
+    }
     EncodeTiledFn enc = get_encode();
     if (!enc) return MLSTM_E_CUDA;
     const cuuint64_t es = dtype == MLSTM_DT_F32 ? 4 : 2;
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(N0), static_cast<cuuint64_t>(N1), static_cast<cuuint64_t>(N2)};
     cuuint64_t strides[2] = {static_cast<cuuint64_t>(N0) * es, static_cast<cuuint64_t>(N1) * N0 * es};
-    cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(box_rows), 1};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(box_bytes / es), static_cast<cuuint32_t>(box_rows), 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUtensorMapDataType dt = dtype == MLSTM_DT_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                              : dtype == MLSTM_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                       : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? MLSTM_OK : MLSTM_E_CUDA;
+    CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, promo,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return MLSTM_E_CUDA;
+    g_map_cache.put(key, *map);
+    return MLSTM_OK;
+}
+
+// Boxes of 128 bytes x box_rows rows with the 128-byte swizzle.
+// atom32: 128-byte swizzle with 32-byte atoms (needed where a 32-bit tile is read MN-major).
+int make_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, bool atom32 = false, int box_rows = 128) {
+    return encode_map(map, base, N2, N1, N0, dtype, atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                      box_rows, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
 }
 
 int sm_count() {
-    static int cached[64] = {};
+    static std::atomic<int> cached[MAX_DEVICES];   // zero-initialised; the query is idempotent
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
-    if (cached[dev] == 0) {
-        int n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -1;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
-        cached[dev] = n;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
-    return cached[dev];
+    return n;
 }
 
-template <int MODE, int D, int ABFMT, typename OutT, bool SPLIT>
+template <int MODE, int D, int ABFMT, typename OutT>
 int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
     PassParams p = p_in;
-    p.slice_set = tc_slice_set();
+    p.slice_set = SLICE_SET_DEFAULT;
     CUtensorMap mx, my, mz, mi, ms, mo;
     int rc;
-    const int Dfull = SPLIT ? p.Dfull : D;
-    if (SPLIT && (Dfull <= 0 || Dfull % D != 0)) return MLSTM_E_SHAPE;
-    if ((rc = make_map(&mx, p.X, p.BH, p.S, Dfull, in_dtype)) != MLSTM_OK) return rc;
-    if ((rc = make_map(&my, p.Y, p.BH, p.S, Dfull, in_dtype)) != MLSTM_OK) return rc;
-    if ((rc = make_map(&mz, p.Z, p.BH, p.S, Dfull, in_dtype, ABFMT == 2)) != MLSTM_OK) return rc;
+    if ((rc = make_map(&mx, p.X, p.BH, p.S, D, in_dtype)) != MLSTM_OK) return rc;
+    if ((rc = make_map(&my, p.Y, p.BH, p.S, D, in_dtype)) != MLSTM_OK) return rc;
+    if ((rc = make_map(&mz, p.Z, p.BH, p.S, D, in_dtype, ABFMT == 2)) != MLSTM_OK) return rc;
     mi = mx;
     ms = mx;
     if (MODE == FWDC || MODE == STATE) {
@@ -911,22 +888,30 @@ int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
         if ((rc = make_map(&ms, p.states, p.BH * p.NB, D, D, in_dtype)) != MLSTM_OK) return rc;
     }
     mo = mx;
-    if (TcCfg<D, ABFMT == 2 ? 4 : 2>::STAGED && !SPLIT) {
+    if (TcCfg<D, ABFMT == 2 ? 4 : 2>::STAGED) {
         constexpr int out_dtype = sizeof(OutT) == 4 ? MLSTM_DT_F32 : (ABFMT == 1 ? MLSTM_DT_BF16 : MLSTM_DT_F16);
         if (MODE == STATE) rc = tc_make_map_out(&mo, p.out, p.BH * p.NB, D, D, out_dtype, 32);
         else rc = tc_make_map_out(&mo, p.out, p.BH, p.S, D, out_dtype, 32);
         if (rc != MLSTM_OK) return rc;
     }
-    auto kern = mlstm_tc_pass<MODE, D, ABFMT, OutT, SPLIT>;
+    auto kern = mlstm_tc_pass<MODE, D, ABFMT, OutT>;
     constexpr int smem = TcCfg<D, ABFMT == 2 ? 4 : 2>::SMEM_BYTES;
-    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (ce != cudaSuccess) {
-        cudaGetLastError();
-        return note_cuda_error(ce, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
+    cudaError_t ce;
+    {   // the shared-memory opt-in is a per-device property of the kernel: set once per device
+        static std::atomic<bool> opted[MAX_DEVICES];
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return MLSTM_E_CUDA;
+        if (!opted[dev].load(std::memory_order_acquire)) {
+            ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (ce != cudaSuccess) {
+                cudaGetLastError();
+                return note_cuda_error(ce, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
+            }
+            opted[dev].store(true, std::memory_order_release);
+        }
     }
     const int NT = p.Spad / TILE;
-    const int nsl = SPLIT ? (Dfull / D) * (Dfull / D) : 1;  // contraction slices x output slices
-    const long long total = static_cast<long long>(MODE == STATE ? p.NB : NT) * p.BH * nsl;
+    const long long total = static_cast<long long>(MODE == STATE ? p.NB : NT) * p.BH;
     if (total > 0x7fffffffLL) return MLSTM_E_SHAPE;
     const int sms = sm_count();
     if (sms <= 0) return MLSTM_E_CUDA;
@@ -941,11 +926,11 @@ int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
 
 template <int MODE, int D, int ABFMT>
 int launch_out(const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) {
-    if (out_dtype == MLSTM_DT_F32) return launch_one<MODE, D, ABFMT, float, false>(p, in_dtype, st);
+    if (out_dtype == MLSTM_DT_F32) return launch_one<MODE, D, ABFMT, float>(p, in_dtype, st);
     if constexpr (ABFMT != 2) {
         if (out_dtype == in_dtype) {
-            if (ABFMT == 1) return launch_one<MODE, D, ABFMT, __nv_bfloat16, false>(p, in_dtype, st);
-            return launch_one<MODE, D, ABFMT, __half, false>(p, in_dtype, st);
+            if (ABFMT == 1) return launch_one<MODE, D, ABFMT, __nv_bfloat16>(p, in_dtype, st);
+            return launch_one<MODE, D, ABFMT, __half>(p, in_dtype, st);
         }
     }
     return MLSTM_E_ARG;
@@ -973,63 +958,27 @@ int launch_d(const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) 
 
 }  // namespace
 
-#ifdef MLSTM_TRACE
-extern "C" int mlstm_debug_trace(long long* out, int n) {
-    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * (n < 2560 ? n : 2560)) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 int tc_make_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, bool atom32, int box_rows) {
     return make_map(map, base, N2, N1, N0, dtype, atom32, box_rows);
 }
 
 int tc_make_map_out(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, int box_rows) {
-    EncodeTiledFn enc = get_encode();
-    if (!enc) return MLSTM_E_CUDA;
-    const cuuint64_t es = dtype == MLSTM_DT_F32 ? 4 : 2;
-    cuuint64_t dims[3] = {static_cast<cuuint64_t>(N0), static_cast<cuuint64_t>(N1), static_cast<cuuint64_t>(N2)};
-    cuuint64_t strides[2] = {static_cast<cuuint64_t>(N0) * es, static_cast<cuuint64_t>(N1) * N0 * es};
-    cuuint32_t box[3] = {static_cast<cuuint32_t>(64 / es), static_cast<cuuint32_t>(box_rows), 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUtensorMapDataType dt = dtype == MLSTM_DT_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                             : dtype == MLSTM_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? MLSTM_OK : MLSTM_E_CUDA;
+    return encode_map(map, base, N2, N1, N0, dtype, CU_TENSOR_MAP_SWIZZLE_64B, box_rows, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE);
 }
 
 int tc_sm_count() { return sm_count(); }
 
-int tc_slice_set() {
-    static int slice_set = 0;   // MLSTM_SLICE_SET overrides the default (tuning aid)
-    if (slice_set == 0) {
-        const char* e = getenv("MLSTM_SLICE_SET");
-        slice_set = (e && atoi(e) > 0) ? atoi(e) : SLICE_SET_DEFAULT;
-    }
-    return slice_set;
-}
+int tc_slice_set() { return SLICE_SET_DEFAULT; }
 
 bool tc_supported(int S, int D, int in_dtype) {
     return S >= 1 && (D == 64 || D == 128 || D == 256) &&
            (in_dtype == MLSTM_DT_F16 || in_dtype == MLSTM_DT_BF16 || in_dtype == MLSTM_DT_F32);
 }
 
-bool tc_split_supported(int S, int D, int in_dtype) {
-    return S >= 1 && D > 256 && D % 256 == 0 && D <= 4096 &&
-           (in_dtype == MLSTM_DT_F16 || in_dtype == MLSTM_DT_BF16 || in_dtype == MLSTM_DT_F32);
-}
-
 int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) {
     if (!tc_supported(p.S, p.D, in_dtype)) return MLSTM_E_UNSUPPORTED;
-    if (mode <= DV && tc_pair_supported(p.S, p.D, in_dtype)) {
-        static int use_pairs = -1;   // MLSTM_NO_PAIR=1 keeps the one-CTA kernel (comparison aid)
-        if (use_pairs < 0) {
-            const char* e = getenv("MLSTM_NO_PAIR");
-            use_pairs = (e && atoi(e) > 0) ? 0 : 1;
-        }
-        if (use_pairs) return launch_pass_tc_pair(mode, p, in_dtype, out_dtype, st);
-    }
+    if (mode <= DV && tc_pair_supported(p.S, p.D, in_dtype)) return launch_pass_tc_pair(mode, p, in_dtype, out_dtype, st);
     switch (mode) {
         case FWD: return launch_d<FWD>(p, in_dtype, out_dtype, st);
         case DQ: return launch_d<DQ>(p, in_dtype, out_dtype, st);
@@ -1041,19 +990,6 @@ int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, c
         case STATE:
             if (p.D != 128 || out_dtype != MLSTM_DT_F32) return MLSTM_E_UNSUPPORTED;
             return launch_fmt<STATE, 128>(p, in_dtype, out_dtype, st);
-    }
-    return MLSTM_E_ARG;
-}
-
-// Sliced forward for head dimensions above 256: p.D is the slice width (256), p.Dfull the head
-// dimension, p.out an fp32 [BH, S, Dfull] buffer and p.b_out an fp32 [BH, S] buffer, both zeroed by
-// the caller; the launch adds the un-normalised numerator and the row sums into them.
-int launch_fwd_split_tc(const PassParams& p, int in_dtype, cudaStream_t st) {
-    if (p.D != 256 || !tc_split_supported(p.S, p.Dfull, in_dtype)) return MLSTM_E_UNSUPPORTED;
-    switch (in_dtype) {
-        case MLSTM_DT_F32: return launch_one<FWD, 256, 2, float, true>(p, in_dtype, st);
-        case MLSTM_DT_BF16: return launch_one<FWD, 256, 1, float, true>(p, in_dtype, st);
-        case MLSTM_DT_F16: return launch_one<FWD, 256, 0, float, true>(p, in_dtype, st);
     }
     return MLSTM_E_ARG;
 }

@@ -25,7 +25,7 @@
 // barriers that the MMA thread signals exist in both CTAs and get one tcgen05.commit each.  Every CTA
 // issues its own loads into its own shared memory.  Every wait is bounded as in mm_tc.cu; the two hardware cluster barriers
 // (after initialisation, before exit) are reached by every thread on every path.
-#include <cstdlib>
+#include <atomic>
 #include <type_traits>
 
 #include "mlstm_common.cuh"
@@ -55,35 +55,6 @@ constexpr float MAX_ROW_EXP2 = 60.0f;           // clamp of the per-row exponent
 constexpr int SLACK_SLEEP_NS = 64;              // poll interval of the roles that wait with slack (gate warps, producer)
 static_assert(SMEM_BYTES <= 232448, "exceeds the shared memory of a CTA");
 
-#ifdef MLSTM_TRACE
-// Development aid (not built into the library): clock64() stamps of cluster 0.
-//   [0, 512)      leader MMA warp, item 1, [step][event]
-//   [512, 1536)   gate warp 2 of the leader / follower, item 1, [step][event]; step 60 = epilogue of item 0
-//   [1536, 2048)  leader MMA warp, per item [item][event]
-__device__ long long g_trace_pair[4 * 64 * 8];
-#define PTRACE(step, ev)                                                                                   \
-    do {                                                                                                   \
-        if (blockIdx.x == 0 && n == 1 && issuer && (step) < 64) g_trace_pair[(step) * 8 + (ev)] = clock64(); \
-    } while (0)
-#define ETRACE(ev)                                                                                         \
-    do {                                                                                                   \
-        if (blockIdx.x < 2 && n == 0 && threadIdx.x == 64) g_trace_pair[(1 + blockIdx.x) * 512 + 60 * 8 + (ev)] = clock64(); \
-    } while (0)
-#define ITRACE(item, ev, val)                                                                              \
-    do {                                                                                                   \
-        if (blockIdx.x == 0 && issuer && (item) < 64) g_trace_pair[1536 + (item) * 8 + (ev)] = (val);      \
-    } while (0)
-#define GTRACE(step, ev)                                                                                   \
-    do {                                                                                                   \
-        if (blockIdx.x < 2 && n == 1 && threadIdx.x == 64 && (step) < 60)                                  \
-            g_trace_pair[(1 + blockIdx.x) * 512 + (step) * 8 + (ev)] = clock64();                          \
-    } while (0)
-#else
-#define PTRACE(step, ev) do { } while (0)
-#define ETRACE(ev) do { } while (0)
-#define ITRACE(item, ev, val) do { } while (0)
-#define GTRACE(step, ev) do { } while (0)
-#endif
 
 template <int MODE, int ABFMT, typename OutT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1)
@@ -281,23 +252,18 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                 const int id = uni(item_ids[n & 3]);
                 if (id < 0) break;
                 const Item it = decode(id);
-                ITRACE(n, 0, clock64());
                 ok = wait_u(bar_x, n & 1);
                 if (!ok) break;
                 tc_fence_after();
-                ITRACE(n, 1, clock64());
-                ITRACE(n, 4, it.nsteps);
                 auto second = [&](int u) {  // ACC += W(u) Z(u), both CTAs
                     const int gu = gstep + u;
                     ok = ok && wait_u(&bar_w[gu & 1], (gu >> 1) & 1);
-                    PTRACE(u, 3);
                     if (ok && u == 0) ok = wait_u(bar_accfree, (n & 1) ^ 1);
                     if (!ok) return;
                     tc_fence_after();
                     const int s = slot_it % NSLOT;
                     ok = wait_u(&bar_full[s], (slot_it / NSLOT) & 1);
                     if (!ok) return;
-                    PTRACE(u, 4);
                     const uint32_t w_tmem = tmem_T0u + (gu & 1) * 128;
                     const uint64_t zdesc = smem_desc_advance(zdesc0, s * SLOT_BYTES);
                     if (issuer) {
@@ -309,17 +275,14 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                         commit_both(&bar_empty[s]);
                     }
                     __syncwarp();
-                    PTRACE(u, 5);
                     slot_it++;
                 };
                 for (int t = 0; t < it.nsteps && ok; t++) {
                     const int gt = gstep + t;
                     const uint32_t t_tmem = tmem_T0u + (gt & 1) * 128;
                     const int s = slot_it % NSLOT;
-                    PTRACE(t, 0);
                     ok = wait_u(&bar_full[s], (slot_it / NSLOT) & 1);
                     if (!ok) break;
-                    PTRACE(t, 1);
                     const uint64_t ydesc = smem_desc_advance(ydesc0, s * SLOT_BYTES);
                     if (issuer) {
 #pragma unroll
@@ -332,15 +295,12 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                         if (t == it.nsteps - 1) commit_both(bar_xfree);
                     }
                     __syncwarp();
-                    PTRACE(t, 2);
                     slot_it++;
                     if (t >= 1) second(t - 1);
                 }
-                ITRACE(n, 2, clock64());
                 if (ok) second(it.nsteps - 1);
                 if (ok && issuer) commit_both(bar_acc);
                 __syncwarp();
-                ITRACE(n, 3, clock64());
                 gstep += it.nsteps;
             }
         }
@@ -413,10 +373,8 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             // DK adds a per-column term to T.  Each lane fetches one column's value before the wait (32 more
             // registers are not to be had) and the warp passes them round with shuffles afterwards.
             const float g_lane = (MODE == DK && !dead) ? __ldg(p.col_g + vec_base + st * TILE + cbase + lane) : 0.0f;
-            GTRACE(t, 0);
             ok = mbar_wait_warp<SLACK_SLEEP_NS>(&bar_t[buf], (gt >> 1) & 1, abort_flag, WAIT_LIMIT);
             if (!ok) break;
-            GTRACE(t, 1);
             tc_fence_after();
             const uint32_t t_tmem = tmem_T0 + buf * 128 + lane_bits + cbase;
             uint32_t pk[16];
@@ -467,13 +425,11 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                     }
                 }
             }
-            GTRACE(t, 2);
             tmem_st16(t_tmem, pk);
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(lead_w[buf]);
-            GTRACE(t, 3);
         }
         if (!ok) break;
         gstep += nsteps;
@@ -499,7 +455,6 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         // The row partials are reused from item to item.  Nobody still reads the previous item's: a warp gets
         // past step 2 of this item only after every gate warp of the pair has finished step 0 of it (the third
         // T tile follows the first W tile), which follows its previous epilogue.  Shorter items exchange later.
-        ETRACE(0);
         if (IS_FWD && nsteps > 2) fwd_norm();
         if (!ok) break;
         // next work item, if it is published already, and its row terms
@@ -513,7 +468,6 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         // ---- epilogue: each group drains a quarter of this CTA's accumulator columns
         ok = mbar_wait_warp<SLACK_SLEEP_NS>(bar_acc, n & 1, abort_flag, WAIT_LIMIT);
         if (!ok) break;
-        ETRACE(1);
         {
             tc_fence_after();
             constexpr int QUART = D / NGROUPS;   // 64
@@ -521,7 +475,6 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             const size_t row_off = (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * D;
             if (IS_FWD && nsteps <= 2) fwd_norm();
             if (!ok) break;
-            ETRACE(2);
             float dot = 0.0f;
             const InT* ogate_row = (IS_FWD && p.ogate) ? reinterpret_cast<const InT*>(p.ogate) + row_off + c0 : nullptr;
             const InT* drow = ((MODE == DQ || MODE == DK) && p.dot_src) ? reinterpret_cast<const InT*>(p.dot_src) + row_off + c0
@@ -531,12 +484,10 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                 uint32_t av[32];
                 tmem_ld32(tmem_ACC + lane_bits + c0 + ch * 32, av);
                 tc_wait_ld();
-                if (ch == 0) ETRACE(5);
                 if (ch == QUART / 32 - 1) {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_remote(lead_accfree);
-                    ETRACE(3);
                 }
                 float vals[32];
 #pragma unroll
@@ -564,7 +515,6 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                 for (int sub = 0; sub < NSUB; sub++) {
                     if (lane == 0) bulk_wait_read_all();   // the previous store has read the buffer
                     __syncwarp();
-                    if (ch == 0 && sub == 0) ETRACE(6);
                     uint4* srow = reinterpret_cast<uint4*>(stage + lane * 64);
                     const int sw = (lane >> 1) & 3;   // 64-byte swizzle of the store's tensor map: no bank conflicts
                     if constexpr (sizeof(OutT) == 4) {
@@ -589,23 +539,15 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                             srow[j4 ^ sw] = make_uint4(o32[0], o32[1], o32[2], o32[3]);
                         }
                     }
-#ifdef MLSTM_TRACE
-                    if (ch == 0 && sub == 0) ETRACE(6);   // after the shared-memory writes
                     fence_async_smem();
-                    if (ch == 0 && sub == 0) ETRACE(5);   // after the proxy fence
-#else
-                    fence_async_smem();
-#endif
                     __syncwarp();
                     if (lane == 0 && active) {
                         tma_store_3d(&tmO, stage, c0 + ch * 32 + sub * (64 / static_cast<int>(sizeof(OutT))),
                                      tile * TILE + (warp & 3) * 32, bh);
                         bulk_commit();
                     }
-                    if (ch == 0 && sub == 0) ETRACE(7);
                 }
             }
-            ETRACE(4);
             if ((MODE == DQ || MODE == DK) && p.dot_out) {
                 const float dsum = exchange(dot);
                 if (ok && grp == 0 && active) p.dot_out[vec_base + grow] = row_ok ? dsum : 0.0f;
@@ -649,11 +591,13 @@ int launch_pair_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
     if ((rc = tc_make_map(&myh, p.Y, p.BH, p.S, D, in_dtype, false, 64)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map(&mz, p.Z, p.BH, p.S, D, in_dtype, false, 128)) != MLSTM_OK) return rc;
     auto kern = mlstm_tc_pass_pair<MODE, ABFMT, OutT>;
-    // per device: shared-memory opt-in and how many pairs can be resident at once
-    static int pairs_resident[64] = {};
+    // per device: shared-memory opt-in and how many pairs can be resident at once (both idempotent, so
+    // concurrent first callers may both run the set-up; the count is published last)
+    static std::atomic<int> pairs_resident_dev[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MLSTM_E_CUDA;
-    if (pairs_resident[dev] == 0) {
+    int pairs_resident = pairs_resident_dev[dev].load(std::memory_order_acquire);
+    if (pairs_resident == 0) {
         cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (ce != cudaSuccess) {
             cudaGetLastError();
@@ -678,12 +622,13 @@ int launch_pair_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
             cudaGetLastError();
             nclusters = sms / 2;   // the grid does not have to be resident at once: CTAs only wait inside their pair
         }
-        pairs_resident[dev] = nclusters < sms / 2 ? nclusters : sms / 2;
+        pairs_resident = nclusters < sms / 2 ? nclusters : sms / 2;
+        pairs_resident_dev[dev].store(pairs_resident, std::memory_order_release);
     }
     const int NT = p.Spad / TILE;
     const long long total = static_cast<long long>((NT + 1) / 2) * p.BH;
     if (total > 0x3fffffffLL) return MLSTM_E_SHAPE;
-    const unsigned npairs = static_cast<unsigned>(total < pairs_resident[dev] ? total : pairs_resident[dev]);
+    const unsigned npairs = static_cast<unsigned>(total < pairs_resident ? total : pairs_resident);
     if (!p.sched) return MLSTM_E_ARG;
     cudaError_t ce = cudaMemsetAsync(p.sched + MODE, 0, sizeof(int), st);
     if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
@@ -706,11 +651,6 @@ int launch_pair_fmt(const PassParams& p, int in_dtype, int out_dtype, cudaStream
 
 }  // namespace
 
-#ifdef MLSTM_TRACE
-extern "C" int mlstm_debug_trace_pair(long long* out, int n) {
-    return cudaMemcpyFromSymbol(out, g_trace_pair, sizeof(long long) * (n < 2048 ? n : 2048)) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 // 16-bit inputs, head dimension 256, at least two tiles per slice (a single tile has no partner)
 bool tc_pair_supported(int S, int Dh, int in_dtype) {

@@ -1,0 +1,546 @@
+// Two-pass tensor-core forward for head dimensions above 256, the shape of the reference's scan demo
+// (mlstm_scan.py:375-394: S = 2048, D = 1024, where the D x D state of the recurrent form is larger
+// than the S x S decay matrix, so the quadratic form is the one with the least arithmetic).
+//
+// It takes the place of the three contraction kernels of the reference's scan path
+// (precompute_mlstm_triton_scan mlstm_scan.py:74-137, reduce_mlstm_triton :143-195, mlstm_triton_scan
+// :200-278), which re-read K and Q once per 4 x 4 state patch.  Here every contraction is done once:
+//
+//   pass 1 (GATE)  W[r, c] = (q_r . k_c) * exp2(ec[c] + er[r])  for c <= r       [BH, S, S], causal part only
+//                  one work item = 128 query rows x 256 key columns, contraction over the whole head
+//                  dimension in 128-byte chunks; the gate factor, the causal mask and the partial row
+//                  sums (the normaliser's b) are applied in the epilogue, W goes to a workspace that
+//                  stays in L2 at the demo's size (33.5 MB written, read four times by pass 2)
+//   pass 2 (APPLY) h[r, :] = (sum_c W[r, c] v_c) / n_r * silu(o_r)
+//                  one work item = 128 query rows x 256 output columns, contraction over the causal
+//                  extent of the row tile; n_r = max(|b_r|, exp(-m_r)) + 1e-6 from pass 1's row sums
+//
+// Both passes are the same persistent warp-specialised GEMM: warp 0 = TMA producer (ring of 48 KB
+// stages: a 128 x 128-byte A box and 32 KB of B), warp 1 = MMA issuer (tcgen05.mma, M = 128, N = 256,
+// both operands from shared memory; fp32 inputs are read as tf32, 16-bit inputs as they are),
+// warps 2-5 = epilogue (one TMEM lane = one row per thread; per-warp staging and TMA stores).
+// TMEM holds two 256-column accumulators, so the epilogue of one item overlaps the contraction of the
+// next.  Work items come from a global counter, heaviest first, published to the roles through an
+// eight-deep shared-memory ring.  Every wait is bounded (see ptx_sm100.cuh); a wait that runs out ends
+// the kernel with a code in the status word.
+#include <atomic>
+#include <type_traits>
+
+#include "mlstm_common.cuh"
+#include "ptx_sm100.cuh"
+#include "tc_host.cuh"
+
+namespace mlstm {
+namespace {
+
+using namespace ptx;
+
+constexpr int GATE = 0, APPLY = 1;
+constexpr int NTHREADS_G = 192;
+constexpr int TN = 256;                       // columns of a work item
+constexpr int A_BYTES = 128 * 128;            // 128 rows x 128 bytes
+constexpr int B_BYTES = 256 * 128;            // pass 1: 256 key rows x 128 bytes; pass 2: TN columns x one chunk of rows
+constexpr int STAGE_BYTES_G = A_BYTES + B_BYTES;
+constexpr int NSTAGE = 4;
+constexpr int OUT_WARP_BYTES = 2 * 2048;      // per epilogue warp: two staging buffers of 32 rows x 64 bytes
+constexpr int NEPI = 4;                       // epilogue warps
+constexpr int ITEM_RING = 8;
+constexpr int NBAR_G = 2 * NSTAGE + 4 + ITEM_RING;
+constexpr int SMEM_BYTES_G = NSTAGE * STAGE_BYTES_G + NEPI * OUT_WARP_BYTES + NBAR_G * 8 + 128;
+constexpr long long WAIT_LIMIT_G = 4000000000LL;   // cycles (about two seconds)
+constexpr float MAX_ROW_EXP2_G = 60.0f;
+constexpr int SLEEP_NS_G = 64;
+static_assert(SMEM_BYTES_G <= 232448, "exceeds the shared memory of a CTA");
+
+struct GemmParams {
+    int S, Spad, BH, D;
+    int NT;        // 128-row tiles per slice
+    int NKT;       // 256-column key tiles per slice
+    int NVS;       // 256-column output slices
+    int per_head;  // pass 1: work items per slice
+    int items;     // work items of the launch
+    // pass 1: gate vectors (see mlstm_common.cuh / gates.cu)
+    const float* row_rel;
+    const double* row_ref;
+    const float* col_rel;
+    const float* col_w;
+    const double* col_ref;
+    float er_add;
+    float* bpart;       // [BH, NKT, Spad] partial row sums, one per key tile
+    // pass 2
+    const float* m;     // [BH, S]
+    const void* ogate;  // [BH, S, D] or nullptr
+    int* status;
+    int* counter;       // work-item counter of this launch (zeroed by the launcher)
+};
+
+__device__ __forceinline__ uint32_t to_tf32_rn(float x) {
+    uint32_t y;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(y) : "f"(x));
+    return y;
+}
+
+// at most `N` of this thread's bulk groups are still reading their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+template <int PHASE, int ABFMT>
+__global__ void __launch_bounds__(NTHREADS_G, 1)
+mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmO, const GemmParams p) {
+    constexpr bool TF32 = ABFMT == 2;
+    constexpr int ES = TF32 ? 4 : 2;
+    constexpr int KC = 128 / ES;                 // contraction elements per stage (one 128-byte row)
+    constexpr int KSTEP = 32 / ES;               // contraction elements per MMA
+    using InT = typename std::conditional<ABFMT == 2, float,
+                                          typename std::conditional<ABFMT == 1, __nv_bfloat16, __half>::type>::type;
+    // pass 1 writes W in the input type, pass 2 writes h in fp32
+    constexpr int OUT_ES = PHASE == GATE ? ES : 4;
+    constexpr int NSUB = OUT_ES == 4 ? 2 : 1;    // TMA stores of 64 bytes per row for a 32-column chunk
+    // pass 2: B boxes are KC rows x 128 bytes, one per 128-byte column group of the item's 256 columns
+    constexpr int B2_BOX = KC * 128;
+    constexpr int B2_GROUPS = TN * ES / 128;
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
+    uint8_t* sOut = smem + NSTAGE * STAGE_BYTES_G;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + NEPI * OUT_WARP_BYTES);
+    uint64_t* bar_full = bars;
+    uint64_t* bar_empty = bars + NSTAGE;
+    uint64_t* bar_accfull = bars + 2 * NSTAGE;        // [2]
+    uint64_t* bar_accempty = bar_accfull + 2;         // [2]
+    uint64_t* bar_item = bar_accempty + 2;            // [ITEM_RING]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBAR_G);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* item_ids = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [ITEM_RING]
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const bool misaligned = (smem_u32(smem) & 1023u) != 0;   // the swizzled tiles need a 1024-byte aligned base
+
+    struct Item {
+        int bh, qt, ct, nchunks;   // ct: key tile (pass 1) or output slice (pass 2)
+    };
+    auto decode = [&](int id) {
+        Item it;
+        if (PHASE == GATE) {
+            it.bh = id / p.per_head;
+            int idx = id - it.bh * p.per_head;
+            int qt = 0;
+            while (idx >= qt / 2 + 1) {   // row tile qt has qt/2 + 1 key tiles on or below the diagonal
+                idx -= qt / 2 + 1;
+                qt++;
+            }
+            it.qt = qt;
+            it.ct = idx;
+            it.nchunks = p.D / KC;
+        } else {
+            const int per_w = p.BH * p.NVS;
+            const int w = id / per_w;
+            const int rem = id - w * per_w;
+            it.qt = p.NT - 1 - w;            // longest contractions first
+            it.bh = rem / p.NVS;
+            it.ct = rem - it.bh * p.NVS;
+            it.nchunks = (it.qt + 1) * TILE / KC;
+        }
+        return it;
+    };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSTAGE; s++) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_empty[s], 1);
+        }
+        for (int k = 0; k < 2; k++) {
+            mbar_init(&bar_accfull[k], 1);
+            mbar_init(&bar_accempty[k], NEPI);
+        }
+        for (int k = 0; k < ITEM_RING; k++) mbar_init(&bar_item[k], 1);
+        *abort_flag = misaligned ? 1 : 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0 && !misaligned) {
+            prefetch_tmap(&tmA);
+            prefetch_tmap(&tmB);
+            int seq = 0;   // stages filled so far
+            bool ok = true;
+            for (int n = 0; ok; n++) {
+                int id = atomicAdd(p.counter, 1);
+                if (id >= p.items) id = -1;
+                item_ids[n % ITEM_RING] = id;
+                mbar_arrive(&bar_item[n % ITEM_RING]);   // release: the id is visible to whoever passes the wait
+                if (id < 0) break;
+                const Item it = decode(id);
+                for (int c = 0; c < it.nchunks && ok; c++, seq++) {
+                    const int s = seq % NSTAGE;
+                    if (seq >= NSTAGE) {
+                        ok = mbar_wait<SLEEP_NS_G>(&bar_empty[s], ((seq / NSTAGE) & 1) ^ 1, abort_flag, WAIT_LIMIT_G);
+                        if (!ok) break;
+                    }
+                    uint8_t* sa = smem + s * STAGE_BYTES_G;
+                    uint8_t* sb = sa + A_BYTES;
+                    mbar_expect_tx(&bar_full[s], STAGE_BYTES_G);
+                    // A: rows of the query tile, one 128-byte chunk of the contraction (pass 1: of the head
+                    // dimension of Q; pass 2: of the key positions of W)
+                    tma_load_3d(sa, &tmA, &bar_full[s], c * KC, it.qt * TILE, it.bh);
+                    if (PHASE == GATE) {
+                        tma_load_3d(sb, &tmB, &bar_full[s], c * KC, it.ct * TN, it.bh);      // 256 key rows, same chunk
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < B2_GROUPS; g++)                                   // KC value rows x 256 columns
+                            tma_load_3d(sb + g * B2_BOX, &tmB, &bar_full[s], it.ct * TN + g * KC, c * KC, it.bh);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        // the whole warp runs the loop, one elected lane issues (tcgen05.mma wants warp-uniform operands)
+        const bool issuer = elect_one();
+        auto uni = [](int x) { return __shfl_sync(0xffffffffu, x, 0); };
+        auto wait_u = [&](uint64_t* bar, uint32_t parity) { return mbar_wait_warp(bar, parity, abort_flag, WAIT_LIMIT_G); };
+        constexpr uint32_t idesc = make_idesc(ABFMT, 128, TN, 0, PHASE == GATE ? 0 : 1);
+        const uint32_t smem_u = static_cast<uint32_t>(uni(static_cast<int>(smem_u32(smem))));
+        const uint32_t tmem_u = static_cast<uint32_t>(uni(static_cast<int>(tmem_base)));
+        const uint64_t adesc0 = smem_desc_sw128(smem_u, 16, 1024);                      // K-major, 128-byte rows
+        const uint64_t bdesc0 = PHASE == GATE ? smem_desc_sw128(smem_u + A_BYTES, 16, 1024)           // K-major, 256 rows
+                                : (TF32 ? smem_desc_sw128(smem_u + A_BYTES, B2_BOX, 512, 1)          // MN-major, 32-bit
+                                        : smem_desc_sw128(smem_u + A_BYTES, B2_BOX, 1024, 2));        // MN-major, 16-bit
+        constexpr int B_KSTEP_BYTES = PHASE == GATE ? 32 : KSTEP * 128;   // advance of B per MMA
+        int seq = 0;
+        bool ok = __all_sync(0xffffffffu, *abort_flag ? 0 : 1) != 0;
+        for (int n = 0; ok; n++) {
+            ok = wait_u(&bar_item[n % ITEM_RING], (n / ITEM_RING) & 1);
+            if (!ok) break;
+            const int id = uni(item_ids[n % ITEM_RING]);
+            if (id < 0) break;
+            const Item it = decode(id);
+            const int buf = n & 1;
+            if (n >= 2) {   // the epilogue of the item before last has drained this accumulator
+                ok = wait_u(&bar_accempty[buf], ((n >> 1) & 1) ^ 1);
+                if (!ok) break;
+                tc_fence_after();
+            }
+            const uint32_t acc = tmem_u + buf * TN;
+            for (int c = 0; c < it.nchunks && ok; c++, seq++) {
+                const int s = seq % NSTAGE;
+                ok = wait_u(&bar_full[s], (seq / NSTAGE) & 1);
+                if (!ok) break;
+                if (issuer) {
+                    const uint64_t ad = smem_desc_advance(adesc0, s * STAGE_BYTES_G);
+                    const uint64_t bd = smem_desc_advance(bdesc0, s * STAGE_BYTES_G);
+#pragma unroll
+                    for (int kk = 0; kk < KC / KSTEP; kk++)
+                        mma_ss<TF32>(acc, smem_desc_advance(ad, kk * 32), smem_desc_advance(bd, kk * B_KSTEP_BYTES), idesc,
+                                     (c > 0 || kk > 0) ? 1u : 0u);
+                    tc_commit(&bar_empty[s]);
+                    if (c == it.nchunks - 1) tc_commit(&bar_accfull[buf]);
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps
+        const int r = (warp & 3) * 32 + lane;          // TMEM lane == row inside the tile (lane quarter = warp % 4)
+        const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        uint8_t* stage = sOut + (warp - 2) * OUT_WARP_BYTES;
+        if (lane == 0) prefetch_tmap(&tmO);
+        int nstore = 0;   // stores issued by this warp: alternates its two staging buffers
+        bool ok = __all_sync(0xffffffffu, *abort_flag ? 0 : 1) != 0;
+        // 32 rows x 64 bytes of `vals` (16 fp32 or 32 16-bit values per row, already converted) to global memory
+        auto store64 = [&](const uint4 (&v)[4], int x, int y, int z) {
+            uint8_t* buf = stage + (nstore & 1) * 2048;
+            if (lane == 0) bulk_wait_read<1>();    // the store before last has read this buffer
+            __syncwarp();
+            uint4* srow = reinterpret_cast<uint4*>(buf + lane * 64);
+            const int sw = (lane >> 1) & 3;        // 64-byte swizzle of the store's tensor map: no bank conflicts
+#pragma unroll
+            for (int j4 = 0; j4 < 4; j4++) srow[j4 ^ sw] = v[j4];
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_3d(&tmO, buf, x, y, z);
+                bulk_commit();
+            }
+            nstore++;
+        };
+        for (int n = 0; ok; n++) {
+            ok = mbar_wait_warp<SLEEP_NS_G>(&bar_item[n % ITEM_RING], (n / ITEM_RING) & 1, abort_flag, WAIT_LIMIT_G);
+            if (!ok) break;
+            const int id = __shfl_sync(0xffffffffu, item_ids[n % ITEM_RING], 0);
+            if (id < 0) break;
+            const Item it = decode(id);
+            const int buf = n & 1;
+            const int grow = it.qt * TILE + r;
+            const bool row_ok = grow < p.S;
+            const size_t vec_base = static_cast<size_t>(it.bh) * p.Spad;
+            const size_t ref_base = static_cast<size_t>(it.bh) * (p.Spad / REF_BLOCK);
+            // row terms, requested before the accumulator wait
+            double er_d = 0.0;
+            float inv_n = 1.0f;
+            if (PHASE == GATE) {
+                er_d = static_cast<double>(p.row_rel[vec_base + grow]) + p.row_ref[ref_base + grow / REF_BLOCK] +
+                       static_cast<double>(p.er_add);
+            } else {
+                float bsum = 0.0f;
+                for (int kt = 0; kt <= it.qt / 2; kt++)
+                    bsum += p.bpart[(static_cast<size_t>(it.bh) * p.NKT + kt) * p.Spad + grow];
+                const float mrow = row_ok ? p.m[static_cast<size_t>(it.bh) * p.S + grow] : 0.0f;
+                inv_n = 1.0f / (fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f);
+            }
+            ok = mbar_wait_warp<SLEEP_NS_G>(&bar_accfull[buf], (n >> 1) & 1, abort_flag, WAIT_LIMIT_G);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + buf * TN + lane_bits;
+            float rowsum = 0.0f;
+            // pass 1: chunks right of the row tile's diagonal tile are never read by pass 2: not computed, not stored
+            const int nch = PHASE == GATE ? min(TN / 32, ((it.qt + 1) * TILE - it.ct * TN) / 32) : TN / 32;
+#pragma unroll 1
+            for (int ch = 0; ch < nch; ch++) {
+                const int c0 = it.ct * TN + ch * 32;           // first column of the chunk (pass 1: key position)
+                float cv[32];
+                bool diag = false;
+                float er = 0.0f;
+                if (PHASE == GATE) {
+                    diag = (c0 / TILE) == it.qt;
+                    const float4* p4 = reinterpret_cast<const float4*>((diag ? p.col_rel : p.col_w) + vec_base + c0);
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; q4++) {
+                        const float4 e4 = __ldg(p4 + q4);
+                        cv[q4 * 4 + 0] = e4.x; cv[q4 * 4 + 1] = e4.y; cv[q4 * 4 + 2] = e4.z; cv[q4 * 4 + 3] = e4.w;
+                    }
+                    er = static_cast<float>(er_d + p.col_ref[ref_base + c0 / REF_BLOCK]);
+                } else if (p.ogate && row_ok) {
+                    const InT* orow = reinterpret_cast<const InT*>(p.ogate) +
+                                      (static_cast<size_t>(it.bh) * p.S + grow) * p.D + c0;
+                    constexpr int VEC = 16 / ES;
+#pragma unroll
+                    for (int jv = 0; jv < 32 / VEC; jv++) {
+                        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(orow) + jv);
+                        const InT* ev = reinterpret_cast<const InT*>(&raw);
+#pragma unroll
+                        for (int j = 0; j < VEC; j++) cv[jv * VEC + j] = silu_f(to_f32<InT>(ev[j]));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) cv[j] = 1.0f;
+                }
+                uint32_t tv[32];
+                tmem_ld32(acc + ch * 32, tv);
+                tc_wait_ld();
+                if (ch == nch - 1) {
+                    // this warp's share of the accumulator is in registers: the item after next may overwrite it
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar_accempty[buf]);
+                }
+                if (PHASE == GATE) {
+                    if (diag) {
+                        const int rel0 = c0 - it.qt * TILE;    // column index inside the diagonal tile
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            float wj = __uint_as_float(tv[j]) * fast_exp2(cv[j] + er);
+                            if (rel0 + j > r) wj = 0.0f;
+                            rowsum += wj;
+                            cv[j] = wj;
+                        }
+                    } else {
+                        // off the diagonal tile exp2(ec + er) = exp2(ec) exp2(er) with both factors bounded; a
+                        // block of pure padding has no reference of its own, hence the clamp (its factors are 0)
+                        const float u = fast_exp2(fminf(er, MAX_ROW_EXP2_G));
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const float wj = __uint_as_float(tv[j]) * u * cv[j];
+                            rowsum += wj;
+                            cv[j] = wj;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) cv[j] *= __uint_as_float(tv[j]) * inv_n;
+                }
+                const int y = it.qt * TILE + (warp & 3) * 32;
+                if constexpr (OUT_ES == 4) {
+#pragma unroll
+                    for (int sub = 0; sub < NSUB; sub++) {
+                        uint4 v[4];
+#pragma unroll
+                        for (int j4 = 0; j4 < 4; j4++) {
+                            const float* s4 = &cv[sub * 16 + j4 * 4];
+                            if (PHASE == GATE)
+                                v[j4] = make_uint4(to_tf32_rn(s4[0]), to_tf32_rn(s4[1]), to_tf32_rn(s4[2]), to_tf32_rn(s4[3]));
+                            else
+                                v[j4] = make_uint4(__float_as_uint(s4[0]), __float_as_uint(s4[1]), __float_as_uint(s4[2]),
+                                                   __float_as_uint(s4[3]));
+                        }
+                        store64(v, c0 + sub * 16, y, it.bh);
+                    }
+                } else {
+                    uint4 v[4];
+#pragma unroll
+                    for (int j4 = 0; j4 < 4; j4++) {
+                        uint32_t o32[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            if constexpr (ABFMT == 1) {
+                                __nv_bfloat162 v2 = __floats2bfloat162_rn(cv[j4 * 8 + 2 * j], cv[j4 * 8 + 2 * j + 1]);
+                                o32[j] = *reinterpret_cast<uint32_t*>(&v2);
+                            } else {
+                                __half2 v2 = __floats2half2_rn(cv[j4 * 8 + 2 * j], cv[j4 * 8 + 2 * j + 1]);
+                                o32[j] = *reinterpret_cast<uint32_t*>(&v2);
+                            }
+                        }
+                        v[j4] = make_uint4(o32[0], o32[1], o32[2], o32[3]);
+                    }
+                    store64(v, c0, y, it.bh);
+                }
+            }
+            if (PHASE == GATE) p.bpart[(static_cast<size_t>(it.bh) * p.NKT + it.ct) * p.Spad + grow] = rowsum;
+        }
+        if (lane == 0) bulk_wait_all();   // the last stores have left shared memory before the CTA goes away
+        tc_fence_before();
+    }
+
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.status, misaligned ? 2000 : 5000 + PHASE);
+        // give copies and MMAs that are still in flight time to land before the CTA's memory goes away
+        for (int k = 0; k < 64; k++) __nanosleep(16000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+template <int PHASE, int ABFMT>
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& p, cudaStream_t st) {
+    auto kern = mlstm_scan_gemm<PHASE, ABFMT>;
+    cudaError_t ce;
+    {
+        static std::atomic<bool> opted[64];
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MLSTM_E_CUDA;
+        if (!opted[dev].load(std::memory_order_acquire)) {
+            ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_G);
+            if (ce != cudaSuccess) {
+                cudaGetLastError();
+                return note_cuda_error(ce, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
+            }
+            opted[dev].store(true, std::memory_order_release);
+        }
+    }
+    const int sms = tc_sm_count();
+    if (sms <= 0) return MLSTM_E_CUDA;
+    ce = cudaMemsetAsync(p.counter, 0, sizeof(int), st);
+    if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
+    const unsigned grid = static_cast<unsigned>(p.items < sms ? p.items : sms);   // persistent: one CTA per SM
+    kern<<<grid, NTHREADS_G, SMEM_BYTES_G, st>>>(ma, mb, mo, p);
+    ce = cudaGetLastError();
+    return ce == cudaSuccess ? MLSTM_OK : note_cuda_error(ce, "launch of mlstm_scan_gemm");
+}
+
+template <int ABFMT>
+int run_group(const void* q, const void* k, const void* v, const void* o, float* h, void* W, const ScanGemmArgs& a, int bh0,
+              int nbh, int dtype, cudaStream_t st) {
+    const size_t es = dtype == MLSTM_DT_F32 ? 4 : 2;
+    const size_t slice = static_cast<size_t>(a.S) * a.D;
+    const uint8_t* qg = static_cast<const uint8_t*>(q) + bh0 * slice * es;
+    const uint8_t* kg = static_cast<const uint8_t*>(k) + bh0 * slice * es;
+    const uint8_t* vg = static_cast<const uint8_t*>(v) + bh0 * slice * es;
+    const uint8_t* og = o ? static_cast<const uint8_t*>(o) + bh0 * slice * es : nullptr;
+    float* hg = h + bh0 * slice;
+    GemmParams p{};
+    p.S = a.S; p.Spad = a.Spad; p.BH = nbh; p.D = a.D;
+    p.NT = a.Spad / TILE;
+    p.NKT = (a.Spad + TN - 1) / TN;
+    p.NVS = a.D / TN;
+    p.per_head = 0;
+    for (int qt = 0; qt < p.NT; qt++) p.per_head += qt / 2 + 1;
+    const size_t vec0 = static_cast<size_t>(bh0) * a.Spad, ref0 = static_cast<size_t>(bh0) * (a.Spad / REF_BLOCK);
+    p.row_rel = a.gAn + vec0; p.row_ref = a.An_ref + ref0;
+    p.col_rel = a.ga + vec0; p.col_w = a.gaw + vec0; p.col_ref = a.a_ref + ref0;
+    p.er_add = -0.5f * log2f(static_cast<float>(a.D));
+    p.bpart = a.bpart;   // per group: reused
+    p.m = a.m + static_cast<size_t>(bh0) * a.S;
+    p.ogate = og;
+    p.status = a.status;
+    int rc;
+    CUtensorMap ma, mb, mo;
+    // ---- pass 1: W = gate(Q K^T)
+    if ((rc = tc_make_map(&ma, qg, nbh, a.S, a.D, dtype, false, 128)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map(&mb, kg, nbh, a.S, a.D, dtype, false, 256)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map_out(&mo, W, nbh, a.Spad, a.Spad, dtype, 32)) != MLSTM_OK) return rc;
+    p.items = p.per_head * nbh;
+    p.counter = a.counters;
+    if ((rc = launch_gemm<GATE, ABFMT>(ma, mb, mo, p, st)) != MLSTM_OK) return rc;
+    // ---- pass 2: h = (W V) / n * silu(o)
+    constexpr int KC = ABFMT == 2 ? 32 : 64;
+    if ((rc = tc_make_map(&ma, W, nbh, a.Spad, a.Spad, dtype, false, 128)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map(&mb, vg, nbh, a.S, a.D, dtype, ABFMT == 2, KC)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map_out(&mo, hg, nbh, a.S, a.D, MLSTM_DT_F32, 32)) != MLSTM_OK) return rc;
+    p.items = p.NT * nbh * p.NVS;
+    p.counter = a.counters + 1;
+    return launch_gemm<APPLY, ABFMT>(ma, mb, mo, p, st);
+}
+
+}  // namespace
+
+bool scan_gemm_supported(int S, int D, int in_dtype) {
+    return S >= 1 && D > 256 && D % TN == 0 && D <= 4096 &&
+           (in_dtype == MLSTM_DT_F16 || in_dtype == MLSTM_DT_BF16 || in_dtype == MLSTM_DT_F32);
+}
+
+// Slices whose gated matrices fit the budget at once (at least one): the passes run group by group.
+int scan_gemm_group(int BH, int S, int dtype) {
+    const size_t Spad = round_up(S, TILE);
+    const size_t per_head = Spad * Spad * (dtype == MLSTM_DT_F32 ? 4 : 2);
+    const size_t budget = static_cast<size_t>(512) << 20;
+    size_t g = budget / per_head;
+    if (g < 1) g = 1;
+    return static_cast<int>(g < static_cast<size_t>(BH) ? g : BH);
+}
+
+size_t scan_gemm_w_bytes(int BH, int S, int dtype) {
+    const size_t Spad = round_up(S, TILE);
+    return static_cast<size_t>(scan_gemm_group(BH, S, dtype)) * Spad * Spad * (dtype == MLSTM_DT_F32 ? 4 : 2);
+}
+
+size_t scan_gemm_bpart_bytes(int BH, int S, int dtype) {
+    const size_t Spad = round_up(S, TILE);
+    return static_cast<size_t>(scan_gemm_group(BH, S, dtype)) * ((Spad + TN - 1) / TN) * Spad * sizeof(float);
+}
+
+int launch_scan_gemm(const void* q, const void* k, const void* v, const void* o, float* h, void* W, const ScanGemmArgs& a,
+                     int dtype, cudaStream_t st) {
+    if (!scan_gemm_supported(a.S, a.D, dtype)) return MLSTM_E_UNSUPPORTED;
+    const int group = scan_gemm_group(a.BH, a.S, dtype);
+    for (int bh0 = 0; bh0 < a.BH; bh0 += group) {
+        const int nbh = a.BH - bh0 < group ? a.BH - bh0 : group;
+        int rc;
+        switch (dtype) {
+            case MLSTM_DT_F32: rc = run_group<2>(q, k, v, o, h, W, a, bh0, nbh, dtype, st); break;
+            case MLSTM_DT_BF16: rc = run_group<1>(q, k, v, o, h, W, a, bh0, nbh, dtype, st); break;
+            case MLSTM_DT_F16: rc = run_group<0>(q, k, v, o, h, W, a, bh0, nbh, dtype, st); break;
+            default: return MLSTM_E_ARG;
+        }
+        if (rc != MLSTM_OK) return rc;
+    }
+    return MLSTM_OK;
+}
+
+}  // namespace mlstm

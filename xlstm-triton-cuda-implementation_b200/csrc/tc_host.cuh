@@ -15,7 +15,7 @@ int tc_make_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int 
 // is 512-byte aligned).
 int tc_make_map_out(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, int box_rows);
 int tc_sm_count();    // SMs of the current device (cached), -1 on error
-int tc_slice_set();   // slices interleaved in the work-item order (MLSTM_SLICE_SET overrides the default)
+int tc_slice_set();   // slices interleaved in the work-item order
 
 // CTA-pair form of the tensor-core pass (mm_tc_pair.cu): head dimension 256, 16-bit inputs
 bool tc_pair_supported(int S, int D, int in_dtype);

@@ -8,25 +8,27 @@ of its scan path (mlstm_scan.py:143-195) with the carry algebra of its scan oper
 (mlstm_scan.py:15-26).  Inputs are 16-bit, D = 128; h is float32 unless ``h_dtype`` says otherwise.
 
 Sequence-parallel form: rank r of the group holds the r-th contiguous segment of every sequence
-(all heads).  Two small all-gathers connect the ranks and there is no other communication:
-  1. per-slice gate summaries {F_end, A_end} (16 bytes per slice) -> every rank's carry-in {F_in, A_in};
-  2. per-slice segment states (S [D,D], z [D], A_end, packed into one buffer; 0.53 MB per rank at 8
-     heads) -> every rank's inbound state, folded locally from the lower ranks' states.
-The folds are plain tensor arithmetic (``fold_gate_summaries``, ``fold_states``) and do not care where
-the tensors live, which is how the CPU tests drive them over gloo.
+(all heads).  ONE all-gather connects the ranks and there is no other communication: every rank first
+does all the work that needs no other rank (gates, per-block states, and the state its segment adds,
+stabilised by its own prefix maximum with F counted from zero) and packs, per slice, one record
+``S [D*D] | z [D] | {F_end, A_end}`` (0.53 MB per rank at 8 heads).  After the all-gather one kernel
+folds the lower ranks' records into the inbound state and carry of this rank (``fold_records`` states
+the same arithmetic in torch, for the CPU tests), and the output pass applies it.
+``fold_gate_summaries`` / ``fold_states`` are the same combine on separate tensors, for callers that
+move summaries and states themselves (state continuation across calls).
 """
 import torch
 
 from . import _lib
 
 __all__ = ["mlstm_chunkwise", "mlstm_chunkwise_sequence_parallel", "fold_gate_summaries", "fold_states",
-           "ChunkSegment"]
+           "fold_records", "ChunkSegment"]
 
 
 class ChunkSegment:
     """One segment's pass through the four C-ABI stages, holding its workspace."""
 
-    def __init__(self, q, k, v, f, i, chunk_size=256, shared_workspace=False):
+    def __init__(self, q, k, v, f, i, chunk_size=256, shared_workspace=False, o=None):
         if q.dim() != 4 or k.shape != q.shape or v.shape != q.shape:
             raise ValueError("q, k, v must share the shape [B, NH, S, D]")
         if f.shape != q.shape[:3] or i.shape != q.shape[:3]:
@@ -34,7 +36,11 @@ class ChunkSegment:
         if not (k.dtype == v.dtype == f.dtype == i.dtype == q.dtype):
             raise TypeError("q, k, v, f, i must share one element type")
         self.dev = _lib.require_cuda(q, k, v, f, i)
-        self.q, self.k, self.v, self.f, self.i = q, k, v, f, i
+        if o is not None:
+            if o.shape != q.shape or o.dtype != q.dtype:
+                raise ValueError("o must match q in shape and element type")
+            _lib.require_cuda(q, o)
+        self.q, self.k, self.v, self.f, self.i, self.o = q, k, v, f, i, o
         self.B, self.NH, self.S, self.D = q.shape
         self.dt = _lib.dtype_code(q)
         self.chunk = int(chunk_size)
@@ -98,23 +104,49 @@ class ChunkSegment:
             z_out = torch.empty((self.B * self.NH, self.D), dtype=torch.float32, device=self.dev)
         ptr = lambda t: t.data_ptr() if t is not None else None
         with torch.cuda.device(self.dev):
-            rc = self.L.mlstm_chunk_apply(self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), ptr(S_in), ptr(z_in),
-                                          h.data_ptr(), _lib.dtype_code(h), ptr(S_out), ptr(z_out), self.ws.data_ptr(),
-                                          self.ws.numel(), *self.dims, self._stream())
+            rc = self.L.mlstm_chunk_apply(self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), ptr(self.o), ptr(S_in),
+                                          ptr(z_in), h.data_ptr(), _lib.dtype_code(h), ptr(S_out), ptr(z_out),
+                                          self.ws.data_ptr(), self.ws.numel(), *self.dims, self._stream())
         _lib.check(rc, "mlstm_chunk_apply")
         _lib.maybe_read_status(self.ws, self.dev, "mlstm_chunk_apply")
         return (h, (S_out, z_out)) if return_state else h
 
+    # ---- sequence-parallel stages (one exchange between them)
+    def sp_local(self):
+        """Everything that needs no other rank; returns this segment's record [B*NH, D*D + D + 4] float32
+        (S | z | {F_end, A_end} as two float64 in four float32 words)."""
+        rec = torch.empty((self.B * self.NH, self.L.mlstm_chunk_sp_record_floats(self.D)), dtype=torch.float32,
+                          device=self.dev)
+        with torch.cuda.device(self.dev):
+            rc = self.L.mlstm_chunk_sp_local(self.k.data_ptr(), self.v.data_ptr(), self.f.data_ptr(), self.i.data_ptr(),
+                                             rec.data_ptr(), self.ws.data_ptr(), self.ws.numel(), *self.dims, self._stream())
+        _lib.check(rc, "mlstm_chunk_sp_local")
+        return rec
 
-def mlstm_chunkwise(q, k, v, f, i, chunk_size=256, h_dtype=torch.float32, initial=None, return_state=False):
-    """Chunkwise forward on one GPU.
+    def sp_apply(self, gathered, rank, h_dtype=torch.float32):
+        """h of the segment from the gathered records [G, B*NH, record] of all ranks (rank order = sequence order)."""
+        gathered = gathered.contiguous()
+        world = gathered.shape[0]
+        h = torch.empty((self.B, self.NH, self.S, self.D), dtype=h_dtype, device=self.dev)
+        with torch.cuda.device(self.dev):
+            rc = self.L.mlstm_chunk_sp_apply(self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(),
+                                             self.o.data_ptr() if self.o is not None else None, gathered.data_ptr(), world,
+                                             int(rank), h.data_ptr(), _lib.dtype_code(h), None, self.ws.data_ptr(),
+                                             self.ws.numel(), *self.dims, self._stream())
+        _lib.check(rc, "mlstm_chunk_sp_apply")
+        _lib.maybe_read_status(self.ws, self.dev, "mlstm_chunk_sp_apply")
+        return h
+
+
+def mlstm_chunkwise(q, k, v, f, i, chunk_size=256, h_dtype=torch.float32, initial=None, return_state=False, o=None):
+    """Chunkwise forward on one GPU (times silu(o) when the output-gate pre-activation ``o`` is given).
 
     ``initial`` = (S, z, F, A) continues an earlier segment: S [B*NH, D, D] and z [B*NH, D] float32
     stabilised by A, and F, A float64 [B*NH] (the log-forget total and the prefix maximum of a = i - F
     at the end of that segment).  With ``return_state`` the same tuple for the end of this call is
     returned beside h.
     """
-    seg = ChunkSegment(q, k, v, f, i, chunk_size, shared_workspace=True)
+    seg = ChunkSegment(q, k, v, f, i, chunk_size, shared_workspace=True, o=o)
     carry = None
     state_in = None
     if initial is not None:
@@ -160,6 +192,28 @@ def fold_states(S_all, z_all, A_end_all, rank):
     return S, z
 
 
+def fold_records(gathered, rank):
+    """The arithmetic of the fold kernel in torch: gathered [G, BH, D*D + D + 4] float32 records (see
+    ``ChunkSegment.sp_local``) -> (S_in [BH, D, D], z_in [BH, D], F_in [BH], A_in [BH]) of segment ``rank``.
+    Segment g's state is stabilised by its own prefix maximum A_g with F counted from zero, i.e. by
+    A_g - F_in(g) in global terms; A_in is the maximum of those over g < rank."""
+    G, BH, R = gathered.shape
+    D = int(round((-1 + (1 + 4 * (R - 4)) ** 0.5) / 2))
+    tail = gathered[:, :, D * D + D:].contiguous().view(torch.float64).reshape(G, BH, 2)
+    F_loc, A_loc = tail[..., 0], tail[..., 1]
+    F_before = torch.cumsum(F_loc, 0) - F_loc                   # [G, BH] log-forget total before each segment
+    A_hat = A_loc - F_before
+    S_in = torch.zeros((BH, D, D), dtype=torch.float32, device=gathered.device)
+    z_in = torch.zeros((BH, D), dtype=torch.float32, device=gathered.device)
+    A_in = torch.full((BH,), -float("inf"), dtype=torch.float64, device=gathered.device)
+    if rank > 0:
+        A_in = A_hat[:rank].max(0).values
+        w = torch.exp(A_hat[:rank] - A_in).float()              # [rank, BH], <= 1
+        S_in = (w[:, :, None] * gathered[:rank, :, :D * D]).sum(0).reshape(BH, D, D)
+        z_in = (w[:, :, None] * gathered[:rank, :, D * D:D * D + D]).sum(0)
+    return S_in, z_in, F_before[rank], A_in
+
+
 def _all_gather(t, group):
     import torch.distributed as dist
     t = t.contiguous()
@@ -170,28 +224,18 @@ def _all_gather(t, group):
 
 
 def sequence_parallel_forward(segment, group=None, h_dtype=torch.float32):
-    """The sequence-parallel protocol over any object with the ChunkSegment interface: two all-gathers
-    (gate summaries; then every segment's state with its A_end packed into one buffer)."""
+    """The sequence-parallel protocol over any object with the ``sp_local`` / ``sp_apply`` stages of
+    ChunkSegment: local work, one all-gather of the per-slice records, fold + output."""
     import torch.distributed as dist
     rank = dist.get_rank(group)
-    local = segment.gate_summary()                                   # [BH, 2]
-    carry_all = fold_gate_summaries(_all_gather(local, group))       # [G, BH, 2]
-    summary = segment.prepare(carry_all[rank] if rank > 0 else None)  # [BH, 2] incl. carry
-    S_loc, z_loc = segment.local_state()
-    BH, D = z_loc.shape
-    # one buffer per rank: S [D*D] | z [D] | A_end (float64 carried as two float32 words)
-    a_words = summary[:, 1].contiguous().view(torch.float32).reshape(BH, 2)
-    packed = torch.cat([S_loc.reshape(BH, D * D).float(), z_loc.float(), a_words], dim=1)
-    allp = _all_gather(packed, group)                                # [G, BH, D*D + D + 2]
-    S_all = allp[:, :, :D * D].reshape(-1, BH, D, D)
-    z_all = allp[:, :, D * D:D * D + D]
-    A_end_all = allp[:, :, D * D + D:].contiguous().view(torch.float64).reshape(-1, BH)
-    state_in = fold_states(S_all, z_all, A_end_all, rank)
-    return segment.apply(state_in, h_dtype=h_dtype)
+    record = segment.sp_local()                                      # [BH, D*D + D + 4]
+    gathered = _all_gather(record, group)                            # [G, BH, D*D + D + 4]
+    return segment.sp_apply(gathered, rank, h_dtype=h_dtype)
 
 
-def mlstm_chunkwise_sequence_parallel(q, k, v, f, i, chunk_size=256, group=None, h_dtype=torch.float32):
+def mlstm_chunkwise_sequence_parallel(q, k, v, f, i, chunk_size=256, group=None, h_dtype=torch.float32, o=None):
     """Every rank passes its contiguous segment [B, NH, S/G, D] (rank order = sequence order) and gets
-    the outputs of that segment.  Needs an initialised torch.distributed process group (NCCL)."""
-    return sequence_parallel_forward(ChunkSegment(q, k, v, f, i, chunk_size, shared_workspace=True), group=group,
+    the outputs of that segment (times silu(o) when the output-gate pre-activation ``o`` is given).
+    Needs an initialised torch.distributed process group (NCCL)."""
+    return sequence_parallel_forward(ChunkSegment(q, k, v, f, i, chunk_size, shared_workspace=True, o=o), group=group,
                                      h_dtype=h_dtype)

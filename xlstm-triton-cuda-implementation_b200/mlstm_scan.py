@@ -7,21 +7,79 @@ Same name, arguments and result as the reference's ``mlstm_scan`` (mlstm_scan.py
 q, k, v, o: [B, NH, S, D]; f, i: [B, NH, S]; CUDA, contiguous; h is float32 (mlstm_scan.py:303).
 The block-size arguments are the reference's tiling hints: they are validated the way the
 reference's grid needs them (positive, dividing D, mlstm_scan.py:297, 309-310) and otherwise ignored.
-Forward only, like the reference (README.md:97).
+
+The library picks one of three forms by shape (``mlstm_scan_fwd`` in include/mlstm_b200.h):
+  * D above 256 (the reference demo, D = 1024): two tensor-core passes, the gated S x S matrix once
+    and then W V; the quadratic form is the cheapest there because the D x D state is larger than S x S;
+  * S much longer than D (16-bit inputs, D = 128): chunkwise, i.e. per-block (C, n) states with the
+    stabiliser known up front, an inter-block carry and the output from the carried state, which is
+    the mechanism of the reference's three scan kernels (mlstm_scan.py:74-137, 143-195, 200-278);
+  * otherwise the parallel forward with silu(o) in its epilogue.
+``initial`` / ``return_state`` expose the carried state (S [B*NH, D, D] key-major, z [B*NH, D], F, A
+[B*NH] float64; see ``mlstm_chunkwise``) and need the chunkwise form's shapes.
 
 Arithmetic: 16-bit inputs always run on the tensor cores.  float32 inputs run on them with tf32
-operands and fp32 accumulation when ``allow_tf32`` is true (the default here: max-abs-rel error about
-5e-4, inside the reference's own 1e-2 check) and D is 64, 128, 256 or a multiple of 256 up to 4096;
-``allow_tf32=False`` gives IEEE fp32 dot products on the CUDA cores (error about 1e-6, much slower).
+operands and fp32 accumulation when ``allow_tf32`` is true (the default here; measured max-abs-rel
+error about 5e-4 to 1e-3, inside the reference's own 1e-2 check) and D is 64, 128, 256 or a multiple of
+256 up to 4096; ``allow_tf32=False`` gives IEEE fp32 dot products on the CUDA cores (error about 1e-6,
+much slower).
+
+The reference's scan is forward only (README.md:97).  Here inputs that require gradients get them: the
+function computed is exactly the parallel form times silu(o), so the backward runs the parallel
+backward kernels (``mlstm_matmul_backward``) behind the output gate's own derivative; its cost is
+quadratic in S whatever form the forward took.
 """
 import torch
 
 from . import _lib
+from .mlstm_matmul import mlstm_matmul_backward, mlstm_matmul_forward
 
-__all__ = ["mlstm_scan"]
+__all__ = ["mlstm_scan", "output_gate_forward", "output_gate_backward"]
 
 
-def mlstm_scan(q, k, v, f, i, o, reduce_block_size=4, value_block_size=4, num_warps=8, allow_tf32=True, flags=0):
+def output_gate_forward(h_inner, o):
+    """h = h_inner * silu(o) (mlstm_scan.py:273-278), one elementwise kernel."""
+    dev = _lib.require_cuda(h_inner, o)
+    h = torch.empty_like(h_inner)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().mlstm_ogate_fwd(h_inner.data_ptr(), o.data_ptr(), h.data_ptr(), h_inner.numel(),
+                                        _lib.dtype_code(h_inner), _lib.dtype_code(o), _lib.stream_ptr(dev))
+    _lib.check(rc, "mlstm_ogate_fwd")
+    return h
+
+
+def output_gate_backward(dh, h_inner, o):
+    """(dh_inner, do) of h = h_inner * silu(o): dh_inner = dh silu(o), do = dh h_inner silu'(o)."""
+    dev = _lib.require_cuda(dh, h_inner, o)
+    dh_inner = torch.empty_like(h_inner)
+    do = torch.empty_like(o)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().mlstm_ogate_bwd(dh.data_ptr(), h_inner.data_ptr(), o.data_ptr(), dh_inner.data_ptr(), do.data_ptr(),
+                                        h_inner.numel(), _lib.dtype_code(h_inner), _lib.dtype_code(o), _lib.stream_ptr(dev))
+    _lib.check(rc, "mlstm_ogate_bwd")
+    return dh_inner, do
+
+
+class _ScanWithGrad(torch.autograd.Function):
+    """mLSTM(q, k, v, f, i) * silu(o) with gradients for all six inputs."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, f, i, o, flags):
+        h_inner, m, b = mlstm_matmul_forward(q, k, v, f, i, flags=flags)
+        ctx.save_for_backward(q, k, v, f, i, o, m, b, h_inner)
+        ctx.flags = flags
+        return output_gate_forward(h_inner, o)
+
+    @staticmethod
+    def backward(ctx, dh):
+        q, k, v, f, i, o, m, b, h_inner = ctx.saved_tensors
+        dh_inner, do = output_gate_backward(dh.contiguous(), h_inner, o)
+        dq, dk, dv, df, di = mlstm_matmul_backward(dh_inner, q, k, v, f, i, h_inner, m, b, flags=ctx.flags)
+        return dq, dk, dv, df, di, do, None
+
+
+def mlstm_scan(q, k, v, f, i, o, reduce_block_size=4, value_block_size=4, num_warps=8, allow_tf32=True, flags=0,
+               initial=None, return_state=False):
     if q.dim() != 4 or k.shape != q.shape or v.shape != q.shape or o.shape != q.shape:
         raise ValueError("q, k, v, o must share the shape [B, NH, S, D]")
     if f.shape != q.shape[:3] or i.shape != q.shape[:3]:
@@ -38,6 +96,11 @@ def mlstm_scan(q, k, v, f, i, o, reduce_block_size=4, value_block_size=4, num_wa
     dev = _lib.require_cuda(q, k, v, f, i, o)
     if allow_tf32:
         flags |= _lib.F_ALLOW_TF32
+    if initial is not None or return_state:
+        from .mlstm_chunkwise import mlstm_chunkwise
+        return mlstm_chunkwise(q, k, v, f, i, chunk_size=256, initial=initial, return_state=return_state, o=o)
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, f, i, o)):
+        return _ScanWithGrad.apply(q, k, v, f, i, o, flags)
     dt = _lib.dtype_code(q)
     h = torch.empty((B, NH, S, D), device=dev, dtype=torch.float32)
     L = _lib.lib()
