@@ -43,16 +43,19 @@ extern "C" {
 /* flags */
 #define MLSTM_F_FORCE_SIMT 1 /* use the CUDA-core kernels even where the tensor-core path applies */
 #define MLSTM_F_FORCE_TC 2   /* fail with MLSTM_E_UNSUPPORTED instead of using the CUDA-core path */
-#define MLSTM_F_ALLOW_TF32 4 /* fp32 inputs may use the tensor cores with tf32 operands (fp32 accumulate);
-                                without it fp32 inputs get IEEE fp32 dot products, as the reference's
-                                tl.dot(..., allow_tf32=False) (mlstm_matmul.py:19) */
+#define MLSTM_F_ALLOW_TF32 4 /* fp32 inputs may use the tensor cores with single tf32 products (fp32 accumulate,
+                                error about 5e-4).  Without it fp32 inputs keep fp32-level accuracy, as the
+                                reference's tl.dot(..., allow_tf32=False) (mlstm_matmul.py:19): for D = 64 and
+                                128 on the tensor cores with every operand split into two bf16 halves and three
+                                products per fp32 product (error about 1e-5), else IEEE fp32 on the CUDA cores */
+#define MLSTM_F_NO_SPLIT 8   /* fp32 inputs: do not use the split tensor-core form (IEEE fp32 on the CUDA cores) */
 
 const char* mlstm_status_string(int status);
 /* Text of the last CUDA failure behind an MLSTM_E_CUDA on this host thread (which call, which error). */
 const char* mlstm_last_error_detail(void);
 
 /* Whether the tcgen05 path handles this case (D in {64, 128, 256}): 1 for 16-bit inputs, 2 for fp32
- * inputs (used only with MLSTM_F_ALLOW_TF32), else 0.  The scan entry also takes D = 512 .. 4096 in
+ * inputs (single tf32 products with MLSTM_F_ALLOW_TF32; split bf16 products by default at D = 64, 128), else 0.  The scan entry also takes D = 512 .. 4096 in
  * multiples of 256 on the tensor cores (two-pass forward). */
 int mlstm_tc_supported(int S, int D, int dtype);
 

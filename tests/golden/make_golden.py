@@ -1,9 +1,9 @@
 """Generate the golden vectors under tests/golden/ from the reference project itself.
 
-Run where the reference checkout is present ($MLSTM_REF, or the default below) and where
-oracle/_ref/libmlstm_ref.so has been built (``make -C oracle ref``):
+Run where the reference checkout is present, with MLSTM_REF pointing at it, and where
+oracle/_ref/libmlstm_ref.so has been built (``make -C oracle ref REF=$MLSTM_REF``):
 
-    python tests/golden/make_golden.py
+    MLSTM_REF=<reference checkout> python tests/golden/make_golden.py
 
 It imports the reference's own PyTorch functions (mlstm_matmul.py:104-118, 336-365;
 mlstm_scan.py:343-372) on CPU and calls the reference's own host C++ forward (mlstmCpu,
@@ -19,7 +19,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("MLSTM_REF", "/root/reference")
+REF = os.environ.get("MLSTM_REF")
+if not REF or not os.path.isfile(os.path.join(REF, "mlstm_matmul.py")):
+    raise SystemExit("set MLSTM_REF to the reference checkout (the directory that holds mlstm_matmul.py)")
 sys.path.insert(0, REF)
 
 import mlstm_matmul as ref_mm  # noqa: E402  (the reference module)
@@ -67,7 +69,7 @@ def gen_cpp(name, S, D, seed):
 
 def gen_cpp_backward(name, S, D, seed):
     """Inputs in the backward driver's recipe (uniform [-1, 1) halves, srand(seed); cuda-src/mlstm_backward.cu:
-    560-566), gradients from the reference's PyTorch backward (mlstm_matmul.py:336-365) in fp32 on those values.
+    580-586), gradients from the reference's PyTorch backward (mlstm_matmul.py:336-365) in fp32 on those values.
     The reference's C++ host backward covers dB, dQ and dK only and is not used."""
     lib = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libmlstm_ref.so"))
     mk = lambda n: np.zeros(n, dtype=np.float16)

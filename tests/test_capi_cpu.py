@@ -26,7 +26,14 @@ def test_workspace_sizes_and_support_matrix(pkg):
     assert L.mlstm_mm_fwd_workspace(1, 1, 128, 64, 2, 0) >= 256 + 2 * 128 * 4
     assert L.mlstm_mm_fwd_workspace(0, 1, 128, 64, 2, 0) == 0
     assert L.mlstm_mm_bwd_workspace(1, 1, 100, 64, 2, 0, 0) > L.mlstm_mm_bwd_workspace(1, 1, 100, 64, 2, 2, 0)
-    assert L.mlstm_mm_fwd_workspace(1, 1, 128, 64, 0, 4) > L.mlstm_mm_fwd_workspace(1, 1, 128, 64, 0, 0)   # tf32 copies
+    # fp32 inputs on the tensor cores work on converted operand copies (split bf16 by default, tf32 on request)
+    assert L.mlstm_mm_fwd_workspace(1, 1, 128, 64, 0, 4) > L.mlstm_mm_fwd_workspace(1, 1, 128, 64, 0, 1)
+    assert L.mlstm_mm_fwd_workspace(1, 1, 128, 64, 0, 0) > L.mlstm_mm_fwd_workspace(1, 1, 128, 64, 0, 8)
+    assert L.mlstm_mm_fwd_workspace(1, 1, 128, 256, 0, 0) == L.mlstm_mm_fwd_workspace(1, 1, 128, 256, 0, 1)   # no split form at D = 256
+    # the scan entry: two-pass scratch above D = 256, chunkwise scratch for long 16-bit sequences at D = 128
+    assert L.mlstm_scan_fwd_workspace(1, 4, 2048, 1024, 0, 4) > 4 * 2048 * 2048 * 4
+    assert L.mlstm_scan_fwd_workspace(1, 2, 4096, 128, 2, 0) == L.mlstm_chunk_workspace(1, 2, 4096, 128, 2, 256)
+    assert L.mlstm_chunk_sp_record_floats(128) == 128 * 128 + 128 + 4
     assert L.mlstm_tc_supported(4096, 256, 2) == 1
     assert L.mlstm_tc_supported(4096, 256, 0) == 2   # fp32: only with MLSTM_F_ALLOW_TF32
     assert L.mlstm_tc_supported(4096, 96, 2) == 0
@@ -52,3 +59,58 @@ def test_python_wrappers_refuse_cpu_tensors(pkg):
         pkg.mlstm_scan(q, q, q, f, f, q)
     with pytest.raises(ValueError):
         pkg.mlstm_scan(q, q, q, f, f, q, reduce_block_size=3)
+
+
+def test_static_scratch_figure_matches_the_workspace_query(pkg):
+    """The built-in scratch of mlstm_forward_f16_static is exactly the forward scratch at its length limit."""
+    L = pkg._lib.lib()
+    header = open(os.path.join(ROOT, "include", "mlstm_b200.h")).read()
+    max_s = int(re.search(r"#define MLSTM_STATIC_MAX_S (\d+)u", header).group(1))
+    nbytes = int(re.search(r"#define MLSTM_STATIC_SCRATCH_BYTES (\d+)u", header).group(1))
+    assert L.mlstm_forward_f16_workspace(max_s, 128) == nbytes
+    assert L.mlstm_forward_f16_workspace(max_s + 1, 128) > nbytes
+
+
+def test_slice_partition_is_contiguous_and_complete(pkg):
+    for n, world in ((128, 1), (128, 8), (10, 4), (3, 8)):
+        edges = [pkg.slice_range(n, r, world) for r in range(world)]
+        assert edges[0][0] == 0 and edges[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(edges, edges[1:]))
+        sizes = [hi - lo for lo, hi in edges]
+        assert max(sizes) - min(sizes) <= 1
+    t = torch.arange(2 * 3 * 5).reshape(2, 3, 5)
+    parts = [pkg.shard_slices(t, r, 4) for r in range(4)]
+    assert torch.equal(pkg.unshard_slices(parts, 2, 3), t)
+
+
+def _partition_worker(rank, world, port, out):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import importlib
+        pkg = importlib.import_module("xlstm-triton-cuda-implementation_b200")
+        g = torch.Generator().manual_seed(0)
+        full = torch.randn(3, 4, 6, 2, generator=g)            # every rank holds the same global problem
+        mine = pkg.shard_slices(full, rank, world).contiguous() * 2.0   # stand-in for the per-slice computation
+        sizes = [torch.zeros(1, dtype=torch.long) for _ in range(world)]
+        dist.all_gather(sizes, torch.tensor([mine.shape[1]]))
+        parts = [torch.empty((1, int(n), 6, 2)) for n in sizes]
+        dist.all_gather(parts, mine)
+        out[rank] = bool(torch.equal(pkg.unshard_slices(parts, 3, 4), full * 2.0))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_slice_partition_over_gloo():
+    """Two ranks shard one global problem by (batch, head) slices, work on their shards and the shards tile the
+    problem exactly (the collective here only carries the check; the data path has none)."""
+    import socket
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = mp.Manager().dict()
+    mp.spawn(_partition_worker, args=(2, port, out), nprocs=2, join=True)
+    assert dict(out) == {0: True, 1: True}

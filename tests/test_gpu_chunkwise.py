@@ -79,6 +79,54 @@ def test_state_continuation_equals_one_call(gc):
     assert orc.max_abs_rel(torch.cat([h1, h2], 2), ref) < TOL_16
 
 
+@pytest.mark.parametrize("cuts,f_mean", [((1024,), 3.0), ((512, 1536, 2560), 0.0), ((256, 512, 768, 1024, 1280, 1536, 3584), 4.0)])
+def test_sequence_parallel_stages_on_one_gpu(gc, cuts, f_mean):
+    """The one-exchange protocol with the ranks emulated one after the other on one GPU: every segment's
+    record with no carry (sp_local), the records stacked as the all-gather would, then fold + output per
+    segment (sp_apply).  Checks the fold kernel against its torch statement and h against the unsplit oracle."""
+    mc = importlib.import_module(PKG + ".mlstm_chunkwise")
+    S = 4096
+    x = gc.make_inputs(1, 2, S, 128, torch.bfloat16, f_mean=f_mean, qkv_scale=128 ** -0.5, seed=len(cuts), with_o=True)
+    edges = (0,) + tuple(cuts) + (S,)
+    segs = []
+    for a, b in zip(edges[:-1], edges[1:]):
+        part = [x[n][:, :, a:b].contiguous().cuda() for n in ("q", "k", "v", "f", "i")]
+        segs.append(mc.ChunkSegment(*part, chunk_size=256, o=x["o"][:, :, a:b].contiguous().cuda()))
+    gathered = torch.stack([s.sp_local() for s in segs])
+    h = torch.cat([s.sp_apply(gathered, g) for g, s in enumerate(segs)], 2)
+    torch.cuda.synchronize()
+    ref = orc.matmul_forward(x["q"], x["k"], x["v"], x["f"], x["i"]) * torch.nn.functional.silu(x["o"].double())
+    assert orc.max_abs_rel(h, ref) < TOL_16
+    # the fold kernel against its torch statement, for the last segment
+    g = len(segs) - 1
+    S_in, z_in, F_in, A_in = mc.fold_records(gathered, g)
+    L = gc._lib.lib()
+    carry = torch.empty((2, 2), dtype=torch.float64, device="cuda")
+    seg = segs[g]
+    hbuf = torch.empty((1, 2, seg.S, 128), dtype=torch.float32, device="cuda")
+    rc = L.mlstm_chunk_sp_apply(seg.q.data_ptr(), seg.k.data_ptr(), seg.v.data_ptr(), None, gathered.data_ptr(), len(segs), g,
+                                hbuf.data_ptr(), 0, carry.data_ptr(), seg.ws.data_ptr(), seg.ws.numel(), *seg.dims, seg._stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert orc.max_abs_rel(carry[:, 0].cpu(), F_in.cpu()) < 1e-12
+    assert orc.max_abs_rel(carry[:, 1].cpu(), A_in.cpu()) < 1e-12
+
+
+def test_long_context_configuration_at_its_own_size(gc):
+    """Configuration 5 (S = 65 536, D = 128, bf16, chunk 256: 256 blocks of carry) on one head against the
+    recurrent oracle (one step per time index), compared on the first block, two blocks in the middle and
+    the last block."""
+    S, D = 65536, 128
+    x = gc.make_inputs(1, 1, S, D, torch.bfloat16, f_mean=3.0, qkv_scale=D ** -0.5, seed=65)
+    h = gc.PKG.mlstm_chunkwise(*_dev(x), chunk_size=256).cpu()
+    ref = orc.scan_forward(x["q"], x["k"], x["v"], x["f"], x["i"], torch.zeros_like(x["q"]).float() + 1.2784645,
+                           dtype=torch.float64)   # silu(1.2784645...) = 1: the gate drops out
+    ref = ref / torch.nn.functional.silu(torch.tensor(1.2784645, dtype=torch.float64))
+    for lo in (0, 20 * 256, 133 * 256, S - 256):
+        err = orc.max_abs_rel(h[:, :, lo:lo + 256], ref[:, :, lo:lo + 256])
+        assert err < TOL_16, (lo, err)
+
+
 def test_chunkwise_rejects_unsupported_cases(gc):
     x = gc.make_inputs(1, 1, 256, 64, torch.bfloat16)
     with pytest.raises(gc._lib.MlstmError):
@@ -107,7 +155,7 @@ def _sp_worker(rank, world, port, x, out):
 
 
 def test_sequence_parallel_over_nccl(gc):
-    """Contiguous segments on 2 (or 4) GPUs, carry over NCCL all-gathers, against the unsplit oracle."""
+    """Contiguous segments on 2 (or 4) GPUs, carry over one NCCL all-gather, against the unsplit oracle."""
     import torch.multiprocessing as mp
     world = min(torch.cuda.device_count(), 4)
     if world < 2:

@@ -1,7 +1,8 @@
 """GPU parity tests of the parallel (matmul) path, through the C ABI, against the CPU oracle.
 
-Tolerances (max |a-b| / max |b|): 1e-4 for the fp32 CUDA-core path (the reference computes IEEE fp32
-dots), 1e-2 for 16-bit tensor-core math (the reference's own check tolerance, utils.py:4).
+Tolerances (max |a-b| / max |b|): 1e-4 forward / 3e-4 gradients for fp32 inputs (the reference computes
+IEEE fp32 dots; here the CUDA-core path and, at D = 64 and 128, the split tensor-core form), 1e-2 for
+16-bit and tf32 tensor-core math (the reference's own check tolerance, utils.py:4).
 """
 import numpy as np
 import pytest
@@ -48,11 +49,34 @@ def test_fp32_against_reference_golden(gc, golden_dir, name):
 ])
 def test_fp32_simt_forward_backward(gc, B, NH, S, D, f_mean):
     x = gc.make_inputs(B, NH, S, D, torch.float32, f_mean=f_mean, seed=S + D)
-    h, m, b = gc.run_forward(x)
+    flags = gc._lib.F_FORCE_SIMT
+    h, m, b = gc.run_forward(x, flags=flags)
     ef = gc.errors_forward(x, h, m, b)
     assert ef["h"] < TOL_F32 and ef["m"] < 1e-5 and ef["b"] < TOL_F32, ef
-    eb = gc.errors_backward(x, gc.run_backward(x, h, m, b), torch.float32)
+    eb = gc.errors_backward(x, gc.run_backward(x, h, m, b, flags=flags), torch.float32)
     assert all(v < 3e-4 for v in eb.values()), eb
+
+
+@pytest.mark.parametrize("B,NH,S,D,f_mean,scale", [
+    (1, 4, 2048, 64, 0.0, 1.0),      # the reference demo / configuration 2, through the default path
+    (1, 2, 328, 128, 1.0, 128 ** -0.5),
+    (2, 2, 200, 64, 3.0, 1.0),       # ragged S
+    (1, 2, 192, 128, -0.5, 1.0),     # strong decay, last 64-position block pure padding
+    (1, 1, 1, 64, 0.0, 1.0),         # a single step (forward only, see test_single_step_sequence)
+])
+def test_fp32_split_tensor_core_forward_backward(gc, B, NH, S, D, f_mean, scale):
+    """fp32 inputs at D = 64 / 128 take the tensor cores by default with operands split into two bf16 halves
+    (three products per fp32 product): the fp32 tolerances apply, and the elementwise comparator must pass."""
+    x = gc.make_inputs(B, NH, S, D, torch.float32, f_mean=f_mean, qkv_scale=scale, seed=S + D)
+    assert gc._lib.lib().mlstm_mm_fwd_workspace(B, NH, S, D, 0, 0) > gc._lib.lib().mlstm_mm_fwd_workspace(B, NH, S, D, 0, 8)
+    h, m, b = gc.run_forward(x, flags=gc._lib.F_FORCE_TC)
+    ef = gc.errors_forward(x, h, m, b)
+    assert ef["h"] < TOL_F32 and ef["m"] < 1e-5 and ef["b"] < TOL_F32, ef
+    assert ef["h_check_frac"] == 0.0, ef
+    if S > 1:
+        eb = gc.errors_backward(x, gc.run_backward(x, h, m, b, flags=gc._lib.F_FORCE_TC), torch.float32)
+        assert all(v < 3e-4 for k, v in eb.items() if k != "check_frac"), eb
+        assert eb["check_frac"] == 0.0, eb
 
 
 def test_single_step_sequence(gc):
@@ -78,6 +102,7 @@ def test_tensor_core_forward_backward(gc, dtype, D, S, f_mean):
         h, m, b = gc.run_forward(x, h_dtype=h_dtype, flags=flags)
         ef = gc.errors_forward(x, h, m, b)
         assert ef["h"] < TOL_16 and ef["m"] < 1e-5 and ef["b"] < TOL_16, (h_dtype, ef)
+        assert ef["h_check_frac"] < gc.CHECK_FRAC_16 and ef["h_first_tile_row_rel"] < gc.ROW_REL_16, (h_dtype, ef)
         eb = gc.errors_backward(x, gc.run_backward(x, h, m, b, flags=flags), h_dtype)
         assert all(v < TOL_16 for v in eb.values()), (h_dtype, eb)
 
@@ -93,6 +118,7 @@ def test_strong_decay_with_a_fully_padded_column_block(gc, dtype, D, S):
     h, m, b = gc.run_forward(x, h_dtype=dtype, flags=flags)
     ef = gc.errors_forward(x, h, m, b)
     assert ef["h"] < TOL_16 and ef["b"] < TOL_16, ef
+    assert ef["h_check_frac"] < gc.CHECK_FRAC_16 and ef["h_first_tile_row_rel"] < gc.ROW_REL_16, ef
     grads = gc.run_backward(x, h, m, b, flags=flags)
     assert all(bool(torch.isfinite(t.float()).all()) for t in grads)
     eb = gc.errors_backward(x, grads, dtype)
@@ -141,10 +167,12 @@ def test_autograd_function_matches_reference_api(gc):
     assert torch.equal(h2, h.detach())
 
 
-def test_model_scale_slice_properties(gc):
-    """Configuration-4 shape per slice (S=4096, D=256, bf16) on a few slices: oracle parity on one
-    slice, and slice independence (each slice equals the same slice run alone)."""
-    x = gc.make_inputs(1, 3, 4096, 256, torch.bfloat16, f_mean=3.0, qkv_scale=256 ** -0.5, seed=0)
+@pytest.mark.parametrize("f_mean", [3.0, 0.0])
+def test_model_scale_slice_properties(gc, f_mean):
+    """Configuration-4 shape per slice (S=4096, D=256, bf16) on a few slices, with retention-biased gates
+    (the configuration's own) and with N(0,1) gates: oracle parity on one slice, and slice independence
+    (each slice equals the same slice run alone)."""
+    x = gc.make_inputs(1, 3, 4096, 256, torch.bfloat16, f_mean=f_mean, qkv_scale=256 ** -0.5, seed=0)
     h, m, b = gc.run_forward(x, h_dtype=torch.bfloat16)
     grads = gc.run_backward(x, h, m, b)
     one = {k: v[:, 1:2].contiguous() for k, v in x.items()}
@@ -155,8 +183,32 @@ def test_model_scale_slice_properties(gc):
         assert torch.equal(a, b_[:, 1:2])
     ef = gc.errors_forward(one, h1, m1, b1)
     assert ef["h"] < TOL_16, ef
+    assert ef["h_check_frac"] < gc.CHECK_FRAC_16, ef
     eb = gc.errors_backward(one, g1, torch.bfloat16)
     assert all(v < TOL_16 for v in eb.values()), eb
+
+
+def test_bounded_wait_runs_out_and_the_device_stays_usable(gc):
+    """The waits of every kernel are bounded; this makes one run out on purpose, the allowed way: a warp waits
+    (limit: two million cycles, about a millisecond) on a barrier that nothing completes, then stores a code in the
+    status word.  mlstm_read_status must report MLSTM_E_TIMEOUT with that code, and ordinary work must still pass."""
+    import ctypes
+    L = gc._lib.lib()
+    dev = torch.device("cuda", 0)
+    ws = torch.zeros(4096, dtype=torch.uint8, device=dev)
+    stream = gc._lib.stream_ptr(dev)
+    assert L.mlstm_selftest_wait_timeout(ws.data_ptr(), ws.numel(), 2_000_000, stream) == 0
+    code = ctypes.c_int(0)
+    assert L.mlstm_read_status(ws.data_ptr(), ctypes.byref(code), stream) == -7   # MLSTM_E_TIMEOUT
+    assert code.value == 4000
+    assert b"gave up" in L.mlstm_status_string(-7)
+    assert L.mlstm_selftest_wait_timeout(ws.data_ptr(), 16, 2_000_000, stream) == -5
+    assert L.mlstm_selftest_wait_timeout(ws.data_ptr(), ws.numel(), 0, stream) == -1
+    # the context is intact: an ordinary call on the same device passes and reports a clean status
+    x = gc.make_inputs(1, 2, 256, 64, torch.bfloat16, f_mean=1.0, qkv_scale=0.125, seed=2)
+    h, m, b = gc.run_forward(x, flags=gc._lib.F_FORCE_TC)
+    ef = gc.errors_forward(x, h, m, b)
+    assert ef["h"] < TOL_16, ef
 
 
 def test_argument_errors(gc):
@@ -167,4 +219,4 @@ def test_argument_errors(gc):
         gc.run_forward(x)  # D not a multiple of 8
     x = gc.make_inputs(1, 1, 64, 32, torch.float32)
     with pytest.raises(gc._lib.MlstmError):
-        gc.run_forward(x, flags=gc._lib.F_FORCE_TC)  # fp32 has no tensor-core path
+        gc.run_forward(x, flags=gc._lib.F_FORCE_TC)  # fp32 at D = 32 has no tensor-core path

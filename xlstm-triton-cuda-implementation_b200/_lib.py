@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libmlstm_b200.so")
 
 DT_F32, DT_F16, DT_BF16 = 0, 1, 2
-F_FORCE_SIMT, F_FORCE_TC, F_ALLOW_TF32 = 1, 2, 4
+F_FORCE_SIMT, F_FORCE_TC, F_ALLOW_TF32, F_NO_SPLIT = 1, 2, 4, 8
 _DTYPES = {torch.float32: DT_F32, torch.float16: DT_F16, torch.bfloat16: DT_BF16}
 
 _lib = None

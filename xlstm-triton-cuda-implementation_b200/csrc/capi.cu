@@ -12,7 +12,6 @@ namespace {
 constexpr size_t WS_ALIGN = 256;
 constexpr size_t al(size_t x) { return (x + WS_ALIGN - 1) / WS_ALIGN * WS_ALIGN; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-inline size_t esize(int dt) { return dt == MLSTM_DT_F32 ? 4 : 2; }
 inline bool dtype_ok(int dt) { return dt == MLSTM_DT_F32 || dt == MLSTM_DT_F16 || dt == MLSTM_DT_BF16; }
 
 struct Carver {
@@ -109,47 +108,60 @@ int check_dims(int B, int NH, int S, int D) {
     return MLSTM_OK;
 }
 
-bool use_tc(int S, int D, int dtype, int flags, int* rc) {
+// How a pass runs.  fp32 inputs: IEEE fp32 on the CUDA cores when forced or when no tensor-core form applies;
+// single tf32 products only when the caller allows that arithmetic; otherwise, for D = 64 and 128, the
+// split form (three bf16 products per fp32 product, fp32 accumulate) whose error is at fp32 level.
+enum PassKind { KIND_SIMT = 0, KIND_TC = 1, KIND_TC_X3 = 2 };
+
+int pass_kind(int S, int D, int dtype, int flags, int* rc) {
     *rc = MLSTM_OK;
     if ((flags & MLSTM_F_FORCE_SIMT) && (flags & MLSTM_F_FORCE_TC)) {
         *rc = MLSTM_E_ARG;
-        return false;
+        return KIND_SIMT;
     }
-    // fp32 inputs take the tensor cores (as tf32) only when the caller allows that arithmetic
-    const bool can = tc_supported(S, D, dtype) && (dtype != MLSTM_DT_F32 || (flags & MLSTM_F_ALLOW_TF32));
-    if (flags & MLSTM_F_FORCE_TC) {
-        if (!can) *rc = MLSTM_E_UNSUPPORTED;
-        return can;
+    int kind = KIND_SIMT;
+    if (dtype != MLSTM_DT_F32) {
+        if (tc_supported(S, D, dtype)) kind = KIND_TC;
+    } else if ((flags & MLSTM_F_ALLOW_TF32) && tc_supported(S, D, dtype)) {
+        kind = KIND_TC;
+    } else if (!(flags & MLSTM_F_NO_SPLIT) && tc_x3_supported(S, D)) {
+        kind = KIND_TC_X3;
     }
-    return can && !(flags & MLSTM_F_FORCE_SIMT);
+    if (flags & MLSTM_F_FORCE_SIMT) return KIND_SIMT;
+    if ((flags & MLSTM_F_FORCE_TC) && kind == KIND_SIMT) *rc = MLSTM_E_UNSUPPORTED;
+    return kind;
 }
 
-// fp32 inputs on the tensor cores are first rounded to tf32 into workspace copies (n tensors)
+// fp32 inputs on the tensor cores work on converted copies of the operands in the workspace (n tensors):
+// tf32-rounded fp32 copies, or bf16 hi | mid copies of the same size.
 size_t tf32_copy_bytes(int BH, int S, int D, int dtype, int flags, int ntensors) {
-    const bool tc = tc_supported(S, D, dtype) && (flags & MLSTM_F_ALLOW_TF32) && !(flags & MLSTM_F_FORCE_SIMT);
-    return (dtype == MLSTM_DT_F32 && tc) ? ntensors * al(static_cast<size_t>(BH) * S * D * sizeof(float)) : 0;
+    int rc;
+    const int kind = pass_kind(S, D, dtype, flags, &rc);
+    return (dtype == MLSTM_DT_F32 && kind != KIND_SIMT) ? ntensors * al(static_cast<size_t>(BH) * S * D * sizeof(float)) : 0;
 }
-// rounds `count` tensors into consecutive regions of `buf` and redirects the pointers
-int round_inputs(const void** ptrs, int count, void* buf, int BH, int S, int D, cudaStream_t st) {
+// converts `count` tensors into consecutive regions of `buf` and redirects the pointers
+int round_inputs(const void** ptrs, int count, void* buf, int BH, int S, int D, int kind, cudaStream_t st) {
     const size_t one = al(static_cast<size_t>(BH) * S * D * sizeof(float));
     for (int k = 0; k < count; k++) {
         void* dst = static_cast<uint8_t*>(buf) + k * one;
-        int rc = launch_round_tf32(ptrs[k], dst, static_cast<long long>(BH) * S * D, st);
+        int rc = kind == KIND_TC_X3 ? launch_split_bf16(ptrs[k], dst, static_cast<long long>(BH) * S, D, st)
+                                    : launch_round_tf32(ptrs[k], dst, static_cast<long long>(BH) * S * D, st);
         if (rc != MLSTM_OK) return rc;
         ptrs[k] = dst;
     }
     return MLSTM_OK;
 }
 
-int run_pass(bool tc, int mode, const PassParams& p, int in_dt, int out_dt, cudaStream_t st) {
-    return tc ? launch_pass_tc(mode, p, in_dt, out_dt, st) : launch_pass_simt(mode, p, in_dt, out_dt, st);
+int run_pass(int kind, int mode, const PassParams& p, int in_dt, int out_dt, cudaStream_t st) {
+    if (kind == KIND_TC_X3) return launch_pass_tc_x3(mode, p, st);
+    return kind == KIND_TC ? launch_pass_tc(mode, p, in_dt, out_dt, st) : launch_pass_simt(mode, p, in_dt, out_dt, st);
 }
 
 int forward_impl(const void* q, const void* k, const void* v, const void* f, const void* i, const void* o, void* h,
                  float* m, float* b, const FwdWs& w, int BH, int S, int D, int dtype, int h_dtype, int flags,
                  cudaStream_t st, void* tf32buf = nullptr) {
     int rc;
-    const bool tc = use_tc(S, D, dtype, flags, &rc);
+    const int kind = pass_kind(S, D, dtype, flags, &rc);
     if (rc != MLSTM_OK) return rc;
     const int Spad = round_up(S, TILE);
     if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
@@ -157,9 +169,9 @@ int forward_impl(const void* q, const void* k, const void* v, const void* f, con
                                w.gaw)) != MLSTM_OK)
         return rc;
     const void* in[3] = {q, k, v};
-    if (tc && dtype == MLSTM_DT_F32) {
+    if (kind != KIND_SIMT && dtype == MLSTM_DT_F32) {
         if (!tf32buf) return MLSTM_E_WORKSPACE;
-        if ((rc = round_inputs(in, 3, tf32buf, BH, S, D, st)) != MLSTM_OK) return rc;
+        if ((rc = round_inputs(in, 3, tf32buf, BH, S, D, kind, st)) != MLSTM_OK) return rc;
     }
     PassParams p{};
     p.S = S; p.Spad = Spad; p.BH = BH; p.D = D;
@@ -168,7 +180,7 @@ int forward_impl(const void* q, const void* k, const void* v, const void* f, con
     p.er_add = -0.5f * log2f(static_cast<float>(D));
     p.out = h; p.m = m; p.b_out = b; p.ogate = o;
     p.status = w.status; p.sched = w.status + 8;
-    return run_pass(tc, FWD, p, dtype, h_dtype, st);
+    return run_pass(kind, FWD, p, dtype, h_dtype, st);
 }
 
 }  // namespace
@@ -249,7 +261,7 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     BwdWs w = carve_bwd(workspace, BH, S, D, need16);
     const size_t extra = tf32_copy_bytes(BH, S, D, dtype, flags, 4);
     if (!workspace || workspace_bytes < w.bytes + extra || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
-    const bool tc = use_tc(S, D, dtype, flags, &rc);
+    const int kind = pass_kind(S, D, dtype, flags, &rc);
     if (rc != MLSTM_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
@@ -262,10 +274,10 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     const void* dhp = need16 ? w.dh16 : dh;  // dh in the element type of q, k, v
     const void* orig_q = q;
     const void* orig_k = k;
-    if (tc && dtype == MLSTM_DT_F32) {  // tf32 operands: rounded copies of q, k, v, dh
+    if (kind != KIND_SIMT && dtype == MLSTM_DT_F32) {  // converted copies of q, k, v, dh
         if (!extra) return MLSTM_E_WORKSPACE;
         const void* in[4] = {q, k, v, dhp};
-        if ((rc = round_inputs(in, 4, static_cast<uint8_t*>(workspace) + w.bytes, BH, S, D, st)) != MLSTM_OK) return rc;
+        if ((rc = round_inputs(in, 4, static_cast<uint8_t*>(workspace) + w.bytes, BH, S, D, kind, st)) != MLSTM_OK) return rc;
         q = in[0]; k = in[1]; v = in[2]; dhp = in[3];
     }
 
@@ -275,17 +287,17 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     p.X = dhp; p.Y = v; p.Z = k;
     p.row_rel = w.gB; p.row_ref = w.An_ref; p.row_g = w.g; p.col_rel = w.ga; p.col_w = w.gaw; p.col_ref = w.a_ref; p.col_g = nullptr;
     p.out = dq; p.dot_src = orig_q; p.dot_out = w.R;
-    if ((rc = run_pass(tc, DQ, p, dtype, dtype, st)) != MLSTM_OK) return rc;
+    if ((rc = run_pass(kind, DQ, p, dtype, dtype, st)) != MLSTM_OK) return rc;
     // dK = ((V dH^T + g_c) * decay)  Q
     p.X = v; p.Y = dhp; p.Z = q;
     p.row_rel = w.ga; p.row_ref = w.a_ref; p.row_g = nullptr; p.col_rel = w.gB; p.col_w = w.gBw; p.col_ref = w.An_ref; p.col_g = w.g;
     p.out = dk; p.dot_src = orig_k; p.dot_out = w.dI;
-    if ((rc = run_pass(tc, DK, p, dtype, dtype, st)) != MLSTM_OK) return rc;
+    if ((rc = run_pass(kind, DK, p, dtype, dtype, st)) != MLSTM_OK) return rc;
     // dV = ((K Q^T) * decay / n) dH
     p.X = k; p.Y = q; p.Z = dhp;
     p.col_g = nullptr;
     p.out = dv; p.dot_src = nullptr; p.dot_out = nullptr;
-    if ((rc = run_pass(tc, DV, p, dtype, dtype, st)) != MLSTM_OK) return rc;
+    if ((rc = run_pass(kind, DV, p, dtype, dtype, st)) != MLSTM_OK) return rc;
     return launch_df(f, w.dI, w.R, df, di, BH, S, Spad, dtype, st);
 }
 

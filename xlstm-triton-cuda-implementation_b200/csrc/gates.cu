@@ -358,7 +358,36 @@ __global__ void round_tf32_kernel(const float4* __restrict__ in, float4* __restr
     out[idx] = *reinterpret_cast<float4*>(&y);
 }
 
+// fp32 -> two bf16 halves: hi = bf16(x), mid = bf16(x - hi), written side by side as rows of 2 D values
+// (hi | mid).  x - hi is exact in fp32, so hi + mid carries 16 mantissa bits of x.  Four values per thread.
+__global__ void split_bf16_kernel(const float4* __restrict__ in, __nv_bfloat16* __restrict__ out, long long n4, int D) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= n4) return;
+    const float4 x = in[idx];
+    const long long e = idx * 4;
+    const long long row = e / D;
+    const int col = static_cast<int>(e - row * D);
+    __nv_bfloat162 h01 = __floats2bfloat162_rn(x.x, x.y), h23 = __floats2bfloat162_rn(x.z, x.w);
+    const float2 f01 = __bfloat1622float2(h01), f23 = __bfloat1622float2(h23);
+    __nv_bfloat162 m01 = __floats2bfloat162_rn(x.x - f01.x, x.y - f01.y), m23 = __floats2bfloat162_rn(x.z - f23.x, x.w - f23.y);
+    __nv_bfloat16* dst = out + row * 2 * D + col;
+    uint2 hv, mv;
+    hv.x = *reinterpret_cast<uint32_t*>(&h01); hv.y = *reinterpret_cast<uint32_t*>(&h23);
+    mv.x = *reinterpret_cast<uint32_t*>(&m01); mv.y = *reinterpret_cast<uint32_t*>(&m23);
+    *reinterpret_cast<uint2*>(dst) = hv;
+    *reinterpret_cast<uint2*>(dst + D) = mv;
+}
+
 }  // namespace
+
+int launch_split_bf16(const void* in, void* out, long long rows, int D, cudaStream_t st) {
+    const long long n4 = rows * D / 4;
+    const int threads = 256;
+    const long long blocks = (n4 + threads - 1) / threads;
+    if (blocks <= 0 || blocks > 0x7fffffffLL || (D & 3)) return MLSTM_E_SHAPE;
+    split_bf16_kernel<<<(unsigned)blocks, threads, 0, st>>>(static_cast<const float4*>(in), static_cast<__nv_bfloat16*>(out), n4, D);
+    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+}
 
 int launch_ogate_fwd(const void* h_inner, const void* o, void* h, long long n, int h_dtype, int o_dtype, cudaStream_t st) {
     return ogate_dispatch<false>(nullptr, h_inner, o, h, nullptr, n, h_dtype, o_dtype, st);

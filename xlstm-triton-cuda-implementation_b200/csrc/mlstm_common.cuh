@@ -143,6 +143,10 @@ int launch_pass_simt(int mode, const PassParams& p, int in_dtype, int out_dtype,
 int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st);
 bool tc_supported(int S, int D, int in_dtype);
 int launch_round_tf32(const void* in, void* out, long long n, cudaStream_t st);
+// fp32 [rows, D] -> bf16 [rows, 2 D] (hi | mid): the operands of the split tensor-core form (mm_tc.cu)
+int launch_split_bf16(const void* in, void* out, long long rows, int D, cudaStream_t st);
+bool tc_x3_supported(int S, int D);
+int launch_pass_tc_x3(int mode, const PassParams& p, cudaStream_t st);
 int launch_ogate_fwd(const void* h_inner, const void* o, void* h, long long n, int h_dtype, int o_dtype, cudaStream_t st);
 int launch_ogate_bwd(const void* dh, const void* h_inner, const void* o, void* dh_inner, void* d_o, long long n, int h_dtype,
                      int o_dtype, cudaStream_t st);

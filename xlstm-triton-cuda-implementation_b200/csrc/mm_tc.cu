@@ -98,7 +98,13 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
     return y;
 }
 
-template <int MODE, int D, int ABFMT, typename OutT>
+// X3: fp32 operands carried as two bf16 halves each (x = hi + mid to 16 mantissa bits; the split kernel in
+// gates.cu writes them side by side as rows of 2 D bf16 values, hi | mid).  Every contraction then issues the
+// three products hi*hi + hi*mid + mid*hi into the same fp32 accumulator (kind::f16 MMAs; the dropped mid*mid
+// term is 2^-18 relative), and the gated tile W is split the same way in TMEM: a 16-bit W tile fills only
+// half of the columns of the T tile it overwrites, the mid halves take the other half.  This gives fp32
+// inputs the tensor cores at an accuracy of about 1e-5, where single tf32 products are at 5e-4.
+template <int MODE, int D, int ABFMT, typename OutT, bool X3 = false>
 // 18 warps = up to 5 per SM sub-partition (16384 registers each): at most 96 registers per thread
 __global__ void __launch_bounds__(NTHREADS, 1)
 mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
@@ -106,9 +112,15 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
               const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmO, const PassParams p) {
     constexpr int ES = ABFMT == 2 ? 4 : 2;
     constexpr bool TF32 = ABFMT == 2;
-    using C = TcCfg<D, ES>;
+    constexpr int DL = X3 ? 2 * D : D;            // width of the loaded tiles
+    using C = TcCfg<DL, ES>;
     using InT = typename std::conditional<ABFMT == 2, float,
                                           typename std::conditional<ABFMT == 1, __nv_bfloat16, __half>::type>::type;
+    // element type of the tensors the epilogue reads straight from global memory (output gate, row-dot operand)
+    using SideT = typename std::conditional<X3, float, InT>::type;
+    static_assert(!X3 || (ABFMT == 1 && (D == 64 || D == 128) && MODE <= DV), "the split form serves D = 64, 128 of the four parallel passes");
+    constexpr int BPS = C::CH / 64;               // X3: 128-byte boxes per ring slot
+    constexpr int NBX = D / 64;                   // X3: boxes per operand half
     constexpr bool ROWS_ARE_Q = (MODE == FWD || MODE == DQ || MODE == FWDC);
     constexpr bool IS_FWD = (MODE == FWD || MODE == FWDC);   // normalised output, row sums kept
     static_assert((MODE != FWDC && MODE != STATE) || (D == 128 && ES == 2), "chunkwise passes are built for 16-bit D = 128");
@@ -138,7 +150,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     volatile int* item_ids = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [4] ring of published work items
     // [PARTS][NGROUPS][128]: row sums in FWD / STATE, row dots in DQ / DK, one value per gate group and row
     float* part_base = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + C::NBAR * 8 + 64);
-    constexpr bool STAGED = C::STAGED;
+    constexpr bool STAGED = C::STAGED && !X3;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -255,7 +267,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 ok = mbar_wait<SLACK_SLEEP_NS>(bar_xfree, (n & 1) ^ 1, abort_flag, WAIT_LIMIT);
                 if (!ok) break;
                 mbar_expect_tx(bar_x, C::X_BYTES);
-                for (int c = 0; c < D / C::EPB; c++) {
+                for (int c = 0; c < DL / C::EPB; c++) {
                     if (MODE == STATE) tma_load_3d(sX + c * BOX_BYTES, &tmI, bar_x, c * C::EPB, 0, 0);
                     else tma_load_3d(sX + c * BOX_BYTES, &tmX, bar_x, c * C::EPB, it.tile * TILE, it.bh);
                 }
@@ -289,7 +301,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             auto uni = [](int x) { return __shfl_sync(0xffffffffu, x, 0); };
             auto wait_u = [&](uint64_t* bar, uint32_t parity) { return mbar_wait_warp(bar, parity, abort_flag, WAIT_LIMIT); };
             constexpr uint32_t idesc1 = make_idesc(ABFMT, 128, 128, 0, 0);
-            constexpr uint32_t idesc2 = make_idesc(ABFMT, 128, C::CH, 0, 1);
+            constexpr uint32_t idesc2 = make_idesc(ABFMT, 128, X3 ? D : C::CH, 0, 1);
             constexpr int KROWS_BYTES = C::KSTEP * 128;  // KSTEP streamed rows of the Z tile
             const uint32_t sX_u = static_cast<uint32_t>(uni(static_cast<int>(smem_u32(sX))));
             const uint32_t sSlot_u = sX_u + C::X_BYTES;
@@ -342,7 +354,25 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                         if (!ok) return;
 #pragma unroll
                         for (int part = 0; part < 2; part++) {
-                            if (issuer) {
+                            if constexpr (X3) {
+                                if (issuer) {
+#pragma unroll
+                                    for (int pr = 0; pr < 3; pr++) {   // (W hi, Z hi), (W hi, Z mid), (W mid, Z hi)
+                                        const int box = (pr == 1) ? NBX : 0;   // first box of the Z half
+                                        const uint64_t zdesc = smem_desc_advance(
+                                            zdesc0, ((useq * C::UH + box / BPS) % C::NSLOT) * C::SLOT_BYTES + (box % BPS) * BOX_BYTES);
+#pragma unroll
+                                        for (int kk = 0; kk < KS2; kk++) {
+                                            if (((pr * KS2 + kk) * 2) / (3 * KS2) != part) continue;
+                                            // W hi of gate group g in columns [32g, 32g+16), W mid in [32g+16, 32g+32)
+                                            const uint32_t at = w_tmem + (kk >> 1) * 32 + (kk & 1) * 8 + (pr == 2 ? 16 : 0);
+                                            mma_ts<false>(tmem_ACCu, at, smem_desc_advance(zdesc, kk * KROWS_BYTES), idesc2,
+                                                          (u > 0 || pr > 0 || kk > 0) ? 1u : 0u);
+                                        }
+                                    }
+                                    if (part == 1) tc_commit(&bar_cons[useq % C::RING]);
+                                }
+                            } else if (issuer) {
 #pragma unroll
                                 for (int h2 = 0; h2 < C::UH; h2++) {
                                     const int hf = un * C::UH + h2;
@@ -379,7 +409,27 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                         if (!ok) break;
 #pragma unroll
                         for (int part = 0; part < 2; part++) {
-                            if (issuer) {
+                            if constexpr (X3) {
+                                if (issuer) {
+                                    constexpr int KSX = D / 16;    // K steps per operand half
+#pragma unroll
+                                    for (int pr = 0; pr < 3; pr++) {   // (X hi, Y hi), (X hi, Y mid), (X mid, Y hi)
+#pragma unroll
+                                        for (int ks = 0; ks < KSX; ks++) {
+                                            if (((pr * KSX + ks) * 2) / (3 * KSX) != part) continue;
+                                            const int xb = (pr == 2 ? NBX : 0) + (ks >> 2), yb = (pr == 1 ? NBX : 0) + (ks >> 2);
+                                            const uint64_t yd = smem_desc_advance(
+                                                ydesc0, ((useq * C::UH + yb / BPS) % C::NSLOT) * C::SLOT_BYTES + (yb % BPS) * BOX_BYTES + (ks & 3) * 32);
+                                            mma_ss<false>(t_tmem, smem_desc_advance(xdesc0, xb * BOX_BYTES + (ks & 3) * 32), yd, idesc1,
+                                                          (pr > 0 || ks > 0) ? 1u : 0u);
+                                        }
+                                    }
+                                    if (part == 1) {
+                                        tc_commit(&bar_cons[useq % C::RING]);
+                                        if (t == it.nsteps - 1) tc_commit(bar_xfree);
+                                    }
+                                }
+                            } else if (issuer) {
 #pragma unroll
                                 for (int h2 = 0; h2 < C::UH; h2++) {
                                     const int hf = un * C::UH + h2;
@@ -559,6 +609,16 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
 #pragma unroll
                 for (int j = 0; j < 32; j++) tv[j] = to_tf32(cv[j]);
                 tmem_st32(t_tmem, tv);   // in place: column for column
+            } else if constexpr (X3) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) {   // W = hi + mid, both bf16: hi halves in the first 16 columns, mid in the other 16
+                    __nv_bfloat162 hi2 = __floats2bfloat162_rn(cv[2 * j], cv[2 * j + 1]);
+                    const float2 hf2 = __bfloat1622float2(hi2);
+                    __nv_bfloat162 mid2 = __floats2bfloat162_rn(cv[2 * j] - hf2.x, cv[2 * j + 1] - hf2.y);
+                    tv[j] = *reinterpret_cast<uint32_t*>(&hi2);
+                    tv[16 + j] = *reinterpret_cast<uint32_t*>(&mid2);
+                }
+                tmem_st32(t_tmem, tv);
             } else {
                 uint32_t pk[16];
 #pragma unroll
@@ -584,7 +644,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         // ---- while the last contractions run: everything of the epilogue that does not need the accumulator
         constexpr int QUART = D / NGROUPS;             // 16, 32 or 64 columns
         constexpr int CW = QUART < 32 ? QUART : 32;    // columns per TMEM load
-        constexpr int VEC = 16 / sizeof(InT);          // input elements per 16-byte access
+        constexpr int VEC = 16 / sizeof(SideT);        // elements per 16-byte access of the tensors read in the epilogue
         const int c0 = grp * QUART;
         const bool row_ok = (MODE == STATE) ? true : (grow < p.S);
         float* part = part_base + (C::PARTS == 2 ? (n & 1) * NGROUPS * 128 : 0);
@@ -642,9 +702,9 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                                        : (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * D;
             float dot = 0.0f;
             OutT* orow = reinterpret_cast<OutT*>(p.out) + row_off + c0;
-            const InT* ogate_row = (IS_FWD && p.ogate) ? reinterpret_cast<const InT*>(p.ogate) + row_off + c0 : nullptr;
-            const InT* drow = ((MODE == DQ || MODE == DK) && p.dot_src)
-                                  ? reinterpret_cast<const InT*>(p.dot_src) + row_off + c0 : nullptr;
+            const SideT* ogate_row = (IS_FWD && p.ogate) ? reinterpret_cast<const SideT*>(p.ogate) + row_off + c0 : nullptr;
+            const SideT* drow = ((MODE == DQ || MODE == DK) && p.dot_src)
+                                    ? reinterpret_cast<const SideT*>(p.dot_src) + row_off + c0 : nullptr;
 #pragma unroll 1
             for (int ch = 0; ch < QUART / CW; ch++) {
                 uint32_t av[32];
@@ -666,15 +726,15 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 if (row_ok) {
                     if (IS_FWD && ogate_row) {
 #pragma unroll
-                        for (int j = 0; j < CW; j++) vals[j] *= silu_f(to_f32<InT>(ogate_row[ch * CW + j]));
+                        for (int j = 0; j < CW; j++) vals[j] *= silu_f(to_f32<SideT>(ogate_row[ch * CW + j]));
                     }
                     if ((MODE == DQ || MODE == DK) && drow) {
 #pragma unroll
                         for (int jv = 0; jv < CW / VEC; jv++) {
                             const uint4 raw = *reinterpret_cast<const uint4*>(drow + ch * CW + jv * VEC);
-                            const InT* ev = reinterpret_cast<const InT*>(&raw);
+                            const SideT* ev = reinterpret_cast<const SideT*>(&raw);
 #pragma unroll
-                            for (int j = 0; j < VEC; j++) dot += vals[jv * VEC + j] * to_f32<InT>(ev[j]);
+                            for (int j = 0; j < VEC; j++) dot += vals[jv * VEC + j] * to_f32<SideT>(ev[j]);
                         }
                     }
                 }
@@ -868,15 +928,16 @@ int sm_count() {
     return n;
 }
 
-template <int MODE, int D, int ABFMT, typename OutT>
+template <int MODE, int D, int ABFMT, typename OutT, bool X3 = false>
 int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
     PassParams p = p_in;
     p.slice_set = SLICE_SET_DEFAULT;
     CUtensorMap mx, my, mz, mi, ms, mo;
     int rc;
-    if ((rc = make_map(&mx, p.X, p.BH, p.S, D, in_dtype)) != MLSTM_OK) return rc;
-    if ((rc = make_map(&my, p.Y, p.BH, p.S, D, in_dtype)) != MLSTM_OK) return rc;
-    if ((rc = make_map(&mz, p.Z, p.BH, p.S, D, in_dtype, ABFMT == 2)) != MLSTM_OK) return rc;
+    constexpr int DL = X3 ? 2 * D : D;   // X3: X, Y, Z are the split copies, rows of hi | mid
+    if ((rc = make_map(&mx, p.X, p.BH, p.S, DL, in_dtype)) != MLSTM_OK) return rc;
+    if ((rc = make_map(&my, p.Y, p.BH, p.S, DL, in_dtype)) != MLSTM_OK) return rc;
+    if ((rc = make_map(&mz, p.Z, p.BH, p.S, DL, in_dtype, ABFMT == 2)) != MLSTM_OK) return rc;
     mi = mx;
     ms = mx;
     if (MODE == FWDC || MODE == STATE) {
@@ -888,14 +949,14 @@ int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
         if ((rc = make_map(&ms, p.states, p.BH * p.NB, D, D, in_dtype)) != MLSTM_OK) return rc;
     }
     mo = mx;
-    if (TcCfg<D, ABFMT == 2 ? 4 : 2>::STAGED) {
+    if (TcCfg<DL, ABFMT == 2 ? 4 : 2>::STAGED && !X3) {
         constexpr int out_dtype = sizeof(OutT) == 4 ? MLSTM_DT_F32 : (ABFMT == 1 ? MLSTM_DT_BF16 : MLSTM_DT_F16);
         if (MODE == STATE) rc = tc_make_map_out(&mo, p.out, p.BH * p.NB, D, D, out_dtype, 32);
         else rc = tc_make_map_out(&mo, p.out, p.BH, p.S, D, out_dtype, 32);
         if (rc != MLSTM_OK) return rc;
     }
-    auto kern = mlstm_tc_pass<MODE, D, ABFMT, OutT>;
-    constexpr int smem = TcCfg<D, ABFMT == 2 ? 4 : 2>::SMEM_BYTES;
+    auto kern = mlstm_tc_pass<MODE, D, ABFMT, OutT, X3>;
+    constexpr int smem = TcCfg<DL, ABFMT == 2 ? 4 : 2>::SMEM_BYTES;
     cudaError_t ce;
     {   // the shared-memory opt-in is a per-device property of the kernel: set once per device
         static std::atomic<bool> opted[MAX_DEVICES];
@@ -974,6 +1035,26 @@ int tc_slice_set() { return SLICE_SET_DEFAULT; }
 bool tc_supported(int S, int D, int in_dtype) {
     return S >= 1 && (D == 64 || D == 128 || D == 256) &&
            (in_dtype == MLSTM_DT_F16 || in_dtype == MLSTM_DT_BF16 || in_dtype == MLSTM_DT_F32);
+}
+
+bool tc_x3_supported(int S, int D) { return S >= 1 && (D == 64 || D == 128); }
+
+// fp32 problem on the tensor cores with split operands: p.X, p.Y, p.Z point to the bf16 hi | mid copies
+// ([BH, S, 2 D]); everything else (outputs, dot_src, ogate) is fp32.
+int launch_pass_tc_x3(int mode, const PassParams& p, cudaStream_t st) {
+    if (!tc_x3_supported(p.S, p.D)) return MLSTM_E_UNSUPPORTED;
+#define X3_CASE(M)                                                                             \
+    case M:                                                                                    \
+        return p.D == 64 ? launch_one<M, 64, 1, float, true>(p, MLSTM_DT_BF16, st)            \
+                         : launch_one<M, 128, 1, float, true>(p, MLSTM_DT_BF16, st);
+    switch (mode) {
+        X3_CASE(FWD)
+        X3_CASE(DQ)
+        X3_CASE(DK)
+        X3_CASE(DV)
+    }
+#undef X3_CASE
+    return MLSTM_E_ARG;
 }
 
 int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) {

@@ -11,20 +11,34 @@ q, k, v: [B, NH, S, D]; f, i: [B, NH, S]; CUDA, contiguous, float32 / float16 / 
 the inputs' type (:389-393).  ``SB`` and ``num_warps`` are the reference's tiling hints: they are
 checked (positive integers) and otherwise ignored, the kernels pick their own tiles.
 
-float32 inputs are computed with IEEE fp32 dot products, like the reference's
-``tl.dot(..., allow_tf32=False)`` (mlstm_matmul.py:19).  Setting the environment variable
-``MLSTM_B200_TF32=1`` (or passing ``flags=_lib.F_ALLOW_TF32`` to the two plain functions) lets them
-use the tensor cores with tf32 operands instead (D in {64, 128, 256}; error about 5e-4).
+float32 inputs keep fp32-level accuracy, like the reference's ``tl.dot(..., allow_tf32=False)``
+(mlstm_matmul.py:19): at D = 64 and 128 they run on the tensor cores with every operand split into two
+bf16 halves and three products per fp32 product (error about 1e-5); at other head dimensions with IEEE
+fp32 dot products on the CUDA cores.  Setting the environment variable ``MLSTM_B200_TF32=1`` (or passing
+``flags=_lib.F_ALLOW_TF32`` to the two plain functions) trades accuracy for speed: single tf32 products
+(D in {64, 128, 256}; error about 5e-4).  ``fp32_math_mode(D)`` says which of these a call will use.
 """
 import os
 import torch
 
 from . import _lib
 
-__all__ = ["Triton_mLSTM", "mlstm_matmul", "mlstm_matmul_forward", "mlstm_matmul_backward"]
+__all__ = ["Triton_mLSTM", "mlstm_matmul", "mlstm_matmul_forward", "mlstm_matmul_backward", "fp32_math_mode"]
 
 
 _DEFAULT_FLAGS = _lib.F_ALLOW_TF32 if os.environ.get("MLSTM_B200_TF32", "0") not in ("", "0") else 0
+
+
+def fp32_math_mode(D, flags=None):
+    """The arithmetic float32 inputs get at head dimension D with the given flags (default: the module's)."""
+    flags = _DEFAULT_FLAGS if flags is None else flags
+    if flags & _lib.F_FORCE_SIMT:
+        return "IEEE fp32 FMA on the CUDA cores"
+    if (flags & _lib.F_ALLOW_TF32) and D in (64, 128, 256):
+        return "single tf32 products on the tensor cores, fp32 accumulate"
+    if not (flags & _lib.F_NO_SPLIT) and D in (64, 128):
+        return "split bf16 products (hi*hi + hi*mid + mid*hi) on the tensor cores, fp32 accumulate"
+    return "IEEE fp32 FMA on the CUDA cores"
 
 
 def _check_hints(SB, num_warps):
