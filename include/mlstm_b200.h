@@ -175,6 +175,22 @@ int mlstm_chunk_apply(const void* q, const void* k, const void* v, const void* o
                       void* h, int h_dtype, float* S_out, float* z_out, void* workspace, size_t workspace_bytes, int B,
                       int NH, int S, int D, int dtype, int chunk, void* stream);
 
+/* Backward of the chunkwise forward, in time linear in S (the reference's scan is forward only, README.md:97;
+ * the gradient formulas are those of mlstm_matmul.py:336-365 split into the part inside a block and the part
+ * carried across blocks).  For a segment processed with no inbound state.
+ *   mlstm_chunk_read_mb   after mlstm_chunk_apply: copies the stabiliser m and the row sums b [B,NH,S] fp32 out
+ *                         of the workspace (what the parallel forward returns as M and B)
+ *   mlstm_chunk_bwd       dh, h of `h_dtype` (fp32 or the input type); q, k, v, f, i and dq, dk, dv, df, di of
+ *                         `dtype`; m, b as read above.  Its workspace is its own (mlstm_chunk_bwd_workspace);
+ *                         the gates and block states are recomputed in it.  df[..., 0] is exactly 0. */
+int mlstm_chunk_read_mb(const void* workspace, size_t workspace_bytes, float* m, float* b, int B, int NH, int S, int D,
+                        int dtype, int chunk, void* stream);
+size_t mlstm_chunk_bwd_workspace(int B, int NH, int S, int D, int dtype, int h_dtype, int chunk);
+int mlstm_chunk_bwd(const void* dh, const void* q, const void* k, const void* v, const void* f, const void* i,
+                    const void* h, const float* m, const float* b, void* dq, void* dk, void* dv, void* df, void* di,
+                    void* workspace, size_t workspace_bytes, int B, int NH, int S, int D, int dtype, int h_dtype,
+                    int chunk, void* stream);
+
 /* Sequence-parallel form of the chunkwise forward: rank r of `world` holds the r-th contiguous segment
  * of every sequence, and ONE exchange connects the ranks (the carry combine of mlstm_scan.py:15-26
  * applied to whole segments; SURVEY of the reference: no multi-GPU code exists there).

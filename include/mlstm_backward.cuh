@@ -11,7 +11,7 @@
 // inside the call, so there is nothing for the host to precompute.  dH, Q, K, V, dQ, dK, dV: [S, D_DIM]
 // half; F, I, dF, dI: [S] half; device pointers owned by the caller; default stream unless one is given.
 // The tile parameters are kept for source compatibility and checked for plausibility only.  Returns an
-// MLSTM_* status.  Scratch memory: one grow-only device buffer per host thread, as in mlstm_forward.cuh;
+// MLSTM_* status.  Scratch memory: one grow-only device buffer per host thread and device, as in mlstm_forward.cuh;
 // callers that manage memory themselves use mlstm_backward_f16() from mlstm_b200.h.
 // Link with libmlstm_b200.so.
 #pragma once
@@ -29,7 +29,7 @@ inline int mlstm_backward(const half* dH, const half* Q, const half* K, const ha
     static_assert(D_DIM % 8 == 0, "head dimension must be a multiple of 8");
     const size_t bytes = mlstm_backward_f16_workspace(S_DIM, D_DIM);
     if (bytes == 0) return MLSTM_E_SHAPE;
-    void* ws = mlstm_driver_detail::scratch(bytes);
+    void* ws = mlstm_driver_detail::scratch(bytes, stream);
     if (!ws) return MLSTM_E_CUDA;
     return mlstm_backward_f16(dH, Q, K, V, F, I, dQ, dK, dV, dF, dI, S_DIM, D_DIM, ws, bytes, stream);
 }

@@ -13,8 +13,13 @@
 // nothing and reported errors through CUDA_CHECK, cuda-src/cpu_utils.cuh:10-27).
 //
 // The kernels need a little scratch memory.  This header keeps one grow-only device buffer per host
-// thread for it (allocated with cudaMalloc on first use or growth, never freed before exit); callers
-// that manage memory themselves call mlstm_forward_f16() from mlstm_b200.h with their own workspace.
+// thread AND device for it: allocated with cudaMalloc on first use on that device, replaced by a larger
+// one when a longer sequence comes (the smaller buffer is released with cudaFreeAsync on the stream that
+// last used it, i.e. after the work queued there), never touched otherwise.  The current device must be
+// the one that owns `stream`.  mlstm_driver_scratch_status() reads the status word of the calling
+// thread's buffer on the current device (0 = no kernel gave up on a wait).  Callers that manage memory
+// themselves call mlstm_forward_f16() from mlstm_b200.h with their own workspace, and callers that must
+// not allocate at all mlstm_forward_f16_static().
 // Link with libmlstm_b200.so.
 #pragma once
 #include <cuda_fp16.h>
@@ -23,22 +28,43 @@
 #include "mlstm_b200.h"
 
 namespace mlstm_driver_detail {
-inline void* scratch(size_t bytes) {
-    thread_local void* buf = nullptr;
-    thread_local size_t cap = 0;
-    thread_local int dev_of_buf = -1;
+constexpr int MAX_DEVICES = 64;
+struct Scratch {
+    void* buf = nullptr;
+    size_t cap = 0;
+    cudaStream_t last_stream = 0;
+};
+inline Scratch* slots() {
+    thread_local Scratch per_device[MAX_DEVICES];
+    return per_device;
+}
+inline void* scratch(size_t bytes, cudaStream_t stream) {
     int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
-    if (bytes > cap || dev != dev_of_buf) {
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
+    Scratch& s = slots()[dev];
+    if (bytes > s.cap) {
         void* p = nullptr;
         if (cudaMalloc(&p, bytes) != cudaSuccess) return nullptr;
-        buf = p;  // the previous buffer may still be in use by queued work: it is left to process exit
-        cap = bytes;
-        dev_of_buf = dev;
+        if (s.buf) cudaFreeAsync(s.buf, s.last_stream);   // ordered after the work that last used it
+        s.buf = p;
+        s.cap = bytes;
     }
-    return buf;
+    s.last_stream = stream;
+    return s.buf;
 }
 }  // namespace mlstm_driver_detail
+
+// Status word of this thread's scratch buffer on the current device (synchronises `stream`).
+inline int mlstm_driver_scratch_status(int* host_status, cudaStream_t stream = 0) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= mlstm_driver_detail::MAX_DEVICES) return MLSTM_E_CUDA;
+    void* buf = mlstm_driver_detail::slots()[dev].buf;
+    if (!buf) {
+        *host_status = 0;
+        return MLSTM_OK;
+    }
+    return mlstm_read_status(buf, host_status, stream);
+}
 
 template <unsigned BS_DIM, unsigned WS_DIM, unsigned D_DIM, unsigned MMA_M_DIM, unsigned MMA_N_DIM, unsigned MMA_K_DIM>
 inline int mlstm_forward(const half* Q, const half* K, const half* V, const half* F, const half* I, half* H,
@@ -48,7 +74,7 @@ inline int mlstm_forward(const half* Q, const half* K, const half* V, const half
     static_assert(D_DIM % 8 == 0, "head dimension must be a multiple of 8");
     const size_t bytes = mlstm_forward_f16_workspace(S_DIM, D_DIM);
     if (bytes == 0) return MLSTM_E_SHAPE;
-    void* ws = mlstm_driver_detail::scratch(bytes);
+    void* ws = mlstm_driver_detail::scratch(bytes, stream);
     if (!ws) return MLSTM_E_CUDA;
     return mlstm_forward_f16(Q, K, V, F, I, H, S_DIM, D_DIM, ws, bytes, stream);
 }

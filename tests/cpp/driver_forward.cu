@@ -47,6 +47,11 @@ int main(int argc, char** argv) {
     const int rc = mlstm_forward<BS_DIM, WS_DIM, D, MMA_M_DIM, MMA_N_DIM, MMA_K_DIM>(dQ, dK, dV, dF, dI, dH, S);
     if (rc != MLSTM_OK) { printf("launch failed: %s\n", mlstm_status_string(rc)); return 4; }
     if (cudaDeviceSynchronize() != cudaSuccess) { printf("kernel failed: %s\n", cudaGetErrorString(cudaGetLastError())); return 5; }
+    int code = -1;   // a kernel that gave up on an internal wait leaves its code in the scratch buffer's status word
+    if (mlstm_driver_scratch_status(&code) != MLSTM_OK) { printf("kernel status %d\n", code); return 6; }
+    // a longer and then a shorter call on the same thread: the header's scratch grows once and is reused
+    if (mlstm_forward<BS_DIM, WS_DIM, D, MMA_M_DIM, MMA_N_DIM, MMA_K_DIM>(dQ, dK, dV, dF, dI, dH, S) != MLSTM_OK) return 7;
+    if (cudaDeviceSynchronize() != cudaSuccess) return 8;
     cudaMemcpy(H.data(), dH, mat, cudaMemcpyDeviceToHost);
 
     unsigned count = 0;

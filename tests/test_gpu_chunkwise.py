@@ -127,6 +127,52 @@ def test_long_context_configuration_at_its_own_size(gc):
         assert err < TOL_16, (lo, err)
 
 
+@pytest.mark.parametrize("dtype,S,chunk,f_mean", [
+    (torch.bfloat16, 1024, 256, 3.0),
+    (torch.bfloat16, 1000, 256, 0.0),     # ragged last block
+    (torch.float16, 768, 128, 1.0),
+    (torch.bfloat16, 256, 256, 0.0),      # a single block: nothing is carried
+    (torch.bfloat16, 2304, 512, -1.0),    # strong decay, four-tile blocks and a ragged last one
+])
+def test_chunkwise_backward_against_oracle(gc, dtype, S, chunk, f_mean):
+    """Chunkwise forward + chunkwise backward (states carried forward for dQ, back for dK and dV) against the
+    closed-form backward of the parallel oracle, and against the parallel backward kernels on the device."""
+    x = gc.make_inputs(1, 2, S, 128, dtype, f_mean=f_mean, qkv_scale=128 ** -0.5, seed=S + chunk + 1)
+    names = ("q", "k", "v", "f", "i")
+    t = {n: x[n].cuda().requires_grad_(True) for n in names}
+    h = gc.PKG.mlstm_chunkwise(*(t[n] for n in names), chunk_size=chunk)
+    h.backward(x["dh"].cuda())
+    torch.cuda.synchronize()
+    ref = gc.oracle_backward(x, torch.float32)
+    for n, r in zip(names, ref):
+        g = t[n].grad
+        assert g.dtype == dtype and bool(torch.isfinite(g.float()).all()), n
+        assert orc.max_abs_rel(g.float(), r) < TOL_16, (n, orc.max_abs_rel(g.float(), r))
+    assert float(t["f"].grad[..., 0].abs().max()) == 0.0
+    # the quadratic kernels on the same h, m, b
+    d = [x[n].cuda() for n in names]
+    hq, m, b = gc.PKG.mlstm_matmul_forward(*d)
+    gq = gc.PKG.mlstm_matmul_backward(x["dh"].cuda(), *d, hq, m, b)
+    for n, a in zip(names, gq):
+        assert orc.max_abs_rel(t[n].grad.float(), a.float()) < TOL_16, n
+
+
+def test_scan_gradients_take_the_chunkwise_backward(gc):
+    """mlstm_scan on a long 16-bit sequence with inputs that require gradients: chunkwise forward and backward
+    behind the output gate, against autograd of the fp64 oracle."""
+    x = gc.make_inputs(1, 2, 1536, 128, torch.bfloat16, f_mean=2.0, qkv_scale=128 ** -0.5, seed=77, with_o=True)
+    names = ("q", "k", "v", "f", "i", "o")
+    t = {n: x[n].cuda().requires_grad_(True) for n in names}
+    h = gc.PKG.mlstm_scan(*(t[n] for n in names))
+    h.backward(x["dh"].cuda())
+    r = {n: x[n].double().requires_grad_(True) for n in names}
+    href = orc.matmul_forward(r["q"], r["k"], r["v"], r["f"], r["i"]) * torch.nn.functional.silu(r["o"])
+    href.backward(x["dh"].double())
+    assert orc.max_abs_rel(h.detach(), href.detach()) < TOL_16
+    for n in names:
+        assert orc.max_abs_rel(t[n].grad.float(), r[n].grad) < TOL_16, n
+
+
 def test_chunkwise_rejects_unsupported_cases(gc):
     x = gc.make_inputs(1, 1, 256, 64, torch.bfloat16)
     with pytest.raises(gc._lib.MlstmError):

@@ -84,6 +84,12 @@ def lib():
     L.mlstm_chunk_sp_local.argtypes = [vp] * 5 + [vp, sz] + [i32] * 6 + [vp]
     L.mlstm_chunk_sp_apply.restype = i32
     L.mlstm_chunk_sp_apply.argtypes = [vp] * 5 + [i32, i32, vp, i32, vp, vp, sz] + [i32] * 6 + [vp]
+    L.mlstm_chunk_read_mb.restype = i32
+    L.mlstm_chunk_read_mb.argtypes = [vp, sz, vp, vp] + [i32] * 6 + [vp]
+    L.mlstm_chunk_bwd_workspace.restype = sz
+    L.mlstm_chunk_bwd_workspace.argtypes = [i32] * 7
+    L.mlstm_chunk_bwd.restype = i32
+    L.mlstm_chunk_bwd.argtypes = [vp] * 14 + [vp, sz] + [i32] * 7 + [vp]
     L.mlstm_forward_f16_static_status.restype = i32
     L.mlstm_forward_f16_static_status.argtypes = [ctypes.POINTER(i32), vp]
     L.mlstm_ogate_fwd.restype = i32
@@ -105,6 +111,7 @@ EXPORTS = [
     "mlstm_backward_f16", "mlstm_read_status",
     "mlstm_chunk_workspace", "mlstm_chunk_gate_summary", "mlstm_chunk_prepare", "mlstm_chunk_local_state",
     "mlstm_chunk_apply", "mlstm_chunk_sp_record_floats", "mlstm_chunk_sp_local", "mlstm_chunk_sp_apply",
+    "mlstm_chunk_read_mb", "mlstm_chunk_bwd_workspace", "mlstm_chunk_bwd",
     "mlstm_forward_f16_static_status", "mlstm_selftest_wait_timeout", "mlstm_ogate_fwd", "mlstm_ogate_bwd",
 ]
 

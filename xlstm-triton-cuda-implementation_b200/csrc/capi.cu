@@ -363,7 +363,7 @@ int mlstm_scan_fwd(const void* q, const void* k, const void* v, const void* f, c
         ScanGemmArgs a{};
         a.S = S; a.Spad = Spad; a.BH = BH; a.D = D;
         a.ga = w.ga; a.gAn = w.gAn; a.gaw = w.gaw; a.a_ref = w.a_ref; a.An_ref = w.An_ref; a.m = w.m;
-        a.bpart = bpart; a.status = w.status; a.counters = w.status + 8 + 6;
+        a.bpart = bpart; a.status = w.status; a.counters = w.status + 8 + 12;
         return launch_scan_gemm(q, k, v, o, static_cast<float*>(h), W, a, dtype, st);
     }
     if ((flags & MLSTM_F_FORCE_TC) && D > 256) return MLSTM_E_UNSUPPORTED;

@@ -32,6 +32,10 @@ __global__ void identity_kernel(T16* ident) {
 // late_bound (optional, per slice): a carry that became known after the gate pass, see PassParams;
 // block contributions U_k were stabilised by the local block-end maximum and are rescaled to the
 // later, larger one on the way in.
+// statesT (optional): the same per-block matrices transposed ([value, key]), for passes whose state step
+// contracts over the value dimension.  reverse: walk the blocks from the last to the first, which turns
+// the same recurrence into the backward's carried state R_{k-1} = exp(A_end(k-1) - A_end(k)) R_k + P_k
+// (block k then receives what the LATER blocks contribute).
 template <typename T16>
 __global__ void state_scan_kernel(const float* __restrict__ U, const float* __restrict__ zU,
                                   const double* __restrict__ An_bound, const float* __restrict__ S_in,
@@ -39,7 +43,7 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
                                   float* __restrict__ S_end, float* __restrict__ z_end, size_t S_end_stride,
                                   size_t z_end_stride, int NB, int D, const double* __restrict__ late_bound,
                                   const double* __restrict__ summary, double* __restrict__ summary_dst,
-                                  size_t summary_dst_stride) {
+                                  size_t summary_dst_stride, T16* __restrict__ statesT, int reverse) {
     const int bh = blockIdx.y;
     const int DD = D * D;
     const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
@@ -65,8 +69,9 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
 #pragma unroll
         for (int j = 0; j < PF; j++) {
             if (k0 + j < NB) {
-                u[j] = __ldg(reinterpret_cast<const float4*>(src + static_cast<size_t>(k0 + j) * per_block));
-                const double b1 = bound[k0 + j + 1], b0 = bound[k0 + j];
+                const int kb = reverse ? NB - 1 - (k0 + j) : k0 + j;
+                u[j] = __ldg(reinterpret_cast<const float4*>(src + static_cast<size_t>(kb) * per_block));
+                const double b1 = bound[kb + 1], b0 = bound[kb];
                 const double b1c = fmin(b1, lb), b0c = fmin(b0, lb);
                 // exp(A_end(k-1) - A_end(k)); 0 for the first block when there is no inbound carry (bound = +inf)
                 d[j] = exp2f(static_cast<float>(b1c - b0c));
@@ -75,13 +80,19 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
         }
 #pragma unroll
         for (int j = 0; j < PF; j++) {
-            const int k = k0 + j;
-            if (k >= NB) break;
+            if (k0 + j >= NB) break;
+            const int k = reverse ? NB - 1 - (k0 + j) : k0 + j;
             if (is_vec) {
                 if (zstate) *reinterpret_cast<float4*>(zstate + (static_cast<size_t>(bh) * NB + k) * D + off) = s;
-            } else if (states) {
+            } else if (states || statesT) {
                 T16 o[4] = {from_f32<T16>(s.x), from_f32<T16>(s.y), from_f32<T16>(s.z), from_f32<T16>(s.w)};
-                *reinterpret_cast<uint2*>(states + (static_cast<size_t>(bh) * NB + k) * DD + off) = *reinterpret_cast<uint2*>(o);
+                if (states)
+                    *reinterpret_cast<uint2*>(states + (static_cast<size_t>(bh) * NB + k) * DD + off) = *reinterpret_cast<uint2*>(o);
+                if (statesT) {
+                    const int row = off / D, col = off - row * D;
+                    T16* dstT = statesT + (static_cast<size_t>(bh) * NB + k) * DD + static_cast<size_t>(col) * D + row;
+                    dstT[0] = o[0]; dstT[D] = o[1]; dstT[2 * D] = o[2]; dstT[3 * D] = o[3];
+                }
             }
             s.x = (d[j] == 0.0f ? 0.0f : d[j] * s.x) + c[j] * u[j].x;
             s.y = (d[j] == 0.0f ? 0.0f : d[j] * s.y) + c[j] * u[j].y;
@@ -92,6 +103,28 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
     float* dst = is_vec ? z_end : S_end;
     const size_t stride = is_vec ? z_end_stride : S_end_stride;
     if (dst) *reinterpret_cast<float4*>(dst + static_cast<size_t>(bh) * stride + off) = s;
+}
+
+// Vector part of what block k contributes to the backward's carried state:
+//   p_k[d] = sum_{t in block k} beta_t g_t q_t[d],  beta_t = exp(A_end(k-1) - A_t) scale / n_t,  g_t = db_t n_t
+// (the matrix part sum_t beta_t q_t dh_t^T comes from the tensor-core STATE pass).  One block of D threads per
+// (block, slice); log2 beta_t = gB_rel[t] + An_ref[t / 64] - bound[k] with the vectors of the backward preparation.
+template <typename T16>
+__global__ void rvec_partial_kernel(const T16* __restrict__ q, const float* __restrict__ gB_rel,
+                                    const double* __restrict__ An_ref, const double* __restrict__ An_bound,
+                                    const float* __restrict__ g, float* __restrict__ out, int S, int Spad, int NB, int chunk,
+                                    int D) {
+    const int k = blockIdx.x, bh = blockIdx.y, d = threadIdx.x;
+    const double b0 = An_bound[static_cast<size_t>(bh) * (NB + 1) + k];
+    const int t0 = k * chunk, t1 = min(t0 + chunk, S);
+    float acc = 0.0f;
+    for (int t = t0; t < t1; t++) {
+        const size_t vi = static_cast<size_t>(bh) * Spad + t;
+        const float e = gB_rel[vi] + static_cast<float>(An_ref[static_cast<size_t>(bh) * (Spad / REF_BLOCK) + t / REF_BLOCK] - b0);
+        const float w = exp2f(e) * g[vi];   // exp2(-inf) = 0 for the first block when nothing is carried in
+        acc = fmaf(w, to_f32<T16>(q[(static_cast<size_t>(bh) * S + t) * D + d]), acc);
+    }
+    out[(static_cast<size_t>(bh) * NB + k) * D + d] = acc;
 }
 
 // Sequence-parallel fold: from the gathered records of all segments (per slice: S | z | {F_end, A_end},
@@ -220,7 +253,8 @@ int launch_identity(void* ident, int dtype, cudaStream_t st) {
 
 int launch_state_scan(const float* U, const float* zU, const double* An_bound, const float* S_in, const float* z_in,
                       void* states16, float* zstate, float* S_end, float* z_end, int BH, int NB, int D, int dtype,
-                      cudaStream_t st, const double* late_bound, float* rec, size_t rec_stride, const double* summary) {
+                      cudaStream_t st, const double* late_bound, float* rec, size_t rec_stride, const double* summary,
+                      void* statesT16, int reverse) {
     const int threads = 256;
     const int work = (D * D + D) / 4;
     dim3 grid((work + threads - 1) / threads, BH);
@@ -236,11 +270,13 @@ int launch_state_scan(const float* U, const float* zU, const double* An_bound, c
         state_scan_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(U, zU, An_bound, S_in, z_in,
                                                                    static_cast<__nv_bfloat16*>(states16), zstate, S_end,
                                                                    z_end, s_stride, z_stride, NB, D, late_bound, summary,
-                                                                   sum_dst, rec_stride);
+                                                                   sum_dst, rec_stride, static_cast<__nv_bfloat16*>(statesT16),
+                                                                   reverse);
     else
         state_scan_kernel<__half><<<grid, threads, 0, st>>>(U, zU, An_bound, S_in, z_in, static_cast<__half*>(states16),
                                                             zstate, S_end, z_end, s_stride, z_stride, NB, D, late_bound,
-                                                            summary, sum_dst, rec_stride);
+                                                            summary, sum_dst, rec_stride, static_cast<__half*>(statesT16),
+                                                            reverse);
     return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
@@ -326,6 +362,143 @@ int mlstm_chunk_apply(const void* q, const void* k, const void* v, const void* o
                                 st)) != MLSTM_OK)
         return rc;
     return launch_fwdc(q, k, v, o, h, h_dtype, w, BH, S, Spad, D, dtype, chunk, nullptr, st);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Backward of the chunkwise forward (no inbound state): dq, dk, dv, df, di in time linear in S.
+// Within a block the three parallel backward passes run restricted to the block (modes DQC, DKC, DVC of
+// the tensor-core pass); across blocks dQ uses the forward's inbound state S_k, and dK, dV use a state
+// carried BACK over the blocks,
+//   R_k = sum_{t after block k} exp(A_end(k) - A_t) (scale / n_t) q_t dh_t^T   (+ the vector r_k with g_t q_t),
+// built like the forward states: per-block contributions from one STATE pass (Y = Q, Z = dH, column
+// weights from the backward preparation), then the block recurrence walked in reverse.  dI and the row
+// sums behind dF are row dots of the complete fp32 accumulators, as in the parallel backward
+// (mlstm_matmul.py:256-316, 319-333 give the quantities; the reference has no chunkwise backward).
+struct ChunkBwdWs {
+    ChunkWs f;
+    float *gB, *gBw, *g, *dI, *Rdot, *rvec;
+    void *dh16, *statesT, *statesT2;
+    size_t bytes;
+};
+static ChunkBwdWs carve_bwd_chunk(void* ws, int BH, int S, int D, int chunk, bool need_dh16) {
+    ChunkBwdWs w{};
+    w.f = carve(ws, BH, S, D, chunk);
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    size_t off = w.f.bytes;
+    auto take = [&](size_t bytes) {
+        void* p = base ? base + off : nullptr;
+        off += al(bytes);
+        return p;
+    };
+    const size_t vec = static_cast<size_t>(BH) * round_up(S, TILE) * sizeof(float);
+    const size_t nblk = static_cast<size_t>(BH) * w.f.NB;
+    w.gB = static_cast<float*>(take(vec));
+    w.gBw = static_cast<float*>(take(vec));
+    w.g = static_cast<float*>(take(vec));
+    w.dI = static_cast<float*>(take(vec));
+    w.Rdot = static_cast<float*>(take(vec));
+    w.rvec = static_cast<float*>(take(nblk * D * sizeof(float)));
+    w.statesT = take(nblk * D * D * 2);
+    w.statesT2 = take(nblk * D * D * 2);
+    w.dh16 = need_dh16 ? take(static_cast<size_t>(BH) * S * D * 2) : nullptr;
+    w.bytes = off;
+    return w;
+}
+
+size_t mlstm_chunk_bwd_workspace(int B, int NH, int S, int D, int dtype, int h_dtype, int chunk) {
+    if (check_chunk_args(B, NH, S, D, dtype, chunk) != MLSTM_OK) return 0;
+    return carve_bwd_chunk(nullptr, B * NH, S, D, chunk, h_dtype != dtype).bytes;
+}
+
+int mlstm_chunk_bwd(const void* dh, const void* q, const void* k, const void* v, const void* f, const void* i, const void* h,
+                    const float* m, const float* b, void* dq, void* dk, void* dv, void* df, void* di, void* workspace,
+                    size_t workspace_bytes, int B, int NH, int S, int D, int dtype, int h_dtype, int chunk, void* stream) {
+    if (!dh || !q || !k || !v || !f || !i || !h || !m || !b || !dq || !dk || !dv || !df || !di) return MLSTM_E_ARG;
+    int rc = check_chunk_args(B, NH, S, D, dtype, chunk);
+    if (rc != MLSTM_OK) return rc;
+    if (h_dtype != MLSTM_DT_F32 && h_dtype != dtype) return MLSTM_E_ARG;
+    if (!aligned16(dh) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(h) || !aligned16(dq) ||
+        !aligned16(dk) || !aligned16(dv))
+        return MLSTM_E_ALIGN;
+    const int BH = B * NH, Spad = round_up(S, TILE);
+    const bool need16 = h_dtype != dtype;
+    ChunkBwdWs w = carve_bwd_chunk(workspace, BH, S, D, chunk, need16);
+    if (!workspace || workspace_bytes < w.bytes || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const ChunkWs& c = w.f;
+    if (cudaMemsetAsync(c.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
+    // gates and forward states, as in the forward
+    if ((rc = launch_gates_fwd(f, i, c.ga, c.gAn, c.a_ref, c.An_ref, nullptr, BH, S, Spad, dtype, st, nullptr, nullptr,
+                               c.An_bound, chunk, c.gscratch, c.gaw)) != MLSTM_OK)
+        return rc;
+    if ((rc = launch_identity(c.ident, dtype, st)) != MLSTM_OK) return rc;
+    PassParams p{};
+    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = c.status; p.sched = c.status + 8;
+    p.chunk_tiles = chunk / TILE; p.NB = c.NB; p.An_bound = c.An_bound; p.ident = c.ident;
+    p.X = k; p.Y = k; p.Z = v;
+    p.col_rel = c.ga; p.col_w = c.gaw; p.col_ref = c.a_ref; p.row_rel = c.gAn; p.row_ref = c.An_ref;
+    p.out = c.U; p.b_out = c.zU;
+    if ((rc = launch_pass_tc(STATE, p, dtype, MLSTM_DT_F32, st)) != MLSTM_OK) return rc;
+    // inbound states of the blocks, transposed (dQ's state step contracts over the value dimension), and z
+    if ((rc = launch_state_scan(c.U, c.zU, c.An_bound, nullptr, nullptr, nullptr, c.zstate, nullptr, nullptr, BH, c.NB, D,
+                                dtype, st, nullptr, nullptr, 0, nullptr, w.statesT, 0)) != MLSTM_OK)
+        return rc;
+    // delta = dh . h, n, db -> the backward's per-row vectors (and dh in the input type)
+    if ((rc = launch_bwd_prep(h, dh, b, m, c.gAn, w.gB, w.gBw, w.g, w.dh16, BH, S, Spad, D, h_dtype, dtype, st)) != MLSTM_OK)
+        return rc;
+    const void* dhp = need16 ? w.dh16 : dh;
+    // what every block contributes to the state carried back: P_k = sum_t beta_t q_t dh_t^T (tensor cores), p_k (vector)
+    p.X = q; p.Y = q; p.Z = dhp;
+    p.col_rel = w.gB; p.col_w = w.gBw; p.col_ref = c.An_ref;
+    p.out = c.U; p.b_out = nullptr; p.state_reverse = 1;
+    if ((rc = launch_pass_tc(STATE, p, dtype, MLSTM_DT_F32, st)) != MLSTM_OK) return rc;
+    p.state_reverse = 0;
+    {
+        dim3 grid(c.NB, BH);
+        if (dtype == MLSTM_DT_BF16)
+            rvec_partial_kernel<__nv_bfloat16><<<grid, D, 0, st>>>(static_cast<const __nv_bfloat16*>(q), w.gB, c.An_ref, c.An_bound,
+                                                                  w.g, c.zU, S, Spad, c.NB, chunk, D);
+        else
+            rvec_partial_kernel<__half><<<grid, D, 0, st>>>(static_cast<const __half*>(q), w.gB, c.An_ref, c.An_bound, w.g, c.zU,
+                                                           S, Spad, c.NB, chunk, D);
+        if (cudaGetLastError() != cudaSuccess) return MLSTM_E_CUDA;
+    }
+    // the block recurrence in reverse: R_k [key, value] (for dV), its transpose (for dK) and r_k
+    if ((rc = launch_state_scan(c.U, c.zU, c.An_bound, nullptr, nullptr, c.states, w.rvec, nullptr, nullptr, BH, c.NB, D,
+                                dtype, st, nullptr, nullptr, 0, nullptr, w.statesT2, 1)) != MLSTM_OK)
+        return rc;
+    // dQ = ((dH V^T + g_r) * decay) K within the block, + beta (S_k dh + g z_k) from the inbound state
+    p.X = dhp; p.Y = v; p.Z = k;
+    p.row_rel = w.gB; p.row_ref = c.An_ref; p.row_g = w.g; p.col_rel = c.ga; p.col_w = c.gaw; p.col_ref = c.a_ref; p.col_g = nullptr;
+    p.states = w.statesT; p.zstate = c.zstate;
+    p.out = dq; p.dot_src = q; p.dot_out = w.Rdot;
+    if ((rc = launch_pass_tc(DQC, p, dtype, dtype, st)) != MLSTM_OK) return rc;
+    // dK = ((V dH^T + g_c) * decay) Q within the block, + gamma (R_k v + r_k) from the later blocks
+    p.X = v; p.Y = dhp; p.Z = q;
+    p.row_rel = c.ga; p.row_ref = c.a_ref; p.row_g = nullptr; p.col_rel = w.gB; p.col_w = w.gBw; p.col_ref = c.An_ref; p.col_g = w.g;
+    p.states = w.statesT2; p.rvec = w.rvec;
+    p.out = dk; p.dot_src = k; p.dot_out = w.dI;
+    if ((rc = launch_pass_tc(DKC, p, dtype, dtype, st)) != MLSTM_OK) return rc;
+    // dV = ((K Q^T) * decay / n) dH within the block, + gamma R_k^T k from the later blocks
+    p.X = k; p.Y = q; p.Z = dhp;
+    p.col_g = nullptr; p.states = c.states;
+    p.out = dv; p.dot_src = nullptr; p.dot_out = nullptr;
+    if ((rc = launch_pass_tc(DVC, p, dtype, dtype, st)) != MLSTM_OK) return rc;
+    return launch_df(f, w.dI, w.Rdot, df, di, BH, S, Spad, dtype, st);
+}
+
+int mlstm_chunk_read_mb(const void* workspace, size_t workspace_bytes, float* m, float* b, int B, int NH, int S, int D, int dtype,
+                        int chunk, void* stream) {
+    if (!m || !b) return MLSTM_E_ARG;
+    int rc = check_chunk_args(B, NH, S, D, dtype, chunk);
+    if (rc != MLSTM_OK) return rc;
+    ChunkWs w = carve(const_cast<void*>(workspace), B * NH, S, D, chunk);
+    if (!workspace || workspace_bytes < w.bytes) return MLSTM_E_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t bytes = static_cast<size_t>(B) * NH * S * sizeof(float);
+    if (cudaMemcpyAsync(m, w.m, bytes, cudaMemcpyDeviceToDevice, st) != cudaSuccess) return MLSTM_E_CUDA;
+    if (cudaMemcpyAsync(b, w.b, bytes, cudaMemcpyDeviceToDevice, st) != cudaSuccess) return MLSTM_E_CUDA;
+    return MLSTM_OK;
 }
 
 size_t mlstm_chunk_sp_record_floats(int D) { return D > 0 ? static_cast<size_t>(D) * D + D + 4 : 0; }

@@ -34,7 +34,10 @@ namespace mlstm {
 // `chunk_tiles` tiles, U = sum_j w_j k_j v_j^T (rows = key dimensions, X = identity, Y = K, Z = V);
 // FWDC is FWD restricted to the query's own block plus one step that applies the block's inbound
 // state (Y = identity, Z = state), so T = Q and W = Q scaled per row.
-enum Mode : int { FWD = 0, DQ = 1, DK = 2, DV = 3, FWDC = 4, STATE = 5 };
+// DQC, DKC, DVC are the backward passes of the chunkwise form: DQ / DK / DV restricted to the row tile's own
+// block plus one step that applies a carried state (the inbound state S_k for dQ; for dK and dV the state
+// R_k = sum over later positions t of exp(A_end(k) - A_t) (scale / n_t) q_t dh_t^T carried BACK over the blocks).
+enum Mode : int { FWD = 0, DQ = 1, DK = 2, DV = 3, FWDC = 4, STATE = 5, DQC = 6, DKC = 7, DVC = 8 };
 
 constexpr int TILE = 128;      // rows of a tensor-core tile; gate vectors are padded to a multiple of it
 constexpr int REF_BLOCK = 64;  // positions per reference block of the re-centred gate vectors (gates.cu)
@@ -73,15 +76,18 @@ struct PassParams {
     int NB;                  // blocks per slice
     const double* An_bound;  // [BH, NB + 1]  -A*log2e at the block boundaries (entry 0: the inbound carry)
     const void* ident;       // [128, 128] identity in the input type
-    const void* states;      // FWDC: [BH, NB, D, D] inbound state of every block, input type
-    const float* zstate;     // FWDC: [BH, NB, D] inbound normaliser vector of every block
+    const void* states;      // FWDC and the chunkwise backward passes: [BH, NB, D, D] the state applied to every block
+                             // (input type; rows = the contraction index of the state step)
+    const float* zstate;     // FWDC, DQC: [BH, NB, D] inbound normaliser vector of every block
+    const float* rvec;       // DKC: [BH, NB, D] vector part of the state carried back from the later blocks
+    int state_reverse;       // STATE: rows carry +A_end(previous block) (contributions to the backward's carried state)
     // FWDC, optional: a carry that became known after the gate pass (sequence-parallel segments).
     // late_bound[bh] = -(A_in + F_in) * log2e, the inbound prefix maximum in this segment's own
     // coordinates; every stabiliser -A*log2e of the slice (rows, block boundaries) becomes
     // min(local value, late_bound[bh]) and m grows by the difference.  +inf = no carry.
     const double* late_bound;
     int* status;         // device word; a kernel that gave up on a wait stores a non-zero code
-    int* sched;          // tensor-core passes: 8 device words, one work-item counter per pass mode
+    int* sched;          // tensor-core passes: 12 device words, one work-item counter per pass mode
     int slice_set;       // tensor-core passes: slices interleaved in the work-item order (set by the launcher)
 };
 
@@ -115,7 +121,7 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)
 // DK/DV (column >= row is valid).
 template <int MODE>
 __device__ __forceinline__ bool causal_ok(int row, int col) {
-    return (MODE == FWD || MODE == DQ || MODE == FWDC) ? (col <= row) : (col >= row);
+    return (MODE == FWD || MODE == DQ || MODE == FWDC || MODE == DQC) ? (col <= row) : (col >= row);
 }
 
 // Remembers the last CUDA failure of this host thread for mlstm_last_error_detail(); returns MLSTM_E_CUDA.
@@ -134,7 +140,7 @@ int launch_identity(void* ident, int dtype, cudaStream_t st);
 int launch_state_scan(const float* U, const float* zU, const double* An_bound, const float* S_in, const float* z_in,
                       void* states16, float* zstate, float* S_end, float* z_end, int BH, int NB, int D, int dtype,
                       cudaStream_t st, const double* late_bound = nullptr, float* rec = nullptr, size_t rec_stride = 0,
-                      const double* summary = nullptr);
+                      const double* summary = nullptr, void* statesT16 = nullptr, int reverse = 0);
 int launch_bwd_prep(const void* h, const void* dh, const float* b, const float* m, const float* gAn, float* gB,
                     float* gBw, float* g, void* dh16, int BH, int S, int Spad, int D, int h_dtype, int dtype, cudaStream_t st);
 int launch_df(const void* f, const float* dI, const float* R, void* df, void* di, int BH, int S, int Spad, int dtype,

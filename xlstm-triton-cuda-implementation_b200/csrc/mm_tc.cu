@@ -121,9 +121,13 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     static_assert(!X3 || (ABFMT == 1 && (D == 64 || D == 128) && MODE <= DV), "the split form serves D = 64, 128 of the four parallel passes");
     constexpr int BPS = C::CH / 64;               // X3: 128-byte boxes per ring slot
     constexpr int NBX = D / 64;                   // X3: boxes per operand half
-    constexpr bool ROWS_ARE_Q = (MODE == FWD || MODE == DQ || MODE == FWDC);
+    constexpr bool ROWS_ARE_Q = (MODE == FWD || MODE == DQ || MODE == FWDC || MODE == DQC);
     constexpr bool IS_FWD = (MODE == FWD || MODE == FWDC);   // normalised output, row sums kept
-    static_assert((MODE != FWDC && MODE != STATE) || (D == 128 && ES == 2), "chunkwise passes are built for 16-bit D = 128");
+    constexpr bool IS_DQ = (MODE == DQ || MODE == DQC);
+    constexpr bool IS_DK = (MODE == DK || MODE == DKC);
+    // chunkwise passes: the row tile's own block plus one step that applies a carried state
+    constexpr bool CHUNKED = (MODE == FWDC || MODE == DQC || MODE == DKC || MODE == DVC);
+    static_assert((!CHUNKED && MODE != STATE) || (D == 128 && ES == 2), "chunkwise passes are built for 16-bit D = 128");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
@@ -183,22 +187,24 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         it.bh = set * SLICE_SET + (within - w * set_size);
         // tile: the stationary tile (STATE: the block).  nsteps / stream_tile: what is streamed.
         //   FWD, DQ   key tiles 0..tile, diagonal last          DK, DV  query tiles tile..NT-1, diagonal first
-        //   FWDC      step 0 applies the block's inbound state, then key tiles block_start..tile
+        //   FWDC, DQC step 0 applies the block's inbound state, then key tiles block_start..tile
+        //   DKC, DVC  step 0 applies the state carried back from the later blocks, then query tiles tile..block_end
         //   STATE     the block's tiles
         it.tile = (MODE == STATE) ? w : (ROWS_ARE_Q ? (NT - 1 - w) : w);
-        it.blk = (MODE == FWDC) ? it.tile / p.chunk_tiles : (MODE == STATE ? it.tile : 0);
-        it.first = (MODE == FWDC || MODE == STATE) ? it.blk * p.chunk_tiles : 0;
-        it.nsteps = (MODE == FWDC) ? (it.tile - it.first + 2)
+        it.blk = CHUNKED ? it.tile / p.chunk_tiles : (MODE == STATE ? it.tile : 0);
+        it.first = (CHUNKED || MODE == STATE) ? it.blk * p.chunk_tiles : 0;
+        const int last = min(it.first + p.chunk_tiles, NT) - 1;   // last tile of the block
+        it.nsteps = CHUNKED ? (ROWS_ARE_Q ? (it.tile - it.first + 2) : (last - it.tile + 2))
                   : (MODE == STATE) ? (min(p.chunk_tiles, NT - it.first))
                   : (ROWS_ARE_Q ? (it.tile + 1) : (NT - it.tile));
         return it;
     };
     auto stream_tile = [&](const Item& it, int t) {
-        if (MODE == FWDC) return it.first + t - 1;  // t >= 1
+        if (CHUNKED) return ROWS_ARE_Q ? (it.first + t - 1) : (it.tile + t - 1);  // t >= 1
         if (MODE == STATE) return it.first + t;
         return ROWS_ARE_Q ? t : (it.tile + t);
     };
-    auto is_state_step = [&](int t) { return MODE == FWDC && t == 0; };
+    auto is_state_step = [&](int t) { return CHUNKED && t == 0; };
 
     if (threadIdx.x == 0) {
         mbar_init(bar_x, 1);
@@ -504,7 +510,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             RowRaw rr{0.0f, 0.0f, 0.0, 0.0, 0.0, static_cast<double>(INFINITY)};
             const int grow = it.tile * TILE + r;
             const size_t vec_base = static_cast<size_t>(it.bh) * p.Spad;
-            if (MODE == FWDC || MODE == STATE) {
+            if (CHUNKED || MODE == STATE) {
                 const double* bound = p.An_bound + static_cast<size_t>(it.bh) * (p.NB + 1) + it.blk;
                 rr.b0 = bound[0];
                 rr.b1 = bound[1];
@@ -514,7 +520,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 rr.rel = p.row_rel[vec_base + grow];
                 rr.ref = p.row_ref[static_cast<size_t>(it.bh) * (p.Spad / REF_BLOCK) + grow / REF_BLOCK];
             }
-            if (MODE == DQ) rr.g = p.row_g[vec_base + grow];
+            if (IS_DQ) rr.g = p.row_g[vec_base + grow];
             return rr;
         };
         constexpr int UNKNOWN = -2;
@@ -533,8 +539,14 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         const double negA = static_cast<double>(raw.rel) + raw.ref;
         const double negA_c = (MODE == FWDC) ? fmin(negA, raw.lb) : negA;
         const float m_shift = (MODE == FWDC) ? static_cast<float>((negA - negA_c) * 0.6931471805599453) : 0.0f;
-        const double er_d = (MODE == STATE) ? raw.b1 : negA_c + static_cast<double>(p.er_add);
-        const float er_state = (MODE == FWDC) ? static_cast<float>(er_d - fmin(raw.b0, raw.lb)) : 0.0f;
+        // STATE: every row carries the block's stabiliser: -A_end(block) for the forward states, +A_end(previous
+        // block) for the states carried back in the backward (weights exp(A_end(k-1) - A_t) scale / n_t)
+        const double er_d = (MODE == STATE) ? (p.state_reverse ? -raw.b0 : raw.b1) : negA_c + static_cast<double>(p.er_add);
+        // log2 of the row weight of the state step: FWDC, DQC exp(A_end(k-1) - A_t) (times scale, resp. scale / n_t);
+        // DKC, DVC exp(a_j - A_end(k))
+        const float er_state = !CHUNKED ? 0.0f
+                               : ROWS_ARE_Q ? static_cast<float>(er_d - fmin(raw.b0, raw.lb)) : static_cast<float>(er_d + raw.b1);
+        const float state_w = (MODE == DQC || MODE == DKC) ? fast_exp2(er_state) : 0.0f;   // for the epilogue's rank-1 term
         const float g_row = raw.g;
         float rowsum = 0.0f;
 
@@ -547,17 +559,17 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             // state step: the column term is the inbound normaliser vector z (a weight, not an exponent)
             // off the diagonal the column term comes as a factor exp2(ec) (see gates.cu), on the diagonal tile as
             // the exponent itself: there a masked column can lie above the row's maximum and only the sum is safe
-            const float* ce = state_step ? p.zstate + (static_cast<size_t>(bh) * p.NB + blk) * D
-                                         : (diag ? p.col_rel : p.col_w) + vec_base + st * TILE;
+            const float* ce = (state_step && MODE == FWDC) ? p.zstate + (static_cast<size_t>(bh) * p.NB + blk) * D
+                                                           : (diag ? p.col_rel : p.col_w) + vec_base + st * TILE;
             // column terms do not depend on the contraction: fetch them before waiting
             float cv[32];
             load_cols(ce, cv);
             const float er = state_step ? er_state
                                         : static_cast<float>(er_d + p.col_ref[ref_base + st * (TILE / REF_BLOCK) + (grp >> 1)]);
-            const float er_w = (MODE == FWDC && state_step) ? fast_exp2(er) : 0.0f;
+            const float er_w = (CHUNKED && state_step) ? fast_exp2(er) : 0.0f;
             // DK adds a per-column term to T.  Each lane fetches one column's value before the wait (32 more
             // registers are not to be had) and the warp passes them round with shuffles afterwards.
-            const float g_lane = (MODE == DK) ? __ldg(p.col_g + vec_base + st * TILE + cbase + lane) : 0.0f;
+            const float g_lane = (IS_DK && !state_step) ? __ldg(p.col_g + vec_base + st * TILE + cbase + lane) : 0.0f;
             // units before the last one of Y(t): tiles go Y(0), Y(1), Z(0), Y(2), Z(1), ... in every item
             const int sq = (2 * gstep + (t == 0 ? 0 : 2 * t - 1) + 1) * C::UPT - 1;
             ok = mbar_wait_warp<SLACK_SLEEP_NS>(&bar_cons[sq % C::RING], (sq / C::RING) & 1, abort_flag, WAIT_LIMIT);
@@ -567,23 +579,23 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             uint32_t tv[32];
             tmem_ld32(t_tmem, tv);
             tc_wait_ld();
-            if (MODE == DK) {   // T + g with g per column: added eight columns at a time to keep registers free
+            if (IS_DK && !state_step) {   // T + g with g per column: added eight columns at a time to keep registers free
 #pragma unroll
                 for (int j = 0; j < 32; j++)
                     tv[j] = __float_as_uint(__uint_as_float(tv[j]) + __shfl_sync(0xffffffffu, g_lane, j));
             }
-            if (MODE == FWDC && state_step) {
+            if (CHUNKED && state_step) {
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
-                    const float wj = __uint_as_float(tv[j]) * er_w;   // T = Q: scale the row, b += (scaled q) . z
-                    rowsum = fmaf(wj, cv[j], rowsum);
+                    const float wj = __uint_as_float(tv[j]) * er_w;   // T = X: scale the row; FWDC: b += (scaled q) . z
+                    if (MODE == FWDC) rowsum = fmaf(wj, cv[j], rowsum);
                     cv[j] = wj;
                 }
             } else if (diag) {
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
                     float tval = __uint_as_float(tv[j]);
-                    if (MODE == DQ) tval += g_row;
+                    if (IS_DQ) tval += g_row;
                     float wj = tval * fast_exp2(cv[j] + er);
                     if (!causal_ok<MODE>(r, cbase + j)) wj = 0.0f;
                     if (IS_FWD) rowsum += wj;
@@ -596,10 +608,10 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 // row term alone can be large with strong decay: its column factors are 0, and 0 times an overflowed
                 // u would be NaN.  Real columns keep er far below the clamp.
                 const float u = fast_exp2(fminf(er, MAX_ROW_EXP2));
-                const float gu = (MODE == DQ) ? g_row * u : 0.0f;
+                const float gu = IS_DQ ? g_row * u : 0.0f;
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
-                    const float tu = (MODE == DQ) ? fmaf(__uint_as_float(tv[j]), u, gu) : __uint_as_float(tv[j]) * u;
+                    const float tu = IS_DQ ? fmaf(__uint_as_float(tv[j]), u, gu) : __uint_as_float(tv[j]) * u;
                     const float wj = tu * cv[j];
                     if (IS_FWD || MODE == STATE) rowsum += wj;
                     cv[j] = wj;
@@ -703,8 +715,14 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             float dot = 0.0f;
             OutT* orow = reinterpret_cast<OutT*>(p.out) + row_off + c0;
             const SideT* ogate_row = (IS_FWD && p.ogate) ? reinterpret_cast<const SideT*>(p.ogate) + row_off + c0 : nullptr;
-            const SideT* drow = ((MODE == DQ || MODE == DK) && p.dot_src)
+            const SideT* drow = ((IS_DQ || IS_DK) && p.dot_src)
                                     ? reinterpret_cast<const SideT*>(p.dot_src) + row_off + c0 : nullptr;
+            // DQC / DKC: the state step leaves out a rank-1 term, coef_row * vec[column]:
+            //   dQ_t += beta_t g_t z_k    (the db part of the carried-in state, z_k the inbound normaliser vector)
+            //   dK_j += gamma_j r_k       (r_k: the same part of the state carried back from the later blocks)
+            [[maybe_unused]] const float rank1_coef = (MODE == DQC) ? state_w * g_row : state_w;
+            [[maybe_unused]] const float* rank1_vec = (MODE == DQC || MODE == DKC)
+                                         ? (MODE == DQC ? p.zstate : p.rvec) + (static_cast<size_t>(bh) * p.NB + blk) * D + c0 : nullptr;
 #pragma unroll 1
             for (int ch = 0; ch < QUART / CW; ch++) {
                 uint32_t av[32];
@@ -723,12 +741,22 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 float vals[CW];
 #pragma unroll
                 for (int j = 0; j < CW; j++) vals[j] = __uint_as_float(av[j]) * inv_n;
+                if constexpr (MODE == DQC || MODE == DKC) {
+#pragma unroll
+                    for (int j4 = 0; j4 < CW / 4; j4++) {
+                        const float4 e4 = __ldg(reinterpret_cast<const float4*>(rank1_vec + ch * CW) + j4);
+                        vals[j4 * 4 + 0] = fmaf(rank1_coef, e4.x, vals[j4 * 4 + 0]);
+                        vals[j4 * 4 + 1] = fmaf(rank1_coef, e4.y, vals[j4 * 4 + 1]);
+                        vals[j4 * 4 + 2] = fmaf(rank1_coef, e4.z, vals[j4 * 4 + 2]);
+                        vals[j4 * 4 + 3] = fmaf(rank1_coef, e4.w, vals[j4 * 4 + 3]);
+                    }
+                }
                 if (row_ok) {
                     if (IS_FWD && ogate_row) {
 #pragma unroll
                         for (int j = 0; j < CW; j++) vals[j] *= silu_f(to_f32<SideT>(ogate_row[ch * CW + j]));
                     }
-                    if ((MODE == DQ || MODE == DK) && drow) {
+                    if ((IS_DQ || IS_DK) && drow) {
 #pragma unroll
                         for (int jv = 0; jv < CW / VEC; jv++) {
                             const uint4 raw = *reinterpret_cast<const uint4*>(drow + ch * CW + jv * VEC);
@@ -806,7 +834,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     }
                 }
             }
-            if ((MODE == DQ || MODE == DK) && p.dot_out) {
+            if ((IS_DQ || IS_DK) && p.dot_out) {
                 const float dsum = exchange(dot);
                 if (ok && grp == 0) p.dot_out[vec_base + grow] = row_ok ? dsum : 0.0f;
             }
@@ -940,12 +968,13 @@ int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
     if ((rc = make_map(&mz, p.Z, p.BH, p.S, DL, in_dtype, ABFMT == 2)) != MLSTM_OK) return rc;
     mi = mx;
     ms = mx;
-    if (MODE == FWDC || MODE == STATE) {
+    constexpr bool CHUNKED = (MODE == FWDC || MODE == DQC || MODE == DKC || MODE == DVC);
+    if (CHUNKED || MODE == STATE) {
         if (!p.ident || p.chunk_tiles <= 0 || p.NB <= 0 || !p.An_bound) return MLSTM_E_ARG;
         if ((rc = make_map(&mi, p.ident, 1, TILE, TILE, in_dtype)) != MLSTM_OK) return rc;
     }
-    if (MODE == FWDC) {
-        if (!p.states || !p.zstate) return MLSTM_E_ARG;
+    if (CHUNKED) {
+        if (!p.states || ((MODE == FWDC || MODE == DQC) && !p.zstate) || (MODE == DKC && !p.rvec)) return MLSTM_E_ARG;
         if ((rc = make_map(&ms, p.states, p.BH * p.NB, D, D, in_dtype)) != MLSTM_OK) return rc;
     }
     mo = mx;
@@ -1001,7 +1030,7 @@ template <int MODE, int D>
 int launch_fmt(const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st) {
     if (in_dtype == MLSTM_DT_BF16) return launch_out<MODE, D, 1>(p, in_dtype, out_dtype, st);
     if (in_dtype == MLSTM_DT_F16) return launch_out<MODE, D, 0>(p, in_dtype, out_dtype, st);
-    if constexpr (MODE != FWDC && MODE != STATE) {
+    if constexpr (MODE <= DV) {
         if (in_dtype == MLSTM_DT_F32) return launch_out<MODE, D, 2>(p, in_dtype, out_dtype, st);
     }
     return MLSTM_E_UNSUPPORTED;
@@ -1071,6 +1100,15 @@ int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, c
         case STATE:
             if (p.D != 128 || out_dtype != MLSTM_DT_F32) return MLSTM_E_UNSUPPORTED;
             return launch_fmt<STATE, 128>(p, in_dtype, out_dtype, st);
+        case DQC:
+            if (p.D != 128) return MLSTM_E_UNSUPPORTED;
+            return launch_fmt<DQC, 128>(p, in_dtype, out_dtype, st);
+        case DKC:
+            if (p.D != 128) return MLSTM_E_UNSUPPORTED;
+            return launch_fmt<DKC, 128>(p, in_dtype, out_dtype, st);
+        case DVC:
+            if (p.D != 128) return MLSTM_E_UNSUPPORTED;
+            return launch_fmt<DVC, 128>(p, in_dtype, out_dtype, st);
     }
     return MLSTM_E_ARG;
 }

@@ -465,6 +465,10 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             if (id_next >= 0) raw_next = fetch_rows(decode(id_next));
         }
 
+        // DQ / DK: the operand of the epilogue's row dot (this thread's 64 values of q resp. k: one 128-byte line) is
+        // read by no other part of the pass, so it would come from DRAM after the accumulator wait; ask for it now
+        if ((MODE == DQ || MODE == DK) && p.dot_src && row_ok)
+            prefetch_l2(reinterpret_cast<const InT*>(p.dot_src) + (static_cast<size_t>(bh) * p.S + grow) * D + grp * (D / NGROUPS));
         // ---- epilogue: each group drains a quarter of this CTA's accumulator columns
         ok = mbar_wait_warp<SLACK_SLEEP_NS>(bar_acc, n & 1, abort_flag, WAIT_LIMIT);
         if (!ok) break;

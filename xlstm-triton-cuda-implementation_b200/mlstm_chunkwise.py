@@ -21,7 +21,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["mlstm_chunkwise", "mlstm_chunkwise_sequence_parallel", "fold_gate_summaries", "fold_states",
+__all__ = ["mlstm_chunkwise", "mlstm_chunkwise_backward", "mlstm_chunkwise_sequence_parallel", "fold_gate_summaries", "fold_states",
            "fold_records", "ChunkSegment"]
 
 
@@ -111,6 +111,16 @@ class ChunkSegment:
         _lib.maybe_read_status(self.ws, self.dev, "mlstm_chunk_apply")
         return (h, (S_out, z_out)) if return_state else h
 
+    def read_mb(self):
+        """After ``apply``: the stabiliser m and the row sums b [B, NH, S] float32 (the parallel forward's M, B)."""
+        m = torch.empty((self.B, self.NH, self.S), dtype=torch.float32, device=self.dev)
+        b = torch.empty_like(m)
+        with torch.cuda.device(self.dev):
+            rc = self.L.mlstm_chunk_read_mb(self.ws.data_ptr(), self.ws.numel(), m.data_ptr(), b.data_ptr(), *self.dims,
+                                            self._stream())
+        _lib.check(rc, "mlstm_chunk_read_mb")
+        return m, b
+
     # ---- sequence-parallel stages (one exchange between them)
     def sp_local(self):
         """Everything that needs no other rank; returns this segment's record [B*NH, D*D + D + 4] float32
@@ -138,14 +148,62 @@ class ChunkSegment:
         return h
 
 
+def mlstm_chunkwise_backward(dh, q, k, v, f, i, h, m, b, chunk_size=256):
+    """Gradients (dq, dk, dv, df, di) of the chunkwise forward without inbound state, in time linear in S."""
+    dev = _lib.require_cuda(dh, q, k, v, f, i, h, m, b)
+    B, NH, S, D = q.shape
+    if dh.shape != q.shape or dh.dtype != h.dtype:
+        raise ValueError("dh must match h in shape and element type")
+    dt, hdt, chunk = _lib.dtype_code(q), _lib.dtype_code(h), int(chunk_size)
+    L = _lib.lib()
+    nbytes = L.mlstm_chunk_bwd_workspace(B, NH, S, D, dt, hdt, chunk)
+    if nbytes == 0:
+        raise _lib.MlstmError(-4, "mlstm_chunk_bwd_workspace (needs float16/bfloat16, D = 128, chunk % 128 == 0)")
+    ws = _lib.workspace(nbytes, dev)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    df, di = torch.empty_like(f), torch.empty_like(i)
+    with torch.cuda.device(dev):
+        rc = L.mlstm_chunk_bwd(dh.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), f.data_ptr(), i.data_ptr(), h.data_ptr(),
+                               m.data_ptr(), b.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), df.data_ptr(),
+                               di.data_ptr(), ws.data_ptr(), ws.numel(), B, NH, S, D, dt, hdt, chunk, _lib.stream_ptr(dev))
+    _lib.check(rc, "mlstm_chunk_bwd")
+    _lib.maybe_read_status(ws, dev, "mlstm_chunk_bwd")
+    return dq, dk, dv, df, di
+
+
+class _ChunkwiseWithGrad(torch.autograd.Function):
+    """Chunkwise forward and chunkwise backward (both linear in S); h is float32 like the parallel path's."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, f, i, chunk_size):
+        seg = ChunkSegment(q, k, v, f, i, chunk_size, shared_workspace=True)
+        seg.prepare(None)
+        h = seg.apply(None)
+        m, b = seg.read_mb()
+        ctx.save_for_backward(q, k, v, f, i, h, m, b)
+        ctx.chunk = chunk_size
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        q, k, v, f, i, h, m, b = ctx.saved_tensors
+        return mlstm_chunkwise_backward(dh.contiguous(), q, k, v, f, i, h, m, b, ctx.chunk) + (None,)
+
+
 def mlstm_chunkwise(q, k, v, f, i, chunk_size=256, h_dtype=torch.float32, initial=None, return_state=False, o=None):
     """Chunkwise forward on one GPU (times silu(o) when the output-gate pre-activation ``o`` is given).
+    Inputs that require gradients get them through the chunkwise backward (no ``initial`` / ``return_state``
+    / ``o`` in that case; wrap the output gate around it, as ``mlstm_scan`` does).
 
     ``initial`` = (S, z, F, A) continues an earlier segment: S [B*NH, D, D] and z [B*NH, D] float32
     stabilised by A, and F, A float64 [B*NH] (the log-forget total and the prefix maximum of a = i - F
     at the end of that segment).  With ``return_state`` the same tuple for the end of this call is
     returned beside h.
     """
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, f, i)):
+        if initial is not None or return_state or o is not None or h_dtype != torch.float32:
+            raise ValueError("gradients are available for the plain call: no initial / return_state / o, float32 h")
+        return _ChunkwiseWithGrad.apply(q, k, v, f, i, int(chunk_size))
     seg = ChunkSegment(q, k, v, f, i, chunk_size, shared_workspace=True, o=o)
     carry = None
     state_in = None

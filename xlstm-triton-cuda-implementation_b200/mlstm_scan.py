@@ -24,10 +24,10 @@ error about 5e-4 to 1e-3, inside the reference's own 1e-2 check) and D is 64, 12
 256 up to 4096; ``allow_tf32=False`` gives IEEE fp32 dot products on the CUDA cores (error about 1e-6,
 much slower).
 
-The reference's scan is forward only (README.md:97).  Here inputs that require gradients get them: the
-function computed is exactly the parallel form times silu(o), so the backward runs the parallel
-backward kernels (``mlstm_matmul_backward``) behind the output gate's own derivative; its cost is
-quadratic in S whatever form the forward took.
+The reference's scan is forward only (README.md:97).  Here inputs that require gradients get them, behind
+the output gate's own derivative: long 16-bit sequences at D = 128 through the chunkwise forward and the
+chunkwise backward (states carried forward for dQ and back for dK, dV; linear in S), everything else
+through the parallel kernels (``mlstm_matmul_backward``), whose cost is quadratic in S.
 """
 import torch
 
@@ -60,12 +60,27 @@ def output_gate_backward(dh, h_inner, o):
     return dh_inner, do
 
 
+def _chunkwise_shape(q):
+    """Whether the scan entry's chunkwise form (and with it the chunkwise backward) serves this input."""
+    B, NH, S, D = q.shape
+    return q.dtype in (torch.float16, torch.bfloat16) and D == 128 and S > 2 * D and S > 512
+
+
 class _ScanWithGrad(torch.autograd.Function):
-    """mLSTM(q, k, v, f, i) * silu(o) with gradients for all six inputs."""
+    """mLSTM(q, k, v, f, i) * silu(o) with gradients for all six inputs.  Long 16-bit sequences at D = 128 take
+    the chunkwise forward and backward (linear in S); everything else the parallel kernels (quadratic)."""
 
     @staticmethod
     def forward(ctx, q, k, v, f, i, o, flags):
-        h_inner, m, b = mlstm_matmul_forward(q, k, v, f, i, flags=flags)
+        ctx.chunked = _chunkwise_shape(q)
+        if ctx.chunked:
+            from .mlstm_chunkwise import ChunkSegment
+            seg = ChunkSegment(q, k, v, f, i, 256, shared_workspace=True)
+            seg.prepare(None)
+            h_inner = seg.apply(None)
+            m, b = seg.read_mb()
+        else:
+            h_inner, m, b = mlstm_matmul_forward(q, k, v, f, i, flags=flags)
         ctx.save_for_backward(q, k, v, f, i, o, m, b, h_inner)
         ctx.flags = flags
         return output_gate_forward(h_inner, o)
@@ -74,7 +89,11 @@ class _ScanWithGrad(torch.autograd.Function):
     def backward(ctx, dh):
         q, k, v, f, i, o, m, b, h_inner = ctx.saved_tensors
         dh_inner, do = output_gate_backward(dh.contiguous(), h_inner, o)
-        dq, dk, dv, df, di = mlstm_matmul_backward(dh_inner, q, k, v, f, i, h_inner, m, b, flags=ctx.flags)
+        if ctx.chunked:
+            from .mlstm_chunkwise import mlstm_chunkwise_backward
+            dq, dk, dv, df, di = mlstm_chunkwise_backward(dh_inner, q, k, v, f, i, h_inner, m, b, 256)
+        else:
+            dq, dk, dv, df, di = mlstm_matmul_backward(dh_inner, q, k, v, f, i, h_inner, m, b, flags=ctx.flags)
         return dq, dk, dv, df, di, do, None
 
 
