@@ -18,11 +18,12 @@ The library picks one of three forms by shape (``mlstm_scan_fwd`` in include/mls
 ``initial`` / ``return_state`` expose the carried state (S [B*NH, D, D] key-major, z [B*NH, D], F, A
 [B*NH] float64; see ``mlstm_chunkwise``) and need the chunkwise form's shapes.
 
-Arithmetic: 16-bit inputs always run on the tensor cores.  float32 inputs run on them with tf32
-operands and fp32 accumulation when ``allow_tf32`` is true (the default here; measured max-abs-rel
+Arithmetic: 16-bit inputs always run on the tensor cores.  float32 inputs run on them with single tf32
+products and fp32 accumulation when ``allow_tf32`` is true (the default here; measured max-abs-rel
 error about 5e-4 to 1e-3, inside the reference's own 1e-2 check) and D is 64, 128, 256 or a multiple of
-256 up to 4096; ``allow_tf32=False`` gives IEEE fp32 dot products on the CUDA cores (error about 1e-6,
-much slower).
+256 up to 4096.  ``allow_tf32=False`` keeps fp32-level accuracy: the split tensor-core form at D = 64
+and 128 (three bf16 products per fp32 product, error about 1e-5), IEEE fp32 dot products on the CUDA
+cores elsewhere (much slower).
 
 The reference's scan is forward only (README.md:97).  Here inputs that require gradients get them, behind
 the output gate's own derivative: long 16-bit sequences at D = 128 through the chunkwise forward and the
