@@ -55,6 +55,26 @@ def gen_scan(name, B, NH, S, D, f_mean, seed):
     print(name, "h max", float(h.abs().max()))
 
 
+def gen_long_bf16(name, S, D, f_mean, seed):
+    """One head of a long 16-bit case (the chunkwise path's shape): inputs are bf16 values (stored as their bit
+    patterns), outputs come from the reference's PyTorch forward (mlstm_matmul.py:104-118) and backward
+    (mlstm_matmul.py:336-365) in fp32 on exactly those values and are stored as float16."""
+    g = torch.Generator().manual_seed(seed)
+    mk = lambda *s: torch.randn(*s, generator=g)
+    q, k, v = ((mk(1, 1, S, D) * D ** -0.5).bfloat16() for _ in range(3))
+    f, i = (f_mean + mk(1, 1, S)).bfloat16(), mk(1, 1, S).bfloat16()
+    dh = mk(1, 1, S, D).bfloat16()
+    ref_mm.DEVICE = torch.device("cpu")
+    x = [t.float() for t in (q, k, v, f, i)]
+    h = ref_mm.mlstm_matmul_pytorch(*x)
+    dq, dk, dv, df, di = ref_mm.mlstm_matmul_backward_pytorch(dh.float(), *x)
+    bits = lambda t: t.view(torch.int16).numpy()
+    np.savez(os.path.join(HERE, name), q=bits(q), k=bits(k), v=bits(v), f=bits(f), i=bits(i), dh=bits(dh),
+             h=h.half().numpy(), dq=dq.half().numpy(), dk=dk.half().numpy(), dv=dv.half().numpy(),
+             df=df.float().numpy(), di=di.float().numpy())
+    print(name, "h max", float(h.abs().max()), "dq max", float(dq.abs().max()))
+
+
 def gen_cpp(name, S, D, seed):
     lib = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libmlstm_ref.so"))
     mk = lambda n: np.zeros(n, dtype=np.float16)
@@ -89,6 +109,10 @@ def gen_cpp_backward(name, S, D, seed):
 if __name__ == "__main__":
     gen_matmul("matmul_s128_d32_f0.npz", 1, 2, 128, 32, 0.0, 0)
     gen_matmul("matmul_s192_d64_f3.npz", 2, 1, 192, 64, 3.0, 1)
+    # one mid-size case per path: all large-shape parity otherwise rests on the (pinned) port
+    gen_matmul("matmul_s768_d32_f1.npz", 1, 1, 768, 32, 1.0, 4)
+    gen_scan("scan_s512_d32_f1.npz", 1, 1, 512, 32, 1.0, 5)
+    gen_long_bf16("long_bf16_s1024_d128_f3.npz", 1024, 128, 3.0, 6)
     gen_scan("scan_s96_d16_f0.npz", 1, 2, 96, 16, 0.0, 2)
     gen_scan("scan_s64_d32_f3.npz", 1, 1, 64, 32, 3.0, 3)
     # the reference demo's own recipe: srand(100), S = 640 (the README's value), D = 128

@@ -157,6 +157,23 @@ def test_chunkwise_backward_against_oracle(gc, dtype, S, chunk, f_mean):
         assert orc.max_abs_rel(t[n].grad.float(), a.float()) < TOL_16, n
 
 
+def test_chunkwise_forward_backward_against_reference_golden(gc, golden_dir):
+    """S = 1024, D = 128, bf16, chunk 256: chunkwise forward and backward against the reference's own PyTorch
+    forward / backward on the same bf16 values."""
+    from tests.test_oracle import load_long_bf16
+    x, ref = load_long_bf16(golden_dir)
+    names = ("q", "k", "v", "f", "i")
+    t = {n: x[n].cuda().requires_grad_(True) for n in names}
+    h = gc.PKG.mlstm_chunkwise(*(t[n] for n in names), chunk_size=256)
+    h.backward(x["dh"].float().cuda())
+    assert orc.max_abs_rel(h.detach(), ref["h"]) < TOL_16
+    for n in names:
+        r = ref["d" + n].clone()
+        if n == "f":
+            r[..., 0] = 0.0
+        assert orc.max_abs_rel(t[n].grad.float(), r) < TOL_16, n
+
+
 def test_scan_gradients_take_the_chunkwise_backward(gc):
     """mlstm_scan on a long 16-bit sequence with inputs that require gradients: chunkwise forward and backward
     behind the output gate, against autograd of the fp64 oracle."""

@@ -24,7 +24,7 @@ def gc():
     return gpu_cases
 
 
-@pytest.mark.parametrize("name", ["matmul_s128_d32_f0.npz", "matmul_s192_d64_f3.npz"])
+@pytest.mark.parametrize("name", ["matmul_s128_d32_f0.npz", "matmul_s192_d64_f3.npz", "matmul_s768_d32_f1.npz"])
 def test_fp32_against_reference_golden(gc, golden_dir, name):
     z = np.load(f"{golden_dir}/{name}")
     x = {k: torch.from_numpy(z[k]) for k in ("q", "k", "v", "f", "i", "dh")}
@@ -39,6 +39,21 @@ def test_fp32_against_reference_golden(gc, golden_dir, name):
             ref[..., 0] = 0.0
             assert float(g[..., 0].abs().max()) == 0.0
         assert orc.max_abs_rel(g, ref) < 2e-4, key
+
+
+def test_bf16_against_reference_golden_long(gc, golden_dir):
+    """S = 1024, D = 128, bf16: the tensor-core forward and backward against the reference's own PyTorch
+    forward / backward on the same bf16 values (fixture made by tests/golden/make_golden.py)."""
+    from tests.test_oracle import load_long_bf16
+    x, ref = load_long_bf16(golden_dir)
+    h, m, b = gc.run_forward(x, h_dtype=torch.bfloat16, flags=gc._lib.F_FORCE_TC)
+    assert orc.max_abs_rel(h.float(), ref["h"]) < TOL_16
+    grads = gc.run_backward(x, h, m, b, flags=gc._lib.F_FORCE_TC)
+    for key, g in zip(("dq", "dk", "dv", "df", "di"), grads):
+        r = ref[key].clone()
+        if key == "df":
+            r[..., 0] = 0.0
+        assert orc.max_abs_rel(g.float(), r) < TOL_16, key
 
 
 @pytest.mark.parametrize("B,NH,S,D,f_mean", [

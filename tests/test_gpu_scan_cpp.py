@@ -18,7 +18,7 @@ def gc():
     return gpu_cases
 
 
-@pytest.mark.parametrize("name", ["scan_s96_d16_f0.npz", "scan_s64_d32_f3.npz"])
+@pytest.mark.parametrize("name", ["scan_s96_d16_f0.npz", "scan_s64_d32_f3.npz", "scan_s512_d32_f1.npz"])
 def test_scan_against_reference_golden(gc, golden_dir, name):
     z = np.load(f"{golden_dir}/{name}")
     dev = torch.device("cuda", 0)

@@ -19,30 +19,54 @@ def _load(golden_dir, name):
     return {k: T(z[k]) for k in z.files}
 
 
-@pytest.mark.parametrize("name", ["matmul_s128_d32_f0.npz", "matmul_s192_d64_f3.npz"])
+@pytest.mark.parametrize("name", ["matmul_s128_d32_f0.npz", "matmul_s192_d64_f3.npz", "matmul_s768_d32_f1.npz"])
 def test_matmul_oracle_vs_reference_golden(golden_dir, name):
     z = _load(golden_dir, name)
+    # the goldens are the reference's fp32 evaluation; its own rounding grows with S (about 3e-5 at S = 768)
+    long_case = z["q"].shape[-2] > 256
     h = orc.matmul_forward(z["q"], z["k"], z["v"], z["f"], z["i"])
-    assert orc.max_abs_rel(h, z["h"]) < 2e-5
+    assert orc.max_abs_rel(h, z["h"]) < (1e-4 if long_case else 2e-5)
     got = orc.matmul_backward(z["dh"], z["q"], z["k"], z["v"], z["f"], z["i"])
     for key, g in zip(("dq", "dk", "dv", "df", "di"), got):
         ref = z[key].clone()
         if key == "df":
             ref[..., 0] = 0.0  # the reference oracle wraps the (zero) total into slot 0
-        assert orc.max_abs_rel(g, ref) < 5e-5, key
+        assert orc.max_abs_rel(g, ref) < (2e-4 if long_case else 5e-5), key
     # fp32 evaluation of the oracle must also sit inside the reference's own tolerance
     ok, frac = orc.check(orc.matmul_forward(z["q"], z["k"], z["v"], z["f"], z["i"], dtype=torch.float32), z["h"])
     assert ok, frac
 
 
-@pytest.mark.parametrize("name", ["scan_s96_d16_f0.npz", "scan_s64_d32_f3.npz"])
+@pytest.mark.parametrize("name", ["scan_s96_d16_f0.npz", "scan_s64_d32_f3.npz", "scan_s512_d32_f1.npz"])
 def test_scan_oracle_vs_reference_golden(golden_dir, name):
     z = _load(golden_dir, name)
     h = orc.scan_forward(z["q"], z["k"], z["v"], z["f"], z["i"], z["o"])
-    assert orc.max_abs_rel(h, z["h"]) < 2e-5
+    assert orc.max_abs_rel(h, z["h"]) < (1e-4 if z["q"].shape[-2] > 256 else 2e-5)
     # recurrent form == parallel form times silu(o)
     hp = orc.matmul_forward(z["q"], z["k"], z["v"], z["f"], z["i"]) * torch.nn.functional.silu(z["o"].double())
     assert orc.max_abs_rel(h, hp) < 1e-5
+
+
+def load_long_bf16(golden_dir, name="long_bf16_s1024_d128_f3.npz"):
+    """The long 16-bit fixture: bf16 inputs (stored as bit patterns), reference outputs in fp16 / fp32."""
+    z = np.load(os.path.join(golden_dir, name))
+    x = {k: T(z[k].copy()).view(torch.bfloat16) for k in ("q", "k", "v", "f", "i", "dh")}
+    ref = {k: T(z[k]).float() for k in ("h", "dq", "dk", "dv", "df", "di")}
+    return x, ref
+
+
+def test_oracle_vs_reference_golden_long_bf16(golden_dir):
+    """S = 1024, D = 128 on bf16 values: the port against the reference's own forward and backward
+    (stored in fp16, hence the 2e-3)."""
+    x, ref = load_long_bf16(golden_dir)
+    h = orc.matmul_forward(x["q"], x["k"], x["v"], x["f"], x["i"])
+    assert orc.max_abs_rel(h, ref["h"]) < 2e-3
+    grads = orc.matmul_backward(x["dh"], x["q"], x["k"], x["v"], x["f"], x["i"])
+    for key, g in zip(("dq", "dk", "dv", "df", "di"), grads):
+        r = ref[key].clone()
+        if key == "df":
+            r[..., 0] = 0.0
+        assert orc.max_abs_rel(g, r) < 2e-3, key
 
 
 def test_scan_oracle_segment_carry(golden_dir):

@@ -142,6 +142,14 @@ size_t tf32_copy_bytes(int BH, int S, int D, int dtype, int flags, int ntensors)
 // converts `count` tensors into consecutive regions of `buf` and redirects the pointers
 int round_inputs(const void** ptrs, int count, void* buf, int BH, int S, int D, int kind, cudaStream_t st) {
     const size_t one = al(static_cast<size_t>(BH) * S * D * sizeof(float));
+    if (kind == KIND_TC_X3 && count <= 4) {   // one launch for all of them
+        void* dst[4];
+        for (int k = 0; k < count; k++) dst[k] = static_cast<uint8_t*>(buf) + k * one;
+        int rc = launch_split_bf16_multi(ptrs, dst, count, static_cast<long long>(BH) * S, D, st);
+        if (rc != MLSTM_OK) return rc;
+        for (int k = 0; k < count; k++) ptrs[k] = dst[k];
+        return MLSTM_OK;
+    }
     for (int k = 0; k < count; k++) {
         void* dst = static_cast<uint8_t*>(buf) + k * one;
         int rc = kind == KIND_TC_X3 ? launch_split_bf16(ptrs[k], dst, static_cast<long long>(BH) * S, D, st)
@@ -356,7 +364,8 @@ int mlstm_scan_fwd(const void* q, const void* k, const void* v, const void* f, c
         uint8_t* base = static_cast<uint8_t*>(workspace) + w.bytes;
         float* bpart = reinterpret_cast<float*>(base);
         void* W = base + al(scan_gemm_bpart_bytes(BH, S, dtype));
-        if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
+        // status word and the two work-item counters of the passes in one go
+        if (cudaMemsetAsync(w.status, 0, WS_ALIGN, st) != cudaSuccess) return MLSTM_E_CUDA;
         if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, w.m, BH, S, Spad, dtype, st, nullptr, nullptr, nullptr, 0,
                                    nullptr, w.gaw)) != MLSTM_OK)
             return rc;

@@ -359,10 +359,17 @@ __global__ void round_tf32_kernel(const float4* __restrict__ in, float4* __restr
 }
 
 // fp32 -> two bf16 halves: hi = bf16(x), mid = bf16(x - hi), written side by side as rows of 2 D values
-// (hi | mid).  x - hi is exact in fp32, so hi + mid carries 16 mantissa bits of x.  Four values per thread.
-__global__ void split_bf16_kernel(const float4* __restrict__ in, __nv_bfloat16* __restrict__ out, long long n4, int D) {
+// (hi | mid).  x - hi is exact in fp32, so hi + mid carries 16 mantissa bits of x.  Four values per thread;
+// blockIdx.y selects one of up to four tensors of the same shape.
+struct SplitPtrs {
+    const float4* in[4];
+    __nv_bfloat16* out[4];
+};
+__global__ void split_bf16_kernel(const SplitPtrs ptrs, long long n4, int D) {
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= n4) return;
+    const float4* __restrict__ in = ptrs.in[blockIdx.y];
+    __nv_bfloat16* __restrict__ out = ptrs.out[blockIdx.y];
     const float4 x = in[idx];
     const long long e = idx * 4;
     const long long row = e / D;
@@ -380,13 +387,23 @@ __global__ void split_bf16_kernel(const float4* __restrict__ in, __nv_bfloat16* 
 
 }  // namespace
 
-int launch_split_bf16(const void* in, void* out, long long rows, int D, cudaStream_t st) {
+int launch_split_bf16_multi(const void* const* in, void* const* out, int count, long long rows, int D, cudaStream_t st) {
+    if (count < 1 || count > 4) return MLSTM_E_ARG;
     const long long n4 = rows * D / 4;
     const int threads = 256;
     const long long blocks = (n4 + threads - 1) / threads;
     if (blocks <= 0 || blocks > 0x7fffffffLL || (D & 3)) return MLSTM_E_SHAPE;
-    split_bf16_kernel<<<(unsigned)blocks, threads, 0, st>>>(static_cast<const float4*>(in), static_cast<__nv_bfloat16*>(out), n4, D);
+    SplitPtrs ptrs{};
+    for (int k = 0; k < count; k++) {
+        ptrs.in[k] = static_cast<const float4*>(in[k]);
+        ptrs.out[k] = static_cast<__nv_bfloat16*>(out[k]);
+    }
+    split_bf16_kernel<<<dim3(static_cast<unsigned>(blocks), count), threads, 0, st>>>(ptrs, n4, D);
     return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+}
+
+int launch_split_bf16(const void* in, void* out, long long rows, int D, cudaStream_t st) {
+    return launch_split_bf16_multi(&in, &out, 1, rows, D, st);
 }
 
 int launch_ogate_fwd(const void* h_inner, const void* o, void* h, long long n, int h_dtype, int o_dtype, cudaStream_t st) {

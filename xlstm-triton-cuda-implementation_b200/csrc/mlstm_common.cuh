@@ -151,6 +151,8 @@ bool tc_supported(int S, int D, int in_dtype);
 int launch_round_tf32(const void* in, void* out, long long n, cudaStream_t st);
 // fp32 [rows, D] -> bf16 [rows, 2 D] (hi | mid): the operands of the split tensor-core form (mm_tc.cu)
 int launch_split_bf16(const void* in, void* out, long long rows, int D, cudaStream_t st);
+// the same for up to four tensors of one shape in one launch
+int launch_split_bf16_multi(const void* const* in, void* const* out, int count, long long rows, int D, cudaStream_t st);
 bool tc_x3_supported(int S, int D);
 int launch_pass_tc_x3(int mode, const PassParams& p, cudaStream_t st);
 int launch_ogate_fwd(const void* h_inner, const void* o, void* h, long long n, int h_dtype, int o_dtype, cudaStream_t st);
@@ -159,7 +161,7 @@ int launch_ogate_bwd(const void* dh, const void* h_inner, const void* o, void* d
 
 // Two-pass forward for head dimensions above 256 (scan_gemm.cu).  Gate vectors as written by
 // launch_gates_fwd for all BH slices; bpart and W are scratch of scan_gemm_bpart_bytes / scan_gemm_w_bytes;
-// counters: two device words.
+// counters: two device words, zeroed by the caller.
 struct ScanGemmArgs {
     int S, Spad, BH, D;
     const float *ga, *gAn, *gaw;

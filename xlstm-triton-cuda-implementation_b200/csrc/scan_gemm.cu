@@ -428,7 +428,8 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 template <int PHASE, int ABFMT>
-int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& p, cudaStream_t st) {
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& p, bool zero_counter,
+                cudaStream_t st) {
     auto kern = mlstm_scan_gemm<PHASE, ABFMT>;
     cudaError_t ce;
     {
@@ -446,8 +447,10 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     }
     const int sms = tc_sm_count();
     if (sms <= 0) return MLSTM_E_CUDA;
-    ce = cudaMemsetAsync(p.counter, 0, sizeof(int), st);
-    if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
+    if (zero_counter) {
+        ce = cudaMemsetAsync(p.counter, 0, sizeof(int), st);
+        if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
+    }
     const unsigned grid = static_cast<unsigned>(p.items < sms ? p.items : sms);   // persistent: one CTA per SM
     kern<<<grid, NTHREADS_G, SMEM_BYTES_G, st>>>(ma, mb, mo, p);
     ce = cudaGetLastError();
@@ -457,6 +460,7 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
 template <int ABFMT>
 int run_group(const void* q, const void* k, const void* v, const void* o, float* h, void* W, const ScanGemmArgs& a, int bh0,
               int nbh, int dtype, cudaStream_t st) {
+    const bool zero_counters = bh0 > 0;   // the caller zeroed both counters with the status word for the first group
     const size_t es = dtype == MLSTM_DT_F32 ? 4 : 2;
     const size_t slice = static_cast<size_t>(a.S) * a.D;
     const uint8_t* qg = static_cast<const uint8_t*>(q) + bh0 * slice * es;
@@ -487,7 +491,7 @@ int run_group(const void* q, const void* k, const void* v, const void* o, float*
     if ((rc = tc_make_map_out(&mo, W, nbh, a.Spad, a.Spad, dtype, 32)) != MLSTM_OK) return rc;
     p.items = p.per_head * nbh;
     p.counter = a.counters;
-    if ((rc = launch_gemm<GATE, ABFMT>(ma, mb, mo, p, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gemm<GATE, ABFMT>(ma, mb, mo, p, zero_counters, st)) != MLSTM_OK) return rc;
     // ---- pass 2: h = (W V) / n * silu(o)
     constexpr int KC = ABFMT == 2 ? 32 : 64;
     if ((rc = tc_make_map(&ma, W, nbh, a.Spad, a.Spad, dtype, false, 128)) != MLSTM_OK) return rc;
@@ -495,7 +499,7 @@ int run_group(const void* q, const void* k, const void* v, const void* o, float*
     if ((rc = tc_make_map_out(&mo, hg, nbh, a.S, a.D, MLSTM_DT_F32, 32)) != MLSTM_OK) return rc;
     p.items = p.NT * nbh * p.NVS;
     p.counter = a.counters + 1;
-    return launch_gemm<APPLY, ABFMT>(ma, mb, mo, p, st);
+    return launch_gemm<APPLY, ABFMT>(ma, mb, mo, p, zero_counters, st);
 }
 
 }  // namespace
