@@ -93,8 +93,8 @@ BwdWs carve_bwd(void* ws, int BH, int S, int D, bool need_dh16) {
     w.gB = c.take<float>(vec);
     w.gBw = c.take<float>(vec);
     w.g = c.take<float>(vec);
-    w.dI = c.take<float>(vec);
-    w.R = c.take<float>(vec);
+    w.dI = c.take<float>(vec * TC_DOT_PARTS);   // partial row dots, one per gate group of the tensor-core passes
+    w.R = c.take<float>(vec * TC_DOT_PARTS);
     w.dh16 = need_dh16 ? c.take<uint8_t>(static_cast<size_t>(BH) * S * D * 2) : nullptr;
     w.bytes = c.off;
     return w;
@@ -291,6 +291,7 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
 
     PassParams p{};
     p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8;
+    p.dot_part_stride = static_cast<long long>(BH) * Spad;
     // dQ = ((dH V^T + g_r) * decay) K
     p.X = dhp; p.Y = v; p.Z = k;
     p.row_rel = w.gB; p.row_ref = w.An_ref; p.row_g = w.g; p.col_rel = w.ga; p.col_w = w.gaw; p.col_ref = w.a_ref; p.col_g = nullptr;
@@ -306,7 +307,8 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     p.col_g = nullptr;
     p.out = dv; p.dot_src = nullptr; p.dot_out = nullptr;
     if ((rc = run_pass(kind, DV, p, dtype, dtype, st)) != MLSTM_OK) return rc;
-    return launch_df(f, w.dI, w.R, df, di, BH, S, Spad, dtype, st);
+    return launch_df(f, w.dI, w.R, df, di, BH, S, Spad, dtype, st, kind == KIND_SIMT ? 1 : TC_DOT_PARTS,
+                     static_cast<long long>(BH) * Spad);
 }
 
 // Which of its three forms the scan entry uses.

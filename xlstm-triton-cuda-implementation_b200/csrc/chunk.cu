@@ -395,8 +395,8 @@ static ChunkBwdWs carve_bwd_chunk(void* ws, int BH, int S, int D, int chunk, boo
     w.gB = static_cast<float*>(take(vec));
     w.gBw = static_cast<float*>(take(vec));
     w.g = static_cast<float*>(take(vec));
-    w.dI = static_cast<float*>(take(vec));
-    w.Rdot = static_cast<float*>(take(vec));
+    w.dI = static_cast<float*>(take(vec * TC_DOT_PARTS));     // partial row dots, one per gate group
+    w.Rdot = static_cast<float*>(take(vec * TC_DOT_PARTS));
     w.rvec = static_cast<float*>(take(nblk * D * sizeof(float)));
     w.statesT = take(nblk * D * D * 2);
     w.statesT2 = take(nblk * D * D * 2);
@@ -435,6 +435,7 @@ int mlstm_chunk_bwd(const void* dh, const void* q, const void* k, const void* v,
     PassParams p{};
     p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = c.status; p.sched = c.status + 8;
     p.chunk_tiles = chunk / TILE; p.NB = c.NB; p.An_bound = c.An_bound; p.ident = c.ident;
+    p.dot_part_stride = static_cast<long long>(BH) * Spad;
     p.X = k; p.Y = k; p.Z = v;
     p.col_rel = c.ga; p.col_w = c.gaw; p.col_ref = c.a_ref; p.row_rel = c.gAn; p.row_ref = c.An_ref;
     p.out = c.U; p.b_out = c.zU;
@@ -484,7 +485,7 @@ int mlstm_chunk_bwd(const void* dh, const void* q, const void* k, const void* v,
     p.col_g = nullptr; p.states = c.states;
     p.out = dv; p.dot_src = nullptr; p.dot_out = nullptr;
     if ((rc = launch_pass_tc(DVC, p, dtype, dtype, st)) != MLSTM_OK) return rc;
-    return launch_df(f, w.dI, w.Rdot, df, di, BH, S, Spad, dtype, st);
+    return launch_df(f, w.dI, w.Rdot, df, di, BH, S, Spad, dtype, st, TC_DOT_PARTS, static_cast<long long>(BH) * Spad);
 }
 
 int mlstm_chunk_read_mb(const void* workspace, size_t workspace_bytes, float* m, float* b, int B, int NH, int S, int D, int dtype,

@@ -268,7 +268,8 @@ __global__ void bwd_prep_kernel(const HT* __restrict__ h, const HT* __restrict__
 template <typename T>
 __global__ void __launch_bounds__(SCAN_THREADS) df_kernel(const T* __restrict__ f, const float* __restrict__ dI,
                                                           const float* __restrict__ R, T* __restrict__ df,
-                                                          T* __restrict__ di, int S, int Spad) {
+                                                          T* __restrict__ di, int S, int Spad, int nparts,
+                                                          long long part_stride) {
     __shared__ double wsum[32];
     __shared__ double carry_sum;
     const int bh = blockIdx.x;
@@ -280,8 +281,13 @@ __global__ void __launch_bounds__(SCAN_THREADS) df_kernel(const T* __restrict__ 
         double x = 0.0;
         float dIv = 0.0f;
         if (in) {
-            dIv = dI[static_cast<size_t>(bh) * Spad + t];
-            x = static_cast<double>(dIv) - static_cast<double>(R[static_cast<size_t>(bh) * Spad + t]);
+            // dI and R arrive as partial row dots (one per gate group of the tensor-core passes): fixed order of addition
+            float Rv = 0.0f;
+            for (int k = 0; k < nparts; k++) {
+                dIv += dI[k * part_stride + static_cast<size_t>(bh) * Spad + t];
+                Rv += R[k * part_stride + static_cast<size_t>(bh) * Spad + t];
+            }
+            x = static_cast<double>(dIv) - static_cast<double>(Rv);
         }
         const double G = block_scan_add(x, wsum, carry_sum);  // inclusive
         if (in) {
@@ -500,17 +506,18 @@ int launch_bwd_prep(const void* h, const void* dh, const float* b, const float* 
 }
 
 int launch_df(const void* f, const float* dI, const float* R, void* df, void* di, int BH, int S, int Spad, int dtype,
-              cudaStream_t st) {
+              cudaStream_t st, int nparts, long long part_stride) {
     switch (dtype) {
         case MLSTM_DT_F32:
-            df_kernel<float><<<BH, SCAN_THREADS, 0, st>>>((const float*)f, dI, R, (float*)df, (float*)di, S, Spad);
+            df_kernel<float><<<BH, SCAN_THREADS, 0, st>>>((const float*)f, dI, R, (float*)df, (float*)di, S, Spad, nparts, part_stride);
             break;
         case MLSTM_DT_F16:
-            df_kernel<__half><<<BH, SCAN_THREADS, 0, st>>>((const __half*)f, dI, R, (__half*)df, (__half*)di, S, Spad);
+            df_kernel<__half><<<BH, SCAN_THREADS, 0, st>>>((const __half*)f, dI, R, (__half*)df, (__half*)di, S, Spad, nparts,
+                                                          part_stride);
             break;
         case MLSTM_DT_BF16:
             df_kernel<__nv_bfloat16><<<BH, SCAN_THREADS, 0, st>>>((const __nv_bfloat16*)f, dI, R, (__nv_bfloat16*)df,
-                                                                 (__nv_bfloat16*)di, S, Spad);
+                                                                 (__nv_bfloat16*)di, S, Spad, nparts, part_stride);
             break;
         default: return MLSTM_E_ARG;
     }

@@ -70,7 +70,9 @@ struct PassParams {
     const void* ogate;   // [BH, S, D] optional output gate pre-activation (scan API), input type
     // DQ / DK only: dot_out[r] = sum_d ACC[r, d] * dot_src[r, d], taken on the fp32 accumulator
     const void* dot_src; // [BH, S, D] input type (q for DQ, k for DK)
-    float* dot_out;      // [BH, Spad]
+    float* dot_out;      // [parts][BH, Spad]: the tensor-core passes write one partial per gate group (4 parts,
+                         // dot_part_stride floats apart; df_kernel adds them up), the CUDA-core pass one total
+    long long dot_part_stride;
     // chunkwise passes only
     int chunk_tiles;         // tiles per block
     int NB;                  // blocks per slice
@@ -143,8 +145,10 @@ int launch_state_scan(const float* U, const float* zU, const double* An_bound, c
                       const double* summary = nullptr, void* statesT16 = nullptr, int reverse = 0);
 int launch_bwd_prep(const void* h, const void* dh, const float* b, const float* m, const float* gAn, float* gB,
                     float* gBw, float* g, void* dh16, int BH, int S, int Spad, int D, int h_dtype, int dtype, cudaStream_t st);
+// dI, R: `nparts` partial vectors each, `part_stride` floats apart (see PassParams::dot_out)
 int launch_df(const void* f, const float* dI, const float* R, void* df, void* di, int BH, int S, int Spad, int dtype,
-              cudaStream_t st);
+              cudaStream_t st, int nparts = 1, long long part_stride = 0);
+constexpr int TC_DOT_PARTS = 4;   // gate groups of the tensor-core passes
 int launch_pass_simt(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st);
 int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st);
 bool tc_supported(int S, int D, int in_dtype);

@@ -834,10 +834,8 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     }
                 }
             }
-            if ((IS_DQ || IS_DK) && p.dot_out) {
-                const float dsum = exchange(dot);
-                if (ok && grp == 0) p.dot_out[vec_base + grow] = row_ok ? dsum : 0.0f;
-            }
+            // one partial per gate group: adding them up is left to the dF kernel, so that the groups need not meet here
+            if ((IS_DQ || IS_DK) && p.dot_out) p.dot_out[grp * p.dot_part_stride + vec_base + grow] = row_ok ? dot : 0.0f;
         }
         if (!ok) break;
         // ---- on to the next item

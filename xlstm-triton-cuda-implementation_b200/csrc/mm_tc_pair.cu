@@ -552,10 +552,9 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                     }
                 }
             }
-            if ((MODE == DQ || MODE == DK) && p.dot_out) {
-                const float dsum = exchange(dot);
-                if (ok && grp == 0 && active) p.dot_out[vec_base + grow] = row_ok ? dsum : 0.0f;
-            }
+            // one partial per gate group: adding them up is left to the dF kernel, so that the groups need not meet here
+            if ((MODE == DQ || MODE == DK) && p.dot_out && active)
+                p.dot_out[grp * p.dot_part_stride + vec_base + grow] = row_ok ? dot : 0.0f;
         }
         if (!ok) break;
         // ---- on to the next item
