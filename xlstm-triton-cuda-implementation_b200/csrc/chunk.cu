@@ -62,7 +62,9 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
                     : make_float4(0.f, 0.f, 0.f, 0.f);
     const double* bound = An_bound + static_cast<size_t>(bh) * (NB + 1);
     const double lb = late_bound ? late_bound[bh] : INFINITY;
-    constexpr int PF = 8;  // blocks whose contributions are fetched ahead of the serial update
+    // blocks whose contributions are fetched ahead of the serial update: the walk is bound by memory latency, and
+    // 16 loads of 16 bytes in flight per thread keep about 60 KB per SM on the way
+    constexpr int PF = 16;
     for (int k0 = 0; k0 < NB; k0 += PF) {
         float4 u[PF];
         float d[PF], c[PF];
@@ -255,7 +257,7 @@ int launch_state_scan(const float* U, const float* zU, const double* An_bound, c
                       void* states16, float* zstate, float* S_end, float* z_end, int BH, int NB, int D, int dtype,
                       cudaStream_t st, const double* late_bound, float* rec, size_t rec_stride, const double* summary,
                       void* statesT16, int reverse) {
-    const int threads = 256;
+    const int threads = 128;   // small blocks: a slice has about 4 K threads of work, which should spread over all SMs
     const int work = (D * D + D) / 4;
     dim3 grid((work + threads - 1) / threads, BH);
     size_t s_stride = static_cast<size_t>(D) * D, z_stride = D;

@@ -886,10 +886,10 @@ EncodeTiledFn get_encode() {
 // few maps in several passes: each host thread keeps the last maps it encoded, keyed by everything that goes in.
 struct MapKey {
     const void* base;
-    int n2, n1, n0, dtype, swizzle, box_rows, box_bytes;
+    int n2, n1, n0, dtype, swizzle, box_rows, box_bytes, box_groups;
     bool operator==(const MapKey& o) const {
         return base == o.base && n2 == o.n2 && n1 == o.n1 && n0 == o.n0 && dtype == o.dtype && swizzle == o.swizzle &&
-               box_rows == o.box_rows && box_bytes == o.box_bytes;
+               box_rows == o.box_rows && box_bytes == o.box_bytes && box_groups == o.box_groups;
     }
 };
 struct MapCache {
@@ -913,7 +913,7 @@ thread_local MapCache g_map_cache;
 // [N2, N1, N0] tensor (N0 contiguous): boxes of box_bytes x box_rows, given swizzle, zero fill outside the tensor
 int encode_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, CUtensorMapSwizzle swz, int box_rows,
                int box_bytes, CUtensorMapL2promotion promo) {
-    const MapKey key{base, N2, N1, N0, dtype, static_cast<int>(swz), box_rows, box_bytes};
+    const MapKey key{base, N2, N1, N0, dtype, static_cast<int>(swz), box_rows, box_bytes, 0};
     if (const CUtensorMap* hit = g_map_cache.find(key)) {
         *map = *hit;
         return MLSTM_OK;
@@ -1053,6 +1053,37 @@ int tc_make_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int 
 
 int tc_make_map_out(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, int box_rows) {
     return encode_map(map, base, N2, N1, N0, dtype, CU_TENSOR_MAP_SWIZZLE_64B, box_rows, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+}
+
+// The same [N2, N1, N0] tensor seen as [N2, N0 / G, N1, G] with G = 128 bytes of elements: one box covers box_rows rows
+// of box_groups neighbouring 128-byte column groups and lands in shared memory group after group (each group a
+// box_rows x 128-byte block, 128-byte swizzled).  That is the layout of an MN-major MMA operand that is several
+// column groups wide, fetched with ONE copy instead of one per group.  Coordinates: {0, row, group, slice}.
+int tc_make_map_groups(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, bool atom32, int box_rows,
+                       int box_groups) {
+    const CUtensorMapSwizzle swz = atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
+    const MapKey key{base, N2, N1, N0, dtype, static_cast<int>(swz), box_rows, 128, box_groups};
+    if (const CUtensorMap* hit = g_map_cache.find(key)) {
+        *map = *hit;
+        return MLSTM_OK;
+    }
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return MLSTM_E_CUDA;
+    const cuuint64_t es = dtype == MLSTM_DT_F32 ? 4 : 2;
+    const cuuint64_t G = 128 / es;
+    if (N0 % static_cast<int>(G) != 0) return MLSTM_E_SHAPE;
+    cuuint64_t dims[4] = {G, static_cast<cuuint64_t>(N1), static_cast<cuuint64_t>(N0) / G, static_cast<cuuint64_t>(N2)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(N0) * es, 128, static_cast<cuuint64_t>(N1) * N0 * es};
+    cuuint32_t box[4] = {static_cast<cuuint32_t>(G), static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(box_groups), 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUtensorMapDataType dt = dtype == MLSTM_DT_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                             : dtype == MLSTM_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUresult r = enc(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return MLSTM_E_CUDA;
+    g_map_cache.put(key, *map);
+    return MLSTM_OK;
 }
 
 int tc_sm_count() { return sm_count(); }

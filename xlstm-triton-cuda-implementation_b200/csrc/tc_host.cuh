@@ -14,6 +14,9 @@ int tc_make_map(CUtensorMap* map, const void* base, int N2, int N1, int N0, int 
 // (in shared memory the 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3) of that row; the buffer
 // is 512-byte aligned).
 int tc_make_map_out(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, int box_rows);
+// Several 128-byte column groups per box (4-D view of the same tensor), see mm_tc.cu
+int tc_make_map_groups(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, bool atom32, int box_rows,
+                       int box_groups);
 int tc_sm_count();    // SMs of the current device (cached), -1 on error
 int tc_slice_set();   // slices interleaved in the work-item order
 
