@@ -15,14 +15,24 @@
 //                  one work item = 128 query rows x 256 output columns, contraction over the causal
 //                  extent of the row tile; n_r = max(|b_r|, exp(-m_r)) + 1e-6 from pass 1's row sums
 //
-// Both passes are the same persistent warp-specialised GEMM: warp 0 = TMA producer (ring of 48 KB
-// stages: a 128 x 128-byte A box and 32 KB of B), warp 1 = MMA issuer (tcgen05.mma, M = 128, N = 256,
-// both operands from shared memory; fp32 inputs are read as tf32, 16-bit inputs as they are),
-// warps 2-5 = epilogue (one TMEM lane = one row per thread; per-warp staging and TMA stores).
-// TMEM holds two 256-column accumulators, so the epilogue of one item overlaps the contraction of the
-// next.  Work items come from a global counter, heaviest first, published to the roles through an
-// eight-deep shared-memory ring.  Every wait is bounded (see ptx_sm100.cuh); a wait that runs out ends
-// the kernel with a code in the status word.
+// Both passes are the same persistent warp-specialised GEMM: warp 0 = TMA producer (ring of stages:
+// a 128 x 128-byte A box and this CTA's share of B), warp 1 = MMA issuer (tcgen05.mma, N = 256, both
+// operands from shared memory; fp32 inputs are read as tf32, 16-bit inputs as they are), warps 2-5 =
+// epilogue (one TMEM lane = one row per thread; per-warp staging and TMA stores).  TMEM holds two
+// 256-column accumulators, so the epilogue of one item overlaps the contraction of the next.  Work
+// items come from a global counter, heaviest first, published to the roles through an eight-deep
+// shared-memory ring.  Every wait is bounded (see ptx_sm100.cuh); a wait that runs out ends the
+// kernel with a code in the status word.
+//
+// With fp32 operands a 128 x 256 tile needs 48 KB of operands for 512 cycles of MMA, and the measured
+// rate of the copy engine into one SM (about 45 bytes per cycle here) makes both passes wait on loads.
+// The PAIR form therefore runs on clusters of two CTAs (tcgen05.mma.cta_group::2, M = 256): an item is
+// 256 query rows x 256 columns, each CTA loads its own 128 rows of A and HALF of B (32 KB per stage and
+// CTA instead of 48 KB) and keeps its 128 rows of the accumulator in its own TMEM.  Signals that cross
+// the pair as in mm_tc_pair.cu: loads of both CTAs count on the leader's "full" barrier, the leader's
+// MMA thread commits to both CTAs' "empty" / "accumulator full" barriers, epilogue warps of both CTAs
+// arrive on the leader's "accumulator drained" barrier, and work items travel from the leader's
+// producer to the follower's through distributed shared memory.
 #include <atomic>
 #include <type_traits>
 
@@ -40,21 +50,28 @@ constexpr int NTHREADS_G = 192;
 constexpr int TN = 256;                       // columns of a work item
 constexpr int A_BYTES = 128 * 128;            // 128 rows x 128 bytes
 constexpr int B_BYTES = 256 * 128;            // pass 1: 256 key rows x 128 bytes; pass 2: TN columns x one chunk of rows
-constexpr int STAGE_BYTES_G = A_BYTES + B_BYTES;
-constexpr int NSTAGE = 4;
 constexpr int OUT_WARP_BYTES = 2 * 2048;      // per epilogue warp: two staging buffers of 32 rows x 64 bytes
 constexpr int NEPI = 4;                       // epilogue warps
 constexpr int ITEM_RING = 8;
-constexpr int NBAR_G = 2 * NSTAGE + 4 + ITEM_RING;
-constexpr int SMEM_BYTES_G = NSTAGE * STAGE_BYTES_G + NEPI * OUT_WARP_BYTES + NBAR_G * 8 + 128;
+constexpr int GATE_WARP_BYTES = 2 * 4096;     // pass 2, per epilogue warp: two tiles (32 rows x 128 bytes) of the output gate
+template <bool PAIR, int PHASE>
+struct GemmCfg {
+    static constexpr int B_CTA = PAIR ? B_BYTES / 2 : B_BYTES;    // this CTA's share of B per stage
+    static constexpr int STAGE = A_BYTES + B_CTA;
+    static constexpr int IN_BYTES = PHASE == 1 ? NEPI * GATE_WARP_BYTES : 0;   // output-gate tiles of pass 2
+    static constexpr int NSTAGE = PAIR ? (PHASE == 1 ? 5 : 6) : (PHASE == 1 ? 3 : 4);
+    static constexpr int NBAR = 2 * NSTAGE + 4 + 2 * ITEM_RING + 2 * NEPI;
+    static constexpr int SMEM = NSTAGE * STAGE + NEPI * OUT_WARP_BYTES + IN_BYTES + NBAR * 8 + 128;
+    static_assert(SMEM <= 232448, "exceeds the shared memory of a CTA");
+};
 constexpr long long WAIT_LIMIT_G = 4000000000LL;   // cycles (about two seconds)
 constexpr float MAX_ROW_EXP2_G = 60.0f;
 constexpr int SLEEP_NS_G = 64;
-static_assert(SMEM_BYTES_G <= 232448, "exceeds the shared memory of a CTA");
 
 struct GemmParams {
     int S, Spad, BH, D;
     int NT;        // 128-row tiles per slice
+    int NP;        // pairs of row tiles per slice (PAIR form)
     int NKT;       // 256-column key tiles per slice
     int NVS;       // 256-column output slices
     int per_head;  // pass 1: work items per slice
@@ -86,10 +103,14 @@ __device__ __forceinline__ void bulk_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 
-template <int PHASE, int ABFMT>
+template <int PHASE, int ABFMT, bool PAIR>
 __global__ void __launch_bounds__(NTHREADS_G, 1)
 mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                const __grid_constant__ CUtensorMap tmO, const GemmParams p) {
+                const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmG, const GemmParams p) {
+    using G = GemmCfg<PAIR, PHASE>;
+    constexpr int NSTAGE = G::NSTAGE;
+    constexpr int STAGE_BYTES_G = G::STAGE;
+    constexpr int NBAR_G = G::NBAR;
     constexpr bool TF32 = ABFMT == 2;
     constexpr int ES = TF32 ? 4 : 2;
     constexpr int KC = 128 / ES;                 // contraction elements per stage (one 128-byte row)
@@ -106,44 +127,55 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
     uint8_t* sOut = smem + NSTAGE * STAGE_BYTES_G;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + NEPI * OUT_WARP_BYTES);
+    uint8_t* sIn = sOut + NEPI * OUT_WARP_BYTES;      // pass 2: output-gate tiles (1024-byte aligned: stages and staging are)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sIn + G::IN_BYTES);
     uint64_t* bar_full = bars;
     uint64_t* bar_empty = bars + NSTAGE;
     uint64_t* bar_accfull = bars + 2 * NSTAGE;        // [2]
     uint64_t* bar_accempty = bar_accfull + 2;         // [2]
-    uint64_t* bar_item = bar_accempty + 2;            // [ITEM_RING]
+    uint64_t* bar_item = bar_accempty + 2;            // [ITEM_RING] work item published inside the CTA
+    uint64_t* bar_item_in = bar_item + ITEM_RING;     // [ITEM_RING] PAIR, follower: work item arrived from the leader
+    uint64_t* bar_gate = bar_item_in + ITEM_RING;     // [NEPI][2] pass 2: output-gate tile loaded (one pair per epilogue warp)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBAR_G);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    volatile int* item_ids = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [ITEM_RING]
+    volatile int* item_ids = reinterpret_cast<volatile int*>(tmem_slot + 2);                 // [ITEM_RING]
+    volatile int* item_in = reinterpret_cast<volatile int*>(tmem_slot + 2 + ITEM_RING);      // [ITEM_RING]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const bool misaligned = (smem_u32(smem) & 1023u) != 0;   // the swizzled tiles need a 1024-byte aligned base
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;      // 0 = leader
+    auto at_leader = [&](const void* local) { return mapa_u32(smem_u32(local), 0u); };
+    auto at_peer = [&](const void* local) { return mapa_u32(smem_u32(local), rank ^ 1u); };
 
+    // qt: this CTA's 128-row tile (PAIR: tile 2 * pair + rank, which may lie past the end of an odd-length slice:
+    // such a half loads zeros and only keeps the protocol going); ct: key tile (pass 1) or output slice (pass 2)
     struct Item {
-        int bh, qt, ct, nchunks;   // ct: key tile (pass 1) or output slice (pass 2)
+        int bh, qt, ct, nchunks;
     };
     auto decode = [&](int id) {
         Item it;
         if (PHASE == GATE) {
             it.bh = id / p.per_head;
             int idx = id - it.bh * p.per_head;
-            int qt = 0;
-            while (idx >= qt / 2 + 1) {   // row tile qt has qt/2 + 1 key tiles on or below the diagonal
-                idx -= qt / 2 + 1;
-                qt++;
+            int g = 0;   // row tile (PAIR: pair of row tiles) g has ntiles(g) key tiles on or below its diagonal
+            while (idx >= (PAIR ? g + 1 : g / 2 + 1)) {
+                idx -= PAIR ? g + 1 : g / 2 + 1;
+                g++;
             }
-            it.qt = qt;
+            it.qt = PAIR ? 2 * g + static_cast<int>(rank) : g;
             it.ct = idx;
             it.nchunks = p.D / KC;
         } else {
             const int per_w = p.BH * p.NVS;
             const int w = id / per_w;
             const int rem = id - w * per_w;
-            it.qt = p.NT - 1 - w;            // longest contractions first
+            const int g = (PAIR ? p.NP : p.NT) - 1 - w;   // longest contractions first
+            it.qt = PAIR ? 2 * g + static_cast<int>(rank) : g;
             it.bh = rem / p.NVS;
             it.ct = rem - it.bh * p.NVS;
-            it.nchunks = (it.qt + 1) * TILE / KC;
+            // the causal extent of the (pair's lower) row tile; the gated matrix holds zeros right of a tile's diagonal
+            it.nchunks = (PAIR ? min((2 * g + 2) * TILE, p.Spad) : (g + 1) * TILE) / KC;
         }
         return it;
     };
@@ -155,18 +187,28 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         for (int k = 0; k < 2; k++) {
             mbar_init(&bar_accfull[k], 1);
-            mbar_init(&bar_accempty[k], NEPI);
+            mbar_init(&bar_accempty[k], PAIR ? 2 * NEPI : NEPI);
         }
-        for (int k = 0; k < ITEM_RING; k++) mbar_init(&bar_item[k], 1);
+        for (int k = 0; k < ITEM_RING; k++) {
+            mbar_init(&bar_item[k], 1);
+            mbar_init(&bar_item_in[k], 1);
+        }
+        for (int k = 0; k < 2 * NEPI; k++) mbar_init(&bar_gate[k], 1);
         *abort_flag = misaligned ? 1 : 0;
         fence_mbar_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, 512);
-        tmem_relinquish();
+        if constexpr (PAIR) {
+            tmem_alloc_pair(tmem_slot, 512);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, 512);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();   // the peer's barriers are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -178,8 +220,18 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             int seq = 0;   // stages filled so far
             bool ok = true;
             for (int n = 0; ok; n++) {
-                int id = atomicAdd(p.counter, 1);
-                if (id >= p.items) id = -1;
+                int id;
+                if (rank == 0) {
+                    id = atomicAdd(p.counter, 1);
+                    if (id >= p.items) id = -1;
+                    if constexpr (PAIR) {   // to the follower's producer: cluster-scope release, once per item
+                        st_cluster_u32(at_peer(const_cast<int*>(&item_in[n % ITEM_RING])), static_cast<uint32_t>(id));
+                        mbar_arrive_cluster(at_peer(&bar_item_in[n % ITEM_RING]));
+                    }
+                } else {
+                    ok = mbar_wait_cluster<SLEEP_NS_G>(&bar_item_in[n % ITEM_RING], (n / ITEM_RING) & 1, abort_flag, WAIT_LIMIT_G);
+                    id = ok ? item_in[n % ITEM_RING] : -1;
+                }
                 item_ids[n % ITEM_RING] = id;
                 mbar_arrive(&bar_item[n % ITEM_RING]);   // release: the id is visible to whoever passes the wait
                 if (id < 0) break;
@@ -192,29 +244,50 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
                     uint8_t* sa = smem + s * STAGE_BYTES_G;
                     uint8_t* sb = sa + A_BYTES;
-                    mbar_expect_tx(&bar_full[s], STAGE_BYTES_G);
-                    // A: rows of the query tile, one 128-byte chunk of the contraction (pass 1: of the head
-                    // dimension of Q; pass 2: of the key positions of W)
-                    tma_load_3d(sa, &tmA, &bar_full[s], c * KC, it.qt * TILE, it.bh);
-                    if (PHASE == GATE) {
-                        tma_load_3d(sb, &tmB, &bar_full[s], c * KC, it.ct * TN, it.bh);      // 256 key rows, same chunk
+                    // A: rows of this CTA's query tile, one 128-byte chunk of the contraction (pass 1: of the head
+                    // dimension of Q; pass 2: of the key positions of W).  B, pass 1: key rows of the same chunk (PAIR:
+                    // this CTA's 128 of the 256); pass 2: KC value rows x the item's columns (PAIR: this CTA's half of
+                    // them), all 128-byte column groups with ONE copy (a copy per group made the pass wait on the copy
+                    // engine: nine copies per stage ran at 2900 cycles per stage)
+                    if constexpr (PAIR) {
+                        if (rank == 0) mbar_expect_tx(&bar_full[s], 2 * STAGE_BYTES_G);   // the loads of both CTAs
+                        const uint32_t lead_full = at_leader(&bar_full[s]);
+                        tma_load_3d_pair(sa, &tmA, lead_full, c * KC, it.qt * TILE, it.bh);
+                        if (PHASE == GATE)
+                            tma_load_3d_pair(sb, &tmB, lead_full, c * KC, it.ct * TN + static_cast<int>(rank) * (TN / 2), it.bh);
+                        else
+                            tma_load_4d_pair(sb, &tmB, lead_full, 0, c * KC,
+                                             it.ct * B2_GROUPS + static_cast<int>(rank) * (B2_GROUPS / 2), it.bh);
                     } else {
-                        // KC value rows x 256 columns: all 128-byte column groups with one copy (a copy per group
-                        // made this pass wait on the copy engine: nine copies per stage ran at 2900 cycles per stage)
-                        tma_load_4d(sb, &tmB, &bar_full[s], 0, c * KC, it.ct * B2_GROUPS, it.bh);
+                        mbar_expect_tx(&bar_full[s], STAGE_BYTES_G);
+                        tma_load_3d(sa, &tmA, &bar_full[s], c * KC, it.qt * TILE, it.bh);
+                        if (PHASE == GATE) tma_load_3d(sb, &tmB, &bar_full[s], c * KC, it.ct * TN, it.bh);
+                        else tma_load_4d(sb, &tmB, &bar_full[s], 0, c * KC, it.ct * B2_GROUPS, it.bh);
                     }
                 }
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------ MMA issuer (PAIR: the leader's, for both CTAs)
+        if (rank == 0) {
         // the whole warp runs the loop, one elected lane issues (tcgen05.mma wants warp-uniform operands)
         const bool issuer = elect_one();
         auto uni = [](int x) { return __shfl_sync(0xffffffffu, x, 0); };
         auto wait_u = [&](uint64_t* bar, uint32_t parity) { return mbar_wait_warp(bar, parity, abort_flag, WAIT_LIMIT_G); };
-        constexpr uint32_t idesc = make_idesc(ABFMT, 128, TN, 0, PHASE == GATE ? 0 : 1);
+        constexpr uint32_t idesc = make_idesc(ABFMT, PAIR ? 256 : 128, TN, 0, PHASE == GATE ? 0 : 1);
         const uint32_t smem_u = static_cast<uint32_t>(uni(static_cast<int>(smem_u32(smem))));
         const uint32_t tmem_u = static_cast<uint32_t>(uni(static_cast<int>(tmem_base)));
+        const uint32_t bars_u = smem_u + NSTAGE * STAGE_BYTES_G + NEPI * OUT_WARP_BYTES + G::IN_BYTES;        // this CTA's barriers ...
+        const uint32_t bars_peer_u = PAIR ? static_cast<uint32_t>(uni(static_cast<int>(at_peer(bars)))) : 0u;   // ... and the peer's
+        auto commit = [&](const uint64_t* bar) {   // one arrival (PAIR: in either CTA) once the MMAs issued so far are done
+            if constexpr (PAIR) {
+                const uint32_t off = static_cast<uint32_t>(bar - bars) * 8u;
+                tc_commit_pair(bars_u + off);
+                tc_commit_pair(bars_peer_u + off);
+            } else {
+                tc_commit(const_cast<uint64_t*>(bar));
+            }
+        };
         const uint64_t adesc0 = smem_desc_sw128(smem_u, 16, 1024);                      // K-major, 128-byte rows
         const uint64_t bdesc0 = PHASE == GATE ? smem_desc_sw128(smem_u + A_BYTES, 16, 1024)           // K-major, 256 rows
                                 : (TF32 ? smem_desc_sw128(smem_u + A_BYTES, B2_BOX, 512, 1)          // MN-major, 32-bit
@@ -243,21 +316,38 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const uint64_t ad = smem_desc_advance(adesc0, s * STAGE_BYTES_G);
                     const uint64_t bd = smem_desc_advance(bdesc0, s * STAGE_BYTES_G);
 #pragma unroll
-                    for (int kk = 0; kk < KC / KSTEP; kk++)
-                        mma_ss<TF32>(acc, smem_desc_advance(ad, kk * 32), smem_desc_advance(bd, kk * B_KSTEP_BYTES), idesc,
-                                     (c > 0 || kk > 0) ? 1u : 0u);
-                    tc_commit(&bar_empty[s]);
-                    if (c == it.nchunks - 1) tc_commit(&bar_accfull[buf]);
+                    for (int kk = 0; kk < KC / KSTEP; kk++) {
+                        if constexpr (PAIR)
+                            mma_ss_pair_fmt<TF32>(acc, smem_desc_advance(ad, kk * 32), smem_desc_advance(bd, kk * B_KSTEP_BYTES),
+                                                  idesc, (c > 0 || kk > 0) ? 1u : 0u);
+                        else
+                            mma_ss<TF32>(acc, smem_desc_advance(ad, kk * 32), smem_desc_advance(bd, kk * B_KSTEP_BYTES), idesc,
+                                         (c > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    commit(&bar_empty[s]);
+                    if (c == it.nchunks - 1) commit(&bar_accfull[buf]);
                 }
                 __syncwarp();
             }
         }
+        }   // rank == 0
     } else {
         // ------------------------------------------------------------ epilogue warps
         const int r = (warp & 3) * 32 + lane;          // TMEM lane == row inside the tile (lane quarter = warp % 4)
         const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
         uint8_t* stage = sOut + (warp - 2) * OUT_WARP_BYTES;
         if (lane == 0) prefetch_tmap(&tmO);
+        // Pass 2: the output gate o of this warp's 32 rows comes in tiles of 32 rows x 128 bytes through the copy
+        // engine, two tiles ahead of their use (per-thread loads of a row each, 32 lines per instruction, were what
+        // the whole pass waited for: 75 of its 100 microseconds at the reference demo's size).
+        [[maybe_unused]] uint8_t* gate_buf = sIn + (warp - 2) * GATE_WARP_BYTES;
+        [[maybe_unused]] uint64_t* gate_bar = bar_gate + (warp - 2) * 2;
+        [[maybe_unused]] int ngate = 0;   // gate tiles consumed by this warp: buffer and barrier phase follow it
+        constexpr int GATE_COLS = 128 / ES;               // columns of o per tile
+        constexpr int GATE_TILES = TN / GATE_COLS;        // tiles per item and warp
+        constexpr int GATE_TILE_BYTES = 32 * 128;
+        [[maybe_unused]] const bool gated = PHASE == APPLY && p.ogate != nullptr;
+        if (PHASE == APPLY && lane == 0) prefetch_tmap(&tmG);
         int nstore = 0;   // stores issued by this warp: alternates its two staging buffers
         bool ok = __all_sync(0xffffffffu, *abort_flag ? 0 : 1) != 0;
         // 32 rows x 64 bytes of `vals` (16 fp32 or 32 16-bit values per row, already converted) to global memory
@@ -285,13 +375,25 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const Item it = decode(id);
             const int buf = n & 1;
             const int grow = it.qt * TILE + r;
+            const bool active = it.qt < p.NT;      // PAIR: the second half of an odd last pair has no rows
             const bool row_ok = grow < p.S;
+            auto load_gate_tile = [&](int tile, int seq) {   // lane 0: tile `tile` of this item into buffer seq & 1
+                mbar_expect_tx(&gate_bar[seq & 1], GATE_TILE_BYTES);
+                tma_load_3d(gate_buf + (seq & 1) * GATE_TILE_BYTES, &tmG, &gate_bar[seq & 1], it.ct * TN + tile * GATE_COLS,
+                            it.qt * TILE + (warp & 3) * 32, it.bh);
+            };
+            if (gated && active && lane == 0) {
+                load_gate_tile(0, ngate);
+                load_gate_tile(1, ngate + 1);
+            }
             const size_t vec_base = static_cast<size_t>(it.bh) * p.Spad;
             const size_t ref_base = static_cast<size_t>(it.bh) * (p.Spad / REF_BLOCK);
             // row terms, requested before the accumulator wait
             double er_d = 0.0;
             float inv_n = 1.0f;
-            if (PHASE == GATE) {
+            if (!active) {
+                // nothing to read: the accumulator holds zeros and nothing is stored
+            } else if (PHASE == GATE) {
                 er_d = static_cast<double>(p.row_rel[vec_base + grow]) + p.row_ref[ref_base + grow / REF_BLOCK] +
                        static_cast<double>(p.er_add);
             } else {
@@ -307,7 +409,16 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const uint32_t acc = tmem_base + buf * TN + lane_bits;
             float rowsum = 0.0f;
             // pass 1: chunks right of the row tile's diagonal tile are never read by pass 2: not computed, not stored
-            const int nch = PHASE == GATE ? min(TN / 32, ((it.qt + 1) * TILE - it.ct * TN) / 32) : TN / 32;
+            const int nch = !active ? 0 : (PHASE == GATE ? min(TN / 32, ((it.qt + 1) * TILE - it.ct * TN) / 32) : TN / 32);
+            auto release_acc = [&]() {   // this warp's share of the accumulator is in registers (or not needed)
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (PAIR) mbar_arrive_remote(at_leader(&bar_accempty[buf]));
+                    else mbar_arrive(&bar_accempty[buf]);
+                }
+            };
+            if (nch == 0) release_acc();
 #pragma unroll 1
             for (int ch = 0; ch < nch; ch++) {
                 const int c0 = it.ct * TN + ch * 32;           // first column of the chunk (pass 1: key position)
@@ -323,16 +434,29 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         cv[q4 * 4 + 0] = e4.x; cv[q4 * 4 + 1] = e4.y; cv[q4 * 4 + 2] = e4.z; cv[q4 * 4 + 3] = e4.w;
                     }
                     er = static_cast<float>(er_d + p.col_ref[ref_base + c0 / REF_BLOCK]);
-                } else if (p.ogate && row_ok) {
-                    const InT* orow = reinterpret_cast<const InT*>(p.ogate) +
-                                      (static_cast<size_t>(it.bh) * p.S + grow) * p.D + c0;
+                } else if (gated) {
+                    // 32 columns of this row from the warp's gate tile (128-byte swizzle: the 16-byte piece j of row
+                    // r sits at piece j ^ (r & 7)); a tile holds GATE_COLS columns, i.e. one or two chunks
                     constexpr int VEC = 16 / ES;
+                    constexpr int CH_PER_TILE = GATE_COLS / 32;
+                    const int tile = ch / CH_PER_TILE, sub = ch % CH_PER_TILE;
+                    const int seq = ngate + tile;
+                    if (sub == 0) {
+                        ok = mbar_wait_warp<SLEEP_NS_G>(&gate_bar[seq & 1], (seq >> 1) & 1, abort_flag, WAIT_LIMIT_G);
+                        if (!ok) break;
+                    }
+                    const uint8_t* grow_smem = gate_buf + (seq & 1) * GATE_TILE_BYTES + lane * 128;
 #pragma unroll
                     for (int jv = 0; jv < 32 / VEC; jv++) {
-                        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(orow) + jv);
+                        const int piece = sub * (32 / VEC) + jv;
+                        const uint4 raw = *reinterpret_cast<const uint4*>(grow_smem + ((piece ^ (lane & 7)) << 4));
                         const InT* ev = reinterpret_cast<const InT*>(&raw);
 #pragma unroll
                         for (int j = 0; j < VEC; j++) cv[jv * VEC + j] = silu_f(to_f32<InT>(ev[j]));
+                    }
+                    if (sub == CH_PER_TILE - 1) {   // the tile is in registers: fetch the tile after next into its buffer
+                        __syncwarp();
+                        if (lane == 0 && tile + 2 < GATE_TILES) load_gate_tile(tile + 2, seq + 2);
                     }
                 } else {
 #pragma unroll
@@ -341,12 +465,7 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 uint32_t tv[32];
                 tmem_ld32(acc + ch * 32, tv);
                 tc_wait_ld();
-                if (ch == nch - 1) {
-                    // this warp's share of the accumulator is in registers: the item after next may overwrite it
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&bar_accempty[buf]);
-                }
+                if (ch == nch - 1) release_acc();   // the item after next may overwrite the accumulator
                 if (PHASE == GATE) {
                     if (diag) {
                         const int rel0 = c0 - it.qt * TILE;    // column index inside the diagonal tile
@@ -408,7 +527,27 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     store64(v, c0, y, it.bh);
                 }
             }
-            if (PHASE == GATE) p.bpart[(static_cast<size_t>(it.bh) * p.NKT + it.ct) * p.Spad + grow] = rowsum;
+            if (!ok) break;
+            if (gated && active) ngate += GATE_TILES;
+            if (PHASE == GATE && active) {
+                p.bpart[(static_cast<size_t>(it.bh) * p.NKT + it.ct) * p.Spad + grow] = rowsum;
+                if constexpr (PAIR) {
+                    // Pass 2 contracts a pair of row tiles over the causal extent of the lower one.  For the upper tile
+                    // that includes the 128 columns right of its diagonal tile, which nothing computes: they must read
+                    // as zeros (the workspace may hold anything).
+                    if (rank == 0 && it.ct * TN + nch * 32 < min((it.qt + 2) * TILE, p.Spad) && it.ct == it.qt / 2) {
+                        uint4 z[4];
+#pragma unroll
+                        for (int j4 = 0; j4 < 4; j4++) z[j4] = make_uint4(0u, 0u, 0u, 0u);
+                        const int y = it.qt * TILE + (warp & 3) * 32;
+                        for (int ch = nch; ch < TN / 32; ch++) {
+                            const int c0 = it.ct * TN + ch * 32;
+#pragma unroll
+                            for (int sub = 0; sub < NSUB; sub++) store64(z, c0 + sub * (64 / OUT_ES), y, it.bh);
+                        }
+                    }
+                }
+            }
         }
         if (lane == 0) bulk_wait_all();   // the last stores have left shared memory before the CTA goes away
         tc_fence_before();
@@ -421,23 +560,26 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         for (int k = 0; k < 64; k++) __nanosleep(16000);
         __syncthreads();
     }
+    if constexpr (PAIR) cluster_sync_all();   // neither CTA releases shared memory or TMEM the other may still touch
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        if constexpr (PAIR) tmem_dealloc_pair(tmem_base, 512);
+        else tmem_dealloc(tmem_base, 512);
     }
 }
 
-template <int PHASE, int ABFMT>
-int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& p, bool zero_counter,
-                cudaStream_t st) {
-    auto kern = mlstm_scan_gemm<PHASE, ABFMT>;
+template <int PHASE, int ABFMT, bool PAIR>
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mg, const GemmParams& p,
+                bool zero_counter, cudaStream_t st) {
+    auto kern = mlstm_scan_gemm<PHASE, ABFMT, PAIR>;
+    constexpr int smem = GemmCfg<PAIR, PHASE>::SMEM;
     cudaError_t ce;
     {
         static std::atomic<bool> opted[64];
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MLSTM_E_CUDA;
         if (!opted[dev].load(std::memory_order_acquire)) {
-            ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_G);
+            ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
             if (ce != cudaSuccess) {
                 cudaGetLastError();
                 return note_cuda_error(ce, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
@@ -451,13 +593,33 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
         ce = cudaMemsetAsync(p.counter, 0, sizeof(int), st);
         if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
     }
-    const unsigned grid = static_cast<unsigned>(p.items < sms ? p.items : sms);   // persistent: one CTA per SM
-    kern<<<grid, NTHREADS_G, SMEM_BYTES_G, st>>>(ma, mb, mo, p);
-    ce = cudaGetLastError();
-    return ce == cudaSuccess ? MLSTM_OK : note_cuda_error(ce, "launch of mlstm_scan_gemm");
+    // persistent: one CTA (PAIR: one CTA of a cluster of two) per SM
+    const int units = PAIR ? sms / 2 : sms;
+    const int n = p.items < units ? p.items : units;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(PAIR ? 2 * n : n), 1, 1);
+    cfg.blockDim = dim3(NTHREADS_G, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = PAIR ? 2 : 1;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    ce = cudaLaunchKernelEx(&cfg, kern, ma, mb, mo, mg, p);
+    if (ce != cudaSuccess) {
+        cudaGetLastError();
+        return note_cuda_error(ce, "launch of mlstm_scan_gemm");
+    }
+    return MLSTM_OK;
 }
 
-template <int ABFMT>
+// The pair form needs at least two row tiles per slice and two SMs; a single tile runs on one CTA.
+inline bool use_pairs(int Spad) { return Spad > TILE && tc_sm_count() >= 2; }
+
+template <int ABFMT, bool PAIR>
 int run_group(const void* q, const void* k, const void* v, const void* o, float* h, void* W, const ScanGemmArgs& a, int bh0,
               int nbh, int dtype, cudaStream_t st) {
     const bool zero_counters = bh0 > 0;   // the caller zeroed both counters with the status word for the first group
@@ -471,10 +633,12 @@ int run_group(const void* q, const void* k, const void* v, const void* o, float*
     GemmParams p{};
     p.S = a.S; p.Spad = a.Spad; p.BH = nbh; p.D = a.D;
     p.NT = a.Spad / TILE;
+    p.NP = (p.NT + 1) / 2;
     p.NKT = (a.Spad + TN - 1) / TN;
     p.NVS = a.D / TN;
     p.per_head = 0;
-    for (int qt = 0; qt < p.NT; qt++) p.per_head += qt / 2 + 1;
+    if (PAIR) for (int g = 0; g < p.NP; g++) p.per_head += g + 1;
+    else for (int qt = 0; qt < p.NT; qt++) p.per_head += qt / 2 + 1;
     const size_t vec0 = static_cast<size_t>(bh0) * a.Spad, ref0 = static_cast<size_t>(bh0) * (a.Spad / REF_BLOCK);
     p.row_rel = a.gAn + vec0; p.row_ref = a.An_ref + ref0;
     p.col_rel = a.ga + vec0; p.col_w = a.gaw + vec0; p.col_ref = a.a_ref + ref0;
@@ -487,19 +651,29 @@ int run_group(const void* q, const void* k, const void* v, const void* o, float*
     CUtensorMap ma, mb, mo;
     // ---- pass 1: W = gate(Q K^T)
     if ((rc = tc_make_map(&ma, qg, nbh, a.S, a.D, dtype, false, 128)) != MLSTM_OK) return rc;
-    if ((rc = tc_make_map(&mb, kg, nbh, a.S, a.D, dtype, false, 256)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map(&mb, kg, nbh, a.S, a.D, dtype, false, PAIR ? TN / 2 : TN)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map_out(&mo, W, nbh, a.Spad, a.Spad, dtype, 32)) != MLSTM_OK) return rc;
     p.items = p.per_head * nbh;
     p.counter = a.counters;
-    if ((rc = launch_gemm<GATE, ABFMT>(ma, mb, mo, p, zero_counters, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gemm<GATE, ABFMT, PAIR>(ma, mb, mo, mo, p, zero_counters, st)) != MLSTM_OK) return rc;
     // ---- pass 2: h = (W V) / n * silu(o)
     constexpr int KC = ABFMT == 2 ? 32 : 64;
+    constexpr int GROUPS = TN * (ABFMT == 2 ? 4 : 2) / 128;   // 128-byte column groups of an item's 256 columns
     if ((rc = tc_make_map(&ma, W, nbh, a.Spad, a.Spad, dtype, false, 128)) != MLSTM_OK) return rc;
-    if ((rc = tc_make_map_groups(&mb, vg, nbh, a.S, a.D, dtype, ABFMT == 2, KC, TN * (ABFMT == 2 ? 4 : 2) / 128)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map_groups(&mb, vg, nbh, a.S, a.D, dtype, ABFMT == 2, KC, PAIR ? GROUPS / 2 : GROUPS)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map_out(&mo, hg, nbh, a.S, a.D, MLSTM_DT_F32, 32)) != MLSTM_OK) return rc;
-    p.items = p.NT * nbh * p.NVS;
+    CUtensorMap mg = mo;   // output gate: tiles of 32 rows x 128 bytes, one per epilogue warp and step
+    if (og && (rc = tc_make_map(&mg, og, nbh, a.S, a.D, dtype, false, 32)) != MLSTM_OK) return rc;
+    p.items = (PAIR ? p.NP : p.NT) * nbh * p.NVS;
     p.counter = a.counters + 1;
-    return launch_gemm<APPLY, ABFMT>(ma, mb, mo, p, zero_counters, st);
+    return launch_gemm<APPLY, ABFMT, PAIR>(ma, mb, mo, mg, p, zero_counters, st);
+}
+
+template <int ABFMT>
+int run_group_any(const void* q, const void* k, const void* v, const void* o, float* h, void* W, const ScanGemmArgs& a, int bh0,
+                  int nbh, int dtype, cudaStream_t st) {
+    if (use_pairs(a.Spad)) return run_group<ABFMT, true>(q, k, v, o, h, W, a, bh0, nbh, dtype, st);
+    return run_group<ABFMT, false>(q, k, v, o, h, W, a, bh0, nbh, dtype, st);
 }
 
 }  // namespace
@@ -537,9 +711,9 @@ int launch_scan_gemm(const void* q, const void* k, const void* v, const void* o,
         const int nbh = a.BH - bh0 < group ? a.BH - bh0 : group;
         int rc;
         switch (dtype) {
-            case MLSTM_DT_F32: rc = run_group<2>(q, k, v, o, h, W, a, bh0, nbh, dtype, st); break;
-            case MLSTM_DT_BF16: rc = run_group<1>(q, k, v, o, h, W, a, bh0, nbh, dtype, st); break;
-            case MLSTM_DT_F16: rc = run_group<0>(q, k, v, o, h, W, a, bh0, nbh, dtype, st); break;
+            case MLSTM_DT_F32: rc = run_group_any<2>(q, k, v, o, h, W, a, bh0, nbh, dtype, st); break;
+            case MLSTM_DT_BF16: rc = run_group_any<1>(q, k, v, o, h, W, a, bh0, nbh, dtype, st); break;
+            case MLSTM_DT_F16: rc = run_group_any<0>(q, k, v, o, h, W, a, bh0, nbh, dtype, st); break;
             default: return MLSTM_E_ARG;
         }
         if (rc != MLSTM_OK) return rc;
