@@ -36,6 +36,8 @@ __global__ void identity_kernel(T16* ident) {
 // contracts over the value dimension.  reverse: walk the blocks from the last to the first, which turns
 // the same recurrence into the backward's carried state R_{k-1} = exp(A_end(k-1) - A_end(k)) R_k + P_k
 // (block k then receives what the LATER blocks contribute).
+constexpr int SCAN_TB = 1024;   // blocks per tile of the factor tables of state_scan_kernel
+
 template <typename T16>
 __global__ void state_scan_kernel(const float* __restrict__ U, const float* __restrict__ zU,
                                   const double* __restrict__ An_bound, const float* __restrict__ S_in,
@@ -52,56 +54,70 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
         dst[0] = summary[2 * bh];
         dst[1] = summary[2 * bh + 1];
     }
-    if (e >= DD + D) return;
+    const bool valid = e < DD + D;     // threads past the end still help with the factor tables and the barriers
     const bool is_vec = e >= DD;
     const int off = is_vec ? e - DD : e;
     const size_t per_block = is_vec ? D : DD;
     const float* src = (is_vec ? zU : U) + static_cast<size_t>(bh) * NB * per_block + off;
     const float* init = is_vec ? z_in : S_in;
-    float4 s = init ? *reinterpret_cast<const float4*>(init + static_cast<size_t>(bh) * per_block + off)
-                    : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 s = (init && valid) ? *reinterpret_cast<const float4*>(init + static_cast<size_t>(bh) * per_block + off)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
     const double* bound = An_bound + static_cast<size_t>(bh) * (NB + 1);
     const double lb = late_bound ? late_bound[bh] : INFINITY;
-    // blocks whose contributions are fetched ahead of the serial update: the walk is bound by memory latency, and
-    // 16 loads of 16 bytes in flight per thread keep about 60 KB per SM on the way
+    // The two factors of a block (decay of the carried state, rescaling of the block's own contribution) are the
+    // same for every element: the CTA computes them once per tile of SCAN_TB blocks into shared memory (evaluated
+    // per thread and block they were most of the kernel's instructions: 107 per warp and block against about 20 now).
+    __shared__ float sd[SCAN_TB], sc[SCAN_TB];
+    // blocks whose contributions are fetched ahead of the serial update
     constexpr int PF = 16;
-    for (int k0 = 0; k0 < NB; k0 += PF) {
-        float4 u[PF];
-        float d[PF], c[PF];
-#pragma unroll
-        for (int j = 0; j < PF; j++) {
-            if (k0 + j < NB) {
-                const int kb = reverse ? NB - 1 - (k0 + j) : k0 + j;
-                u[j] = __ldg(reinterpret_cast<const float4*>(src + static_cast<size_t>(kb) * per_block));
-                const double b1 = bound[kb + 1], b0 = bound[kb];
-                const double b1c = fmin(b1, lb), b0c = fmin(b0, lb);
-                // exp(A_end(k-1) - A_end(k)); 0 for the first block when there is no inbound carry (bound = +inf)
-                d[j] = exp2f(static_cast<float>(b1c - b0c));
-                c[j] = exp2f(static_cast<float>(b1c - b1));   // 1 unless the late carry raised the block's stabiliser
-            }
+    for (int t0 = 0; t0 < NB; t0 += SCAN_TB) {
+        const int tn = min(SCAN_TB, NB - t0);
+        __syncthreads();   // the previous tile's factors are no longer read
+        for (int j = threadIdx.x; j < tn; j += blockDim.x) {
+            const int kb = reverse ? NB - 1 - (t0 + j) : t0 + j;
+            const double b1 = bound[kb + 1], b0 = bound[kb];
+            const double b1c = fmin(b1, lb), b0c = fmin(b0, lb);
+            // exp(A_end(k-1) - A_end(k)); 0 for the first block when there is no inbound carry (bound = +inf)
+            sd[j] = exp2f(static_cast<float>(b1c - b0c));
+            sc[j] = exp2f(static_cast<float>(b1c - b1));   // 1 unless the late carry raised the block's stabiliser
         }
+        __syncthreads();
+        if (!valid) continue;
+        for (int k0 = 0; k0 < tn; k0 += PF) {
+            float4 u[PF];
 #pragma unroll
-        for (int j = 0; j < PF; j++) {
-            if (k0 + j >= NB) break;
-            const int k = reverse ? NB - 1 - (k0 + j) : k0 + j;
-            if (is_vec) {
-                if (zstate) *reinterpret_cast<float4*>(zstate + (static_cast<size_t>(bh) * NB + k) * D + off) = s;
-            } else if (states || statesT) {
-                T16 o[4] = {from_f32<T16>(s.x), from_f32<T16>(s.y), from_f32<T16>(s.z), from_f32<T16>(s.w)};
-                if (states)
-                    *reinterpret_cast<uint2*>(states + (static_cast<size_t>(bh) * NB + k) * DD + off) = *reinterpret_cast<uint2*>(o);
-                if (statesT) {
-                    const int row = off / D, col = off - row * D;
-                    T16* dstT = statesT + (static_cast<size_t>(bh) * NB + k) * DD + static_cast<size_t>(col) * D + row;
-                    dstT[0] = o[0]; dstT[D] = o[1]; dstT[2 * D] = o[2]; dstT[3 * D] = o[3];
+            for (int j = 0; j < PF; j++) {
+                if (k0 + j < tn) {
+                    const int kb = reverse ? NB - 1 - (t0 + k0 + j) : t0 + k0 + j;
+                    u[j] = __ldg(reinterpret_cast<const float4*>(src + static_cast<size_t>(kb) * per_block));
                 }
             }
-            s.x = (d[j] == 0.0f ? 0.0f : d[j] * s.x) + c[j] * u[j].x;
-            s.y = (d[j] == 0.0f ? 0.0f : d[j] * s.y) + c[j] * u[j].y;
-            s.z = (d[j] == 0.0f ? 0.0f : d[j] * s.z) + c[j] * u[j].z;
-            s.w = (d[j] == 0.0f ? 0.0f : d[j] * s.w) + c[j] * u[j].w;
+#pragma unroll
+            for (int j = 0; j < PF; j++) {
+                if (k0 + j >= tn) break;
+                const int k = reverse ? NB - 1 - (t0 + k0 + j) : t0 + k0 + j;
+                if (is_vec) {
+                    if (zstate) *reinterpret_cast<float4*>(zstate + (static_cast<size_t>(bh) * NB + k) * D + off) = s;
+                } else if (states || statesT) {
+                    T16 o[4] = {from_f32<T16>(s.x), from_f32<T16>(s.y), from_f32<T16>(s.z), from_f32<T16>(s.w)};
+                    if (states)
+                        *reinterpret_cast<uint2*>(states + (static_cast<size_t>(bh) * NB + k) * DD + off) = *reinterpret_cast<uint2*>(o);
+                    if (statesT) {
+                        const int row = off / D, col = off - row * D;
+                        T16* dstT = statesT + (static_cast<size_t>(bh) * NB + k) * DD + static_cast<size_t>(col) * D + row;
+                        dstT[0] = o[0]; dstT[D] = o[1]; dstT[2 * D] = o[2]; dstT[3 * D] = o[3];
+                    }
+                }
+                const float d = sd[k0 + j], c = sc[k0 + j];
+                // a decay of exactly 0 (nothing carried in) must also wipe an inbound state that is not finite
+                s.x = (d == 0.0f ? 0.0f : d * s.x) + c * u[j].x;
+                s.y = (d == 0.0f ? 0.0f : d * s.y) + c * u[j].y;
+                s.z = (d == 0.0f ? 0.0f : d * s.z) + c * u[j].z;
+                s.w = (d == 0.0f ? 0.0f : d * s.w) + c * u[j].w;
+            }
         }
     }
+    if (!valid) return;
     float* dst = is_vec ? z_end : S_end;
     const size_t stride = is_vec ? z_end_stride : S_end_stride;
     if (dst) *reinterpret_cast<float4*>(dst + static_cast<size_t>(bh) * stride + off) = s;
