@@ -212,10 +212,21 @@ L2_BYTES = 126e6   # B200: inputs smaller than this are flushed out of L2 betwee
 
 
 def time_small(ctx, fn, iters=10, warmup=3, flush=True):
-    """Mean CUDA-event time (ms) of fn() over `iters` calls, L2 flushed before each (when asked), max over ranks."""
+    """Mean CUDA-event time (ms) of fn() over `iters` calls, max over ranks.  flush: L2 is flushed before every call
+    and every call is timed by itself (workloads that fit in L2)."""
     torch = ctx.torch
     for _ in range(warmup):
         fn()
+    if not flush:
+        # inputs larger than L2: the calls run back to back inside one timed region
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ctx.barrier()
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        ctx.barrier()
+        return ctx.max_over_ranks([e0.elapsed_time(e1) / iters])[0]
     total = 0.0
     for _ in range(iters):
         if flush:
