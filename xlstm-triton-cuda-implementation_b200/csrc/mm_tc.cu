@@ -1086,12 +1086,6 @@ int tc_make_map_groups(CUtensorMap* map, const void* base, int N2, int N1, int N
     return MLSTM_OK;
 }
 
-int tc_make_map_wide(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, int box_rows) {
-    const int es = dtype == MLSTM_DT_F32 ? 4 : 2;
-    const int cols = N0 < 256 ? N0 : 256;
-    return encode_map(map, base, N2, N1, N0, dtype, CU_TENSOR_MAP_SWIZZLE_NONE, box_rows, cols * es, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
-}
-
 int tc_sm_count() { return sm_count(); }
 
 int tc_slice_set() { return SLICE_SET_DEFAULT; }

@@ -121,15 +121,6 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uin
         : "memory");
 }
 
-// Brings a tile into L2 without a destination in shared memory.  Used with tensor maps whose boxes are a kilobyte
-// wide: DRAM then serves whole pages where the 128-byte-wide boxes of the swizzled operand loads would touch a
-// different page with every row.
-__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* m, int x, int y, int z) {
-    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
-                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z)
-                 : "memory");
-}
-
 // 4-D tile load (used for boxes that span several 128-byte column groups: {0, row, group, slice})
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2, int c3) {
     asm volatile(

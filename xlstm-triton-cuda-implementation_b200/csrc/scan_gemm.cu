@@ -106,8 +106,7 @@ __device__ __forceinline__ void bulk_wait_read() {
 template <int PHASE, int ABFMT, bool PAIR>
 __global__ void __launch_bounds__(NTHREADS_G, 1)
 mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmG,
-                const __grid_constant__ CUtensorMap tmPA, const __grid_constant__ CUtensorMap tmPB, const GemmParams p) {
+                const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmG, const GemmParams p) {
     using G = GemmCfg<PAIR, PHASE>;
     constexpr int NSTAGE = G::NSTAGE;
     constexpr int STAGE_BYTES_G = G::STAGE;
@@ -237,21 +236,6 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 mbar_arrive(&bar_item[n % ITEM_RING]);   // release: the id is visible to whoever passes the wait
                 if (id < 0) break;
                 const Item it = decode(id);
-                // What this item reads for the first time from DRAM, asked for in kilobyte-wide boxes ahead of the
-                // 128-byte-wide operand loads (which alone keep DRAM at a quarter of its rate: a new page with
-                // every row).  Pass 1: this CTA's rows of Q and of K over the whole head dimension; pass 2: the
-                // item's 128 x 256 tile of the output gate (V comes in kilobyte rows anyway, W out of L2).
-                if (PHASE == GATE) {
-                    const int wide = 1024 / ES;   // columns per prefetch box
-                    const int krow = it.ct * TN + (PAIR ? static_cast<int>(rank) * (TN / 2) : 0);
-                    for (int x = 0; x < p.D; x += wide) {
-                        if (it.qt < p.NT) tma_prefetch_3d(&tmPA, x, it.qt * TILE, it.bh);
-                        if (krow < p.S) tma_prefetch_3d(&tmPB, x, krow, it.bh);
-                        if (!PAIR && krow + TN / 2 < p.S) tma_prefetch_3d(&tmPB, x, krow + TN / 2, it.bh);
-                    }
-                } else if (p.ogate && it.qt < p.NT) {
-                    tma_prefetch_3d(&tmPB, it.ct * TN, it.qt * TILE, it.bh);
-                }
                 for (int c = 0; c < it.nchunks && ok; c++, seq++) {
                     const int s = seq % NSTAGE;
                     if (seq >= NSTAGE) {
@@ -585,8 +569,8 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 template <int PHASE, int ABFMT, bool PAIR>
-int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mg, const CUtensorMap& mpa,
-                const CUtensorMap& mpb, const GemmParams& p, bool zero_counter, cudaStream_t st) {
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mg, const GemmParams& p,
+                bool zero_counter, cudaStream_t st) {
     auto kern = mlstm_scan_gemm<PHASE, ABFMT, PAIR>;
     constexpr int smem = GemmCfg<PAIR, PHASE>::SMEM;
     cudaError_t ce;
@@ -624,7 +608,7 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    ce = cudaLaunchKernelEx(&cfg, kern, ma, mb, mo, mg, mpa, mpb, p);
+    ce = cudaLaunchKernelEx(&cfg, kern, ma, mb, mo, mg, p);
     if (ce != cudaSuccess) {
         cudaGetLastError();
         return note_cuda_error(ce, "launch of mlstm_scan_gemm");
@@ -671,10 +655,7 @@ int run_group(const void* q, const void* k, const void* v, const void* o, float*
     if ((rc = tc_make_map_out(&mo, W, nbh, a.Spad, a.Spad, dtype, 32)) != MLSTM_OK) return rc;
     p.items = p.per_head * nbh;
     p.counter = a.counters;
-    CUtensorMap mpa, mpb;   // kilobyte-wide boxes of 128 rows for the L2 prefetches
-    if ((rc = tc_make_map_wide(&mpa, qg, nbh, a.S, a.D, dtype, 128)) != MLSTM_OK) return rc;
-    if ((rc = tc_make_map_wide(&mpb, kg, nbh, a.S, a.D, dtype, 128)) != MLSTM_OK) return rc;
-    if ((rc = launch_gemm<GATE, ABFMT, PAIR>(ma, mb, mo, mo, mpa, mpb, p, zero_counters, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gemm<GATE, ABFMT, PAIR>(ma, mb, mo, mo, p, zero_counters, st)) != MLSTM_OK) return rc;
     // ---- pass 2: h = (W V) / n * silu(o)
     constexpr int KC = ABFMT == 2 ? 32 : 64;
     constexpr int GROUPS = TN * (ABFMT == 2 ? 4 : 2) / 128;   // 128-byte column groups of an item's 256 columns
@@ -685,8 +666,7 @@ int run_group(const void* q, const void* k, const void* v, const void* o, float*
     if (og && (rc = tc_make_map(&mg, og, nbh, a.S, a.D, dtype, false, 32)) != MLSTM_OK) return rc;
     p.items = (PAIR ? p.NP : p.NT) * nbh * p.NVS;
     p.counter = a.counters + 1;
-    if (og && (rc = tc_make_map_wide(&mpb, og, nbh, a.S, a.D, dtype, 128)) != MLSTM_OK) return rc;
-    return launch_gemm<APPLY, ABFMT, PAIR>(ma, mb, mo, mg, mpa, mpb, p, zero_counters, st);
+    return launch_gemm<APPLY, ABFMT, PAIR>(ma, mb, mo, mg, p, zero_counters, st);
 }
 
 template <int ABFMT>

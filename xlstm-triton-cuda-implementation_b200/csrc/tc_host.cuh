@@ -17,8 +17,6 @@ int tc_make_map_out(CUtensorMap* map, const void* base, int N2, int N1, int N0, 
 // Several 128-byte column groups per box (4-D view of the same tensor), see mm_tc.cu
 int tc_make_map_groups(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, bool atom32, int box_rows,
                        int box_groups);
-// Boxes of up to 256 elements x box_rows rows without swizzle: for L2 prefetches (no shared-memory destination).
-int tc_make_map_wide(CUtensorMap* map, const void* base, int N2, int N1, int N0, int dtype, int box_rows);
 int tc_sm_count();    // SMs of the current device (cached), -1 on error
 int tc_slice_set();   // slices interleaved in the work-item order
 
