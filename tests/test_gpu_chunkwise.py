@@ -174,6 +174,26 @@ def test_chunkwise_forward_backward_against_reference_golden(gc, golden_dir):
         assert orc.max_abs_rel(t[n].grad.float(), r) < TOL_16, n
 
 
+def test_chunkwise_backward_with_16_bit_h(gc):
+    """The backward through the C ABI with h and dh in the input type (no fp32 copy of h anywhere)."""
+    mc = importlib.import_module(PKG + ".mlstm_chunkwise")
+    x = gc.make_inputs(2, 2, 1280, 128, torch.bfloat16, f_mean=3.0, qkv_scale=128 ** -0.5, seed=12)
+    d = _dev(x)
+    seg = mc.ChunkSegment(*d, chunk_size=256)
+    seg.prepare(None)
+    h = seg.apply(None, h_dtype=torch.bfloat16)
+    m, b = seg.read_mb()
+    dh = x["dh"].bfloat16().cuda()
+    grads = mc.mlstm_chunkwise_backward(dh, *d, h, m, b, chunk_size=256)
+    torch.cuda.synchronize()
+    ref = gc.oracle_backward(x, torch.bfloat16)
+    for n, g, r in zip(("dq", "dk", "dv", "df", "di"), grads, ref):
+        assert orc.max_abs_rel(g.float(), r) < TOL_16, (n, orc.max_abs_rel(g.float(), r))
+    # m and b are what the parallel forward returns
+    hq, mq, bq = gc.PKG.mlstm_matmul_forward(*d, h_dtype=torch.bfloat16)
+    assert orc.max_abs_rel(m, mq) < 1e-5 and orc.max_abs_rel(b, bq) < TOL_16
+
+
 def test_scan_gradients_take_the_chunkwise_backward(gc):
     """mlstm_scan on a long 16-bit sequence with inputs that require gradients: chunkwise forward and backward
     behind the output gate, against autograd of the fp64 oracle."""

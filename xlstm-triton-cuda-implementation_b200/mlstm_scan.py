@@ -18,12 +18,12 @@ The library picks one of three forms by shape (``mlstm_scan_fwd`` in include/mls
 ``initial`` / ``return_state`` expose the carried state (S [B*NH, D, D] key-major, z [B*NH, D], F, A
 [B*NH] float64; see ``mlstm_chunkwise``) and need the chunkwise form's shapes.
 
-Arithmetic: 16-bit inputs always run on the tensor cores.  float32 inputs run on them with single tf32
-products and fp32 accumulation when ``allow_tf32`` is true (the default here; measured max-abs-rel
-error about 5e-4 to 1e-3, inside the reference's own 1e-2 check) and D is 64, 128, 256 or a multiple of
-256 up to 4096.  ``allow_tf32=False`` keeps fp32-level accuracy: the split tensor-core form at D = 64
-and 128 (three bf16 products per fp32 product, error about 1e-5), IEEE fp32 dot products on the CUDA
-cores elsewhere (much slower).
+Arithmetic: 16-bit inputs always run on the tensor cores.  float32 inputs: at D = 64 and 128 the split
+tensor-core form (three bf16 products per fp32 product, error about 1e-5, as fast as tf32 there), whatever
+``allow_tf32`` says; at D = 256 and at multiples of 256 up to 4096 single tf32 products with fp32
+accumulation when ``allow_tf32`` is true (the default here; measured max-abs-rel error about 5e-4 to 2e-3,
+inside the reference's own 1e-2 check), IEEE fp32 dot products on the CUDA cores (much slower) when it is
+false or at any other D.
 
 The reference's scan is forward only (README.md:97).  Here inputs that require gradients get them, behind
 the output gate's own derivative: long 16-bit sequences at D = 128 through the chunkwise forward and the
@@ -114,7 +114,7 @@ def mlstm_scan(q, k, v, f, i, o, reduce_block_size=4, value_block_size=4, num_wa
     if D % int(reduce_block_size) or D % int(value_block_size):
         raise ValueError("reduce_block_size and value_block_size must divide D")
     dev = _lib.require_cuda(q, k, v, f, i, o)
-    if allow_tf32:
+    if allow_tf32 and D not in (64, 128):   # at D = 64, 128 the split form is as fast and at fp32 accuracy
         flags |= _lib.F_ALLOW_TF32
     if initial is not None or return_state:
         from .mlstm_chunkwise import mlstm_chunkwise
