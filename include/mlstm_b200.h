@@ -55,8 +55,9 @@ const char* mlstm_status_string(int status);
 const char* mlstm_last_error_detail(void);
 
 /* Whether the tcgen05 path handles this case (D in {64, 128, 256}): 1 for 16-bit inputs, 2 for fp32
- * inputs (single tf32 products with MLSTM_F_ALLOW_TF32; split bf16 products by default at D = 64, 128), else 0.  The scan entry also takes D = 512 .. 4096 in
- * multiples of 256 on the tensor cores (two-pass forward). */
+ * inputs (single tf32 products with MLSTM_F_ALLOW_TF32; split bf16 products by default at D = 64, 128), else 0.
+ * The scan entry, the parallel forward (float32 h) and the parallel backward also take D = 512 .. 4096 in multiples
+ * of 256 on the tensor cores (two passes: gated S x S matrices to scratch, then plain contractions). */
 int mlstm_tc_supported(int S, int D, int dtype);
 
 /* Parallel (matmul) forward.
@@ -64,6 +65,9 @@ int mlstm_tc_supported(int S, int D, int dtype);
  * mlstm_matmul_kernel (mlstm_matmul.py:37-101).
  *   q, k, v [B,NH,S,D], f, i [B,NH,S] of `dtype`; h [B,NH,S,D] of `h_dtype` (MLSTM_DT_F32 as the
  *   reference's Python path, or the input type); m, b [B,NH,S] fp32 (the reference's saved M, B).
+ * D in {64, 128, 256}: one fused pass.  D = 512 .. 4096 in multiples of 256 with float32 h (16-bit inputs, or
+ * float32 inputs with MLSTM_F_ALLOW_TF32): two tensor-core passes; the workspace then holds the gated matrices
+ * of as many slices as fit 512 MB at once.  Everything else: the CUDA-core kernels.
  */
 size_t mlstm_mm_fwd_workspace(int B, int NH, int S, int D, int dtype, int flags);
 int mlstm_mm_fwd(const void* q, const void* k, const void* v, const void* f, const void* i, void* h, float* m,
@@ -76,6 +80,10 @@ int mlstm_mm_fwd(const void* q, const void* k, const void* v, const void* f, con
  * mlstm_matmul_kernel_df (:319-333).
  *   dh, h of `h_dtype`; q, k, v, f, i and the outputs dq, dk, dv, df, di of `dtype`; m, b fp32 as
  *   written by mlstm_mm_fwd.  df[..., 0] is exactly 0 (mlstm_matmul.py:316, 392).
+ * D in {64, 128, 256}: three fused passes (dQ, dK, dV).  D = 512 .. 4096 in multiples of 256 (16-bit inputs, or
+ * float32 inputs with MLSTM_F_ALLOW_TF32): the normalised gated matrix and its gradient go to scratch (as many
+ * slices at once as fit 512 MB), then dQ = dT K, dK = dT^T Q, dV = W^T dH as plain contractions: five
+ * contractions in all.  Everything else: the CUDA-core kernels.
  */
 size_t mlstm_mm_bwd_workspace(int B, int NH, int S, int D, int dtype, int h_dtype, int flags);
 int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, const void* f, const void* i,

@@ -153,6 +153,42 @@ def test_tf32_tensor_core_forward_backward(gc, D):
     assert all(v < TOL_16 for v in eb.values()), eb
 
 
+@pytest.mark.parametrize("dtype,D,S,f_mean", [
+    (torch.bfloat16, 512, 400, 2.0),      # ragged: three full row tiles and a bit
+    (torch.float16, 768, 128, 0.0),
+    (torch.float32, 512, 300, 1.0),       # tf32 operands (by flag); an odd number of row tiles
+    (torch.bfloat16, 512, 1300, 3.0),     # eleven row tiles
+])
+def test_head_dimensions_above_256_take_the_two_pass_form(gc, dtype, D, S, f_mean):
+    """The parallel forward (float32 h) and backward at D = 512, 768: gated S x S matrices to scratch, then plain
+    contractions, on the tensor cores; h, m, b and the five gradients against the oracle.  The workspace query
+    says which form a call gets: the two-pass one needs room for the gated matrices."""
+    x = gc.make_inputs(1, 2, S, D, dtype, f_mean=f_mean, qkv_scale=D ** -0.5, seed=D + S)
+    flags = gc._lib.F_ALLOW_TF32 if dtype == torch.float32 else 0
+    L = gc._lib.lib()
+    dt = gc._lib.dtype_code(x["q"])
+    Spad = (S + 127) // 128 * 128
+    es = 4 if dtype == torch.float32 else 2
+    assert L.mlstm_mm_fwd_workspace(1, 2, S, D, dt, flags) >= 2 * Spad * Spad * es
+    assert L.mlstm_mm_fwd_workspace(1, 2, S, D, dt, flags | gc._lib.F_FORCE_SIMT) < Spad * Spad * es
+    h, m, b = gc.run_forward(x, flags=flags)
+    ef = gc.errors_forward(x, h, m, b)
+    tol = 3e-3 if dtype == torch.float32 else TOL_16
+    assert ef["h"] < tol and ef["m"] < 1e-5 and ef["b"] < tol, ef
+    assert ef["h_check_frac"] < gc.CHECK_FRAC_16 and ef["h_first_tile_row_rel"] < gc.ROW_REL_16, ef
+    # the same call on the CUDA cores agrees
+    h2, m2, b2 = gc.run_forward(x, flags=gc._lib.F_FORCE_SIMT)
+    assert orc.max_abs_rel(h, h2) < tol and orc.max_abs_rel(b, b2) < tol and torch.equal(m, m2)
+    assert L.mlstm_mm_bwd_workspace(1, 2, S, D, dt, gc._lib.dtype_code(h), flags) >= 4 * Spad * Spad * es
+    grads = gc.run_backward(x, h, m, b, flags=flags)
+    eb = gc.errors_backward(x, grads, torch.float32)
+    assert all(v < TOL_16 for v in eb.values()), eb
+    # the CUDA-core backward of the same call agrees
+    grads2 = gc.run_backward(x, h, m, b, flags=gc._lib.F_FORCE_SIMT)
+    for name, g1, g2 in zip(("dq", "dk", "dv", "df", "di"), grads, grads2):
+        assert orc.max_abs_rel(g1, g2) < TOL_16, name
+
+
 def test_tensor_core_matches_simt_on_device(gc):
     """Same 16-bit inputs through both kernel families."""
     x = gc.make_inputs(2, 2, 640, 128, torch.bfloat16, f_mean=3.0, qkv_scale=128 ** -0.5, seed=3)

@@ -191,6 +191,54 @@ int forward_impl(const void* q, const void* k, const void* v, const void* f, con
     return run_pass(kind, FWD, p, dtype, h_dtype, st);
 }
 
+// Two-pass forward for head dimensions above 256 (scan_gemm.cu): gates, W = gate(Q K^T) into scratch, h = (W V) / n
+// (times silu(o) when o is given).  `extra` points behind the gate vectors of `w`: row-sum partials, then W.
+size_t two_pass_extra_bytes(int BH, int S, int dtype) {
+    return al(scan_gemm_bpart_bytes(BH, S, dtype)) + al(scan_gemm_w_bytes(BH, S, dtype));
+}
+
+int two_pass_forward(const void* q, const void* k, const void* v, const void* f, const void* i, const void* o, float* h,
+                     float* m, float* b, const FwdWs& w, uint8_t* extra, int BH, int S, int D, int dtype, cudaStream_t st) {
+    const int Spad = round_up(S, TILE);
+    float* bpart = reinterpret_cast<float*>(extra);
+    void* W = extra + al(scan_gemm_bpart_bytes(BH, S, dtype));
+    // status word and the two work-item counters of the passes in one go
+    if (cudaMemsetAsync(w.status, 0, WS_ALIGN, st) != cudaSuccess) return MLSTM_E_CUDA;
+    int rc;
+    if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, m, BH, S, Spad, dtype, st, nullptr, nullptr, nullptr, 0,
+                               nullptr, w.gaw)) != MLSTM_OK)
+        return rc;
+    ScanGemmArgs a{};
+    a.S = S; a.Spad = Spad; a.BH = BH; a.D = D;
+    a.ga = w.ga; a.gAn = w.gAn; a.gaw = w.gaw; a.a_ref = w.a_ref; a.An_ref = w.An_ref; a.m = m; a.b = b;
+    a.bpart = bpart; a.status = w.status; a.counters = w.status + 8 + 12;
+    return launch_scan_gemm(q, k, v, o, h, W, a, dtype, st);
+}
+
+// The parallel forward's own use of the two-pass form: head dimension above 256, float32 h, and for float32 inputs
+// only where single tf32 products are allowed.
+bool mm_fwd_two_pass(int S, int D, int dtype, int h_dtype, int flags) {
+    if (flags & (MLSTM_F_FORCE_SIMT | MLSTM_F_FORCE_TC)) return false;
+    if (h_dtype != MLSTM_DT_F32) return false;
+    if (dtype == MLSTM_DT_F32 && !(flags & MLSTM_F_ALLOW_TF32)) return false;
+    return scan_gemm_supported(S, D, dtype);
+}
+
+// The parallel backward's use of the same two passes: head dimension above 256, any h type, and for float32
+// inputs only where single tf32 products are allowed.
+bool mm_bwd_two_pass(int S, int D, int dtype, int flags) {
+    if (flags & (MLSTM_F_FORCE_SIMT | MLSTM_F_FORCE_TC)) return false;
+    if (dtype == MLSTM_DT_F32 && !(flags & MLSTM_F_ALLOW_TF32)) return false;
+    return scan_gemm_supported(S, D, dtype);
+}
+
+// behind the gate vectors: the two gated matrices of a group of slices, then the row-dot partials R and dI
+// (one per 256-column output slice)
+size_t two_pass_bwd_extra_bytes(int BH, int S, int D, int dtype) {
+    const size_t vec = static_cast<size_t>(BH) * round_up(S, TILE) * sizeof(float);
+    return 2 * al(scan_gemm_bwd_matrix_bytes(BH, S, dtype)) + 2 * al(vec * (D / 256));
+}
+
 }  // namespace
 
 static thread_local char g_error_detail[256] = "";
@@ -230,6 +278,9 @@ int mlstm_tc_supported(int S, int D, int dtype) {
 
 size_t mlstm_mm_fwd_workspace(int B, int NH, int S, int D, int dtype, int flags) {
     if (check_dims(B, NH, S, D) != MLSTM_OK) return 0;
+    // (sized for float32 h; a 16-bit h at these head dimensions takes the smaller one-pass workspace)
+    if (mm_fwd_two_pass(S, D, dtype, MLSTM_DT_F32, flags))
+        return carve_fwd(nullptr, B * NH, S, false).bytes + two_pass_extra_bytes(B * NH, S, dtype);
     return carve_fwd(nullptr, B * NH, S, false).bytes + tf32_copy_bytes(B * NH, S, D, dtype, flags, 3);
 }
 
@@ -242,6 +293,12 @@ int mlstm_mm_fwd(const void* q, const void* k, const void* v, const void* f, con
     if (rc != MLSTM_OK) return rc;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(h)) return MLSTM_E_ALIGN;
     FwdWs w = carve_fwd(workspace, B * NH, S, false);
+    if (mm_fwd_two_pass(S, D, dtype, h_dtype, flags)) {
+        if (!workspace || workspace_bytes < w.bytes + two_pass_extra_bytes(B * NH, S, dtype) || !aligned16(workspace))
+            return MLSTM_E_WORKSPACE;
+        return two_pass_forward(q, k, v, f, i, nullptr, static_cast<float*>(h), m, b, w, static_cast<uint8_t*>(workspace) + w.bytes,
+                                B * NH, S, D, dtype, static_cast<cudaStream_t>(stream));
+    }
     const size_t extra = tf32_copy_bytes(B * NH, S, D, dtype, flags, 3);
     if (!workspace || workspace_bytes < w.bytes + extra || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
     return forward_impl(q, k, v, f, i, nullptr, h, m, b, w, B * NH, S, D, dtype, h_dtype, flags,
@@ -250,6 +307,9 @@ int mlstm_mm_fwd(const void* q, const void* k, const void* v, const void* f, con
 
 size_t mlstm_mm_bwd_workspace(int B, int NH, int S, int D, int dtype, int h_dtype, int flags) {
     if (check_dims(B, NH, S, D) != MLSTM_OK) return 0;
+    if (mm_bwd_two_pass(S, D, dtype, flags))
+        return carve_bwd(nullptr, B * NH, S, D, dtype != MLSTM_DT_F32 && h_dtype != dtype).bytes +
+               two_pass_bwd_extra_bytes(B * NH, S, D, dtype);
     return carve_bwd(nullptr, B * NH, S, D, dtype != MLSTM_DT_F32 && h_dtype != dtype).bytes +
            tf32_copy_bytes(B * NH, S, D, dtype, flags, 4);
 }
@@ -267,11 +327,37 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     const int BH = B * NH, Spad = round_up(S, TILE);
     const bool need16 = dtype != MLSTM_DT_F32 && h_dtype != dtype;
     BwdWs w = carve_bwd(workspace, BH, S, D, need16);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (mm_bwd_two_pass(S, D, dtype, flags)) {
+        if (!workspace || workspace_bytes < w.bytes + two_pass_bwd_extra_bytes(BH, S, D, dtype) || !aligned16(workspace))
+            return MLSTM_E_WORKSPACE;
+        // status word and the work-item counters of the five launches in one go
+        if (cudaMemsetAsync(w.status, 0, WS_ALIGN, st) != cudaSuccess) return MLSTM_E_CUDA;
+        if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, nullptr, BH, S, Spad, dtype, st, nullptr, nullptr, nullptr,
+                                   0, nullptr, w.gaw)) != MLSTM_OK)
+            return rc;
+        if ((rc = launch_bwd_prep(h, dh, b, m, w.gAn, w.gB, w.gBw, w.g, w.dh16, BH, S, Spad, D, h_dtype, dtype, st)) != MLSTM_OK)
+            return rc;
+        const size_t vec = static_cast<size_t>(BH) * Spad * sizeof(float);
+        const size_t mat = al(scan_gemm_bwd_matrix_bytes(BH, S, dtype));
+        uint8_t* extra_base = static_cast<uint8_t*>(workspace) + w.bytes;
+        ScanGemmBwdArgs a{};
+        a.S = S; a.Spad = Spad; a.BH = BH; a.D = D;
+        a.q = q; a.k = k; a.v = v; a.dh = need16 ? w.dh16 : dh;
+        a.dq = dq; a.dk = dk; a.dv = dv;
+        a.ga = w.ga; a.gaw = w.gaw; a.gB = w.gB; a.g = w.g; a.a_ref = w.a_ref; a.An_ref = w.An_ref;
+        a.Wn = extra_base; a.dT = extra_base + mat;
+        a.R = reinterpret_cast<float*>(extra_base + 2 * mat);
+        a.dI = reinterpret_cast<float*>(extra_base + 2 * mat + al(vec * (D / 256)));
+        a.dot_stride = static_cast<long long>(BH) * Spad;
+        a.status = w.status; a.counters = w.status + 8 + 12;
+        if ((rc = launch_scan_gemm_bwd(a, dtype, st)) != MLSTM_OK) return rc;
+        return launch_df(f, a.dI, a.R, df, di, BH, S, Spad, dtype, st, D / 256, a.dot_stride);
+    }
     const size_t extra = tf32_copy_bytes(BH, S, D, dtype, flags, 4);
     if (!workspace || workspace_bytes < w.bytes + extra || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
     const int kind = pass_kind(S, D, dtype, flags, &rc);
     if (rc != MLSTM_OK) return rc;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
     if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, nullptr, BH, S, Spad, dtype, st, nullptr, nullptr, nullptr, 0,
@@ -333,8 +419,7 @@ size_t mlstm_scan_fwd_workspace(int B, int NH, int S, int D, int dtype, int flag
     if (check_dims(B, NH, S, D) != MLSTM_OK) return 0;
     switch (scan_route(B, NH, S, D, dtype, flags)) {
         case SCAN_TWO_PASS:
-            return carve_fwd(nullptr, B * NH, S, true).bytes + al(scan_gemm_bpart_bytes(B * NH, S, dtype)) +
-                   al(scan_gemm_w_bytes(B * NH, S, dtype));
+            return carve_fwd(nullptr, B * NH, S, true).bytes + two_pass_extra_bytes(B * NH, S, dtype);
         case SCAN_CHUNKWISE: return mlstm_chunk_workspace(B, NH, S, D, dtype, SCAN_CHUNK);
         default: return carve_fwd(nullptr, B * NH, S, true).bytes + tf32_copy_bytes(B * NH, S, D, dtype, flags, 3);
     }
@@ -361,22 +446,9 @@ int mlstm_scan_fwd(const void* q, const void* k, const void* v, const void* f, c
                                  B, NH, S, D, dtype, SCAN_CHUNK, stream);
     }
     FwdWs w = carve_fwd(workspace, BH, S, true);
-    if (route == SCAN_TWO_PASS) {
-        const int Spad = round_up(S, TILE);
-        uint8_t* base = static_cast<uint8_t*>(workspace) + w.bytes;
-        float* bpart = reinterpret_cast<float*>(base);
-        void* W = base + al(scan_gemm_bpart_bytes(BH, S, dtype));
-        // status word and the two work-item counters of the passes in one go
-        if (cudaMemsetAsync(w.status, 0, WS_ALIGN, st) != cudaSuccess) return MLSTM_E_CUDA;
-        if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, w.m, BH, S, Spad, dtype, st, nullptr, nullptr, nullptr, 0,
-                                   nullptr, w.gaw)) != MLSTM_OK)
-            return rc;
-        ScanGemmArgs a{};
-        a.S = S; a.Spad = Spad; a.BH = BH; a.D = D;
-        a.ga = w.ga; a.gAn = w.gAn; a.gaw = w.gaw; a.a_ref = w.a_ref; a.An_ref = w.An_ref; a.m = w.m;
-        a.bpart = bpart; a.status = w.status; a.counters = w.status + 8 + 12;
-        return launch_scan_gemm(q, k, v, o, static_cast<float*>(h), W, a, dtype, st);
-    }
+    if (route == SCAN_TWO_PASS)
+        return two_pass_forward(q, k, v, f, i, o, static_cast<float*>(h), w.m, nullptr, w, static_cast<uint8_t*>(workspace) + w.bytes,
+                                BH, S, D, dtype, st);
     if ((flags & MLSTM_F_FORCE_TC) && D > 256) return MLSTM_E_UNSUPPORTED;
     const size_t extra = tf32_copy_bytes(BH, S, D, dtype, flags, 3);
     void* tf32buf = extra ? static_cast<uint8_t*>(workspace) + w.bytes : nullptr;

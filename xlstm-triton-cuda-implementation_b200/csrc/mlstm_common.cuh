@@ -165,7 +165,7 @@ int launch_ogate_fwd(const void* h_inner, const void* o, void* h, long long n, i
 int launch_ogate_bwd(const void* dh, const void* h_inner, const void* o, void* dh_inner, void* d_o, long long n, int h_dtype,
                      int o_dtype, cudaStream_t st);
 
-// Two-pass forward for head dimensions above 256 (scan_gemm.cu).  Gate vectors as written by
+// Two-pass forward for head dimensions above 256 (scan_gemm.cu); o may be null (no output gate).  Gate vectors as written by
 // launch_gates_fwd for all BH slices; bpart and W are scratch of scan_gemm_bpart_bytes / scan_gemm_w_bytes;
 // counters: two device words, zeroed by the caller.
 struct ScanGemmArgs {
@@ -173,6 +173,7 @@ struct ScanGemmArgs {
     const float *ga, *gAn, *gaw;
     const double *a_ref, *An_ref;
     const float* m;
+    float* b;        // [BH, S] row sums out (optional)
     float* bpart;
     int* status;
     int* counters;
@@ -182,5 +183,23 @@ size_t scan_gemm_w_bytes(int BH, int S, int dtype);
 size_t scan_gemm_bpart_bytes(int BH, int S, int dtype);
 int launch_scan_gemm(const void* q, const void* k, const void* v, const void* o, float* h, void* W, const ScanGemmArgs& a,
                      int dtype, cudaStream_t st);
+// The parallel backward in the same two passes (head dimensions above 256).  q, k, v, dh and the outputs dq, dk, dv
+// in the input type; gate vectors of launch_gates_fwd and launch_bwd_prep (gB, g) for all BH slices; Wn, dT: scratch
+// of scan_gemm_bwd_matrix_bytes each; R, dI: [D / 256][BH, Spad] row-dot partials (dot_stride apart) for launch_df;
+// counters: five device words (zeroed by the launches).
+struct ScanGemmBwdArgs {
+    int S, Spad, BH, D;
+    const void *q, *k, *v, *dh;
+    void *dq, *dk, *dv;
+    const float *ga, *gaw, *gB, *g;
+    const double *a_ref, *An_ref;
+    void *Wn, *dT;
+    float *R, *dI;
+    long long dot_stride;
+    int* status;
+    int* counters;
+};
+size_t scan_gemm_bwd_matrix_bytes(int BH, int S, int dtype);
+int launch_scan_gemm_bwd(const ScanGemmBwdArgs& a, int dtype, cudaStream_t st);
 
 }  // namespace mlstm

@@ -46,6 +46,10 @@ namespace {
 using namespace ptx;
 
 constexpr int GATE = 0, APPLY = 1;
+// pass 2: the tensor that comes in per-warp tiles beside the accumulator
+constexpr int SIDE_NONE = 0;    // nothing
+constexpr int SIDE_OGATE = 1;   // output gate o: the row is multiplied by silu(o)
+constexpr int SIDE_DOT = 2;     // q resp. k: the row is dotted with it (the backward's R and dI vectors)
 constexpr int NTHREADS_G = 192;
 constexpr int TN = 256;                       // columns of a work item
 constexpr int A_BYTES = 128 * 128;            // 128 rows x 128 bytes
@@ -83,10 +87,14 @@ struct GemmParams {
     const float* col_w;
     const double* col_ref;
     float er_add;
-    float* bpart;       // [BH, NKT, Spad] partial row sums, one per key tile
+    const float* row_g; // [BH, Spad] added to every element of the row before the gate factor (backward), or nullptr
+    float* bpart;       // [BH, NKT, Spad] partial row sums, one per key tile, or nullptr
     // pass 2
-    const float* m;     // [BH, S]
-    const void* ogate;  // [BH, S, D] or nullptr
+    const float* m;     // [BH, S]; nullptr: rows are not normalised (backward)
+    int side;           // what the [BH, S, D] tensor behind the fourth tensor map is: SIDE_NONE, SIDE_OGATE, SIDE_DOT
+    float* b_out;       // [BH, S] row sums (optional)
+    float* dot_out;     // SIDE_DOT: [NVS][BH, Spad] row dots, one partial per 256-column output slice
+    long long dot_stride;
     int* status;
     int* counter;       // work-item counter of this launch (zeroed by the launcher)
 };
@@ -103,7 +111,10 @@ __device__ __forceinline__ void bulk_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 
-template <int PHASE, int ABFMT, bool PAIR>
+// TRANS (pass 2 only): the contraction runs over the ROWS of the S x S matrix, out[c, :] = sum_r M[r, c] Z[r, :] for
+// r >= c (the backward's dK and dV): the A operand is the matrix read MN-major, in the same boxes as B.
+// OUT_IN (pass 2 only): the output has the inputs' element type (gradients) instead of fp32 (h).
+template <int PHASE, int ABFMT, bool PAIR, bool TRANS = false, bool OUT_IN = false>
 __global__ void __launch_bounds__(NTHREADS_G, 1)
 mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmG, const GemmParams p) {
@@ -117,12 +128,14 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     constexpr int KSTEP = 32 / ES;               // contraction elements per MMA
     using InT = typename std::conditional<ABFMT == 2, float,
                                           typename std::conditional<ABFMT == 1, __nv_bfloat16, __half>::type>::type;
-    // pass 1 writes W in the input type, pass 2 writes h in fp32
-    constexpr int OUT_ES = PHASE == GATE ? ES : 4;
+    static_assert(PHASE == APPLY || (!TRANS && !OUT_IN), "pass 1 has one form");
+    // pass 1 writes W in the input type, pass 2 writes h in fp32 or gradients in the input type
+    constexpr int OUT_ES = (PHASE == GATE || OUT_IN) ? ES : 4;
     constexpr int NSUB = OUT_ES == 4 ? 2 : 1;    // TMA stores of 64 bytes per row for a 32-column chunk
     // pass 2: B boxes are KC rows x 128 bytes, one per 128-byte column group of the item's 256 columns
     constexpr int B2_BOX = KC * 128;
     constexpr int B2_GROUPS = TN * ES / 128;
+    constexpr int AT_GROUPS = TILE * ES / 128;   // TRANS: 128-byte column groups of a row tile's 128 matrix columns
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
@@ -170,12 +183,14 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const int per_w = p.BH * p.NVS;
             const int w = id / per_w;
             const int rem = id - w * per_w;
-            const int g = (PAIR ? p.NP : p.NT) - 1 - w;   // longest contractions first
+            const int g = TRANS ? w : (PAIR ? p.NP : p.NT) - 1 - w;   // longest contractions first
             it.qt = PAIR ? 2 * g + static_cast<int>(rank) : g;
             it.bh = rem / p.NVS;
             it.ct = rem - it.bh * p.NVS;
-            // the causal extent of the (pair's lower) row tile; the gated matrix holds zeros right of a tile's diagonal
-            it.nchunks = (PAIR ? min((2 * g + 2) * TILE, p.Spad) : (g + 1) * TILE) / KC;
+            // the causal extent of the (pair's lower) row tile; the gated matrix holds zeros right of a tile's diagonal.
+            // TRANS: the matrix rows from the (pair's upper) tile's first one to the end.
+            if (TRANS) it.nchunks = (p.Spad - (PAIR ? 2 * g : g) * TILE) / KC;
+            else it.nchunks = (PAIR ? min((2 * g + 2) * TILE, p.Spad) : (g + 1) * TILE) / KC;
         }
         return it;
     };
@@ -249,20 +264,25 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     // this CTA's 128 of the 256); pass 2: KC value rows x the item's columns (PAIR: this CTA's half of
                     // them), all 128-byte column groups with ONE copy (a copy per group made the pass wait on the copy
                     // engine: nine copies per stage ran at 2900 cycles per stage)
+                    // TRANS: chunk c is KC matrix rows from the item's first one; A = this CTA's 128 matrix columns of them
+                    // (all their 128-byte groups with one copy, like B), B = the same rows of Z
+                    const int k0 = TRANS ? (PAIR ? it.qt - static_cast<int>(rank) : it.qt) * TILE + c * KC : c * KC;
                     if constexpr (PAIR) {
                         if (rank == 0) mbar_expect_tx(&bar_full[s], 2 * STAGE_BYTES_G);   // the loads of both CTAs
                         const uint32_t lead_full = at_leader(&bar_full[s]);
-                        tma_load_3d_pair(sa, &tmA, lead_full, c * KC, it.qt * TILE, it.bh);
+                        if (TRANS) tma_load_4d_pair(sa, &tmA, lead_full, 0, k0, it.qt * AT_GROUPS, it.bh);
+                        else tma_load_3d_pair(sa, &tmA, lead_full, k0, it.qt * TILE, it.bh);
                         if (PHASE == GATE)
-                            tma_load_3d_pair(sb, &tmB, lead_full, c * KC, it.ct * TN + static_cast<int>(rank) * (TN / 2), it.bh);
+                            tma_load_3d_pair(sb, &tmB, lead_full, k0, it.ct * TN + static_cast<int>(rank) * (TN / 2), it.bh);
                         else
-                            tma_load_4d_pair(sb, &tmB, lead_full, 0, c * KC,
+                            tma_load_4d_pair(sb, &tmB, lead_full, 0, k0,
                                              it.ct * B2_GROUPS + static_cast<int>(rank) * (B2_GROUPS / 2), it.bh);
                     } else {
                         mbar_expect_tx(&bar_full[s], STAGE_BYTES_G);
-                        tma_load_3d(sa, &tmA, &bar_full[s], c * KC, it.qt * TILE, it.bh);
-                        if (PHASE == GATE) tma_load_3d(sb, &tmB, &bar_full[s], c * KC, it.ct * TN, it.bh);
-                        else tma_load_4d(sb, &tmB, &bar_full[s], 0, c * KC, it.ct * B2_GROUPS, it.bh);
+                        if (TRANS) tma_load_4d(sa, &tmA, &bar_full[s], 0, k0, it.qt * AT_GROUPS, it.bh);
+                        else tma_load_3d(sa, &tmA, &bar_full[s], k0, it.qt * TILE, it.bh);
+                        if (PHASE == GATE) tma_load_3d(sb, &tmB, &bar_full[s], k0, it.ct * TN, it.bh);
+                        else tma_load_4d(sb, &tmB, &bar_full[s], 0, k0, it.ct * B2_GROUPS, it.bh);
                     }
                 }
             }
@@ -274,7 +294,7 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const bool issuer = elect_one();
         auto uni = [](int x) { return __shfl_sync(0xffffffffu, x, 0); };
         auto wait_u = [&](uint64_t* bar, uint32_t parity) { return mbar_wait_warp(bar, parity, abort_flag, WAIT_LIMIT_G); };
-        constexpr uint32_t idesc = make_idesc(ABFMT, PAIR ? 256 : 128, TN, 0, PHASE == GATE ? 0 : 1);
+        constexpr uint32_t idesc = make_idesc(ABFMT, PAIR ? 256 : 128, TN, TRANS ? 1 : 0, PHASE == GATE ? 0 : 1);
         const uint32_t smem_u = static_cast<uint32_t>(uni(static_cast<int>(smem_u32(smem))));
         const uint32_t tmem_u = static_cast<uint32_t>(uni(static_cast<int>(tmem_base)));
         const uint32_t bars_u = smem_u + NSTAGE * STAGE_BYTES_G + NEPI * OUT_WARP_BYTES + G::IN_BYTES;        // this CTA's barriers ...
@@ -288,7 +308,10 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 tc_commit(const_cast<uint64_t*>(bar));
             }
         };
-        const uint64_t adesc0 = smem_desc_sw128(smem_u, 16, 1024);                      // K-major, 128-byte rows
+        const uint64_t adesc0 = !TRANS ? smem_desc_sw128(smem_u, 16, 1024)              // K-major, 128-byte rows
+                                : (TF32 ? smem_desc_sw128(smem_u, B2_BOX, 512, 1)        // MN-major like B of pass 2
+                                        : smem_desc_sw128(smem_u, B2_BOX, 1024, 2));
+        constexpr int A_KSTEP_BYTES = TRANS ? KSTEP * 128 : 32;          // advance of A per MMA
         const uint64_t bdesc0 = PHASE == GATE ? smem_desc_sw128(smem_u + A_BYTES, 16, 1024)           // K-major, 256 rows
                                 : (TF32 ? smem_desc_sw128(smem_u + A_BYTES, B2_BOX, 512, 1)          // MN-major, 32-bit
                                         : smem_desc_sw128(smem_u + A_BYTES, B2_BOX, 1024, 2));        // MN-major, 16-bit
@@ -318,11 +341,11 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                     for (int kk = 0; kk < KC / KSTEP; kk++) {
                         if constexpr (PAIR)
-                            mma_ss_pair_fmt<TF32>(acc, smem_desc_advance(ad, kk * 32), smem_desc_advance(bd, kk * B_KSTEP_BYTES),
-                                                  idesc, (c > 0 || kk > 0) ? 1u : 0u);
+                            mma_ss_pair_fmt<TF32>(acc, smem_desc_advance(ad, kk * A_KSTEP_BYTES),
+                                                  smem_desc_advance(bd, kk * B_KSTEP_BYTES), idesc, (c > 0 || kk > 0) ? 1u : 0u);
                         else
-                            mma_ss<TF32>(acc, smem_desc_advance(ad, kk * 32), smem_desc_advance(bd, kk * B_KSTEP_BYTES), idesc,
-                                         (c > 0 || kk > 0) ? 1u : 0u);
+                            mma_ss<TF32>(acc, smem_desc_advance(ad, kk * A_KSTEP_BYTES), smem_desc_advance(bd, kk * B_KSTEP_BYTES),
+                                         idesc, (c > 0 || kk > 0) ? 1u : 0u);
                     }
                     commit(&bar_empty[s]);
                     if (c == it.nchunks - 1) commit(&bar_accfull[buf]);
@@ -346,7 +369,8 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         constexpr int GATE_COLS = 128 / ES;               // columns of o per tile
         constexpr int GATE_TILES = TN / GATE_COLS;        // tiles per item and warp
         constexpr int GATE_TILE_BYTES = 32 * 128;
-        [[maybe_unused]] const bool gated = PHASE == APPLY && p.ogate != nullptr;
+        [[maybe_unused]] const bool gated = PHASE == APPLY && p.side != SIDE_NONE;   // a side tensor comes in tiles
+        [[maybe_unused]] const bool side_dot = PHASE == APPLY && p.side == SIDE_DOT;
         if (PHASE == APPLY && lane == 0) prefetch_tmap(&tmG);
         int nstore = 0;   // stores issued by this warp: alternates its two staging buffers
         bool ok = __all_sync(0xffffffffu, *abort_flag ? 0 : 1) != 0;
@@ -391,17 +415,20 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             // row terms, requested before the accumulator wait
             double er_d = 0.0;
             float inv_n = 1.0f;
+            [[maybe_unused]] float g_row = 0.0f, dot = 0.0f;
             if (!active) {
                 // nothing to read: the accumulator holds zeros and nothing is stored
             } else if (PHASE == GATE) {
                 er_d = static_cast<double>(p.row_rel[vec_base + grow]) + p.row_ref[ref_base + grow / REF_BLOCK] +
                        static_cast<double>(p.er_add);
-            } else {
+                if (p.row_g) g_row = p.row_g[vec_base + grow];
+            } else if (p.m) {
                 float bsum = 0.0f;
                 for (int kt = 0; kt <= it.qt / 2; kt++)
                     bsum += p.bpart[(static_cast<size_t>(it.bh) * p.NKT + kt) * p.Spad + grow];
                 const float mrow = row_ok ? p.m[static_cast<size_t>(it.bh) * p.S + grow] : 0.0f;
                 inv_n = 1.0f / (fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f);
+                if (p.b_out && it.ct == 0 && row_ok) p.b_out[static_cast<size_t>(it.bh) * p.S + grow] = bsum;
             }
             ok = mbar_wait_warp<SLEEP_NS_G>(&bar_accfull[buf], (n >> 1) & 1, abort_flag, WAIT_LIMIT_G);
             if (!ok) break;
@@ -452,7 +479,7 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         const uint4 raw = *reinterpret_cast<const uint4*>(grow_smem + ((piece ^ (lane & 7)) << 4));
                         const InT* ev = reinterpret_cast<const InT*>(&raw);
 #pragma unroll
-                        for (int j = 0; j < VEC; j++) cv[jv * VEC + j] = silu_f(to_f32<InT>(ev[j]));
+                        for (int j = 0; j < VEC; j++) cv[jv * VEC + j] = side_dot ? to_f32<InT>(ev[j]) : silu_f(to_f32<InT>(ev[j]));
                     }
                     if (sub == CH_PER_TILE - 1) {   // the tile is in registers: fetch the tile after next into its buffer
                         __syncwarp();
@@ -471,7 +498,7 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         const int rel0 = c0 - it.qt * TILE;    // column index inside the diagonal tile
 #pragma unroll
                         for (int j = 0; j < 32; j++) {
-                            float wj = __uint_as_float(tv[j]) * fast_exp2(cv[j] + er);
+                            float wj = (__uint_as_float(tv[j]) + g_row) * fast_exp2(cv[j] + er);
                             if (rel0 + j > r) wj = 0.0f;
                             rowsum += wj;
                             cv[j] = wj;
@@ -480,12 +507,20 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         // off the diagonal tile exp2(ec + er) = exp2(ec) exp2(er) with both factors bounded; a
                         // block of pure padding has no reference of its own, hence the clamp (its factors are 0)
                         const float u = fast_exp2(fminf(er, MAX_ROW_EXP2_G));
+                        const float gu = g_row * u;
 #pragma unroll
                         for (int j = 0; j < 32; j++) {
-                            const float wj = __uint_as_float(tv[j]) * u * cv[j];
+                            const float wj = fmaf(__uint_as_float(tv[j]), u, gu) * cv[j];
                             rowsum += wj;
                             cv[j] = wj;
                         }
+                    }
+                } else if (side_dot) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float x = __uint_as_float(tv[j]);
+                        dot = fmaf(x, cv[j], dot);
+                        cv[j] = x;
                     }
                 } else {
 #pragma unroll
@@ -529,8 +564,10 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
             if (!ok) break;
             if (gated && active) ngate += GATE_TILES;
+            if (side_dot && active && p.dot_out)
+                p.dot_out[it.ct * p.dot_stride + static_cast<long long>(vec_base) + grow] = row_ok ? dot : 0.0f;
             if (PHASE == GATE && active) {
-                p.bpart[(static_cast<size_t>(it.bh) * p.NKT + it.ct) * p.Spad + grow] = rowsum;
+                if (p.bpart) p.bpart[(static_cast<size_t>(it.bh) * p.NKT + it.ct) * p.Spad + grow] = rowsum;
                 if constexpr (PAIR) {
                     // Pass 2 contracts a pair of row tiles over the causal extent of the lower one.  For the upper tile
                     // that includes the 128 columns right of its diagonal tile, which nothing computes: they must read
@@ -568,10 +605,10 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
 }
 
-template <int PHASE, int ABFMT, bool PAIR>
+template <int PHASE, int ABFMT, bool PAIR, bool TRANS = false, bool OUT_IN = false>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mg, const GemmParams& p,
                 bool zero_counter, cudaStream_t st) {
-    auto kern = mlstm_scan_gemm<PHASE, ABFMT, PAIR>;
+    auto kern = mlstm_scan_gemm<PHASE, ABFMT, PAIR, TRANS, OUT_IN>;
     constexpr int smem = GemmCfg<PAIR, PHASE>::SMEM;
     cudaError_t ce;
     {
@@ -645,7 +682,8 @@ int run_group(const void* q, const void* k, const void* v, const void* o, float*
     p.er_add = -0.5f * log2f(static_cast<float>(a.D));
     p.bpart = a.bpart;   // per group: reused
     p.m = a.m + static_cast<size_t>(bh0) * a.S;
-    p.ogate = og;
+    p.side = og ? SIDE_OGATE : SIDE_NONE;
+    p.b_out = a.b ? a.b + static_cast<size_t>(bh0) * a.S : nullptr;
     p.status = a.status;
     int rc;
     CUtensorMap ma, mb, mo;
@@ -676,6 +714,90 @@ int run_group_any(const void* q, const void* k, const void* v, const void* o, fl
     return run_group<ABFMT, false>(q, k, v, o, h, W, a, bh0, nbh, dtype, st);
 }
 
+// Backward of one group of slices in the same two passes (the parallel backward at head dimensions above 256):
+//   pass 1 twice   Wn[r, c] = (q_r . k_c) e[r, c]            e[r, c] = exp2(gB_r + ga_c) = decay * scale / n_r
+//                  dT[r, c] = (dh_r . v_c + g_r) e[r, c]     (c <= r; g_r = db_r n_r, gates.cu)
+//   pass 2 thrice  dQ = dT K          (rows dotted with q: R)
+//                  dK = dT^T Q        (rows dotted with k: dI)       contraction over the matrix rows (TRANS)
+//                  dV = Wn^T dH
+// Five contractions, the algorithmic minimum; the two matrices stay in L2 at moderate S.
+template <int ABFMT, bool PAIR>
+int run_group_bwd(const ScanGemmBwdArgs& a, int bh0, int nbh, int dtype, cudaStream_t st) {
+    const size_t es = dtype == MLSTM_DT_F32 ? 4 : 2;
+    const size_t slice = static_cast<size_t>(a.S) * a.D;
+    auto at = [&](const void* base) { return static_cast<const uint8_t*>(base) + bh0 * slice * es; };
+    auto at_out = [&](void* base) { return static_cast<uint8_t*>(base) + bh0 * slice * es; };
+    GemmParams p{};
+    p.S = a.S; p.Spad = a.Spad; p.BH = nbh; p.D = a.D;
+    p.NT = a.Spad / TILE;
+    p.NP = (p.NT + 1) / 2;
+    p.NKT = (a.Spad + TN - 1) / TN;
+    p.NVS = a.D / TN;
+    p.per_head = 0;
+    if (PAIR) for (int g = 0; g < p.NP; g++) p.per_head += g + 1;
+    else for (int qt = 0; qt < p.NT; qt++) p.per_head += qt / 2 + 1;
+    const size_t vec0 = static_cast<size_t>(bh0) * a.Spad, ref0 = static_cast<size_t>(bh0) * (a.Spad / REF_BLOCK);
+    p.row_rel = a.gB + vec0; p.row_ref = a.An_ref + ref0;
+    p.col_rel = a.ga + vec0; p.col_w = a.gaw + vec0; p.col_ref = a.a_ref + ref0;
+    p.er_add = 0.0f;   // the scale is part of gB
+    p.status = a.status;
+    p.dot_stride = a.dot_stride;
+    constexpr int KC = ABFMT == 2 ? 32 : 64;
+    constexpr int GROUPS = TN * (ABFMT == 2 ? 4 : 2) / 128;
+    constexpr int AT_GROUPS = TILE * (ABFMT == 2 ? 4 : 2) / 128;
+    int rc;
+    CUtensorMap ma, mb, mo, mg;
+    int launch = 0;
+    auto counter = [&]() { p.counter = a.counters + launch++; };
+    // ---- pass 1: Wn = gate(Q K^T), dT = gate(dH V^T + g)
+    p.items = p.per_head * nbh;
+    if ((rc = tc_make_map(&ma, at(a.q), nbh, a.S, a.D, dtype, false, 128)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map(&mb, at(a.k), nbh, a.S, a.D, dtype, false, PAIR ? TN / 2 : TN)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map_out(&mo, a.Wn, nbh, a.Spad, a.Spad, dtype, 32)) != MLSTM_OK) return rc;
+    counter();
+    if ((rc = launch_gemm<GATE, ABFMT, PAIR>(ma, mb, mo, mo, p, true, st)) != MLSTM_OK) return rc;
+    p.row_g = a.g + vec0;
+    if ((rc = tc_make_map(&ma, at(a.dh), nbh, a.S, a.D, dtype, false, 128)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map(&mb, at(a.v), nbh, a.S, a.D, dtype, false, PAIR ? TN / 2 : TN)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map_out(&mo, a.dT, nbh, a.Spad, a.Spad, dtype, 32)) != MLSTM_OK) return rc;
+    counter();
+    if ((rc = launch_gemm<GATE, ABFMT, PAIR>(ma, mb, mo, mo, p, true, st)) != MLSTM_OK) return rc;
+    p.row_g = nullptr;
+    // ---- pass 2
+    p.items = (PAIR ? p.NP : p.NT) * nbh * p.NVS;
+    // dQ = dT K, R = q . dQ
+    p.side = SIDE_DOT;
+    p.dot_out = a.R + vec0;
+    if ((rc = tc_make_map(&ma, a.dT, nbh, a.Spad, a.Spad, dtype, false, 128)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map_groups(&mb, at(a.k), nbh, a.S, a.D, dtype, ABFMT == 2, KC, PAIR ? GROUPS / 2 : GROUPS)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map_out(&mo, at_out(a.dq), nbh, a.S, a.D, dtype, 32)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map(&mg, at(a.q), nbh, a.S, a.D, dtype, false, 32)) != MLSTM_OK) return rc;
+    counter();
+    if ((rc = launch_gemm<APPLY, ABFMT, PAIR, false, true>(ma, mb, mo, mg, p, true, st)) != MLSTM_OK) return rc;
+    // dK = dT^T Q, dI = k . dK
+    p.dot_out = a.dI + vec0;
+    if ((rc = tc_make_map_groups(&ma, a.dT, nbh, a.Spad, a.Spad, dtype, ABFMT == 2, KC, AT_GROUPS)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map_groups(&mb, at(a.q), nbh, a.S, a.D, dtype, ABFMT == 2, KC, PAIR ? GROUPS / 2 : GROUPS)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map_out(&mo, at_out(a.dk), nbh, a.S, a.D, dtype, 32)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map(&mg, at(a.k), nbh, a.S, a.D, dtype, false, 32)) != MLSTM_OK) return rc;
+    counter();
+    if ((rc = launch_gemm<APPLY, ABFMT, PAIR, true, true>(ma, mb, mo, mg, p, true, st)) != MLSTM_OK) return rc;
+    // dV = Wn^T dH
+    p.side = SIDE_NONE;
+    p.dot_out = nullptr;
+    if ((rc = tc_make_map_groups(&ma, a.Wn, nbh, a.Spad, a.Spad, dtype, ABFMT == 2, KC, AT_GROUPS)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map_groups(&mb, at(a.dh), nbh, a.S, a.D, dtype, ABFMT == 2, KC, PAIR ? GROUPS / 2 : GROUPS)) != MLSTM_OK) return rc;
+    if ((rc = tc_make_map_out(&mo, at_out(a.dv), nbh, a.S, a.D, dtype, 32)) != MLSTM_OK) return rc;
+    counter();
+    return launch_gemm<APPLY, ABFMT, PAIR, true, true>(ma, mb, mo, mo, p, true, st);
+}
+
+template <int ABFMT>
+int run_group_bwd_any(const ScanGemmBwdArgs& a, int bh0, int nbh, int dtype, cudaStream_t st) {
+    if (use_pairs(a.Spad)) return run_group_bwd<ABFMT, true>(a, bh0, nbh, dtype, st);
+    return run_group_bwd<ABFMT, false>(a, bh0, nbh, dtype, st);
+}
+
 }  // namespace
 
 bool scan_gemm_supported(int S, int D, int in_dtype) {
@@ -696,6 +818,38 @@ int scan_gemm_group(int BH, int S, int dtype) {
 size_t scan_gemm_w_bytes(int BH, int S, int dtype) {
     const size_t Spad = round_up(S, TILE);
     return static_cast<size_t>(scan_gemm_group(BH, S, dtype)) * Spad * Spad * (dtype == MLSTM_DT_F32 ? 4 : 2);
+}
+
+// The backward keeps two gated matrices per slice: half as many slices per group.
+int scan_gemm_bwd_group(int BH, int S, int dtype) {
+    const size_t Spad = round_up(S, TILE);
+    const size_t per_head = 2 * Spad * Spad * (dtype == MLSTM_DT_F32 ? 4 : 2);
+    const size_t budget = static_cast<size_t>(512) << 20;
+    size_t g = budget / per_head;
+    if (g < 1) g = 1;
+    return static_cast<int>(g < static_cast<size_t>(BH) ? g : BH);
+}
+
+size_t scan_gemm_bwd_matrix_bytes(int BH, int S, int dtype) {   // one of the two matrices
+    const size_t Spad = round_up(S, TILE);
+    return static_cast<size_t>(scan_gemm_bwd_group(BH, S, dtype)) * Spad * Spad * (dtype == MLSTM_DT_F32 ? 4 : 2);
+}
+
+int launch_scan_gemm_bwd(const ScanGemmBwdArgs& a, int dtype, cudaStream_t st) {
+    if (!scan_gemm_supported(a.S, a.D, dtype)) return MLSTM_E_UNSUPPORTED;
+    const int group = scan_gemm_bwd_group(a.BH, a.S, dtype);
+    for (int bh0 = 0; bh0 < a.BH; bh0 += group) {
+        const int nbh = a.BH - bh0 < group ? a.BH - bh0 : group;
+        int rc;
+        switch (dtype) {
+            case MLSTM_DT_F32: rc = run_group_bwd_any<2>(a, bh0, nbh, dtype, st); break;
+            case MLSTM_DT_BF16: rc = run_group_bwd_any<1>(a, bh0, nbh, dtype, st); break;
+            case MLSTM_DT_F16: rc = run_group_bwd_any<0>(a, bh0, nbh, dtype, st); break;
+            default: return MLSTM_E_ARG;
+        }
+        if (rc != MLSTM_OK) return rc;
+    }
+    return MLSTM_OK;
 }
 
 size_t scan_gemm_bpart_bytes(int BH, int S, int dtype) {

@@ -17,6 +17,10 @@ bf16 halves and three products per fp32 product (error about 1e-5); at other hea
 fp32 dot products on the CUDA cores.  Setting the environment variable ``MLSTM_B200_TF32=1`` (or passing
 ``flags=_lib.F_ALLOW_TF32`` to the two plain functions) trades accuracy for speed: single tf32 products
 (D in {64, 128, 256}; error about 5e-4).  ``fp32_math_mode(D)`` says which of these a call will use.
+
+Head dimensions above 256 (multiples of 256 up to 4096), 16-bit inputs, or float32 inputs with tf32 allowed:
+forward (float32 ``h``) and backward run on the tensor cores in two passes each (gated S x S matrices to scratch,
+then plain contractions: W V forward; dT K, dT^T Q, W^T dH backward).
 """
 import os
 import torch
@@ -36,6 +40,8 @@ def fp32_math_mode(D, flags=None):
         return "IEEE fp32 FMA on the CUDA cores"
     if (flags & _lib.F_ALLOW_TF32) and D in (64, 128, 256):
         return "single tf32 products on the tensor cores, fp32 accumulate"
+    if (flags & _lib.F_ALLOW_TF32) and 256 < D <= 4096 and D % 256 == 0:
+        return "single tf32 products on the tensor cores (two passes per direction), fp32 accumulate"
     if not (flags & _lib.F_NO_SPLIT) and D in (64, 128):
         return "split bf16 products (hi*hi + hi*mid + mid*hi) on the tensor cores, fp32 accumulate"
     return "IEEE fp32 FMA on the CUDA cores"
