@@ -354,6 +354,44 @@ def sec_cfg2(ctx):
     return out
 
 
+def sec_wide_head(ctx):
+    """Head dimension above 256 in the matmul path (not one of the named configurations): bf16, B=4, NH=8, S=2048,
+    D=512 through Triton_mLSTM.apply + backward; both directions take the two-pass tensor-core form."""
+    torch, pkg, dev = ctx.torch, ctx.pkg, ctx.dev
+    from oracle import mlstm_oracle as orc
+    B, NH, S, D = 4, 8, 2048, 512
+    g = torch.Generator().manual_seed(0)
+    mk = lambda *s: torch.randn(*s, generator=g)
+    host = {"q": (mk(B, NH, S, D) * D ** -0.5).bfloat16(), "k": (mk(B, NH, S, D) * D ** -0.5).bfloat16(),
+            "v": (mk(B, NH, S, D) * D ** -0.5).bfloat16(), "f": (3.0 + mk(B, NH, S)).bfloat16(), "i": mk(B, NH, S).bfloat16()}
+    dh = mk(B, NH, S, D)
+    d = {k: v.to(dev).requires_grad_(True) for k, v in host.items()}
+    dhd = dh.to(dev)
+
+    def fn():
+        for t in d.values():
+            t.grad = None
+        h = pkg.Triton_mLSTM.apply(d["q"], d["k"], d["v"], d["f"], d["i"], 32, 8)
+        h.backward(dhd)
+        return h
+    ms = time_small(ctx, fn)
+    ff, fb = algorithmic_flops(B, NH, S, D)
+    out = {"workload": "Triton_mLSTM.apply + backward, bf16, B=4 NH=8 S=2048 D=512 (two-pass form in both directions)",
+           "ms": ms, "value": B * S / (ms * 1e-3), "unit": "tokens/s", "roofline": roofline_tensor(ctx, ff + fb, ms)}
+    if ctx.rank == 0:
+        h = fn().detach()
+        sl = (slice(1, 2), slice(3, 4))     # one (batch, head) slice against the oracle
+        one = {k: v[sl] for k, v in host.items()}
+        ref_h = orc.matmul_forward(*(one[k] for k in ("q", "k", "v", "f", "i")))
+        ref_g = orc.matmul_backward(dh[sl], *(one[k] for k in ("q", "k", "v", "f", "i")))
+        errs = {"h": orc.max_abs_rel(h[sl].cpu(), ref_h)}
+        for n, r in zip(("q", "k", "v", "f", "i"), ref_g):
+            errs["d" + n] = orc.max_abs_rel(d[n].grad[sl].float().cpu(), r)
+        out["parity_max_abs_rel"] = max(errs.values())
+        out["parity_sample"] = "slice (batch 1, head 3); tolerance 1e-2"
+    return out
+
+
 def sec_cfg3(ctx):
     """The reference demo of the scan path: fp32, B=1, NH=4, S=2048, D=1024 with output gate."""
     torch, pkg, dev = ctx.torch, ctx.pkg, ctx.dev
@@ -473,7 +511,7 @@ def sec_cfg4_parity(ctx):
 
 def run_workload(args, ctx):
     """One configuration alone, printed as one line (profiler captures and ad-hoc runs)."""
-    fn = {"cfg1": sec_cfg1, "cfg2": sec_cfg2, "cfg3": sec_cfg3, "cfg5": sec_cfg5}[args.workload]
+    fn = {"cfg1": sec_cfg1, "cfg2": sec_cfg2, "cfg3": sec_cfg3, "cfg5": sec_cfg5, "d512": sec_wide_head}[args.workload]
     sec = fn(ctx) if args.workload != "cfg5" else sec_cfg5(ctx, S=args.seq or 65536)
     if ctx.rank == 0:
         line = {"metric": args.workload + "_" + sec["unit"].replace("/", "_per_"), "value": sec["value"], "unit": sec["unit"],
@@ -495,7 +533,7 @@ def main():
     ap.add_argument("--batch", type=int, default=None,
                     help="cfg4 only: a smaller global batch of the same shape (profiler captures); the line's config says so")
     ap.add_argument("--seq", type=int, default=None, help="cfg5 only: sequence length (default 65536)")
-    ap.add_argument("--workload", default="cfg4", choices=["cfg4", "cfg5", "cfg3", "cfg2", "cfg1"],
+    ap.add_argument("--workload", default="cfg4", choices=["cfg4", "cfg5", "cfg3", "cfg2", "cfg1", "d512"],
                     help="cfg4 (default, the headline); the others run one secondary configuration alone")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -679,6 +717,7 @@ def main():
                 secondary["cfg2"] = sec_cfg2(ctx)
                 secondary["cfg3"] = sec_cfg3(ctx)
                 secondary["cfg5_long"] = sec_cfg5(ctx, S=262144, parity=False)
+                secondary["wide_head_d512"] = sec_wide_head(ctx)
     sampler.stop()
 
     if rank == 0:

@@ -218,6 +218,32 @@ def test_autograd_function_matches_reference_api(gc):
     assert torch.equal(h2, h.detach())
 
 
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 64), (torch.bfloat16, 256)])
+def test_autograd_function_with_output_gate(gc, dtype, D):
+    """The optional eighth argument o of Triton_mLSTM.apply: h * silu(o), and gradients for all six inputs."""
+    x = gc.make_inputs(1, 2, 256, D, dtype, f_mean=1.0, qkv_scale=D ** -0.5, seed=D + 5, with_o=True)
+    dev = torch.device("cuda", 0)
+    names = ("q", "k", "v", "f", "i", "o")
+    t = {n: x[n].to(dev).requires_grad_(True) for n in names}
+    h = gc.PKG.Triton_mLSTM.apply(t["q"], t["k"], t["v"], t["f"], t["i"], 32, 4, t["o"])
+    assert h.dtype == torch.float32
+    h.backward(x["dh"].to(dev))
+    # reference: the oracle's forward and closed-form backward around the gate's own derivative
+    od = x["o"].double()
+    sig = torch.sigmoid(od)
+    h_inner = orc.matmul_forward(x["q"], x["k"], x["v"], x["f"], x["i"], dtype=torch.float64)
+    dhd = x["dh"].double()
+    ref = dict(zip(("q", "k", "v", "f", "i"), orc.matmul_backward(dhd * od * sig, x["q"], x["k"], x["v"], x["f"], x["i"])))
+    ref["o"] = dhd * h_inner * sig * (1 + od * (1 - sig))
+    tol = 3e-4 if dtype == torch.float32 else TOL_16
+    assert orc.max_abs_rel(h.detach(), h_inner * od * sig) < tol
+    for n in names:
+        assert t[n].grad.dtype == t[n].dtype
+        assert orc.max_abs_rel(t[n].grad, ref[n]) < tol, n
+    with pytest.raises(ValueError):
+        gc.PKG.Triton_mLSTM.apply(t["q"], t["k"], t["v"], t["f"], t["i"], 32, 4, t["o"][..., :8])
+
+
 @pytest.mark.parametrize("f_mean", [3.0, 0.0])
 def test_model_scale_slice_properties(gc, f_mean):
     """Configuration-4 shape per slice (S=4096, D=256, bf16) on a few slices, with retention-biased gates

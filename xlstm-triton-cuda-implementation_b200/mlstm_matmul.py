@@ -27,7 +27,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["Triton_mLSTM", "mlstm_matmul", "mlstm_matmul_forward", "mlstm_matmul_backward", "fp32_math_mode"]
+__all__ = ["Triton_mLSTM", "mlstm_matmul", "mlstm_matmul_forward", "mlstm_matmul_backward", "fp32_math_mode",
+           "output_gate_forward", "output_gate_backward"]
 
 
 _DEFAULT_FLAGS = _lib.F_ALLOW_TF32 if os.environ.get("MLSTM_B200_TF32", "0") not in ("", "0") else 0
@@ -102,23 +103,61 @@ def mlstm_matmul_backward(dh, q, k, v, f, i, h, m, b, flags=0):
     return dq, dk, dv, df, di
 
 
+def output_gate_forward(h_inner, o):
+    """h = h_inner * silu(o) (mlstm_scan.py:273-278), one elementwise kernel."""
+    dev = _lib.require_cuda(h_inner, o)
+    h = torch.empty_like(h_inner)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().mlstm_ogate_fwd(h_inner.data_ptr(), o.data_ptr(), h.data_ptr(), h_inner.numel(),
+                                        _lib.dtype_code(h_inner), _lib.dtype_code(o), _lib.stream_ptr(dev))
+    _lib.check(rc, "mlstm_ogate_fwd")
+    return h
+
+
+def output_gate_backward(dh, h_inner, o):
+    """(dh_inner, do) of h = h_inner * silu(o): dh_inner = dh silu(o), do = dh h_inner silu'(o)."""
+    dev = _lib.require_cuda(dh, h_inner, o)
+    dh_inner = torch.empty_like(h_inner)
+    do = torch.empty_like(o)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().mlstm_ogate_bwd(dh.data_ptr(), h_inner.data_ptr(), o.data_ptr(), dh_inner.data_ptr(), do.data_ptr(),
+                                        h_inner.numel(), _lib.dtype_code(h_inner), _lib.dtype_code(o), _lib.stream_ptr(dev))
+    _lib.check(rc, "mlstm_ogate_bwd")
+    return dh_inner, do
+
+
 class Triton_mLSTM(torch.autograd.Function):
-    """Drop-in for the reference's autograd function (mlstm_matmul.py:368-405); the name is kept."""
+    """Drop-in for the reference's autograd function (mlstm_matmul.py:368-405); the name is kept.
+
+    One argument more than the reference takes: ``o`` ([B, NH, S, D], optional, after the two tiling hints) is the
+    output gate the reference leaves as a note ("Integrate o", mlstm_matmul.py:36): the result is then
+    h * silu(o) as in its scan path (mlstm_scan.py:273-278), and ``o`` gets its gradient."""
 
     @staticmethod
-    def forward(ctx, q, k, v, f, i, SB=16, num_warps=8):
+    def forward(ctx, q, k, v, f, i, SB=16, num_warps=8, o=None):
         _check_hints(SB, num_warps)
+        if o is not None and (o.shape != q.shape or o.dtype != q.dtype):
+            raise ValueError("o must match q in shape and element type")
         h, m, b = mlstm_matmul_forward(q, k, v, f, i, flags=_DEFAULT_FLAGS)
-        ctx.save_for_backward(q, k, v, f, i, m, b, h)
+        ctx.gated = o is not None
         ctx.sb = SB
-        return h
+        if o is None:
+            ctx.save_for_backward(q, k, v, f, i, m, b, h)
+            return h
+        ctx.save_for_backward(q, k, v, f, i, m, b, h, o)
+        return output_gate_forward(h, o)
 
     @staticmethod
     def backward(ctx, dh):
         assert dh.is_contiguous()  # mlstm_matmul.py:385
-        q, k, v, f, i, m, b, h = ctx.saved_tensors
+        if ctx.gated:
+            q, k, v, f, i, m, b, h, o = ctx.saved_tensors
+            dh, do = output_gate_backward(dh, h, o)
+        else:
+            q, k, v, f, i, m, b, h = ctx.saved_tensors
+            do = None
         dq, dk, dv, df, di = mlstm_matmul_backward(dh, q, k, v, f, i, h, m, b, flags=_DEFAULT_FLAGS)
-        return dq, dk, dv, df, di, None, None
+        return dq, dk, dv, df, di, None, None, do
 
 
 def mlstm_matmul(q, k, v, f, i, SB=16, num_warps=8):

@@ -33,32 +33,9 @@ through the parallel kernels (``mlstm_matmul_backward``), whose cost is quadrati
 import torch
 
 from . import _lib
-from .mlstm_matmul import mlstm_matmul_backward, mlstm_matmul_forward
+from .mlstm_matmul import mlstm_matmul_backward, mlstm_matmul_forward, output_gate_backward, output_gate_forward
 
 __all__ = ["mlstm_scan", "output_gate_forward", "output_gate_backward"]
-
-
-def output_gate_forward(h_inner, o):
-    """h = h_inner * silu(o) (mlstm_scan.py:273-278), one elementwise kernel."""
-    dev = _lib.require_cuda(h_inner, o)
-    h = torch.empty_like(h_inner)
-    with torch.cuda.device(dev):
-        rc = _lib.lib().mlstm_ogate_fwd(h_inner.data_ptr(), o.data_ptr(), h.data_ptr(), h_inner.numel(),
-                                        _lib.dtype_code(h_inner), _lib.dtype_code(o), _lib.stream_ptr(dev))
-    _lib.check(rc, "mlstm_ogate_fwd")
-    return h
-
-
-def output_gate_backward(dh, h_inner, o):
-    """(dh_inner, do) of h = h_inner * silu(o): dh_inner = dh silu(o), do = dh h_inner silu'(o)."""
-    dev = _lib.require_cuda(dh, h_inner, o)
-    dh_inner = torch.empty_like(h_inner)
-    do = torch.empty_like(o)
-    with torch.cuda.device(dev):
-        rc = _lib.lib().mlstm_ogate_bwd(dh.data_ptr(), h_inner.data_ptr(), o.data_ptr(), dh_inner.data_ptr(), do.data_ptr(),
-                                        h_inner.numel(), _lib.dtype_code(h_inner), _lib.dtype_code(o), _lib.stream_ptr(dev))
-    _lib.check(rc, "mlstm_ogate_bwd")
-    return dh_inner, do
 
 
 def _chunkwise_shape(q):
