@@ -185,6 +185,9 @@ class Ctx:
         self.rank, self.world, self.dist = rank, world, None
         if world > 1:
             import torch.distributed as dist
+            # the one collective here is a 0.5 MB all-gather: in-switch multicast buys nothing, and without it no rank's
+            # memory is bound to a multicast object if another rank dies
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
             dist.init_process_group("nccl", device_id=self.dev)
             self.dist = dist
         self.peaks = measured_peaks()
