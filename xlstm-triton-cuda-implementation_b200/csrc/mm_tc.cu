@@ -1,10 +1,11 @@
 // Tensor-core contraction pass of the parallel mLSTM for sm_100a (tcgen05 MMA, TMEM accumulators,
 // TMA-staged 128-byte-swizzled shared-memory tiles).  One kernel template serves the forward and
-// the three backward passes (see mlstm_common.cuh for the algebra) and the two chunkwise passes.
-// It takes the place of the reference's mlstm_matmul_kernel (mlstm_matmul.py:37-101),
-// mlstm_matmul_kernel_backward_db (:132-197) and mlstm_matmul_kernel_backward (:200-316), of the
-// single-head fp16 kernel mlstm_forward (cuda-src/mlstm_forward.cu:12-189) and, with its sliced
-// form, of the scan kernels' contractions (mlstm_scan.py:74-137, 200-278).
+// the three backward passes (see mlstm_common.cuh for the algebra) and the chunkwise passes (block
+// states, forward and backward with a carried state).  It takes the place of the reference's
+// mlstm_matmul_kernel (mlstm_matmul.py:37-101), mlstm_matmul_kernel_backward_db (:132-197) and
+// mlstm_matmul_kernel_backward (:200-316), of the single-head fp16 kernel mlstm_forward
+// (cuda-src/mlstm_forward.cu:12-189) and, in its chunkwise modes, of the scan kernels' contractions
+// (mlstm_scan.py:74-137, 200-278).  Head dimensions above 256 are served by scan_gemm.cu.
 //
 // One CTA owns one stationary 128-row tile (queries in FWD/DQ, keys in DK/DV) of one batch*head
 // slice and streams the tiles on the causal side of it.  Warp roles (576 threads):

@@ -1,4 +1,4 @@
-// Two-pass tensor-core forward for head dimensions above 256, the shape of the reference's scan demo
+// Two-pass tensor-core form for head dimensions above 256, the shape of the reference's scan demo
 // (mlstm_scan.py:375-394: S = 2048, D = 1024, where the D x D state of the recurrent form is larger
 // than the S x S decay matrix, so the quadratic form is the one with the least arithmetic).
 //
@@ -14,6 +14,10 @@
 //   pass 2 (APPLY) h[r, :] = (sum_c W[r, c] v_c) / n_r * silu(o_r)
 //                  one work item = 128 query rows x 256 output columns, contraction over the causal
 //                  extent of the row tile; n_r = max(|b_r|, exp(-m_r)) + 1e-6 from pass 1's row sums
+//
+// The parallel (matmul) path uses the same two passes above D = 256, forward and backward (run_group_bwd below:
+// pass 1 for the normalised gated matrix and for its gradient, pass 2 for dQ and, with the matrix read
+// MN-major as the A operand, for dK and dV).
 //
 // Both passes are the same persistent warp-specialised GEMM: warp 0 = TMA producer (ring of stages:
 // a 128 x 128-byte A box and this CTA's share of B), warp 1 = MMA issuer (tcgen05.mma, N = 256, both
