@@ -97,7 +97,7 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
  * (:200-278).  q, k, v, o [B,NH,S,D], f, i [B,NH,S] of `dtype`; h fp32 [B,NH,S,D].
  * Three forms, chosen by shape: head dimensions above 256 (the reference demo, D = 1024) run as two
  * tensor-core passes (gated S x S matrix once, then W V); sequences much longer than the head dimension
- * run chunkwise (per-block states, inter-block carry, output from the carried state; 16-bit, D = 128);
+ * run chunkwise (per-block states, inter-block carry, output from the carried state; 16-bit, D = 128 or 256);
  * everything else is the parallel forward with the output gate in its epilogue.
  */
 size_t mlstm_scan_fwd_workspace(int B, int NH, int S, int D, int dtype, int flags);
@@ -159,7 +159,8 @@ int mlstm_forward_f16_static_status(int* host_status, void* stream);
 
 /* Chunkwise forward for long sequences, with a state that can be carried across segments (GPUs).
  * The reference has no such entry point; the mechanism it extends is the scan path's inter-block carry
- * (mlstm_scan.py:143-195, operators :15-26).  16-bit inputs, D = 128, chunk a multiple of 128.
+ * (mlstm_scan.py:143-195, operators :15-26).  16-bit inputs, D = 128 or 256 (mlstm_chunk_bwd: D = 128), chunk a
+ * multiple of 128.
  * mlstm_scan_fwd uses it by itself for sequences much longer than the head dimension.
  * A segment is processed in this order (all on one stream, one workspace):
  *   mlstm_chunk_gate_summary  (optional) local {F_end, A_end} per slice with no carry

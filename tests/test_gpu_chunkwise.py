@@ -112,6 +112,64 @@ def test_sequence_parallel_stages_on_one_gpu(gc, cuts, f_mean):
     assert orc.max_abs_rel(carry[:, 1].cpu(), A_in.cpu()) < 1e-12
 
 
+@pytest.mark.parametrize("dtype,S,chunk,f_mean", [
+    (torch.bfloat16, 1024, 256, 3.0),
+    (torch.float16, 900, 256, 0.0),       # ragged last block
+    (torch.bfloat16, 2048, 512, 1.0),     # four-tile blocks
+    (torch.bfloat16, 256, 256, -2.0),     # a single block
+    (torch.bfloat16, 640, 128, 2.0),      # one-tile blocks: every row tile has a state step only plus its own tile
+])
+def test_chunkwise_at_head_dimension_256(gc, dtype, S, chunk, f_mean):
+    """D = 256: a block's state is written in two halves of 128 key rows and applied in two state steps; the
+    forward against the oracle, with the output gate, in two calls with the state carried, and split over three
+    segments through the sequence-parallel stages."""
+    D = 256
+    mc = importlib.import_module(PKG + ".mlstm_chunkwise")
+    x = gc.make_inputs(1, 2, S, D, dtype, f_mean=f_mean, qkv_scale=D ** -0.5, seed=S + chunk + 2, with_o=True)
+    ref = orc.matmul_forward(x["q"], x["k"], x["v"], x["f"], x["i"])
+    h = gc.PKG.mlstm_chunkwise(*_dev(x), chunk_size=chunk)
+    torch.cuda.synchronize()
+    assert h.dtype == torch.float32 and orc.max_abs_rel(h, ref) < TOL_16
+    ref_o = ref * torch.nn.functional.silu(x["o"].double())
+    ho = gc.PKG.mlstm_chunkwise(*_dev(x), chunk_size=chunk, o=x["o"].cuda())
+    assert orc.max_abs_rel(ho, ref_o) < TOL_16
+    if S >= 2 * chunk:
+        cut = chunk
+        first = [t[:, :, :cut].contiguous() for t in _dev(x)]
+        second = [t[:, :, cut:].contiguous() for t in _dev(x)]
+        h1, st = gc.PKG.mlstm_chunkwise(*first, chunk_size=chunk, return_state=True)
+        h2 = gc.PKG.mlstm_chunkwise(*second, chunk_size=chunk, initial=st)
+        assert orc.max_abs_rel(torch.cat([h1, h2], 2), ref) < TOL_16
+    if S >= 3 * chunk:
+        edges = (0, chunk, 2 * chunk, S)
+        segs = []
+        for a, b in zip(edges[:-1], edges[1:]):
+            part = [x[n][:, :, a:b].contiguous().cuda() for n in ("q", "k", "v", "f", "i")]
+            segs.append(mc.ChunkSegment(*part, chunk_size=chunk, o=x["o"][:, :, a:b].contiguous().cuda()))
+        gathered = torch.stack([sg.sp_local() for sg in segs])
+        hs = torch.cat([sg.sp_apply(gathered, g) for g, sg in enumerate(segs)], 2)
+        assert orc.max_abs_rel(hs, ref_o) < TOL_16
+    # the backward is built for D = 128: the library says so instead of computing something else
+    L = gc._lib.lib()
+    assert L.mlstm_chunk_bwd_workspace(1, 2, S, D, gc._lib.dtype_code(x["q"]), 0, chunk) == 0
+
+
+def test_scan_entry_takes_the_chunkwise_form_at_256(gc):
+    """mlstm_scan on a long 16-bit sequence at D = 256 (S > 2 D): routed to the chunkwise form by the library; against
+    the oracle and against the parallel kernel forced by hand."""
+    S, D = 2304, 256
+    x = gc.make_inputs(1, 2, S, D, torch.bfloat16, f_mean=3.0, qkv_scale=D ** -0.5, seed=77, with_o=True)
+    d = [x[n].cuda() for n in ("q", "k", "v", "f", "i", "o")]
+    L = gc._lib.lib()
+    dt = gc._lib.dtype_code(x["q"])
+    assert L.mlstm_scan_fwd_workspace(1, 2, S, D, dt, 0) == L.mlstm_chunk_workspace(1, 2, S, D, dt, 256)
+    h = gc.PKG.mlstm_scan(*d)
+    ref = orc.matmul_forward(x["q"], x["k"], x["v"], x["f"], x["i"]) * torch.nn.functional.silu(x["o"].double())
+    assert orc.max_abs_rel(h, ref) < TOL_16
+    h2 = gc.PKG.mlstm_matmul(*d[:5]) * torch.nn.functional.silu(d[5].float())
+    assert orc.max_abs_rel(h, h2) < TOL_16
+
+
 def test_long_context_configuration_at_its_own_size(gc):
     """Configuration 5 (S = 65 536, D = 128, bf16, chunk 256: 256 blocks of carry) on one head against the
     recurrent oracle (one step per time index), compared on the first block, two blocks in the middle and

@@ -20,9 +20,9 @@ inline size_t al(size_t x) { return (x + WS_ALIGN - 1) / WS_ALIGN * WS_ALIGN; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <typename T16>
-__global__ void identity_kernel(T16* ident) {
+__global__ void identity_kernel(T16* ident, int D) {   // D x D
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx < TILE * TILE) ident[idx] = from_f32<T16>((idx / TILE) == (idx % TILE) ? 1.0f : 0.0f);
+    if (idx < D * D) ident[idx] = from_f32<T16>((idx / D) == (idx % D) ? 1.0f : 0.0f);
 }
 
 // One thread owns four consecutive elements of a slice's [D*D + D] state (matrix, then normaliser
@@ -220,7 +220,7 @@ ChunkWs carve(void* ws, int BH, int S, int D, int chunk) {
     w.An_bound = static_cast<double*>(take(static_cast<size_t>(BH) * (w.NB + 1) * sizeof(double)));
     const size_t gs = gates_scratch_bytes(BH, static_cast<int>(Spad));
     w.gscratch = gs ? static_cast<double*>(take(gs)) : nullptr;
-    w.ident = take(static_cast<size_t>(TILE) * TILE * 2);
+    w.ident = take(static_cast<size_t>(D) * D * 2);
     w.U = static_cast<float*>(take(nblk * D * D * sizeof(float)));
     w.zU = static_cast<float*>(take(nblk * D * sizeof(float)));
     w.states = take(nblk * D * D * 2);
@@ -234,10 +234,11 @@ ChunkWs carve(void* ws, int BH, int S, int D, int chunk) {
     return w;
 }
 
-int check_chunk_args(int B, int NH, int S, int D, int dtype, int chunk) {
+// The forward (block states, carry, output, sequence-parallel stages) takes D = 128 and 256, the backward D = 128.
+int check_chunk_args(int B, int NH, int S, int D, int dtype, int chunk, bool backward = false) {
     if (B <= 0 || NH <= 0 || S <= 0 || D <= 0 || chunk <= 0) return MLSTM_E_ARG;
     if (dtype != MLSTM_DT_F16 && dtype != MLSTM_DT_BF16) return MLSTM_E_UNSUPPORTED;  // tensor-core path only
-    if (D != 128) return MLSTM_E_UNSUPPORTED;
+    if (D != 128 && !(D == 256 && !backward)) return MLSTM_E_UNSUPPORTED;
     if (chunk % TILE != 0) return MLSTM_E_SHAPE;
     if (static_cast<long long>(B) * NH > 65535) return MLSTM_E_SHAPE;
     return MLSTM_OK;
@@ -260,12 +261,12 @@ int launch_fwdc(const void* q, const void* k, const void* v, const void* o, void
 
 }  // namespace
 
-int launch_identity(void* ident, int dtype, cudaStream_t st) {
-    const int n = TILE * TILE;
+int launch_identity(void* ident, int D, int dtype, cudaStream_t st) {
+    const int n = D * D;
     if (dtype == MLSTM_DT_BF16)
-        identity_kernel<__nv_bfloat16><<<(n + 255) / 256, 256, 0, st>>>(static_cast<__nv_bfloat16*>(ident));
+        identity_kernel<__nv_bfloat16><<<(n + 255) / 256, 256, 0, st>>>(static_cast<__nv_bfloat16*>(ident), D);
     else
-        identity_kernel<__half><<<(n + 255) / 256, 256, 0, st>>>(static_cast<__half*>(ident));
+        identity_kernel<__half><<<(n + 255) / 256, 256, 0, st>>>(static_cast<__half*>(ident), D);
     return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
@@ -335,7 +336,7 @@ int mlstm_chunk_prepare(const void* k, const void* v, const void* f, const void*
     if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, w.m, BH, S, Spad, dtype, st, carry_in, summary_out,
                                w.An_bound, chunk, w.gscratch, w.gaw)) != MLSTM_OK)
         return rc;
-    if ((rc = launch_identity(w.ident, dtype, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_identity(w.ident, D, dtype, st)) != MLSTM_OK) return rc;
     // U_k[key, value] = sum_j exp(a_j - A_end(k)) k_j[key] v_j[value];  zU_k[key] = sum_j exp(...) k_j[key]
     PassParams p{};
     p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8;
@@ -424,7 +425,7 @@ static ChunkBwdWs carve_bwd_chunk(void* ws, int BH, int S, int D, int chunk, boo
 }
 
 size_t mlstm_chunk_bwd_workspace(int B, int NH, int S, int D, int dtype, int h_dtype, int chunk) {
-    if (check_chunk_args(B, NH, S, D, dtype, chunk) != MLSTM_OK) return 0;
+    if (check_chunk_args(B, NH, S, D, dtype, chunk, true) != MLSTM_OK) return 0;
     return carve_bwd_chunk(nullptr, B * NH, S, D, chunk, h_dtype != dtype).bytes;
 }
 
@@ -432,7 +433,7 @@ int mlstm_chunk_bwd(const void* dh, const void* q, const void* k, const void* v,
                     const float* m, const float* b, void* dq, void* dk, void* dv, void* df, void* di, void* workspace,
                     size_t workspace_bytes, int B, int NH, int S, int D, int dtype, int h_dtype, int chunk, void* stream) {
     if (!dh || !q || !k || !v || !f || !i || !h || !m || !b || !dq || !dk || !dv || !df || !di) return MLSTM_E_ARG;
-    int rc = check_chunk_args(B, NH, S, D, dtype, chunk);
+    int rc = check_chunk_args(B, NH, S, D, dtype, chunk, true);
     if (rc != MLSTM_OK) return rc;
     if (h_dtype != MLSTM_DT_F32 && h_dtype != dtype) return MLSTM_E_ARG;
     if (!aligned16(dh) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(h) || !aligned16(dq) ||
@@ -449,7 +450,7 @@ int mlstm_chunk_bwd(const void* dh, const void* q, const void* k, const void* v,
     if ((rc = launch_gates_fwd(f, i, c.ga, c.gAn, c.a_ref, c.An_ref, nullptr, BH, S, Spad, dtype, st, nullptr, nullptr,
                                c.An_bound, chunk, c.gscratch, c.gaw)) != MLSTM_OK)
         return rc;
-    if ((rc = launch_identity(c.ident, dtype, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_identity(c.ident, D, dtype, st)) != MLSTM_OK) return rc;
     PassParams p{};
     p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = c.status; p.sched = c.status + 8;
     p.chunk_tiles = chunk / TILE; p.NB = c.NB; p.An_bound = c.An_bound; p.ident = c.ident;

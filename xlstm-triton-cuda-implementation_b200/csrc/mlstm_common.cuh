@@ -139,7 +139,7 @@ int launch_gates_fwd(const void* f, const void* i, float* ga_rel, float* gAn_rel
 // bytes of `scratch` that let launch_gates_fwd cut long slices into segments (0: not worth it)
 size_t gates_scratch_bytes(int BH, int Spad);
 // chunk.cu
-int launch_identity(void* ident, int dtype, cudaStream_t st);
+int launch_identity(void* ident, int D, int dtype, cudaStream_t st);
 // rec (optional): per-slice records of rec_stride floats that receive S_end | z_end | summary {F, A} (two doubles)
 int launch_state_scan(const float* U, const float* zU, const double* An_bound, const float* S_in, const float* z_in,
                       void* states16, float* zstate, float* S_end, float* z_end, int BH, int NB, int D, int dtype,

@@ -128,7 +128,13 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     constexpr bool IS_DK = (MODE == DK || MODE == DKC);
     // chunkwise passes: the row tile's own block plus one step that applies a carried state
     constexpr bool CHUNKED = (MODE == FWDC || MODE == DQC || MODE == DKC || MODE == DVC);
-    static_assert((!CHUNKED && MODE != STATE) || (D == 128 && ES == 2), "chunkwise passes are built for 16-bit D = 128");
+    static_assert((!CHUNKED && MODE != STATE) || (ES == 2 && (D == 128 || (D == 256 && (MODE == FWDC || MODE == STATE)))),
+                  "chunkwise passes are built for 16-bit inputs: D = 128, and D = 256 in the forward");
+    // A carried state is D x D.  As a streamed operand it comes in D / 128 tiles of 128 key rows, each with its own
+    // "state step" (T = the matching 128 columns of the stationary tile through the matching rows of the identity);
+    // as the output of STATE it is written in D / 128 work items of 128 key rows each.
+    constexpr int NS = CHUNKED ? D / TILE : 0;
+    constexpr int NHV = (MODE == STATE) ? D / TILE : 1;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
@@ -160,7 +166,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int NT = p.Spad / TILE;
-    const int per_slice = (MODE == STATE) ? p.NB : NT;     // work items per batch*head slice
+    const int per_slice = (MODE == STATE) ? p.NB * NHV : NT;     // work items per batch*head slice
     const int total = per_slice * p.BH;
 
     // A work item = one stationary tile (STATE: one block) of one slice.  The CTA is persistent and
@@ -174,7 +180,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         return ok ? __shfl_sync(0xffffffffu, item_ids[n & 3], 0) : -1;
     };
     struct Item {
-        int bh, tile, blk, first, nsteps;
+        int bh, tile, blk, first, nsteps, half;
     };
     auto decode = [&](int id) {
         Item it;
@@ -188,24 +194,25 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         it.bh = set * SLICE_SET + (within - w * set_size);
         // tile: the stationary tile (STATE: the block).  nsteps / stream_tile: what is streamed.
         //   FWD, DQ   key tiles 0..tile, diagonal last          DK, DV  query tiles tile..NT-1, diagonal first
-        //   FWDC, DQC step 0 applies the block's inbound state, then key tiles block_start..tile
-        //   DKC, DVC  step 0 applies the state carried back from the later blocks, then query tiles tile..block_end
+        //   FWDC, DQC the first NS steps apply the block's inbound state, then key tiles block_start..tile
+        //   DKC, DVC  the first NS steps apply the state carried back from the later blocks, then query tiles tile..block_end
         //   STATE     the block's tiles
-        it.tile = (MODE == STATE) ? w : (ROWS_ARE_Q ? (NT - 1 - w) : w);
+        it.tile = (MODE == STATE) ? w / NHV : (ROWS_ARE_Q ? (NT - 1 - w) : w);
+        it.half = (MODE == STATE) ? w % NHV : 0;     // STATE: which 128 key rows of the block's state
         it.blk = CHUNKED ? it.tile / p.chunk_tiles : (MODE == STATE ? it.tile : 0);
         it.first = (CHUNKED || MODE == STATE) ? it.blk * p.chunk_tiles : 0;
         const int last = min(it.first + p.chunk_tiles, NT) - 1;   // last tile of the block
-        it.nsteps = CHUNKED ? (ROWS_ARE_Q ? (it.tile - it.first + 2) : (last - it.tile + 2))
+        it.nsteps = CHUNKED ? (ROWS_ARE_Q ? (it.tile - it.first + 1 + NS) : (last - it.tile + 1 + NS))
                   : (MODE == STATE) ? (min(p.chunk_tiles, NT - it.first))
                   : (ROWS_ARE_Q ? (it.tile + 1) : (NT - it.tile));
         return it;
     };
     auto stream_tile = [&](const Item& it, int t) {
-        if (CHUNKED) return ROWS_ARE_Q ? (it.first + t - 1) : (it.tile + t - 1);  // t >= 1
+        if (CHUNKED) return ROWS_ARE_Q ? (it.first + t - NS) : (it.tile + t - NS);  // t >= NS
         if (MODE == STATE) return it.first + t;
         return ROWS_ARE_Q ? t : (it.tile + t);
     };
-    auto is_state_step = [&](int t) { return CHUNKED && t == 0; };
+    auto is_state_step = [&](int t) { return CHUNKED && t < NS; };
 
     if (threadIdx.x == 0) {
         mbar_init(bar_x, 1);
@@ -275,15 +282,15 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 if (!ok) break;
                 mbar_expect_tx(bar_x, C::X_BYTES);
                 for (int c = 0; c < DL / C::EPB; c++) {
-                    if (MODE == STATE) tma_load_3d(sX + c * BOX_BYTES, &tmI, bar_x, c * C::EPB, 0, 0);
+                    if (MODE == STATE) tma_load_3d(sX + c * BOX_BYTES, &tmI, bar_x, c * C::EPB, it.half * TILE, 0);
                     else tma_load_3d(sX + c * BOX_BYTES, &tmX, bar_x, c * C::EPB, it.tile * TILE, it.bh);
                 }
                 auto load_y = [&](int t) {
-                    if (is_state_step(t)) load_tile(&tmI, 0, 0, 0);
+                    if (is_state_step(t)) load_tile(&tmI, 0, t * TILE, 0);
                     else load_tile(&tmY, 0, stream_tile(it, t) * TILE, it.bh);
                 };
                 auto load_z = [&](int t) {
-                    if (is_state_step(t)) load_tile(&tmS, 0, 0, it.bh * p.NB + it.blk);
+                    if (is_state_step(t)) load_tile(&tmS, 0, t * TILE, it.bh * p.NB + it.blk);
                     else load_tile(&tmZ, 0, stream_tile(it, t) * TILE, it.bh);
                 };
                 // same order as the MMA issuer consumes: Y(0), then Y(t), Z(t-1) ..., Z(last)
@@ -560,7 +567,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             // state step: the column term is the inbound normaliser vector z (a weight, not an exponent)
             // off the diagonal the column term comes as a factor exp2(ec) (see gates.cu), on the diagonal tile as
             // the exponent itself: there a masked column can lie above the row's maximum and only the sum is safe
-            const float* ce = (state_step && MODE == FWDC) ? p.zstate + (static_cast<size_t>(bh) * p.NB + blk) * D
+            const float* ce = (state_step && MODE == FWDC) ? p.zstate + (static_cast<size_t>(bh) * p.NB + blk) * D + t * TILE
                                                            : (diag ? p.col_rel : p.col_w) + vec_base + st * TILE;
             // column terms do not depend on the contraction: fetch them before waiting
             float cv[32];
@@ -672,7 +679,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         auto row_sums = [&]() {
             if (MODE == STATE) {
                 const float zsum = exchange(rowsum);
-                if (ok && grp == 0 && p.b_out) p.b_out[(static_cast<size_t>(bh) * p.NB + blk) * D + r] = zsum;
+                if (ok && grp == 0 && p.b_out) p.b_out[(static_cast<size_t>(bh) * p.NB + blk) * D + it.half * TILE + r] = zsum;
             }
             if (IS_FWD) {
                 // on its way during the exchange
@@ -711,7 +718,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             if (!ok) break;
             // STATE writes block (bh, blk) of [BH, NB, D, D]; everything else row `grow` of [BH, S, D]
             const size_t row_off = (MODE == STATE)
-                                       ? ((static_cast<size_t>(bh) * p.NB + blk) * D + r) * D
+                                       ? ((static_cast<size_t>(bh) * p.NB + blk) * D + it.half * TILE + r) * D
                                        : (static_cast<size_t>(bh) * p.S + (row_ok ? grow : 0)) * D;
             float dot = 0.0f;
             OutT* orow = reinterpret_cast<OutT*>(p.out) + row_off + c0;
@@ -970,7 +977,7 @@ int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
     constexpr bool CHUNKED = (MODE == FWDC || MODE == DQC || MODE == DKC || MODE == DVC);
     if (CHUNKED || MODE == STATE) {
         if (!p.ident || p.chunk_tiles <= 0 || p.NB <= 0 || !p.An_bound) return MLSTM_E_ARG;
-        if ((rc = make_map(&mi, p.ident, 1, TILE, TILE, in_dtype)) != MLSTM_OK) return rc;
+        if ((rc = make_map(&mi, p.ident, 1, D, D, in_dtype)) != MLSTM_OK) return rc;
     }
     if (CHUNKED) {
         if (!p.states || ((MODE == FWDC || MODE == DQC) && !p.zstate) || (MODE == DKC && !p.rvec)) return MLSTM_E_ARG;
@@ -1000,7 +1007,7 @@ int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
         }
     }
     const int NT = p.Spad / TILE;
-    const long long total = static_cast<long long>(MODE == STATE ? p.NB : NT) * p.BH;
+    const long long total = static_cast<long long>(MODE == STATE ? p.NB * (D / TILE) : NT) * p.BH;
     if (total > 0x7fffffffLL) return MLSTM_E_SHAPE;
     const int sms = sm_count();
     if (sms <= 0) return MLSTM_E_CUDA;
@@ -1125,10 +1132,13 @@ int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, c
         case DK: return launch_d<DK>(p, in_dtype, out_dtype, st);
         case DV: return launch_d<DV>(p, in_dtype, out_dtype, st);
         case FWDC:
+            if (p.D == 256) return launch_fmt<FWDC, 256>(p, in_dtype, out_dtype, st);
             if (p.D != 128) return MLSTM_E_UNSUPPORTED;
             return launch_fmt<FWDC, 128>(p, in_dtype, out_dtype, st);
         case STATE:
-            if (p.D != 128 || out_dtype != MLSTM_DT_F32) return MLSTM_E_UNSUPPORTED;
+            if (out_dtype != MLSTM_DT_F32) return MLSTM_E_UNSUPPORTED;
+            if (p.D == 256) return launch_fmt<STATE, 256>(p, in_dtype, out_dtype, st);
+            if (p.D != 128) return MLSTM_E_UNSUPPORTED;
             return launch_fmt<STATE, 128>(p, in_dtype, out_dtype, st);
         case DQC:
             if (p.D != 128) return MLSTM_E_UNSUPPORTED;

@@ -5,7 +5,8 @@
 
 The reference has no long-sequence entry point of its own; what this extends is the inter-block carry
 of its scan path (mlstm_scan.py:143-195) with the carry algebra of its scan operators
-(mlstm_scan.py:15-26).  Inputs are 16-bit, D = 128; h is float32 unless ``h_dtype`` says otherwise.
+(mlstm_scan.py:15-26).  Inputs are 16-bit, D = 128 or 256 (the backward: D = 128); h is float32 unless ``h_dtype``
+says otherwise.
 
 Sequence-parallel form: rank r of the group holds the r-th contiguous segment of every sequence
 (all heads).  ONE all-gather connects the ranks and there is no other communication: every rank first
@@ -47,7 +48,7 @@ class ChunkSegment:
         self.L = _lib.lib()
         nbytes = self.L.mlstm_chunk_workspace(self.B, self.NH, self.S, self.D, self.dt, self.chunk)
         if nbytes == 0:
-            raise _lib.MlstmError(-4, "mlstm_chunk_workspace (needs float16/bfloat16, D = 128, chunk % 128 == 0)")
+            raise _lib.MlstmError(-4, "mlstm_chunk_workspace (needs float16/bfloat16, D = 128 or 256, chunk % 128 == 0)")
         # The workspace carries the gates and block states from stage to stage.  A private buffer is safe
         # however segments are interleaved; the per-stream shared one saves a large allocation per call
         # and is what the one-shot functions below use (they finish a segment before starting another).

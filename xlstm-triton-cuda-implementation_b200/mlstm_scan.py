@@ -11,7 +11,7 @@ reference's grid needs them (positive, dividing D, mlstm_scan.py:297, 309-310) a
 The library picks one of three forms by shape (``mlstm_scan_fwd`` in include/mlstm_b200.h):
   * D above 256 (the reference demo, D = 1024): two tensor-core passes, the gated S x S matrix once
     and then W V; the quadratic form is the cheapest there because the D x D state is larger than S x S;
-  * S much longer than D (16-bit inputs, D = 128): chunkwise, i.e. per-block (C, n) states with the
+  * S much longer than D (16-bit inputs, D = 128 or 256): chunkwise, i.e. per-block (C, n) states with the
     stabiliser known up front, an inter-block carry and the output from the carried state, which is
     the mechanism of the reference's three scan kernels (mlstm_scan.py:74-137, 143-195, 200-278);
   * otherwise the parallel forward with silu(o) in its epilogue.
