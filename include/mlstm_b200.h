@@ -159,8 +159,7 @@ int mlstm_forward_f16_static_status(int* host_status, void* stream);
 
 /* Chunkwise forward for long sequences, with a state that can be carried across segments (GPUs).
  * The reference has no such entry point; the mechanism it extends is the scan path's inter-block carry
- * (mlstm_scan.py:143-195, operators :15-26).  16-bit inputs, D = 128 or 256 (mlstm_chunk_bwd: D = 128), chunk a
- * multiple of 128.
+ * (mlstm_scan.py:143-195, operators :15-26).  16-bit inputs, D = 128 or 256, chunk a multiple of 128.
  * mlstm_scan_fwd uses it by itself for sequences much longer than the head dimension.
  * A segment is processed in this order (all on one stream, one workspace):
  *   mlstm_chunk_gate_summary  (optional) local {F_end, A_end} per slice with no carry

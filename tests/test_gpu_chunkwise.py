@@ -122,7 +122,8 @@ def test_sequence_parallel_stages_on_one_gpu(gc, cuts, f_mean):
 def test_chunkwise_at_head_dimension_256(gc, dtype, S, chunk, f_mean):
     """D = 256: a block's state is written in two halves of 128 key rows and applied in two state steps; the
     forward against the oracle, with the output gate, in two calls with the state carried, and split over three
-    segments through the sequence-parallel stages."""
+    segments through the sequence-parallel stages; then the chunkwise backward (its state steps are split the same
+    way) against the closed-form backward of the oracle."""
     D = 256
     mc = importlib.import_module(PKG + ".mlstm_chunkwise")
     x = gc.make_inputs(1, 2, S, D, dtype, f_mean=f_mean, qkv_scale=D ** -0.5, seed=S + chunk + 2, with_o=True)
@@ -149,9 +150,14 @@ def test_chunkwise_at_head_dimension_256(gc, dtype, S, chunk, f_mean):
         gathered = torch.stack([sg.sp_local() for sg in segs])
         hs = torch.cat([sg.sp_apply(gathered, g) for g, sg in enumerate(segs)], 2)
         assert orc.max_abs_rel(hs, ref_o) < TOL_16
-    # the backward is built for D = 128: the library says so instead of computing something else
-    L = gc._lib.lib()
-    assert L.mlstm_chunk_bwd_workspace(1, 2, S, D, gc._lib.dtype_code(x["q"]), 0, chunk) == 0
+    names = ("q", "k", "v", "f", "i")
+    t = {n: x[n].cuda().requires_grad_(True) for n in names}
+    hg = gc.PKG.mlstm_chunkwise(*(t[n] for n in names), chunk_size=chunk)
+    hg.backward(x["dh"].cuda())
+    torch.cuda.synchronize()
+    for n, r in zip(names, gc.oracle_backward(x, torch.float32)):
+        assert t[n].grad.dtype == dtype
+        assert orc.max_abs_rel(t[n].grad, r) < TOL_16, n
 
 
 def test_scan_entry_takes_the_chunkwise_form_at_256(gc):

@@ -234,11 +234,10 @@ ChunkWs carve(void* ws, int BH, int S, int D, int chunk) {
     return w;
 }
 
-// The forward (block states, carry, output, sequence-parallel stages) takes D = 128 and 256, the backward D = 128.
-int check_chunk_args(int B, int NH, int S, int D, int dtype, int chunk, bool backward = false) {
+int check_chunk_args(int B, int NH, int S, int D, int dtype, int chunk) {
     if (B <= 0 || NH <= 0 || S <= 0 || D <= 0 || chunk <= 0) return MLSTM_E_ARG;
     if (dtype != MLSTM_DT_F16 && dtype != MLSTM_DT_BF16) return MLSTM_E_UNSUPPORTED;  // tensor-core path only
-    if (D != 128 && !(D == 256 && !backward)) return MLSTM_E_UNSUPPORTED;
+    if (D != 128 && D != 256) return MLSTM_E_UNSUPPORTED;
     if (chunk % TILE != 0) return MLSTM_E_SHAPE;
     if (static_cast<long long>(B) * NH > 65535) return MLSTM_E_SHAPE;
     return MLSTM_OK;
@@ -425,7 +424,7 @@ static ChunkBwdWs carve_bwd_chunk(void* ws, int BH, int S, int D, int chunk, boo
 }
 
 size_t mlstm_chunk_bwd_workspace(int B, int NH, int S, int D, int dtype, int h_dtype, int chunk) {
-    if (check_chunk_args(B, NH, S, D, dtype, chunk, true) != MLSTM_OK) return 0;
+    if (check_chunk_args(B, NH, S, D, dtype, chunk) != MLSTM_OK) return 0;
     return carve_bwd_chunk(nullptr, B * NH, S, D, chunk, h_dtype != dtype).bytes;
 }
 
@@ -433,7 +432,7 @@ int mlstm_chunk_bwd(const void* dh, const void* q, const void* k, const void* v,
                     const float* m, const float* b, void* dq, void* dk, void* dv, void* df, void* di, void* workspace,
                     size_t workspace_bytes, int B, int NH, int S, int D, int dtype, int h_dtype, int chunk, void* stream) {
     if (!dh || !q || !k || !v || !f || !i || !h || !m || !b || !dq || !dk || !dv || !df || !di) return MLSTM_E_ARG;
-    int rc = check_chunk_args(B, NH, S, D, dtype, chunk, true);
+    int rc = check_chunk_args(B, NH, S, D, dtype, chunk);
     if (rc != MLSTM_OK) return rc;
     if (h_dtype != MLSTM_DT_F32 && h_dtype != dtype) return MLSTM_E_ARG;
     if (!aligned16(dh) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(h) || !aligned16(dq) ||

@@ -128,8 +128,8 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     constexpr bool IS_DK = (MODE == DK || MODE == DKC);
     // chunkwise passes: the row tile's own block plus one step that applies a carried state
     constexpr bool CHUNKED = (MODE == FWDC || MODE == DQC || MODE == DKC || MODE == DVC);
-    static_assert((!CHUNKED && MODE != STATE) || (ES == 2 && (D == 128 || (D == 256 && (MODE == FWDC || MODE == STATE)))),
-                  "chunkwise passes are built for 16-bit inputs: D = 128, and D = 256 in the forward");
+    static_assert((!CHUNKED && MODE != STATE) || (ES == 2 && (D == 128 || D == 256)),
+                  "chunkwise passes are built for 16-bit inputs, D = 128 and 256");
     // A carried state is D x D.  As a streamed operand it comes in D / 128 tiles of 128 key rows, each with its own
     // "state step" (T = the matching 128 columns of the stationary tile through the matching rows of the identity);
     // as the output of STATE it is written in D / 128 work items of 128 key rows each.
@@ -1141,12 +1141,15 @@ int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, c
             if (p.D != 128) return MLSTM_E_UNSUPPORTED;
             return launch_fmt<STATE, 128>(p, in_dtype, out_dtype, st);
         case DQC:
+            if (p.D == 256) return launch_fmt<DQC, 256>(p, in_dtype, out_dtype, st);
             if (p.D != 128) return MLSTM_E_UNSUPPORTED;
             return launch_fmt<DQC, 128>(p, in_dtype, out_dtype, st);
         case DKC:
+            if (p.D == 256) return launch_fmt<DKC, 256>(p, in_dtype, out_dtype, st);
             if (p.D != 128) return MLSTM_E_UNSUPPORTED;
             return launch_fmt<DKC, 128>(p, in_dtype, out_dtype, st);
         case DVC:
+            if (p.D == 256) return launch_fmt<DVC, 256>(p, in_dtype, out_dtype, st);
             if (p.D != 128) return MLSTM_E_UNSUPPORTED;
             return launch_fmt<DVC, 128>(p, in_dtype, out_dtype, st);
     }

@@ -5,8 +5,7 @@
 
 The reference has no long-sequence entry point of its own; what this extends is the inter-block carry
 of its scan path (mlstm_scan.py:143-195) with the carry algebra of its scan operators
-(mlstm_scan.py:15-26).  Inputs are 16-bit, D = 128 or 256 (the backward: D = 128); h is float32 unless ``h_dtype``
-says otherwise.
+(mlstm_scan.py:15-26).  Inputs are 16-bit, D = 128 or 256; h is float32 unless ``h_dtype`` says otherwise.
 
 Sequence-parallel form: rank r of the group holds the r-th contiguous segment of every sequence
 (all heads).  ONE all-gather connects the ranks and there is no other communication: every rank first
@@ -159,7 +158,7 @@ def mlstm_chunkwise_backward(dh, q, k, v, f, i, h, m, b, chunk_size=256):
     L = _lib.lib()
     nbytes = L.mlstm_chunk_bwd_workspace(B, NH, S, D, dt, hdt, chunk)
     if nbytes == 0:
-        raise _lib.MlstmError(-4, "mlstm_chunk_bwd_workspace (needs float16/bfloat16, D = 128, chunk % 128 == 0)")
+        raise _lib.MlstmError(-4, "mlstm_chunk_bwd_workspace (needs float16/bfloat16, D = 128 or 256, chunk % 128 == 0)")
     ws = _lib.workspace(nbytes, dev)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     df, di = torch.empty_like(f), torch.empty_like(i)

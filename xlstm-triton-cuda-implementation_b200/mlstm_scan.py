@@ -26,7 +26,7 @@ inside the reference's own 1e-2 check), IEEE fp32 dot products on the CUDA cores
 false or at any other D.
 
 The reference's scan is forward only (README.md:97).  Here inputs that require gradients get them, behind
-the output gate's own derivative: long 16-bit sequences at D = 128 through the chunkwise forward and the
+the output gate's own derivative: long 16-bit sequences at D = 128 or 256 through the chunkwise forward and the
 chunkwise backward (states carried forward for dQ and back for dK, dV; linear in S), everything else
 through the parallel kernels (``mlstm_matmul_backward``), whose cost is quadratic in S.
 """
@@ -41,11 +41,11 @@ __all__ = ["mlstm_scan", "output_gate_forward", "output_gate_backward"]
 def _chunkwise_shape(q):
     """Whether the scan entry's chunkwise form (and with it the chunkwise backward) serves this input."""
     B, NH, S, D = q.shape
-    return q.dtype in (torch.float16, torch.bfloat16) and D == 128 and S > 2 * D and S > 512
+    return q.dtype in (torch.float16, torch.bfloat16) and D in (128, 256) and S > 2 * D and S > 512
 
 
 class _ScanWithGrad(torch.autograd.Function):
-    """mLSTM(q, k, v, f, i) * silu(o) with gradients for all six inputs.  Long 16-bit sequences at D = 128 take
+    """mLSTM(q, k, v, f, i) * silu(o) with gradients for all six inputs.  Long 16-bit sequences at D = 128, 256 take
     the chunkwise forward and backward (linear in S); everything else the parallel kernels (quadratic)."""
 
     @staticmethod
