@@ -238,6 +238,22 @@ def test_chunkwise_forward_backward_against_reference_golden(gc, golden_dir):
         assert orc.max_abs_rel(t[n].grad.float(), r) < TOL_16, n
 
 
+def test_chunkwise_backward_of_a_long_slice(gc):
+    """S = 8448 (three 4096-position segments of the gate scan and of the dF scan, 33 blocks of carried state in each
+    direction): the chunkwise backward against the parallel backward kernels on the same inputs."""
+    S, D = 8448, 128
+    x = gc.make_inputs(1, 2, S, D, torch.bfloat16, f_mean=3.0, qkv_scale=D ** -0.5, seed=84)
+    d = _dev(x)
+    h, m, b = gc.PKG.mlstm_matmul_forward(*d)
+    dh = x["dh"].cuda()
+    ref = gc.PKG.mlstm_matmul_backward(dh, *d, h, m, b)
+    mc = importlib.import_module(PKG + ".mlstm_chunkwise")
+    got = mc.mlstm_chunkwise_backward(dh, *d, h, m, b, chunk_size=256)
+    torch.cuda.synchronize()
+    for name, g1, g2 in zip(("dq", "dk", "dv", "df", "di"), got, ref):
+        assert orc.max_abs_rel(g1, g2) < TOL_16, name
+
+
 def test_chunkwise_backward_with_16_bit_h(gc):
     """The backward through the C ABI with h and dh in the input type (no fp32 copy of h anywhere)."""
     mc = importlib.import_module(PKG + ".mlstm_chunkwise")

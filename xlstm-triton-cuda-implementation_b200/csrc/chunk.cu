@@ -25,10 +25,15 @@ __global__ void identity_kernel(T16* ident, int D) {   // D x D
     if (idx < D * D) ident[idx] = from_f32<T16>((idx / D) == (idx % D) ? 1.0f : 0.0f);
 }
 
-// One thread owns four consecutive elements of a slice's [D*D + D] state (matrix, then normaliser
-// vector) and walks the blocks in order.  It writes the INBOUND state of every block (16-bit matrix
-// for the tensor cores, fp32 vector; skipped when `states` is null) and, optionally, the state after
-// the last block (S_end / z_end with per-slice strides, so that they can sit inside a packed record).
+// One thread owns four consecutive elements of a slice's state (D x D matrix and D-vector, the normaliser) and walks
+// the blocks in order.  It writes the INBOUND state of every block (16-bit matrix for the tensor cores, fp32 vector;
+// skipped when `states` is null) and, optionally, the state after the last block (S_end / z_end with per-slice
+// strides, so that they can sit inside a packed record).
+// Work split: a CTA of SCAN_THREADS threads owns a patch of 32 rows x 16 columns of the matrix (thread t: row t / 4,
+// columns 4 (t % 4) .. +3), so that it writes 32 bytes per row of the row-major copy and, through a transpose in
+// shared memory, 64 bytes per row of the transposed copy (written element by element from registers, the
+// transposed copy cost 16 times its size in memory transactions: 0.4 ms per scan at 256 blocks of 128 x 128).
+// The CTAs behind the patches own the vector.
 // late_bound (optional, per slice): a carry that became known after the gate pass, see PassParams;
 // block contributions U_k were stabilised by the local block-end maximum and are rescaled to the
 // later, larger one on the way in.
@@ -36,27 +41,32 @@ __global__ void identity_kernel(T16* ident, int D) {   // D x D
 // contracts over the value dimension.  reverse: walk the blocks from the last to the first, which turns
 // the same recurrence into the backward's carried state R_{k-1} = exp(A_end(k-1) - A_end(k)) R_k + P_k
 // (block k then receives what the LATER blocks contribute).
-constexpr int SCAN_TB = 1024;   // blocks per tile of the factor tables of state_scan_kernel
+constexpr int SCAN_TB = 1024;       // blocks per tile of the factor tables of state_scan_kernel
+constexpr int SCAN_THREADS_S = 128;
+constexpr int PATCH_ROWS = 32, PATCH_COLS = 16;
 
 template <typename T16>
-__global__ void state_scan_kernel(const float* __restrict__ U, const float* __restrict__ zU,
-                                  const double* __restrict__ An_bound, const float* __restrict__ S_in,
-                                  const float* __restrict__ z_in, T16* __restrict__ states, float* __restrict__ zstate,
-                                  float* __restrict__ S_end, float* __restrict__ z_end, size_t S_end_stride,
-                                  size_t z_end_stride, int NB, int D, const double* __restrict__ late_bound,
-                                  const double* __restrict__ summary, double* __restrict__ summary_dst,
-                                  size_t summary_dst_stride, T16* __restrict__ statesT, int reverse) {
+__global__ void __launch_bounds__(SCAN_THREADS_S)
+state_scan_kernel(const float* __restrict__ U, const float* __restrict__ zU, const double* __restrict__ An_bound,
+                  const float* __restrict__ S_in, const float* __restrict__ z_in, T16* __restrict__ states,
+                  float* __restrict__ zstate, float* __restrict__ S_end, float* __restrict__ z_end, size_t S_end_stride,
+                  size_t z_end_stride, int NB, int D, const double* __restrict__ late_bound,
+                  const double* __restrict__ summary, double* __restrict__ summary_dst, size_t summary_dst_stride,
+                  T16* __restrict__ statesT, int reverse) {
     const int bh = blockIdx.y;
     const int DD = D * D;
-    const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    if (e == 0 && summary_dst) {
+    const int npc = D / PATCH_COLS;
+    const int npatch = (D / PATCH_ROWS) * npc;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && summary_dst) {
         double* dst = reinterpret_cast<double*>(reinterpret_cast<float*>(summary_dst) + bh * summary_dst_stride);
         dst[0] = summary[2 * bh];
         dst[1] = summary[2 * bh + 1];
     }
-    const bool valid = e < DD + D;     // threads past the end still help with the factor tables and the barriers
-    const bool is_vec = e >= DD;
-    const int off = is_vec ? e - DD : e;
+    const bool is_vec = static_cast<int>(blockIdx.x) >= npatch;     // uniform over the CTA
+    const int prow0 = (blockIdx.x / npc) * PATCH_ROWS, pcol0 = (blockIdx.x % npc) * PATCH_COLS;
+    const int lrow = threadIdx.x >> 2, lcol = (threadIdx.x & 3) * 4;
+    const int off = is_vec ? ((blockIdx.x - npatch) * SCAN_THREADS_S + threadIdx.x) * 4 : (prow0 + lrow) * D + pcol0 + lcol;
+    const bool valid = !is_vec || off < D;     // threads past the end still help with the factor tables and the barriers
     const size_t per_block = is_vec ? D : DD;
     const float* src = (is_vec ? zU : U) + static_cast<size_t>(bh) * NB * per_block + off;
     const float* init = is_vec ? z_in : S_in;
@@ -68,6 +78,11 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
     // same for every element: the CTA computes them once per tile of SCAN_TB blocks into shared memory (evaluated
     // per thread and block they were most of the kernel's instructions: 107 per warp and block against about 20 now).
     __shared__ float sd[SCAN_TB], sc[SCAN_TB];
+    // transposed patches on their way out: [column][row], two buffers so that one barrier per block is enough
+    __shared__ __align__(16) T16 tp[2][PATCH_COLS][PATCH_ROWS + 8];
+    const bool transposing = statesT != nullptr && !is_vec;
+    const int trow = threadIdx.x >> 3, tcol = (threadIdx.x & 7) * 4;   // this thread's piece of the transposed patch
+    int tbuf = 0;
     // blocks whose contributions are fetched ahead of the serial update
     constexpr int PF = 16;
     for (int t0 = 0; t0 < NB; t0 += SCAN_TB) {
@@ -82,7 +97,7 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
             sc[j] = exp2f(static_cast<float>(b1c - b1));   // 1 unless the late carry raised the block's stabiliser
         }
         __syncthreads();
-        if (!valid) continue;
+        if (is_vec && !valid) continue;
         for (int k0 = 0; k0 < tn; k0 += PF) {
             float4 u[PF];
 #pragma unroll
@@ -102,10 +117,15 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
                     T16 o[4] = {from_f32<T16>(s.x), from_f32<T16>(s.y), from_f32<T16>(s.z), from_f32<T16>(s.w)};
                     if (states)
                         *reinterpret_cast<uint2*>(states + (static_cast<size_t>(bh) * NB + k) * DD + off) = *reinterpret_cast<uint2*>(o);
-                    if (statesT) {
-                        const int row = off / D, col = off - row * D;
-                        T16* dstT = statesT + (static_cast<size_t>(bh) * NB + k) * DD + static_cast<size_t>(col) * D + row;
-                        dstT[0] = o[0]; dstT[D] = o[1]; dstT[2 * D] = o[2]; dstT[3 * D] = o[3];
+                    if (transposing) {   // (uniform over the CTA)
+                        tp[tbuf][lcol + 0][lrow] = o[0];
+                        tp[tbuf][lcol + 1][lrow] = o[1];
+                        tp[tbuf][lcol + 2][lrow] = o[2];
+                        tp[tbuf][lcol + 3][lrow] = o[3];
+                        __syncthreads();
+                        T16* dstT = statesT + (static_cast<size_t>(bh) * NB + k) * DD + static_cast<size_t>(pcol0 + trow) * D + prow0 + tcol;
+                        *reinterpret_cast<uint2*>(dstT) = *reinterpret_cast<const uint2*>(&tp[tbuf][trow][tcol]);
+                        tbuf ^= 1;
                     }
                 }
                 const float d = sd[k0 + j], c = sc[k0 + j];
@@ -127,20 +147,33 @@ __global__ void state_scan_kernel(const float* __restrict__ U, const float* __re
 //   p_k[d] = sum_{t in block k} beta_t g_t q_t[d],  beta_t = exp(A_end(k-1) - A_t) scale / n_t,  g_t = db_t n_t
 // (the matrix part sum_t beta_t q_t dh_t^T comes from the tensor-core STATE pass).  One block of D threads per
 // (block, slice); log2 beta_t = gB_rel[t] + An_ref[t / 64] - bound[k] with the vectors of the backward preparation.
+// The weights beta_t g_t of the block's positions are computed once (into shared memory), then every thread adds up
+// its dimension over them: evaluated per thread and position they were most of the kernel.
+constexpr int RVEC_MAX_CHUNK = 2048;   // positions of a block whose weights fit the table; longer blocks take several rounds
+
 template <typename T16>
 __global__ void rvec_partial_kernel(const T16* __restrict__ q, const float* __restrict__ gB_rel,
                                     const double* __restrict__ An_ref, const double* __restrict__ An_bound,
                                     const float* __restrict__ g, float* __restrict__ out, int S, int Spad, int NB, int chunk,
                                     int D) {
+    __shared__ float wt[RVEC_MAX_CHUNK];
     const int k = blockIdx.x, bh = blockIdx.y, d = threadIdx.x;
     const double b0 = An_bound[static_cast<size_t>(bh) * (NB + 1) + k];
     const int t0 = k * chunk, t1 = min(t0 + chunk, S);
     float acc = 0.0f;
-    for (int t = t0; t < t1; t++) {
-        const size_t vi = static_cast<size_t>(bh) * Spad + t;
-        const float e = gB_rel[vi] + static_cast<float>(An_ref[static_cast<size_t>(bh) * (Spad / REF_BLOCK) + t / REF_BLOCK] - b0);
-        const float w = exp2f(e) * g[vi];   // exp2(-inf) = 0 for the first block when nothing is carried in
-        acc = fmaf(w, to_f32<T16>(q[(static_cast<size_t>(bh) * S + t) * D + d]), acc);
+    for (int r0 = t0; r0 < t1; r0 += RVEC_MAX_CHUNK) {
+        const int rn = min(RVEC_MAX_CHUNK, t1 - r0);
+        __syncthreads();
+        for (int j = threadIdx.x; j < rn; j += blockDim.x) {
+            const int t = r0 + j;
+            const size_t vi = static_cast<size_t>(bh) * Spad + t;
+            const float e = gB_rel[vi] + static_cast<float>(An_ref[static_cast<size_t>(bh) * (Spad / REF_BLOCK) + t / REF_BLOCK] - b0);
+            wt[j] = exp2f(e) * g[vi];   // exp2(-inf) = 0 for the first block when nothing is carried in
+        }
+        __syncthreads();
+        const T16* qp = q + (static_cast<size_t>(bh) * S + r0) * D + d;
+#pragma unroll 8
+        for (int j = 0; j < rn; j++) acc = fmaf(wt[j], to_f32<T16>(qp[static_cast<size_t>(j) * D]), acc);
     }
     out[(static_cast<size_t>(bh) * NB + k) * D + d] = acc;
 }
@@ -273,9 +306,11 @@ int launch_state_scan(const float* U, const float* zU, const double* An_bound, c
                       void* states16, float* zstate, float* S_end, float* z_end, int BH, int NB, int D, int dtype,
                       cudaStream_t st, const double* late_bound, float* rec, size_t rec_stride, const double* summary,
                       void* statesT16, int reverse) {
-    const int threads = 128;   // small blocks: a slice has about 4 K threads of work, which should spread over all SMs
-    const int work = (D * D + D) / 4;
-    dim3 grid((work + threads - 1) / threads, BH);
+    // small CTAs: a slice has about 4 K threads of work, which should spread over all SMs
+    const int threads = SCAN_THREADS_S;
+    if (D % PATCH_ROWS != 0) return MLSTM_E_SHAPE;
+    const int npatch = (D / PATCH_ROWS) * (D / PATCH_COLS);
+    dim3 grid(npatch + (D / 4 + threads - 1) / threads, BH);
     size_t s_stride = static_cast<size_t>(D) * D, z_stride = D;
     double* sum_dst = nullptr;
     if (rec) {   // S_end | z_end | summary inside per-slice records
@@ -503,7 +538,7 @@ int mlstm_chunk_bwd(const void* dh, const void* q, const void* k, const void* v,
     p.col_g = nullptr; p.states = c.states;
     p.out = dv; p.dot_src = nullptr; p.dot_out = nullptr;
     if ((rc = launch_pass_tc(DVC, p, dtype, dtype, st)) != MLSTM_OK) return rc;
-    return launch_df(f, w.dI, w.Rdot, df, di, BH, S, Spad, dtype, st, TC_DOT_PARTS, static_cast<long long>(BH) * Spad);
+    return launch_df(f, w.dI, w.Rdot, df, di, BH, S, Spad, dtype, st, TC_DOT_PARTS, static_cast<long long>(BH) * Spad, c.gscratch);
 }
 
 int mlstm_chunk_read_mb(const void* workspace, size_t workspace_bytes, float* m, float* b, int B, int NH, int S, int D, int dtype,

@@ -263,30 +263,68 @@ __global__ void bwd_prep_kernel(const HT* __restrict__ h, const HT* __restrict__
     }
 }
 
-// One block per slice: dF_t = sigmoid(-f_t) * sum_{s<t} (dI_s - R_s), dF_0 = 0, and dI converted to
-// the output type (mlstm_matmul.py:316, 319-333).
+// dF_t = sigmoid(-f_t) * sum_{s<t} (dI_s - R_s), dF_0 = 0, and dI converted to the output type
+// (mlstm_matmul.py:316, 319-333).  One block per slice, or, for long slices, one block per segment of
+// seg_tokens positions (blockIdx.x = slice * nseg + segment) that starts from the sum of the segments before it:
+// seg_totals[slice * nseg + s] from df_total_kernel.
+// dI and R arrive as partial row dots (one per gate group of the tensor-core passes): fixed order of addition.
+__device__ __forceinline__ void df_terms(const float* __restrict__ dI, const float* __restrict__ R, size_t idx, int nparts,
+                                         long long part_stride, float& dIv, float& Rv) {
+    dIv = 0.0f;
+    Rv = 0.0f;
+    for (int k = 0; k < nparts; k++) {
+        dIv += dI[k * part_stride + idx];
+        Rv += R[k * part_stride + idx];
+    }
+}
+
+__global__ void __launch_bounds__(SCAN_THREADS) df_total_kernel(const float* __restrict__ dI, const float* __restrict__ R,
+                                                                double* __restrict__ seg_totals, int S, int Spad, int nparts,
+                                                                long long part_stride, int nseg, int seg_tokens) {
+    __shared__ double wsum[32];
+    const int bh = blockIdx.x / nseg, seg = blockIdx.x - bh * nseg;
+    const int t_begin = seg * seg_tokens, t_end = min(t_begin + seg_tokens, S);
+    double x = 0.0;
+    for (int t = t_begin + threadIdx.x; t < t_end; t += SCAN_THREADS) {
+        float dIv, Rv;
+        df_terms(dI, R, static_cast<size_t>(bh) * Spad + t, nparts, part_stride, dIv, Rv);
+        x += static_cast<double>(dIv) - static_cast<double>(Rv);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = x;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double tot = 0.0;
+        for (int w = 0; w < SCAN_THREADS / 32; w++) tot += wsum[w];
+        seg_totals[blockIdx.x] = tot;
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(SCAN_THREADS) df_kernel(const T* __restrict__ f, const float* __restrict__ dI,
                                                           const float* __restrict__ R, T* __restrict__ df,
                                                           T* __restrict__ di, int S, int Spad, int nparts,
-                                                          long long part_stride) {
+                                                          long long part_stride, const double* __restrict__ seg_totals,
+                                                          int nseg, int seg_tokens) {
     __shared__ double wsum[32];
     __shared__ double carry_sum;
-    const int bh = blockIdx.x;
-    if (threadIdx.x == 0) carry_sum = 0.0;
+    const int bh = blockIdx.x / nseg, seg = blockIdx.x - bh * nseg;
+    const int t_begin = seg * seg_tokens, t_end = min(t_begin + seg_tokens, S);
+    if (threadIdx.x == 0) {
+        double c = 0.0;
+        for (int s2 = 0; s2 < seg; s2++) c += seg_totals[bh * nseg + s2];
+        carry_sum = c;
+    }
     __syncthreads();
-    for (int base = 0; base < S; base += SCAN_THREADS) {
+    for (int base = t_begin; base < t_end; base += SCAN_THREADS) {
         const int t = base + threadIdx.x;
-        const bool in = t < S;
+        const bool in = t < t_end;
         double x = 0.0;
         float dIv = 0.0f;
         if (in) {
-            // dI and R arrive as partial row dots (one per gate group of the tensor-core passes): fixed order of addition
-            float Rv = 0.0f;
-            for (int k = 0; k < nparts; k++) {
-                dIv += dI[k * part_stride + static_cast<size_t>(bh) * Spad + t];
-                Rv += R[k * part_stride + static_cast<size_t>(bh) * Spad + t];
-            }
+            float Rv;
+            df_terms(dI, R, static_cast<size_t>(bh) * Spad + t, nparts, part_stride, dIv, Rv);
             x = static_cast<double>(dIv) - static_cast<double>(Rv);
         }
         const double G = block_scan_add(x, wsum, carry_sum);  // inclusive
@@ -506,18 +544,26 @@ int launch_bwd_prep(const void* h, const void* dh, const float* b, const float* 
 }
 
 int launch_df(const void* f, const float* dI, const float* R, void* df, void* di, int BH, int S, int Spad, int dtype,
-              cudaStream_t st, int nparts, long long part_stride) {
+              cudaStream_t st, int nparts, long long part_stride, double* scratch) {
+    // long slices, when the caller has scratch for the segment totals (gates_scratch_bytes covers it): one block per segment
+    const int nseg = scratch ? (S + GATE_SEG_TOKENS - 1) / GATE_SEG_TOKENS : 1;
+    const int seg_tokens = nseg > 1 ? GATE_SEG_TOKENS : S;
+    if (nseg > 1)
+        df_total_kernel<<<BH * nseg, SCAN_THREADS, 0, st>>>(dI, R, scratch, S, Spad, nparts, part_stride, nseg, seg_tokens);
+    const int blocks = BH * nseg;
     switch (dtype) {
         case MLSTM_DT_F32:
-            df_kernel<float><<<BH, SCAN_THREADS, 0, st>>>((const float*)f, dI, R, (float*)df, (float*)di, S, Spad, nparts, part_stride);
+            df_kernel<float><<<blocks, SCAN_THREADS, 0, st>>>((const float*)f, dI, R, (float*)df, (float*)di, S, Spad, nparts,
+                                                              part_stride, scratch, nseg, seg_tokens);
             break;
         case MLSTM_DT_F16:
-            df_kernel<__half><<<BH, SCAN_THREADS, 0, st>>>((const __half*)f, dI, R, (__half*)df, (__half*)di, S, Spad, nparts,
-                                                          part_stride);
+            df_kernel<__half><<<blocks, SCAN_THREADS, 0, st>>>((const __half*)f, dI, R, (__half*)df, (__half*)di, S, Spad, nparts,
+                                                               part_stride, scratch, nseg, seg_tokens);
             break;
         case MLSTM_DT_BF16:
-            df_kernel<__nv_bfloat16><<<BH, SCAN_THREADS, 0, st>>>((const __nv_bfloat16*)f, dI, R, (__nv_bfloat16*)df,
-                                                                 (__nv_bfloat16*)di, S, Spad, nparts, part_stride);
+            df_kernel<__nv_bfloat16><<<blocks, SCAN_THREADS, 0, st>>>((const __nv_bfloat16*)f, dI, R, (__nv_bfloat16*)df,
+                                                                      (__nv_bfloat16*)di, S, Spad, nparts, part_stride, scratch,
+                                                                      nseg, seg_tokens);
             break;
         default: return MLSTM_E_ARG;
     }

@@ -147,9 +147,10 @@ int launch_state_scan(const float* U, const float* zU, const double* An_bound, c
                       const double* summary = nullptr, void* statesT16 = nullptr, int reverse = 0);
 int launch_bwd_prep(const void* h, const void* dh, const float* b, const float* m, const float* gAn, float* gB,
                     float* gBw, float* g, void* dh16, int BH, int S, int Spad, int D, int h_dtype, int dtype, cudaStream_t st);
-// dI, R: `nparts` partial vectors each, `part_stride` floats apart (see PassParams::dot_out)
+// dI, R: `nparts` partial vectors each, `part_stride` floats apart (see PassParams::dot_out).  scratch (optional,
+// gates_scratch_bytes(BH, Spad) bytes): long slices are then scanned in segments, one block each.
 int launch_df(const void* f, const float* dI, const float* R, void* df, void* di, int BH, int S, int Spad, int dtype,
-              cudaStream_t st, int nparts = 1, long long part_stride = 0);
+              cudaStream_t st, int nparts = 1, long long part_stride = 0, double* scratch = nullptr);
 constexpr int TC_DOT_PARTS = 4;   // gate groups of the tensor-core passes
 int launch_pass_simt(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st);
 int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, cudaStream_t st);
