@@ -29,9 +29,10 @@ __global__ void identity_kernel(T16* ident, int D) {   // D x D
 // the blocks in order.  It writes the INBOUND state of every block (16-bit matrix for the tensor cores, fp32 vector;
 // skipped when `states` is null) and, optionally, the state after the last block (S_end / z_end with per-slice
 // strides, so that they can sit inside a packed record).
-// Work split: a CTA of SCAN_THREADS threads owns a patch of 32 rows x 16 columns of the matrix (thread t: row t / 4,
-// columns 4 (t % 4) .. +3), so that it writes 32 bytes per row of the row-major copy and, through a transpose in
-// shared memory, 64 bytes per row of the transposed copy (written element by element from registers, the
+// Work split: a CTA owns 512 elements of the matrix: whole rows when only the row-major copy is written; when a
+// transposed copy is wanted too, a patch of 32 rows x 16 columns (thread t: row t / 4, columns 4 (t % 4) .. +3), so
+// that it writes 32 bytes per row of the row-major copy and, through a transpose in shared memory, 64 bytes per row of
+// the transposed copy (written element by element from registers, the
 // transposed copy cost 16 times its size in memory transactions: 0.4 ms per scan at 256 blocks of 128 x 128).
 // The CTAs behind the patches own the vector.
 // late_bound (optional, per slice): a carry that became known after the gate pass, see PassParams;
@@ -55,16 +56,19 @@ state_scan_kernel(const float* __restrict__ U, const float* __restrict__ zU, con
                   T16* __restrict__ statesT, int reverse) {
     const int bh = blockIdx.y;
     const int DD = D * D;
-    const int npc = D / PATCH_COLS;
-    const int npatch = (D / PATCH_ROWS) * npc;
+    // patch shape: 32 x 16 when a transposed copy is written, else whole rows (512 consecutive elements per CTA)
+    const int pcols = statesT ? PATCH_COLS : D;
+    const int prows = 4 * SCAN_THREADS_S / pcols;
+    const int npc = D / pcols;
+    const int npatch = (D / prows) * npc;
     if (blockIdx.x == 0 && threadIdx.x == 0 && summary_dst) {
         double* dst = reinterpret_cast<double*>(reinterpret_cast<float*>(summary_dst) + bh * summary_dst_stride);
         dst[0] = summary[2 * bh];
         dst[1] = summary[2 * bh + 1];
     }
     const bool is_vec = static_cast<int>(blockIdx.x) >= npatch;     // uniform over the CTA
-    const int prow0 = (blockIdx.x / npc) * PATCH_ROWS, pcol0 = (blockIdx.x % npc) * PATCH_COLS;
-    const int lrow = threadIdx.x >> 2, lcol = (threadIdx.x & 3) * 4;
+    const int prow0 = (blockIdx.x / npc) * prows, pcol0 = (blockIdx.x % npc) * pcols;
+    const int lrow = threadIdx.x / (pcols / 4), lcol = (threadIdx.x % (pcols / 4)) * 4;
     const int off = is_vec ? ((blockIdx.x - npatch) * SCAN_THREADS_S + threadIdx.x) * 4 : (prow0 + lrow) * D + pcol0 + lcol;
     const bool valid = !is_vec || off < D;     // threads past the end still help with the factor tables and the barriers
     const size_t per_block = is_vec ? D : DD;
@@ -308,8 +312,8 @@ int launch_state_scan(const float* U, const float* zU, const double* An_bound, c
                       void* statesT16, int reverse) {
     // small CTAs: a slice has about 4 K threads of work, which should spread over all SMs
     const int threads = SCAN_THREADS_S;
-    if (D % PATCH_ROWS != 0) return MLSTM_E_SHAPE;
-    const int npatch = (D / PATCH_ROWS) * (D / PATCH_COLS);
+    if (D % PATCH_ROWS != 0 || D > 4 * threads) return MLSTM_E_SHAPE;
+    const int npatch = D * D / (4 * threads);
     dim3 grid(npatch + (D / 4 + threads - 1) / threads, BH);
     size_t s_stride = static_cast<size_t>(D) * D, z_stride = D;
     double* sum_dst = nullptr;
