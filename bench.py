@@ -395,6 +395,42 @@ def sec_wide_head(ctx):
     return out
 
 
+def sec_cfg5_train(ctx, S=65536):
+    """Configuration 5's shape with gradients: chunkwise forward + chunkwise backward through mlstm_chunkwise's autograd
+    (one GPU).  Parity: dq depends on the past only, so dq of the first 2048 positions of head 0 is compared with the
+    closed-form backward of the oracle on that prefix."""
+    torch, pkg, dev = ctx.torch, ctx.pkg, ctx.dev
+    from oracle import mlstm_oracle as orc
+    B, NH, D, L = 1, 8, 128, 256
+    host = cfg5_segment(torch, S, 1, 0)
+    g = torch.Generator().manual_seed(5)
+    dh = torch.randn(B, NH, S, D, generator=g)
+    d = {k: v.to(dev).requires_grad_(True) for k, v in host.items()}
+    dhd = dh.to(dev)
+
+    def fn():
+        for t in d.values():
+            t.grad = None
+        h = pkg.mlstm_chunkwise(d["q"], d["k"], d["v"], d["f"], d["i"], chunk_size=L)
+        h.backward(dhd)
+        return h
+    ms = time_small(ctx, fn)
+    # credited like the parallel form: 2 contractions forward, 5 backward, each intra-block (triangles) + state part
+    intra = 2 * D * (L * (L + 1) // 2) * (S // L)
+    inter = 2 * S * D * D
+    flops = (2 + 5) * (intra + inter) * B * NH
+    out = {"workload": f"chunkwise forward + backward bf16 B=1 NH=8 S={S} D=128 chunk 256 (mlstm_chunkwise autograd)", "ms": ms,
+           "value": B * S / (ms * 1e-3), "unit": "tokens/s", "roofline": roofline_tensor(ctx, flops, ms)}
+    if ctx.rank == 0:
+        fn()
+        n = 2048
+        one = {k: v[:, :1, :n] for k, v in host.items()}
+        ref = orc.matmul_backward(dh[:, :1, :n], *(one[k] for k in ("q", "k", "v", "f", "i")))
+        out["parity_max_abs_rel"] = orc.max_abs_rel(d["q"].grad[:, :1, :n].float().cpu(), ref[0])
+        out["parity_sample"] = "dq of head 0, positions [0, 2048), against the oracle's closed-form backward of that prefix"
+    return out
+
+
 def sec_cfg3(ctx):
     """The reference demo of the scan path: fp32, B=1, NH=4, S=2048, D=1024 with output gate."""
     torch, pkg, dev = ctx.torch, ctx.pkg, ctx.dev
@@ -514,7 +550,7 @@ def sec_cfg4_parity(ctx):
 
 def run_workload(args, ctx):
     """One configuration alone, printed as one line (profiler captures and ad-hoc runs)."""
-    fn = {"cfg1": sec_cfg1, "cfg2": sec_cfg2, "cfg3": sec_cfg3, "cfg5": sec_cfg5, "d512": sec_wide_head}[args.workload]
+    fn = {"cfg1": sec_cfg1, "cfg2": sec_cfg2, "cfg3": sec_cfg3, "cfg5": sec_cfg5, "d512": sec_wide_head, "cfg5train": sec_cfg5_train}[args.workload]
     sec = fn(ctx) if args.workload != "cfg5" else sec_cfg5(ctx, S=args.seq or 65536)
     if ctx.rank == 0:
         line = {"metric": args.workload + "_" + sec["unit"].replace("/", "_per_"), "value": sec["value"], "unit": sec["unit"],
@@ -536,7 +572,7 @@ def main():
     ap.add_argument("--batch", type=int, default=None,
                     help="cfg4 only: a smaller global batch of the same shape (profiler captures); the line's config says so")
     ap.add_argument("--seq", type=int, default=None, help="cfg5 only: sequence length (default 65536)")
-    ap.add_argument("--workload", default="cfg4", choices=["cfg4", "cfg5", "cfg3", "cfg2", "cfg1", "d512"],
+    ap.add_argument("--workload", default="cfg4", choices=["cfg4", "cfg5", "cfg3", "cfg2", "cfg1", "d512", "cfg5train"],
                     help="cfg4 (default, the headline); the others run one secondary configuration alone")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -721,6 +757,7 @@ def main():
                 secondary["cfg3"] = sec_cfg3(ctx)
                 secondary["cfg5_long"] = sec_cfg5(ctx, S=262144, parity=False)
                 secondary["wide_head_d512"] = sec_wide_head(ctx)
+                secondary["cfg5_train"] = sec_cfg5_train(ctx)
     sampler.stop()
 
     if rank == 0:
