@@ -54,18 +54,21 @@ constexpr int GATE = 0, APPLY = 1;
 constexpr int SIDE_NONE = 0;    // nothing
 constexpr int SIDE_OGATE = 1;   // output gate o: the row is multiplied by silu(o)
 constexpr int SIDE_DOT = 2;     // q resp. k: the row is dotted with it (the backward's R and dI vectors)
-constexpr int NTHREADS_G = 192;
+// Epilogue warps: pass 1 has eight (two per TMEM lane quarter, each taking every other 32-column chunk of the row:
+// gating 256 elements per row with four warps took as long as the tile's contraction at D = 512), pass 2 four.
+__host__ __device__ constexpr int nepi(int phase) { return phase == 0 ? 8 : 4; }
+__host__ __device__ constexpr int nthreads_g(int phase) { return 64 + 32 * nepi(phase); }
 constexpr int TN = 256;                       // columns of a work item
 constexpr int A_BYTES = 128 * 128;            // 128 rows x 128 bytes
 constexpr int B_BYTES = 256 * 128;            // pass 1: 256 key rows x 128 bytes; pass 2: TN columns x one chunk of rows
 constexpr int OUT_WARP_BYTES = 2 * 2048;      // per epilogue warp: two staging buffers of 32 rows x 64 bytes
-constexpr int NEPI = 4;                       // epilogue warps
 constexpr int ITEM_RING = 8;
 constexpr int GATE_WARP_BYTES = 2 * 4096;     // pass 2, per epilogue warp: two tiles (32 rows x 128 bytes) of the output gate
 template <bool PAIR, int PHASE>
 struct GemmCfg {
     static constexpr int B_CTA = PAIR ? B_BYTES / 2 : B_BYTES;    // this CTA's share of B per stage
     static constexpr int STAGE = A_BYTES + B_CTA;
+    static constexpr int NEPI = nepi(PHASE);
     static constexpr int IN_BYTES = PHASE == 1 ? NEPI * GATE_WARP_BYTES : 0;   // output-gate tiles of pass 2
     static constexpr int NSTAGE = PAIR ? (PHASE == 1 ? 5 : 6) : (PHASE == 1 ? 3 : 4);
     static constexpr int NBAR = 2 * NSTAGE + 4 + 2 * ITEM_RING + 2 * NEPI;
@@ -92,7 +95,7 @@ struct GemmParams {
     const double* col_ref;
     float er_add;
     const float* row_g; // [BH, Spad] added to every element of the row before the gate factor (backward), or nullptr
-    float* bpart;       // [BH, NKT, Spad] partial row sums, one per key tile, or nullptr
+    float* bpart;       // [BH, 2 NKT, Spad] partial row sums, one per key tile and epilogue warp set, or nullptr
     // pass 2
     const float* m;     // [BH, S]; nullptr: rows are not normalised (backward)
     int side;           // what the [BH, S, D] tensor behind the fourth tensor map is: SIDE_NONE, SIDE_OGATE, SIDE_DOT
@@ -119,10 +122,11 @@ __device__ __forceinline__ void bulk_wait_read() {
 // r >= c (the backward's dK and dV): the A operand is the matrix read MN-major, in the same boxes as B.
 // OUT_IN (pass 2 only): the output has the inputs' element type (gradients) instead of fp32 (h).
 template <int PHASE, int ABFMT, bool PAIR, bool TRANS = false, bool OUT_IN = false>
-__global__ void __launch_bounds__(NTHREADS_G, 1)
+__global__ void __launch_bounds__(nthreads_g(PHASE), 1)
 mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmG, const GemmParams p) {
     using G = GemmCfg<PAIR, PHASE>;
+    constexpr int NEPI = G::NEPI;
     constexpr int NSTAGE = G::NSTAGE;
     constexpr int STAGE_BYTES_G = G::STAGE;
     constexpr int NBAR_G = G::NBAR;
@@ -362,6 +366,9 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // ------------------------------------------------------------ epilogue warps
         const int r = (warp & 3) * 32 + lane;          // TMEM lane == row inside the tile (lane quarter = warp % 4)
         const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        // with eight epilogue warps two share a lane quarter: warp set e takes the chunks ch = e, e + 2, ...
+        constexpr int NSET = NEPI / 4;
+        const int eset = (warp - 2) >> 2;
         uint8_t* stage = sOut + (warp - 2) * OUT_WARP_BYTES;
         if (lane == 0) prefetch_tmap(&tmO);
         // Pass 2: the output gate o of this warp's 32 rows comes in tiles of 32 rows x 128 bytes through the copy
@@ -428,8 +435,9 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (p.row_g) g_row = p.row_g[vec_base + grow];
             } else if (p.m) {
                 float bsum = 0.0f;
-                for (int kt = 0; kt <= it.qt / 2; kt++)
-                    bsum += p.bpart[(static_cast<size_t>(it.bh) * p.NKT + kt) * p.Spad + grow];
+                constexpr int PARTS_PER_TILE = nepi(GATE) / 4;   // pass 1 wrote one partial per key tile and warp set
+                for (int kt = 0; kt < (it.qt / 2 + 1) * PARTS_PER_TILE; kt++)
+                    bsum += p.bpart[(static_cast<size_t>(it.bh) * p.NKT * PARTS_PER_TILE + kt) * p.Spad + grow];
                 const float mrow = row_ok ? p.m[static_cast<size_t>(it.bh) * p.S + grow] : 0.0f;
                 inv_n = 1.0f / (fmaxf(fabsf(bsum), __expf(-mrow)) + 1e-6f);
                 if (p.b_out && it.ct == 0 && row_ok) p.b_out[static_cast<size_t>(it.bh) * p.S + grow] = bsum;
@@ -449,9 +457,9 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     else mbar_arrive(&bar_accempty[buf]);
                 }
             };
-            if (nch == 0) release_acc();
+            if (nch <= eset) release_acc();     // (nch is a multiple of four: every warp set has chunks, or none has)
 #pragma unroll 1
-            for (int ch = 0; ch < nch; ch++) {
+            for (int ch = eset; ch < nch; ch += NSET) {
                 const int c0 = it.ct * TN + ch * 32;           // first column of the chunk (pass 1: key position)
                 float cv[32];
                 bool diag = false;
@@ -496,7 +504,7 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 uint32_t tv[32];
                 tmem_ld32(acc + ch * 32, tv);
                 tc_wait_ld();
-                if (ch == nch - 1) release_acc();   // the item after next may overwrite the accumulator
+                if (ch + NSET >= nch) release_acc();   // this warp's last chunk: the item after next may overwrite the accumulator
                 if (PHASE == GATE) {
                     if (diag) {
                         const int rel0 = c0 - it.qt * TILE;    // column index inside the diagonal tile
@@ -571,7 +579,8 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             if (side_dot && active && p.dot_out)
                 p.dot_out[it.ct * p.dot_stride + static_cast<long long>(vec_base) + grow] = row_ok ? dot : 0.0f;
             if (PHASE == GATE && active) {
-                if (p.bpart) p.bpart[(static_cast<size_t>(it.bh) * p.NKT + it.ct) * p.Spad + grow] = rowsum;
+                // one partial per key tile and warp set
+                if (p.bpart) p.bpart[(static_cast<size_t>(it.bh) * p.NKT * NSET + it.ct * NSET + eset) * p.Spad + grow] = rowsum;
                 if constexpr (PAIR) {
                     // Pass 2 contracts a pair of row tiles over the causal extent of the lower one.  For the upper tile
                     // that includes the 128 columns right of its diagonal tile, which nothing computes: they must read
@@ -581,7 +590,7 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                         for (int j4 = 0; j4 < 4; j4++) z[j4] = make_uint4(0u, 0u, 0u, 0u);
                         const int y = it.qt * TILE + (warp & 3) * 32;
-                        for (int ch = nch; ch < TN / 32; ch++) {
+                        for (int ch = nch + eset; ch < TN / 32; ch += NSET) {
                             const int c0 = it.ct * TN + ch * 32;
 #pragma unroll
                             for (int sub = 0; sub < NSUB; sub++) store64(z, c0 + sub * (64 / OUT_ES), y, it.bh);
@@ -639,7 +648,7 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     const int n = p.items < units ? p.items : units;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(PAIR ? 2 * n : n), 1, 1);
-    cfg.blockDim = dim3(NTHREADS_G, 1, 1);
+    cfg.blockDim = dim3(nthreads_g(PHASE), 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr;
@@ -858,7 +867,7 @@ int launch_scan_gemm_bwd(const ScanGemmBwdArgs& a, int dtype, cudaStream_t st) {
 
 size_t scan_gemm_bpart_bytes(int BH, int S, int dtype) {
     const size_t Spad = round_up(S, TILE);
-    return static_cast<size_t>(scan_gemm_group(BH, S, dtype)) * ((Spad + TN - 1) / TN) * Spad * sizeof(float);
+    return static_cast<size_t>(scan_gemm_group(BH, S, dtype)) * ((Spad + TN - 1) / TN) * (nepi(GATE) / 4) * Spad * sizeof(float);
 }
 
 int launch_scan_gemm(const void* q, const void* k, const void* v, const void* o, float* h, void* W, const ScanGemmArgs& a,
