@@ -34,6 +34,19 @@ def test_workspace_sizes_and_support_matrix(pkg):
     assert L.mlstm_scan_fwd_workspace(1, 4, 2048, 1024, 0, 4) > 4 * 2048 * 2048 * 4
     assert L.mlstm_scan_fwd_workspace(1, 2, 4096, 128, 2, 0) == L.mlstm_chunk_workspace(1, 2, 4096, 128, 2, 256)
     assert L.mlstm_chunk_sp_record_floats(128) == 128 * 128 + 128 + 4
+    # the chunkwise form (forward and backward) takes D = 128 and 256, 16-bit inputs
+    assert L.mlstm_chunk_workspace(1, 2, 4096, 256, 2, 256) > L.mlstm_chunk_workspace(1, 2, 4096, 128, 2, 256) > 0
+    assert L.mlstm_chunk_bwd_workspace(1, 2, 4096, 256, 2, 0, 256) > 0
+    assert L.mlstm_chunk_workspace(1, 2, 4096, 64, 2, 256) == 0 and L.mlstm_chunk_workspace(1, 2, 4096, 128, 0, 256) == 0
+    assert L.mlstm_scan_fwd_workspace(1, 2, 4096, 256, 2, 0) == L.mlstm_chunk_workspace(1, 2, 4096, 256, 2, 256)
+    # the parallel path above D = 256 (multiples of 256): two passes per direction with the gated S x S matrices in scratch;
+    # float32 inputs only where tf32 is allowed; forced CUDA-core calls need none of it
+    S, Spad = 300, 384
+    assert L.mlstm_mm_fwd_workspace(1, 2, S, 512, 2, 0) >= 2 * Spad * Spad * 2
+    assert L.mlstm_mm_fwd_workspace(1, 2, S, 512, 2, 1) < Spad * Spad * 2
+    assert L.mlstm_mm_fwd_workspace(1, 2, S, 512, 0, 0) < Spad * Spad * 4 <= L.mlstm_mm_fwd_workspace(1, 2, S, 512, 0, 4) // 2
+    assert L.mlstm_mm_bwd_workspace(1, 2, S, 512, 2, 0, 0) >= 4 * Spad * Spad * 2
+    assert L.mlstm_mm_bwd_workspace(1, 2, S, 384, 2, 2, 0) < Spad * Spad * 2   # not a multiple of 256: CUDA cores
     assert L.mlstm_tc_supported(4096, 256, 2) == 1
     assert L.mlstm_tc_supported(4096, 256, 0) == 2   # fp32: only with MLSTM_F_ALLOW_TF32
     assert L.mlstm_tc_supported(4096, 96, 2) == 0
