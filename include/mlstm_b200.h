@@ -201,7 +201,7 @@ int mlstm_chunk_bwd(const void* dh, const void* q, const void* k, const void* v,
 
 /* Sequence-parallel form of the chunkwise forward: rank r of `world` holds the r-th contiguous segment
  * of every sequence, and ONE exchange connects the ranks (the carry combine of mlstm_scan.py:15-26
- * applied to whole segments; SURVEY of the reference: no multi-GPU code exists there).
+ * applied to whole segments; the reference itself has no multi-GPU code).
  *   mlstm_chunk_sp_local   everything that needs no other rank: gates, per-block states, and this
  *                          segment's record [B*NH][mlstm_chunk_sp_record_floats(D)] fp32 =
  *                          S (D*D, key-major) | z (D) | {F_end, A_end} as two doubles; the state is
