@@ -189,6 +189,29 @@ def test_head_dimensions_above_256_take_the_two_pass_form(gc, dtype, D, S, f_mea
         assert orc.max_abs_rel(g1, g2) < TOL_16, name
 
 
+def test_two_pass_form_in_slice_groups(gc):
+    """Nine slices at S = 4096, D = 512: the backward keeps two gated matrices per slice (64 MB here), so it runs in
+    two groups of slices (eight, then one) through the same scratch, the forward in one.  Slices of both groups agree
+    with the same slice computed alone."""
+    B, NH, S, D = 1, 9, 4096, 512
+    x = gc.make_inputs(B, NH, S, D, torch.bfloat16, f_mean=3.0, qkv_scale=D ** -0.5, seed=99)
+    L = gc._lib.lib()
+    dt = gc._lib.dtype_code(x["q"])
+    assert L.mlstm_mm_bwd_workspace(B, NH, S, D, dt, 0, 0) < 700 << 20     # two matrices of eight slices, not of nine
+    h, m, b = gc.run_forward(x)
+    grads = gc.run_backward(x, h, m, b)
+    for hd in (0, 7, 8):
+        one = {n: t[:, hd:hd + 1].contiguous() for n, t in x.items()}
+        h1, m1, b1 = gc.run_forward(one)
+        assert orc.max_abs_rel(h[:, hd:hd + 1], h1) < 1e-6 and orc.max_abs_rel(b[:, hd:hd + 1], b1) < 1e-6
+        for name, g_all, g_one in zip(("dq", "dk", "dv", "df", "di"), grads, gc.run_backward(one, h1, m1, b1)):
+            assert orc.max_abs_rel(g_all[:, hd:hd + 1], g_one) < 1e-6, (hd, name)
+    # and one slice of the second group against the oracle
+    one = {n: t[:, 8:9].contiguous() for n, t in x.items()}
+    eb = gc.errors_backward(one, [g[:, 8:9] for g in grads], torch.float32)
+    assert all(v < TOL_16 for v in eb.values()), eb
+
+
 def test_tensor_core_matches_simt_on_device(gc):
     """Same 16-bit inputs through both kernel families."""
     x = gc.make_inputs(2, 2, 640, 128, torch.bfloat16, f_mean=3.0, qkv_scale=128 ** -0.5, seed=3)

@@ -40,7 +40,9 @@ __device__ __forceinline__ double block_scan_add(double x, double* warp_tot, dou
     return x + before;
 }
 
-__device__ __forceinline__ double block_scan_max(double x, double* warp_tot, double& carry_smem_view) {
+// Exclusive running maximum over the block's threads, seeded with the carry; the carry then takes the block's
+// total in.
+__device__ __forceinline__ double block_scan_max_excl(double x, double* warp_tot, double& carry_smem_view) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -48,6 +50,8 @@ __device__ __forceinline__ double block_scan_max(double x, double* warp_tot, dou
         if (lane >= o) x = fmax(x, y);
     }
     if (lane == 31) warp_tot[warp] = x;
+    double excl = __shfl_up_sync(0xffffffffu, x, 1);
+    if (lane == 0) excl = -INFINITY;
     __syncthreads();
     if (warp == 0) {
         double t = warp_tot[lane];
@@ -64,8 +68,14 @@ __device__ __forceinline__ double block_scan_max(double x, double* warp_tot, dou
     __syncthreads();
     if (threadIdx.x == 0) carry_smem_view = fmax(carry_smem_view, total);
     __syncthreads();
-    return fmax(x, before);
+    return fmax(excl, before);
 }
+
+// Four consecutive positions per thread and round (a round = 4096 positions = one segment): the two block scans,
+// with their barriers, run once per round on the threads' totals.
+constexpr int GATE_V = 4;
+static_assert(GATE_SEG_TOKENS == GATE_V * SCAN_THREADS && REF_BLOCK % GATE_V == 0 && 32 % (REF_BLOCK / GATE_V) == 0,
+              "a round is one segment; a reference block is a group of lanes inside a warp");
 
 // One block per slice.  With F = cumsum(logsigmoid f), a = i - F, A = running maximum of a (all in
 // double), it writes m = F + A and the two gate vectors in log2 units, re-centred per block of
@@ -99,61 +109,84 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
     __shared__ double wmax[32];
     __shared__ double carry_sum;
     __shared__ double carry_max;
-    __shared__ double ref_a[SCAN_THREADS / REF_BLOCK];
-    __shared__ double ref_A[SCAN_THREADS / REF_BLOCK];
     const int bh = blockIdx.x / nseg;
     const int seg = blockIdx.x - bh * nseg;
     const int t_begin = seg * seg_tokens;
     const int t_end = min(t_begin + seg_tokens, Spad);
     const int nref = Spad / REF_BLOCK;
     const int nb = chunk_len > 0 ? (S + chunk_len - 1) / chunk_len : 0;
+    constexpr int LANES_PER_REF = REF_BLOCK / GATE_V;   // 16 threads share a reference block
     if (threadIdx.x == 0) {
         carry_sum = carry_in ? carry_in[2 * blockIdx.x] : 0.0;
         carry_max = carry_in ? carry_in[2 * blockIdx.x + 1] : -INFINITY;
         if (An_bound && seg == 0) An_bound[static_cast<size_t>(bh) * (nb + 1)] = -carry_max * LOG2E_D;
     }
     __syncthreads();
-    for (int base = t_begin; base < t_end; base += SCAN_THREADS) {
-        const int t = base + threadIdx.x;
-        const bool in = t < S;
-        double lf = 0.0, iv = 0.0;
-        if (in) {
-            // logsigmoid in fp32 (relative error 1e-7 per term), summed in double
-            const float x = to_f32<T>(f[static_cast<size_t>(bh) * S + t]);
-            lf = static_cast<double>(x < 0.0f ? x - log1pf(expf(x)) : -log1pf(expf(-x)));
-            iv = static_cast<double>(to_f32<T>(i[static_cast<size_t>(bh) * S + t]));
+    for (int base = t_begin; base < t_end; base += GATE_V * SCAN_THREADS) {
+        const int t0 = base + GATE_V * threadIdx.x;     // this thread's first position (a multiple of four)
+        double F[GATE_V], a[GATE_V], A[GATE_V];
+        double run = 0.0;
+#pragma unroll
+        for (int j = 0; j < GATE_V; j++) {
+            const int t = t0 + j;
+            double lf = 0.0;
+            a[j] = 0.0;
+            if (t < S) {
+                // logsigmoid in fp32 (relative error 1e-7 per term), summed in double
+                const float x = to_f32<T>(f[static_cast<size_t>(bh) * S + t]);
+                lf = static_cast<double>(x < 0.0f ? x - log1pf(expf(x)) : -log1pf(expf(-x)));
+                a[j] = static_cast<double>(to_f32<T>(i[static_cast<size_t>(bh) * S + t]));   // i for now
+            }
+            run += lf;
+            F[j] = run;    // relative to the thread's first position
         }
-        const double F = block_scan_add(lf, wsum, carry_sum);
-        const double a = in ? iv - F : -INFINITY;
-        const double A = block_scan_max(a, wmax, carry_max);
+        const double incl = block_scan_add(run, wsum, carry_sum);   // carry + everything up to and including this thread
+        const double offs = incl - run;
+        double amax = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < GATE_V; j++) {
+            F[j] += offs;
+            a[j] = (t0 + j < S) ? a[j] - F[j] : -INFINITY;
+            amax = fmax(amax, a[j]);
+            A[j] = amax;   // running maximum inside the thread
+        }
+        const double pre = block_scan_max_excl(amax, wmax, carry_max);
+#pragma unroll
+        for (int j = 0; j < GATE_V; j++) A[j] = fmax(A[j], pre);
         // reference of a: the block's maximum (so ga_rel <= 0 and exp2(ga_rel) cannot overflow);
         // reference of -A: the block's first element, which is its maximum because A never decreases
-        double amax = a;
+        double bm = amax;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) amax = fmax(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = amax;   // wmax is free between the scans
-        if ((threadIdx.x % REF_BLOCK) == 0) ref_A[threadIdx.x / REF_BLOCK] = in ? A : 0.0;
-        __syncthreads();
-        if ((threadIdx.x % REF_BLOCK) == 0) {
-            const double bm = fmax(wmax[threadIdx.x >> 5], wmax[(threadIdx.x >> 5) + 1]);
-            ref_a[threadIdx.x / REF_BLOCK] = (bm == -INFINITY) ? 0.0 : bm;
-        }
-        __syncthreads();
-        if (t < Spad && ga_rel) {
-            const double ra = ref_a[threadIdx.x / REF_BLOCK], rA = ref_A[threadIdx.x / REF_BLOCK];
-            const float rel = in ? static_cast<float>((a - ra) * LOG2E_D) : -INFINITY;
-            ga_rel[static_cast<size_t>(bh) * Spad + t] = rel;
-            if (ga_w) ga_w[static_cast<size_t>(bh) * Spad + t] = exp2f(rel);   // in (0, 1]; 0 in the padding
-            gAn_rel[static_cast<size_t>(bh) * Spad + t] = in ? static_cast<float>((rA - A) * LOG2E_D) : 0.0f;
-            if ((threadIdx.x % REF_BLOCK) == 0) {
-                a_ref[static_cast<size_t>(bh) * nref + t / REF_BLOCK] = ra * LOG2E_D;
-                An_ref[static_cast<size_t>(bh) * nref + t / REF_BLOCK] = -rA * LOG2E_D;
+        for (int o = LANES_PER_REF / 2; o > 0; o >>= 1) bm = fmax(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+        const double ra = (bm == -INFINITY) ? 0.0 : bm;
+        const int lead = (threadIdx.x & 31) & ~(LANES_PER_REF - 1);      // lane that holds the block's first position
+        double rA = __shfl_sync(0xffffffffu, A[0], lead);
+        if (base + GATE_V * (static_cast<int>(threadIdx.x) & ~(LANES_PER_REF - 1)) >= S) rA = 0.0;   // block of pure padding
+        if (t0 < Spad && ga_rel) {
+            float rel[GATE_V], w[GATE_V], An[GATE_V];
+#pragma unroll
+            for (int j = 0; j < GATE_V; j++) {
+                const bool in = t0 + j < S;
+                rel[j] = in ? static_cast<float>((a[j] - ra) * LOG2E_D) : -INFINITY;
+                w[j] = exp2f(rel[j]);   // in (0, 1]; 0 in the padding
+                An[j] = in ? static_cast<float>((rA - A[j]) * LOG2E_D) : 0.0f;
+            }
+            const size_t vi = static_cast<size_t>(bh) * Spad + t0;    // Spad and t0 are multiples of four
+            *reinterpret_cast<float4*>(ga_rel + vi) = make_float4(rel[0], rel[1], rel[2], rel[3]);
+            if (ga_w) *reinterpret_cast<float4*>(ga_w + vi) = make_float4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<float4*>(gAn_rel + vi) = make_float4(An[0], An[1], An[2], An[3]);
+            if ((threadIdx.x & (LANES_PER_REF - 1)) == 0) {
+                a_ref[static_cast<size_t>(bh) * nref + t0 / REF_BLOCK] = ra * LOG2E_D;
+                An_ref[static_cast<size_t>(bh) * nref + t0 / REF_BLOCK] = -rA * LOG2E_D;
             }
         }
-        if (in && m) m[static_cast<size_t>(bh) * S + t] = static_cast<float>(F + A);
-        if (in && An_bound && ((t + 1) % chunk_len == 0 || t == S - 1))
-            An_bound[static_cast<size_t>(bh) * (nb + 1) + t / chunk_len + 1] = -A * LOG2E_D;
-        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < GATE_V; j++) {
+            const int t = t0 + j;
+            if (t < S && m) m[static_cast<size_t>(bh) * S + t] = static_cast<float>(F[j] + A[j]);
+            if (t < S && An_bound && ((t + 1) % chunk_len == 0 || t == S - 1))
+                An_bound[static_cast<size_t>(bh) * (nb + 1) + t / chunk_len + 1] = -A[j] * LOG2E_D;
+        }
     }
     if (threadIdx.x == 0 && summary_out) {
         summary_out[2 * blockIdx.x] = carry_sum;
