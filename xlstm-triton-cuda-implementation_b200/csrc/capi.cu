@@ -172,9 +172,9 @@ int forward_impl(const void* q, const void* k, const void* v, const void* f, con
     const int kind = pass_kind(S, D, dtype, flags, &rc);
     if (rc != MLSTM_OK) return rc;
     const int Spad = round_up(S, TILE);
-    if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
+    // (the gate pass also clears the status word and the passes' work-item counters)
     if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, m, BH, S, Spad, dtype, st, nullptr, nullptr, nullptr, 0, nullptr,
-                               w.gaw)) != MLSTM_OK)
+                               w.gaw, w.status, STATUS_WORDS)) != MLSTM_OK)
         return rc;
     const void* in[3] = {q, k, v};
     if (kind != KIND_SIMT && dtype == MLSTM_DT_F32) {
@@ -187,7 +187,7 @@ int forward_impl(const void* q, const void* k, const void* v, const void* f, con
     p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_w = w.gaw; p.col_ref = w.a_ref;
     p.er_add = -0.5f * log2f(static_cast<float>(D));
     p.out = h; p.m = m; p.b_out = b; p.ogate = o;
-    p.status = w.status; p.sched = w.status + 8;
+    p.status = w.status; p.sched = w.status + 8; p.sched_zeroed = 1;
     return run_pass(kind, FWD, p, dtype, h_dtype, st);
 }
 
@@ -202,11 +202,10 @@ int two_pass_forward(const void* q, const void* k, const void* v, const void* f,
     const int Spad = round_up(S, TILE);
     float* bpart = reinterpret_cast<float*>(extra);
     void* W = extra + al(scan_gemm_bpart_bytes(BH, S, dtype));
-    // status word and the two work-item counters of the passes in one go
-    if (cudaMemsetAsync(w.status, 0, WS_ALIGN, st) != cudaSuccess) return MLSTM_E_CUDA;
+    // the gate pass clears the status word and the work-item counters of the two passes
     int rc;
     if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, m, BH, S, Spad, dtype, st, nullptr, nullptr, nullptr, 0,
-                               nullptr, w.gaw)) != MLSTM_OK)
+                               nullptr, w.gaw, w.status, STATUS_WORDS)) != MLSTM_OK)
         return rc;
     ScanGemmArgs a{};
     a.S = S; a.Spad = Spad; a.BH = BH; a.D = D;
@@ -331,10 +330,9 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     if (mm_bwd_two_pass(S, D, dtype, flags)) {
         if (!workspace || workspace_bytes < w.bytes + two_pass_bwd_extra_bytes(BH, S, D, dtype) || !aligned16(workspace))
             return MLSTM_E_WORKSPACE;
-        // status word and the work-item counters of the five launches in one go
-        if (cudaMemsetAsync(w.status, 0, WS_ALIGN, st) != cudaSuccess) return MLSTM_E_CUDA;
+        // the gate pass clears the status word and the work-item counters of the five launches
         if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, nullptr, BH, S, Spad, dtype, st, nullptr, nullptr, nullptr,
-                                   0, nullptr, w.gaw)) != MLSTM_OK)
+                                   0, nullptr, w.gaw, w.status, STATUS_WORDS)) != MLSTM_OK)
             return rc;
         if ((rc = launch_bwd_prep(h, dh, b, m, w.gAn, w.gB, w.gBw, w.g, w.dh16, BH, S, Spad, D, h_dtype, dtype, st)) != MLSTM_OK)
             return rc;
@@ -359,9 +357,8 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     const int kind = pass_kind(S, D, dtype, flags, &rc);
     if (rc != MLSTM_OK) return rc;
 
-    if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
     if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, nullptr, BH, S, Spad, dtype, st, nullptr, nullptr, nullptr, 0,
-                               nullptr, w.gaw)) != MLSTM_OK)
+                               nullptr, w.gaw, w.status, STATUS_WORDS)) != MLSTM_OK)
         return rc;
     if ((rc = launch_bwd_prep(h, dh, b, m, w.gAn, w.gB, w.gBw, w.g, w.dh16, BH, S, Spad, D, h_dtype, dtype, st)) != MLSTM_OK)
         return rc;
@@ -376,7 +373,7 @@ int mlstm_mm_bwd(const void* dh, const void* q, const void* k, const void* v, co
     }
 
     PassParams p{};
-    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8;
+    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8; p.sched_zeroed = 1;
     p.dot_part_stride = static_cast<long long>(BH) * Spad;
     // dQ = ((dH V^T + g_r) * decay) K
     p.X = dhp; p.Y = v; p.Z = k;

@@ -370,14 +370,14 @@ int mlstm_chunk_prepare(const void* k, const void* v, const void* f, const void*
     ChunkWs w = carve(workspace, BH, S, D, chunk);
     if (!workspace || workspace_bytes < w.bytes || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (cudaMemsetAsync(w.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
+    // (the gate pass also clears the status word and the work-item counters)
     if ((rc = launch_gates_fwd(f, i, w.ga, w.gAn, w.a_ref, w.An_ref, w.m, BH, S, Spad, dtype, st, carry_in, summary_out,
-                               w.An_bound, chunk, w.gscratch, w.gaw)) != MLSTM_OK)
+                               w.An_bound, chunk, w.gscratch, w.gaw, w.status, STATUS_WORDS)) != MLSTM_OK)
         return rc;
     if ((rc = launch_identity(w.ident, D, dtype, st)) != MLSTM_OK) return rc;
     // U_k[key, value] = sum_j exp(a_j - A_end(k)) k_j[key] v_j[value];  zU_k[key] = sum_j exp(...) k_j[key]
     PassParams p{};
-    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8;
+    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8; p.sched_zeroed = 1;
     p.X = k;  // unused by STATE (the stationary operand is the identity); keeps the tensor map valid
     p.Y = k; p.Z = v;
     p.col_rel = w.ga; p.col_w = w.gaw; p.col_ref = w.a_ref;
@@ -483,14 +483,13 @@ int mlstm_chunk_bwd(const void* dh, const void* q, const void* k, const void* v,
     if (!workspace || workspace_bytes < w.bytes || !aligned16(workspace)) return MLSTM_E_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const ChunkWs& c = w.f;
-    if (cudaMemsetAsync(c.status, 0, sizeof(int), st) != cudaSuccess) return MLSTM_E_CUDA;
-    // gates and forward states, as in the forward
+    // gates and forward states, as in the forward (the gate pass also clears the status word and the work-item counters)
     if ((rc = launch_gates_fwd(f, i, c.ga, c.gAn, c.a_ref, c.An_ref, nullptr, BH, S, Spad, dtype, st, nullptr, nullptr,
-                               c.An_bound, chunk, c.gscratch, c.gaw)) != MLSTM_OK)
+                               c.An_bound, chunk, c.gscratch, c.gaw, c.status, STATUS_WORDS)) != MLSTM_OK)
         return rc;
     if ((rc = launch_identity(c.ident, D, dtype, st)) != MLSTM_OK) return rc;
     PassParams p{};
-    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = c.status; p.sched = c.status + 8;
+    p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = c.status; p.sched = c.status + 8; p.sched_zeroed = 1;
     p.chunk_tiles = chunk / TILE; p.NB = c.NB; p.An_bound = c.An_bound; p.ident = c.ident;
     p.dot_part_stride = static_cast<long long>(BH) * Spad;
     p.X = k; p.Y = k; p.Z = v;
@@ -509,8 +508,10 @@ int mlstm_chunk_bwd(const void* dh, const void* q, const void* k, const void* v,
     p.X = q; p.Y = q; p.Z = dhp;
     p.col_rel = w.gB; p.col_w = w.gBw; p.col_ref = c.An_ref;
     p.out = c.U; p.b_out = nullptr; p.state_reverse = 1;
+    p.sched_zeroed = 0;     // the second STATE pass of the call: its counter is cleared again by the launcher
     if ((rc = launch_pass_tc(STATE, p, dtype, MLSTM_DT_F32, st)) != MLSTM_OK) return rc;
     p.state_reverse = 0;
+    p.sched_zeroed = 1;
     {
         dim3 grid(c.NB, BH);
         if (dtype == MLSTM_DT_BF16)

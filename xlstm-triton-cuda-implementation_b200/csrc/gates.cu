@@ -104,9 +104,12 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
                                                                  const double* __restrict__ carry_in,
                                                                  double* __restrict__ summary_out,
                                                                  double* __restrict__ An_bound, int chunk_len, int nseg,
-                                                                 int seg_tokens) {
+                                                                 int seg_tokens, int* __restrict__ zero_words, int n_zero) {
     __shared__ double wsum[32];
     __shared__ double wmax[32];
+    // the call's status word and work-item counters start at zero: cleared here, by the call's first kernel,
+    // instead of by memsets of their own in front of every pass
+    if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < n_zero) zero_words[threadIdx.x] = 0;
     __shared__ double carry_sum;
     __shared__ double carry_max;
     const int bh = blockIdx.x / nseg;
@@ -505,23 +508,24 @@ namespace {
 template <typename T>
 int gates_launch_typed(const void* f, const void* i, float* ga, float* gA, double* a_ref, double* An_ref, float* m, int BH,
                        int S, int Spad, cudaStream_t st, const double* carry_in, double* summary_out, double* An_bound,
-                       int chunk_len, double* scratch, float* ga_w) {
+                       int chunk_len, double* scratch, float* ga_w, int* zero_words, int n_zero) {
     const int nseg = scratch ? (Spad + GATE_SEG_TOKENS - 1) / GATE_SEG_TOKENS : 1;
+    if (n_zero > SCAN_THREADS) return MLSTM_E_ARG;
     if (nseg <= 1) {
         gates_fwd_kernel<T><<<BH, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, ga, gA, ga_w, a_ref, An_ref, m, S, Spad, carry_in,
-                                                         summary_out, An_bound, chunk_len, 1, Spad);
+                                                         summary_out, An_bound, chunk_len, 1, Spad, zero_words, n_zero);
         return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
     }
     double* local = scratch;                                         // [BH * nseg][2]
     double* seg_carry = scratch + static_cast<size_t>(BH) * nseg * 2;  // [BH * nseg][2]
     gates_fwd_kernel<T><<<BH * nseg, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, nullptr, nullptr, nullptr, nullptr, nullptr,
                                                             nullptr, S, Spad, nullptr, local, nullptr, 0, nseg,
-                                                            GATE_SEG_TOKENS);
+                                                            GATE_SEG_TOKENS, zero_words, n_zero);
     gates_fold_kernel<<<(BH + 127) / 128, 128, 0, st>>>(local, carry_in, seg_carry, summary_out, BH, nseg);
     if (ga || m || An_bound)
         gates_fwd_kernel<T><<<BH * nseg, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, ga, gA, ga_w, a_ref, An_ref, m, S, Spad,
                                                                 seg_carry, nullptr, An_bound, chunk_len, nseg,
-                                                                GATE_SEG_TOKENS);
+                                                                GATE_SEG_TOKENS, nullptr, 0);
     return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 }  // namespace
@@ -533,17 +537,17 @@ size_t gates_scratch_bytes(int BH, int Spad) {
 
 int launch_gates_fwd(const void* f, const void* i, float* ga, float* gA, double* a_ref, double* An_ref, float* m, int BH,
                      int S, int Spad, int dtype, cudaStream_t st, const double* carry_in, double* summary_out,
-                     double* An_bound, int chunk_len, double* scratch, float* ga_w) {
+                     double* An_bound, int chunk_len, double* scratch, float* ga_w, int* zero_words, int n_zero) {
     switch (dtype) {
         case MLSTM_DT_F32:
             return gates_launch_typed<float>(f, i, ga, gA, a_ref, An_ref, m, BH, S, Spad, st, carry_in, summary_out, An_bound,
-                                             chunk_len, scratch, ga_w);
+                                             chunk_len, scratch, ga_w, zero_words, n_zero);
         case MLSTM_DT_F16:
             return gates_launch_typed<__half>(f, i, ga, gA, a_ref, An_ref, m, BH, S, Spad, st, carry_in, summary_out, An_bound,
-                                              chunk_len, scratch, ga_w);
+                                              chunk_len, scratch, ga_w, zero_words, n_zero);
         case MLSTM_DT_BF16:
             return gates_launch_typed<__nv_bfloat16>(f, i, ga, gA, a_ref, An_ref, m, BH, S, Spad, st, carry_in, summary_out,
-                                                     An_bound, chunk_len, scratch, ga_w);
+                                                     An_bound, chunk_len, scratch, ga_w, zero_words, n_zero);
     }
     return MLSTM_E_ARG;
 }

@@ -90,6 +90,7 @@ struct PassParams {
     const double* late_bound;
     int* status;         // device word; a kernel that gave up on a wait stores a non-zero code
     int* sched;          // tensor-core passes: 12 device words, one work-item counter per pass mode
+    int sched_zeroed;    // the counters were cleared by an earlier kernel of the call (else the launcher clears its own)
     int slice_set;       // tensor-core passes: slices interleaved in the work-item order (set by the launcher)
 };
 
@@ -135,7 +136,10 @@ int note_cuda_error(cudaError_t err, const char* where);
 int launch_gates_fwd(const void* f, const void* i, float* ga_rel, float* gAn_rel, double* a_ref, double* An_ref, float* m,
                      int BH, int S, int Spad, int dtype, cudaStream_t st, const double* carry_in = nullptr,
                      double* summary_out = nullptr, double* An_bound = nullptr, int chunk_len = 0,
-                     double* scratch = nullptr, float* ga_w = nullptr);
+                     double* scratch = nullptr, float* ga_w = nullptr, int* zero_words = nullptr, int n_zero = 0);
+// zero_words / n_zero: device words the gate pass clears (the call's status block: status word and the work-item
+// counters of the passes that follow; STATUS_WORDS covers them all)
+constexpr int STATUS_WORDS = 64;
 // bytes of `scratch` that let launch_gates_fwd cut long slices into segments (0: not worth it)
 size_t gates_scratch_bytes(int BH, int Spad);
 // chunk.cu

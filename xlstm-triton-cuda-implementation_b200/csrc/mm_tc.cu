@@ -1013,8 +1013,10 @@ int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
     if (sms <= 0) return MLSTM_E_CUDA;
     const unsigned grid = static_cast<unsigned>(total < sms ? total : sms);  // persistent: one CTA per SM
     if (!p.sched) return MLSTM_E_ARG;
-    ce = cudaMemsetAsync(p.sched + MODE, 0, sizeof(int), st);  // this pass's item counter
-    if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
+    if (!p.sched_zeroed) {
+        ce = cudaMemsetAsync(p.sched + MODE, 0, sizeof(int), st);  // this pass's item counter
+        if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
+    }
     kern<<<grid, NTHREADS, smem, st>>>(mx, my, mz, mi, ms, mo, p);
     ce = cudaGetLastError();
     return ce == cudaSuccess ? MLSTM_OK : note_cuda_error(ce, "launch of mlstm_tc_pass");

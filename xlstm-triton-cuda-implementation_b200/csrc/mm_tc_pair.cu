@@ -633,8 +633,11 @@ int launch_pair_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
     if (total > 0x3fffffffLL) return MLSTM_E_SHAPE;
     const unsigned npairs = static_cast<unsigned>(total < pairs_resident ? total : pairs_resident);
     if (!p.sched) return MLSTM_E_ARG;
-    cudaError_t ce = cudaMemsetAsync(p.sched + MODE, 0, sizeof(int), st);
-    if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
+    cudaError_t ce = cudaSuccess;
+    if (!p.sched_zeroed) {
+        ce = cudaMemsetAsync(p.sched + MODE, 0, sizeof(int), st);
+        if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
+    }
     kern<<<2 * npairs, NTHREADS, SMEM_BYTES, st>>>(mx, myh, mz, mo, p);
     ce = cudaGetLastError();
     return ce == cudaSuccess ? MLSTM_OK : note_cuda_error(ce, "launch of mlstm_tc_pass_pair");

@@ -672,7 +672,7 @@ inline bool use_pairs(int Spad) { return Spad > TILE && tc_sm_count() >= 2; }
 template <int ABFMT, bool PAIR>
 int run_group(const void* q, const void* k, const void* v, const void* o, float* h, void* W, const ScanGemmArgs& a, int bh0,
               int nbh, int dtype, cudaStream_t st) {
-    const bool zero_counters = bh0 > 0;   // the caller zeroed both counters with the status word for the first group
+    const bool zero_counters = bh0 > 0;   // the gate pass cleared both counters with the status word for the first group
     const size_t es = dtype == MLSTM_DT_F32 ? 4 : 2;
     const size_t slice = static_cast<size_t>(a.S) * a.D;
     const uint8_t* qg = static_cast<const uint8_t*>(q) + bh0 * slice * es;
@@ -762,19 +762,20 @@ int run_group_bwd(const ScanGemmBwdArgs& a, int bh0, int nbh, int dtype, cudaStr
     CUtensorMap ma, mb, mo, mg;
     int launch = 0;
     auto counter = [&]() { p.counter = a.counters + launch++; };
+    const bool zero_counters = bh0 > 0;   // the gate pass cleared the five counters with the status word for the first group
     // ---- pass 1: Wn = gate(Q K^T), dT = gate(dH V^T + g)
     p.items = p.per_head * nbh;
     if ((rc = tc_make_map(&ma, at(a.q), nbh, a.S, a.D, dtype, false, 128)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map(&mb, at(a.k), nbh, a.S, a.D, dtype, false, PAIR ? TN / 2 : TN)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map_out(&mo, a.Wn, nbh, a.Spad, a.Spad, dtype, 32)) != MLSTM_OK) return rc;
     counter();
-    if ((rc = launch_gemm<GATE, ABFMT, PAIR>(ma, mb, mo, mo, p, true, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gemm<GATE, ABFMT, PAIR>(ma, mb, mo, mo, p, zero_counters, st)) != MLSTM_OK) return rc;
     p.row_g = a.g + vec0;
     if ((rc = tc_make_map(&ma, at(a.dh), nbh, a.S, a.D, dtype, false, 128)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map(&mb, at(a.v), nbh, a.S, a.D, dtype, false, PAIR ? TN / 2 : TN)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map_out(&mo, a.dT, nbh, a.Spad, a.Spad, dtype, 32)) != MLSTM_OK) return rc;
     counter();
-    if ((rc = launch_gemm<GATE, ABFMT, PAIR>(ma, mb, mo, mo, p, true, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gemm<GATE, ABFMT, PAIR>(ma, mb, mo, mo, p, zero_counters, st)) != MLSTM_OK) return rc;
     p.row_g = nullptr;
     // ---- pass 2
     p.items = (PAIR ? p.NP : p.NT) * nbh * p.NVS;
@@ -786,7 +787,7 @@ int run_group_bwd(const ScanGemmBwdArgs& a, int bh0, int nbh, int dtype, cudaStr
     if ((rc = tc_make_map_out(&mo, at_out(a.dq), nbh, a.S, a.D, dtype, 32)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map(&mg, at(a.q), nbh, a.S, a.D, dtype, false, 32)) != MLSTM_OK) return rc;
     counter();
-    if ((rc = launch_gemm<APPLY, ABFMT, PAIR, false, true>(ma, mb, mo, mg, p, true, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gemm<APPLY, ABFMT, PAIR, false, true>(ma, mb, mo, mg, p, zero_counters, st)) != MLSTM_OK) return rc;
     // dK = dT^T Q, dI = k . dK
     p.dot_out = a.dI + vec0;
     if ((rc = tc_make_map_groups(&ma, a.dT, nbh, a.Spad, a.Spad, dtype, ABFMT == 2, KC, AT_GROUPS)) != MLSTM_OK) return rc;
@@ -794,7 +795,7 @@ int run_group_bwd(const ScanGemmBwdArgs& a, int bh0, int nbh, int dtype, cudaStr
     if ((rc = tc_make_map_out(&mo, at_out(a.dk), nbh, a.S, a.D, dtype, 32)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map(&mg, at(a.k), nbh, a.S, a.D, dtype, false, 32)) != MLSTM_OK) return rc;
     counter();
-    if ((rc = launch_gemm<APPLY, ABFMT, PAIR, true, true>(ma, mb, mo, mg, p, true, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gemm<APPLY, ABFMT, PAIR, true, true>(ma, mb, mo, mg, p, zero_counters, st)) != MLSTM_OK) return rc;
     // dV = Wn^T dH
     p.side = SIDE_NONE;
     p.dot_out = nullptr;
@@ -802,7 +803,7 @@ int run_group_bwd(const ScanGemmBwdArgs& a, int bh0, int nbh, int dtype, cudaStr
     if ((rc = tc_make_map_groups(&mb, at(a.dh), nbh, a.S, a.D, dtype, ABFMT == 2, KC, PAIR ? GROUPS / 2 : GROUPS)) != MLSTM_OK) return rc;
     if ((rc = tc_make_map_out(&mo, at_out(a.dv), nbh, a.S, a.D, dtype, 32)) != MLSTM_OK) return rc;
     counter();
-    return launch_gemm<APPLY, ABFMT, PAIR, true, true>(ma, mb, mo, mo, p, true, st);
+    return launch_gemm<APPLY, ABFMT, PAIR, true, true>(ma, mb, mo, mo, p, zero_counters, st);
 }
 
 template <int ABFMT>
