@@ -564,6 +564,31 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             const bool state_step = is_state_step(t);
             const int st = state_step ? 0 : stream_tile(it, t);
             const bool diag = (MODE != STATE) && !state_step && (st == tile);
+            // On the diagonal tile the 32 x 32 patch of a gate group and a row quarter lies wholly on the masked side
+            // for six of the sixteen (group, quarter) pairs: those warps write zeros over their part of T and read nothing.
+            if (diag && (ROWS_ARE_Q ? (grp > (warp & 3)) : (grp < (warp & 3)))) {
+                const int sq0 = (2 * gstep + (t == 0 ? 0 : 2 * t - 1) + 1) * C::UPT - 1;
+                ok = mbar_wait_warp<SLACK_SLEEP_NS>(&bar_cons[sq0 % C::RING], (sq0 / C::RING) & 1, abort_flag, WAIT_LIMIT);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t z_tmem = tmem_T0 + buf * 128 + lane_bits + cbase;
+                if constexpr (TF32 || X3) {
+                    uint32_t zv[32];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) zv[j] = 0u;
+                    tmem_st32(z_tmem, zv);
+                } else {
+                    uint32_t zv[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) zv[j] = 0u;
+                    tmem_st16(z_tmem, zv);
+                }
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_w[buf]);
+                continue;
+            }
             // state step: the column term is the inbound normaliser vector z (a weight, not an exponent)
             // off the diagonal the column term comes as a factor exp2(ec) (see gates.cu), on the diagonal tile as
             // the exponent itself: there a masked column can lie above the row's maximum and only the sum is safe
