@@ -176,6 +176,20 @@ def test_scan_entry_takes_the_chunkwise_form_at_256(gc):
     assert orc.max_abs_rel(h, h2) < TOL_16
 
 
+def test_long_carry_at_head_dimension_256(gc):
+    """S = 16 384 at D = 256 (64 blocks of carried state, two state steps each) on one head against the recurrent
+    oracle (one step per time index), on the first block, one in the middle and the last."""
+    S, D = 16384, 256
+    x = gc.make_inputs(1, 1, S, D, torch.bfloat16, f_mean=3.0, qkv_scale=D ** -0.5, seed=66)
+    h = gc.PKG.mlstm_chunkwise(*_dev(x), chunk_size=256).cpu()
+    ref = orc.scan_forward(x["q"], x["k"], x["v"], x["f"], x["i"], torch.zeros_like(x["q"]).float() + 1.2784645,
+                           dtype=torch.float64)   # silu(1.2784645...) = 1: the gate drops out
+    ref = ref / torch.nn.functional.silu(torch.tensor(1.2784645, dtype=torch.float64))
+    for lo in (0, 31 * 256, S - 256):
+        err = orc.max_abs_rel(h[:, :, lo:lo + 256], ref[:, :, lo:lo + 256])
+        assert err < TOL_16, (lo, err)
+
+
 def test_long_context_configuration_at_its_own_size(gc):
     """Configuration 5 (S = 65 536, D = 128, bf16, chunk 256: 256 blocks of carry) on one head against the
     recurrent oracle (one step per time index), compared on the first block, two blocks in the middle and
