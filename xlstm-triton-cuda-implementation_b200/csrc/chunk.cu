@@ -21,6 +21,8 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 template <typename T16>
 __global__ void identity_kernel(T16* ident, int D) {   // D x D
+    grid_dep_wait();
+    grid_dep_launch();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx < D * D) ident[idx] = from_f32<T16>((idx / D) == (idx % D) ? 1.0f : 0.0f);
 }
@@ -53,9 +55,13 @@ state_scan_kernel(const float* __restrict__ U, const float* __restrict__ zU, con
                   float* __restrict__ zstate, float* __restrict__ S_end, float* __restrict__ z_end, size_t S_end_stride,
                   size_t z_end_stride, int NB, int D, const double* __restrict__ late_bound,
                   const double* __restrict__ summary, double* __restrict__ summary_dst, size_t summary_dst_stride,
-                  T16* __restrict__ statesT, int reverse) {
+                  T16* __restrict__ statesT, int reverse, int* __restrict__ zero_word) {
+    grid_dep_wait();
+    grid_dep_launch();
     const int bh = blockIdx.y;
     const int DD = D * D;
+    // the work-item counter of the pass that follows in the same call (its launcher then needs no memset of its own)
+    if (zero_word && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *zero_word = 0;
     // patch shape: 32 x 16 when a transposed copy is written, else whole rows (512 consecutive elements per CTA)
     const int pcols = statesT ? PATCH_COLS : D;
     const int prows = 4 * SCAN_THREADS_S / pcols;
@@ -160,6 +166,8 @@ __global__ void rvec_partial_kernel(const T16* __restrict__ q, const float* __re
                                     const double* __restrict__ An_ref, const double* __restrict__ An_bound,
                                     const float* __restrict__ g, float* __restrict__ out, int S, int Spad, int NB, int chunk,
                                     int D) {
+    grid_dep_wait();
+    grid_dep_launch();
     __shared__ float wt[RVEC_MAX_CHUNK];
     const int k = blockIdx.x, bh = blockIdx.y, d = threadIdx.x;
     const double b0 = An_bound[static_cast<size_t>(bh) * (NB + 1) + k];
@@ -192,6 +200,8 @@ __global__ void rvec_partial_kernel(const T16* __restrict__ q, const float* __re
 __global__ void sp_fold_kernel(const float* __restrict__ gathered, int rank, int BH, int D, size_t rec_stride,
                                float* __restrict__ S_in, float* __restrict__ z_in, double* __restrict__ late_bound,
                                double* __restrict__ carry) {
+    grid_dep_wait();
+    grid_dep_launch();
     const int bh = blockIdx.y;
     const int DD = D * D;
     const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
@@ -285,6 +295,7 @@ int launch_fwdc(const void* q, const void* k, const void* v, const void* o, void
                 int S, int Spad, int D, int dtype, int chunk, const double* late_bound, cudaStream_t st) {
     PassParams p{};
     p.S = S; p.Spad = Spad; p.BH = BH; p.D = D; p.status = w.status; p.sched = w.status + 8;
+    p.sched_zeroed = 1;   // by the state scan in front of this pass
     p.X = q; p.Y = k; p.Z = v;
     p.row_rel = w.gAn; p.row_ref = w.An_ref; p.col_rel = w.ga; p.col_w = w.gaw; p.col_ref = w.a_ref;
     p.er_add = -0.5f * log2f(static_cast<float>(D));
@@ -299,17 +310,18 @@ int launch_fwdc(const void* q, const void* k, const void* v, const void* o, void
 
 int launch_identity(void* ident, int D, int dtype, cudaStream_t st) {
     const int n = D * D;
+    cudaError_t ce;
     if (dtype == MLSTM_DT_BF16)
-        identity_kernel<__nv_bfloat16><<<(n + 255) / 256, 256, 0, st>>>(static_cast<__nv_bfloat16*>(ident), D);
+        ce = launch_plain(identity_kernel<__nv_bfloat16>, dim3((n + 255) / 256), dim3(256), 0, st, static_cast<__nv_bfloat16*>(ident), D);
     else
-        identity_kernel<__half><<<(n + 255) / 256, 256, 0, st>>>(static_cast<__half*>(ident), D);
-    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+        ce = launch_plain(identity_kernel<__half>, dim3((n + 255) / 256), dim3(256), 0, st, static_cast<__half*>(ident), D);
+    return ce == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
 int launch_state_scan(const float* U, const float* zU, const double* An_bound, const float* S_in, const float* z_in,
                       void* states16, float* zstate, float* S_end, float* z_end, int BH, int NB, int D, int dtype,
                       cudaStream_t st, const double* late_bound, float* rec, size_t rec_stride, const double* summary,
-                      void* statesT16, int reverse) {
+                      void* statesT16, int reverse, int* zero_word) {
     // small CTAs: a slice has about 4 K threads of work, which should spread over all SMs
     const int threads = SCAN_THREADS_S;
     if (D % PATCH_ROWS != 0 || D > 4 * threads) return MLSTM_E_SHAPE;
@@ -323,17 +335,16 @@ int launch_state_scan(const float* U, const float* zU, const double* An_bound, c
         sum_dst = reinterpret_cast<double*>(rec + s_stride + D);
         s_stride = z_stride = rec_stride;
     }
+    cudaError_t ce;
     if (dtype == MLSTM_DT_BF16)
-        state_scan_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(U, zU, An_bound, S_in, z_in,
-                                                                   static_cast<__nv_bfloat16*>(states16), zstate, S_end,
-                                                                   z_end, s_stride, z_stride, NB, D, late_bound, summary,
-                                                                   sum_dst, rec_stride, static_cast<__nv_bfloat16*>(statesT16),
-                                                                   reverse);
+        ce = launch_plain(state_scan_kernel<__nv_bfloat16>, grid, dim3(threads), 0, st, U, zU, An_bound, S_in, z_in,
+                        static_cast<__nv_bfloat16*>(states16), zstate, S_end, z_end, s_stride, z_stride, NB, D, late_bound, summary,
+                        sum_dst, rec_stride, static_cast<__nv_bfloat16*>(statesT16), reverse, zero_word);
     else
-        state_scan_kernel<__half><<<grid, threads, 0, st>>>(U, zU, An_bound, S_in, z_in, static_cast<__half*>(states16),
-                                                            zstate, S_end, z_end, s_stride, z_stride, NB, D, late_bound,
-                                                            summary, sum_dst, rec_stride, static_cast<__half*>(statesT16),
-                                                            reverse);
+        ce = launch_plain(state_scan_kernel<__half>, grid, dim3(threads), 0, st, U, zU, An_bound, S_in, z_in,
+                        static_cast<__half*>(states16), zstate, S_end, z_end, s_stride, z_stride, NB, D, late_bound, summary, sum_dst,
+                        rec_stride, static_cast<__half*>(statesT16), reverse, zero_word);
+    if (ce != cudaSuccess) return MLSTM_E_CUDA;
     return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
@@ -415,8 +426,9 @@ int mlstm_chunk_apply(const void* q, const void* k, const void* v, const void* o
     ChunkWs w = carve(workspace, BH, S, D, chunk);
     if (!workspace || workspace_bytes < w.bytes) return MLSTM_E_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // (the scan also clears the work-item counter of the output pass)
     if ((rc = launch_state_scan(w.U, w.zU, w.An_bound, S_in, z_in, w.states, w.zstate, S_out, z_out, BH, w.NB, D, dtype,
-                                st)) != MLSTM_OK)
+                                st, nullptr, nullptr, 0, nullptr, nullptr, 0, w.status + 8 + FWDC)) != MLSTM_OK)
         return rc;
     return launch_fwdc(q, k, v, o, h, h_dtype, w, BH, S, Spad, D, dtype, chunk, nullptr, st);
 }
@@ -515,11 +527,11 @@ int mlstm_chunk_bwd(const void* dh, const void* q, const void* k, const void* v,
     {
         dim3 grid(c.NB, BH);
         if (dtype == MLSTM_DT_BF16)
-            rvec_partial_kernel<__nv_bfloat16><<<grid, D, 0, st>>>(static_cast<const __nv_bfloat16*>(q), w.gB, c.An_ref, c.An_bound,
-                                                                  w.g, c.zU, S, Spad, c.NB, chunk, D);
+            launch_plain(rvec_partial_kernel<__nv_bfloat16>, grid, dim3(D), 0, st, static_cast<const __nv_bfloat16*>(q), w.gB, c.An_ref,
+                       c.An_bound, w.g, c.zU, S, Spad, c.NB, chunk, D);
         else
-            rvec_partial_kernel<__half><<<grid, D, 0, st>>>(static_cast<const __half*>(q), w.gB, c.An_ref, c.An_bound, w.g, c.zU,
-                                                           S, Spad, c.NB, chunk, D);
+            launch_plain(rvec_partial_kernel<__half>, grid, dim3(D), 0, st, static_cast<const __half*>(q), w.gB, c.An_ref, c.An_bound, w.g,
+                       c.zU, S, Spad, c.NB, chunk, D);
         if (cudaGetLastError() != cudaSuccess) return MLSTM_E_CUDA;
     }
     // the block recurrence in reverse: R_k [key, value] (for dV), its transpose (for dK) and r_k
@@ -600,7 +612,7 @@ int mlstm_chunk_sp_apply(const void* q, const void* k, const void* v, const void
         if (cudaGetLastError() != cudaSuccess) return MLSTM_E_CUDA;
     }
     if ((rc = launch_state_scan(w.U, w.zU, w.An_bound, w.S_in, w.z_in, w.states, w.zstate, nullptr, nullptr, BH, w.NB, D,
-                                dtype, st, w.late)) != MLSTM_OK)
+                                dtype, st, w.late, nullptr, 0, nullptr, nullptr, 0, w.status + 8 + FWDC)) != MLSTM_OK)
         return rc;
     return launch_fwdc(q, k, v, o, h, h_dtype, w, BH, S, Spad, D, dtype, chunk, w.late, st);
 }

@@ -107,6 +107,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
                                                                  int seg_tokens, int* __restrict__ zero_words, int n_zero) {
     __shared__ double wsum[32];
     __shared__ double wmax[32];
+    grid_dep_wait();
+    grid_dep_launch();
     // the call's status word and work-item counters start at zero: cleared here, by the call's first kernel,
     // instead of by memsets of their own in front of every pass
     if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < n_zero) zero_words[threadIdx.x] = 0;
@@ -202,6 +204,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
 // so a segment's prefix maximum in slice terms is A_loc - F_in.
 __global__ void gates_fold_kernel(const double* __restrict__ local, const double* __restrict__ slice_carry,
                                   double* __restrict__ seg_carry, double* __restrict__ slice_summary, int BH, int nseg) {
+    grid_dep_wait();
+    grid_dep_launch();
     const int bh = blockIdx.x * blockDim.x + threadIdx.x;
     if (bh >= BH) return;
     double F = slice_carry ? slice_carry[2 * bh] : 0.0;
@@ -231,6 +235,8 @@ __global__ void bwd_prep_kernel(const HT* __restrict__ h, const HT* __restrict__
                                 const float* __restrict__ m, const float* __restrict__ gAn_rel,
                                 float* __restrict__ gB_rel, float* __restrict__ gB_w, float* __restrict__ g,
                                 T16* __restrict__ dh16, int BH, int S, int Spad, int D, float log2_scale) {
+    grid_dep_wait();
+    grid_dep_launch();
     // A warp takes PREP_ROWS consecutive positions of one slice (Spad is a multiple of 128): all of their row
     // loads and the per-position scalars are requested before anything is used, so a warp pays the memory
     // latency once instead of twice per position.
@@ -318,6 +324,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) df_total_kernel(const float* __r
                                                                 double* __restrict__ seg_totals, int S, int Spad, int nparts,
                                                                 long long part_stride, int nseg, int seg_tokens) {
     __shared__ double wsum[32];
+    grid_dep_wait();
+    grid_dep_launch();
     const int bh = blockIdx.x / nseg, seg = blockIdx.x - bh * nseg;
     const int t_begin = seg * seg_tokens, t_end = min(t_begin + seg_tokens, S);
     double x = 0.0;
@@ -345,6 +353,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) df_kernel(const T* __restrict__ 
                                                           int nseg, int seg_tokens) {
     __shared__ double wsum[32];
     __shared__ double carry_sum;
+    grid_dep_wait();
+    grid_dep_launch();
     const int bh = blockIdx.x / nseg, seg = blockIdx.x - bh * nseg;
     const int t_begin = seg * seg_tokens, t_end = min(t_begin + seg_tokens, S);
     if (threadIdx.x == 0) {
@@ -427,6 +437,8 @@ static int ogate_dispatch(const void* dh, const void* h_inner, const void* o, vo
 // Round fp32 values to the nearest tf32 (10 mantissa bits).  The tensor cores drop the low 13 bits
 // of fp32 operands; rounding first halves the error and removes its bias.
 __global__ void round_tf32_kernel(const float4* __restrict__ in, float4* __restrict__ out, long long n4) {
+    grid_dep_wait();
+    grid_dep_launch();
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= n4) return;
     const float4 x = in[idx];
@@ -446,6 +458,8 @@ struct SplitPtrs {
     __nv_bfloat16* out[4];
 };
 __global__ void split_bf16_kernel(const SplitPtrs ptrs, long long n4, int D) {
+    grid_dep_wait();
+    grid_dep_launch();
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= n4) return;
     const float4* __restrict__ in = ptrs.in[blockIdx.y];
@@ -478,8 +492,8 @@ int launch_split_bf16_multi(const void* const* in, void* const* out, int count, 
         ptrs.in[k] = static_cast<const float4*>(in[k]);
         ptrs.out[k] = static_cast<__nv_bfloat16*>(out[k]);
     }
-    split_bf16_kernel<<<dim3(static_cast<unsigned>(blocks), count), threads, 0, st>>>(ptrs, n4, D);
-    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+    return launch_plain(split_bf16_kernel, dim3(static_cast<unsigned>(blocks), count), dim3(threads), 0, st, ptrs, n4, D) == cudaSuccess
+               ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
 int launch_split_bf16(const void* in, void* out, long long rows, int D, cudaStream_t st) {
@@ -500,8 +514,8 @@ int launch_round_tf32(const void* in, void* out, long long n, cudaStream_t st) {
     const int threads = 256;
     const long long blocks = (n4 + threads - 1) / threads;
     if (blocks > 0x7fffffffLL || (n & 3)) return MLSTM_E_SHAPE;
-    round_tf32_kernel<<<(unsigned)blocks, threads, 0, st>>>(static_cast<const float4*>(in), static_cast<float4*>(out), n4);
-    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+    return launch_plain(round_tf32_kernel, dim3((unsigned)blocks), dim3(threads), 0, st, static_cast<const float4*>(in),
+                      static_cast<float4*>(out), n4) == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
 namespace {
@@ -512,21 +526,26 @@ int gates_launch_typed(const void* f, const void* i, float* ga, float* gA, doubl
     const int nseg = scratch ? (Spad + GATE_SEG_TOKENS - 1) / GATE_SEG_TOKENS : 1;
     if (n_zero > SCAN_THREADS) return MLSTM_E_ARG;
     if (nseg <= 1) {
-        gates_fwd_kernel<T><<<BH, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, ga, gA, ga_w, a_ref, An_ref, m, S, Spad, carry_in,
-                                                         summary_out, An_bound, chunk_len, 1, Spad, zero_words, n_zero);
-        return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+        return launch_plain(gates_fwd_kernel<T>, dim3(BH), dim3(SCAN_THREADS), 0, st, (const T*)f, (const T*)i, ga, gA, ga_w, a_ref, An_ref,
+                          m, S, Spad, carry_in, summary_out, An_bound, chunk_len, 1, Spad, zero_words, n_zero) == cudaSuccess
+                   ? MLSTM_OK : MLSTM_E_CUDA;
     }
     double* local = scratch;                                         // [BH * nseg][2]
     double* seg_carry = scratch + static_cast<size_t>(BH) * nseg * 2;  // [BH * nseg][2]
-    gates_fwd_kernel<T><<<BH * nseg, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, nullptr, nullptr, nullptr, nullptr, nullptr,
-                                                            nullptr, S, Spad, nullptr, local, nullptr, 0, nseg,
-                                                            GATE_SEG_TOKENS, zero_words, n_zero);
-    gates_fold_kernel<<<(BH + 127) / 128, 128, 0, st>>>(local, carry_in, seg_carry, summary_out, BH, nseg);
-    if (ga || m || An_bound)
-        gates_fwd_kernel<T><<<BH * nseg, SCAN_THREADS, 0, st>>>((const T*)f, (const T*)i, ga, gA, ga_w, a_ref, An_ref, m, S, Spad,
-                                                                seg_carry, nullptr, An_bound, chunk_len, nseg,
-                                                                GATE_SEG_TOKENS, nullptr, 0);
-    return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
+    // (typed null pointers for the summary-only launch: the launcher converts arguments to the kernel's parameter types)
+    float* nof = nullptr;
+    double* nod = nullptr;
+    const double* nocd = nullptr;
+    int* noi = nullptr;
+    cudaError_t ce = launch_plain(gates_fwd_kernel<T>, dim3(BH * nseg), dim3(SCAN_THREADS), 0, st, (const T*)f, (const T*)i, nof, nof, nof,
+                                nod, nod, nof, S, Spad, nocd, local, nod, 0, nseg, GATE_SEG_TOKENS, zero_words, n_zero);
+    if (ce == cudaSuccess)
+        ce = launch_plain(gates_fold_kernel, dim3((BH + 127) / 128), dim3(128), 0, st, (const double*)local, carry_in, seg_carry,
+                        summary_out, BH, nseg);
+    if (ce == cudaSuccess && (ga || m || An_bound))
+        ce = launch_plain(gates_fwd_kernel<T>, dim3(BH * nseg), dim3(SCAN_THREADS), 0, st, (const T*)f, (const T*)i, ga, gA, ga_w, a_ref,
+                        An_ref, m, S, Spad, (const double*)seg_carry, nod, An_bound, chunk_len, nseg, GATE_SEG_TOKENS, noi, 0);
+    return ce == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 }  // namespace
 
@@ -561,10 +580,10 @@ static int bwd_prep_dispatch(const void* h, const void* dh, const float* b, cons
     if (blocks > 0x7fffffffLL) return MLSTM_E_SHAPE;
     const float log2_scale = -0.5f * log2f(static_cast<float>(D));
     if (dtype == MLSTM_DT_BF16)
-        bwd_prep_kernel<HT, __nv_bfloat16><<<(unsigned)blocks, threads, 0, st>>>(
+        launch_plain(bwd_prep_kernel<HT, __nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, st, 
             (const HT*)h, (const HT*)dh, b, m, gA, gB, gBw, g, (__nv_bfloat16*)dh16, BH, S, Spad, D, log2_scale);
     else
-        bwd_prep_kernel<HT, __half><<<(unsigned)blocks, threads, 0, st>>>((const HT*)h, (const HT*)dh, b, m, gA, gB, gBw, g,
+        launch_plain(bwd_prep_kernel<HT, __half>, dim3((unsigned)blocks), dim3(threads), 0, st, (const HT*)h, (const HT*)dh, b, m, gA, gB, gBw, g,
                                                                          (__half*)dh16, BH, S, Spad, D, log2_scale);
     return cudaGetLastError() == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
@@ -586,21 +605,20 @@ int launch_df(const void* f, const float* dI, const float* R, void* df, void* di
     const int nseg = scratch ? (S + GATE_SEG_TOKENS - 1) / GATE_SEG_TOKENS : 1;
     const int seg_tokens = nseg > 1 ? GATE_SEG_TOKENS : S;
     if (nseg > 1)
-        df_total_kernel<<<BH * nseg, SCAN_THREADS, 0, st>>>(dI, R, scratch, S, Spad, nparts, part_stride, nseg, seg_tokens);
+        launch_plain(df_total_kernel, dim3(BH * nseg), dim3(SCAN_THREADS), 0, st, dI, R, scratch, S, Spad, nparts, part_stride, nseg, seg_tokens);
     const int blocks = BH * nseg;
     switch (dtype) {
         case MLSTM_DT_F32:
-            df_kernel<float><<<blocks, SCAN_THREADS, 0, st>>>((const float*)f, dI, R, (float*)df, (float*)di, S, Spad, nparts,
-                                                              part_stride, scratch, nseg, seg_tokens);
+            launch_plain(df_kernel<float>, dim3(blocks), dim3(SCAN_THREADS), 0, st, (const float*)f, dI, R, (float*)df, (float*)di, S, Spad,
+                       nparts, part_stride, (const double*)scratch, nseg, seg_tokens);
             break;
         case MLSTM_DT_F16:
-            df_kernel<__half><<<blocks, SCAN_THREADS, 0, st>>>((const __half*)f, dI, R, (__half*)df, (__half*)di, S, Spad, nparts,
-                                                               part_stride, scratch, nseg, seg_tokens);
+            launch_plain(df_kernel<__half>, dim3(blocks), dim3(SCAN_THREADS), 0, st, (const __half*)f, dI, R, (__half*)df, (__half*)di, S,
+                       Spad, nparts, part_stride, (const double*)scratch, nseg, seg_tokens);
             break;
         case MLSTM_DT_BF16:
-            df_kernel<__nv_bfloat16><<<blocks, SCAN_THREADS, 0, st>>>((const __nv_bfloat16*)f, dI, R, (__nv_bfloat16*)df,
-                                                                      (__nv_bfloat16*)di, S, Spad, nparts, part_stride, scratch,
-                                                                      nseg, seg_tokens);
+            launch_plain(df_kernel<__nv_bfloat16>, dim3(blocks), dim3(SCAN_THREADS), 0, st, (const __nv_bfloat16*)f, dI, R,
+                       (__nv_bfloat16*)df, (__nv_bfloat16*)di, S, Spad, nparts, part_stride, (const double*)scratch, nseg, seg_tokens);
             break;
         default: return MLSTM_E_ARG;
     }

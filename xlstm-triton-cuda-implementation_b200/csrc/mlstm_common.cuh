@@ -129,6 +129,37 @@ __device__ __forceinline__ bool causal_ok(int row, int col) {
     return (MODE == FWD || MODE == DQ || MODE == FWDC || MODE == DQC) ? (col <= row) : (col >= row);
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute (launch_pdl
+// below) may start while the kernel before it in the stream is still running; grid_dep_wait() returns once that kernel
+// has completed and its writes are visible (at once when the launch had no such attribute), so everything in front of
+// it must touch no global memory.  grid_dep_launch() says that the kernel after this one may be started now.  The
+// kernels of this library begin with both (the tensor-core kernels after their shared-memory / TMEM prologue), and the
+// tensor-core passes are launched this way: their launch and prologue overlap the tail of the kernel before them.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <bool PDL = true, typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = PDL ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+// The small kernels (gate pass, scans, preparation, conversions) are launched the ordinary way: launched programmatically
+// as well, their many early, waiting CTAs cost the chunkwise paths 3 to 9 % (measured).  They still begin with
+// grid_dep_launch(), so that the tensor-core pass after them starts its prologue under their tail.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_plain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    return launch_pdl<false>(kern, grid, block, smem, st, static_cast<Args&&>(args)...);
+}
+
 // Remembers the last CUDA failure of this host thread for mlstm_last_error_detail(); returns MLSTM_E_CUDA.
 int note_cuda_error(cudaError_t err, const char* where);
 
@@ -148,7 +179,7 @@ int launch_identity(void* ident, int D, int dtype, cudaStream_t st);
 int launch_state_scan(const float* U, const float* zU, const double* An_bound, const float* S_in, const float* z_in,
                       void* states16, float* zstate, float* S_end, float* z_end, int BH, int NB, int D, int dtype,
                       cudaStream_t st, const double* late_bound = nullptr, float* rec = nullptr, size_t rec_stride = 0,
-                      const double* summary = nullptr, void* statesT16 = nullptr, int reverse = 0);
+                      const double* summary = nullptr, void* statesT16 = nullptr, int reverse = 0, int* zero_word = nullptr);
 int launch_bwd_prep(const void* h, const void* dh, const float* b, const float* m, const float* gAn, float* gB,
                     float* gBw, float* g, void* dh16, int BH, int S, int Spad, int D, int h_dtype, int dtype, cudaStream_t st);
 // dI, R: `nparts` partial vectors each, `part_stride` floats apart (see PassParams::dot_out).  scratch (optional,

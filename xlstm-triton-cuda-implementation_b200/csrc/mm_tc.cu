@@ -139,6 +139,7 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
     if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base; never seen otherwise
+        grid_dep_wait();
         if (threadIdx.x == 0) atomicExch(p.status, 2000);
         return;
     }
@@ -240,6 +241,10 @@ mlstm_tc_pass(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_T0 = tmem_base;
     const uint32_t tmem_ACC = tmem_base + 256;
+    // Nothing above touched global memory: with a programmatic launch it ran under the tail of the kernel before this one
+    // in the stream.  From here on that kernel's results (gate vectors, counters, earlier passes' outputs) are needed.
+    grid_dep_wait();
+    grid_dep_launch();
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -1042,8 +1047,8 @@ int launch_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
         ce = cudaMemsetAsync(p.sched + MODE, 0, sizeof(int), st);  // this pass's item counter
         if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
     }
-    kern<<<grid, NTHREADS, smem, st>>>(mx, my, mz, mi, ms, mo, p);
-    ce = cudaGetLastError();
+    ce = launch_pdl(kern, dim3(grid), dim3(NTHREADS), smem, st, mx, my, mz, mi, ms, mo, p);
+    if (ce != cudaSuccess) cudaGetLastError();
     return ce == cudaSuccess ? MLSTM_OK : note_cuda_error(ce, "launch of mlstm_tc_pass");
 }
 

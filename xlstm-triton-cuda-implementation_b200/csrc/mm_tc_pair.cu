@@ -151,6 +151,9 @@ mlstm_tc_pass_pair(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_T0 = tmem_base;
     const uint32_t tmem_ACC = tmem_base + 256;
+    // nothing above touched global memory (see grid_dep_wait in mlstm_common.cuh)
+    grid_dep_wait();
+    grid_dep_launch();
 
     // Work items cross the pair once, from the leader's producer to the follower's (an ordinary shared-memory word
     // written remotely: cluster-scope release / acquire, which costs a thousand cycles and more); each producer
@@ -638,8 +641,8 @@ int launch_pair_one(const PassParams& p_in, int in_dtype, cudaStream_t st) {
         ce = cudaMemsetAsync(p.sched + MODE, 0, sizeof(int), st);
         if (ce != cudaSuccess) return note_cuda_error(ce, "cudaMemsetAsync(item counter)");
     }
-    kern<<<2 * npairs, NTHREADS, SMEM_BYTES, st>>>(mx, myh, mz, mo, p);
-    ce = cudaGetLastError();
+    ce = launch_pdl(kern, dim3(2 * npairs), dim3(NTHREADS), SMEM_BYTES, st, mx, myh, mz, mo, p);
+    if (ce != cudaSuccess) cudaGetLastError();
     return ce == cudaSuccess ? MLSTM_OK : note_cuda_error(ce, "launch of mlstm_tc_pass_pair");
 }
 

@@ -234,6 +234,10 @@ mlstm_scan_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if constexpr (PAIR) cluster_sync_all();   // the peer's barriers are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above (barriers, TMEM, tensor-map fetches come later) touched no global memory: it may run under the tail
+    // of the kernel before this one in the stream (the gate pass, or pass 1).  From here on that kernel's results are needed.
+    grid_dep_wait();
+    grid_dep_launch();
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -651,13 +655,15 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     cfg.blockDim = dim3(nthreads_g(PHASE), 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = PAIR ? 2 : 1;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see grid_dep_wait() in the kernel
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
     ce = cudaLaunchKernelEx(&cfg, kern, ma, mb, mo, mg, p);
     if (ce != cudaSuccess) {
         cudaGetLastError();
