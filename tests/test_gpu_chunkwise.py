@@ -190,6 +190,35 @@ def test_long_carry_at_head_dimension_256(gc):
         assert err < TOL_16, (lo, err)
 
 
+def test_chunkwise_calls_back_to_back(gc):
+    """Twenty chunkwise forward + backward calls without a synchronize in between, alternating two sequences on one
+    workspace size: equal to the same calls made alone."""
+    dev = torch.device("cuda", 0)
+    mc = importlib.import_module(PKG + ".mlstm_chunkwise")
+    sets = []
+    for seed in (3, 4):
+        x = gc.make_inputs(1, 2, 1024, 128, torch.bfloat16, f_mean=3.0, qkv_scale=128 ** -0.5, seed=seed)
+        sets.append({n: t.to(dev) for n, t in x.items()})
+    def call(d):
+        seg = mc.ChunkSegment(d["q"], d["k"], d["v"], d["f"], d["i"], 256, shared_workspace=True)
+        seg.prepare(None)
+        h = seg.apply(None)
+        m, b = seg.read_mb()
+        return (h,) + tuple(mc.mlstm_chunkwise_backward(d["dh"], d["q"], d["k"], d["v"], d["f"], d["i"], h, m, b, chunk_size=256))
+    alone = []
+    for d in sets:
+        out = call(d)
+        torch.cuda.synchronize()
+        alone.append([t.clone() for t in out])
+    last = [None, None]
+    for it in range(20):
+        last[it & 1] = call(sets[it & 1])
+    torch.cuda.synchronize()
+    for k in range(2):
+        for a, b in zip(last[k], alone[k]):
+            assert torch.equal(a, b)
+
+
 def test_long_context_configuration_at_its_own_size(gc):
     """Configuration 5 (S = 65 536, D = 128, bf16, chunk 256: 256 blocks of carry) on one head against the
     recurrent oracle (one step per time index), compared on the first block, two blocks in the middle and
