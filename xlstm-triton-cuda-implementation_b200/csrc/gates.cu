@@ -390,6 +390,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) df_kernel(const T* __restrict__ 
 template <typename HT, typename OT, bool BWD>
 __global__ void ogate_kernel(const HT* __restrict__ dh, const HT* __restrict__ h_inner, const OT* __restrict__ o,
                              HT* __restrict__ out_h, OT* __restrict__ out_o, long long n) {
+    grid_dep_wait();
+    grid_dep_launch();
     const long long base = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
     if (base >= n) return;
 #pragma unroll

@@ -17,6 +17,8 @@ constexpr int BV = 64;   // output columns per block
 
 template <int MODE, typename InT, typename OutT>
 __global__ void __launch_bounds__(256) mlstm_simt_pass(const PassParams p) {
+    grid_dep_wait();
+    grid_dep_launch();
     constexpr bool ROWS_ARE_Q = (MODE == FWD || MODE == DQ);
     // the X/Y chunks of the first contraction and the Z tile of the second are live at different
     // times and share storage
