@@ -68,7 +68,11 @@ def config_for(world, B):
 class ClockSampler:
     """SM clock and throttle-reason samples taken in-process through NVML while the timed region runs
     (two light queries every 10 ms; a polling nvidia-smi process disturbed sub-millisecond kernels)."""
-    REASONS = (("hw_slowdown", 0x8), ("sw_power_cap", 0x4), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40))
+    # NVML clocks-event bits; the last three are not throttling, but they explain a clock below the maximum
+    # (a clock limit somebody set on the device, a boost group, a display setting)
+    REASONS = (("hw_slowdown", 0x8), ("sw_power_cap", 0x4), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40),
+               ("hw_power_brake_slowdown", 0x80), ("applications_clocks_setting", 0x2), ("sync_boost", 0x10),
+               ("display_clock_setting", 0x100))
 
     def __init__(self, index):
         self.index, self.samples, self.stop_flag, self.thread = int(index), [], False, None
