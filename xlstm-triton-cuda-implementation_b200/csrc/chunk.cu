@@ -50,7 +50,7 @@ constexpr int PATCH_ROWS = 32, PATCH_COLS = 16;
 
 template <typename T16>
 __global__ void __launch_bounds__(SCAN_THREADS_S)
-state_scan_kernel(const float* __restrict__ U, const float* __restrict__ zU, const double* __restrict__ An_bound,
+state_scan_kernel(const T16* __restrict__ U, const float* __restrict__ zU, const double* __restrict__ An_bound,
                   const float* __restrict__ S_in, const float* __restrict__ z_in, T16* __restrict__ states,
                   float* __restrict__ zstate, float* __restrict__ S_end, float* __restrict__ z_end, size_t S_end_stride,
                   size_t z_end_stride, int NB, int D, const double* __restrict__ late_bound,
@@ -78,7 +78,9 @@ state_scan_kernel(const float* __restrict__ U, const float* __restrict__ zU, con
     const int off = is_vec ? ((blockIdx.x - npatch) * SCAN_THREADS_S + threadIdx.x) * 4 : (prow0 + lrow) * D + pcol0 + lcol;
     const bool valid = !is_vec || off < D;     // threads past the end still help with the factor tables and the barriers
     const size_t per_block = is_vec ? D : DD;
-    const float* src = (is_vec ? zU : U) + static_cast<size_t>(bh) * NB * per_block + off;
+    // block contributions: the matrices in the 16-bit input type (as the tensor-core pass wrote them), the vectors in fp32
+    const float* srcz = zU + static_cast<size_t>(bh) * NB * per_block + off;
+    const T16* srcU = U + static_cast<size_t>(bh) * NB * per_block + off;
     const float* init = is_vec ? z_in : S_in;
     float4 s = (init && valid) ? *reinterpret_cast<const float4*>(init + static_cast<size_t>(bh) * per_block + off)
                                : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -110,11 +112,27 @@ state_scan_kernel(const float* __restrict__ U, const float* __restrict__ zU, con
         if (is_vec && !valid) continue;
         for (int k0 = 0; k0 < tn; k0 += PF) {
             float4 u[PF];
+            if (is_vec) {     // (uniform over the CTA: the loads of either kind go out as one batch)
 #pragma unroll
-            for (int j = 0; j < PF; j++) {
-                if (k0 + j < tn) {
-                    const int kb = reverse ? NB - 1 - (t0 + k0 + j) : t0 + k0 + j;
-                    u[j] = __ldg(reinterpret_cast<const float4*>(src + static_cast<size_t>(kb) * per_block));
+                for (int j = 0; j < PF; j++) {
+                    if (k0 + j < tn) {
+                        const int kb = reverse ? NB - 1 - (t0 + k0 + j) : t0 + k0 + j;
+                        u[j] = __ldg(reinterpret_cast<const float4*>(srcz + static_cast<size_t>(kb) * per_block));
+                    }
+                }
+            } else {
+                uint2 raw[PF];
+#pragma unroll
+                for (int j = 0; j < PF; j++) {
+                    if (k0 + j < tn) {
+                        const int kb = reverse ? NB - 1 - (t0 + k0 + j) : t0 + k0 + j;
+                        raw[j] = __ldg(reinterpret_cast<const uint2*>(srcU + static_cast<size_t>(kb) * per_block));
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < PF; j++) {
+                    const T16* e4 = reinterpret_cast<const T16*>(&raw[j]);
+                    u[j] = make_float4(to_f32<T16>(e4[0]), to_f32<T16>(e4[1]), to_f32<T16>(e4[2]), to_f32<T16>(e4[3]));
                 }
             }
 #pragma unroll
@@ -236,7 +254,8 @@ __global__ void sp_fold_kernel(const float* __restrict__ gathered, int rank, int
 
 struct ChunkWs {
     int* status;
-    float *ga, *gAn, *gaw, *m, *b, *U, *zU, *zstate, *S_in, *z_in;
+    float *ga, *gAn, *gaw, *m, *b, *zU, *zstate, *S_in, *z_in;
+    void* U;          // per-block contributions to the state, 16-bit
     double *a_ref, *An_ref, *An_bound, *gscratch, *summary, *late;
     void *ident, *states;
     int NB;
@@ -268,7 +287,7 @@ ChunkWs carve(void* ws, int BH, int S, int D, int chunk) {
     const size_t gs = gates_scratch_bytes(BH, static_cast<int>(Spad));
     w.gscratch = gs ? static_cast<double*>(take(gs)) : nullptr;
     w.ident = take(static_cast<size_t>(D) * D * 2);
-    w.U = static_cast<float*>(take(nblk * D * D * sizeof(float)));
+    w.U = take(nblk * D * D * 2);
     w.zU = static_cast<float*>(take(nblk * D * sizeof(float)));
     w.states = take(nblk * D * D * 2);
     w.zstate = static_cast<float*>(take(nblk * D * sizeof(float)));
@@ -318,7 +337,7 @@ int launch_identity(void* ident, int D, int dtype, cudaStream_t st) {
     return ce == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 
-int launch_state_scan(const float* U, const float* zU, const double* An_bound, const float* S_in, const float* z_in,
+int launch_state_scan(const void* U, const float* zU, const double* An_bound, const float* S_in, const float* z_in,
                       void* states16, float* zstate, float* S_end, float* z_end, int BH, int NB, int D, int dtype,
                       cudaStream_t st, const double* late_bound, float* rec, size_t rec_stride, const double* summary,
                       void* statesT16, int reverse, int* zero_word) {
@@ -337,11 +356,11 @@ int launch_state_scan(const float* U, const float* zU, const double* An_bound, c
     }
     cudaError_t ce;
     if (dtype == MLSTM_DT_BF16)
-        ce = launch_plain(state_scan_kernel<__nv_bfloat16>, grid, dim3(threads), 0, st, U, zU, An_bound, S_in, z_in,
+        ce = launch_plain(state_scan_kernel<__nv_bfloat16>, grid, dim3(threads), 0, st, static_cast<const __nv_bfloat16*>(U), zU, An_bound, S_in, z_in,
                         static_cast<__nv_bfloat16*>(states16), zstate, S_end, z_end, s_stride, z_stride, NB, D, late_bound, summary,
                         sum_dst, rec_stride, static_cast<__nv_bfloat16*>(statesT16), reverse, zero_word);
     else
-        ce = launch_plain(state_scan_kernel<__half>, grid, dim3(threads), 0, st, U, zU, An_bound, S_in, z_in,
+        ce = launch_plain(state_scan_kernel<__half>, grid, dim3(threads), 0, st, static_cast<const __half*>(U), zU, An_bound, S_in, z_in,
                         static_cast<__half*>(states16), zstate, S_end, z_end, s_stride, z_stride, NB, D, late_bound, summary, sum_dst,
                         rec_stride, static_cast<__half*>(statesT16), reverse, zero_word);
     if (ce != cudaSuccess) return MLSTM_E_CUDA;
@@ -395,7 +414,7 @@ int mlstm_chunk_prepare(const void* k, const void* v, const void* f, const void*
     p.row_rel = w.gAn; p.row_ref = w.An_ref;  // unused by STATE
     p.out = w.U; p.b_out = w.zU;
     p.chunk_tiles = chunk / TILE; p.NB = w.NB; p.An_bound = w.An_bound; p.ident = w.ident;
-    return launch_pass_tc(STATE, p, dtype, MLSTM_DT_F32, st);
+    return launch_pass_tc(STATE, p, dtype, dtype, st);
 }
 
 int mlstm_chunk_local_state(void* workspace, size_t workspace_bytes, float* S_end, float* z_end, int B, int NH, int S,
@@ -507,7 +526,7 @@ int mlstm_chunk_bwd(const void* dh, const void* q, const void* k, const void* v,
     p.X = k; p.Y = k; p.Z = v;
     p.col_rel = c.ga; p.col_w = c.gaw; p.col_ref = c.a_ref; p.row_rel = c.gAn; p.row_ref = c.An_ref;
     p.out = c.U; p.b_out = c.zU;
-    if ((rc = launch_pass_tc(STATE, p, dtype, MLSTM_DT_F32, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_pass_tc(STATE, p, dtype, dtype, st)) != MLSTM_OK) return rc;
     // inbound states of the blocks, transposed (dQ's state step contracts over the value dimension), and z
     if ((rc = launch_state_scan(c.U, c.zU, c.An_bound, nullptr, nullptr, nullptr, c.zstate, nullptr, nullptr, BH, c.NB, D,
                                 dtype, st, nullptr, nullptr, 0, nullptr, w.statesT, 0)) != MLSTM_OK)
@@ -521,7 +540,7 @@ int mlstm_chunk_bwd(const void* dh, const void* q, const void* k, const void* v,
     p.col_rel = w.gB; p.col_w = w.gBw; p.col_ref = c.An_ref;
     p.out = c.U; p.b_out = nullptr; p.state_reverse = 1;
     p.sched_zeroed = 0;     // the second STATE pass of the call: its counter is cleared again by the launcher
-    if ((rc = launch_pass_tc(STATE, p, dtype, MLSTM_DT_F32, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_pass_tc(STATE, p, dtype, dtype, st)) != MLSTM_OK) return rc;
     p.state_reverse = 0;
     p.sched_zeroed = 1;
     {

@@ -176,7 +176,7 @@ size_t gates_scratch_bytes(int BH, int Spad);
 // chunk.cu
 int launch_identity(void* ident, int D, int dtype, cudaStream_t st);
 // rec (optional): per-slice records of rec_stride floats that receive S_end | z_end | summary {F, A} (two doubles)
-int launch_state_scan(const float* U, const float* zU, const double* An_bound, const float* S_in, const float* z_in,
+int launch_state_scan(const void* U, const float* zU, const double* An_bound, const float* S_in, const float* z_in,
                       void* states16, float* zstate, float* S_end, float* z_end, int BH, int NB, int D, int dtype,
                       cudaStream_t st, const double* late_bound = nullptr, float* rec = nullptr, size_t rec_stride = 0,
                       const double* summary = nullptr, void* statesT16 = nullptr, int reverse = 0, int* zero_word = nullptr);

@@ -1170,7 +1170,6 @@ int launch_pass_tc(int mode, const PassParams& p, int in_dtype, int out_dtype, c
             if (p.D != 128) return MLSTM_E_UNSUPPORTED;
             return launch_fmt<FWDC, 128>(p, in_dtype, out_dtype, st);
         case STATE:
-            if (out_dtype != MLSTM_DT_F32) return MLSTM_E_UNSUPPORTED;
             if (p.D == 256) return launch_fmt<STATE, 256>(p, in_dtype, out_dtype, st);
             if (p.D != 128) return MLSTM_E_UNSUPPORTED;
             return launch_fmt<STATE, 128>(p, in_dtype, out_dtype, st);
