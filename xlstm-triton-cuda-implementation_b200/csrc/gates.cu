@@ -3,6 +3,9 @@
 // maxima of the reference (mlstm_matmul.py:59, 73-84; cuda-src/gpu_utils.cuh:125-144), of its
 // db kernel (mlstm_matmul.py:132-197, reduced here to a row dot product by the identity
 // sum_c C~_rc dC_rc = n_r (dh_r . h_r)) and of its dF kernel (mlstm_matmul.py:319-333).
+#include <atomic>
+#include <cooperative_groups.h>
+
 #include "mlstm_common.cuh"
 
 namespace mlstm {
@@ -95,7 +98,11 @@ static_assert(GATE_SEG_TOKENS == GATE_V * SCAN_THREADS && REF_BLOCK % GATE_V == 
 // slice * nseg + segment; carry_in and summary_out are then per block): first a summary-only launch
 // with no carries, then gates_fold_kernel turns the segment summaries into per-segment carries, then
 // the full launch.  nseg = 1 is the plain one-block-per-slice form.
-template <typename T>
+// COOP (long slices, all segments resident at once, cooperative launch): the three steps in one kernel.  Every block
+// scans its segment with no carry, publishes the segment's {F, A} totals in coop_local, the grid meets, every block
+// folds the totals of the segments before it (carry_in and summary_out are then per SLICE) and shifts what it holds in
+// registers: F += F_in, a -= F_in, A = max(A - F_in, A_in).  One pass over f and i, one launch.
+template <typename T, bool COOP = false>
 __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __restrict__ f, const T* __restrict__ i,
                                                                  float* __restrict__ ga_rel, float* __restrict__ gAn_rel,
                                                                  float* __restrict__ ga_w,
@@ -104,9 +111,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
                                                                  const double* __restrict__ carry_in,
                                                                  double* __restrict__ summary_out,
                                                                  double* __restrict__ An_bound, int chunk_len, int nseg,
-                                                                 int seg_tokens, int* __restrict__ zero_words, int n_zero) {
+                                                                 int seg_tokens, int* __restrict__ zero_words, int n_zero,
+                                                                 double* __restrict__ coop_local) {
     __shared__ double wsum[32];
     __shared__ double wmax[32];
+    [[maybe_unused]] __shared__ double fold_in[2];
     grid_dep_wait();
     grid_dep_launch();
     // the call's status word and work-item counters start at zero: cleared here, by the call's first kernel,
@@ -122,9 +131,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
     const int nb = chunk_len > 0 ? (S + chunk_len - 1) / chunk_len : 0;
     constexpr int LANES_PER_REF = REF_BLOCK / GATE_V;   // 16 threads share a reference block
     if (threadIdx.x == 0) {
-        carry_sum = carry_in ? carry_in[2 * blockIdx.x] : 0.0;
-        carry_max = carry_in ? carry_in[2 * blockIdx.x + 1] : -INFINITY;
-        if (An_bound && seg == 0) An_bound[static_cast<size_t>(bh) * (nb + 1)] = -carry_max * LOG2E_D;
+        carry_sum = (carry_in && !COOP) ? carry_in[2 * blockIdx.x] : 0.0;
+        carry_max = (carry_in && !COOP) ? carry_in[2 * blockIdx.x + 1] : -INFINITY;
+        if (!COOP && An_bound && seg == 0) An_bound[static_cast<size_t>(bh) * (nb + 1)] = -carry_max * LOG2E_D;
     }
     __syncthreads();
     for (int base = t_begin; base < t_end; base += GATE_V * SCAN_THREADS) {
@@ -158,6 +167,41 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
         const double pre = block_scan_max_excl(amax, wmax, carry_max);
 #pragma unroll
         for (int j = 0; j < GATE_V; j++) A[j] = fmax(A[j], pre);
+        if constexpr (COOP) {
+            // (the host launches this form with one round per block: the segment is in registers)
+            if (threadIdx.x == 0) {
+                coop_local[2 * blockIdx.x] = carry_sum;       // the segment's totals, no carry
+                coop_local[2 * blockIdx.x + 1] = carry_max;
+                __threadfence();
+            }
+            cooperative_groups::this_grid().sync();
+            if (threadIdx.x == 0) {
+                double Fin = carry_in ? carry_in[2 * bh] : 0.0;
+                double Ain = carry_in ? carry_in[2 * bh + 1] : -INFINITY;
+                for (int s2 = 0; s2 < seg; s2++) {     // a position's a = i - F shifts by -F_in when F_in precedes it
+                    const double* tot = coop_local + 2 * (static_cast<size_t>(bh) * nseg + s2);
+                    Ain = fmax(Ain, tot[1] - Fin);
+                    Fin += tot[0];
+                }
+                fold_in[0] = Fin;
+                fold_in[1] = Ain;
+                if (An_bound && seg == 0) An_bound[static_cast<size_t>(bh) * (nb + 1)] = -Ain * LOG2E_D;
+                if (summary_out && seg == nseg - 1) {
+                    summary_out[2 * bh] = Fin + carry_sum;
+                    summary_out[2 * bh + 1] = fmax(Ain, carry_max - Fin);
+                }
+            }
+            __syncthreads();
+            const double Fin = fold_in[0], Ain = fold_in[1];
+            amax = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < GATE_V; j++) {
+                F[j] += Fin;
+                a[j] -= Fin;                       // (-inf in the padding stays -inf)
+                A[j] = fmax(A[j] - Fin, Ain);
+                amax = fmax(amax, a[j]);
+            }
+        }
         // reference of a: the block's maximum (so ga_rel <= 0 and exp2(ga_rel) cannot overflow);
         // reference of -A: the block's first element, which is its maximum because A never decreases
         double bm = amax;
@@ -193,7 +237,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) gates_fwd_kernel(const T* __rest
                 An_bound[static_cast<size_t>(bh) * (nb + 1) + t / chunk_len + 1] = -A[j] * LOG2E_D;
         }
     }
-    if (threadIdx.x == 0 && summary_out) {
+    if (!COOP && threadIdx.x == 0 && summary_out) {
         summary_out[2 * blockIdx.x] = carry_sum;
         summary_out[2 * blockIdx.x + 1] = carry_max;
     }
@@ -521,6 +565,23 @@ int launch_round_tf32(const void* in, void* out, long long n, cudaStream_t st) {
 }
 
 namespace {
+// Blocks of the cooperative gate kernel that can be resident on the current device at once (cached per device).
+template <typename T>
+int coop_capacity() {
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    int v = cached[dev].load(std::memory_order_acquire);
+    if (v > 0) return v;
+    int per_sm = 0, sms = 0, coop = 0;
+    if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) != cudaSuccess || !coop) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gates_fwd_kernel<T, true>, SCAN_THREADS, 0) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    v = per_sm * sms;
+    if (v > 0) cached[dev].store(v, std::memory_order_release);
+    return v;
+}
+
 template <typename T>
 int gates_launch_typed(const void* f, const void* i, float* ga, float* gA, double* a_ref, double* An_ref, float* m, int BH,
                        int S, int Spad, cudaStream_t st, const double* carry_in, double* summary_out, double* An_bound,
@@ -528,25 +589,44 @@ int gates_launch_typed(const void* f, const void* i, float* ga, float* gA, doubl
     const int nseg = scratch ? (Spad + GATE_SEG_TOKENS - 1) / GATE_SEG_TOKENS : 1;
     if (n_zero > SCAN_THREADS) return MLSTM_E_ARG;
     if (nseg <= 1) {
-        return launch_plain(gates_fwd_kernel<T>, dim3(BH), dim3(SCAN_THREADS), 0, st, (const T*)f, (const T*)i, ga, gA, ga_w, a_ref, An_ref,
-                          m, S, Spad, carry_in, summary_out, An_bound, chunk_len, 1, Spad, zero_words, n_zero) == cudaSuccess
+        return launch_plain(gates_fwd_kernel<T, false>, dim3(BH), dim3(SCAN_THREADS), 0, st, (const T*)f, (const T*)i, ga, gA, ga_w, a_ref,
+                            An_ref, m, S, Spad, carry_in, summary_out, An_bound, chunk_len, 1, Spad, zero_words, n_zero,
+                            static_cast<double*>(nullptr)) == cudaSuccess
                    ? MLSTM_OK : MLSTM_E_CUDA;
     }
     double* local = scratch;                                         // [BH * nseg][2]
+    if ((ga || m || An_bound) && BH * nseg <= coop_capacity<T>()) {
+        // all segments fit on the device at once: one cooperative launch does summaries, fold and gates
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(BH * nseg);
+        cfg.blockDim = dim3(SCAN_THREADS);
+        cfg.stream = st;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeCooperative;
+        attr.val.cooperative = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        cudaError_t ce = cudaLaunchKernelEx(&cfg, gates_fwd_kernel<T, true>, (const T*)f, (const T*)i, ga, gA, ga_w, a_ref, An_ref, m, S,
+                                            Spad, carry_in, summary_out, An_bound, chunk_len, nseg, GATE_SEG_TOKENS, zero_words, n_zero,
+                                            local);
+        if (ce == cudaSuccess) return MLSTM_OK;
+        cudaGetLastError();   // (not launched: take the three-launch path)
+    }
     double* seg_carry = scratch + static_cast<size_t>(BH) * nseg * 2;  // [BH * nseg][2]
     // (typed null pointers for the summary-only launch: the launcher converts arguments to the kernel's parameter types)
     float* nof = nullptr;
     double* nod = nullptr;
     const double* nocd = nullptr;
     int* noi = nullptr;
-    cudaError_t ce = launch_plain(gates_fwd_kernel<T>, dim3(BH * nseg), dim3(SCAN_THREADS), 0, st, (const T*)f, (const T*)i, nof, nof, nof,
-                                nod, nod, nof, S, Spad, nocd, local, nod, 0, nseg, GATE_SEG_TOKENS, zero_words, n_zero);
+    cudaError_t ce = launch_plain(gates_fwd_kernel<T, false>, dim3(BH * nseg), dim3(SCAN_THREADS), 0, st, (const T*)f, (const T*)i, nof, nof,
+                                  nof, nod, nod, nof, S, Spad, nocd, local, nod, 0, nseg, GATE_SEG_TOKENS, zero_words, n_zero, nod);
     if (ce == cudaSuccess)
         ce = launch_plain(gates_fold_kernel, dim3((BH + 127) / 128), dim3(128), 0, st, (const double*)local, carry_in, seg_carry,
                         summary_out, BH, nseg);
     if (ce == cudaSuccess && (ga || m || An_bound))
-        ce = launch_plain(gates_fwd_kernel<T>, dim3(BH * nseg), dim3(SCAN_THREADS), 0, st, (const T*)f, (const T*)i, ga, gA, ga_w, a_ref,
-                        An_ref, m, S, Spad, (const double*)seg_carry, nod, An_bound, chunk_len, nseg, GATE_SEG_TOKENS, noi, 0);
+        ce = launch_plain(gates_fwd_kernel<T, false>, dim3(BH * nseg), dim3(SCAN_THREADS), 0, st, (const T*)f, (const T*)i, ga, gA, ga_w,
+                          a_ref, An_ref, m, S, Spad, (const double*)seg_carry, nod, An_bound, chunk_len, nseg, GATE_SEG_TOKENS, noi, 0,
+                          nod);
     return ce == cudaSuccess ? MLSTM_OK : MLSTM_E_CUDA;
 }
 }  // namespace
